@@ -1,0 +1,25 @@
+// pybind11 surface of the sm_100a extension.  Each function is defined in its own .cu file.
+#include <torch/extension.h>
+
+namespace b200 {
+void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
+               bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta, bool sym,
+               c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo, int64_t nsplit);
+int64_t read_status(int64_t dev);
+void reserve_scratch(int64_t dev, int64_t nfloats);
+void cast_pad_bf16(at::Tensor src, at::Tensor hi, c10::optional<at::Tensor> lo, double scale);
+void im2col_bf16(at::Tensor x, at::Tensor out, std::vector<int64_t> kernel,
+                 std::vector<int64_t> stride, std::vector<int64_t> padding,
+                 std::vector<int64_t> dilation, bool c_major);
+}  // namespace b200
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("umma_gemm", &b200::umma_gemm, "tcgen05 TN GEMM / SYRK", py::arg("a_segs"),
+        py::arg("b_segs"), py::arg("a_kmajor"), py::arg("b_kmajor"), py::arg("C"),
+        py::arg("alpha"), py::arg("beta"), py::arg("sym"), py::arg("out_hi"), py::arg("out_lo"),
+        py::arg("nsplit"));
+  m.def("read_status", &b200::read_status);
+  m.def("reserve_scratch", &b200::reserve_scratch);
+  m.def("cast_pad_bf16", &b200::cast_pad_bf16);
+  m.def("im2col_bf16", &b200::im2col_bf16);
+}

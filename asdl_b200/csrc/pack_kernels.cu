@@ -1,0 +1,199 @@
+// Bandwidth-bound staging kernels that feed the tcgen05 GEMMs:
+//   * cast_pad_bf16  : [rows, n] fp32/bf16 -> bf16 with a TMA-legal row pitch, optional residual
+//                      ("lo") so that hi+lo carries ~16 mantissa bits.
+//   * im2col_bf16    : conv input (any strides: NCHW or channels_last) -> patch matrix
+//                      [N*Ho*Wo, ld] bf16, columns ordered (kh, kw, c) or (c, kh, kw).
+#include "host_utils.h"
+#include <cuda_bf16.h>
+
+namespace b200 {
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+template <typename T>
+__global__ void cast_pad_bf16_kernel(const T* __restrict__ src, long long lds, float scale,
+                                     __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
+                                     long long ldo, long long rows, int n) {
+  const long long total = rows * ldo;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / ldo;
+    const int c = static_cast<int>(i - r * ldo);
+    float v = (c < n) ? to_f32<T>(src[r * lds + c]) * scale : 0.f;
+    __nv_bfloat16 h = __float2bfloat16_rn(v);
+    hi[i] = h;
+    if (lo != nullptr) lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+  }
+}
+
+void cast_pad_bf16(at::Tensor src, at::Tensor hi, c10::optional<at::Tensor> lo, double scale) {
+  TORCH_CHECK(src.is_cuda() && src.dim() == 2 && src.stride(1) == 1, "src must be 2-D, unit col stride");
+  TORCH_CHECK(hi.is_cuda() && hi.scalar_type() == at::kBFloat16 && hi.dim() == 2 &&
+                  hi.is_contiguous() && hi.size(0) == src.size(0) && hi.size(1) >= src.size(1),
+              "hi must be contiguous bf16 [rows, >= n]");
+  __nv_bfloat16* lo_p = nullptr;
+  if (lo.has_value()) {
+    TORCH_CHECK(lo->sizes() == hi.sizes() && lo->is_contiguous() &&
+                    lo->scalar_type() == at::kBFloat16, "lo must match hi");
+    lo_p = reinterpret_cast<__nv_bfloat16*>(lo->data_ptr());
+  }
+  c10::cuda::CUDAGuard guard(src.get_device());
+  const long long rows = src.size(0);
+  const int n = static_cast<int>(src.size(1));
+  const long long ldo = hi.size(1);
+  const long long total = rows * ldo;
+  if (total == 0) return;
+  const int threads = 256;
+  const int blocks = static_cast<int>(std::min<long long>((total + threads - 1) / threads, 148 * 16));
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  auto* hi_p = reinterpret_cast<__nv_bfloat16*>(hi.data_ptr());
+  if (src.scalar_type() == at::kFloat) {
+    cast_pad_bf16_kernel<float><<<blocks, threads, 0, stream>>>(
+        src.data_ptr<float>(), src.stride(0), static_cast<float>(scale), hi_p, lo_p, ldo, rows, n);
+  } else if (src.scalar_type() == at::kBFloat16) {
+    cast_pad_bf16_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(src.data_ptr()), src.stride(0),
+        static_cast<float>(scale), hi_p, lo_p, ldo, rows, n);
+  } else if (src.scalar_type() == at::kHalf) {
+    cast_pad_bf16_kernel<__half><<<blocks, threads, 0, stream>>>(
+        reinterpret_cast<const __half*>(src.data_ptr()), src.stride(0), static_cast<float>(scale),
+        hi_p, lo_p, ldo, rows, n);
+  } else {
+    TORCH_CHECK(false, "unsupported source dtype");
+  }
+  B200_CUDA_CHECK(cudaGetLastError());
+}
+
+struct Im2colParams {
+  long long sN, sC, sH, sW;  // input strides in elements
+  int N, C, H, W;
+  int KH, KW, SH, SW, PH, PW, DH, DW;
+  int Ho, Wo;
+  long long ldo;   // output row pitch (elements), >= C*KH*KW
+  int c_major;     // 1: columns ordered (c, kh, kw); 0: (kh, kw, c)
+};
+
+// Scalar path: one thread per output element (coalesced along the output row).
+template <typename T>
+__global__ void im2col_generic_kernel(const T* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                      Im2colParams p) {
+  const long long rows = static_cast<long long>(p.N) * p.Ho * p.Wo;
+  const long long total = rows * p.ldo;
+  const int ncols = p.C * p.KH * p.KW;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / p.ldo;
+    const int col = static_cast<int>(i - r * p.ldo);
+    float v = 0.f;
+    if (col < ncols) {
+      int c, kh, kw;
+      if (p.c_major) {
+        c = col / (p.KH * p.KW);
+        const int t = col - c * p.KH * p.KW;
+        kh = t / p.KW;
+        kw = t - kh * p.KW;
+      } else {
+        const int t = col / p.C;
+        c = col - t * p.C;
+        kh = t / p.KW;
+        kw = t - kh * p.KW;
+      }
+      const int wo = static_cast<int>(r % p.Wo);
+      const long long t2 = r / p.Wo;
+      const int ho = static_cast<int>(t2 % p.Ho);
+      const int n = static_cast<int>(t2 / p.Ho);
+      const int hi = ho * p.SH - p.PH + kh * p.DH;
+      const int wi = wo * p.SW - p.PW + kw * p.DW;
+      if (hi >= 0 && hi < p.H && wi >= 0 && wi < p.W)
+        v = to_f32<T>(x[n * p.sN + c * p.sC + hi * p.sH + wi * p.sW]);
+    }
+    out[i] = __float2bfloat16_rn(v);
+  }
+}
+
+// Vector path: channels_last bf16 input, C % 8 == 0, (kh, kw, c) column order.  One thread moves
+// 8 channels (16 bytes) of one tap of one output pixel.
+__global__ void im2col_nhwc_vec8_kernel(const __nv_bfloat16* __restrict__ x,
+                                        __nv_bfloat16* __restrict__ out, Im2colParams p) {
+  const int c8n = p.C >> 3;
+  const int taps = p.KH * p.KW;
+  const long long rows = static_cast<long long>(p.N) * p.Ho * p.Wo;
+  const long long total = rows * taps * c8n;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c8 = static_cast<int>(i % c8n);
+    const long long t = i / c8n;
+    const int tap = static_cast<int>(t % taps);
+    const long long r = t / taps;
+    const int kh = tap / p.KW, kw = tap - kh * p.KW;
+    const int wo = static_cast<int>(r % p.Wo);
+    const long long t2 = r / p.Wo;
+    const int ho = static_cast<int>(t2 % p.Ho);
+    const int n = static_cast<int>(t2 / p.Ho);
+    const int hi = ho * p.SH - p.PH + kh * p.DH;
+    const int wi = wo * p.SW - p.PW + kw * p.DW;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (hi >= 0 && hi < p.H && wi >= 0 && wi < p.W)
+      v = *reinterpret_cast<const uint4*>(x + n * p.sN + hi * p.sH + wi * p.sW + c8 * 8);
+    *reinterpret_cast<uint4*>(out + r * p.ldo + static_cast<long long>(tap) * p.C + c8 * 8) = v;
+  }
+}
+
+// x: 4-D conv input [N, C, H, W] (logical), any memory format.  out: [N*Ho*Wo, ld] bf16, contiguous.
+void im2col_bf16(at::Tensor x, at::Tensor out, std::vector<int64_t> kernel,
+                 std::vector<int64_t> stride, std::vector<int64_t> padding,
+                 std::vector<int64_t> dilation, bool c_major) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 4, "x must be a 4-D CUDA tensor");
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == at::kBFloat16 &&
+                  out.dim() == 2, "out must be contiguous 2-D bf16");
+  Im2colParams p;
+  p.N = x.size(0); p.C = x.size(1); p.H = x.size(2); p.W = x.size(3);
+  p.sN = x.stride(0); p.sC = x.stride(1); p.sH = x.stride(2); p.sW = x.stride(3);
+  p.KH = kernel[0]; p.KW = kernel[1]; p.SH = stride[0]; p.SW = stride[1];
+  p.PH = padding[0]; p.PW = padding[1]; p.DH = dilation[0]; p.DW = dilation[1];
+  p.Ho = (p.H + 2 * p.PH - p.DH * (p.KH - 1) - 1) / p.SH + 1;
+  p.Wo = (p.W + 2 * p.PW - p.DW * (p.KW - 1) - 1) / p.SW + 1;
+  p.ldo = out.size(1);
+  p.c_major = c_major ? 1 : 0;
+  const long long rows = static_cast<long long>(p.N) * p.Ho * p.Wo;
+  TORCH_CHECK(out.size(0) == rows && p.ldo >= static_cast<long long>(p.C) * p.KH * p.KW,
+              "out has the wrong shape");
+  if (rows == 0) return;
+  c10::cuda::CUDAGuard guard(x.get_device());
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  auto* out_p = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  const int threads = 256;
+  const bool vec = !c_major && x.scalar_type() == at::kBFloat16 && p.sC == 1 && (p.C % 8) == 0 &&
+                   p.ldo == static_cast<long long>(p.C) * p.KH * p.KW && (p.sW % 8) == 0 &&
+                   (p.sH % 8) == 0 && (p.sN % 8) == 0 &&
+                   (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0;
+  if (vec) {
+    const long long total = rows * p.KH * p.KW * (p.C >> 3);
+    const int blocks = static_cast<int>(std::min<long long>((total + threads - 1) / threads, 148 * 32));
+    im2col_nhwc_vec8_kernel<<<blocks, threads, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), out_p, p);
+  } else {
+    const long long total = rows * p.ldo;
+    const int blocks = static_cast<int>(std::min<long long>((total + threads - 1) / threads, 148 * 32));
+    if (x.scalar_type() == at::kFloat)
+      im2col_generic_kernel<float><<<blocks, threads, 0, stream>>>(x.data_ptr<float>(), out_p, p);
+    else if (x.scalar_type() == at::kBFloat16)
+      im2col_generic_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+          reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), out_p, p);
+    else if (x.scalar_type() == at::kHalf)
+      im2col_generic_kernel<__half><<<blocks, threads, 0, stream>>>(
+          reinterpret_cast<const __half*>(x.data_ptr()), out_p, p);
+    else
+      TORCH_CHECK(false, "unsupported input dtype");
+  }
+  B200_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace b200

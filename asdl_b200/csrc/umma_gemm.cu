@@ -1,0 +1,178 @@
+// Host launcher for the tcgen05 TN-GEMM / SYRK kernel (see umma_gemm.cuh).
+#include "host_utils.h"
+#include "umma_gemm.cuh"
+
+namespace b200 {
+
+namespace {
+
+struct Ring {
+  size_t off = 0;
+};
+Ring g_scratch_ring[16];
+
+void check_operand(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2, name,
+              " must be a 2-D CUDA bf16 tensor");
+  TORCH_CHECK(t.stride(1) == 1, name, " must have unit stride in its last dimension");
+  TORCH_CHECK((t.stride(0) * 2) % 16 == 0, name, " row pitch must be a multiple of 16 bytes");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, name,
+              " must be 16-byte aligned");
+}
+
+bool g_attr_set = false;
+
+}  // namespace
+
+// Fills the scalar fields of a problem and encodes its tensor maps.
+void gemm_fill_problem(GemmProblem& P, const std::vector<at::Tensor>& a_segs,
+                       const std::vector<at::Tensor>& b_segs, bool a_kmajor, bool b_kmajor,
+                       const c10::optional<at::Tensor>& C, double alpha, double beta, bool sym,
+                       const c10::optional<at::Tensor>& out_hi,
+                       const c10::optional<at::Tensor>& out_lo, int64_t nsplit_req, int n_sms) {
+  const int nseg = static_cast<int>(a_segs.size());
+  TORCH_CHECK(nseg >= 1 && nseg <= 3 && b_segs.size() == a_segs.size(),
+              "between 1 and 3 operand segments are supported");
+  std::memset(&P, 0, sizeof(P));
+  const at::Tensor& a0 = a_segs[0];
+  const at::Tensor& b0 = b_segs[0];
+  const int64_t M = a_kmajor ? a0.size(0) : a0.size(1);
+  const int64_t K = a_kmajor ? a0.size(1) : a0.size(0);
+  const int64_t N = b_kmajor ? b0.size(0) : b0.size(1);
+  const int64_t Kb = b_kmajor ? b0.size(1) : b0.size(0);
+  TORCH_CHECK(K == Kb, "contraction sizes differ: ", K, " vs ", Kb);
+  for (int s = 0; s < nseg; ++s) {
+    check_operand(a_segs[s], "A");
+    check_operand(b_segs[s], "B");
+    TORCH_CHECK(a_segs[s].sizes() == a0.sizes() && b_segs[s].sizes() == b0.sizes(),
+                "all segments must have the same shape");
+    if (a_kmajor)
+      encode_tmap_bf16_2d(&P.tmA[s], a_segs[s].data_ptr(), K, M, a_segs[s].stride(0), 64, G_BM);
+    else
+      encode_tmap_bf16_2d(&P.tmA[s], a_segs[s].data_ptr(), M, K, a_segs[s].stride(0), 64, G_BK);
+    if (b_kmajor)
+      encode_tmap_bf16_2d(&P.tmB[s], b_segs[s].data_ptr(), K, N, b_segs[s].stride(0), 64, G_BN);
+    else
+      encode_tmap_bf16_2d(&P.tmB[s], b_segs[s].data_ptr(), N, K, b_segs[s].stride(0), 64, G_BK);
+  }
+  bool same_ab = sym && a_kmajor == b_kmajor;
+  for (int s = 0; s < nseg && same_ab; ++s)
+    same_ab = a_segs[s].data_ptr() == b_segs[s].data_ptr() &&
+              a_segs[s].stride(0) == b_segs[s].stride(0);
+  if (sym) TORCH_CHECK(M == N, "symmetric mode needs a square output");
+
+  P.M = static_cast<int>(M);
+  P.N = static_cast<int>(N);
+  P.K = static_cast<int>(K);
+  P.nseg = nseg;
+  P.alpha = static_cast<float>(alpha);
+  P.beta = static_cast<float>(beta);
+  P.flags = (sym ? GF_SYM : 0) | (a_kmajor ? GF_A_KMAJOR : 0) | (b_kmajor ? GF_B_KMAJOR : 0) |
+            (same_ab ? GF_SAME_AB : 0);
+  if (C.has_value()) {
+    const at::Tensor& c = *C;
+    TORCH_CHECK(c.is_cuda() && c.scalar_type() == at::kFloat && c.dim() == 2 && c.stride(1) == 1 &&
+                    c.size(0) == M && c.size(1) == N,
+                "C must be a [M, N] fp32 CUDA tensor with unit column stride");
+    P.C = c.data_ptr<float>();
+    P.Cin = P.C;
+    P.ldc = static_cast<int>(c.stride(0));
+  } else {
+    TORCH_CHECK(beta == 0.0, "beta needs C");
+  }
+  if (out_hi.has_value()) {
+    const at::Tensor& h = *out_hi;
+    TORCH_CHECK(h.is_cuda() && h.scalar_type() == at::kBFloat16 && h.dim() == 2 &&
+                    h.stride(1) == 1 && h.size(0) == M && h.size(1) >= N,
+                "out_hi must be a [M, >=N] bf16 CUDA tensor");
+    P.out_hi = reinterpret_cast<__nv_bfloat16*>(h.data_ptr());
+    P.ld_out = static_cast<int>(h.stride(0));
+    if (out_lo.has_value()) {
+      TORCH_CHECK(out_lo->sizes() == h.sizes() && out_lo->strides() == h.strides() &&
+                      out_lo->scalar_type() == at::kBFloat16,
+                  "out_lo must match out_hi");
+      P.out_lo = reinterpret_cast<__nv_bfloat16*>(out_lo->data_ptr());
+    }
+  }
+  TORCH_CHECK(P.C != nullptr || P.out_hi != nullptr, "no output given");
+
+  P.tiles_m = (P.M + G_BM - 1) / G_BM;
+  P.tiles_n = (P.N + G_BN - 1) / G_BN;
+  P.ntiles = sym ? P.tiles_m * (P.tiles_m + 1) / 2 : P.tiles_m * P.tiles_n;
+  const int kb_total = (P.K + G_BK - 1) / G_BK;
+  int nsplit = static_cast<int>(nsplit_req);
+  if (nsplit <= 0) {
+    const int target = 2 * n_sms;
+    nsplit = target / (P.ntiles > 0 ? P.ntiles : 1);
+    const int max_by_k = kb_total / 8;
+    if (nsplit > max_by_k) nsplit = max_by_k;
+    if (nsplit > 32) nsplit = 32;
+  }
+  if (nsplit > kb_total) nsplit = kb_total;
+  if (nsplit < 1) nsplit = 1;
+  P.nsplit = nsplit;
+}
+
+void gemm_attach_scratch(GemmProblem& P, int dev) {
+  DeviceState& st = device_state(dev);
+  P.status = st.status.data_ptr<int>();
+  const int slot = dev & 15;
+  if (P.nsplit > 1) {
+    const size_t need = static_cast<size_t>(P.ntiles) * P.nsplit * G_BM * G_BN;
+    const size_t cap_min = need * 4;
+    float* base = ensure_scratch(dev, cap_min);
+    const size_t cap = static_cast<size_t>(device_state(dev).scratch.numel());
+    Ring& sr = g_scratch_ring[slot];
+    if (sr.off + need > cap) sr.off = 0;
+    P.ws = base + sr.off;
+    sr.off += need;
+  }
+}
+
+void gemm_launch_single(const GemmProblem& P, cudaStream_t stream) {
+  if (!g_attr_set) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(umma_gemm_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM_BYTES));
+    g_attr_set = true;
+  }
+  dim3 grid(P.ntiles, P.nsplit, 1);
+  umma_gemm_kernel<<<grid, G_THREADS, G_SMEM_BYTES, stream>>>(P, nullptr, nullptr);
+  B200_CUDA_CHECK(cudaGetLastError());
+  if (P.nsplit > 1) {
+    dim3 rgrid(P.ntiles, 16, 1);
+    splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(P, nullptr, nullptr);
+    B200_CUDA_CHECK(cudaGetLastError());
+  }
+}
+
+// Python entry: C = alpha * A^T B (+ beta C), optionally symmetric, optionally bf16 hi/lo outputs.
+void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
+               bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta, bool sym,
+               c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
+               int64_t nsplit) {
+  TORCH_CHECK(!a_segs.empty(), "no operands");
+  const int dev = a_segs[0].get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  const int n_sms = at::cuda::getDeviceProperties(dev)->multiProcessorCount;
+  GemmProblem P;
+  gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, C, alpha, beta, sym, out_hi, out_lo,
+                    nsplit, n_sms);
+  gemm_attach_scratch(P, dev);
+  gemm_launch_single(P, at::cuda::getCurrentCUDAStream(dev).stream());
+}
+
+// Reads and clears the device status word (synchronises the current stream).
+int64_t read_status(int64_t dev) {
+  c10::cuda::CUDAGuard guard(static_cast<int>(dev));
+  DeviceState& st = device_state(static_cast<int>(dev));
+  int v = st.status.item<int>();
+  if (v != 0) st.status.zero_();
+  return v;
+}
+
+void reserve_scratch(int64_t dev, int64_t nfloats) {
+  c10::cuda::CUDAGuard guard(static_cast<int>(dev));
+  ensure_scratch(static_cast<int>(dev), static_cast<size_t>(nfloats));
+}
+
+}  // namespace b200
