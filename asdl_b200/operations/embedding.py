@@ -1,0 +1,81 @@
+"""Statistics of ``nn.Embedding``.
+
+``a`` is the integer index tensor n x *, ``g`` is n x * x d.  The A factor of the one-hot input is
+counts^T counts (V x V, only sensible for small vocabularies); per-example gradients and the
+diagonal are built with scatter-adds (one fused ``index_add_`` instead of a Python loop over
+tokens).  Parity: asdl/operations/embedding.py:7-78.
+"""
+import torch
+from torch import nn
+
+from .. import ops
+from .operation import (Operation, BASIC_OPS, OP_COV_KRON, OP_BATCH_GRADS, OP_COV_DIAG,
+                        OP_COV_DIAG_INV)
+
+__all__ = ['Embedding']
+
+
+class Embedding(Operation):
+    supported_operations = set(BASIC_OPS + [OP_COV_KRON, OP_BATCH_GRADS, 'diag', OP_COV_DIAG,
+                                            OP_COV_DIAG_INV])
+
+    @staticmethod
+    def _per_example(in_data, out_grads):
+        n = in_data.shape[0]
+        idx = in_data.reshape(n, -1)
+        g = out_grads.reshape(n, idx.shape[1], -1)
+        return idx, g
+
+    @classmethod
+    def batch_grads_weight(cls, module, in_data, out_grads):
+        """n x num_embeddings x embedding_dim (dense; intended for small vocabularies)."""
+        idx, g = cls._per_example(in_data, out_grads)
+        n, t = idx.shape
+        out = g.new_zeros(n * module.num_embeddings, module.embedding_dim)
+        rows = (idx + torch.arange(n, device=idx.device).unsqueeze(1) * module.num_embeddings)
+        out.index_add_(0, rows.reshape(-1), g.reshape(n * t, -1))
+        out = out.view(n, module.num_embeddings, module.embedding_dim)
+        if module.padding_idx is not None:
+            out[:, module.padding_idx].zero_()
+        return out
+
+    @staticmethod
+    def cov_kron_A(module, in_data):
+        n = in_data.shape[0]
+        idx = in_data.reshape(n, -1).long()
+        counts = torch.zeros(n, module.num_embeddings, device=idx.device, dtype=torch.float32)
+        counts.scatter_add_(1, idx, torch.ones_like(idx, dtype=torch.float32))
+        counts = counts.to(module.weight.device)
+        return counts.T @ counts  # V x V
+
+    @staticmethod
+    def cov_kron_B(module, out_grads):
+        return ops.gram(out_grads.reshape(-1, out_grads.shape[-1]))
+
+    @staticmethod
+    def cov_diag_weight(module, in_data, out_grads):
+        """Sum over tokens of the squared output-gradient, scattered to the looked-up rows
+        (every token counts as its own example, as in the reference)."""
+        idx = in_data.reshape(-1).long()
+        g2 = out_grads.reshape(idx.shape[0], -1).square()
+        cov = torch.zeros_like(module.weight)
+        cov.index_add_(0, idx, g2.to(cov.dtype))
+        if module.padding_idx is not None:
+            cov[module.padding_idx].zero_()
+        return cov
+
+    @staticmethod
+    def in_data_mean(module, in_data):
+        return in_data.float().mean(dim=0)
+
+    @staticmethod
+    def out_data_mean(module, out_data):
+        return out_data.reshape(-1, out_data.shape[-1]).mean(dim=0)
+
+    @staticmethod
+    def out_grads_mean(module, out_grads):
+        return out_grads.reshape(-1, out_grads.shape[-1]).mean(dim=0)
+
+    @staticmethod
+    def out_spatial_size(module, out_data):
+        return 1

@@ -1,0 +1,266 @@
+"""Numerical primitives with two implementations each:
+
+  * a plain PyTorch one (any device / dtype) that doubles as the oracle in the tests, and
+  * the library's sm_100a CUDA kernels (tcgen05 GEMM/SYRK fed by TMA, bf16 staging kernels,
+    fp32 Cholesky inverse, fused elementwise epilogues), used automatically for CUDA tensors.
+
+The CUDA path never falls back silently: if a CUDA tensor is passed and the extension cannot be
+loaded an ImportError is raised.  ``set_backend('torch')`` selects the PyTorch implementation
+explicitly (used to build reference results on the GPU).
+
+Precision policy of the tensor-core products (``set_precision``):
+  * ``'auto'``   : bf16/fp16 inputs -> one bf16 pass (fp32 accumulation);
+                   fp32 inputs      -> three bf16 passes on hi/lo splits ("bf16x3", ~2^-16 relative);
+  * ``'bf16'``   : always one pass;  ``'bf16x3'``: always three passes.
+"""
+from typing import Optional
+
+import torch
+
+from . import _build
+
+__all__ = ['gram', 'matmul_tn', 'kron_apply', 'spd_inverse', 'unitwise_inverse', 'conv_patch_gram',
+           'set_backend', 'get_backend', 'set_precision', 'get_precision', 'extension',
+           'cuda_kernels_enabled', 'check_status']
+
+_backend = 'auto'      # 'auto' | 'torch'
+_precision = 'auto'    # 'auto' | 'bf16' | 'bf16x3'
+_ext = None
+
+
+def set_backend(name: str):
+    global _backend
+    if name not in ('auto', 'torch'):
+        raise ValueError("backend has to be 'auto' or 'torch'")
+    _backend = name
+
+
+def get_backend():
+    return _backend
+
+
+def set_precision(name: str):
+    global _precision
+    if name not in ('auto', 'bf16', 'bf16x3'):
+        raise ValueError("precision has to be 'auto', 'bf16' or 'bf16x3'")
+    _precision = name
+
+
+def get_precision():
+    return _precision
+
+
+def extension():
+    """The compiled extension module (built in-tree on first use)."""
+    global _ext
+    if _ext is None:
+        _ext = _build.load()
+    return _ext
+
+
+def cuda_kernels_enabled(*tensors):
+    """True when the custom kernels should handle these tensors."""
+    if _backend == 'torch':
+        return False
+    return all(t.is_cuda for t in tensors) and all(
+        t.dtype in (torch.float32, torch.bfloat16, torch.float16) for t in tensors)
+
+
+def check_status(device=None):
+    """Raises if a kernel reported a problem (timed-out wait, non-SPD matrix) since the last
+    check.  Synchronises the current stream."""
+    if not torch.cuda.is_available():
+        return
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    code = extension().read_status(dev or 0)
+    if code != 0:
+        names = {1: 'timed out waiting for a TMA stage', 2: 'timed out waiting for a free stage',
+                 3: 'timed out waiting for the accumulator', 4: 'timed out waiting for a peer GPU',
+                 5: 'matrix is not positive definite', 6: 'bad argument'}
+        raise RuntimeError(f'asdl_b200 CUDA kernel error {code}: {names.get(code, "unknown")}')
+
+
+# --------------------------------------------------------------------------------------------
+# staging helpers
+# --------------------------------------------------------------------------------------------
+def _round_up(v, m):
+    return (v + m - 1) // m * m
+
+
+def _use_x3(dtype):
+    if _precision == 'bf16':
+        return False
+    if _precision == 'bf16x3':
+        return True
+    return dtype == torch.float32
+
+
+def _stage_bf16(x: torch.Tensor, want_lo: bool):
+    """[rows, n] -> bf16 operand(s) with a 16-byte aligned row pitch.  Returns (hi, lo|None),
+    both views [rows, n] into padded storage."""
+    rows, n = x.shape
+    if (not want_lo and x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0):
+        return x, None
+    ld = _round_up(max(n, 8), 8)
+    hi = torch.empty(rows, ld, device=x.device, dtype=torch.bfloat16)
+    lo = torch.empty_like(hi) if want_lo else None
+    src = x if x.stride(1) == 1 else x.contiguous()
+    extension().cast_pad_bf16(src, hi, lo, 1.0)
+    return hi[:, :n], (lo[:, :n] if want_lo else None)
+
+
+def _segments(a_hi, a_lo, b_hi, b_lo):
+    if a_lo is None or b_lo is None:
+        return [a_hi], [b_hi]
+    return [a_hi, a_hi, a_lo], [b_hi, b_lo, b_hi]
+
+
+# --------------------------------------------------------------------------------------------
+# products
+# --------------------------------------------------------------------------------------------
+def gram(x: torch.Tensor, scale: float = 1.0, out: Optional[torch.Tensor] = None,
+         beta: float = 0.0) -> torch.Tensor:
+    """``scale * x^T x (+ beta * out)`` for a sample matrix x [rows, n] -> [n, n].
+
+    This is the Kronecker-factor product of K-FAC (A = a^T a, B = g^T g) and Shampoo's R = G^T G.
+    CUDA: tcgen05 SYRK (lower-triangular tiles mirrored in the epilogue, split-K over rows,
+    the EMA ``beta`` folded into the epilogue); the result is fp32 and exactly symmetric."""
+    if x.ndim != 2:
+        raise ValueError(f'x has to be 2-D. Got {x.ndim}-D.')
+    if not cuda_kernels_enabled(x) or x.shape[0] == 0:
+        prod = (x.T @ x) * scale if scale != 1.0 else x.T @ x
+        if out is None:
+            return prod
+        if beta != 0.0:
+            out.mul_(beta).add_(prod.to(out.dtype))
+        else:
+            out.copy_(prod)
+        return out
+    hi, lo = _stage_bf16(x, _use_x3(x.dtype))
+    n = x.shape[1]
+    if out is None:
+        out = torch.empty(n, n, device=x.device, dtype=torch.float32)
+        beta = 0.0
+    a_segs, b_segs = _segments(hi, lo, hi, lo)
+    extension().umma_gemm(a_segs, b_segs, False, False, out, float(scale), float(beta), True,
+                          None, None, 0)
+    return out
+
+
+def matmul_tn(a: torch.Tensor, b: torch.Tensor, scale: float = 1.0,
+              out: Optional[torch.Tensor] = None, beta: float = 0.0) -> torch.Tensor:
+    """``scale * a^T b (+ beta*out)`` with a: [k, m], b: [k, n] (both "sample-major")."""
+    if not cuda_kernels_enabled(a, b) or a.shape[0] == 0:
+        prod = (a.T @ b) * scale
+        if out is None:
+            return prod
+        return out.mul_(beta).add_(prod.to(out.dtype)) if beta != 0.0 else out.copy_(prod)
+    x3 = _use_x3(a.dtype) or _use_x3(b.dtype)
+    a_hi, a_lo = _stage_bf16(a, x3)
+    b_hi, b_lo = _stage_bf16(b, x3)
+    if out is None:
+        out = torch.empty(a.shape[1], b.shape[1], device=a.device, dtype=torch.float32)
+        beta = 0.0
+    a_segs, b_segs = _segments(a_hi, a_lo, b_hi, b_lo)
+    extension().umma_gemm(a_segs, b_segs, False, False, out, float(scale), float(beta), False,
+                          None, None, 0)
+    return out
+
+
+def kron_apply(left: torch.Tensor, mid: torch.Tensor, right: torch.Tensor) -> torch.Tensor:
+    """``left @ mid @ right`` with symmetric ``left`` [m, m] and ``right`` [n, n]: the K-FAC
+    preconditioning step B^-1 . grad . A^-1 (also used un-inverted for curvature products).
+
+    CUDA: two chained tcgen05 GEMMs.  The symmetry of the outer matrices lets both be read in
+    their stored row-major layout as MN-major operands; the intermediate is written by the first
+    GEMM's epilogue directly as bf16 hi/lo pairs in the K-major layout the second one consumes."""
+    if not cuda_kernels_enabled(left, mid, right) or mid.numel() == 0:
+        dt = mid.dtype
+        return left.to(dt) @ mid @ right.to(dt)
+    ext = extension()
+    m, n = mid.shape
+    x3 = _use_x3(torch.float32) if (left.dtype == torch.float32 or mid.dtype == torch.float32) \
+        else _use_x3(mid.dtype)
+    l_hi, l_lo = _stage_bf16(left, x3)
+    g_hi, g_lo = _stage_bf16(mid, x3)
+    r_hi, r_lo = _stage_bf16(right, x3)
+    ld = _round_up(max(n, 8), 8)
+    t_hi = torch.empty(m, ld, device=mid.device, dtype=torch.bfloat16)
+    t_lo = torch.empty_like(t_hi) if x3 else None
+    # T = left^T-as-stored . mid : A operand = left ([k=m, m] row-major, symmetric), B = mid [k=m, n]
+    a_segs, b_segs = _segments(l_hi, l_lo, g_hi, g_lo)
+    ext.umma_gemm(a_segs, b_segs, False, False, None, 1.0, 0.0, False, t_hi, t_lo, 0)
+    # Y = T . right : A operand = T ([m, k=n] K-major), B = right ([k=n, n] row-major, symmetric)
+    out = torch.empty(m, n, device=mid.device, dtype=torch.float32)
+    a_segs, b_segs = _segments(t_hi[:, :n], t_lo[:, :n] if x3 else None, r_hi, r_lo)
+    ext.umma_gemm(a_segs, b_segs, True, False, out, 1.0, 0.0, False, None, None, 0)
+    return out.to(mid.dtype) if mid.dtype != torch.float32 else out
+
+
+def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
+                    out: Optional[torch.Tensor] = None, beta: float = 0.0,
+                    channels_last_order: bool = False) -> torch.Tensor:
+    """K-FAC A factor of a convolution straight from its input:
+    ``scale * M M^T`` with M the (c_in*kh*kw) x (n*h_out*w_out) patch matrix.
+
+    ``channels_last_order=False`` orders rows/columns as (c, kh, kw) (matching
+    ``weight.view(c_out, -1)``); ``True`` uses (kh, kw, c), the order of a channels_last weight.
+    CUDA: a bf16 im2col kernel (vectorised for channels_last inputs) feeds the tcgen05 SYRK; 1x1
+    stride-1 convolutions on channels_last activations need no staging at all."""
+    from ..utils import im2col_2d, _conv_geometry
+    (kh, kw), (sh, sw), (ph, pw), (dh, dw) = _conv_geometry(conv)
+    if not cuda_kernels_enabled(x):
+        patches = im2col_2d(x, conv)  # n x (c kh kw) x L
+        if channels_last_order:
+            n, _, L = patches.shape
+            patches = patches.view(n, x.shape[1], kh * kw, L).permute(0, 2, 1, 3).reshape(n, -1, L)
+        rows = patches.permute(0, 2, 1).reshape(-1, patches.shape[1])
+        return gram(rows, scale=scale, out=out, beta=beta)
+    n, c, h, w = x.shape
+    ho = (h + 2 * ph - dh * (kh - 1) - 1) // sh + 1
+    wo = (w + 2 * pw - dw * (kw - 1) - 1) // sw + 1
+    ncol = c * kh * kw
+    pointwise = (kh == 1 and kw == 1 and sh == 1 and sw == 1 and ph == 0 and pw == 0)
+    if (pointwise and x.dtype == torch.bfloat16 and x.is_contiguous(memory_format=torch.channels_last)
+            and c % 8 == 0 and not _use_x3(x.dtype)):
+        rows = x.permute(0, 2, 3, 1).reshape(n * h * w, c)  # a view: NHWC memory is already [rows, c]
+        return gram(rows, scale=scale, out=out, beta=beta)
+    ld = _round_up(max(ncol, 8), 8)
+    patches = torch.empty(n * ho * wo, ld, device=x.device, dtype=torch.bfloat16)
+    extension().im2col_bf16(x, patches, [kh, kw], [sh, sw], [ph, pw], [dh, dw],
+                            not channels_last_order)
+    return gram(patches[:, :ncol], scale=scale, out=out, beta=beta)
+
+
+# --------------------------------------------------------------------------------------------
+# inverses
+# --------------------------------------------------------------------------------------------
+def spd_inverse(mat: torch.Tensor, damping: float = 0.0) -> torch.Tensor:
+    """``(mat + damping*I)^-1`` for symmetric positive (semi-)definite ``mat``; the input is left
+    untouched.  CUDA fp32: the library's blocked Cholesky-inverse kernels."""
+    n = mat.shape[-1]
+    if cuda_kernels_enabled(mat) and mat.dtype == torch.float32 and mat.ndim == 2 \
+            and hasattr(extension(), 'chol_inverse'):
+        out = torch.empty_like(mat)
+        extension().chol_inverse([mat], [out], [float(damping)])
+        return out
+    eye = torch.eye(n, device=mat.device, dtype=mat.dtype)
+    chol = torch.linalg.cholesky(mat + damping * eye)
+    return torch.cholesky_inverse(chol)
+
+
+def unitwise_inverse(blocks: torch.Tensor, damping: float = 0.0) -> torch.Tensor:
+    """Batched ``(block + damping*I)^-1`` for f x k x k blocks.  2x2 blocks (normalisation
+    layers) use the closed form, evaluated in one fused elementwise pass."""
+    k = blocks.shape[-1]
+    if k == 2 and blocks.shape[-2] == 2:
+        a = blocks[..., 0, 0] + damping
+        b = blocks[..., 0, 1]
+        c = blocks[..., 1, 0]
+        d = blocks[..., 1, 1] + damping
+        det = a * d - b * c
+        inv = torch.stack([torch.stack([d, -b], dim=-1), torch.stack([-c, a], dim=-1)], dim=-2)
+        return inv / det[..., None, None]
+    eye = torch.eye(k, device=blocks.device, dtype=blocks.dtype)
+    return torch.linalg.inv(blocks + damping * eye)
