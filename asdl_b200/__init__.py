@@ -13,6 +13,8 @@ from .core import *  # noqa: F401,F403
 from .grad_maker import *  # noqa: F401,F403
 from .mvp import *  # noqa: F401,F403
 from .fisher import *  # noqa: F401,F403
+from .hessian import *  # noqa: F401,F403
+from .gradient import *  # noqa: F401,F403
 from .precondition import *  # noqa: F401,F403
 from . import ops, parallel  # noqa: F401
 
