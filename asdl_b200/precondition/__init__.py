@@ -8,3 +8,4 @@ from .newton import *  # noqa: F401,F403
 from .kbfgs import *  # noqa: F401,F403
 from .curve_ball import *  # noqa: F401,F403
 from .seng import *  # noqa: F401,F403
+from .kfac_fused import *  # noqa: F401,F403

@@ -1,0 +1,433 @@
+"""K-FAC with persistent curvature buffers and fused statistics kernels - the production path for
+CUDA (it also runs, through the PyTorch implementations of :mod:`asdl_b200.ops`, on CPU, which is
+how it is tested against :class:`KfacGradientMaker`).
+
+Compared with the generic maker (same numerics, see asdl/precondition/natural_gradient.py:397-506
+for the reference life cycle) nothing is allocated or re-packed per step:
+
+  * every Kronecker factor lives in a persistent fp32 buffer; the statistics hooks launch one SYRK
+    per factor whose epilogue performs the whole moving-average update
+    ``A <- (1-e) A + e*s * a^T a`` (conv layers: bf16 im2col kernel -> SYRK, 1x1 convolutions on
+    channels_last activations read the activation tensor in place);
+  * convolution factors use the (kh, kw, c) column order of channels_last weights, so weight
+    gradients are preconditioned through a view, without layout copies;
+  * the pi-damping split and "is this factor still zero" tests stay on the device: no host
+    synchronisation anywhere in a step;
+  * inverses are cached as bf16 hi/lo pairs, the two-sided product B^-1 G A^-1 runs as chained
+    tcgen05 GEMMs writing straight into ``param.grad``;
+  * the 2x2 unit-wise blocks of all normalisation layers are applied with multi-tensor kernels.
+"""
+from typing import Dict, List
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..matrices import FISHER_EMP, FISHER_MC, SHAPE_KRON, SHAPE_UNIT_WISE
+from ..symmatrix import SymMatrix, Kron, UnitWise
+from ..utils import skip_param_grad, nvtx_range
+from ..grad_maker import LOSS_CROSS_ENTROPY
+from .natural_gradient import KfacGradientMaker
+from .prec_grad_maker import PreconditioningConfig
+
+__all__ = ['FusedKfacGradientMaker']
+
+_NORMS = (nn.BatchNorm1d, nn.BatchNorm2d, nn.LayerNorm)
+
+
+def _khwc_order(module):
+    """True when the conv weight is stored channels_last, i.e. its rows are ordered (kh, kw, c)."""
+    w = module.weight
+    return (isinstance(module, nn.Conv2d) and w.shape[2] * w.shape[3] > 1
+            and w.is_contiguous(memory_format=torch.channels_last) and not w.is_contiguous())
+
+
+class _KronState:
+    def __init__(self, name, module, device):
+        self.name, self.module = name, module
+        w = module.weight
+        self.d_out = w.shape[0]
+        self.d_in = w[0].numel()
+        self.khwc = _khwc_order(module)
+        self.has_bias = getattr(module, 'bias', None) is not None and module.bias.requires_grad
+        f32 = dict(device=device, dtype=torch.float32)
+        self.A = torch.zeros(self.d_in, self.d_in, **f32)
+        self.B = torch.zeros(self.d_out, self.d_out, **f32)
+        self.A_inv = torch.zeros(self.d_in, self.d_in, **f32)
+        self.B_inv = torch.zeros(self.d_out, self.d_out, **f32)
+        self.has_inv = False
+        self.kron = Kron(self.A, self.B)
+        module.fisher = SymMatrix(kron=self.kron)
+
+    def grad_matrix(self):
+        """(d_out x d_in view of the weight gradient, tensor to copy back into or None)."""
+        g = self.module.weight.grad
+        if g.ndim == 2:
+            return g, None
+        if self.khwc:
+            if g.is_contiguous(memory_format=torch.channels_last):
+                return g.permute(0, 2, 3, 1).reshape(self.d_out, self.d_in), None
+            staged = g.contiguous(memory_format=torch.channels_last)
+            return staged.permute(0, 2, 3, 1).reshape(self.d_out, self.d_in), staged
+        if g.is_contiguous():
+            return g.view(self.d_out, self.d_in), None
+        staged = g.contiguous()
+        return staged.view(self.d_out, self.d_in), staged
+
+
+class _NormState:
+    def __init__(self, name, module, device):
+        self.name, self.module = name, module
+        f = module.weight.numel()
+        self.stats = torch.zeros(f, 2, 2, device=device, dtype=torch.float32)
+        self.inv = torch.zeros(f, 2, 2, device=device, dtype=torch.float32)
+        self.has_inv = False
+        self.unit = UnitWise(self.stats)
+        module.fisher = SymMatrix(unit=self.unit)
+        self.saved_out = None
+
+
+class FusedKfacGradientMaker(KfacGradientMaker):
+    """Drop-in replacement of :class:`KfacGradientMaker` for Linear / Conv2d (Kronecker factors)
+    and BatchNorm / LayerNorm (unit-wise 2x2 blocks) with persistent state.
+
+    Extra args:
+        precond_precision: ``'bf16x3'`` (default, ~2^-16 relative) or ``'bf16'`` for the products
+            that apply the inverses.
+        clone_norm_outputs: copy normalisation-layer outputs in the statistics hook (needed only
+            if the model modifies them in place afterwards, e.g. ``ReLU(inplace=True)``).
+    Embedding layers are not handled here; list them in ``config.ignore_modules``.
+    """
+
+    def __init__(self, model, config: PreconditioningConfig, fisher_type: str = FISHER_MC,
+                 loss_type: str = LOSS_CROSS_ENTROPY, scale: float = 1, grad_scale: float = 1,
+                 n_mc_samples: int = 1, var: float = 1., seed: int = None,
+                 precond_precision: str = 'bf16x3', clone_norm_outputs: bool = False, **kwargs):
+        if fisher_type not in (FISHER_MC, FISHER_EMP):
+            raise ValueError('FusedKfacGradientMaker supports fisher_mc and fisher_emp.')
+        if loss_type != LOSS_CROSS_ENTROPY and fisher_type == FISHER_MC:
+            raise ValueError('Monte-Carlo sampling is implemented for cross-entropy only.')
+        super().__init__(model, config, fisher_type=fisher_type, loss_type=loss_type, scale=scale,
+                         grad_scale=grad_scale, n_mc_samples=n_mc_samples, var=var, seed=seed, **kwargs)
+        self.precond_precision = precond_precision
+        self.clone_norm_outputs = clone_norm_outputs
+        device = self.device
+        self._kron: List[_KronState] = []
+        self._norm: List[_NormState] = []
+        for name, module in self.named_modules_for_curvature:
+            shape = self.shape_for[module]
+            if shape == SHAPE_KRON and isinstance(module, (nn.Linear, nn.Conv2d)):
+                self._kron.append(_KronState(name, module, device))
+            elif shape == SHAPE_UNIT_WISE and isinstance(module, _NORMS):
+                self._norm.append(_NormState(name, module, device))
+            else:
+                raise ValueError(f'{type(module).__name__} with shape {shape} is not supported by the '
+                                 f'fused K-FAC path; add it to config.ignore_modules.')
+        self._by_module: Dict[nn.Module, object] = {s.module: s for s in self._kron + self._norm}
+        self._bf16_cache = {}
+
+    # ------------------------------------------------------------------ curvature
+    def _stat_weights(self):
+        """(alpha, beta): new statistics enter with alpha, stored curvature is kept with beta."""
+        cfg = self.config
+        if cfg.data_size == -1:
+            raise ValueError('data_size is not specified.')
+        if self.do_accumulate:
+            return self.scale * cfg.ema_decay / cfg.data_size, 1.0 - cfg.ema_decay
+        return self.scale / cfg.data_size, 0.0
+
+    def _install_hooks(self):
+        alpha, beta = self._stat_weights()
+        handles = []
+        state = {'on': True}
+
+        def kron_hook(st: _KronState):
+            module = st.module
+
+            def fwd(_m, inputs, output):
+                if not state['on']:
+                    return
+                x = inputs[0].detach()
+                with torch.no_grad():
+                    if isinstance(module, nn.Conv2d):
+                        out_size = output.shape[-2] * output.shape[-1]
+                        ops.conv_patch_gram(x, module, scale=alpha / out_size, out=st.A, beta=beta,
+                                            channels_last_order=st.khwc)
+                    else:
+                        ops.gram(x.reshape(-1, x.shape[-1]), scale=alpha, out=st.A, beta=beta)
+                if output.requires_grad:
+                    def bwd(grad):
+                        if not state['on']:
+                            return
+                        g = grad.detach()
+                        with torch.no_grad():
+                            if g.ndim == 4:
+                                rows = g.permute(0, 2, 3, 1).reshape(-1, g.shape[1])
+                            else:
+                                rows = g.reshape(-1, g.shape[-1])
+                            ops.gram(rows, scale=alpha, out=st.B, beta=beta)
+                    output.register_hook(bwd)
+            return fwd
+
+        def norm_hook(st: _NormState):
+            module = st.module
+
+            def fwd(_m, inputs, output):
+                if not state['on']:
+                    return
+                y = output.detach()
+                if output.requires_grad:
+                    saved = y.clone() if self.clone_norm_outputs else y
+
+                    def bwd(grad):
+                        if not state['on']:
+                            return
+                        with torch.no_grad():
+                            self._norm_statistics(st, saved, grad.detach(), alpha, beta)
+                    output.register_hook(bwd)
+            return fwd
+
+        for st in self._kron:
+            handles.append(st.module.register_forward_hook(kron_hook(st)))
+        for st in self._norm:
+            handles.append(st.module.register_forward_hook(norm_hook(st)))
+        return handles, state
+
+    @staticmethod
+    def _norm_statistics(st: _NormState, y, g, alpha, beta):
+        module = st.module
+        if isinstance(module, nn.LayerNorm):
+            k = module.weight.ndim
+            xh = (y.float() - module.bias) / module.weight
+            gw = (xh * g).reshape(-1, *y.shape[-k:]).flatten(start_dim=1)
+            gb = g.float().reshape(-1, *y.shape[-k:]).flatten(start_dim=1)
+        else:
+            shape = (1, -1) + (1,) * (y.ndim - 2)
+            xh = (y.float() - module.bias.view(shape)) / module.weight.view(shape)
+            dims = tuple(range(2, y.ndim))
+            gw = (xh * g).sum(dim=dims) if dims else xh * g
+            gb = g.float().sum(dim=dims) if dims else g.float()
+        ww = gw.square().sum(dim=0)
+        wb = (gw * gb).sum(dim=0)
+        bb = gb.square().sum(dim=0)
+        new = torch.stack([torch.stack([ww, wb], dim=1), torch.stack([wb, bb], dim=1)], dim=1)
+        st.stats.mul_(beta).add_(new, alpha=alpha)
+
+    def update_curvature(self):
+        cfg = self.config
+        model = self.model
+        handles, state = self._install_hooks()
+        if cfg is not None and self.fisher_maker.config.seed is not None:
+            torch.random.manual_seed(self.fisher_maker.config.seed)
+        try:
+            with nvtx_range('kfac_curvature'):
+                self.call_model()
+                saved = self._loss_reduction
+                self._loss_reduction = 'sum'
+                try:
+                    loss = self.call_loss()
+                finally:
+                    self._loss_reduction = saved
+                if self.fisher_type == FISHER_EMP:
+                    loss.backward()
+                else:
+                    logits = self._logits
+                    n_mc = self.fisher_maker.config.n_mc_samples
+                    log_probs = F.log_softmax(logits.float(), dim=-1).reshape(-1, logits.shape[-1])
+                    for _ in range(n_mc):
+                        with torch.no_grad():
+                            targets = torch.multinomial(log_probs.exp(), 1).squeeze(1)
+                        nll = F.nll_loss(log_probs, targets, reduction='sum') / n_mc
+                        with skip_param_grad(model):
+                            nll.backward(retain_graph=True)
+                    state['on'] = False
+                    loss.backward()
+        finally:
+            state['on'] = False
+            for h in handles:
+                h.remove()
+        with torch.no_grad():
+            for p in model.parameters():
+                if p.grad is not None:
+                    p.grad.div_(cfg.data_size)
+            loss.div_(cfg.data_size)
+        self._loss = loss
+        if self.world_size > 1:
+            self.reduce_scatter_curvature()
+
+    def do_update_preconditioner(self, step=None) -> bool:
+        if not self.do_accumulate and (self.curvature_upd_schedule is not None
+                                       or self.config.curvature_upd_interval is not None):
+            return self.do_update_curvature(step)  # nothing is kept: invert whenever measured
+        return KfacGradientMaker.do_update_preconditioner(self, step)
+
+    # ------------------------------------------------------------------ inverses
+    @torch.no_grad()
+    def update_preconditioner(self, damping=None, **kwargs):
+        damping = self.config.damping if damping is None else damping
+        root = damping ** 0.5
+        with nvtx_range('kfac_inverse'):
+            for st in self._kron:
+                if not self.is_module_for_inv_and_precondition(st.module):
+                    continue
+                tr_a = torch.diagonal(st.A).sum() / st.d_in
+                tr_b = torch.diagonal(st.B).sum() / st.d_out
+                pi = torch.sqrt(tr_a / tr_b)
+                ok = torch.isfinite(pi) & (pi > 0)
+                pi = torch.where(ok, pi, torch.ones_like(pi))
+                d_a = torch.where(ok, (root * pi).clamp_min(1e-7), torch.full_like(pi, damping))
+                d_b = torch.where(ok, (root / pi).clamp_min(1e-7), torch.full_like(pi, damping))
+                self._invert(st.A, d_a, st.A_inv)
+                self._invert(st.B, d_b, st.B_inv)
+                st.kron.A_inv, st.kron.B_inv = st.A_inv, st.B_inv
+                st.has_inv = True
+                self._refresh_cache(st)
+            for st in self._norm:
+                if not self.is_module_for_inv_and_precondition(st.module):
+                    continue
+                st.inv.copy_(ops.unitwise_inverse(st.stats, damping))
+                st.unit.inv = st.inv
+                st.has_inv = True
+
+    @staticmethod
+    def _invert(mat, damping_t, out):
+        """out <- (mat + damping*I)^-1 with the damping given as a device scalar."""
+        n = mat.shape[0]
+        eye = torch.eye(n, device=mat.device, dtype=mat.dtype)
+        out.copy_(ops.spd_inverse(mat + damping_t * eye, 0.0))
+
+    def _refresh_cache(self, st: _KronState):
+        """bf16 hi/lo images of the inverses used by the tensor-core preconditioning products."""
+        if not st.A.is_cuda or ops.get_backend() == 'torch':
+            return
+        x3 = self.precond_precision == 'bf16x3'
+        for key, mat in (('A', st.A_inv), ('B', st.B_inv)):
+            n = mat.shape[0]
+            ld = (max(n, 8) + 7) // 8 * 8
+            slot = self._bf16_cache.get((st, key))
+            if slot is None:
+                hi = torch.empty(n, ld, device=mat.device, dtype=torch.bfloat16)
+                lo = torch.empty_like(hi) if x3 else None
+                slot = self._bf16_cache[(st, key)] = (hi, lo)
+            ops.extension().cast_pad_bf16(mat, slot[0], slot[1], 1.0)
+
+    # ------------------------------------------------------------------ preconditioning
+    @torch.no_grad()
+    def precondition(self, vectors=None, grad_scale=None, use_inv=True):
+        if vectors is not None or not use_inv:
+            return super().precondition(vectors=vectors, grad_scale=grad_scale, use_inv=use_inv)
+        grad_scale = self.grad_scale if grad_scale is None else grad_scale
+        distributed = self.world_size > 1
+        if distributed:
+            self.sync_grad_pre_precondition()
+        with nvtx_range('kfac_precondition'):
+            for st in self._kron:
+                if not st.has_inv or not self.is_module_for_inv_and_precondition(st.module):
+                    continue
+                if st.module.weight.grad is None:
+                    continue
+                self._precondition_kron(st, grad_scale)
+            self._precondition_norms(grad_scale)
+        if distributed:
+            self.sync_grad_post_precondition()
+
+    def _precondition_kron(self, st: _KronState, grad_scale):
+        g2d, staged = st.grad_matrix()
+        if grad_scale != 1:
+            g2d.mul_(grad_scale)
+        if g2d.is_cuda and ops.get_backend() != 'torch':
+            self._kron_apply_cached(st, g2d)
+        else:
+            g2d.copy_(st.B_inv @ g2d @ st.A_inv)
+        if staged is not None:
+            st.module.weight.grad.copy_(staged)
+        if st.has_bias and st.module.bias.grad is not None:
+            b = st.module.bias.grad
+            if grad_scale != 1:
+                b.mul_(grad_scale)
+            b.copy_(torch.mv(st.B_inv, b))
+
+    def _kron_apply_cached(self, st: _KronState, g2d):
+        """g2d <- B^-1 g2d A^-1 with the cached bf16 images of the inverses."""
+        ext = ops.extension()
+        x3 = self.precond_precision == 'bf16x3'
+        m, n = g2d.shape
+        ld = (max(n, 8) + 7) // 8 * 8
+        bufs = self._bf16_cache.get((st, 'work'))
+        if bufs is None:
+            mk = lambda: torch.empty(m, ld, device=g2d.device, dtype=torch.bfloat16)  # noqa: E731
+            bufs = self._bf16_cache[(st, 'work')] = (mk(), mk() if x3 else None, mk(), mk() if x3 else None)
+        g_hi, g_lo, t_hi, t_lo = bufs
+        ext.cast_pad_bf16(g2d, g_hi, g_lo, 1.0)
+        b_hi, b_lo = self._bf16_cache[(st, 'B')]
+        a_hi, a_lo = self._bf16_cache[(st, 'A')]
+        bm = b_hi[:, :m]
+        am = a_hi[:, :n]
+        if x3:
+            seg_a, seg_b = [bm, bm, b_lo[:, :m]], [g_hi[:, :n], g_lo[:, :n], g_hi[:, :n]]
+        else:
+            seg_a, seg_b = [bm], [g_hi[:, :n]]
+        ext.umma_gemm(seg_a, seg_b, False, False, None, 1.0, 0.0, False, t_hi, t_lo, 0)
+        if x3:
+            seg_a = [t_hi[:, :n], t_hi[:, :n], t_lo[:, :n]]
+            seg_b = [am, a_lo[:, :n], am]
+        else:
+            seg_a, seg_b = [t_hi[:, :n]], [am]
+        if g2d.stride(1) == 1:
+            ext.umma_gemm(seg_a, seg_b, True, False, g2d, 1.0, 0.0, False, None, None, 0)
+        else:
+            out = torch.empty(m, n, device=g2d.device, dtype=torch.float32)
+            ext.umma_gemm(seg_a, seg_b, True, False, out, 1.0, 0.0, False, None, None, 0)
+            g2d.copy_(out)
+
+    def _precondition_norms(self, grad_scale):
+        gw, gb, i00, i01, i10, i11 = [], [], [], [], [], []
+        for st in self._norm:
+            if not st.has_inv or not self.is_module_for_inv_and_precondition(st.module):
+                continue
+            w, b = st.module.weight.grad, st.module.bias.grad
+            if w is None or b is None:
+                continue
+            gw.append(w.view(-1))
+            gb.append(b.view(-1))
+            i00.append(st.inv[:, 0, 0])
+            i01.append(st.inv[:, 0, 1])
+            i10.append(st.inv[:, 1, 0])
+            i11.append(st.inv[:, 1, 1])
+        if not gw:
+            return
+        if grad_scale != 1:
+            torch._foreach_mul_(gw, grad_scale)
+            torch._foreach_mul_(gb, grad_scale)
+        new_w = torch._foreach_mul(gw, i00)
+        torch._foreach_addcmul_(new_w, gb, i01)
+        new_b = torch._foreach_mul(gw, i10)
+        torch._foreach_addcmul_(new_b, gb, i11)
+        torch._foreach_copy_(gw, new_w)
+        torch._foreach_copy_(gb, new_b)
+
+    # ------------------------------------------------------------------ checkpointing
+    def _load_curvature_state(self, tensors):
+        grouped: Dict[str, Dict[str, torch.Tensor]] = {}
+        for key, value in tensors.items():
+            name, rest = key.split('.', 1)
+            grouped.setdefault(name, {})[rest] = value
+        for st in self._kron:
+            items = grouped.get(st.name, {})
+            for key, buf in (('kron.A', st.A), ('kron.B', st.B), ('kron.A_inv', st.A_inv),
+                             ('kron.B_inv', st.B_inv)):
+                if key in items:
+                    buf.copy_(items[key])
+            if 'kron.A_inv' in items and 'kron.B_inv' in items:
+                st.kron.A_inv, st.kron.B_inv = st.A_inv, st.B_inv
+                st.has_inv = True
+                self._refresh_cache(st)
+        for st in self._norm:
+            items = grouped.get(st.name, {})
+            if 'unit.data' in items:
+                st.stats.copy_(items['unit.data'])
+            if 'unit.inv' in items:
+                st.inv.copy_(items['unit.inv'])
+                st.unit.inv = st.inv
+                st.has_inv = True

@@ -294,7 +294,9 @@ class NaturalGradientMaker(PreconditionedGradientMaker):
         return not self.do_update_curvature(step)
 
     def do_update_preconditioner(self, step=None) -> bool:
-        if not self.do_accumulate and self.world_size > 1:
+        has_curvature_rule = (self.curvature_upd_schedule is not None
+                              or self.config.curvature_upd_interval is not None)
+        if not self.do_accumulate and self.world_size > 1 and has_curvature_rule:
             return self.do_update_curvature(step)  # nothing is kept, so invert whenever measured
         return super().do_update_preconditioner(step)
 
