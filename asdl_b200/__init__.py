@@ -16,6 +16,8 @@ from .fisher import *  # noqa: F401,F403
 from .hessian import *  # noqa: F401,F403
 from .gradient import *  # noqa: F401,F403
 from .precondition import *  # noqa: F401,F403
+from .kernel import *  # noqa: F401,F403
+from .counter import *  # noqa: F401,F403
 from . import ops, parallel  # noqa: F401
 
 __version__ = '0.1.0'

@@ -6,11 +6,20 @@ void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, b
                bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta, bool sym,
                c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo, int64_t nsplit);
 int64_t read_status(int64_t dev);
+int64_t launch_count();
 void reserve_scratch(int64_t dev, int64_t nfloats);
 void cast_pad_bf16(at::Tensor src, at::Tensor hi, c10::optional<at::Tensor> lo, double scale);
-void im2col_bf16(at::Tensor x, at::Tensor out, std::vector<int64_t> kernel,
-                 std::vector<int64_t> stride, std::vector<int64_t> padding,
-                 std::vector<int64_t> dilation, bool c_major);
+void im2col_bf16(at::Tensor x, at::Tensor out, c10::optional<at::Tensor> out_lo,
+                 std::vector<int64_t> kernel, std::vector<int64_t> stride,
+                 std::vector<int64_t> padding, std::vector<int64_t> dilation, bool c_major);
+void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
+                      bool b_kmajor, int64_t dst_ptr, int64_t ldc, double alpha, bool sym, bool atomic,
+                      std::vector<int64_t> extra_ptrs, int64_t nsplit);
+void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot);
+void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale);
+void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs);
+void symm_scale_segments(at::Tensor local, at::Tensor segs, double beta);
+void chol_inverse(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs, at::Tensor damping);
 }  // namespace b200
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -19,7 +28,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("alpha"), py::arg("beta"), py::arg("sym"), py::arg("out_hi"), py::arg("out_lo"),
         py::arg("nsplit"));
   m.def("read_status", &b200::read_status);
+  m.def("launch_count", &b200::launch_count);
   m.def("reserve_scratch", &b200::reserve_scratch);
   m.def("cast_pad_bf16", &b200::cast_pad_bf16);
   m.def("im2col_bf16", &b200::im2col_bf16);
+  m.def("umma_gemm_to_ptr", &b200::umma_gemm_to_ptr);
+  m.def("symm_barrier", &b200::symm_barrier);
+  m.def("symm_reduce_segments", &b200::symm_reduce_segments);
+  m.def("symm_bcast_segments", &b200::symm_bcast_segments);
+  m.def("symm_scale_segments", &b200::symm_scale_segments);
+  m.def("chol_inverse", &b200::chol_inverse, "grouped damped SPD inverse (fp32)");
 }

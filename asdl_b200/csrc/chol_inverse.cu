@@ -1,0 +1,381 @@
+// Grouped fp32 inverse of damped symmetric positive-definite matrices:
+//     out_m = (A_m + damping_m * I)^-1        for m = 0 .. count-1, sizes n_m arbitrary
+// by blocked Cholesky (A = L L^T), blocked triangular inversion (X = L^-1) and X^T X.
+// All matrices of a call advance through the same sequence of launches ("grouped"): the launch
+// for block column k covers every matrix that still has such a column, so a ResNet-50's ~100
+// factors of sizes 64..4608 cost O(n_max/64) launches, not O(sum n_m/64).
+//
+// The damping values are read from device memory, so a caller can compute them on the device
+// (pi-damping from traces) without synchronising.  The inputs are not modified.  A non-positive
+// pivot sets the status word to ERR_NOT_SPD and the factorisation continues with pivot 1.
+//
+// Everything here is fp32 on the CUDA cores (64x64x64 shared-memory tiles, 4x4 register blocks).
+#include "host_utils.h"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+constexpr int CB = 64;  // block size
+
+struct CholMat {
+  const float* A;   // input n x n (ld = lda)
+  float* L;         // n x n work matrix (the output buffer): lower Cholesky factor, later the inverse
+  float* X;         // n x n scratch: L^-1
+  float* D;         // nb x 64 x 64 scratch: inverses of the diagonal blocks of L
+  int n, nb, lda, pad;
+};
+
+// ---- shared 64x64x64 tile product -----------------------------------------------------------
+// As/Bs are stored k-major: As[k][m], Bs[k][n].  Thread (tx, ty) of a 16x16 block owns the
+// output elements (ty + 16u, tx + 16v), u,v = 0..3 (bank-conflict free shared-memory reads).
+struct Acc {
+  float v[4][4];
+};
+
+__device__ __forceinline__ void acc_zero(Acc& c) {
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int v = 0; v < 4; ++v) c.v[u][v] = 0.f;
+}
+
+__device__ __forceinline__ void tile_fma(Acc& c, const float (*As)[CB + 1], const float (*Bs)[CB + 1],
+                                         int tx, int ty) {
+#pragma unroll 8
+  for (int k = 0; k < CB; ++k) {
+    float a[4], b[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) a[u] = As[k][ty + 16 * u];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) b[v] = Bs[k][tx + 16 * v];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int v = 0; v < 4; ++v) c.v[u][v] = fmaf(a[u], b[v], c.v[u][v]);
+  }
+}
+
+// dst[k][m] = src(m, k) where src(m, k) = trans ? S[(r0 + k) * ld + c0 + m] : S[(r0 + m) * ld + c0 + k];
+// elements outside the n x n matrix read as zero.
+__device__ __forceinline__ void load_tile(float (*dst)[CB + 1], const float* S, int ld, int n, int r0,
+                                          int c0, bool trans, int tid) {
+  for (int e = tid; e < CB * CB; e += 256) {
+    const int hi = e >> 6, lo = e & 63;  // lo runs along contiguous memory
+    const int gr = r0 + hi, gc = c0 + lo;
+    const float val = (gr < n && gc < n) ? S[static_cast<size_t>(gr) * ld + gc] : 0.f;
+    if (trans)
+      dst[hi][lo] = val;  // src(m = lo, k = hi)
+    else
+      dst[lo][hi] = val;  // src(m = hi, k = lo)
+  }
+}
+
+// ---- phase 0: L = A + damping * I ------------------------------------------------------------
+__global__ void chol_prepare_kernel(const CholMat* mats, const float* damping) {
+  const CholMat M = mats[blockIdx.y];
+  const float d = damping[blockIdx.y];
+  const size_t total = static_cast<size_t>(M.n) * M.n;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / M.n), c = static_cast<int>(i % M.n);
+    float v = M.A[static_cast<size_t>(r) * M.lda + c];
+    if (r == c) v += d;
+    M.L[i] = v;
+  }
+}
+
+// ---- phase 1a: factor the diagonal block k and invert it -------------------------------------
+__global__ void __launch_bounds__(256) chol_diag_kernel(const CholMat* mats, int k, int* status) {
+  const CholMat M = mats[blockIdx.x];
+  if (k >= M.nb) return;
+  __shared__ float S[CB][CB + 1];
+  __shared__ float T[CB][CB + 1];
+  const int tid = threadIdx.x;
+  const int r0 = k * CB;
+  for (int e = tid; e < CB * CB; e += 256) {
+    const int r = e >> 6, c = e & 63;
+    const int gr = r0 + r, gc = r0 + c;
+    float v = 0.f;
+    if (gr < M.n && gc < M.n)
+      v = (c <= r) ? M.L[static_cast<size_t>(gr) * M.n + gc] : 0.f;
+    else if (r == c)
+      v = 1.f;  // identity padding keeps the block factorisable
+    S[r][c] = v;
+  }
+  __syncthreads();
+  for (int j = 0; j < CB; ++j) {
+    if (tid == 0) {
+      float p = S[j][j];
+      if (!(p > 0.f)) {
+        set_error(status, ERR_NOT_SPD);
+        p = 1.f;
+      }
+      S[j][j] = sqrtf(p);
+    }
+    __syncthreads();
+    if (tid > j && tid < CB) S[tid][j] /= S[j][j];
+    __syncthreads();
+    // trailing update of the lower triangle: rows i > j, columns j < c <= i
+    for (int e = tid; e < CB * CB; e += 256) {
+      const int i = e >> 6, c = e & 63;
+      if (i > j && c > j && c <= i) S[i][c] -= S[i][j] * S[c][j];
+    }
+    __syncthreads();
+  }
+  // T = S^-1 (lower triangular), one column per thread
+  if (tid < CB) {
+    const int c = tid;
+    for (int i = 0; i < c; ++i) T[i][c] = 0.f;
+    T[c][c] = 1.f / S[c][c];
+    for (int i = c + 1; i < CB; ++i) {
+      float s = 0.f;
+      for (int j = c; j < i; ++j) s = fmaf(S[i][j], T[j][c], s);
+      T[i][c] = -s / S[i][i];
+    }
+  }
+  __syncthreads();
+  float* D = M.D + static_cast<size_t>(k) * CB * CB;
+  for (int e = tid; e < CB * CB; e += 256) {
+    const int r = e >> 6, c = e & 63;
+    const int gr = r0 + r, gc = r0 + c;
+    D[e] = T[r][c];
+    if (gr < M.n && gc < M.n) {
+      M.L[static_cast<size_t>(gr) * M.n + gc] = S[r][c];
+      M.X[static_cast<size_t>(gr) * M.n + gc] = T[r][c];
+    }
+  }
+}
+
+// ---- phase 1b: panel  L_ik <- L_ik * inv(L_kk)^T  for i > k -----------------------------------
+__global__ void __launch_bounds__(256) chol_panel_kernel(const CholMat* mats, int k) {
+  const CholMat M = mats[blockIdx.y];
+  const int i = k + 1 + blockIdx.x;
+  if (i >= M.nb) return;
+  __shared__ float As[CB][CB + 1];
+  __shared__ float Bs[CB][CB + 1];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  // C[r][c] = sum_j Lik[r][j] * T[c][j]
+  load_tile(As, M.L, M.n, M.n, i * CB, k * CB, false, tid);
+  const float* D = M.D + static_cast<size_t>(k) * CB * CB;
+  for (int e = tid; e < CB * CB; e += 256) Bs[e & 63][e >> 6] = D[e];  // Bs[j][c] = T[c][j]
+  __syncthreads();
+  Acc acc;
+  acc_zero(acc);
+  tile_fma(acc, As, Bs, tx, ty);
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int gr = i * CB + ty + 16 * u, gc = k * CB + tx + 16 * v;
+      if (gr < M.n && gc < M.n) M.L[static_cast<size_t>(gr) * M.n + gc] = acc.v[u][v];
+    }
+}
+
+// ---- phase 1c: trailing update  L_ij -= L_ik L_jk^T  for k < j <= i ---------------------------
+__global__ void __launch_bounds__(256) chol_trailing_kernel(const CholMat* mats, int k) {
+  const CholMat M = mats[blockIdx.y];
+  const int m = M.nb - k - 1;
+  if (m <= 0) return;
+  const int t = blockIdx.x;
+  if (t >= m * (m + 1) / 2) return;
+  int r = static_cast<int>((sqrtf(8.f * t + 1.f) - 1.f) * 0.5f);
+  while ((r + 1) * (r + 2) / 2 <= t) ++r;
+  while (r * (r + 1) / 2 > t) --r;
+  const int i = k + 1 + r, j = k + 1 + (t - r * (r + 1) / 2);
+  __shared__ float As[CB][CB + 1];
+  __shared__ float Bs[CB][CB + 1];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  load_tile(As, M.L, M.n, M.n, i * CB, k * CB, false, tid);  // As[kk][row] = L_ik[row][kk]
+  load_tile(Bs, M.L, M.n, M.n, j * CB, k * CB, false, tid);  // Bs[kk][col] = L_jk[col][kk]
+  __syncthreads();
+  Acc acc;
+  acc_zero(acc);
+  tile_fma(acc, As, Bs, tx, ty);
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int gr = i * CB + ty + 16 * u, gc = j * CB + tx + 16 * v;
+      if (gr < M.n && gc < M.n) M.L[static_cast<size_t>(gr) * M.n + gc] -= acc.v[u][v];
+    }
+}
+
+// ---- phase 2: X = L^-1, block anti-diagonal d:  X_ik = -inv(L_ii) * sum_{j=k}^{i-1} L_ij X_jk ---
+__global__ void __launch_bounds__(256) trtri_level_kernel(const CholMat* mats, int d) {
+  const CholMat M = mats[blockIdx.y];
+  const int k = blockIdx.x, i = k + d;
+  if (i >= M.nb) return;
+  __shared__ float As[CB][CB + 1];
+  __shared__ float Bs[CB][CB + 1];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  Acc acc;
+  acc_zero(acc);
+  for (int j = k; j < i; ++j) {
+    load_tile(As, M.L, M.n, M.n, i * CB, j * CB, false, tid);  // As[kk][row] = L_ij[row][kk]
+    load_tile(Bs, M.X, M.n, M.n, j * CB, k * CB, true, tid);   // Bs[kk][col] = X_jk[kk][col]
+    __syncthreads();
+    tile_fma(acc, As, Bs, tx, ty);
+    __syncthreads();
+  }
+  // second product: X_ik = -T_i * acc, with acc staged through shared memory as the B operand
+  const float* D = M.D + static_cast<size_t>(i) * CB * CB;
+  for (int e = tid; e < CB * CB; e += 256) As[e & 63][e >> 6] = D[e];  // As[kk][row] = T[row][kk]
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int v = 0; v < 4; ++v) Bs[ty + 16 * u][tx + 16 * v] = acc.v[u][v];  // Bs[kk][col]
+  __syncthreads();
+  Acc out;
+  acc_zero(out);
+  tile_fma(out, As, Bs, tx, ty);
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int gr = i * CB + ty + 16 * u, gc = k * CB + tx + 16 * v;
+      if (gr < M.n && gc < M.n) M.X[static_cast<size_t>(gr) * M.n + gc] = -out.v[u][v];
+    }
+}
+
+// ---- phase 3: out = X^T X,  C_ij = sum_{k >= i} X_ki^T X_kj  (i >= j), mirrored ----------------
+__global__ void __launch_bounds__(256) lauum_kernel(const CholMat* mats) {
+  const CholMat M = mats[blockIdx.y];
+  const int t = blockIdx.x;
+  if (t >= M.nb * (M.nb + 1) / 2) return;
+  int r = static_cast<int>((sqrtf(8.f * t + 1.f) - 1.f) * 0.5f);
+  while ((r + 1) * (r + 2) / 2 <= t) ++r;
+  while (r * (r + 1) / 2 > t) --r;
+  const int i = r, j = t - r * (r + 1) / 2;
+  __shared__ float As[CB][CB + 1];
+  __shared__ float Bs[CB][CB + 1];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  Acc acc;
+  acc_zero(acc);
+  for (int k = i; k < M.nb; ++k) {
+    load_tile(As, M.X, M.n, M.n, k * CB, i * CB, true, tid);  // As[kk][row] = X_ki[kk][row]
+    load_tile(Bs, M.X, M.n, M.n, k * CB, j * CB, true, tid);  // Bs[kk][col] = X_kj[kk][col]
+    __syncthreads();
+    if (k == i) {
+      // X_ii is lower triangular: entries above the diagonal of the stored block belong to L^-1's
+      // zero part but the storage holds whatever was there before; mask them.
+      for (int e = tid; e < CB * CB; e += 256) {
+        const int kk = e >> 6, col = e & 63;
+        if (col > kk) As[kk][col] = 0.f;
+      }
+      if (i == j) {
+        __syncthreads();
+        for (int e = tid; e < CB * CB; e += 256) Bs[e >> 6][e & 63] = As[e >> 6][e & 63];
+      }
+      __syncthreads();
+    }
+    tile_fma(acc, As, Bs, tx, ty);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int gr = i * CB + ty + 16 * u, gc = j * CB + tx + 16 * v;
+      if (gr < M.n && gc < M.n) {
+        if (i != j || gc <= gr) {
+          M.L[static_cast<size_t>(gr) * M.n + gc] = acc.v[u][v];
+          if (gc != gr) M.L[static_cast<size_t>(gc) * M.n + gr] = acc.v[u][v];
+        }
+      }
+    }
+}
+
+// ---- host ------------------------------------------------------------------------------------
+void chol_inverse(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs, at::Tensor damping) {
+  const int count = static_cast<int>(mats.size());
+  TORCH_CHECK(count > 0 && outs.size() == mats.size(), "mats and outs must have the same length");
+  TORCH_CHECK(damping.is_cuda() && damping.scalar_type() == at::kFloat && damping.is_contiguous() &&
+                  damping.numel() == count, "damping must be a CUDA fp32 vector with one entry per matrix");
+  const int dev = mats[0].get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+
+  // process the matrices in order of decreasing size so that "still active at block k" is a prefix
+  std::vector<int> order(count);
+  for (int i = 0; i < count; ++i) order[i] = i;
+  std::stable_sort(order.begin(), order.end(),
+                   [&](int a, int b) { return mats[a].size(0) > mats[b].size(0); });
+  size_t x_total = 0, d_total = 0;
+  for (int i = 0; i < count; ++i) {
+    const at::Tensor& a = mats[i];
+    const at::Tensor& o = outs[i];
+    TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kFloat && a.dim() == 2 && a.size(0) == a.size(1) &&
+                    a.stride(1) == 1, "matrices must be square fp32 CUDA tensors with unit column stride");
+    TORCH_CHECK(o.is_cuda() && o.scalar_type() == at::kFloat && o.is_contiguous() && o.sizes() == a.sizes(),
+                "outputs must be contiguous fp32 tensors of the same shape");
+    TORCH_CHECK(o.data_ptr() != a.data_ptr(), "the inverse cannot be written over its input");
+    const size_t n = a.size(0), nb = (n + CB - 1) / CB;
+    x_total += n * n;
+    d_total += nb * CB * CB;
+  }
+  auto f32 = at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, dev);
+  at::Tensor x_buf = at::empty({static_cast<int64_t>(x_total)}, f32);
+  at::Tensor d_buf = at::empty({static_cast<int64_t>(d_total)}, f32);
+  at::Tensor damp_sorted = at::empty({count}, f32);
+
+  std::vector<CholMat> host(count);
+  std::vector<int64_t> perm(count);
+  size_t x_off = 0, d_off = 0;
+  int nb_max = 0;
+  for (int s = 0; s < count; ++s) {
+    const int i = order[s];
+    perm[s] = i;
+    CholMat& M = host[s];
+    M.A = mats[i].data_ptr<float>();
+    M.lda = static_cast<int>(mats[i].stride(0));
+    M.L = outs[i].data_ptr<float>();
+    M.n = static_cast<int>(mats[i].size(0));
+    M.nb = (M.n + CB - 1) / CB;
+    M.X = x_buf.data_ptr<float>() + x_off;
+    M.D = d_buf.data_ptr<float>() + d_off;
+    M.pad = 0;
+    x_off += static_cast<size_t>(M.n) * M.n;
+    d_off += static_cast<size_t>(M.nb) * CB * CB;
+    nb_max = std::max(nb_max, M.nb);
+  }
+  at::Tensor desc = at::empty({static_cast<int64_t>(count * sizeof(CholMat))},
+                              at::TensorOptions().dtype(at::kByte).device(at::kCUDA, dev));
+  B200_CUDA_CHECK(cudaMemcpyAsync(desc.data_ptr(), host.data(), count * sizeof(CholMat),
+                                  cudaMemcpyHostToDevice, stream));
+  at::Tensor perm_t = at::tensor(perm, at::TensorOptions().dtype(at::kLong)).to(damping.device());
+  damp_sorted.copy_(damping.index_select(0, perm_t));
+  const CholMat* dm = reinterpret_cast<const CholMat*>(desc.data_ptr());
+  int* status = device_state(dev).status.data_ptr<int>();
+
+  auto active = [&](int k) {  // number of matrices (prefix of the sorted order) with nb > k
+    int c = 0;
+    while (c < count && host[c].nb > k) ++c;
+    return c;
+  };
+
+  chol_prepare_kernel<<<dim3(64, count), 256, 0, stream>>>(dm, damp_sorted.data_ptr<float>());
+  count_launch();
+  for (int k = 0; k < nb_max; ++k) {
+    const int na = active(k);
+    chol_diag_kernel<<<na, 256, 0, stream>>>(dm, k, status);
+    count_launch();
+    const int below = host[0].nb - k - 1;
+    const int nb1 = active(k + 1);
+    if (below > 0 && nb1 > 0) {
+      chol_panel_kernel<<<dim3(below, nb1), 256, 0, stream>>>(dm, k);
+      chol_trailing_kernel<<<dim3(below * (below + 1) / 2, nb1), 256, 0, stream>>>(dm, k);
+      count_launch(2);
+    }
+  }
+  for (int d = 1; d < nb_max; ++d) {
+    const int na = active(d);
+    if (na == 0) break;
+    trtri_level_kernel<<<dim3(host[0].nb - d, na), 256, 0, stream>>>(dm, d);
+    count_launch();
+  }
+  lauum_kernel<<<dim3(host[0].nb * (host[0].nb + 1) / 2, count), 256, 0, stream>>>(dm);
+  count_launch();
+  B200_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace b200

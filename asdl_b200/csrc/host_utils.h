@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <torch/extension.h>
 
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
@@ -55,6 +56,13 @@ inline void encode_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inn
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", static_cast<int>(r));
 }
+
+// Number of kernels of this extension launched so far in this process (all devices).
+inline std::atomic<long long>& launch_counter() {
+  static std::atomic<long long> n{0};
+  return n;
+}
+inline void count_launch(int n = 1) { launch_counter().fetch_add(n, std::memory_order_relaxed); }
 
 // Per-device persistent buffers: scratch for split-K partials and the status word.
 struct DeviceState {

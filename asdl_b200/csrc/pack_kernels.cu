@@ -69,6 +69,7 @@ void cast_pad_bf16(at::Tensor src, at::Tensor hi, c10::optional<at::Tensor> lo, 
     TORCH_CHECK(false, "unsupported source dtype");
   }
   B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
 }
 
 struct Im2colParams {
@@ -83,7 +84,7 @@ struct Im2colParams {
 // Scalar path: one thread per output element (coalesced along the output row).
 template <typename T>
 __global__ void im2col_generic_kernel(const T* __restrict__ x, __nv_bfloat16* __restrict__ out,
-                                      Im2colParams p) {
+                                      __nv_bfloat16* __restrict__ out_lo, Im2colParams p) {
   const long long rows = static_cast<long long>(p.N) * p.Ho * p.Wo;
   const long long total = rows * p.ldo;
   const int ncols = p.C * p.KH * p.KW;
@@ -114,7 +115,9 @@ __global__ void im2col_generic_kernel(const T* __restrict__ x, __nv_bfloat16* __
       if (hi >= 0 && hi < p.H && wi >= 0 && wi < p.W)
         v = to_f32<T>(x[n * p.sN + c * p.sC + hi * p.sH + wi * p.sW]);
     }
-    out[i] = __float2bfloat16_rn(v);
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    out[i] = h;
+    if (out_lo != nullptr) out_lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
   }
 }
 
@@ -147,9 +150,9 @@ __global__ void im2col_nhwc_vec8_kernel(const __nv_bfloat16* __restrict__ x,
 }
 
 // x: 4-D conv input [N, C, H, W] (logical), any memory format.  out: [N*Ho*Wo, ld] bf16, contiguous.
-void im2col_bf16(at::Tensor x, at::Tensor out, std::vector<int64_t> kernel,
-                 std::vector<int64_t> stride, std::vector<int64_t> padding,
-                 std::vector<int64_t> dilation, bool c_major) {
+void im2col_bf16(at::Tensor x, at::Tensor out, c10::optional<at::Tensor> out_lo,
+                 std::vector<int64_t> kernel, std::vector<int64_t> stride,
+                 std::vector<int64_t> padding, std::vector<int64_t> dilation, bool c_major) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 4, "x must be a 4-D CUDA tensor");
   TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == at::kBFloat16 &&
                   out.dim() == 2, "out must be contiguous 2-D bf16");
@@ -169,8 +172,14 @@ void im2col_bf16(at::Tensor x, at::Tensor out, std::vector<int64_t> kernel,
   c10::cuda::CUDAGuard guard(x.get_device());
   auto stream = at::cuda::getCurrentCUDAStream().stream();
   auto* out_p = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  __nv_bfloat16* lo_p = nullptr;
+  if (out_lo.has_value()) {
+    TORCH_CHECK(out_lo->sizes() == out.sizes() && out_lo->is_contiguous() &&
+                    out_lo->scalar_type() == at::kBFloat16, "out_lo must match out");
+    lo_p = reinterpret_cast<__nv_bfloat16*>(out_lo->data_ptr());
+  }
   const int threads = 256;
-  const bool vec = !c_major && x.scalar_type() == at::kBFloat16 && p.sC == 1 && (p.C % 8) == 0 &&
+  const bool vec = lo_p == nullptr && !c_major && x.scalar_type() == at::kBFloat16 && p.sC == 1 && (p.C % 8) == 0 &&
                    p.ldo == static_cast<long long>(p.C) * p.KH * p.KW && (p.sW % 8) == 0 &&
                    (p.sH % 8) == 0 && (p.sN % 8) == 0 &&
                    (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0;
@@ -183,17 +192,18 @@ void im2col_bf16(at::Tensor x, at::Tensor out, std::vector<int64_t> kernel,
     const long long total = rows * p.ldo;
     const int blocks = static_cast<int>(std::min<long long>((total + threads - 1) / threads, 148 * 32));
     if (x.scalar_type() == at::kFloat)
-      im2col_generic_kernel<float><<<blocks, threads, 0, stream>>>(x.data_ptr<float>(), out_p, p);
+      im2col_generic_kernel<float><<<blocks, threads, 0, stream>>>(x.data_ptr<float>(), out_p, lo_p, p);
     else if (x.scalar_type() == at::kBFloat16)
       im2col_generic_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
-          reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), out_p, p);
+          reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), out_p, lo_p, p);
     else if (x.scalar_type() == at::kHalf)
       im2col_generic_kernel<__half><<<blocks, threads, 0, stream>>>(
-          reinterpret_cast<const __half*>(x.data_ptr()), out_p, p);
+          reinterpret_cast<const __half*>(x.data_ptr()), out_p, lo_p, p);
     else
       TORCH_CHECK(false, "unsupported input dtype");
   }
   B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
 }
 
 }  // namespace b200

@@ -1,0 +1,203 @@
+// Collectives over NVLink peer memory for buffers that every rank allocated symmetrically (the
+// same size at the same offset on every GPU, mapped into every rank's address space).
+//
+//   symm_barrier          all ranks meet: each rank stores an epoch into its slot on every peer
+//                         (st.release.sys) and waits until all of its own slots carry that epoch
+//                         (ld.acquire.sys).  Every wait is bounded in wall time; on expiry the
+//                         status word is set to ERR_WAIT_PEER and the kernel returns.
+//   symm_reduce_segments  the calling rank pulls the listed segments from every peer with plain
+//                         peer loads, sums them, scales, and stores the result locally
+//                         (reduce-to-owner of gradients / statistics).
+//   symm_bcast_segments   the calling rank stores the listed segments into every peer's copy
+//                         (broadcast-from-owner of preconditioned gradients).
+//   symm_scale_segments   local beta-scaling of segments (moving-average decay of owned factors).
+//
+// The first SYMM_FLAG_WORDS 32-bit words of the symmetric buffer are reserved for the barrier
+// slots: word [s * 64 + r] of rank q is "rank r has reached epoch of barrier stream s"; word
+// [s * 64 + 63] counts the barriers this rank has entered on stream s.
+// Peer data is always accessed with plain loads/stores issued by each thread; no TMA and no
+// cluster multicast is involved.
+#include "host_utils.h"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+constexpr int SYMM_FLAG_WORDS = 256;
+
+struct Seg {
+  long long off;    // element offset inside the symmetric buffer (fp32 elements)
+  long long numel;  // multiple of 4
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_peer_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_peer_f4(float* p, float4 v) {
+  asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y),
+               "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
+__global__ void symm_barrier_kernel(const long long* peers, int rank, int world, int slot,
+                                    int* status) {
+  // The epoch lives in this rank's own flag area (word 63 of the slot), so the kernel carries no
+  // per-call argument and can be replayed from a CUDA graph.
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) {
+    uint32_t* counter = reinterpret_cast<uint32_t*>(peers[rank]) + slot * 64 + 63;
+    s_epoch = *counter + 1;
+    *counter = s_epoch;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  __threadfence_system();
+  uint32_t* remote = reinterpret_cast<uint32_t*>(peers[t]) + slot * 64 + rank;
+  st_release_sys(remote, epoch);
+  const uint32_t* mine = reinterpret_cast<const uint32_t*>(peers[rank]) + slot * 64 + t;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
+    if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > B200_WAIT_NS) {
+      set_error(status, ERR_WAIT_PEER);
+      return;
+    }
+  }
+}
+
+__global__ void symm_reduce_segments_kernel(const long long* peers, int rank, int world,
+                                            const Seg* segs, float scale) {
+  const Seg s = segs[blockIdx.y];
+  float* local = reinterpret_cast<float*>(peers[rank]) + s.off;
+  const long long n4 = s.numel >> 2;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float4 v = ld_peer_f4(reinterpret_cast<const float*>(peers[r]) + s.off + 4 * i);
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    acc.x *= scale;
+    acc.y *= scale;
+    acc.z *= scale;
+    acc.w *= scale;
+    *reinterpret_cast<float4*>(local + 4 * i) = acc;
+  }
+}
+
+__global__ void symm_bcast_segments_kernel(const long long* peers, int rank, int world, const Seg* segs) {
+  const Seg s = segs[blockIdx.y];
+  const float* local = reinterpret_cast<const float*>(peers[rank]) + s.off;
+  const long long n4 = s.numel >> 2;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 v = *reinterpret_cast<const float4*>(local + 4 * i);
+    for (int r = 0; r < world; ++r)
+      if (r != rank) st_peer_f4(reinterpret_cast<float*>(peers[r]) + s.off + 4 * i, v);
+  }
+}
+
+__global__ void symm_scale_segments_kernel(float* base, const Seg* segs, float beta) {
+  const Seg s = segs[blockIdx.y];
+  float* p = base + s.off;
+  const long long n4 = s.numel >> 2;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 v = *reinterpret_cast<float4*>(p + 4 * i);
+    v.x *= beta;
+    v.y *= beta;
+    v.z *= beta;
+    v.w *= beta;
+    *reinterpret_cast<float4*>(p + 4 * i) = v;
+  }
+}
+
+// ---- host ------------------------------------------------------------------------------------
+static void check_table(const at::Tensor& peers, int world) {
+  TORCH_CHECK(peers.is_cuda() && peers.scalar_type() == at::kLong && peers.is_contiguous() &&
+                  peers.numel() == world, "peers must be a CUDA int64 vector with one pointer per rank");
+}
+static void check_segs(const at::Tensor& segs) {
+  TORCH_CHECK(segs.is_cuda() && segs.scalar_type() == at::kLong && segs.is_contiguous() &&
+                  segs.dim() == 2 && segs.size(1) == 2, "segments must be a CUDA int64 [k, 2] tensor");
+}
+
+void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot) {
+  check_table(peers, static_cast<int>(world));
+  TORCH_CHECK(world <= 63 && slot >= 0 && slot * 64 + 64 <= SYMM_FLAG_WORDS, "bad barrier slot");
+  const int dev = peers.get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  symm_barrier_kernel<<<1, 64, 0, stream>>>(reinterpret_cast<const long long*>(peers.data_ptr<int64_t>()),
+                                            static_cast<int>(rank), static_cast<int>(world),
+                                            static_cast<int>(slot),
+                                            device_state(dev).status.data_ptr<int>());
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
+void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale) {
+  check_table(peers, static_cast<int>(world));
+  check_segs(segs);
+  if (segs.size(0) == 0) return;
+  const int dev = peers.get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  dim3 grid(148, static_cast<unsigned>(segs.size(0)));
+  symm_reduce_segments_kernel<<<grid, 256, 0, stream>>>(
+      reinterpret_cast<const long long*>(peers.data_ptr<int64_t>()), static_cast<int>(rank),
+      static_cast<int>(world), reinterpret_cast<const Seg*>(segs.data_ptr<int64_t>()),
+      static_cast<float>(scale));
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
+void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs) {
+  check_table(peers, static_cast<int>(world));
+  check_segs(segs);
+  if (segs.size(0) == 0) return;
+  const int dev = peers.get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  dim3 grid(148, static_cast<unsigned>(segs.size(0)));
+  symm_bcast_segments_kernel<<<grid, 256, 0, stream>>>(
+      reinterpret_cast<const long long*>(peers.data_ptr<int64_t>()), static_cast<int>(rank),
+      static_cast<int>(world), reinterpret_cast<const Seg*>(segs.data_ptr<int64_t>()));
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
+void symm_scale_segments(at::Tensor local, at::Tensor segs, double beta) {
+  TORCH_CHECK(local.is_cuda() && local.scalar_type() == at::kFloat && local.is_contiguous(),
+              "local must be a contiguous fp32 CUDA tensor");
+  check_segs(segs);
+  if (segs.size(0) == 0) return;
+  const int dev = local.get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  dim3 grid(148, static_cast<unsigned>(segs.size(0)));
+  symm_scale_segments_kernel<<<grid, 256, 0, stream>>>(
+      local.data_ptr<float>(), reinterpret_cast<const Seg*>(segs.data_ptr<int64_t>()),
+      static_cast<float>(beta));
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
+}  // namespace b200

@@ -29,7 +29,8 @@ void gemm_fill_problem(GemmProblem& P, const std::vector<at::Tensor>& a_segs,
                        const std::vector<at::Tensor>& b_segs, bool a_kmajor, bool b_kmajor,
                        const c10::optional<at::Tensor>& C, double alpha, double beta, bool sym,
                        const c10::optional<at::Tensor>& out_hi,
-                       const c10::optional<at::Tensor>& out_lo, int64_t nsplit_req, int n_sms) {
+                       const c10::optional<at::Tensor>& out_lo, int64_t nsplit_req, int n_sms,
+                       bool allow_no_output = false) {
   const int nseg = static_cast<int>(a_segs.size());
   TORCH_CHECK(nseg >= 1 && nseg <= 3 && b_segs.size() == a_segs.size(),
               "between 1 and 3 operand segments are supported");
@@ -94,7 +95,7 @@ void gemm_fill_problem(GemmProblem& P, const std::vector<at::Tensor>& a_segs,
       P.out_lo = reinterpret_cast<__nv_bfloat16*>(out_lo->data_ptr());
     }
   }
-  TORCH_CHECK(P.C != nullptr || P.out_hi != nullptr, "no output given");
+  TORCH_CHECK(allow_no_output || P.C != nullptr || P.out_hi != nullptr, "no output given");
 
   P.tiles_m = (P.M + G_BM - 1) / G_BM;
   P.tiles_n = (P.N + G_BN - 1) / G_BN;
@@ -117,7 +118,7 @@ void gemm_attach_scratch(GemmProblem& P, int dev) {
   DeviceState& st = device_state(dev);
   P.status = st.status.data_ptr<int>();
   const int slot = dev & 15;
-  if (P.nsplit > 1) {
+  if (P.nsplit > 1 && !(P.flags & GF_ATOMIC)) {
     const size_t need = static_cast<size_t>(P.ntiles) * P.nsplit * G_BM * G_BN;
     const size_t cap_min = need * 4;
     float* base = ensure_scratch(dev, cap_min);
@@ -138,10 +139,12 @@ void gemm_launch_single(const GemmProblem& P, cudaStream_t stream) {
   dim3 grid(P.ntiles, P.nsplit, 1);
   umma_gemm_kernel<<<grid, G_THREADS, G_SMEM_BYTES, stream>>>(P, nullptr, nullptr);
   B200_CUDA_CHECK(cudaGetLastError());
-  if (P.nsplit > 1) {
+  count_launch();
+  if (P.nsplit > 1 && !(P.flags & GF_ATOMIC)) {
     dim3 rgrid(P.ntiles, 16, 1);
     splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(P, nullptr, nullptr);
     B200_CUDA_CHECK(cudaGetLastError());
+    count_launch();
   }
 }
 
@@ -161,6 +164,37 @@ void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, b
   gemm_launch_single(P, at::cuda::getCurrentCUDAStream(dev).stream());
 }
 
+// Variant whose fp32 result goes to raw device addresses - typically symmetric-memory buffers of
+// this or another GPU.  `dst_ptr` receives the result (accumulated with reductions when `atomic`),
+// `extra_ptrs` receive plain copies of it (non-atomic mode only).  All destinations use `ldc`.
+void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
+                      bool b_kmajor, int64_t dst_ptr, int64_t ldc, double alpha, bool sym, bool atomic,
+                      std::vector<int64_t> extra_ptrs, int64_t nsplit) {
+  TORCH_CHECK(!a_segs.empty(), "no operands");
+  TORCH_CHECK(dst_ptr != 0 && (dst_ptr & 15) == 0, "destination must be a 16-byte aligned device address");
+  TORCH_CHECK(static_cast<int>(extra_ptrs.size()) <= G_MAX_EXTRA, "too many extra destinations");
+  TORCH_CHECK(!(atomic && !extra_ptrs.empty()), "extra destinations are not supported in atomic mode");
+  const int dev = a_segs[0].get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  const int n_sms = at::cuda::getDeviceProperties(dev)->multiProcessorCount;
+  GemmProblem P;
+  // a dummy bf16 output satisfies the "some output" check; it is cleared again below
+  gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, c10::nullopt, alpha, 0.0, sym,
+                    c10::nullopt, c10::nullopt, nsplit, n_sms, /*allow_no_output=*/true);
+  P.C = reinterpret_cast<float*>(dst_ptr);
+  P.Cin = P.C;
+  P.ldc = static_cast<int>(ldc);
+  TORCH_CHECK(P.ldc >= P.N, "ldc is smaller than the number of columns");
+  if (atomic) P.flags |= GF_ATOMIC;
+  P.n_extra = static_cast<int>(extra_ptrs.size());
+  for (int e = 0; e < P.n_extra; ++e) {
+    TORCH_CHECK((extra_ptrs[e] & 15) == 0, "destinations must be 16-byte aligned");
+    P.C_extra[e] = reinterpret_cast<float*>(extra_ptrs[e]);
+  }
+  gemm_attach_scratch(P, dev);
+  gemm_launch_single(P, at::cuda::getCurrentCUDAStream(dev).stream());
+}
+
 // Reads and clears the device status word (synchronises the current stream).
 int64_t read_status(int64_t dev) {
   c10::cuda::CUDAGuard guard(static_cast<int>(dev));
@@ -169,6 +203,8 @@ int64_t read_status(int64_t dev) {
   if (v != 0) st.status.zero_();
   return v;
 }
+
+int64_t launch_count() { return static_cast<int64_t>(launch_counter().load()); }
 
 void reserve_scratch(int64_t dev, int64_t nfloats) {
   c10::cuda::CUDAGuard guard(static_cast<int>(dev));

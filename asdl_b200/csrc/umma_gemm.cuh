@@ -38,7 +38,10 @@ enum : int {
   GF_A_KMAJOR = 2,   // A given as [M, K] row-major
   GF_B_KMAJOR = 4,   // B given as [N, K] row-major
   GF_SAME_AB = 8,    // A and B are the same matrix (diagonal tiles load once)
+  GF_ATOMIC = 16,    // C += alpha * result with reductions (C may live on another GPU); beta unused
 };
+
+constexpr int G_MAX_EXTRA = 7;  // additional destinations of the result (peer copies)
 
 struct alignas(64) GemmProblem {
   CUtensorMap tmA[3];
@@ -49,6 +52,8 @@ struct alignas(64) GemmProblem {
   __nv_bfloat16* out_lo; // optional bf16 residual (result - hi)
   float* ws;             // split-K scratch: [tiles][nsplit][128][128] fp32
   int* status;           // device error word
+  float* C_extra[G_MAX_EXTRA];  // the fp32 result is also stored here (same ldc), e.g. peer GPUs
+  int n_extra;
   int M, N, K;
   int ldc, ld_out;
   int nseg;
@@ -76,6 +81,47 @@ __device__ __forceinline__ void gemm_decode_tile(const GemmProblem& P, int t, in
 
 __device__ __forceinline__ int gemm_tile_id(const GemmProblem& P, int tm, int tn) {
   return (P.flags & GF_SYM) ? tm * (tm + 1) / 2 + tn : tm * P.tiles_n + tn;
+}
+
+__device__ __forceinline__ void red_add_f32(float* p, float v) {
+  asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_v4_f32(float* p, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b),
+               "f"(c), "f"(d)
+               : "memory");
+}
+
+// Accumulating variant of the final store (GF_ATOMIC): every element is added to C with a
+// reduction instruction, lower tile and mirror image alike, so that several CTAs / GPUs can
+// contribute to the same matrix.
+__device__ __forceinline__ void gemm_reduce_chunk(const GemmProblem& P, const float (&v)[32], int gr,
+                                                  int gc0, bool diag_tile) {
+  if (gr >= P.M) return;
+  const bool sym = (P.flags & GF_SYM) != 0;
+  const float alpha = P.alpha;
+  float* c = P.C + static_cast<size_t>(gr) * P.ldc + gc0;
+  const bool vec_ok = (gc0 + 32 <= P.N) && ((P.ldc & 3) == 0) && !(sym && diag_tile);
+  if (vec_ok) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      red_add_v4_f32(c + 4 * j, alpha * v[4 * j], alpha * v[4 * j + 1], alpha * v[4 * j + 2],
+                     alpha * v[4 * j + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int gc = gc0 + j;
+      if (gc < P.N && !(sym && diag_tile && gc > gr)) red_add_f32(c + j, alpha * v[j]);
+    }
+  }
+  if (sym) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int gc = gc0 + j;
+      if (gc < P.N && (!diag_tile || gc < gr))
+        red_add_f32(P.C + static_cast<size_t>(gc) * P.ldc + gr, alpha * v[j]);
+    }
+  }
 }
 
 // Final store of one 32-column chunk held by this thread (row `gr`, columns gc0..gc0+31).
@@ -145,6 +191,19 @@ __device__ __forceinline__ void gemm_store_chunk(const GemmProblem& P, const flo
           if (gc < gr) P.C[static_cast<size_t>(gc) * P.ldc + gr] = out[j];
         }
       }
+    }
+  }
+  for (int e = 0; e < P.n_extra; ++e) {  // plain (non-symmetric) result replicated to peers
+    float* c = P.C_extra[e] + static_cast<size_t>(gr) * P.ldc + gc0;
+    if (vec_ok) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float4*>(c + 4 * j) =
+            make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (gc0 + j < P.N) c[j] = out[j];
     }
   }
   if (P.out_hi != nullptr) {
@@ -309,7 +368,8 @@ umma_gemm_kernel(const __grid_constant__ GemmProblem single, const GemmProblem* 
     tc_fence_after_sync();
     if (ok) {
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-      if (P.nsplit == 1) {
+      const bool atomic = (P.flags & GF_ATOMIC) != 0;
+      if (P.nsplit == 1 || atomic) {
 #pragma unroll 1
         for (int c = 0; c < G_BN / 32; ++c) {
           float v[32];
@@ -324,7 +384,12 @@ umma_gemm_kernel(const __grid_constant__ GemmProblem single, const GemmProblem* 
             for (int j = 0; j < 32; ++j) v[j] = 0.f;
           }
           const int gc0 = tn * G_BN + c * 32;
-          if (gc0 < P.N && !(diag_tile && gc0 > gr)) gemm_store_chunk(P, v, gr, gc0, diag_tile);
+          if (gc0 < P.N && !(diag_tile && gc0 > gr)) {
+            if (atomic)
+              gemm_reduce_chunk(P, v, gr, gc0, diag_tile);
+            else
+              gemm_store_chunk(P, v, gr, gc0, diag_tile);
+          }
         }
       } else {
         float* part = P.ws + (static_cast<size_t>(tile_id) * P.nsplit + split) * (G_BM * G_BN) +
@@ -409,6 +474,7 @@ splitk_reduce_kernel(const __grid_constant__ GemmProblem single, const GemmProbl
     const bool keep = inb && !(diag_tile && gc > gr);
     if (keep) {
       if (P.C != nullptr) P.C[static_cast<size_t>(gr) * P.ldc + gc] = val;
+      for (int e = 0; e < P.n_extra; ++e) P.C_extra[e][static_cast<size_t>(gr) * P.ldc + gc] = val;
       if (P.out_hi != nullptr) {
         const __nv_bfloat16 h = __float2bfloat16_rn(val);
         P.out_hi[static_cast<size_t>(gr) * P.ld_out + gc] = h;

@@ -19,7 +19,7 @@ import torch
 
 from . import _build
 
-__all__ = ['gram', 'matmul_tn', 'kron_apply', 'spd_inverse', 'unitwise_inverse', 'conv_patch_gram',
+__all__ = ['gram', 'matmul_tn', 'kron_apply', 'spd_inverse', 'spd_inverse_grouped', 'unitwise_inverse', 'conv_patch_gram',
            'set_backend', 'get_backend', 'set_precision', 'get_precision', 'extension',
            'cuda_kernels_enabled', 'check_status']
 
@@ -207,7 +207,8 @@ def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
     ``channels_last_order=False`` orders rows/columns as (c, kh, kw) (matching
     ``weight.view(c_out, -1)``); ``True`` uses (kh, kw, c), the order of a channels_last weight.
     CUDA: a bf16 im2col kernel (vectorised for channels_last inputs) feeds the tcgen05 SYRK; 1x1
-    stride-1 convolutions on channels_last activations need no staging at all."""
+    stride-1 convolutions on channels_last activations need no staging at all.  fp32 inputs are
+    staged as bf16 hi/lo patch pairs and multiplied in three passes (precision policy 'auto')."""
     from ..utils import im2col_2d, _conv_geometry
     (kh, kw), (sh, sw), (ph, pw), (dh, dw) = _conv_geometry(conv)
     if not cuda_kernels_enabled(x):
@@ -227,27 +228,65 @@ def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
         rows = x.permute(0, 2, 3, 1).reshape(n * h * w, c)  # a view: NHWC memory is already [rows, c]
         return gram(rows, scale=scale, out=out, beta=beta)
     ld = _round_up(max(ncol, 8), 8)
+    x3 = _use_x3(x.dtype)
     patches = torch.empty(n * ho * wo, ld, device=x.device, dtype=torch.bfloat16)
-    extension().im2col_bf16(x, patches, [kh, kw], [sh, sw], [ph, pw], [dh, dw],
+    patches_lo = torch.empty_like(patches) if x3 else None
+    extension().im2col_bf16(x, patches, patches_lo, [kh, kw], [sh, sw], [ph, pw], [dh, dw],
                             not channels_last_order)
-    return gram(patches[:, :ncol], scale=scale, out=out, beta=beta)
+    if not x3:
+        return gram(patches[:, :ncol], scale=scale, out=out, beta=beta)
+    hi, lo = patches[:, :ncol], patches_lo[:, :ncol]
+    if out is None:
+        out = torch.empty(ncol, ncol, device=x.device, dtype=torch.float32)
+        beta = 0.0
+    extension().umma_gemm([hi, hi, lo], [hi, lo, hi], False, False, out, float(scale), float(beta),
+                          True, None, None, 0)
+    return out
 
 
 # --------------------------------------------------------------------------------------------
 # inverses
 # --------------------------------------------------------------------------------------------
-def spd_inverse(mat: torch.Tensor, damping: float = 0.0) -> torch.Tensor:
+def spd_inverse(mat: torch.Tensor, damping=0.0) -> torch.Tensor:
     """``(mat + damping*I)^-1`` for symmetric positive (semi-)definite ``mat``; the input is left
-    untouched.  CUDA fp32: the library's blocked Cholesky-inverse kernels."""
-    n = mat.shape[-1]
-    if cuda_kernels_enabled(mat) and mat.dtype == torch.float32 and mat.ndim == 2 \
-            and hasattr(extension(), 'chol_inverse'):
-        out = torch.empty_like(mat)
-        extension().chol_inverse([mat], [out], [float(damping)])
+    untouched.  ``damping`` may be a Python number or a 0-d / 1-element tensor (kept on the
+    device).  CUDA fp32: the library's grouped blocked Cholesky-inverse kernels."""
+    if cuda_kernels_enabled(mat) and mat.dtype == torch.float32 and mat.ndim == 2:
+        out = torch.empty(mat.shape, device=mat.device, dtype=torch.float32)
+        spd_inverse_grouped([mat], [out], damping)
         return out
+    n = mat.shape[-1]
     eye = torch.eye(n, device=mat.device, dtype=mat.dtype)
     chol = torch.linalg.cholesky(mat + damping * eye)
     return torch.cholesky_inverse(chol)
+
+
+def spd_inverse_grouped(mats, outs, damping):
+    """``outs[i] <- (mats[i] + damping[i]*I)^-1`` for a list of square fp32 matrices of arbitrary
+    sizes.  ``damping``: one number for all, a list of numbers, or a device tensor with one entry
+    per matrix (no host synchronisation).  On CUDA all matrices advance together through one
+    sequence of grouped kernel launches."""
+    count = len(mats)
+    if count == 0:
+        return outs
+    dev = mats[0].device
+    if isinstance(damping, torch.Tensor):
+        damp = damping.to(device=dev, dtype=torch.float32).reshape(-1)
+        if damp.numel() == 1 and count > 1:
+            damp = damp.expand(count)
+        damp = damp.contiguous()
+    elif isinstance(damping, (list, tuple)):
+        damp = torch.tensor([float(d) for d in damping], device=dev, dtype=torch.float32)
+    else:
+        damp = torch.full((count,), float(damping), device=dev, dtype=torch.float32)
+    if cuda_kernels_enabled(*mats) and all(m.dtype == torch.float32 for m in mats):
+        mats = [m if m.stride(-1) == 1 else m.contiguous() for m in mats]
+        extension().chol_inverse(list(mats), list(outs), damp)
+        return outs
+    for m, o, d in zip(mats, outs, damp):
+        eye = torch.eye(m.shape[-1], device=m.device, dtype=m.dtype)
+        o.copy_(torch.cholesky_inverse(torch.linalg.cholesky(m + d.to(m.dtype) * eye)))
+    return outs
 
 
 def unitwise_inverse(blocks: torch.Tensor, damping: float = 0.0) -> torch.Tensor:

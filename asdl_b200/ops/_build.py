@@ -62,6 +62,7 @@ def is_built():
 def build(verbose=False):
     """Compile every .cu under csrc/ for sm_100a (cross-compiles without a GPU)."""
     from torch.utils import cpp_extension
+    digest = _digest()  # of the sources as they are now, not as they are when the build ends
     os.makedirs(_BUILD, exist_ok=True)
     os.environ.setdefault('TORCH_CUDA_ARCH_LIST', '10.0a')
     os.environ.setdefault('MAX_JOBS', str(min(8, os.cpu_count() or 4)))
@@ -69,7 +70,7 @@ def build(verbose=False):
                        extra_cflags=['-O3', '-std=c++17'], build_directory=_BUILD,
                        verbose=verbose, is_python_module=False)
     with open(os.path.join(_BUILD, 'digest.txt'), 'w') as fh:
-        fh.write(_digest())
+        fh.write(digest)
 
 
 def load(allow_build=True):

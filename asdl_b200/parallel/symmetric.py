@@ -1,0 +1,91 @@
+"""Symmetric NVLink-visible memory and the collectives that run on it.
+
+A :class:`SymmetricArena` is one fp32 buffer allocated with the same size on every rank of a
+process group (``torch.distributed._symmetric_memory`` does the allocation and the exchange of
+handles); every rank can address every peer's copy.  The library's own kernels do the rest:
+bounded-wait barriers, pull-reductions to an owner, push-broadcasts from an owner, and GEMM
+epilogues that add tiles into a peer's buffer or replicate results to all peers
+(asdl_b200/csrc/symm_collectives.cu, asdl_b200/csrc/umma_gemm.cuh).
+
+Replaces the packed ``dist.reduce`` / ``dist.broadcast`` calls of the reference
+(asdl/precondition/natural_gradient.py:603-757).
+"""
+from typing import List, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+
+__all__ = ['SymmetricArena']
+
+FLAG_WORDS = 256  # must match SYMM_FLAG_WORDS in csrc/symm_collectives.cu
+_ALIGN = 64       # elements (256 bytes)
+
+
+def _round_up(v, m):
+    return (v + m - 1) // m * m
+
+
+class SymmetricArena:
+    """Bump allocator over one symmetric fp32 buffer.
+
+    Every rank has to make the same sequence of ``alloc`` calls, so that a tensor has the same
+    offset on all ranks.  ``ptr(rank, offset)`` is the device address of that offset in
+    ``rank``'s copy, valid in this process.
+    """
+
+    def __init__(self, numel: int, group=None, device=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.device = torch.device('cuda', torch.cuda.current_device()) if device is None else device
+        self.capacity = _round_up(int(numel), _ALIGN)
+        self.buffer = symm_mem.empty(FLAG_WORDS + self.capacity, dtype=torch.float32, device=self.device)
+        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        self.rank = self.handle.rank
+        self.world = self.handle.world_size
+        self.peer_ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        self.peers_dev = torch.tensor(self.peer_ptrs, dtype=torch.int64, device=self.device)
+        self.buffer.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        self._cursor = 0
+
+    # allocation --------------------------------------------------------------------------------
+    def alloc(self, *shape) -> Tuple[int, torch.Tensor]:
+        """(offset in elements from the start of the buffer, zero-initialised view)."""
+        numel = 1
+        for s in shape:
+            numel *= int(s)
+        start = self._cursor
+        if start + numel > self.capacity:
+            raise RuntimeError(f'symmetric arena exhausted: need {start + numel}, have {self.capacity}')
+        self._cursor = _round_up(start + numel, _ALIGN)
+        offset = FLAG_WORDS + start
+        return offset, self.buffer[offset:offset + numel].view(*shape)
+
+    def ptr(self, rank: int, offset: int) -> int:
+        return self.peer_ptrs[rank] + 4 * offset
+
+    def segments(self, pairs: Sequence[Tuple[int, int]]) -> torch.Tensor:
+        """Device table of (offset, numel rounded up to 4) rows for the segment kernels."""
+        rows = [[int(o), _round_up(int(n), 4)] for o, n in pairs]
+        return torch.tensor(rows, dtype=torch.int64, device=self.device).reshape(-1, 2)
+
+    # collectives -------------------------------------------------------------------------------
+    def barrier(self, slot: int = 0):
+        """All ranks' work issued before the barrier (on the current stream) is complete and
+        visible to all peers after it.  The wait is bounded; a timeout is reported through
+        :func:`asdl_b200.ops.check_status`."""
+        ops.extension().symm_barrier(self.peers_dev, self.rank, self.world, slot)
+
+    def reduce_segments(self, segs: torch.Tensor, scale: float):
+        """local[seg] <- scale * sum over ranks of their [seg] (pull over NVLink)."""
+        ops.extension().symm_reduce_segments(self.peers_dev, self.rank, self.world, segs, float(scale))
+
+    def bcast_segments(self, segs: torch.Tensor):
+        """every peer's [seg] <- local[seg] (push over NVLink)."""
+        ops.extension().symm_bcast_segments(self.peers_dev, self.rank, self.world, segs)
+
+    def scale_segments(self, segs: torch.Tensor, beta: float):
+        ops.extension().symm_scale_segments(self.buffer, segs, float(beta))

@@ -97,13 +97,20 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             that apply the inverses.
         clone_norm_outputs: copy normalisation-layer outputs in the statistics hook (needed only
             if the model modifies them in place afterwards, e.g. ``ReLU(inplace=True)``).
+        cuda_graph: replay steps that update neither curvature nor inverses (forward, loss,
+            backward and preconditioning) from a CUDA graph.  The registered tensor arguments are
+            copied into static buffers before every replay, ``param.grad`` is (re)bound to static
+            gradient tensors that each replay overwrites (so gradients are not accumulated across
+            calls in this mode), and the returned output / loss are static tensors as well.
+            Single-process CUDA runs only; anything else silently uses the eager path.
     Embedding layers are not handled here; list them in ``config.ignore_modules``.
     """
 
     def __init__(self, model, config: PreconditioningConfig, fisher_type: str = FISHER_MC,
                  loss_type: str = LOSS_CROSS_ENTROPY, scale: float = 1, grad_scale: float = 1,
                  n_mc_samples: int = 1, var: float = 1., seed: int = None,
-                 precond_precision: str = 'bf16x3', clone_norm_outputs: bool = False, **kwargs):
+                 precond_precision: str = 'bf16x3', clone_norm_outputs: bool = False,
+                 cuda_graph: bool = False, **kwargs):
         if fisher_type not in (FISHER_MC, FISHER_EMP):
             raise ValueError('FusedKfacGradientMaker supports fisher_mc and fisher_emp.')
         if loss_type != LOSS_CROSS_ENTROPY and fisher_type == FISHER_MC:
@@ -126,6 +133,113 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                                  f'fused K-FAC path; add it to config.ignore_modules.')
         self._by_module: Dict[nn.Module, object] = {s.module: s for s in self._kron + self._norm}
         self._bf16_cache = {}
+        self._graph_enabled = bool(cuda_graph) and device.type == 'cuda' and self.world_size == 1
+        self._graph = None
+        self._graph_key = None
+        self._plain_steps_seen = 0
+        if self._graph_enabled:
+            ops.extension().reserve_scratch(device.index or 0, 64 << 20)
+
+    # ------------------------------------------------------------------ CUDA-graph replay
+    def _tensor_slots(self):
+        """(container, key) of every tensor among the registered model / loss arguments."""
+        slots = []
+        for container in (self._model_args, self._model_kwargs, self._loss_fn_args, self._loss_fn_kwargs):
+            items = container.items() if isinstance(container, dict) else enumerate(container)
+            for key, value in items:
+                if isinstance(value, torch.Tensor):
+                    slots.append((container, key, value))
+        return slots
+
+    def forward_and_backward(self):
+        step = self.state['step']
+        plain = not self.do_update_curvature(step) and not self.do_update_preconditioner(step)
+        ready = all(st.has_inv for st in self._kron) and all(st.has_inv for st in self._norm)
+        if not (self._graph_enabled and plain and ready):
+            return super().forward_and_backward()
+        slots = self._tensor_slots()
+        key = tuple((tuple(v.shape), v.dtype, v.stride()) for _, _, v in slots)
+        if self._graph is None:
+            self._plain_steps_seen += 1
+            if self._plain_steps_seen <= 2:  # let lazy initialisation happen eagerly first
+                return super().forward_and_backward()
+            self._capture(slots, key)
+        elif key != self._graph_key:
+            return super().forward_and_backward()
+        with torch.no_grad():
+            for static, (_, _, value) in zip(self._static_inputs, slots):
+                if static.data_ptr() != value.data_ptr():
+                    static.copy_(value, non_blocking=True)
+        self._graph.replay()
+        for p, g in zip(self._graph_params, self._static_grads):
+            p.grad = g
+        self._model_output, self._loss = self._static_output, self._static_loss
+        self.state['step'] += 1
+        return self._model_output, self._loss
+
+    def _capture(self, slots, key):
+        self._static_inputs = [v.clone() for _, _, v in slots]
+
+        def rebound(container, index_of):
+            if isinstance(container, dict):
+                return {k: (self._static_inputs[index_of[(id(container), k)]]
+                            if (id(container), k) in index_of else v) for k, v in container.items()}
+            return tuple(self._static_inputs[index_of[(id(container), i)]]
+                         if (id(container), i) in index_of else v for i, v in enumerate(container))
+
+        index_of = {(id(c), k): i for i, (c, k, _) in enumerate(slots)}
+        saved = (self._model_args, self._model_kwargs, self._loss_fn_args, self._loss_fn_kwargs)
+        self._model_args, self._model_kwargs, self._loss_fn_args, self._loss_fn_kwargs = (
+            rebound(c, index_of) for c in saved)
+        self._graph_params = [p for p in self.model.parameters() if p.requires_grad]
+        # Inside the capture the model runs on fresh leaf views of its parameters.  Autograd's
+        # gradient accumulators remember the stream they were created on - for the real
+        # parameters that may be the legacy default stream, which a capture must not touch, and
+        # they stay alive as long as anybody holds an output of an earlier step.  Views created
+        # here get their accumulators on the capture stream.  Gradients come from autograd.grad
+        # and are bound to param.grad by hand.  Two warm-up rounds run on the capture stream
+        # first; buffers that the forward pass updates (running statistics) are restored after.
+        from torch.nn.utils.stateless import _reparametrize_module
+        names = [n for n, p in self.model.named_parameters() if p.requires_grad]
+
+        def plain_step():
+            views = [p.detach().requires_grad_(True) for p in self._graph_params]
+            with _reparametrize_module(self.model, dict(zip(names, views))):
+                self.forward()
+            grads = torch.autograd.grad(self._loss, views, allow_unused=True)
+            for p, g in zip(self._graph_params, grads):
+                p.grad = g if g is not None else torch.zeros_like(p)
+            self._loss = self._loss.detach()
+            if isinstance(self._model_output, torch.Tensor):
+                self._model_output = self._model_output.detach()
+            self.precondition()
+
+        stream = torch.cuda.Stream()
+        buffers = [b for b in self.model.buffers()]
+        saved_buffers = [b.detach().clone() for b in buffers]
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                for p in self._graph_params:
+                    p.grad = None
+                plain_step()
+        torch.cuda.current_stream().wait_stream(stream)
+        with torch.no_grad():
+            for b, s_ in zip(buffers, saved_buffers):
+                b.copy_(s_)
+        for p in self._graph_params:
+            p.grad = None
+        self._model_output = self._loss = None
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(graph, stream=stream):
+                plain_step()
+        finally:
+            self._model_args, self._model_kwargs, self._loss_fn_args, self._loss_fn_kwargs = saved
+        self._static_grads = [p.grad for p in self._graph_params]
+        self._static_output, self._static_loss = self._model_output, self._loss
+        self._graph, self._graph_key = graph, key
 
     # ------------------------------------------------------------------ curvature
     def _stat_weights(self):
@@ -268,34 +382,30 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         damping = self.config.damping if damping is None else damping
         root = damping ** 0.5
         with nvtx_range('kfac_inverse'):
-            for st in self._kron:
-                if not self.is_module_for_inv_and_precondition(st.module):
-                    continue
-                tr_a = torch.diagonal(st.A).sum() / st.d_in
-                tr_b = torch.diagonal(st.B).sum() / st.d_out
+            owned = [st for st in self._kron if self.is_module_for_inv_and_precondition(st.module)]
+            if owned:
+                # pi-damping split from the traces, evaluated on the device for all layers at once
+                tr_a = torch.stack([torch.diagonal(st.A).sum() / st.d_in for st in owned])
+                tr_b = torch.stack([torch.diagonal(st.B).sum() / st.d_out for st in owned])
                 pi = torch.sqrt(tr_a / tr_b)
                 ok = torch.isfinite(pi) & (pi > 0)
                 pi = torch.where(ok, pi, torch.ones_like(pi))
-                d_a = torch.where(ok, (root * pi).clamp_min(1e-7), torch.full_like(pi, damping))
-                d_b = torch.where(ok, (root / pi).clamp_min(1e-7), torch.full_like(pi, damping))
-                self._invert(st.A, d_a, st.A_inv)
-                self._invert(st.B, d_b, st.B_inv)
-                st.kron.A_inv, st.kron.B_inv = st.A_inv, st.B_inv
-                st.has_inv = True
-                self._refresh_cache(st)
+                flat = torch.full_like(pi, damping)
+                d_a = torch.where(ok, (root * pi).clamp_min(1e-7), flat)
+                d_b = torch.where(ok, (root / pi).clamp_min(1e-7), flat)
+                mats = [st.A for st in owned] + [st.B for st in owned]
+                outs = [st.A_inv for st in owned] + [st.B_inv for st in owned]
+                ops.spd_inverse_grouped(mats, outs, torch.cat([d_a, d_b]))
+                for st in owned:
+                    st.kron.A_inv, st.kron.B_inv = st.A_inv, st.B_inv
+                    st.has_inv = True
+                    self._refresh_cache(st)
             for st in self._norm:
                 if not self.is_module_for_inv_and_precondition(st.module):
                     continue
                 st.inv.copy_(ops.unitwise_inverse(st.stats, damping))
                 st.unit.inv = st.inv
                 st.has_inv = True
-
-    @staticmethod
-    def _invert(mat, damping_t, out):
-        """out <- (mat + damping*I)^-1 with the damping given as a device scalar."""
-        n = mat.shape[0]
-        eye = torch.eye(n, device=mat.device, dtype=mat.dtype)
-        out.copy_(ops.spd_inverse(mat + damping_t * eye, 0.0))
 
     def _refresh_cache(self, st: _KronState):
         """bf16 hi/lo images of the inverses used by the tensor-core preconditioning products."""

@@ -1,0 +1,294 @@
+"""Headline benchmark: ResNet-50 K-FAC training throughput (images/s) on N B200 GPUs of one node.
+
+    python bench.py --gpus 1 --steps 40 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 40 --warmup 5
+    python bench.py --impl reference ...      # the unmodified reference package, same workload
+
+Workload (both arms): torchvision-topology ResNet-50 with random initialisation, synthetic
+N(0,1) images [32, 3, 224, 224] per GPU and uniform labels over 1000 classes, K-FAC with damping
+1e-3, curvature update every 10 steps, inverse update every 100 steps, factor EMA 0.95
+(``ema_decay=0.05``), Monte-Carlo Fisher, SGD step included.  Weak scaling: the per-GPU batch is
+fixed.  This arm runs bf16 autocast / channels_last with fp32 factors and inverses; the reference
+arm runs its stock fp32 path (its hooks cannot consume bf16 activations).
+
+Two numbers are reported.  ``value`` is timed on the device with CUDA events around exactly K
+steps whose inputs already sit in device memory; ``e2e`` repeats K steps through the same public
+API but copies every step's batch from pinned host memory and reads the loss back to the host.
+One JSON line is printed by rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PER_GPU_BATCH = 32
+NUM_CLASSES = 1000
+IMAGE = (3, 224, 224)
+L2_FLUSH_BYTES = 256 << 20
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=40)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', choices=['ours', 'reference'], default='ours')
+    ap.add_argument('--no-graph', action='store_true', help='disable CUDA-graph replay of plain steps')
+    ap.add_argument('--precond-precision', default='bf16x3', choices=['bf16', 'bf16x3'])
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+             'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+             'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self):
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix='.csv')
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ['nvidia-smi', f'--query-gpu={self.QUERY}', '--format=csv,noheader,nounits', '-lms', '200'],
+                stdout=open(self.path, 'w'), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self, gpu_indices):
+        out = {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        clocks, max_clocks, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(',')]
+                if len(parts) < 9 or not parts[0].isdigit() or int(parts[0]) not in gpu_indices:
+                    continue
+                clocks.append(float(parts[1]))
+                max_clocks.append(float(parts[2]))
+                for name, val in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown',
+                                      'sw_power_cap'), parts[5:9]):
+                    if val.lower().startswith('active'):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if clocks:
+            out['sm_mhz'] = statistics.median(clocks)
+            out['sm_max_mhz'] = max(max_clocks)
+            out['samples'] = len(clocks)
+        out['reasons'] = sorted(reasons)
+        return out
+
+
+def init_distributed(n):
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=torch.device('cuda', local))
+    assert world == n, f'--gpus {n} but WORLD_SIZE={world}'
+    return rank, local, world
+
+
+def make_batches(count, device, seed):
+    g = torch.Generator().manual_seed(seed)
+    xs = [torch.randn(PER_GPU_BATCH, *IMAGE, generator=g).pin_memory() for _ in range(count)]
+    ts = [torch.randint(0, NUM_CLASSES, (PER_GPU_BATCH,), generator=g).pin_memory() for _ in range(count)]
+    return xs, ts
+
+
+# ----------------------------------------------------------------------------------------------
+# the two arms: each returns step(x_dev, t_dev) -> loss tensor, plus a launch counter
+# ----------------------------------------------------------------------------------------------
+def build_ours(args, device, world):
+    import asdl_b200 as asdl
+    from asdl_b200.models import resnet50
+    torch.manual_seed(0)
+    model = resnet50(NUM_CLASSES).to(device).to(memory_format=torch.channels_last)
+    config = asdl.PreconditioningConfig(data_size=PER_GPU_BATCH, damping=1e-3, ema_decay=0.05,
+                                        curvature_upd_interval=10, preconditioner_upd_interval=100)
+    gm = asdl.FusedKfacGradientMaker(model, config, precond_precision=args.precond_precision,
+                                     cuda_graph=not args.no_graph)
+    opt = torch.optim.SGD(model.parameters(), lr=1e-4, momentum=0.9)
+
+    def model_fn(x):
+        with torch.autocast('cuda', dtype=torch.bfloat16):
+            return model(x)
+
+    def step(x, t):
+        opt.zero_grad(set_to_none=False)
+        dummy = gm.setup_model_call(model_fn, x)
+        gm.setup_loss_call(F.cross_entropy, dummy, t)
+        _, loss = gm.forward_and_backward()
+        opt.step()
+        return loss
+
+    def launches():
+        return asdl.ops.extension().launch_count()
+
+    def to_device(x, t):
+        return (x.to(device, non_blocking=True).contiguous(memory_format=torch.channels_last),
+                t.to(device, non_blocking=True))
+
+    return step, launches, to_device, 'bf16'
+
+
+def build_reference(args, device, world):
+    ref_dir = os.path.join(ROOT, 'baseline', '_ref')
+    if not os.path.isdir(os.path.join(ref_dir, 'asdl')):
+        raise ImportError('reference package is not installed under baseline/_ref')
+    sys.path.insert(0, ref_dir)
+    import asdl  # the unmodified reference
+    import torchvision
+    torch.manual_seed(0)
+    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.backends.cudnn.allow_tf32 = True
+    model = torchvision.models.resnet50(num_classes=NUM_CLASSES)
+    for m in model.modules():  # its norm-layer statistics read the layer output after the forward pass
+        if isinstance(m, nn.ReLU):
+            m.inplace = False
+    model = model.to(device)
+    config = asdl.PreconditioningConfig(data_size=PER_GPU_BATCH, damping=1e-3, ema_decay=0.05,
+                                        curvature_upd_interval=10, preconditioner_upd_interval=100)
+    gm = asdl.KfacGradientMaker(model, config)
+    opt = torch.optim.SGD(model.parameters(), lr=1e-4, momentum=0.9)
+
+    def step(x, t):
+        opt.zero_grad(set_to_none=False)
+        dummy = gm.setup_model_call(model, x)
+        gm.setup_loss_call(F.cross_entropy, dummy, t)
+        _, loss = gm.forward_and_backward()
+        opt.step()
+        return loss
+
+    def to_device(x, t):
+        return x.to(device, non_blocking=True), t.to(device, non_blocking=True)
+
+    return step, (lambda: 0), to_device, 'fp32 (tf32 matmul/conv)'
+
+
+def barrier(world):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def main():
+    args = parse_args()
+    if args.impl == 'reference' and not os.path.isdir(os.path.join(ROOT, 'baseline', '_ref', 'asdl')):
+        if int(os.environ.get('RANK', '0')) == 0:
+            print(json.dumps({'impl': 'reference',
+                              'unavailable': 'reference package not installed under baseline/_ref'}))
+        return
+    rank, local, world = init_distributed(args.gpus)
+    device = torch.device('cuda', local)
+    build = build_ours if args.impl == 'ours' else build_reference
+    step, launches, to_device, dtype = build(args, device, world)
+
+    n_host = 8
+    xs, ts = make_batches(n_host, device, seed=1234 + rank)
+    dev_batches = [to_device(x, t) for x, t in zip(xs, ts)]
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+    torch.cuda.synchronize()
+
+    it = 0
+    for _ in range(args.warmup):
+        x, t = dev_batches[it % n_host]
+        step(x, t)
+        it += 1
+
+    # ---- device-timed region: exactly K steps, inputs resident on the device ------------------
+    sampler = ClockSampler()
+    barrier(world)
+    if rank == 0:
+        sampler.start()
+    l0 = launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier(world)
+    e0.record()
+    for _ in range(args.steps):
+        flush.zero_()
+        x, t = dev_batches[it % n_host]
+        loss = step(x, t)
+        it += 1
+    e1.record()
+    barrier(world)
+    ms = e0.elapsed_time(e1)
+    n_launch = launches() - l0
+    clocks = sampler.stop(list(range(world))) if rank == 0 else None
+
+    # ---- end-to-end region: H2D of every batch from pinned memory, loss read back -------------
+    barrier(world)
+    t0 = time.perf_counter()
+    h2d = d2h = 0
+    last = 0.0
+    for _ in range(args.steps):
+        flush.zero_()
+        xh, th = xs[it % n_host], ts[it % n_host]
+        x, t = to_device(xh, th)
+        h2d += xh.numel() * xh.element_size() + th.numel() * th.element_size()
+        loss = step(x, t)
+        last = float(loss.item())
+        d2h += loss.element_size()
+        it += 1
+    barrier(world)
+    e2e_s = time.perf_counter() - t0
+
+    times = torch.tensor([ms, e2e_s * 1e3], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = times.tolist()
+    if rank == 0:
+        global_batch = PER_GPU_BATCH * world
+        value = args.steps * global_batch / (ms / 1e3)
+        e2e_value = args.steps * global_batch / (e2e_ms / 1e3)
+        out = {
+            'metric': 'ResNet-50 K-FAC images/sec', 'value': round(value, 2), 'unit': 'images/s',
+            'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
+            'ms_per_step': round(ms / args.steps, 3), 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': dtype, 'data': 'synthetic N(0,1) images, uniform labels, random-init weights',
+            'impl': args.impl,
+            'config': {'model': 'resnet50', 'global_batch': global_batch, 'per_gpu_batch': PER_GPU_BATCH,
+                       'image': list(IMAGE), 'parallelism': f'dp{world}', 'damping': 1e-3,
+                       'curvature_upd_interval': 10, 'preconditioner_upd_interval': 100,
+                       'ema_decay': 0.05, 'fisher': 'mc', 'optimizer': 'sgd(momentum=0.9) step included',
+                       'l2': 'flushed every step by a 256 MiB memset; per-step activations exceed L2',
+                       'cuda_graph': (not args.no_graph) if args.impl == 'ours' else False},
+            'e2e': {'value': round(e2e_value, 2), 'unit': 'images/s',
+                    'ms_per_step': round(e2e_ms / args.steps, 3),
+                    'h2d_bytes_per_step': h2d // args.steps, 'd2h_bytes_per_step': d2h // args.steps,
+                    'last_loss': last},
+            'gpu_launches': int(n_launch),
+            'clocks': clocks,
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

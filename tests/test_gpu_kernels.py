@@ -1,0 +1,205 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same operation."""
+import copy
+
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+import asdl_b200 as asdl
+from asdl_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = 'cuda'
+
+
+def rel_err(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30)).item()
+
+
+@pytest.fixture(scope='module')
+def ext():
+    e = ops.extension()
+    yield e
+    ops.check_status()
+
+
+@pytest.mark.parametrize('rows,n', [(64, 128), (100, 8), (1000, 200), (777, 152), (4096, 512),
+                                    (8192, 64), (1568, 1024), (33, 17), (5000, 320)])
+@pytest.mark.parametrize('nsplit', [1, 0])
+def test_syrk_bf16(ext, rows, n, nsplit):
+    x = torch.randn(rows, n, device=DEV).to(torch.bfloat16)
+    ld = (n + 7) // 8 * 8
+    buf = torch.zeros(rows, ld, device=DEV, dtype=torch.bfloat16)
+    buf[:, :n] = x
+    c = torch.full((n, n), float('nan'), device=DEV)
+    ext.umma_gemm([buf[:, :n]], [buf[:, :n]], False, False, c, 1.0, 0.0, True, None, None, nsplit)
+    ref = (x.double().T @ x.double()).float()
+    assert rel_err(c, ref) < 1e-4  # the tensor core accumulates long sums with truncation
+    assert torch.equal(c, c.T)
+
+
+def test_syrk_ema_epilogue(ext):
+    rows, n = 2048, 384
+    x = torch.randn(rows, n, device=DEV).to(torch.bfloat16)
+    c0 = torch.randn(n, n, device=DEV)
+    c0 = c0 + c0.T
+    for nsplit in (1, 4):
+        c = c0.clone()
+        ext.umma_gemm([x], [x], False, False, c, 0.05 / rows, 0.95, True, None, None, nsplit)
+        ref = 0.95 * c0 + 0.05 / rows * (x.double().T @ x.double()).float()
+        assert rel_err(c, ref) < 1e-5
+
+
+@pytest.mark.parametrize('m,n,k', [(128, 128, 64), (256, 384, 512), (200, 304, 1000), (512, 4608, 512),
+                                   (64, 2048, 2048), (1000, 2048, 1000)])
+def test_gemm_all_layouts(ext, m, n, k):
+    a = torch.randn(k, m, device=DEV).to(torch.bfloat16)
+    b = torch.randn(k, n, device=DEV).to(torch.bfloat16)
+    ref = (a.double().T @ b.double()).float()
+    ak, bk = a.T.contiguous(), b.T.contiguous()
+    for a_op, b_op, a_k, b_k in ((a, b, False, False), (ak, b, True, False), (ak, bk, True, True),
+                                 (a, bk, False, True)):
+        c = torch.empty(m, n, device=DEV)
+        ext.umma_gemm([a_op], [b_op], a_k, b_k, c, 1.0, 0.0, False, None, None, 0)
+        assert rel_err(c, ref) < 1e-5
+
+
+def test_bf16x3_and_bf16_outputs(ext):
+    m, n, k = 256, 320, 1024
+    af, bf = torch.randn(k, m, device=DEV), torch.randn(k, n, device=DEV)
+    ah, al = torch.empty(k, m, device=DEV, dtype=torch.bfloat16), torch.empty(k, m, device=DEV, dtype=torch.bfloat16)
+    bh, bl = torch.empty(k, n, device=DEV, dtype=torch.bfloat16), torch.empty(k, n, device=DEV, dtype=torch.bfloat16)
+    ext.cast_pad_bf16(af, ah, al, 1.0)
+    ext.cast_pad_bf16(bf, bh, bl, 1.0)
+    assert rel_err(ah.float() + al.float(), af) < 1e-4
+    c = torch.empty(m, n, device=DEV)
+    ext.umma_gemm([ah, ah, al], [bh, bl, bh], False, False, c, 1.0, 0.0, False, None, None, 1)
+    ref = (af.double().T @ bf.double()).float()
+    assert rel_err(c, ref) < 5e-5
+    oh, ol = torch.empty(m, n, device=DEV, dtype=torch.bfloat16), torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    ext.umma_gemm([ah], [bh], False, False, None, 1.0, 0.0, False, oh, ol, 1)
+    assert rel_err(oh.float() + ol.float(), ah.float().T @ bh.float()) < 1e-4
+
+
+@pytest.mark.parametrize('cfg', [(2, 16, 10, 10, 3, 1, 1), (2, 8, 9, 9, 3, 2, 1), (2, 3, 12, 12, 7, 2, 3),
+                                 (2, 16, 8, 8, 1, 2, 0), (3, 24, 7, 7, 3, 1, 1)])
+def test_im2col(ext, cfg):
+    n, c, h, w, k, s, p = cfg
+    x = torch.randn(n, c, h, w, device=DEV)
+    ref = F.unfold(x, k, padding=p, stride=s)
+    ho = (h + 2 * p - k) // s + 1
+    rows, ncol = n * ho * ho, c * k * k
+    ld = (ncol + 7) // 8 * 8
+    out = torch.empty(rows, ld, device=DEV, dtype=torch.bfloat16)
+    ext.im2col_bf16(x, out, None, [k, k], [s, s], [p, p], [1, 1], True)
+    want = ref.transpose(1, 2).reshape(rows, ncol).to(torch.bfloat16)
+    assert torch.equal(out[:, :ncol], want) and out[:, ncol:].abs().sum() == 0
+    xb = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    out2 = torch.empty(rows, ld, device=DEV, dtype=torch.bfloat16)
+    ext.im2col_bf16(xb, out2, None, [k, k], [s, s], [p, p], [1, 1], False)
+    want2 = ref.view(n, c, k * k, -1).permute(0, 3, 2, 1).reshape(rows, ncol).to(torch.bfloat16)
+    assert torch.equal(out2[:, :ncol], want2)
+
+
+def test_ops_gram_and_kron_apply():
+    x = torch.randn(3000, 200, device=DEV)
+    ops.set_backend('torch')
+    ref = ops.gram(x, scale=0.5)
+    ops.set_backend('auto')
+    got = ops.gram(x, scale=0.5)
+    assert rel_err(got, ref) < 5e-5  # fp32 input -> bf16x3
+    xb = x.to(torch.bfloat16)
+    assert rel_err(ops.gram(xb), xb.float().T @ xb.float()) < 1e-5
+    left = torch.randn(96, 96, device=DEV)
+    left = left @ left.T / 96
+    right = torch.randn(200, 200, device=DEV)
+    right = right @ right.T / 200
+    mid = torch.randn(96, 200, device=DEV)
+    assert rel_err(ops.kron_apply(left, mid, right), left @ mid @ right) < 1e-4
+    conv = nn.Conv2d(16, 8, 3, padding=1, stride=2).to(DEV)
+    xc = torch.randn(4, 16, 10, 10, device=DEV)
+    ops.set_backend('torch')
+    ref = ops.conv_patch_gram(xc, conv, scale=0.1)
+    ops.set_backend('auto')
+    assert rel_err(ops.conv_patch_gram(xc, conv, scale=0.1), ref) < 1e-4  # fp32 input -> hi/lo patches
+    xcl = xc.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    got = ops.conv_patch_gram(xcl, conv, scale=0.1, channels_last_order=True)
+    perm = torch.arange(16 * 9, device=DEV).view(16, 9).T.reshape(-1)
+    assert rel_err(got, ref[perm][:, perm]) < 1e-2
+    ops.check_status()
+
+
+def _small_cnn():
+    torch.manual_seed(0)
+    return nn.Sequential(nn.Conv2d(3, 16, 3, padding=1, bias=False), nn.BatchNorm2d(16), nn.ReLU(),
+                         nn.Conv2d(16, 32, 1, bias=False), nn.BatchNorm2d(32), nn.ReLU(),
+                         nn.Conv2d(32, 16, 3, stride=2, padding=1), nn.ReLU(),
+                         nn.AdaptiveAvgPool2d(1), nn.Flatten(), nn.Linear(16, 5))
+
+
+def _fused_kfac_gpu_matches_cpu(graph):
+    x, t = torch.randn(8, 3, 16, 16), torch.randint(0, 5, (8,))
+    cfg = asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=0.3,
+                                     curvature_upd_interval=4, preconditioner_upd_interval=4)
+    base = _small_cnn()
+
+    def run(model, x, t, **kw):
+        gm = asdl.FusedKfacGradientMaker(model, cfg, fisher_type=asdl.FISHER_EMP, **kw)
+        opt = torch.optim.SGD(model.parameters(), lr=0.01)
+        out = []
+        for _ in range(8):
+            opt.zero_grad()
+            d = gm.setup_model_call(model, x)
+            gm.setup_loss_call(F.cross_entropy, d, t)
+            _, loss = gm.forward_and_backward()
+            out.append((loss.item(), [p.grad.detach().cpu().clone() for p in model.parameters()]))
+            opt.step()
+        return out
+
+    ref = run(copy.deepcopy(base), x, t)
+    model = copy.deepcopy(base).to(DEV).to(memory_format=torch.channels_last)
+    got = run(model, x.to(DEV).contiguous(memory_format=torch.channels_last), t.to(DEV), cuda_graph=graph)
+    for (l1, g1), (l2, g2) in zip(ref, got):
+        assert abs(l1 - l2) < 2e-3 * max(1, abs(l1))
+        for a, b in zip(g1, g2):
+            assert rel_err(b, a) < 3e-2, (rel_err(b, a), a.shape)
+    ops.check_status()
+
+
+def test_fused_kfac_gpu_matches_cpu():
+    _fused_kfac_gpu_matches_cpu(False)
+
+
+def test_smoke_entry():
+    import __graft_entry__ as entry
+    entry.smoke()
+
+
+@pytest.mark.parametrize('sizes', [[64], [100], [65, 130, 17], [512, 256, 64, 1000], [2304, 576]])
+def test_chol_inverse_grouped(sizes):
+    torch.manual_seed(0)
+    mats, damp = [], []
+    for i, n in enumerate(sizes):
+        a = torch.randn(n, 2 * n, device=DEV)
+        mats.append(a @ a.T / (2 * n))
+        damp.append(1e-2 * (i + 1))
+    keep = [m.clone() for m in mats]
+    outs = [torch.empty_like(m) for m in mats]
+    ops.spd_inverse_grouped(mats, outs, torch.tensor(damp, device=DEV))
+    ops.check_status()
+    for m, k, o, d in zip(mats, keep, outs, damp):
+        assert torch.equal(m, k)  # inputs untouched
+        n = m.shape[0]
+        eye = torch.eye(n, device=DEV, dtype=torch.float64)
+        ref = torch.linalg.inv(m.double() + d * eye)
+        assert rel_err(o, ref.float()) < 1e-4
+        assert torch.equal(o, o.T)
+        resid = ((m.double() + d * eye) @ o.double() - eye).abs().max().item()
+        assert resid < 1e-3
+    single = ops.spd_inverse(mats[0], damp[0])
+    assert rel_err(single, outs[0]) < 1e-6
+
+
+def test_fused_kfac_cuda_graph_matches_cpu():
+    _fused_kfac_gpu_matches_cpu(True)
