@@ -103,6 +103,13 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             gradient tensors that each replay overwrites (so gradients are not accumulated across
             calls in this mode), and the returned output / loss are static tensors as well.
             Single-process CUDA runs only; anything else silently uses the eager path.
+        comm: data-parallel transport.  ``'symmetric'`` keeps factors and gradients in NVLink
+            symmetric memory and uses the library's own kernels: the statistics SYRKs add their
+            tiles straight into the owner's factor (reductions over NVLink from the MMA
+            epilogue), owners pull-reduce the gradients of their layers, and the preconditioning
+            GEMM's epilogue stores its result into every rank's gradient buffer.  ``'torch'`` uses
+            ``torch.distributed`` collectives (any backend).  ``'auto'`` picks ``'symmetric'``
+            for multi-rank CUDA runs.
     Embedding layers are not handled here; list them in ``config.ignore_modules``.
     """
 
@@ -110,7 +117,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                  loss_type: str = LOSS_CROSS_ENTROPY, scale: float = 1, grad_scale: float = 1,
                  n_mc_samples: int = 1, var: float = 1., seed: int = None,
                  precond_precision: str = 'bf16x3', clone_norm_outputs: bool = False,
-                 cuda_graph: bool = False, **kwargs):
+                 cuda_graph: bool = False, comm: str = 'auto', **kwargs):
         if fisher_type not in (FISHER_MC, FISHER_EMP):
             raise ValueError('FusedKfacGradientMaker supports fisher_mc and fisher_emp.')
         if loss_type != LOSS_CROSS_ENTROPY and fisher_type == FISHER_MC:
@@ -133,12 +140,108 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                                  f'fused K-FAC path; add it to config.ignore_modules.')
         self._by_module: Dict[nn.Module, object] = {s.module: s for s in self._kron + self._norm}
         self._bf16_cache = {}
+        if comm not in ('auto', 'symmetric', 'torch'):
+            raise ValueError("comm has to be 'auto', 'symmetric' or 'torch'")
+        if comm == 'auto':
+            comm = 'symmetric' if (self.world_size > 1 and device.type == 'cuda') else 'torch'
+        self.comm = comm if self.world_size > 1 else 'torch'
+        self._arena = None
+        if self.comm == 'symmetric':
+            self._setup_symmetric()
         self._graph_enabled = bool(cuda_graph) and device.type == 'cuda' and self.world_size == 1
         self._graph = None
         self._graph_key = None
         self._plain_steps_seen = 0
+        self._graph_launches = 0       # custom-kernel launches recorded in the captured graph
+        self.replayed_launches = 0     # ... summed over all replays so far
+        self._timing = None            # phase -> list of (start, end) CUDA events
         if self._graph_enabled:
             ops.extension().reserve_scratch(device.index or 0, 64 << 20)
+
+    # ------------------------------------------------------------------ device-side phase timing
+    def enable_phase_timing(self, enabled=True):
+        """Record CUDA events around the phases of every step (plain step, curvature update,
+        inverse update, preconditioning).  Read the result with :meth:`phase_times`."""
+        self._timing = {} if enabled else None
+
+    def _phase(self, name):
+        maker = self
+
+        class _Ctx:
+            def __enter__(self_inner):
+                if maker._timing is not None:
+                    self_inner.start = torch.cuda.Event(enable_timing=True)
+                    self_inner.start.record()
+
+            def __exit__(self_inner, *exc):
+                if maker._timing is not None:
+                    end = torch.cuda.Event(enable_timing=True)
+                    end.record()
+                    maker._timing.setdefault(name, []).append((self_inner.start, end))
+                return False
+
+        return _Ctx()
+
+    def phase_times(self, reset=True):
+        """{phase: (calls, mean milliseconds)} measured on the device since the last reset."""
+        if self._timing is None:
+            return {}
+        torch.cuda.synchronize()
+        out = {k: (len(v), sum(a.elapsed_time(b) for a, b in v) / len(v)) for k, v in self._timing.items()}
+        if reset:
+            self._timing = {}
+        return out
+
+    # ------------------------------------------------------------------ symmetric-memory transport
+    def _setup_symmetric(self):
+        from ..parallel.symmetric import SymmetricArena, _round_up
+        pad = lambda n: _round_up(n, 64)  # noqa: E731
+        params = [p for p in self.model.parameters() if p.requires_grad]
+        total = sum(pad(st.A.numel()) + pad(st.B.numel()) for st in self._kron)
+        total += sum(pad(st.stats.numel()) for st in self._norm)
+        total += sum(pad(p.numel()) for p in params)
+        arena = self._arena = SymmetricArena(total, group=self.sync_group, device=self.device)
+        rank = self.world_rank
+        factor_segs, stage_segs, grad_segs = [], [], []
+        for st in self._kron:
+            st.A_off, st.A = arena.alloc(st.d_in, st.d_in)
+            st.B_off, st.B = arena.alloc(st.d_out, st.d_out)
+            st.kron.A, st.kron.B = st.A, st.B
+            st.owner = self._owner.get(st.module, 0)
+            if st.owner == rank:
+                factor_segs += [(st.A_off, st.A.numel()), (st.B_off, st.B.numel())]
+        for st in self._norm:
+            st.stage_off, st.stage = arena.alloc(*st.stats.shape)
+            st.owner = self._owner.get(st.module, 0)
+            if st.owner == rank:
+                stage_segs.append((st.stage_off, st.stage.numel()))
+        owner_of_param = {}
+        for st in self._kron + self._norm:
+            for p in st.module.parameters():
+                owner_of_param[p] = st.owner
+        self._grad_slot = {}
+        for i, p in enumerate(params):
+            off, flat = arena.alloc(p.numel())
+            view = flat.as_strided(p.shape, p.stride())
+            self._grad_slot[p] = (off, view)
+            if owner_of_param.get(p, i % self.world_size) == rank:
+                grad_segs.append((off, p.numel()))
+        self._sym_params = params
+        self._factor_segs = arena.segments(factor_segs)
+        self._stage_segs = arena.segments(stage_segs)
+        self._grad_segs = arena.segments(grad_segs)
+
+    def _bind_grads_to_arena(self):
+        """Gradients live in the symmetric arena; anything autograd allocated elsewhere is moved."""
+        with torch.no_grad():
+            for p in self._sym_params:
+                _, view = self._grad_slot[p]
+                g = p.grad
+                if g is None:
+                    view.zero_()
+                elif g.data_ptr() != view.data_ptr():
+                    view.copy_(g)
+                p.grad = view
 
     # ------------------------------------------------------------------ CUDA-graph replay
     def _tensor_slots(self):
@@ -156,26 +259,32 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         plain = not self.do_update_curvature(step) and not self.do_update_preconditioner(step)
         ready = all(st.has_inv for st in self._kron) and all(st.has_inv for st in self._norm)
         if not (self._graph_enabled and plain and ready):
-            return super().forward_and_backward()
+            return self._eager_step(step, plain)
         slots = self._tensor_slots()
         key = tuple((tuple(v.shape), v.dtype, v.stride()) for _, _, v in slots)
         if self._graph is None:
             self._plain_steps_seen += 1
             if self._plain_steps_seen <= 2:  # let lazy initialisation happen eagerly first
-                return super().forward_and_backward()
+                return self._eager_step(step, plain)
             self._capture(slots, key)
         elif key != self._graph_key:
-            return super().forward_and_backward()
+            return self._eager_step(step, plain)
         with torch.no_grad():
             for static, (_, _, value) in zip(self._static_inputs, slots):
                 if static.data_ptr() != value.data_ptr():
                     static.copy_(value, non_blocking=True)
-        self._graph.replay()
+        with self._phase('plain_step_graph'):
+            self._graph.replay()
+        self.replayed_launches += self._graph_launches
         for p, g in zip(self._graph_params, self._static_grads):
             p.grad = g
         self._model_output, self._loss = self._static_output, self._static_loss
         self.state['step'] += 1
         return self._model_output, self._loss
+
+    def _eager_step(self, step, plain):
+        with self._phase('plain_step_eager' if plain else 'update_step'):
+            return KfacGradientMaker.forward_and_backward(self)
 
     def _capture(self, slots, key):
         self._static_inputs = [v.clone() for _, _, v in slots]
@@ -232,9 +341,11 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         self._model_output = self._loss = None
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
+        launches_before = ops.extension().launch_count()
         try:
             with torch.cuda.graph(graph, stream=stream):
                 plain_step()
+            self._graph_launches = ops.extension().launch_count() - launches_before
         finally:
             self._model_args, self._model_kwargs, self._loss_fn_args, self._loss_fn_kwargs = saved
         self._static_grads = [p.grad for p in self._graph_params]
@@ -264,7 +375,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                     return
                 x = inputs[0].detach()
                 with torch.no_grad():
-                    if isinstance(module, nn.Conv2d):
+                    if self._arena is not None:
+                        self._push_factor(st, x, output, alpha, is_A=True)
+                    elif isinstance(module, nn.Conv2d):
                         out_size = output.shape[-2] * output.shape[-1]
                         ops.conv_patch_gram(x, module, scale=alpha / out_size, out=st.A, beta=beta,
                                             channels_last_order=st.khwc)
@@ -276,6 +389,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                             return
                         g = grad.detach()
                         with torch.no_grad():
+                            if self._arena is not None:
+                                self._push_factor(st, g, None, alpha, is_A=False)
+                                return
                             if g.ndim == 4:
                                 rows = g.permute(0, 2, 3, 1).reshape(-1, g.shape[1])
                             else:
@@ -308,6 +424,42 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             handles.append(st.module.register_forward_hook(norm_hook(st)))
         return handles, state
 
+    def _push_factor(self, st: _KronState, t, output, alpha, is_A):
+        """Statistics product of this rank added into the owner's factor through NVLink: the SYRK
+        epilogue issues reductions to the owner's symmetric buffer (scaled by 1/world so that the
+        owner ends up with the average over ranks)."""
+        ext = ops.extension()
+        arena = self._arena
+        module = st.module
+        scale = alpha / self.world_size
+        if is_A and isinstance(module, nn.Conv2d):
+            from ..utils import _conv_geometry
+            (kh, kw), (sh, sw), (ph, pw), (dh, dw) = _conv_geometry(module)
+            n, c, h, w = t.shape
+            scale = scale / (output.shape[-2] * output.shape[-1])
+            pointwise = kh == kw == sh == sw == 1 and ph == pw == 0
+            if (pointwise and t.dtype == torch.bfloat16 and c % 8 == 0
+                    and t.is_contiguous(memory_format=torch.channels_last)):
+                segs_a = [t.permute(0, 2, 3, 1).reshape(-1, c)]
+            else:
+                rows = n * output.shape[-2] * output.shape[-1]
+                ncol = c * kh * kw
+                ld = (max(ncol, 8) + 7) // 8 * 8
+                x3 = t.dtype == torch.float32
+                hi = torch.empty(rows, ld, device=t.device, dtype=torch.bfloat16)
+                lo = torch.empty_like(hi) if x3 else None
+                ext.im2col_bf16(t, hi, lo, [kh, kw], [sh, sw], [ph, pw], [dh, dw], not st.khwc)
+                segs_a = [hi[:, :ncol], hi[:, :ncol], lo[:, :ncol]] if x3 else [hi[:, :ncol]]
+        else:
+            rows2d = t.permute(0, 2, 3, 1).reshape(-1, t.shape[1]) if t.ndim == 4 \
+                else t.reshape(-1, t.shape[-1])
+            hi, lo = ops._stage_bf16(rows2d, ops._use_x3(rows2d.dtype))
+            segs_a = [hi, hi, lo] if lo is not None else [hi]
+        segs_b = [segs_a[0], segs_a[2], segs_a[0]] if len(segs_a) == 3 else segs_a
+        off, n_dim = (st.A_off, st.d_in) if is_A else (st.B_off, st.d_out)
+        ext.umma_gemm_to_ptr(segs_a, segs_b, False, False, arena.ptr(st.owner, off), n_dim,
+                             float(scale), True, True, [], 0)
+
     @staticmethod
     def _norm_statistics(st: _NormState, y, g, alpha, beta):
         module = st.module
@@ -326,7 +478,10 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         wb = (gw * gb).sum(dim=0)
         bb = gb.square().sum(dim=0)
         new = torch.stack([torch.stack([ww, wb], dim=1), torch.stack([wb, bb], dim=1)], dim=1)
-        st.stats.mul_(beta).add_(new, alpha=alpha)
+        if getattr(st, 'stage', None) is not None:
+            st.stage.copy_(new)  # reduced over ranks by the owner after the backward pass
+        else:
+            st.stats.mul_(beta).add_(new, alpha=alpha)
 
     def update_curvature(self):
         cfg = self.config
@@ -334,8 +489,12 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         handles, state = self._install_hooks()
         if cfg is not None and self.fisher_maker.config.seed is not None:
             torch.random.manual_seed(self.fisher_maker.config.seed)
+        if self._arena is not None:
+            # owners decay their factors; nobody may add before every owner has done so
+            self._arena.scale_segments(self._factor_segs, self._stat_weights()[1])
+            self._arena.barrier()
         try:
-            with nvtx_range('kfac_curvature'):
+            with nvtx_range('kfac_curvature'), self._phase('curvature'):
                 self.call_model()
                 saved = self._loss_reduction
                 self._loss_reduction = 'sum'
@@ -367,7 +526,15 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                     p.grad.div_(cfg.data_size)
             loss.div_(cfg.data_size)
         self._loss = loss
-        if self.world_size > 1:
+        if self._arena is not None:
+            alpha, beta = self._stat_weights()
+            self._arena.barrier()  # every rank's tiles have landed in the owners' factors
+            self._arena.reduce_segments(self._stage_segs, 1.0 / self.world_size)
+            with torch.no_grad():
+                for st in self._norm:
+                    if st.owner == self.world_rank:
+                        st.stats.mul_(beta).add_(st.stage, alpha=alpha)
+        elif self.world_size > 1:
             self.reduce_scatter_curvature()
 
     def do_update_preconditioner(self, step=None) -> bool:
@@ -381,7 +548,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
     def update_preconditioner(self, damping=None, **kwargs):
         damping = self.config.damping if damping is None else damping
         root = damping ** 0.5
-        with nvtx_range('kfac_inverse'):
+        with nvtx_range('kfac_inverse'), self._phase('inverse'):
             owned = [st for st in self._kron if self.is_module_for_inv_and_precondition(st.module)]
             if owned:
                 # pi-damping split from the traces, evaluated on the device for all layers at once
@@ -428,10 +595,12 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         if vectors is not None or not use_inv:
             return super().precondition(vectors=vectors, grad_scale=grad_scale, use_inv=use_inv)
         grad_scale = self.grad_scale if grad_scale is None else grad_scale
+        if self._arena is not None:
+            return self._precondition_symmetric(grad_scale)
         distributed = self.world_size > 1
         if distributed:
             self.sync_grad_pre_precondition()
-        with nvtx_range('kfac_precondition'):
+        with nvtx_range('kfac_precondition'), self._phase('precondition'):
             for st in self._kron:
                 if not st.has_inv or not self.is_module_for_inv_and_precondition(st.module):
                     continue
@@ -442,12 +611,27 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         if distributed:
             self.sync_grad_post_precondition()
 
-    def _precondition_kron(self, st: _KronState, grad_scale):
+    def _precondition_symmetric(self, grad_scale):
+        """barrier -> owners pull-reduce the gradients of their layers -> precondition (the final
+        GEMM stores into every rank's gradient buffer) -> push the small rest -> barrier."""
+        arena = self._arena
+        self._bind_grads_to_arena()
+        arena.barrier()
+        arena.reduce_segments(self._grad_segs, 1.0 / self.world_size)
+        with nvtx_range('kfac_precondition'):
+            for st in self._kron:
+                if st.owner == self.world_rank and st.has_inv:
+                    self._precondition_kron(st, grad_scale, replicate=True)
+            self._precondition_norms(grad_scale)
+        arena.bcast_segments(self._grad_segs)
+        arena.barrier()
+
+    def _precondition_kron(self, st: _KronState, grad_scale, replicate=False):
         g2d, staged = st.grad_matrix()
         if grad_scale != 1:
             g2d.mul_(grad_scale)
         if g2d.is_cuda and ops.get_backend() != 'torch':
-            self._kron_apply_cached(st, g2d)
+            self._kron_apply_cached(st, g2d, replicate and staged is None)
         else:
             g2d.copy_(st.B_inv @ g2d @ st.A_inv)
         if staged is not None:
@@ -458,8 +642,10 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                 b.mul_(grad_scale)
             b.copy_(torch.mv(st.B_inv, b))
 
-    def _kron_apply_cached(self, st: _KronState, g2d):
-        """g2d <- B^-1 g2d A^-1 with the cached bf16 images of the inverses."""
+    def _kron_apply_cached(self, st: _KronState, g2d, replicate=False):
+        """g2d <- B^-1 g2d A^-1 with the cached bf16 images of the inverses.  With ``replicate``
+        the epilogue of the second GEMM also stores the result into the peers' gradient buffers
+        (preconditioning fused with the all-gather of its result)."""
         ext = ops.extension()
         x3 = self.precond_precision == 'bf16x3'
         m, n = g2d.shape
@@ -484,7 +670,13 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             seg_b = [am, a_lo[:, :n], am]
         else:
             seg_a, seg_b = [t_hi[:, :n]], [am]
-        if g2d.stride(1) == 1:
+        if replicate and g2d.stride(1) == 1 and g2d.stride(0) == n:
+            off, _ = self._grad_slot[st.module.weight]
+            arena = self._arena
+            peers = [arena.ptr(r, off) for r in range(arena.world) if r != arena.rank]
+            ext.umma_gemm_to_ptr(seg_a, seg_b, True, False, arena.ptr(arena.rank, off), n, 1.0,
+                                 False, False, peers, 0)
+        elif g2d.stride(1) == 1:
             ext.umma_gemm(seg_a, seg_b, True, False, g2d, 1.0, 0.0, False, None, None, 0)
         else:
             out = torch.empty(m, n, device=g2d.device, dtype=torch.float32)

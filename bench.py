@@ -147,8 +147,8 @@ def build_ours(args, device, world):
         opt.step()
         return loss
 
-    def launches():
-        return asdl.ops.extension().launch_count()
+    def launches():  # host-issued launches plus those replayed from the captured step graph
+        return asdl.ops.extension().launch_count() + gm.replayed_launches
 
     def to_device(x, t):
         return (x.to(device, non_blocking=True).contiguous(memory_format=torch.channels_last),

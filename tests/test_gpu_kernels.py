@@ -139,6 +139,7 @@ def _small_cnn():
 
 
 def _fused_kfac_gpu_matches_cpu(graph):
+    torch.backends.cudnn.allow_tf32 = False
     x, t = torch.randn(8, 3, 16, 16), torch.randint(0, 5, (8,))
     cfg = asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=0.3,
                                      curvature_upd_interval=4, preconditioner_upd_interval=4)
