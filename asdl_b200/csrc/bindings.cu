@@ -15,6 +15,16 @@ void im2col_bf16(at::Tensor x, at::Tensor out, c10::optional<at::Tensor> out_lo,
 void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
                       bool b_kmajor, int64_t dst_ptr, int64_t ldc, double alpha, bool sym, bool atomic,
                       std::vector<int64_t> extra_ptrs, int64_t nsplit);
+int64_t gemm_plan_new();
+void gemm_plan_free(int64_t id);
+void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs,
+                   bool a_kmajor, bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta,
+                   bool sym, c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
+                   int64_t dst_ptr, int64_t ldc, bool atomic, std::vector<int64_t> extra_ptrs,
+                   int64_t nsplit);
+void gemm_plan_finalize(int64_t id);
+void gemm_plan_run(int64_t id);
+void cast_pad_bf16_grouped(at::Tensor table, int64_t count);
 void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot);
 void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale);
 void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs);
@@ -33,6 +43,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cast_pad_bf16", &b200::cast_pad_bf16);
   m.def("im2col_bf16", &b200::im2col_bf16);
   m.def("umma_gemm_to_ptr", &b200::umma_gemm_to_ptr);
+  m.def("gemm_plan_new", &b200::gemm_plan_new);
+  m.def("gemm_plan_free", &b200::gemm_plan_free);
+  m.def("gemm_plan_add", &b200::gemm_plan_add);
+  m.def("gemm_plan_finalize", &b200::gemm_plan_finalize);
+  m.def("gemm_plan_run", &b200::gemm_plan_run);
+  m.def("cast_pad_bf16_grouped", &b200::cast_pad_bf16_grouped);
   m.def("symm_barrier", &b200::symm_barrier);
   m.def("symm_reduce_segments", &b200::symm_reduce_segments);
   m.def("symm_bcast_segments", &b200::symm_bcast_segments);

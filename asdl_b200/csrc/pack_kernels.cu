@@ -72,6 +72,38 @@ void cast_pad_bf16(at::Tensor src, at::Tensor hi, c10::optional<at::Tensor> lo, 
   count_launch();
 }
 
+// Grouped fp32 -> bf16 hi/lo staging: one launch converts many matrices.  Each table row holds
+// (src fp32 ptr, hi ptr, lo ptr or 0, rows, n, src pitch, dst pitch) as int64.
+__global__ void cast_pad_grouped_kernel(const long long* __restrict__ table) {
+  const long long* e = table + static_cast<long long>(blockIdx.y) * 7;
+  const float* src = reinterpret_cast<const float*>(e[0]);
+  __nv_bfloat16* hi = reinterpret_cast<__nv_bfloat16*>(e[1]);
+  __nv_bfloat16* lo = reinterpret_cast<__nv_bfloat16*>(e[2]);
+  const long long rows = e[3], n = e[4], lds = e[5], ldo = e[6];
+  const long long total = rows * ldo;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / ldo;
+    const long long c = i - r * ldo;
+    const float v = (c < n) ? src[r * lds + c] : 0.f;
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    hi[i] = h;
+    if (lo != nullptr) lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+  }
+}
+
+void cast_pad_bf16_grouped(at::Tensor table, int64_t count) {
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.is_contiguous() &&
+                  table.numel() == count * 7, "table must be a CUDA int64 [count, 7] tensor");
+  if (count == 0) return;
+  c10::cuda::CUDAGuard guard(table.get_device());
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  cast_pad_grouped_kernel<<<dim3(32, static_cast<unsigned>(count)), 256, 0, stream>>>(
+      reinterpret_cast<const long long*>(table.data_ptr<int64_t>()));
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
 struct Im2colParams {
   long long sN, sC, sH, sW;  // input strides in elements
   int N, C, H, W;

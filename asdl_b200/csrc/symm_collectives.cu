@@ -15,8 +15,8 @@
 // The first SYMM_FLAG_WORDS 32-bit words of the symmetric buffer are reserved for the barrier
 // slots: word [s * 64 + r] of rank q is "rank r has reached epoch of barrier stream s"; word
 // [s * 64 + 63] counts the barriers this rank has entered on stream s.
-// Peer data is always accessed with plain loads/stores issued by each thread; no TMA and no
-// cluster multicast is involved.
+// Peer data is always accessed with plain per-thread loads and stores; bulk-copy engines are
+// not used on peer memory.
 #include "host_utils.h"
 #include "sm100_ptx.cuh"
 

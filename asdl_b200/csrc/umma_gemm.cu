@@ -2,6 +2,8 @@
 #include "host_utils.h"
 #include "umma_gemm.cuh"
 
+#include <unordered_map>
+
 namespace b200 {
 
 namespace {
@@ -193,6 +195,149 @@ void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_
   }
   gemm_attach_scratch(P, dev);
   gemm_launch_single(P, at::cuda::getCurrentCUDAStream(dev).stream());
+}
+
+// ---- grouped execution ---------------------------------------------------------------------------
+// A plan is a fixed list of GEMM problems whose operand addresses do not change (persistent
+// buffers).  Its problem table and tile list live in device memory, so running the plan is two
+// launches at most (all tiles of all problems, then the split-K reductions) with no host-side
+// descriptor work - which also makes it replayable from a CUDA graph.
+struct GemmPlan {
+  std::vector<GemmProblem> problems;
+  std::vector<std::vector<at::Tensor>> keep_alive;  // operands / outputs referenced by raw pointer
+  at::Tensor d_problems, d_work, d_rwork, scratch;
+  int n_work = 0, n_rwork = 0, dev = 0;
+  bool finalized = false;
+};
+
+static std::unordered_map<int64_t, GemmPlan> g_plans;
+static int64_t g_next_plan = 1;
+
+int64_t gemm_plan_new() {
+  const int64_t id = g_next_plan++;
+  g_plans[id];
+  return id;
+}
+
+void gemm_plan_free(int64_t id) { g_plans.erase(id); }
+
+void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs,
+                   bool a_kmajor, bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta,
+                   bool sym, c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
+                   int64_t dst_ptr, int64_t ldc, bool atomic, std::vector<int64_t> extra_ptrs,
+                   int64_t nsplit) {
+  auto it = g_plans.find(id);
+  TORCH_CHECK(it != g_plans.end() && !it->second.finalized, "unknown or finalized plan");
+  GemmPlan& plan = it->second;
+  TORCH_CHECK(!a_segs.empty(), "no operands");
+  plan.dev = a_segs[0].get_device();
+  c10::cuda::CUDAGuard guard(plan.dev);
+  GemmProblem P;
+  gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, C, alpha, beta, sym, out_hi, out_lo,
+                    nsplit <= 0 ? 1 : nsplit, 148, /*allow_no_output=*/dst_ptr != 0);
+  if (dst_ptr != 0) {
+    TORCH_CHECK((dst_ptr & 15) == 0, "destination must be 16-byte aligned");
+    P.C = reinterpret_cast<float*>(dst_ptr);
+    P.Cin = P.C;
+    P.ldc = static_cast<int>(ldc);
+    TORCH_CHECK(P.ldc >= P.N, "ldc is smaller than the number of columns");
+  }
+  if (atomic) P.flags |= GF_ATOMIC;
+  TORCH_CHECK(static_cast<int>(extra_ptrs.size()) <= G_MAX_EXTRA, "too many extra destinations");
+  TORCH_CHECK(!(atomic && !extra_ptrs.empty()), "extra destinations are not supported in atomic mode");
+  P.n_extra = static_cast<int>(extra_ptrs.size());
+  for (int e = 0; e < P.n_extra; ++e) P.C_extra[e] = reinterpret_cast<float*>(extra_ptrs[e]);
+  plan.problems.push_back(P);
+  std::vector<at::Tensor> keep = a_segs;
+  keep.insert(keep.end(), b_segs.begin(), b_segs.end());
+  if (C.has_value()) keep.push_back(*C);
+  if (out_hi.has_value()) keep.push_back(*out_hi);
+  if (out_lo.has_value()) keep.push_back(*out_lo);
+  plan.keep_alive.push_back(std::move(keep));
+}
+
+void gemm_plan_finalize(int64_t id) {
+  auto it = g_plans.find(id);
+  TORCH_CHECK(it != g_plans.end() && !it->second.finalized, "unknown or finalized plan");
+  GemmPlan& plan = it->second;
+  TORCH_CHECK(!plan.problems.empty(), "empty plan");
+  c10::cuda::CUDAGuard guard(plan.dev);
+  DeviceState& st = device_state(plan.dev);
+  // scratch for split-K problems (private to the plan)
+  size_t scratch_floats = 0;
+  for (auto& P : plan.problems)
+    if (P.nsplit > 1 && !(P.flags & GF_ATOMIC))
+      scratch_floats += static_cast<size_t>(P.ntiles) * P.nsplit * G_BM * G_BN;
+  auto f32 = at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, plan.dev);
+  if (scratch_floats > 0) plan.scratch = at::empty({static_cast<int64_t>(scratch_floats)}, f32);
+  size_t off = 0;
+  struct Item { int problem, tm, tn, split; long long cost; };
+  std::vector<Item> items, ritems;
+  for (size_t pi = 0; pi < plan.problems.size(); ++pi) {
+    GemmProblem& P = plan.problems[pi];
+    P.status = st.status.data_ptr<int>();
+    const bool split = P.nsplit > 1 && !(P.flags & GF_ATOMIC);
+    if (split) {
+      P.ws = plan.scratch.data_ptr<float>() + off;
+      off += static_cast<size_t>(P.ntiles) * P.nsplit * G_BM * G_BN;
+    }
+    const long long cost = static_cast<long long>(P.nseg) * ((P.K + G_BK - 1) / G_BK) / P.nsplit + 2;
+    for (int tm = 0; tm < P.tiles_m; ++tm)
+      for (int tn = 0; tn < ((P.flags & GF_SYM) ? tm + 1 : P.tiles_n); ++tn) {
+        for (int s = 0; s < P.nsplit; ++s) items.push_back({static_cast<int>(pi), tm, tn, s, cost});
+        if (split) ritems.push_back({static_cast<int>(pi), tm, tn, 0, 0});
+      }
+  }
+  // longest tiles first: the tail of the launch is then made of short tiles
+  std::stable_sort(items.begin(), items.end(), [](const Item& a, const Item& b) { return a.cost > b.cost; });
+  auto upload_work = [&](const std::vector<Item>& v) {
+    std::vector<int> flat;
+    flat.reserve(v.size() * 4);
+    for (auto& w : v) {
+      flat.push_back(w.problem);
+      flat.push_back(w.tm);
+      flat.push_back(w.tn);
+      flat.push_back(w.split);
+    }
+    at::Tensor host = at::from_blob(flat.data(), {static_cast<int64_t>(flat.size())},
+                                    at::TensorOptions().dtype(at::kInt)).clone();
+    return host.to(at::Device(at::kCUDA, plan.dev));
+  };
+  plan.n_work = static_cast<int>(items.size());
+  plan.n_rwork = static_cast<int>(ritems.size());
+  plan.d_work = upload_work(items);
+  if (plan.n_rwork > 0) plan.d_rwork = upload_work(ritems);
+  at::Tensor host = at::from_blob(plan.problems.data(),
+                                  {static_cast<int64_t>(plan.problems.size() * sizeof(GemmProblem))},
+                                  at::TensorOptions().dtype(at::kByte)).clone();
+  plan.d_problems = host.to(at::Device(at::kCUDA, plan.dev));
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(plan.d_problems.data_ptr()) & 63) == 0,
+              "problem table is not 64-byte aligned");
+  plan.finalized = true;
+}
+
+void gemm_plan_run(int64_t id) {
+  auto it = g_plans.find(id);
+  TORCH_CHECK(it != g_plans.end() && it->second.finalized, "unknown or unfinalized plan");
+  GemmPlan& plan = it->second;
+  c10::cuda::CUDAGuard guard(plan.dev);
+  auto stream = at::cuda::getCurrentCUDAStream(plan.dev).stream();
+  if (!g_attr_set) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(umma_gemm_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM_BYTES));
+    g_attr_set = true;
+  }
+  const GemmProblem* probs = reinterpret_cast<const GemmProblem*>(plan.d_problems.data_ptr());
+  umma_gemm_kernel<<<plan.n_work, G_THREADS, G_SMEM_BYTES, stream>>>(
+      plan.problems[0], probs, reinterpret_cast<const GemmWork*>(plan.d_work.data_ptr<int>()));
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  if (plan.n_rwork > 0) {
+    splitk_reduce_kernel<<<dim3(plan.n_rwork, 16, 1), 256, 0, stream>>>(
+        plan.problems[0], probs, reinterpret_cast<const GemmWork*>(plan.d_rwork.data_ptr<int>()));
+    B200_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+  }
 }
 
 // Reads and clears the device status word (synchronises the current stream).

@@ -103,6 +103,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             gradient tensors that each replay overwrites (so gradients are not accumulated across
             calls in this mode), and the returned output / loss are static tensors as well.
             Single-process CUDA runs only; anything else silently uses the eager path.
+        grouped: apply the inverses of all layers with grouped launches (one staging kernel and
+            two GEMM launches for the whole model) instead of a few launches per layer.
         comm: data-parallel transport.  ``'symmetric'`` keeps factors and gradients in NVLink
             symmetric memory and uses the library's own kernels: the statistics SYRKs add their
             tiles straight into the owner's factor (reductions over NVLink from the MMA
@@ -117,7 +119,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                  loss_type: str = LOSS_CROSS_ENTROPY, scale: float = 1, grad_scale: float = 1,
                  n_mc_samples: int = 1, var: float = 1., seed: int = None,
                  precond_precision: str = 'bf16x3', clone_norm_outputs: bool = False,
-                 cuda_graph: bool = False, comm: str = 'auto', **kwargs):
+                 cuda_graph: bool = False, comm: str = 'auto', grouped: bool = True, **kwargs):
         if fisher_type not in (FISHER_MC, FISHER_EMP):
             raise ValueError('FusedKfacGradientMaker supports fisher_mc and fisher_emp.')
         if loss_type != LOSS_CROSS_ENTROPY and fisher_type == FISHER_MC:
@@ -140,6 +142,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                                  f'fused K-FAC path; add it to config.ignore_modules.')
         self._by_module: Dict[nn.Module, object] = {s.module: s for s in self._kron + self._norm}
         self._bf16_cache = {}
+        self.grouped = grouped
+        self._group = None
         if comm not in ('auto', 'symmetric', 'torch'):
             raise ValueError("comm has to be 'auto', 'symmetric' or 'torch'")
         if comm == 'auto':
@@ -148,6 +152,13 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         self._arena = None
         if self.comm == 'symmetric':
             self._setup_symmetric()
+        elif self.world_size > 1:
+            # torch.distributed transport: new statistics are measured into staging buffers,
+            # averaged onto the owners, and folded into the running factors there
+            for st in self._kron:
+                st.A_new, st.B_new = torch.zeros_like(st.A), torch.zeros_like(st.B)
+            for st in self._norm:
+                st.stage = torch.zeros_like(st.stats)
         self._graph_enabled = bool(cuda_graph) and device.type == 'cuda' and self.world_size == 1
         self._graph = None
         self._graph_key = None
@@ -364,6 +375,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
 
     def _install_hooks(self):
         alpha, beta = self._stat_weights()
+        staged = self._arena is None and self.world_size > 1
+        if staged:
+            beta = 0.0
         handles = []
         state = {'on': True}
 
@@ -379,10 +393,12 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                         self._push_factor(st, x, output, alpha, is_A=True)
                     elif isinstance(module, nn.Conv2d):
                         out_size = output.shape[-2] * output.shape[-1]
-                        ops.conv_patch_gram(x, module, scale=alpha / out_size, out=st.A, beta=beta,
+                        ops.conv_patch_gram(x, module, scale=alpha / out_size,
+                                            out=st.A_new if staged else st.A, beta=beta,
                                             channels_last_order=st.khwc)
                     else:
-                        ops.gram(x.reshape(-1, x.shape[-1]), scale=alpha, out=st.A, beta=beta)
+                        ops.gram(x.reshape(-1, x.shape[-1]), scale=alpha,
+                                 out=st.A_new if staged else st.A, beta=beta)
                 if output.requires_grad:
                     def bwd(grad):
                         if not state['on']:
@@ -396,7 +412,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                                 rows = g.permute(0, 2, 3, 1).reshape(-1, g.shape[1])
                             else:
                                 rows = g.reshape(-1, g.shape[-1])
-                            ops.gram(rows, scale=alpha, out=st.B, beta=beta)
+                            ops.gram(rows, scale=alpha, out=st.B_new if staged else st.B, beta=beta)
                     output.register_hook(bwd)
             return fwd
 
@@ -535,13 +551,35 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                     if st.owner == self.world_rank:
                         st.stats.mul_(beta).add_(st.stage, alpha=alpha)
         elif self.world_size > 1:
-            self.reduce_scatter_curvature()
+            self._reduce_staged_statistics()
 
     def do_update_preconditioner(self, step=None) -> bool:
         if not self.do_accumulate and (self.curvature_upd_schedule is not None
                                        or self.config.curvature_upd_interval is not None):
             return self.do_update_curvature(step)  # nothing is kept: invert whenever measured
         return KfacGradientMaker.do_update_preconditioner(self, step)
+
+    def _reduce_staged_statistics(self):
+        """torch.distributed transport: average the new statistics (and the gradients) of every
+        layer onto its owner with one packed message per owner, then update the running curvature
+        on the owner."""
+        alpha, beta = self._stat_weights()
+        groups = {r: [] for r in range(self.world_size)}
+        for st in self._kron:
+            groups[self._owner.get(st.module, 0)] += [st.A_new, st.B_new] + self._module_grads(st.module)
+        for st in self._norm:
+            groups[self._owner.get(st.module, 0)] += [st.stage] + self._module_grads(st.module)
+        for owner, tensors in groups.items():
+            self._reduce_avg(tensors, dst=owner)
+        self._owned_grads_synced = True
+        with torch.no_grad():
+            for st in self._kron:
+                if self.is_module_for_inv_and_precondition(st.module):
+                    st.A.mul_(beta).add_(st.A_new)
+                    st.B.mul_(beta).add_(st.B_new)
+            for st in self._norm:
+                if self.is_module_for_inv_and_precondition(st.module):
+                    st.stats.mul_(beta).add_(st.stage, alpha=alpha)
 
     # ------------------------------------------------------------------ inverses
     @torch.no_grad()
@@ -601,12 +639,14 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         if distributed:
             self.sync_grad_pre_precondition()
         with nvtx_range('kfac_precondition'), self._phase('precondition'):
-            for st in self._kron:
-                if not st.has_inv or not self.is_module_for_inv_and_precondition(st.module):
-                    continue
-                if st.module.weight.grad is None:
-                    continue
-                self._precondition_kron(st, grad_scale)
+            todo = [st for st in self._kron
+                    if st.has_inv and self.is_module_for_inv_and_precondition(st.module)
+                    and st.module.weight.grad is not None]
+            if todo and self._use_grouped(todo):
+                self._precondition_kron_grouped(todo, grad_scale)
+            else:
+                for st in todo:
+                    self._precondition_kron(st, grad_scale)
             self._precondition_norms(grad_scale)
         if distributed:
             self.sync_grad_post_precondition()
@@ -619,12 +659,96 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         arena.barrier()
         arena.reduce_segments(self._grad_segs, 1.0 / self.world_size)
         with nvtx_range('kfac_precondition'):
-            for st in self._kron:
-                if st.owner == self.world_rank and st.has_inv:
+            todo = [st for st in self._kron if st.owner == self.world_rank and st.has_inv]
+            if todo and self._use_grouped(todo):
+                self._precondition_kron_grouped(todo, grad_scale)
+            else:
+                for st in todo:
                     self._precondition_kron(st, grad_scale, replicate=True)
             self._precondition_norms(grad_scale)
         arena.bcast_segments(self._grad_segs)
         arena.barrier()
+
+    # grouped path: all layers' products in a handful of launches ------------------------------------
+    def _use_grouped(self, todo):
+        return (self.grouped and todo[0].A.is_cuda and ops.get_backend() != 'torch')
+
+    def _build_group(self, todo):
+        """Persistent staging buffers, the cast table and the two GEMM plans for ``todo``."""
+        ext = ops.extension()
+        dev = todo[0].A.device
+        x3 = self.precond_precision == 'bf16x3'
+        arena = self._arena
+        if arena is None:
+            total = sum((st.d_out * st.d_in + 63) // 64 * 64 for st in todo)
+            flat = torch.zeros(total, device=dev, dtype=torch.float32)
+        rows, views, off = [], [], 0
+        plan1, plan2 = ext.gemm_plan_new(), ext.gemm_plan_new()
+        keep = []
+        for st in todo:
+            m, n = st.d_out, st.d_in
+            w = st.module.weight
+            if arena is None:
+                region = flat[off:off + m * n]
+                off += (m * n + 63) // 64 * 64
+                dst_ptr, extra = region.data_ptr(), []
+            else:
+                a_off, view = self._grad_slot[w]
+                region = arena.buffer[a_off:a_off + m * n]
+                dst_ptr = arena.ptr(arena.rank, a_off)
+                extra = [arena.ptr(r, a_off) for r in range(arena.world) if r != arena.rank]
+            # the region holds the gradient as a contiguous [d_out, d_in] matrix in the factor's order
+            if w.ndim == 4 and st.khwc:
+                view = region.view(m, w.shape[2], w.shape[3], w.shape[1]).permute(0, 3, 1, 2)
+            else:
+                view = region.view(w.shape)
+            views.append(view)
+            ld = (max(n, 8) + 7) // 8 * 8
+            mk = lambda: torch.empty(m, ld, device=dev, dtype=torch.bfloat16)  # noqa: E731
+            g_hi, g_lo, t_hi, t_lo = mk(), (mk() if x3 else None), mk(), (mk() if x3 else None)
+            keep.append((g_hi, g_lo, t_hi, t_lo, region))
+            rows.append([region.data_ptr(), g_hi.data_ptr(), g_lo.data_ptr() if x3 else 0, m, n, n, ld])
+            b_hi, b_lo = self._bf16_cache[(st, 'B')]
+            a_hi, a_lo = self._bf16_cache[(st, 'A')]
+            bm, am = b_hi[:, :m], a_hi[:, :n]
+            gh, th = g_hi[:, :n], t_hi[:, :n]
+            if x3:
+                s1a, s1b = [bm, bm, b_lo[:, :m]], [gh, g_lo[:, :n], gh]
+                s2a, s2b = [th, th, t_lo[:, :n]], [am, a_lo[:, :n], am]
+            else:
+                s1a, s1b, s2a, s2b = [bm], [gh], [th], [am]
+            ext.gemm_plan_add(plan1, s1a, s1b, False, False, None, 1.0, 0.0, False, t_hi, t_lo,
+                              0, 0, False, [], 1)
+            ext.gemm_plan_add(plan2, s2a, s2b, True, False, None, 1.0, 0.0, False, None, None,
+                              dst_ptr, n, False, extra, 1)
+        ext.gemm_plan_finalize(plan1)
+        ext.gemm_plan_finalize(plan2)
+        table = torch.tensor(rows, dtype=torch.int64, device=dev)
+        return dict(key=tuple(id(st) for st in todo), views=views, table=table, plans=(plan1, plan2),
+                    keep=keep, flat=None if arena is not None else flat)
+
+    def _precondition_kron_grouped(self, todo, grad_scale):
+        ext = ops.extension()
+        group = self._group
+        if group is None or group['key'] != tuple(id(st) for st in todo):
+            group = self._group = self._build_group(todo)
+        grads = [st.module.weight.grad for st in todo]
+        moved = [(v, g) for v, g in zip(group['views'], grads) if g.data_ptr() != v.data_ptr()]
+        if moved:
+            torch._foreach_copy_([v for v, _ in moved], [g for _, g in moved])
+        if grad_scale != 1:
+            torch._foreach_mul_(group['views'], grad_scale)
+        ext.cast_pad_bf16_grouped(group['table'], len(todo))
+        ext.gemm_plan_run(group['plans'][0])
+        ext.gemm_plan_run(group['plans'][1])
+        if moved:
+            torch._foreach_copy_([g for _, g in moved], [v for v, _ in moved])
+        for st in todo:
+            if st.has_bias and st.module.bias.grad is not None:
+                b = st.module.bias.grad
+                if grad_scale != 1:
+                    b.mul_(grad_scale)
+                b.copy_(torch.mv(st.B_inv, b))
 
     def _precondition_kron(self, st: _KronState, grad_scale, replicate=False):
         g2d, staged = st.grad_matrix()

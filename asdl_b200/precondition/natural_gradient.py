@@ -304,19 +304,60 @@ class NaturalGradientMaker(PreconditionedGradientMaker):
     def update_curvature(self):
         config = self.config
         scale = self.scale
+        distributed = self.world_size > 1
         if self.do_accumulate:
             scale = scale * config.ema_decay
+        stored = None
+        if distributed:
+            # measure the new statistics on their own, average them onto the owners, and let the
+            # owners fold them into their running curvature
+            stored = self._detach_fisher()
+        elif self.do_accumulate:
             self._scale_fisher(1 - config.ema_decay)
         self.delegate_forward_and_backward(self.fisher_maker,
                                            data_size=config.data_size,
                                            scale=scale,
-                                           accumulate=self.do_accumulate,
+                                           accumulate=self.do_accumulate and not distributed,
                                            calc_loss_grad=True,
                                            calc_inv=not self._owner_inverts,
                                            damping=config.damping)
-        self._grads_are_synced = False
-        if self.world_size > 1:
+        if distributed:
             self.reduce_scatter_curvature()
+            self._merge_fisher(stored)
+
+    def _fisher_holders(self):
+        holders = list(self.modules_for_curvature)
+        if any(True for _ in self.parameters_for(SHAPE_FULL)) and self.model not in holders:
+            holders.append(self.model)
+        return holders
+
+    def _detach_fisher(self):
+        """Remove the running curvature from the modules (returned as {module: SymMatrix})."""
+        stored = {}
+        for module in self._fisher_holders():
+            fisher = self._get_module_fisher(module)
+            if fisher is not None:
+                stored[module] = fisher
+                delattr(module, self._fisher_attr)
+        return stored
+
+    def _merge_fisher(self, stored):
+        """Owners: running <- (1 - ema_decay) * running + averaged new statistics (or just the new
+        statistics without EMA).  Other ranks keep no curvature for the layer."""
+        decay = 1 - self.config.ema_decay if self.do_accumulate else 0.0
+        for module in self._fisher_holders():
+            new = self._get_module_fisher(module)
+            owns = module is self.model or self.is_module_for_inv_and_precondition(module)
+            if not owns:
+                if new is not None:
+                    delattr(module, self._fisher_attr)
+                continue
+            old = stored.get(module)
+            if old is None or decay == 0.0 or new is None:
+                continue
+            old.mul_(decay)
+            old += new  # in place: the stored inverses stay attached
+            self._set_module_fisher(module, old)
 
     def update_preconditioner(self, damping=None, module_name=None, kron=None, zero_curvature=False,
                               partition_aware=False):

@@ -138,7 +138,7 @@ def _small_cnn():
                          nn.AdaptiveAvgPool2d(1), nn.Flatten(), nn.Linear(16, 5))
 
 
-def _fused_kfac_gpu_matches_cpu(graph):
+def _fused_kfac_gpu_matches_cpu(graph, **extra):
     torch.backends.cudnn.allow_tf32 = False
     x, t = torch.randn(8, 3, 16, 16), torch.randint(0, 5, (8,))
     cfg = asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=0.3,
@@ -160,7 +160,7 @@ def _fused_kfac_gpu_matches_cpu(graph):
 
     ref = run(copy.deepcopy(base), x, t)
     model = copy.deepcopy(base).to(DEV).to(memory_format=torch.channels_last)
-    got = run(model, x.to(DEV).contiguous(memory_format=torch.channels_last), t.to(DEV), cuda_graph=graph)
+    got = run(model, x.to(DEV).contiguous(memory_format=torch.channels_last), t.to(DEV), cuda_graph=graph, **extra)
     for (l1, g1), (l2, g2) in zip(ref, got):
         assert abs(l1 - l2) < 2e-3 * max(1, abs(l1))
         for a, b in zip(g1, g2):
@@ -170,6 +170,10 @@ def _fused_kfac_gpu_matches_cpu(graph):
 
 def test_fused_kfac_gpu_matches_cpu():
     _fused_kfac_gpu_matches_cpu(False)
+
+
+def test_fused_kfac_per_layer_launches_match_cpu():
+    _fused_kfac_gpu_matches_cpu(False, grouped=False)
 
 
 def test_smoke_entry():
