@@ -25,7 +25,7 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
 void gemm_plan_finalize(int64_t id);
 void gemm_plan_run(int64_t id);
 void cast_pad_bf16_grouped(at::Tensor table, int64_t count);
-void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot);
+void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot, int64_t wait_ms);
 void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale);
 void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs);
 void symm_scale_segments(at::Tensor local, at::Tensor segs, double beta);

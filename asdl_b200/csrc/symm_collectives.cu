@@ -3,8 +3,9 @@
 //
 //   symm_barrier          all ranks meet: each rank stores an epoch into its slot on every peer
 //                         (st.release.sys) and waits until all of its own slots carry that epoch
-//                         (ld.acquire.sys).  Every wait is bounded in wall time; on expiry the
-//                         status word is set to ERR_WAIT_PEER and the kernel returns.
+//                         (ld.acquire.sys).  Every wait is bounded in wall time (the caller
+//                         passes the limit); on expiry the status word is set to
+//                         ERR_WAIT_PEER and the kernel returns.
 //   symm_reduce_segments  the calling rank pulls the listed segments from every peer with plain
 //                         peer loads, sums them, scales, and stores the result locally
 //                         (reduce-to-owner of gradients / statistics).
@@ -52,7 +53,7 @@ __device__ __forceinline__ void st_peer_f4(float* p, float4 v) {
 }
 
 __global__ void symm_barrier_kernel(const long long* peers, int rank, int world, int slot,
-                                    int* status) {
+                                    unsigned long long wait_ns, int* status) {
   // The epoch lives in this rank's own flag area (word 63 of the slot), so the kernel carries no
   // per-call argument and can be replayed from a CUDA graph.
   __shared__ uint32_t s_epoch;
@@ -72,7 +73,7 @@ __global__ void symm_barrier_kernel(const long long* peers, int rank, int world,
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
-    if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > B200_WAIT_NS) {
+    if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > wait_ns) {
       set_error(status, ERR_WAIT_PEER);
       return;
     }
@@ -139,15 +140,17 @@ static void check_segs(const at::Tensor& segs) {
                   segs.dim() == 2 && segs.size(1) == 2, "segments must be a CUDA int64 [k, 2] tensor");
 }
 
-void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot) {
+void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot, int64_t wait_ms) {
   check_table(peers, static_cast<int>(world));
   TORCH_CHECK(world <= 63 && slot >= 0 && slot * 64 + 64 <= SYMM_FLAG_WORDS, "bad barrier slot");
+  TORCH_CHECK(wait_ms > 0 && wait_ms <= 60000, "the barrier wait limit must be in (0, 60000] ms");
   const int dev = peers.get_device();
   c10::cuda::CUDAGuard guard(dev);
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
   symm_barrier_kernel<<<1, 64, 0, stream>>>(reinterpret_cast<const long long*>(peers.data_ptr<int64_t>()),
                                             static_cast<int>(rank), static_cast<int>(world),
                                             static_cast<int>(slot),
+                                            static_cast<unsigned long long>(wait_ms) * 1000000ull,
                                             device_state(dev).status.data_ptr<int>());
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch();

@@ -1,0 +1,70 @@
+"""GPT-2 (decoder-only transformer, learned token and position embeddings, pre-norm blocks, tied
+output head) with ``nn.Linear`` projections, so that K-FAC's Linear hooks see every weight matrix
+of the blocks.  ``ignore_for_kfac`` lists the modules that K-FAC must skip on this model: the
+embeddings and the output head (a vocabulary-sized factor is 50257 x 50257) and the LayerNorms."""
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .vit import SelfAttention
+
+__all__ = ['GPT2', 'gpt2_medium', 'gpt2_tiny']
+
+
+class Block(nn.Module):
+    def __init__(self, dim, heads):
+        super().__init__()
+        self.ln_1 = nn.LayerNorm(dim)
+        self.attn = SelfAttention(dim, heads, causal=True)
+        self.ln_2 = nn.LayerNorm(dim)
+        self.fc = nn.Linear(dim, 4 * dim)
+        self.proj = nn.Linear(4 * dim, dim)
+
+    def forward(self, x):
+        x = x + self.attn(self.ln_1(x))
+        return x + self.proj(F.gelu(self.fc(self.ln_2(x)), approximate='tanh'))
+
+
+class GPT2(nn.Module):
+    def __init__(self, vocab_size=50257, n_positions=1024, n_layer=24, n_head=16, n_embd=1024):
+        super().__init__()
+        self.wte = nn.Embedding(vocab_size, n_embd)
+        self.wpe = nn.Embedding(n_positions, n_embd)
+        self.blocks = nn.ModuleList(Block(n_embd, n_head) for _ in range(n_layer))
+        self.ln_f = nn.LayerNorm(n_embd)
+        self.lm_head = nn.Linear(n_embd, vocab_size, bias=False)
+        self.lm_head.weight = self.wte.weight  # tied
+        for m in self.modules():
+            if isinstance(m, (nn.Linear, nn.Embedding)):
+                nn.init.normal_(m.weight, std=0.02)
+                if getattr(m, 'bias', None) is not None:
+                    nn.init.zeros_(m.bias)
+        for blk in self.blocks:  # residual projections are scaled down with depth
+            nn.init.normal_(blk.proj.weight, std=0.02 / (2 * n_layer) ** 0.5)
+            nn.init.normal_(blk.attn.proj.weight, std=0.02 / (2 * n_layer) ** 0.5)
+
+    def forward(self, tokens):
+        pos = torch.arange(tokens.shape[1], device=tokens.device)
+        x = self.wte(tokens) + self.wpe(pos)
+        for blk in self.blocks:
+            x = blk(x)
+        return self.lm_head(self.ln_f(x))
+
+    def ignore_for_kfac(self):
+        """Modules that K-FAC leaves to the plain gradient on this model."""
+        return [self.wte, self.wpe, self.lm_head, nn.LayerNorm]
+
+
+def next_token_loss(logits, tokens, reduction='mean'):
+    """Cross-entropy of predicting token t+1 from position t (per predicted token)."""
+    return F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).float(), tokens[:, 1:].reshape(-1),
+                           reduction=reduction)
+
+
+def gpt2_medium():
+    return GPT2(50257, 1024, 24, 16, 1024)
+
+
+def gpt2_tiny(vocab_size=97, n_positions=16):
+    """Two-block GPT-2 for tests."""
+    return GPT2(vocab_size, n_positions, 2, 2, 32)

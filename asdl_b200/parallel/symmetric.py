@@ -35,6 +35,10 @@ class SymmetricArena:
     ``rank``'s copy, valid in this process.
     """
 
+    #: wall-clock limit of every barrier wait in milliseconds; ranks drift apart by the length of
+    #: their owner-local work (inverses) and by host stalls, which this has to cover
+    barrier_wait_ms = 5000
+
     def __init__(self, numel: int, group=None, device=None):
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
@@ -50,6 +54,29 @@ class SymmetricArena:
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
         self._cursor = 0
+
+    @classmethod
+    def local_group(cls, numel: int, world: int, device=None) -> List['SymmetricArena']:
+        """``world`` arenas on ONE GPU that address each other like ranks on different GPUs do.
+
+        For exercising the pull / push / GEMM-epilogue kernels without a second GPU.  The kernels
+        of different emulated ranks run one after the other on the same stream, so anything that
+        waits for a peer cannot work: :meth:`barrier` raises on such arenas.
+        """
+        device = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
+        capacity = _round_up(int(numel), _ALIGN)
+        buffers = [torch.zeros(FLAG_WORDS + capacity, dtype=torch.float32, device=device) for _ in range(world)]
+        ptrs = [b.data_ptr() for b in buffers]
+        arenas = []
+        for r in range(world):
+            a = cls.__new__(cls)
+            a.group, a.device, a.capacity, a.buffer, a.handle = None, device, capacity, buffers[r], None
+            a.rank, a.world, a.peer_ptrs = r, world, list(ptrs)
+            a.peers_dev = torch.tensor(ptrs, dtype=torch.int64, device=device)
+            a._cursor = 0
+            a._emulated = True
+            arenas.append(a)
+        return arenas
 
     # allocation --------------------------------------------------------------------------------
     def alloc(self, *shape) -> Tuple[int, torch.Tensor]:
@@ -77,7 +104,9 @@ class SymmetricArena:
         """All ranks' work issued before the barrier (on the current stream) is complete and
         visible to all peers after it.  The wait is bounded; a timeout is reported through
         :func:`asdl_b200.ops.check_status`."""
-        ops.extension().symm_barrier(self.peers_dev, self.rank, self.world, slot)
+        if getattr(self, '_emulated', False) and self.world > 1:
+            raise RuntimeError('emulated ranks share one GPU and cannot wait for each other')
+        ops.extension().symm_barrier(self.peers_dev, self.rank, self.world, slot, int(self.barrier_wait_ms))
 
     def reduce_segments(self, segs: torch.Tensor, scale: float):
         """local[seg] <- scale * sum over ranks of their [seg] (pull over NVLink)."""

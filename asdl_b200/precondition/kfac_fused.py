@@ -21,6 +21,7 @@ from typing import Dict, List
 
 import torch
 import torch.nn as nn
+import torch.distributed as dist
 import torch.nn.functional as F
 
 from .. import ops
@@ -102,7 +103,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             copied into static buffers before every replay, ``param.grad`` is (re)bound to static
             gradient tensors that each replay overwrites (so gradients are not accumulated across
             calls in this mode), and the returned output / loss are static tensors as well.
-            Single-process CUDA runs only; anything else silently uses the eager path.
+            CUDA runs, single process or data parallel with ``comm='symmetric'`` (all ranks must
+            then see the same sequence of input shapes); anything else uses the eager path.
         grouped: apply the inverses of all layers with grouped launches (one staging kernel and
             two GEMM launches for the whole model) instead of a few launches per layer.
         comm: data-parallel transport.  ``'symmetric'`` keeps factors and gradients in NVLink
@@ -159,7 +161,10 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                 st.A_new, st.B_new = torch.zeros_like(st.A), torch.zeros_like(st.B)
             for st in self._norm:
                 st.stage = torch.zeros_like(st.stats)
-        self._graph_enabled = bool(cuda_graph) and device.type == 'cuda' and self.world_size == 1
+        # multi-rank replay needs a transport made of this library's own kernels only: their
+        # barriers keep their epochs on the device, so a replay needs no per-step host arguments
+        self._graph_enabled = (bool(cuda_graph) and device.type == 'cuda'
+                               and (self.world_size == 1 or self.comm == 'symmetric'))
         self._graph = None
         self._graph_key = None
         self._plain_steps_seen = 0
@@ -231,12 +236,17 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             for p in st.module.parameters():
                 owner_of_param[p] = st.owner
         self._grad_slot = {}
+        kron_weights = {st.module.weight for st in self._kron}
+        rest_segs = []  # owned gradients that no GEMM epilogue replicates
         for i, p in enumerate(params):
             off, flat = arena.alloc(p.numel())
             view = flat.as_strided(p.shape, p.stride())
             self._grad_slot[p] = (off, view)
             if owner_of_param.get(p, i % self.world_size) == rank:
                 grad_segs.append((off, p.numel()))
+                if p not in kron_weights:
+                    rest_segs.append((off, p.numel()))
+        self._rest_segs = arena.segments(rest_segs)
         self._sym_params = params
         self._factor_segs = arena.segments(factor_segs)
         self._stage_segs = arena.segments(stage_segs)
@@ -268,7 +278,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
     def forward_and_backward(self):
         step = self.state['step']
         plain = not self.do_update_curvature(step) and not self.do_update_preconditioner(step)
-        ready = all(st.has_inv for st in self._kron) and all(st.has_inv for st in self._norm)
+        ready = all(st.has_inv for st in self._kron + self._norm
+                    if self.is_module_for_inv_and_precondition(st.module))
         if not (self._graph_enabled and plain and ready):
             return self._eager_step(step, plain)
         slots = self._tensor_slots()
@@ -362,6 +373,11 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         self._static_grads = [p.grad for p in self._graph_params]
         self._static_output, self._static_loss = self._model_output, self._loss
         self._graph, self._graph_key = graph, key
+        if self.world_size > 1:
+            # capturing takes host time that differs between ranks; nobody replays (and waits at a
+            # device-side barrier) before everybody is done
+            torch.cuda.synchronize()
+            dist.barrier(self.sync_group)
 
     # ------------------------------------------------------------------ curvature
     def _stat_weights(self):
@@ -659,14 +675,17 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         arena.barrier()
         arena.reduce_segments(self._grad_segs, 1.0 / self.world_size)
         with nvtx_range('kfac_precondition'):
-            todo = [st for st in self._kron if st.owner == self.world_rank and st.has_inv]
+            owned = [st for st in self._kron if st.owner == self.world_rank]
+            todo = [st for st in owned if st.has_inv]
+            replicated = len(todo) == len(owned)
             if todo and self._use_grouped(todo):
                 self._precondition_kron_grouped(todo, grad_scale)
             else:
                 for st in todo:
-                    self._precondition_kron(st, grad_scale, replicate=True)
+                    replicated &= self._precondition_kron(st, grad_scale, replicate=True)
             self._precondition_norms(grad_scale)
-        arena.bcast_segments(self._grad_segs)
+        # the GEMM epilogues have already stored the Kronecker layers' results on every rank
+        arena.bcast_segments(self._rest_segs if replicated else self._grad_segs)
         arena.barrier()
 
     # grouped path: all layers' products in a handful of launches ------------------------------------
@@ -754,8 +773,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         g2d, staged = st.grad_matrix()
         if grad_scale != 1:
             g2d.mul_(grad_scale)
+        replicated = False
         if g2d.is_cuda and ops.get_backend() != 'torch':
-            self._kron_apply_cached(st, g2d, replicate and staged is None)
+            replicated = self._kron_apply_cached(st, g2d, replicate and staged is None)
         else:
             g2d.copy_(st.B_inv @ g2d @ st.A_inv)
         if staged is not None:
@@ -765,6 +785,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             if grad_scale != 1:
                 b.mul_(grad_scale)
             b.copy_(torch.mv(st.B_inv, b))
+        return replicated
 
     def _kron_apply_cached(self, st: _KronState, g2d, replicate=False):
         """g2d <- B^-1 g2d A^-1 with the cached bf16 images of the inverses.  With ``replicate``
@@ -800,12 +821,14 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             peers = [arena.ptr(r, off) for r in range(arena.world) if r != arena.rank]
             ext.umma_gemm_to_ptr(seg_a, seg_b, True, False, arena.ptr(arena.rank, off), n, 1.0,
                                  False, False, peers, 0)
+            return True
         elif g2d.stride(1) == 1:
             ext.umma_gemm(seg_a, seg_b, True, False, g2d, 1.0, 0.0, False, None, None, 0)
         else:
             out = torch.empty(m, n, device=g2d.device, dtype=torch.float32)
             ext.umma_gemm(seg_a, seg_b, True, False, out, 1.0, 0.0, False, None, None, 0)
             g2d.copy_(out)
+        return False
 
     def _precondition_norms(self, grad_scale):
         gw, gb, i00, i01, i10, i11 = [], [], [], [], [], []

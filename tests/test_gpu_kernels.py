@@ -206,5 +206,76 @@ def test_chol_inverse_grouped(sizes):
     assert rel_err(single, outs[0]) < 1e-6
 
 
+def test_symmetric_segment_kernels_on_emulated_ranks(ext):
+    """Pull-reduce, push-broadcast and decay kernels with three ranks emulated on one GPU."""
+    from asdl_b200.parallel.symmetric import SymmetricArena
+    arenas = SymmetricArena.local_group(5000, 3)
+    slots = [[a.alloc(37, 20), a.alloc(1000), a.alloc(8)] for a in arenas]
+    torch.manual_seed(0)
+    for per_rank in slots:
+        for _, view in per_rank:
+            view.copy_(torch.randn_like(view))
+    before = [[v.clone() for _, v in per_rank] for per_rank in slots]
+    owner = arenas[1]
+    segs = owner.segments([(slots[1][0][0], 37 * 20), (slots[1][2][0], 8)])
+    owner.reduce_segments(segs, 1.0 / 3)
+    for k in (0, 2):
+        ref = sum(before[r][k] for r in range(3)) / 3
+        assert torch.allclose(slots[1][k][1], ref, atol=1e-6)
+        assert torch.equal(slots[0][k][1], before[0][k])  # peers are only read
+    assert torch.equal(slots[1][1][1], before[1][1])      # segments not listed stay
+    owner.bcast_segments(segs)
+    for r in (0, 2):
+        for k in (0, 2):
+            assert torch.equal(slots[r][k][1], slots[1][k][1])
+        assert torch.equal(slots[r][1][1], before[r][1])
+    owner.scale_segments(owner.segments([(slots[1][1][0], 1000)]), 0.25)
+    assert torch.allclose(slots[1][1][1], before[1][1] * 0.25)
+    with pytest.raises(RuntimeError):
+        owner.barrier()
+    ops.check_status()
+
+
+def test_gemm_epilogue_reduces_into_and_replicates_to_other_buffers(ext):
+    """The epilogue paths of the data-parallel transport, aimed at plain buffers of this GPU: tiles
+    added into a destination that already holds data (statistics pushed to an owner) and results
+    stored to several destinations (preconditioned gradients replicated to every rank)."""
+    torch.manual_seed(0)
+    x = torch.randn(3000, 200, device=DEV).to(torch.bfloat16)
+    ref = x.float().T @ x.float()
+    target = torch.randn(200, 200, device=DEV)
+    held = target.clone()
+    for _ in range(2):  # two ranks' contributions
+        ext.umma_gemm_to_ptr([x], [x], False, False, target.data_ptr(), 200, 0.5, True, True, [], 0)
+    assert rel_err(target, held + ref) < 1e-4
+    a = torch.randn(96, 160, device=DEV).to(torch.bfloat16)   # [K, M]
+    b = torch.randn(96, 72, device=DEV).to(torch.bfloat16)    # [K, N]
+    outs = [torch.zeros(160, 72, device=DEV) for _ in range(4)]
+    ext.umma_gemm_to_ptr([a], [b], False, False, outs[0].data_ptr(), 72, 2.0, False, False,
+                         [o.data_ptr() for o in outs[1:]], 0)
+    want = 2.0 * a.float().T @ b.float()
+    for o in outs:
+        assert rel_err(o, want) < 1e-5
+    ops.check_status()
+
+
+def test_barrier_completes_alone_and_gives_up_on_a_missing_peer(ext):
+    """A one-rank barrier passes.  A two-rank barrier whose peer never arrives runs into its wait
+    limit, reports it through the status word and leaves the context usable."""
+    from asdl_b200.parallel.symmetric import SymmetricArena
+    solo = SymmetricArena.local_group(64, 1)[0]
+    for _ in range(3):
+        solo.barrier()
+    ops.check_status()
+    assert solo.buffer[:256].view(torch.int32)[63].item() == 3   # entered three times
+    pair = SymmetricArena.local_group(64, 2)
+    ext.symm_barrier(pair[0].peers_dev, 0, 2, 0, 50)             # nothing ever sets rank 1's flag
+    with pytest.raises(RuntimeError, match='peer'):
+        ops.check_status()
+    ops.check_status()                                           # the status was cleared by the read
+    y = torch.randn(256, 64, device=DEV)
+    assert rel_err(ops.gram(y), y.T @ y) < 5e-5                   # the GPU still works
+
+
 def test_fused_kfac_cuda_graph_matches_cpu():
     _fused_kfac_gpu_matches_cpu(True)

@@ -1,0 +1,67 @@
+"""The benchmark model families step through their makers (tiny versions, CPU)."""
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+import asdl_b200 as asdl
+from asdl_b200.models import vit_tiny, gpt2_tiny, next_token_loss, resnet_tiny
+
+
+def _steps(gm, model, x, loss_fn, t, n=3, lr=0.01):
+    opt = torch.optim.SGD(model.parameters(), lr=lr)
+    losses = []
+    for _ in range(n):
+        opt.zero_grad()
+        d = gm.setup_model_call(model, x)
+        gm.setup_loss_call(loss_fn, d, t)
+        _, loss = gm.forward_and_backward()
+        assert all(torch.isfinite(p.grad).all() for p in model.parameters() if p.grad is not None)
+        opt.step()
+        losses.append(loss.item())
+    return losses
+
+
+def test_vit_shampoo_blocks_every_matrix():
+    torch.manual_seed(0)
+    model = vit_tiny()
+    x, t = torch.randn(4, 3, 32, 32), torch.randint(0, 10, (4,))
+    cfg = asdl.PreconditioningConfig(damping=1e-6, preconditioner_upd_interval=2)
+    gm = asdl.ShampooGradientMaker(model, cfg, block_size=16)
+    losses = _steps(gm, model, x, F.cross_entropy, t, n=4, lr=1e-3)
+    assert losses[-1] < losses[0]
+    shapes = {tuple(p.shape) for p in model.parameters() if p.ndim > 1}
+    assert (96, 32) in shapes and (32, 3, 8, 8) in shapes and (1, 17, 32) in shapes
+    assert len(gm.preconditioners) == len([p for p in model.parameters() if p.ndim > 1])
+
+
+def test_vit_kfac_sees_attention_projections():
+    torch.manual_seed(0)
+    model = vit_tiny()
+    x, t = torch.randn(4, 3, 32, 32), torch.randint(0, 10, (4,))
+    cfg = asdl.PreconditioningConfig(data_size=4, damping=1e-2)
+    gm = asdl.FusedKfacGradientMaker(model, cfg, fisher_type=asdl.FISHER_EMP)
+    _steps(gm, model, x, F.cross_entropy, t)
+    assert model.layers[0].attn.qkv.fisher.kron.A.shape == (32, 32)
+    assert model.layers[0].attn.qkv.fisher.kron.B.shape == (96, 96)
+
+
+def test_gpt2_kfac_on_block_linears_only():
+    torch.manual_seed(0)
+    model = gpt2_tiny()
+    tokens = torch.randint(0, 97, (2, 16))
+    cfg = asdl.PreconditioningConfig(data_size=2, damping=1e-3, ignore_modules=model.ignore_for_kfac())
+    gm = asdl.FusedKfacGradientMaker(model, cfg, fisher_type=asdl.FISHER_EMP)
+    losses = _steps(gm, model, tokens, next_token_loss, tokens, n=3)
+    assert losses[-1] < losses[0] + 1e-3
+    assert len(gm._kron) == 2 * 4 and not gm._norm
+    assert not hasattr(model.lm_head, 'fisher') and not hasattr(model.wte, 'fisher')
+    assert model.blocks[1].proj.fisher.kron.A.shape == (128, 128)
+
+
+def test_resnet_tiny_kfac_reference_maker():
+    torch.manual_seed(0)
+    model = resnet_tiny()
+    x, t = torch.randn(4, 3, 32, 32), torch.randint(0, 10, (4,))
+    cfg = asdl.PreconditioningConfig(data_size=4, damping=1e-2)
+    gm = asdl.KfacGradientMaker(model, cfg, fisher_type=asdl.FISHER_EMP)
+    _steps(gm, model, x, F.cross_entropy, t, n=2)
