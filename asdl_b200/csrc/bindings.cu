@@ -25,6 +25,8 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
 void gemm_plan_finalize(int64_t id);
 void gemm_plan_run(int64_t id);
 void cast_pad_bf16_grouped(at::Tensor table, int64_t count);
+void bn_unitwise_stats(at::Tensor y, at::Tensor g, at::Tensor weight, at::Tensor bias, at::Tensor stats,
+                       double alpha, double beta);
 void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot, int64_t wait_ms);
 void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale);
 void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs);
@@ -49,6 +51,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_plan_finalize", &b200::gemm_plan_finalize);
   m.def("gemm_plan_run", &b200::gemm_plan_run);
   m.def("cast_pad_bf16_grouped", &b200::cast_pad_bf16_grouped);
+  m.def("bn_unitwise_stats", &b200::bn_unitwise_stats);
   m.def("symm_barrier", &b200::symm_barrier);
   m.def("symm_reduce_segments", &b200::symm_reduce_segments);
   m.def("symm_bcast_segments", &b200::symm_bcast_segments);

@@ -19,7 +19,7 @@ import torch
 
 from . import _build
 
-__all__ = ['gram', 'matmul_tn', 'kron_apply', 'spd_inverse', 'spd_inverse_grouped', 'unitwise_inverse', 'conv_patch_gram',
+__all__ = ['gram', 'matmul_tn', 'kron_apply', 'spd_inverse', 'spd_inverse_grouped', 'unitwise_inverse', 'batchnorm_unitwise_stats', 'conv_patch_gram',
            'set_backend', 'get_backend', 'set_precision', 'get_precision', 'extension',
            'cuda_kernels_enabled', 'check_status']
 
@@ -287,6 +287,37 @@ def spd_inverse_grouped(mats, outs, damping):
         eye = torch.eye(m.shape[-1], device=m.device, dtype=m.dtype)
         o.copy_(torch.cholesky_inverse(torch.linalg.cholesky(m + d.to(m.dtype) * eye)))
     return outs
+
+
+def batchnorm_unitwise_stats(y: torch.Tensor, g: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+                             out: Optional[torch.Tensor] = None, alpha: float = 1.0,
+                             beta: float = 0.0) -> torch.Tensor:
+    """Unit-wise curvature blocks of a BatchNorm layer from its output ``y`` and output gradient
+    ``g`` ([n, c, *spatial]):  ``out <- beta * out + alpha * sum_n [[gw^2, gw gb], [gw gb, gb^2]]``
+    with per-sample ``gw = sum_spatial ((y - bias) / weight) * g`` and ``gb = sum_spatial g``
+    (out: [c, 2, 2] fp32).  CUDA, 4-d channels_last bf16/fp32: one pass over y and g with the
+    library's kernel; anything else: PyTorch."""
+    c = y.shape[1]
+    if out is None:
+        out = torch.zeros(c, 2, 2, device=y.device, dtype=torch.float32)
+        beta = 0.0
+    vec = 8 if y.dtype == torch.bfloat16 else 4
+    if (cuda_kernels_enabled(y, g) and y.ndim == 4 and y.dtype in (torch.bfloat16, torch.float32)
+            and g.dtype == y.dtype and c % vec == 0 and weight.dtype == torch.float32
+            and y.is_contiguous(memory_format=torch.channels_last) and out.is_contiguous()):
+        if not g.is_contiguous(memory_format=torch.channels_last):
+            g = g.contiguous(memory_format=torch.channels_last)
+        extension().bn_unitwise_stats(y, g, weight.detach().contiguous(), bias.detach().contiguous(), out,
+                                      float(alpha), float(beta))
+        return out
+    shape = (1, -1) + (1,) * (y.ndim - 2)
+    xh = (y.float() - bias.view(shape)) / weight.view(shape)
+    dims = tuple(range(2, y.ndim))
+    gw = (xh * g).sum(dim=dims) if dims else xh * g
+    gb = g.float().sum(dim=dims) if dims else g.float()
+    ww, wb, bb = gw.square().sum(dim=0), (gw * gb).sum(dim=0), gb.square().sum(dim=0)
+    new = torch.stack([torch.stack([ww, wb], dim=1), torch.stack([wb, bb], dim=1)], dim=1)
+    return out.mul_(beta).add_(new, alpha=alpha)
 
 
 def unitwise_inverse(blocks: torch.Tensor, damping: float = 0.0) -> torch.Tensor:

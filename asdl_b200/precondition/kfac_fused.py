@@ -165,10 +165,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         # barriers keep their epochs on the device, so a replay needs no per-step host arguments
         self._graph_enabled = (bool(cuda_graph) and device.type == 'cuda'
                                and (self.world_size == 1 or self.comm == 'symmetric'))
-        self._graph = None
+        self._graphs = {}              # 'plain' / 'curvature' -> captured step
         self._graph_key = None
         self._plain_steps_seen = 0
-        self._graph_launches = 0       # custom-kernel launches recorded in the captured graph
         self.replayed_launches = 0     # ... summed over all replays so far
         self._timing = None            # phase -> list of (start, end) CUDA events
         if self._graph_enabled:
@@ -185,12 +184,13 @@ class FusedKfacGradientMaker(KfacGradientMaker):
 
         class _Ctx:
             def __enter__(self_inner):
-                if maker._timing is not None:
+                self_inner.start = None
+                if maker._timing is not None and not torch.cuda.is_current_stream_capturing():
                     self_inner.start = torch.cuda.Event(enable_timing=True)
                     self_inner.start.record()
 
             def __exit__(self_inner, *exc):
-                if maker._timing is not None:
+                if maker._timing is not None and self_inner.start is not None:
                     end = torch.cuda.Event(enable_timing=True)
                     end.record()
                     maker._timing.setdefault(name, []).append((self_inner.start, end))
@@ -277,30 +277,35 @@ class FusedKfacGradientMaker(KfacGradientMaker):
 
     def forward_and_backward(self):
         step = self.state['step']
-        plain = not self.do_update_curvature(step) and not self.do_update_preconditioner(step)
+        curv, prec = self.do_update_curvature(step), self.do_update_preconditioner(step)
+        plain = not curv and not prec
+        kind = 'plain' if plain else ('curvature' if curv and not prec else None)
         ready = all(st.has_inv for st in self._kron + self._norm
                     if self.is_module_for_inv_and_precondition(st.module))
-        if not (self._graph_enabled and plain and ready):
+        if not (self._graph_enabled and kind is not None and ready):
             return self._eager_step(step, plain)
         slots = self._tensor_slots()
         key = tuple((tuple(v.shape), v.dtype, v.stride()) for _, _, v in slots)
-        if self._graph is None:
+        if not self._graphs:
+            if kind != 'plain':
+                return self._eager_step(step, plain)
             self._plain_steps_seen += 1
             if self._plain_steps_seen <= 2:  # let lazy initialisation happen eagerly first
                 return self._eager_step(step, plain)
             self._capture(slots, key)
-        elif key != self._graph_key:
+        if key != self._graph_key or kind not in self._graphs:
             return self._eager_step(step, plain)
+        captured = self._graphs[kind]
         with torch.no_grad():
             for static, (_, _, value) in zip(self._static_inputs, slots):
                 if static.data_ptr() != value.data_ptr():
                     static.copy_(value, non_blocking=True)
-        with self._phase('plain_step_graph'):
-            self._graph.replay()
-        self.replayed_launches += self._graph_launches
-        for p, g in zip(self._graph_params, self._static_grads):
+        with self._phase('plain_step_graph' if plain else 'curvature_step_graph'):
+            captured['graph'].replay()
+        self.replayed_launches += captured['launches']
+        for p, g in zip(self._graph_params, captured['grads']):
             p.grad = g
-        self._model_output, self._loss = self._static_output, self._static_loss
+        self._model_output, self._loss = captured['output'], captured['loss']
         self.state['step'] += 1
         return self._model_output, self._loss
 
@@ -309,6 +314,14 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             return KfacGradientMaker.forward_and_backward(self)
 
     def _capture(self, slots, key):
+        """Capture the step without updates and, where possible, the step that also measures the
+        curvature.  Both run on fresh leaf views of the parameters: autograd's gradient
+        accumulators remember the stream they were created on - for the real parameters that may
+        be the legacy default stream, which a capture must not touch, and they stay alive as long
+        as anybody holds an output of an earlier step.  Views created inside the capture get their
+        accumulators on the capture stream; gradients come from ``torch.autograd.grad`` and are
+        bound to ``param.grad`` by hand.  Two warm-up rounds run on the capture stream first;
+        everything they change (running statistics of the model, curvature) is restored after."""
         self._static_inputs = [v.clone() for _, _, v in slots]
 
         def rebound(container, index_of):
@@ -323,56 +336,81 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         self._model_args, self._model_kwargs, self._loss_fn_args, self._loss_fn_kwargs = (
             rebound(c, index_of) for c in saved)
         self._graph_params = [p for p in self.model.parameters() if p.requires_grad]
-        # Inside the capture the model runs on fresh leaf views of its parameters.  Autograd's
-        # gradient accumulators remember the stream they were created on - for the real
-        # parameters that may be the legacy default stream, which a capture must not touch, and
-        # they stay alive as long as anybody holds an output of an earlier step.  Views created
-        # here get their accumulators on the capture stream.  Gradients come from autograd.grad
-        # and are bound to param.grad by hand.  Two warm-up rounds run on the capture stream
-        # first; buffers that the forward pass updates (running statistics) are restored after.
         from torch.nn.utils.stateless import _reparametrize_module
         names = [n for n, p in self.model.named_parameters() if p.requires_grad]
 
+        def fresh_views():
+            return [p.detach().requires_grad_(True) for p in self._graph_params]
+
+        def detach_results():
+            self._loss = self._loss.detach()
+            if isinstance(self._model_output, torch.Tensor):
+                self._model_output = self._model_output.detach()
+
         def plain_step():
-            views = [p.detach().requires_grad_(True) for p in self._graph_params]
+            views = fresh_views()
             with _reparametrize_module(self.model, dict(zip(names, views))):
                 self.forward()
             grads = torch.autograd.grad(self._loss, views, allow_unused=True)
             for p, g in zip(self._graph_params, grads):
                 p.grad = g if g is not None else torch.zeros_like(p)
-            self._loss = self._loss.detach()
-            if isinstance(self._model_output, torch.Tensor):
-                self._model_output = self._model_output.detach()
+            detach_results()
+            self.precondition()
+
+        # the sampling passes of the Monte-Carlo Fisher only need gradients of activations: ask for
+        # the gradient of a floating-point model input, which every layer's output leads to
+        float_inputs = [t for t in self._static_inputs
+                        if t.is_floating_point() and any(t is a for a in self._model_args)]
+
+        def curvature_step():
+            for t in float_inputs:
+                t.requires_grad_(True)
+            try:
+                self.update_curvature(views=fresh_views(), names=names, through=float_inputs or None)
+            finally:
+                for t in float_inputs:
+                    t.requires_grad_(False)
+            detach_results()
             self.precondition()
 
         stream = torch.cuda.Stream()
-        buffers = [b for b in self.model.buffers()]
-        saved_buffers = [b.detach().clone() for b in buffers]
-        stream.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(stream):
-            for _ in range(2):
+        kinds = [('plain', plain_step)]
+        if self.fisher_maker.config.seed is None:
+            kinds.append(('curvature', curvature_step))
+        restore = [b for b in self.model.buffers()]
+        restore += [t for st in self._kron for t in (st.A, st.B)] + [st.stats for st in self._norm]
+        pool = None
+        try:
+            for kind, fn in kinds:
+                saved_state = [b.detach().clone() for b in restore]
+                stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(stream):
+                    for _ in range(2):
+                        for p in self._graph_params:
+                            p.grad = None
+                        fn()
+                torch.cuda.current_stream().wait_stream(stream)
+                torch.cuda.synchronize()
+                if self.world_size > 1:
+                    dist.barrier(self.sync_group)  # peers have stopped adding to this rank's factors
+                with torch.no_grad():
+                    torch._foreach_copy_(restore, saved_state)
+                del saved_state
                 for p in self._graph_params:
                     p.grad = None
-                plain_step()
-        torch.cuda.current_stream().wait_stream(stream)
-        with torch.no_grad():
-            for b, s_ in zip(buffers, saved_buffers):
-                b.copy_(s_)
-        for p in self._graph_params:
-            p.grad = None
-        self._model_output = self._loss = None
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        launches_before = ops.extension().launch_count()
-        try:
-            with torch.cuda.graph(graph, stream=stream):
-                plain_step()
-            self._graph_launches = ops.extension().launch_count() - launches_before
+                self._model_output = self._loss = None
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                launches_before = ops.extension().launch_count()
+                with torch.cuda.graph(graph, stream=stream, pool=pool):
+                    fn()
+                pool = graph.pool()
+                self._graphs[kind] = dict(graph=graph, grads=[p.grad for p in self._graph_params],
+                                          output=self._model_output, loss=self._loss,
+                                          launches=ops.extension().launch_count() - launches_before)
         finally:
             self._model_args, self._model_kwargs, self._loss_fn_args, self._loss_fn_kwargs = saved
-        self._static_grads = [p.grad for p in self._graph_params]
-        self._static_output, self._static_loss = self._model_output, self._loss
-        self._graph, self._graph_key = graph, key
+        self._graph_key = key
         if self.world_size > 1:
             # capturing takes host time that differs between ranks; nobody replays (and waits at a
             # device-side barrier) before everybody is done
@@ -495,27 +533,32 @@ class FusedKfacGradientMaker(KfacGradientMaker):
     @staticmethod
     def _norm_statistics(st: _NormState, y, g, alpha, beta):
         module = st.module
-        if isinstance(module, nn.LayerNorm):
-            k = module.weight.ndim
-            xh = (y.float() - module.bias) / module.weight
-            gw = (xh * g).reshape(-1, *y.shape[-k:]).flatten(start_dim=1)
-            gb = g.float().reshape(-1, *y.shape[-k:]).flatten(start_dim=1)
-        else:
-            shape = (1, -1) + (1,) * (y.ndim - 2)
-            xh = (y.float() - module.bias.view(shape)) / module.weight.view(shape)
-            dims = tuple(range(2, y.ndim))
-            gw = (xh * g).sum(dim=dims) if dims else xh * g
-            gb = g.float().sum(dim=dims) if dims else g.float()
+        staged = getattr(st, 'stage', None) is not None  # reduced over ranks after the backward pass
+        target = st.stage if staged else st.stats
+        if staged:
+            alpha, beta = 1.0, 0.0
+        if not isinstance(module, nn.LayerNorm):
+            ops.batchnorm_unitwise_stats(y, g, module.weight, module.bias, out=target, alpha=alpha, beta=beta)
+            return
+        k = module.weight.ndim
+        xh = (y.float() - module.bias) / module.weight
+        gw = (xh * g).reshape(-1, *y.shape[-k:]).flatten(start_dim=1)
+        gb = g.float().reshape(-1, *y.shape[-k:]).flatten(start_dim=1)
         ww = gw.square().sum(dim=0)
         wb = (gw * gb).sum(dim=0)
         bb = gb.square().sum(dim=0)
         new = torch.stack([torch.stack([ww, wb], dim=1), torch.stack([wb, bb], dim=1)], dim=1)
-        if getattr(st, 'stage', None) is not None:
-            st.stage.copy_(new)  # reduced over ranks by the owner after the backward pass
-        else:
-            st.stats.mul_(beta).add_(new, alpha=alpha)
+        target.mul_(beta).add_(new, alpha=alpha)
 
-    def update_curvature(self):
+    def update_curvature(self, views=None, names=None, through=None):
+        """One pass that measures the statistics and leaves the (averaged) loss gradient in
+        ``param.grad``.
+
+        ``views`` / ``names`` (used while capturing a CUDA graph): fresh leaf views of the parameters
+        that the model runs on; gradients then come from ``torch.autograd.grad`` instead of
+        ``backward()``.  ``through``: tensors whose gradient is requested in the sampling passes of
+        the Monte-Carlo Fisher so that the output hooks of every layer fire (``None``: the
+        parameters' ``requires_grad`` is switched off and ``backward()`` is used)."""
         cfg = self.config
         model = self.model
         handles, state = self._install_hooks()
@@ -525,9 +568,23 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             # owners decay their factors; nobody may add before every owner has done so
             self._arena.scale_segments(self._factor_segs, self._stat_weights()[1])
             self._arena.barrier()
+
+        def backward(loss_, retain=False):
+            if views is None:
+                loss_.backward(retain_graph=retain)
+                return
+            grads = torch.autograd.grad(loss_, views, allow_unused=True, retain_graph=retain)
+            for p, g in zip(self._graph_params, grads):
+                p.grad = g if g is not None else torch.zeros_like(p)
+
         try:
             with nvtx_range('kfac_curvature'), self._phase('curvature'):
-                self.call_model()
+                if views is None:
+                    self.call_model()
+                else:
+                    from torch.nn.utils.stateless import _reparametrize_module
+                    with _reparametrize_module(model, dict(zip(names, views))):
+                        self.call_model()
                 saved = self._loss_reduction
                 self._loss_reduction = 'sum'
                 try:
@@ -535,7 +592,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                 finally:
                     self._loss_reduction = saved
                 if self.fisher_type == FISHER_EMP:
-                    loss.backward()
+                    backward(loss)
                 else:
                     logits = self._logits
                     n_mc = self.fisher_maker.config.n_mc_samples
@@ -544,19 +601,23 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                         with torch.no_grad():
                             targets = torch.multinomial(log_probs.exp(), 1).squeeze(1)
                         nll = F.nll_loss(log_probs, targets, reduction='sum') / n_mc
-                        with skip_param_grad(model):
-                            nll.backward(retain_graph=True)
+                        if views is None:
+                            with skip_param_grad(model):
+                                nll.backward(retain_graph=True)
+                        else:
+                            torch.autograd.grad(nll, through if through else views,
+                                                retain_graph=True, allow_unused=True)
                     state['on'] = False
-                    loss.backward()
+                    backward(loss)
         finally:
             state['on'] = False
             for h in handles:
                 h.remove()
         with torch.no_grad():
-            for p in model.parameters():
-                if p.grad is not None:
-                    p.grad.div_(cfg.data_size)
-            loss.div_(cfg.data_size)
+            grads = [p.grad for p in model.parameters() if p.grad is not None]
+            if grads:
+                torch._foreach_div_(grads, cfg.data_size)
+            loss = loss.detach().div_(cfg.data_size) if views is not None else loss.div_(cfg.data_size)
         self._loss = loss
         if self._arena is not None:
             alpha, beta = self._stat_weights()
@@ -671,10 +732,11 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         """barrier -> owners pull-reduce the gradients of their layers -> precondition (the final
         GEMM stores into every rank's gradient buffer) -> push the small rest -> barrier."""
         arena = self._arena
-        self._bind_grads_to_arena()
-        arena.barrier()
-        arena.reduce_segments(self._grad_segs, 1.0 / self.world_size)
-        with nvtx_range('kfac_precondition'):
+        with self._phase('grad_reduce'):
+            self._bind_grads_to_arena()
+            arena.barrier()
+            arena.reduce_segments(self._grad_segs, 1.0 / self.world_size)
+        with nvtx_range('kfac_precondition'), self._phase('precondition'):
             owned = [st for st in self._kron if st.owner == self.world_rank]
             todo = [st for st in owned if st.has_inv]
             replicated = len(todo) == len(owned)
@@ -685,8 +747,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                     replicated &= self._precondition_kron(st, grad_scale, replicate=True)
             self._precondition_norms(grad_scale)
         # the GEMM epilogues have already stored the Kronecker layers' results on every rank
-        arena.bcast_segments(self._rest_segs if replicated else self._grad_segs)
-        arena.barrier()
+        with self._phase('grad_bcast'):
+            arena.bcast_segments(self._rest_segs if replicated else self._grad_segs)
+            arena.barrier()
 
     # grouped path: all layers' products in a handful of launches ------------------------------------
     def _use_grouped(self, todo):

@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', choices=['ours', 'reference'], default='ours')
     ap.add_argument('--no-graph', action='store_true', help='disable CUDA-graph replay of plain steps')
+    ap.add_argument('--nvtx', action='store_true',
+                    help="wrap every device-timed step in an NVTX range ('plain_step' / 'curvature_step')")
     ap.add_argument('--precond-precision', default='bf16x3', choices=['bf16', 'bf16x3'])
     return ap.parse_args()
 
@@ -233,7 +235,11 @@ def main():
     for _ in range(args.steps):
         flush.zero_()
         x, t = dev_batches[it % n_host]
+        if args.nvtx:  # a profiler can select one kind of step by range name
+            torch.cuda.nvtx.range_push('curvature_step' if it % 10 == 0 else 'plain_step')
         loss = step(x, t)
+        if args.nvtx:
+            torch.cuda.nvtx.range_pop()
         it += 1
     e1.record()
     barrier(world)

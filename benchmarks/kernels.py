@@ -1,0 +1,170 @@
+"""Device-timed micro-benchmarks of the library's sm_100a kernels, one JSON line per case.
+
+    python benchmarks/kernels.py                    # all cases
+    python benchmarks/kernels.py --only syrk --rows 8192 --n 4096 --iters 3 --warmup 1   # one small case (profiling)
+
+Every case reports the CUDA-event time (L2 flushed between iterations by writing a 256 MiB buffer),
+the algorithmic FLOP/s or bytes/s, the fraction of the measured peak of the GPU
+(MEASURED_PEAKS.json beside the repository root if present, else 6.65 TB/s and 1.59 PFLOP/s) and,
+where a library routine computes the same thing, its time (cuBLAS through torch.matmul,
+cuSOLVER through torch.linalg).
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from asdl_b200 import ops  # noqa: E402
+
+
+def peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p['hbm_gbs'] * 1e9, p['bf16_tflops'] * 1e12, 'measured'
+    return 6.65e12, 1.59e15, 'fallback'
+
+
+class Timer:
+    def __init__(self, iters, warmup):
+        self.iters, self.warmup = iters, warmup
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device='cuda')
+
+    def __call__(self, fn):
+        for _ in range(self.warmup):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(self.iters):
+            self.flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        times.sort()
+        return times[len(times) // 2]
+
+
+def emit(**kw):
+    print(json.dumps(kw), flush=True)
+
+
+def bench_syrk(timer, rows, n, hbm, flops_peak, src):
+    """C = X^T X, X bf16 [rows, n]; useful FLOPs counted as the full 2*rows*n^2 product (what the
+    library GEMM computes), so a SYRK that only forms the lower triangle can exceed 1.0."""
+    ext = ops.extension()
+    x = torch.randn(rows, n, device='cuda').to(torch.bfloat16)
+    out = torch.empty(n, n, device='cuda')
+    ms = timer(lambda: ext.umma_gemm([x], [x], False, False, out, 1.0, 0.0, True, None, None, 0))
+    ms_lib = timer(lambda: torch.matmul(x.T, x))
+    fl = 2.0 * rows * n * n
+    by = 2.0 * rows * n + 4.0 * n * n
+    emit(case='syrk_bf16', rows=rows, n=n, ms=round(ms, 4), tflops=round(fl / ms / 1e9, 1),
+         frac_of_peak_flops=round(fl / (ms * 1e-3) / flops_peak, 3),
+         frac_of_peak_hbm=round(by / (ms * 1e-3) / hbm, 3), peak_source=src,
+         cublas_bf16_ms=round(ms_lib, 4), speedup_vs_cublas=round(ms_lib / ms, 2))
+
+
+def bench_syrk_x3(timer, rows, n, hbm, flops_peak, src):
+    """fp32-grade X^T X from bf16 hi/lo splits (three tensor-core passes) against cuBLAS fp32."""
+    x = torch.randn(rows, n, device='cuda')
+    out = torch.empty(n, n, device='cuda')
+    ms = timer(lambda: ops.gram(x, out=out))
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ms_lib = timer(lambda: torch.matmul(x.T, x))
+    torch.backends.cuda.matmul.allow_tf32 = True
+    ms_tf32 = timer(lambda: torch.matmul(x.T, x))
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    emit(case='syrk_fp32_as_bf16x3', rows=rows, n=n, ms=round(ms, 4), cublas_fp32_ms=round(ms_lib, 4),
+         cublas_tf32_ms=round(ms_tf32, 4), includes='hi/lo split cast of the input')
+
+
+def bench_precond(timer, m, n, hbm, flops_peak, src):
+    left = torch.randn(m, m, device='cuda')
+    left = left @ left.T / m
+    right = torch.randn(n, n, device='cuda')
+    right = right @ right.T / n
+    g = torch.randn(m, n, device='cuda')
+    ms = timer(lambda: ops.kron_apply(left, g, right))
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ms_lib = timer(lambda: left @ g @ right)
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    emit(case='kron_apply_fp32', m=m, n=n, ms=round(ms, 4), cublas_fp32_ms=round(ms_lib, 4),
+         includes='hi/lo split casts of all three operands (the K-FAC maker caches those of the inverses)')
+
+
+def bench_inverse(timer, sizes, hbm, flops_peak, src):
+    mats = []
+    for s in sizes:
+        a = torch.randn(s, 2 * s, device='cuda')
+        mats.append(a @ a.T / (2 * s))
+    outs = [torch.empty_like(m) for m in mats]
+    ms = timer(lambda: ops.spd_inverse_grouped(mats, outs, 1e-3))
+
+    def lib():
+        for m in mats:
+            eye = torch.eye(m.shape[0], device='cuda')
+            torch.cholesky_inverse(torch.linalg.cholesky(m + 1e-3 * eye))
+    ms_lib = timer(lib)
+    fl = sum(float(s) ** 3 for s in sizes)  # potrf n^3/3 + trtri n^3/3 + lauum n^3/3
+    emit(case='chol_inverse_grouped_fp32', sizes=sizes, ms=round(ms, 3), tflops_fp32=round(fl / ms / 1e9, 2),
+         cusolver_loop_ms=round(ms_lib, 3), speedup_vs_cusolver=round(ms_lib / ms, 2))
+
+
+def bench_im2col(timer, n, c, hw, k, stride, pad, hbm, flops_peak, src):
+    ext = ops.extension()
+    x = torch.randn(n, c, hw, hw, device='cuda').to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    ho = (hw + 2 * pad - k) // stride + 1
+    ncol = c * k * k
+    ld = (ncol + 7) // 8 * 8
+    out = torch.empty(n * ho * ho, ld, device='cuda', dtype=torch.bfloat16)
+    ms = timer(lambda: ext.im2col_bf16(x, out, None, [k, k], [stride, stride], [pad, pad], [1, 1], False))
+    by = 2.0 * x.numel() + 2.0 * out.numel()
+    emit(case='im2col_bf16_nhwc', shape=[n, c, hw, hw], kernel=k, stride=stride, ms=round(ms, 4),
+         gbs=round(by / ms / 1e6, 1), frac_of_peak_hbm=round(by / (ms * 1e-3) / hbm, 3), peak_source=src)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--only', default=None, choices=['syrk', 'syrk_x3', 'precond', 'inverse', 'im2col'])
+    ap.add_argument('--rows', type=int, default=None)
+    ap.add_argument('--n', type=int, default=None)
+    ap.add_argument('--iters', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    args = ap.parse_args()
+    hbm, fl, src = peaks()
+    timer = Timer(args.iters, args.warmup)
+    want = lambda name: args.only in (None, name)  # noqa: E731
+    if want('syrk'):
+        cases = [(args.rows, args.n)] if args.rows and args.n else \
+            [(100352, 64), (100352, 256), (25088, 512), (25088, 1152), (6272, 2304), (6272, 1024), (1568, 4608),
+             (1568, 2048), (8192, 1024), (8192, 4096), (4096, 8192), (32768, 4096)]
+        for rows, n in cases:
+            bench_syrk(timer, rows, n, hbm, fl, src)
+    if want('syrk_x3'):
+        for rows, n in ([(args.rows, args.n)] if args.rows and args.n else [(8192, 1024), (8192, 4096)]):
+            bench_syrk_x3(timer, rows, n, hbm, fl, src)
+    if want('precond'):
+        for m, n in [(512, 4608), (2048, 512), (1024, 4096), (4096, 1024)]:
+            bench_precond(timer, m, n, hbm, fl, src)
+    if want('inverse'):
+        for sizes in ([args.n] if args.n else None, [4608], [1024] * 8, [64] * 16 + [256] * 16 + [512] * 8 + [1024] * 8 + [2304] * 6):
+            if sizes:
+                bench_inverse(timer, sizes, hbm, fl, src)
+    if want('im2col'):
+        bench_im2col(timer, 32, 64, 56, 3, 1, 1, hbm, fl, src)
+        bench_im2col(timer, 32, 256, 14, 3, 1, 1, hbm, fl, src)
+    ops.check_status()
+
+
+if __name__ == '__main__':
+    main()

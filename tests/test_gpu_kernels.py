@@ -206,6 +206,29 @@ def test_chol_inverse_grouped(sizes):
     assert rel_err(single, outs[0]) < 1e-6
 
 
+@pytest.mark.parametrize('shape,dtype', [((6, 64, 9, 7), torch.bfloat16), ((3, 24, 5, 5), torch.bfloat16),
+                                         ((4, 40, 12, 12), torch.float32), ((32, 256, 14, 14), torch.bfloat16),
+                                         ((2, 8, 1, 1), torch.float32)])
+def test_batchnorm_unitwise_stats_kernel(ext, shape, dtype):
+    torch.manual_seed(0)
+    c = shape[1]
+    y = torch.randn(shape, device=DEV).to(dtype).contiguous(memory_format=torch.channels_last)
+    g = torch.randn(shape, device=DEV).to(dtype).contiguous(memory_format=torch.channels_last)
+    w = torch.rand(c, device=DEV) + 0.5
+    b = torch.randn(c, device=DEV)
+    prev = torch.randn(c, 2, 2, device=DEV)
+    ops.set_backend('torch')
+    ref = ops.batchnorm_unitwise_stats(y, g, w, b, out=prev.clone(), alpha=0.3, beta=0.7)
+    ops.set_backend('auto')
+    before = ext.launch_count()
+    got = ops.batchnorm_unitwise_stats(y, g, w, b, out=prev.clone(), alpha=0.3, beta=0.7)
+    assert ext.launch_count() == before + 2
+    assert rel_err(got, ref) < 2e-5
+    fresh = ops.batchnorm_unitwise_stats(y, g, w, b)
+    assert rel_err(fresh, (ref - 0.7 * prev) / 0.3) < 1e-4
+    assert torch.equal(fresh[:, 0, 1], fresh[:, 1, 0])
+
+
 def test_symmetric_segment_kernels_on_emulated_ranks(ext):
     """Pull-reduce, push-broadcast and decay kernels with three ranks emulated on one GPU."""
     from asdl_b200.parallel.symmetric import SymmetricArena
