@@ -1,0 +1,372 @@
+// Training-mode BatchNorm2d for NHWC (channels_last) bf16 activations with fp32 parameters and
+// statistics.  The activation tensor is treated as a row-major [rows = n*h*w, c] matrix; every
+// thread owns 8 consecutive channels (one 16-byte load) and walks down the rows, so all global
+// accesses are full 128-byte lines and each pass moves exactly the bytes it has to:
+//
+//   forward    bn_sums (read x)            -> per-split partial sums and sums of squares
+//              bn_fwd_finalize             -> mean, 1/std, running statistics, scale/shift
+//              bn_apply   (read x, write y)   y = x * scale + shift
+//   backward   bn_bwd_sums (read x, dy)    -> per-split partial sums of dy and dy * xhat
+//              bn_bwd_finalize             -> dweight, dbias and the three dx coefficients
+//              bn_dx      (read x, dy, write dx)
+//
+// Partial sums are combined in double precision by the finalize kernels (one thread per channel),
+// which keeps var = E[x^2] - E[x]^2 accurate.
+#include <cuda_bf16.h>
+
+#include "host_utils.h"
+
+namespace b200 {
+
+namespace {
+
+constexpr int GROUPS = 8;    // channel groups of 8 channels per CTA -> 64 channels
+constexpr int LANES = 32;    // row lanes per CTA
+constexpr int THREADS = GROUPS * LANES;
+constexpr int UNROLL = 4;    // independent 16-byte loads in flight per thread and tensor
+
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&out)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  return raw;
+}
+
+__device__ __forceinline__ uint4 ld_stream(const __nv_bfloat16* p) {
+  return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+// Combines the per-lane accumulators acc[2][8] of a CTA and writes one (first, second) pair per
+// channel to part[(split * channels + c) * 2].
+__device__ __forceinline__ void cta_reduce_store(float (&first)[8], float (&second)[8], float* part,
+                                                 int channels, int split) {
+  __shared__ float red[LANES][GROUPS * 16 + 1];
+  const int group = threadIdx.x % GROUPS;
+  const int lane = threadIdx.x / GROUPS;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    red[lane][(group * 8 + i) * 2] = first[i];
+    red[lane][(group * 8 + i) * 2 + 1] = second[i];
+  }
+  __syncthreads();
+  if (threadIdx.x < GROUPS * 16) {
+    float s = 0.f;
+#pragma unroll 8
+    for (int l = 0; l < LANES; ++l) s += red[l][threadIdx.x];
+    const int c = blockIdx.x * GROUPS * 8 + threadIdx.x / 2;
+    if (c < channels) part[(static_cast<size_t>(split) * channels + c) * 2 + (threadIdx.x & 1)] = s;
+  }
+}
+
+__global__ void __launch_bounds__(THREADS)
+bn_sums(const __nv_bfloat16* __restrict__ x, float* __restrict__ part, long long rows, int channels,
+        long long rows_per_split) {
+  const int group = threadIdx.x % GROUPS;
+  const int lane = threadIdx.x / GROUPS;
+  const int c0 = (blockIdx.x * GROUPS + group) * 8;
+  const long long r_begin = blockIdx.y * rows_per_split;
+  const long long r_end = min(rows, r_begin + rows_per_split);
+  float sum[8], sq[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sum[i] = sq[i] = 0.f;
+  if (c0 < channels) {
+    const __nv_bfloat16* base = x + c0;
+    long long r = r_begin + lane;
+    for (; r + (UNROLL - 1) * LANES < r_end; r += UNROLL * LANES) {
+      uint4 raw[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) raw[u] = ld_stream(base + (r + u * LANES) * channels);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        float v[8];
+        unpack8(raw[u], v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          sum[i] += v[i];
+          sq[i] = fmaf(v[i], v[i], sq[i]);
+        }
+      }
+    }
+    for (; r < r_end; r += LANES) {
+      float v[8];
+      unpack8(ld_stream(base + r * channels), v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        sum[i] += v[i];
+        sq[i] = fmaf(v[i], v[i], sq[i]);
+      }
+    }
+  }
+  cta_reduce_store(sum, sq, part, channels, blockIdx.y);
+}
+
+// coef layout (fp32, [5, c]): scale, shift (forward); k_dy, k_x, k_const (backward)
+__global__ void bn_fwd_finalize(const float* __restrict__ part, const float* __restrict__ weight,
+                                const float* __restrict__ bias, float* __restrict__ running_mean,
+                                float* __restrict__ running_var, float* __restrict__ mean_out,
+                                float* __restrict__ invstd_out, float* __restrict__ coef, int channels,
+                                int splits, long long rows, float momentum, float eps) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  double s = 0.0, q = 0.0;
+  for (int k = 0; k < splits; ++k) {
+    const float2 v = *reinterpret_cast<const float2*>(part + (static_cast<size_t>(k) * channels + c) * 2);
+    s += v.x;
+    q += v.y;
+  }
+  const double mean = s / static_cast<double>(rows);
+  double var = q / static_cast<double>(rows) - mean * mean;
+  var = var > 0.0 ? var : 0.0;
+  const float invstd = static_cast<float>(1.0 / sqrt(var + static_cast<double>(eps)));
+  mean_out[c] = static_cast<float>(mean);
+  invstd_out[c] = invstd;
+  const float scale = weight[c] * invstd;
+  coef[c] = scale;
+  coef[channels + c] = bias[c] - static_cast<float>(mean) * scale;
+  if (running_mean != nullptr) {
+    const double unbiased = rows > 1 ? var * static_cast<double>(rows) / static_cast<double>(rows - 1) : var;
+    running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * static_cast<float>(mean);
+    running_var[c] = (1.f - momentum) * running_var[c] + momentum * static_cast<float>(unbiased);
+  }
+}
+
+// out = in0 * ka[c] + in1 * kb[c] + kc[c]   (in1 / kb optional): the forward transform with
+// (x, -, scale, -, shift) and the input gradient with (dy, x, k_dy, k_x, k_const).
+template <bool TWO>
+__global__ void __launch_bounds__(256)
+bn_affine(const __nv_bfloat16* __restrict__ in0, const __nv_bfloat16* __restrict__ in1,
+          const float* __restrict__ ka, const float* __restrict__ kb, const float* __restrict__ kc,
+          __nv_bfloat16* __restrict__ out, long long vecs, int vec_per_row) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < vecs; i += stride) {
+    const int c0 = static_cast<int>(i % vec_per_row) * 8;
+    float a[8], v0[8], res[8];
+    unpack8(ld_stream(in0 + i * 8), v0);
+    const float4 a_lo = *reinterpret_cast<const float4*>(ka + c0), a_hi = *reinterpret_cast<const float4*>(ka + c0 + 4);
+    const float4 c_lo = *reinterpret_cast<const float4*>(kc + c0), c_hi = *reinterpret_cast<const float4*>(kc + c0 + 4);
+    a[0] = a_lo.x; a[1] = a_lo.y; a[2] = a_lo.z; a[3] = a_lo.w;
+    a[4] = a_hi.x; a[5] = a_hi.y; a[6] = a_hi.z; a[7] = a_hi.w;
+    res[0] = c_lo.x; res[1] = c_lo.y; res[2] = c_lo.z; res[3] = c_lo.w;
+    res[4] = c_hi.x; res[5] = c_hi.y; res[6] = c_hi.z; res[7] = c_hi.w;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) res[k] = fmaf(v0[k], a[k], res[k]);
+    if (TWO) {
+      float v1[8];
+      unpack8(ld_stream(in1 + i * 8), v1);
+      const float4 b_lo = *reinterpret_cast<const float4*>(kb + c0), b_hi = *reinterpret_cast<const float4*>(kb + c0 + 4);
+      const float b[8] = {b_lo.x, b_lo.y, b_lo.z, b_lo.w, b_hi.x, b_hi.y, b_hi.z, b_hi.w};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) res[k] = fmaf(v1[k], b[k], res[k]);
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) = pack8(res);
+  }
+}
+
+__global__ void __launch_bounds__(THREADS)
+bn_bwd_sums(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+            const float* __restrict__ mean, const float* __restrict__ invstd, float* __restrict__ part,
+            long long rows, int channels, long long rows_per_split) {
+  const int group = threadIdx.x % GROUPS;
+  const int lane = threadIdx.x / GROUPS;
+  const int c0 = (blockIdx.x * GROUPS + group) * 8;
+  const long long r_begin = blockIdx.y * rows_per_split;
+  const long long r_end = min(rows, r_begin + rows_per_split);
+  float s_dy[8], s_dyx[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s_dy[i] = s_dyx[i] = 0.f;
+  if (c0 < channels) {
+    float mu[8], is[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      mu[i] = mean[c0 + i];
+      is[i] = invstd[c0 + i];
+    }
+    const __nv_bfloat16* bx = x + c0;
+    const __nv_bfloat16* bg = dy + c0;
+    long long r = r_begin + lane;
+    for (; r + (UNROLL - 1) * LANES < r_end; r += UNROLL * LANES) {
+      uint4 rx[UNROLL], rg[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        rx[u] = ld_stream(bx + (r + u * LANES) * channels);
+        rg[u] = ld_stream(bg + (r + u * LANES) * channels);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        float xv[8], gv[8];
+        unpack8(rx[u], xv);
+        unpack8(rg[u], gv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          s_dy[i] += gv[i];
+          s_dyx[i] = fmaf((xv[i] - mu[i]) * is[i], gv[i], s_dyx[i]);
+        }
+      }
+    }
+    for (; r < r_end; r += LANES) {
+      float xv[8], gv[8];
+      unpack8(ld_stream(bx + r * channels), xv);
+      unpack8(ld_stream(bg + r * channels), gv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        s_dy[i] += gv[i];
+        s_dyx[i] = fmaf((xv[i] - mu[i]) * is[i], gv[i], s_dyx[i]);
+      }
+    }
+  }
+  cta_reduce_store(s_dy, s_dyx, part, channels, blockIdx.y);
+}
+
+// dx = w*invstd * (dy - mean(dy) - xhat * mean(dy*xhat))
+//    = dy * k_dy + x * k_x + k_const  with
+//   k_dy = w*invstd, k_x = -k_dy * invstd * m2, k_const = -k_dy * (m1 - mean * invstd * m2)
+__global__ void bn_bwd_finalize(const float* __restrict__ part, const float* __restrict__ weight,
+                                const float* __restrict__ mean, const float* __restrict__ invstd,
+                                float* __restrict__ dweight, float* __restrict__ dbias,
+                                float* __restrict__ coef, int channels, int splits, long long rows) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  double s1 = 0.0, s2 = 0.0;
+  for (int k = 0; k < splits; ++k) {
+    const float2 v = *reinterpret_cast<const float2*>(part + (static_cast<size_t>(k) * channels + c) * 2);
+    s1 += v.x;
+    s2 += v.y;
+  }
+  dbias[c] = static_cast<float>(s1);
+  dweight[c] = static_cast<float>(s2);
+  const double m1 = s1 / static_cast<double>(rows), m2 = s2 / static_cast<double>(rows);
+  const double k_dy = static_cast<double>(weight[c]) * invstd[c];
+  coef[2 * channels + c] = static_cast<float>(k_dy);
+  coef[3 * channels + c] = static_cast<float>(-k_dy * invstd[c] * m2);
+  coef[4 * channels + c] = static_cast<float>(-k_dy * (m1 - static_cast<double>(mean[c]) * invstd[c] * m2));
+}
+
+struct Shape {
+  long long rows;
+  int channels;
+  int chunks;
+  int splits;
+  long long rows_per_split;
+};
+
+Shape plan(const at::Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.scalar_type() == at::kBFloat16 &&
+                  x.is_contiguous(at::MemoryFormat::ChannelsLast),
+              "expected a 4-d channels_last bf16 CUDA tensor");
+  Shape s;
+  s.channels = static_cast<int>(x.size(1));
+  s.rows = x.size(0) * x.size(2) * x.size(3);
+  TORCH_CHECK(s.channels % 8 == 0 && s.rows > 0, "the channel count must be a multiple of 8");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "16-byte alignment required");
+  s.chunks = (s.channels + GROUPS * 8 - 1) / (GROUPS * 8);
+  long long want = (148 * 8 + s.chunks - 1) / s.chunks;                   // ~8 CTAs per SM in total
+  long long most = (s.rows + 2 * UNROLL * LANES - 1) / (2 * UNROLL * LANES);  // >= 2 unrolled trips each
+  long long splits = std::max<long long>(1, std::min(want, most));
+  s.rows_per_split = (s.rows + splits - 1) / splits;
+  s.splits = static_cast<int>((s.rows + s.rows_per_split - 1) / s.rows_per_split);
+  return s;
+}
+
+void check_vec(const at::Tensor& t, int c, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous() && t.numel() == c, name,
+              " must be a contiguous fp32 CUDA vector with one entry per channel");
+}
+
+int affine_grid(long long vecs) {
+  return static_cast<int>(std::min<long long>((vecs + 255) / 256, 148LL * 16));
+}
+
+}  // namespace
+
+// Returns (y, mean, invstd).  running_mean / running_var are updated in place when given.
+std::vector<at::Tensor> bn_forward_train(at::Tensor x, at::Tensor weight, at::Tensor bias,
+                                         c10::optional<at::Tensor> running_mean,
+                                         c10::optional<at::Tensor> running_var, double momentum, double eps) {
+  const Shape s = plan(x);
+  check_vec(weight, s.channels, "weight");
+  check_vec(bias, s.channels, "bias");
+  float *rm = nullptr, *rv = nullptr;
+  if (running_mean.has_value() && running_var.has_value()) {
+    check_vec(*running_mean, s.channels, "running_mean");
+    check_vec(*running_var, s.channels, "running_var");
+    rm = running_mean->data_ptr<float>();
+    rv = running_var->data_ptr<float>();
+  }
+  const int dev = x.get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  auto f32 = weight.options();
+  auto part = at::empty({s.splits, s.channels, 2}, f32);
+  auto mean = at::empty({s.channels}, f32), invstd = at::empty({s.channels}, f32);
+  auto coef = at::empty({2, s.channels}, f32);
+  auto y = at::empty_like(x);
+  const auto* xp = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
+  bn_sums<<<dim3(s.chunks, s.splits), THREADS, 0, stream>>>(xp, part.data_ptr<float>(), s.rows, s.channels,
+                                                            s.rows_per_split);
+  bn_fwd_finalize<<<(s.channels + 127) / 128, 128, 0, stream>>>(
+      part.data_ptr<float>(), weight.data_ptr<float>(), bias.data_ptr<float>(), rm, rv, mean.data_ptr<float>(),
+      invstd.data_ptr<float>(), coef.data_ptr<float>(), s.channels, s.splits, s.rows,
+      static_cast<float>(momentum), static_cast<float>(eps));
+  const long long vecs = s.rows * (s.channels / 8);
+  bn_affine<false><<<affine_grid(vecs), 256, 0, stream>>>(
+      xp, nullptr, coef.data_ptr<float>(), nullptr, coef.data_ptr<float>() + s.channels,
+      reinterpret_cast<__nv_bfloat16*>(y.data_ptr()), vecs, s.channels / 8);
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  count_launch();
+  count_launch();
+  return {y, mean, invstd};
+}
+
+// Returns (dx, dweight, dbias).
+std::vector<at::Tensor> bn_backward_train(at::Tensor x, at::Tensor dy, at::Tensor weight, at::Tensor mean,
+                                          at::Tensor invstd) {
+  const Shape s = plan(x);
+  TORCH_CHECK(dy.sizes() == x.sizes() && dy.scalar_type() == at::kBFloat16 && dy.is_cuda() &&
+                  dy.is_contiguous(at::MemoryFormat::ChannelsLast) &&
+                  (reinterpret_cast<uintptr_t>(dy.data_ptr()) & 15) == 0,
+              "dy must match x (channels_last bf16)");
+  check_vec(weight, s.channels, "weight");
+  check_vec(mean, s.channels, "mean");
+  check_vec(invstd, s.channels, "invstd");
+  const int dev = x.get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  auto f32 = weight.options();
+  auto part = at::empty({s.splits, s.channels, 2}, f32);
+  auto dweight = at::empty({s.channels}, f32), dbias = at::empty({s.channels}, f32);
+  auto coef = at::empty({5, s.channels}, f32);
+  auto dx = at::empty_like(x);
+  const auto* xp = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
+  const auto* gp = reinterpret_cast<const __nv_bfloat16*>(dy.data_ptr());
+  bn_bwd_sums<<<dim3(s.chunks, s.splits), THREADS, 0, stream>>>(
+      xp, gp, mean.data_ptr<float>(), invstd.data_ptr<float>(), part.data_ptr<float>(), s.rows, s.channels,
+      s.rows_per_split);
+  bn_bwd_finalize<<<(s.channels + 127) / 128, 128, 0, stream>>>(
+      part.data_ptr<float>(), weight.data_ptr<float>(), mean.data_ptr<float>(), invstd.data_ptr<float>(),
+      dweight.data_ptr<float>(), dbias.data_ptr<float>(), coef.data_ptr<float>(), s.channels, s.splits, s.rows);
+  const long long vecs = s.rows * (s.channels / 8);
+  float* k = coef.data_ptr<float>();
+  bn_affine<true><<<affine_grid(vecs), 256, 0, stream>>>(gp, xp, k + 2 * s.channels, k + 3 * s.channels,
+                                                         k + 4 * s.channels,
+                                                         reinterpret_cast<__nv_bfloat16*>(dx.data_ptr()), vecs,
+                                                         s.channels / 8);
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  count_launch();
+  count_launch();
+  return {dx, dweight, dbias};
+}
+
+}  // namespace b200

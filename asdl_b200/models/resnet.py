@@ -5,6 +5,8 @@ and the module runs in channels_last / bf16 autocast without layout changes betw
 import torch
 import torch.nn as nn
 
+from .layers import FusedBatchNorm2d
+
 __all__ = ['ResNet', 'Bottleneck', 'resnet50', 'resnet_tiny']
 
 
@@ -14,11 +16,11 @@ class Bottleneck(nn.Module):
     def __init__(self, inplanes, planes, stride=1, downsample=None):
         super().__init__()
         self.conv1 = nn.Conv2d(inplanes, planes, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(planes)
+        self.bn1 = FusedBatchNorm2d(planes)
         self.conv2 = nn.Conv2d(planes, planes, 3, stride=stride, padding=1, bias=False)
-        self.bn2 = nn.BatchNorm2d(planes)
+        self.bn2 = FusedBatchNorm2d(planes)
         self.conv3 = nn.Conv2d(planes, planes * self.expansion, 1, bias=False)
-        self.bn3 = nn.BatchNorm2d(planes * self.expansion)
+        self.bn3 = FusedBatchNorm2d(planes * self.expansion)
         self.relu = nn.ReLU(inplace=False)
         self.downsample = downsample
 
@@ -35,7 +37,7 @@ class ResNet(nn.Module):
         super().__init__()
         self.inplanes = width
         self.conv1 = nn.Conv2d(in_channels, width, 7, stride=2, padding=3, bias=False)
-        self.bn1 = nn.BatchNorm2d(width)
+        self.bn1 = FusedBatchNorm2d(width)
         self.relu = nn.ReLU(inplace=False)
         self.maxpool = nn.MaxPool2d(3, stride=2, padding=1)
         self.layer1 = self._make_layer(width, layers[0])
@@ -56,7 +58,7 @@ class ResNet(nn.Module):
         if stride != 1 or self.inplanes != planes * Bottleneck.expansion:
             downsample = nn.Sequential(
                 nn.Conv2d(self.inplanes, planes * Bottleneck.expansion, 1, stride=stride, bias=False),
-                nn.BatchNorm2d(planes * Bottleneck.expansion))
+                FusedBatchNorm2d(planes * Bottleneck.expansion))
         layers = [Bottleneck(self.inplanes, planes, stride, downsample)]
         self.inplanes = planes * Bottleneck.expansion
         layers += [Bottleneck(self.inplanes, planes) for _ in range(1, blocks)]

@@ -19,7 +19,7 @@ import torch
 
 from . import _build
 
-__all__ = ['gram', 'matmul_tn', 'kron_apply', 'spd_inverse', 'spd_inverse_grouped', 'unitwise_inverse', 'batchnorm_unitwise_stats', 'conv_patch_gram',
+__all__ = ['gram', 'matmul_tn', 'kron_apply', 'spd_inverse', 'spd_inverse_grouped', 'unitwise_inverse', 'batchnorm_unitwise_stats', 'batch_norm_train', 'conv_patch_gram',
            'set_backend', 'get_backend', 'set_precision', 'get_precision', 'extension',
            'cuda_kernels_enabled', 'check_status']
 
@@ -318,6 +318,43 @@ def batchnorm_unitwise_stats(y: torch.Tensor, g: torch.Tensor, weight: torch.Ten
     ww, wb, bb = gw.square().sum(dim=0), (gw * gb).sum(dim=0), gb.square().sum(dim=0)
     new = torch.stack([torch.stack([ww, wb], dim=1), torch.stack([wb, bb], dim=1)], dim=1)
     return out.mul_(beta).add_(new, alpha=alpha)
+
+
+class _BatchNormTrain(torch.autograd.Function):
+    """Training-mode batch normalisation on the library's NHWC bf16 kernels."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, running_mean, running_var, momentum, eps):
+        y, mean, invstd = extension().bn_forward_train(x, weight.detach(), bias.detach(), running_mean,
+                                                       running_var, float(momentum), float(eps))
+        ctx.save_for_backward(x, weight, mean, invstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, mean, invstd = ctx.saved_tensors
+        if not dy.is_contiguous(memory_format=torch.channels_last):
+            dy = dy.contiguous(memory_format=torch.channels_last)
+        dx, dweight, dbias = extension().bn_backward_train(x, dy, weight.detach(), mean, invstd)
+        return dx, dweight, dbias, None, None, None, None
+
+
+def batch_norm_train_supported(x: torch.Tensor, weight, bias) -> bool:
+    """True when :func:`batch_norm_train` runs on the library's kernels for this input."""
+    return (weight is not None and bias is not None and cuda_kernels_enabled(x) and x.ndim == 4
+            and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.numel() > 0
+            and weight.dtype == torch.float32 and bias.dtype == torch.float32
+            and x.is_contiguous(memory_format=torch.channels_last))
+
+
+def batch_norm_train(x, weight, bias, running_mean=None, running_var=None, momentum=0.1, eps=1e-5):
+    """Batch normalisation with batch statistics (and the running statistics updated in place),
+    differentiable.  CUDA, channels_last bf16 activations with fp32 parameters: three kernels
+    forward (sums, finalize, transform) and three backward, each pass reading / writing every
+    activation exactly once with 16-byte accesses; anything else: ``F.batch_norm``."""
+    if batch_norm_train_supported(x, weight, bias):
+        return _BatchNormTrain.apply(x, weight, bias, running_mean, running_var, momentum, eps)
+    return torch.nn.functional.batch_norm(x, running_mean, running_var, weight, bias, True, momentum, eps)
 
 
 def unitwise_inverse(blocks: torch.Tensor, damping: float = 0.0) -> torch.Tensor:

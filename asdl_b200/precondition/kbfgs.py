@@ -123,7 +123,7 @@ class KronBfgsGradientMaker(PreconditionedGradientMaker):
                     setattr(module, self.bfgs_attr, new)
                     bfgs = new
                 else:
-                    ema = config.ema_decay
+                    ema = config.ema_decay if 0 < config.ema_decay <= 1 else 1.0  # unset: keep the newest
                     bfgs.mul_(1 - ema)
                     bfgs += new.mul_(ema)  # in-place add keeps the stored inverses
                 A = bfgs.kron.A
@@ -197,7 +197,9 @@ def powell_lm_damping_(H: Tensor, s: Tensor, y: Tensor, mu1: float, mu2: float):
     Hy = torch.mv(H, y)
     ytHy = torch.dot(y, Hy)
     sty = torch.dot(s, y)
-    theta = torch.where(sty < mu1 * ytHy, (1 - mu1) * ytHy / (ytHy - sty), torch.ones_like(sty))
+    gap = ytHy - sty
+    theta = torch.where((sty < mu1 * ytHy) & (gap > 0), (1 - mu1) * ytHy / gap.clamp_min(1e-30),
+                        torch.ones_like(sty))
     s.mul_(theta).add_(Hy * (1 - theta))
     y.add_(s, alpha=mu2)
 
@@ -216,6 +218,10 @@ def bfgs_inv_update_(H: Tensor, s: Tensor, y: Tensor):
     Hy = torch.mv(H, y)
     ytHy = torch.dot(y, Hy)
     cross = torch.outer(Hy, s)
-    H.add_(torch.outer(s, s) * ((sty + ytHy) / sty ** 2))
-    H.sub_((cross + cross.T) / sty)
+    # a pair without usable curvature (s^T y not safely positive, e.g. a layer whose mean output
+    # gradient is removed by a following BatchNorm) leaves H as it is; decided on the device
+    ok = torch.isfinite(sty) & (sty > 1e-12 * (1 + s.norm() * y.norm()))
+    safe = torch.where(ok, sty, torch.ones_like(sty))
+    update = torch.outer(s, s) * ((safe + ytHy) / safe ** 2) - (cross + cross.T) / safe
+    H.add_(torch.where(ok & torch.isfinite(update).all(), update, torch.zeros_like(update)))
     return H

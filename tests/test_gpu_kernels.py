@@ -229,6 +229,36 @@ def test_batchnorm_unitwise_stats_kernel(ext, shape, dtype):
     assert torch.equal(fresh[:, 0, 1], fresh[:, 1, 0])
 
 
+@pytest.mark.parametrize('shape', [(8, 64, 14, 14), (4, 24, 7, 5), (32, 256, 28, 28), (2, 8, 1, 3), (3, 72, 33, 9)])
+def test_batch_norm_train_kernels(ext, shape):
+    """Forward (output, running statistics) and backward (input, weight, bias gradients) against
+    F.batch_norm evaluated in fp32 on the same bf16-rounded input."""
+    torch.manual_seed(0)
+    c = shape[1]
+    x = (torch.randn(shape, device=DEV) * 2 + 0.7).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    w = (torch.rand(c, device=DEV) + 0.5).requires_grad_(True)
+    b = torch.randn(c, device=DEV).requires_grad_(True)
+    dy = torch.randn(shape, device=DEV).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    rm, rv = torch.zeros(c, device=DEV), torch.ones(c, device=DEV)
+    xr = x.detach().float().requires_grad_(True)
+    wr, br = w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    rm_ref, rv_ref = rm.clone(), rv.clone()
+    y_ref = F.batch_norm(xr, rm_ref, rv_ref, wr, br, True, 0.1, 1e-5)
+    y_ref.backward(dy.float())
+    xk = x.detach().requires_grad_(True)
+    assert ops.batch_norm_train_supported(xk, w, b)
+    before = ext.launch_count()
+    y = ops.batch_norm_train(xk, w, b, rm, rv, 0.1, 1e-5)
+    y.backward(dy)
+    assert ext.launch_count() == before + 6
+    assert y.dtype == torch.bfloat16 and y.is_contiguous(memory_format=torch.channels_last)
+    assert rel_err(y, y_ref) < 4e-3                      # bf16 rounding of the output
+    assert rel_err(rm, rm_ref) < 1e-5 and rel_err(rv, rv_ref) < 1e-5
+    assert rel_err(w.grad, wr.grad) < 1e-4 and rel_err(b.grad, br.grad) < 1e-4
+    assert rel_err(xk.grad, xr.grad) < 6e-3
+    ops.check_status()
+
+
 def test_symmetric_segment_kernels_on_emulated_ranks(ext):
     """Pull-reduce, push-broadcast and decay kernels with three ranks emulated on one GPU."""
     from asdl_b200.parallel.symmetric import SymmetricArena
