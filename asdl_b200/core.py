@@ -216,8 +216,8 @@ def module_wise_assignments(model, *assign_rules, ignore_modules=None, map_rule=
             hit = next((k for k in name_keys if k in name), None)
             if hit is not None:
                 values = keyed[hit]
-            elif type(module) in keyed:
-                values = keyed[type(module)]
+            elif any(cls in keyed for cls in type(module).__mro__):  # nearest base class wins
+                values = keyed[next(cls for cls in type(module).__mro__ if cls in keyed)]
             elif default_values:
                 values = list(default_values)
             else:
