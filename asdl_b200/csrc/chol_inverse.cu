@@ -1,6 +1,6 @@
 // Grouped fp32 inverse of damped symmetric positive-definite matrices:
 //     out_m = (A_m + damping_m * I)^-1        for m = 0 .. count-1, sizes n_m arbitrary
-// by blocked Cholesky (A = L L^T), blocked triangular inversion (X = L^-1) and X^T X.
+// by blocked Cholesky (A = L L^T), blocked right-looking triangular inversion (X = L^-1) and X^T X.
 // All matrices of a call advance through the same sequence of launches ("grouped"): the launch
 // for block column k covers every matrix that still has such a column, so a ResNet-50's ~100
 // factors of sizes 64..4608 cost O(n_max/64) launches, not O(sum n_m/64).
@@ -116,21 +116,28 @@ __global__ void __launch_bounds__(256) chol_diag_kernel(const CholMat* mats, int
     if (tid > j && tid < CB) S[tid][j] /= S[j][j];
     __syncthreads();
     // trailing update of the lower triangle: rows i > j, columns j < c <= i
-    for (int e = tid; e < CB * CB; e += 256) {
-      const int i = e >> 6, c = e & 63;
-      if (i > j && c > j && c <= i) S[i][c] -= S[i][j] * S[c][j];
+    const int m = CB - 1 - j;
+    for (int e = tid; e < m * m; e += 256) {
+      const int i = j + 1 + e / m, c = j + 1 + e % m;
+      if (c <= i) S[i][c] -= S[i][j] * S[c][j];
     }
     __syncthreads();
   }
-  // T = S^-1 (lower triangular), one column per thread
-  if (tid < CB) {
-    const int c = tid;
-    for (int i = 0; i < c; ++i) T[i][c] = 0.f;
-    T[c][c] = 1.f / S[c][c];
-    for (int i = c + 1; i < CB; ++i) {
+  // T = S^-1 (lower triangular): column c is a forward substitution; four neighbouring lanes of
+  // a warp share one column and split the inner product
+  {
+    const int c = tid >> 2, q = tid & 3;
+    for (int i = q; i < c; i += 4) T[i][c] = 0.f;
+    if (q == 0) T[c][c] = 1.f / S[c][c];
+    __syncwarp();
+    for (int i = 1; i < CB; ++i) {  // uniform trip count: every lane of the warp takes part in the shuffles
       float s = 0.f;
-      for (int j = c; j < i; ++j) s = fmaf(S[i][j], T[j][c], s);
-      T[i][c] = -s / S[i][i];
+      if (i > c)
+        for (int j = c + q; j < i; j += 4) s = fmaf(S[i][j], T[j][c], s);
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      if (q == 0 && i > c) T[i][c] = -s / S[i][i];
+      __syncwarp();
     }
   }
   __syncthreads();
@@ -200,40 +207,60 @@ __global__ void __launch_bounds__(256) chol_trailing_kernel(const CholMat* mats,
     }
 }
 
-// ---- phase 2: X = L^-1, block anti-diagonal d:  X_ik = -inv(L_ii) * sum_{j=k}^{i-1} L_ij X_jk ---
-__global__ void __launch_bounds__(256) trtri_level_kernel(const CholMat* mats, int d) {
+// ---- phase 2: X = L^-1, right-looking over block rows -------------------------------------------
+// For j = 0 .. nb-1:   finalize  X_jk = -inv(L_jj) * S_jk            for k < j
+//                      update    S_ik (+)= L_ij * X_jk               for i > j, k <= j
+// where S_ik = sum_{m=k}^{j} L_im X_mk is accumulated in the storage of X_ik.  Every step exposes
+// (nb-j-1)(j+1) independent tile products, so the critical path is 2 nb short kernels instead of
+// the nb^2/2 dependent tile products of a sweep by anti-diagonals.
+__global__ void __launch_bounds__(256) trtri_finalize_row_kernel(const CholMat* mats, int j) {
   const CholMat M = mats[blockIdx.y];
-  const int k = blockIdx.x, i = k + d;
+  const int k = blockIdx.x;
+  if (j >= M.nb || k >= j) return;
+  __shared__ float As[CB][CB + 1];
+  __shared__ float Bs[CB][CB + 1];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const float* D = M.D + static_cast<size_t>(j) * CB * CB;
+  for (int e = tid; e < CB * CB; e += 256) As[e & 63][e >> 6] = D[e];  // As[kk][row] = T_j[row][kk]
+  load_tile(Bs, M.X, M.n, M.n, j * CB, k * CB, true, tid);             // Bs[kk][col] = S_jk[kk][col]
+  __syncthreads();
+  Acc acc;
+  acc_zero(acc);
+  tile_fma(acc, As, Bs, tx, ty);
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int gr = j * CB + ty + 16 * u, gc = k * CB + tx + 16 * v;
+      if (gr < M.n && gc < M.n) M.X[static_cast<size_t>(gr) * M.n + gc] = -acc.v[u][v];
+    }
+}
+
+__global__ void __launch_bounds__(256) trtri_update_kernel(const CholMat* mats, int j) {
+  const CholMat M = mats[blockIdx.y];
+  const int below = M.nb - j - 1;
+  if (below <= 0) return;
+  const int i = j + 1 + blockIdx.x / (j + 1), k = blockIdx.x % (j + 1);
   if (i >= M.nb) return;
   __shared__ float As[CB][CB + 1];
   __shared__ float Bs[CB][CB + 1];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  load_tile(As, M.L, M.n, M.n, i * CB, j * CB, false, tid);  // As[kk][row] = L_ij[row][kk]
+  load_tile(Bs, M.X, M.n, M.n, j * CB, k * CB, true, tid);   // Bs[kk][col] = X_jk[kk][col]
+  __syncthreads();
   Acc acc;
   acc_zero(acc);
-  for (int j = k; j < i; ++j) {
-    load_tile(As, M.L, M.n, M.n, i * CB, j * CB, false, tid);  // As[kk][row] = L_ij[row][kk]
-    load_tile(Bs, M.X, M.n, M.n, j * CB, k * CB, true, tid);   // Bs[kk][col] = X_jk[kk][col]
-    __syncthreads();
-    tile_fma(acc, As, Bs, tx, ty);
-    __syncthreads();
-  }
-  // second product: X_ik = -T_i * acc, with acc staged through shared memory as the B operand
-  const float* D = M.D + static_cast<size_t>(i) * CB * CB;
-  for (int e = tid; e < CB * CB; e += 256) As[e & 63][e >> 6] = D[e];  // As[kk][row] = T[row][kk]
-#pragma unroll
-  for (int u = 0; u < 4; ++u)
-#pragma unroll
-    for (int v = 0; v < 4; ++v) Bs[ty + 16 * u][tx + 16 * v] = acc.v[u][v];  // Bs[kk][col]
-  __syncthreads();
-  Acc out;
-  acc_zero(out);
-  tile_fma(out, As, Bs, tx, ty);
+  tile_fma(acc, As, Bs, tx, ty);
+  const bool first = (k == j);  // the first contribution to S_ik overwrites whatever the buffer held
 #pragma unroll
   for (int u = 0; u < 4; ++u)
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
       const int gr = i * CB + ty + 16 * u, gc = k * CB + tx + 16 * v;
-      if (gr < M.n && gc < M.n) M.X[static_cast<size_t>(gr) * M.n + gc] = -out.v[u][v];
+      if (gr < M.n && gc < M.n) {
+        float* dst = M.X + static_cast<size_t>(gr) * M.n + gc;
+        *dst = first ? acc.v[u][v] : *dst + acc.v[u][v];
+      }
     }
 }
 
@@ -367,11 +394,18 @@ void chol_inverse(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs, at
       count_launch(2);
     }
   }
-  for (int d = 1; d < nb_max; ++d) {
-    const int na = active(d);
-    if (na == 0) break;
-    trtri_level_kernel<<<dim3(host[0].nb - d, na), 256, 0, stream>>>(dm, d);
-    count_launch();
+  for (int j = 0; j < nb_max; ++j) {
+    const int na = active(j);  // matrices that have a block row j
+    if (j > 0) {
+      trtri_finalize_row_kernel<<<dim3(j, na), 256, 0, stream>>>(dm, j);
+      count_launch();
+    }
+    const int below = host[0].nb - j - 1;
+    const int nb1 = active(j + 1);
+    if (below > 0 && nb1 > 0) {
+      trtri_update_kernel<<<dim3(below * (j + 1), nb1), 256, 0, stream>>>(dm, j);
+      count_launch();
+    }
   }
   lauum_kernel<<<dim3(host[0].nb * (host[0].nb + 1) / 2, count), 256, 0, stream>>>(dm);
   count_launch();

@@ -27,7 +27,8 @@ from torch.linalg import solve_triangular
 
 from .prec_grad_maker import PreconditionedGradientMaker, PreconditioningConfig
 
-__all__ = ['PsgdGradientMaker', 'KronPsgdGradientMaker', 'update_precond_kron', 'precond_grad_kron']
+__all__ = ['PsgdGradientMaker', 'KronPsgdGradientMaker', 'update_precond_kron', 'precond_grad_kron',
+           'update_precond_splu', 'precond_grad_splu']
 
 _TINY = 1.2e-38
 
@@ -383,3 +384,116 @@ def update_precond_kron(Ql, Qr, dX, dG, step=0.01, _tiny=_TINY):
 def precond_grad_kron(Ql, Qr, Grad):
     """``Ql^T Ql . Grad . Qr^T Qr`` for any combination of factor formats."""
     return _factor(Qr).gram_apply_right(_factor(Ql).gram_apply_left(Grad))
+
+
+# ----------------------------------------------------------------------------------------------
+# sparse-LU preconditioner  P = Q^T Q,  Q = L U  with "arrow" factors
+#     L = [[L1, 0], [L2, diag(l3)]]   (L1: r x r lower triangular)
+#     U = [[U1, U2], [0, diag(u3)]]   (U1: r x r upper triangular)
+# stored as L12 = [L1; L2] (n x r), l3 ((n-r) x 1), U12 = [U1, U2] (r x n), u3 ((n-r) x 1).
+# Parity: asdl/precondition/psgd.py:498-629 (a format no gradient maker uses; kept as functions).
+# ----------------------------------------------------------------------------------------------
+class _ArrowLU:
+    """Products and solves with the arrow factors on (head, tail) = (first r, remaining) parts."""
+
+    def __init__(self, L12, l3, U12, u3):
+        r = U12.shape[0]
+        self.r = r
+        self.L1, self.L2, self.l3 = L12[:r], L12[r:], l3.reshape(-1)
+        self.U1, self.U2, self.u3 = U12[:, :r], U12[:, r:], u3.reshape(-1)
+
+    def split(self, v):
+        return v[:self.r], v[self.r:]
+
+    def U(self, h, t):
+        return self.U1 @ h + self.U2 @ t, self.u3 * t
+
+    def L(self, h, t):
+        return self.L1 @ h, self.L2 @ h + self.l3 * t
+
+    def Lt(self, h, t):
+        return self.L1.T @ h + self.L2.T @ t, self.l3 * t
+
+    def Ut(self, h, t):
+        return self.U1.T @ h, self.U2.T @ h + self.u3 * t
+
+    @staticmethod
+    def _tri(mat, rhs, upper, transpose=False):
+        a = mat.T if transpose else mat
+        return torch.linalg.solve_triangular(a, rhs.unsqueeze(1), upper=(upper != transpose)).squeeze(1)
+
+    def Ut_solve(self, h, t):      # U^-T
+        x = self._tri(self.U1, h, upper=True, transpose=True)
+        return x, (t - self.U2.T @ x) / self.u3
+
+    def Lt_solve(self, h, t):      # L^-T
+        y = t / self.l3
+        return self._tri(self.L1, h - self.L2.T @ y, upper=False, transpose=True), y
+
+    def L_solve(self, h, t):       # L^-1
+        x = self._tri(self.L1, h, upper=False)
+        return x, (t - self.L2 @ x) / self.l3
+
+    def U_solve(self, h, t):       # U^-1
+        y = t / self.u3
+        return self._tri(self.U1, h - self.U2 @ y, upper=True), y
+
+
+def _flatten_list(tensors):
+    return torch.cat([t.reshape(-1) for t in tensors])
+
+
+@torch.no_grad()
+def update_precond_splu(L12, l3, U12, u3, dxs, dgs, step=0.01, _tiny=_TINY):
+    """One fitting step of the sparse-LU preconditioner from a parameter perturbation ``dxs`` and
+    the resulting gradient perturbation ``dgs`` (lists of tensors).  Returns the new
+    ``(L12, l3, U12, u3)``; the inputs are rescaled in place so that L and U keep a similar range."""
+    rho = torch.sqrt(torch.maximum(torch.diagonal(L12).max(), l3.max())
+                     / torch.maximum(torch.diagonal(U12).max(), u3.max()))
+    L12 /= rho
+    l3 /= rho
+    U12 *= rho
+    u3 *= rho
+    f = _ArrowLU(L12, l3, U12, u3)
+    dx_h, dx_t = f.split(_flatten_list(dxs))
+    dg_h, dg_t = f.split(_flatten_list(dgs))
+    qg_h, qg_t = f.L(*f.U(dg_h, dg_t))                      # Q dg
+    iq_h, iq_t = f.Lt_solve(*f.Ut_solve(dx_h, dx_t))        # Q^-T dx
+    pg_h, pg_t = f.Ut(*f.Lt(qg_h, qg_t))                    # P dg
+    ip_h, ip_t = f.U_solve(*f.L_solve(iq_h, iq_t))          # P^-1 dx
+
+    def normalised(step_, *grads):
+        return step_ / (torch.stack([g.abs().max() for g in grads]).max() + _tiny)
+
+    # L <- L - mu * [[tril(g1), 0], [g2, diag(g3)]] L
+    g1 = torch.tril(torch.outer(qg_h, qg_h) - torch.outer(iq_h, iq_h))
+    g2 = torch.outer(qg_t, qg_h) - torch.outer(iq_t, iq_h)
+    g3 = qg_t * qg_t - iq_t * iq_t
+    mu = normalised(step, g1, g2, g3)
+    new_L1 = f.L1 - mu * (g1 @ f.L1)
+    new_L2 = f.L2 - mu * (g2 @ f.L1) - mu * g3.unsqueeze(1) * f.L2
+    new_l3 = f.l3 - mu * g3 * f.l3
+    # U <- U - mu * U [[triu(h1), h2], [0, diag(h3)]]
+    h1 = torch.triu(torch.outer(pg_h, dg_h) - torch.outer(dx_h, ip_h))
+    h2 = torch.outer(pg_h, dg_t) - torch.outer(dx_h, ip_t)
+    h3 = pg_t * dg_t - dx_t * ip_t
+    mu = normalised(step, h1, h2, h3)
+    new_U1 = f.U1 - mu * (f.U1 @ h1)
+    new_U2 = f.U2 - mu * (f.U1 @ h2) - mu * h3.unsqueeze(0) * f.U2
+    new_u3 = f.u3 - mu * h3 * f.u3
+    return (torch.cat([new_L1, new_L2], dim=0), new_l3.reshape(-1, 1),
+            torch.cat([new_U1, new_U2], dim=1), new_u3.reshape(-1, 1))
+
+
+@torch.no_grad()
+def precond_grad_splu(L12, l3, U12, u3, grads):
+    """``P g`` with the sparse-LU preconditioner for a list of gradient tensors; returns a list of
+    tensors with the shapes of ``grads``."""
+    f = _ArrowLU(L12, l3, U12, u3)
+    h, t = f.split(_flatten_list(grads))
+    out = torch.cat(f.Ut(*f.Lt(*f.L(*f.U(h, t)))))
+    result, offset = [], 0
+    for g in grads:
+        result.append(out[offset:offset + g.numel()].view_as(g))
+        offset += g.numel()
+    return result

@@ -45,12 +45,17 @@ class ShampooGradientMaker(PreconditionedGradientMaker):
             switches from summed to moving-average statistics).
         block_size: largest factor size; larger modes are split into blocks (``-1``: no blocks).
         sync_group: process group for data-parallel runs.
+        grouped: on CUDA, process all blocks of all 2-D parameters with grouped kernel launches
+            (statistics, and the application of the roots) instead of a few launches per block.
     """
 
     def __init__(self, model: torch.nn.Module, config: PreconditioningConfig,
-                 block_size: int = _invalid, sync_group: dist.ProcessGroup = None):
+                 block_size: int = _invalid, sync_group: dist.ProcessGroup = None, grouped: bool = True):
         super().__init__(model, config)
         self.sync_group = sync_group
+        self.grouped = grouped
+        self._group = None
+        self._group_members = set()
         self.block_size = block_size
         if dist.is_available() and dist.is_initialized():
             self.world_rank = dist.get_rank(sync_group)
@@ -83,8 +88,24 @@ class ShampooGradientMaker(PreconditionedGradientMaker):
         if self.world_size > 1:
             with nvtx_range('reduce_scatter_grads'):
                 self.reduce_scatter_grads()
+        group = self._ensure_group()
+        if group is not None:
+            group.update_statistics()
         for preconditioner in self.preconditioners:
-            preconditioner.update_statistics()
+            if id(preconditioner) not in self._group_members:
+                preconditioner.update_statistics()
+
+    def _ensure_group(self):
+        if self._group is None and self.grouped and self.preconditioners:
+            first = self.preconditioners[0].param
+            if first.is_cuda and ops.get_backend() != 'torch':
+                members = [prec for prec in self.preconditioners if _MatrixBlockGroup.supports(prec)]
+                if members:
+                    self._group = _MatrixBlockGroup(members, self.config.ema_decay)
+                    self._group_members = {id(prec) for prec in members}
+            if self._group is None:
+                self.grouped = False
+        return self._group
 
     def update_preconditioner(self):
         """Inverse roots of every owned factor, batched by factor size."""
@@ -99,12 +120,19 @@ class ShampooGradientMaker(PreconditionedGradientMaker):
             roots = inverse_pth_root_batched(stack, exponent, ridge_epsilon=self.config.damping)
             for (prec, i), root in zip(members, roots):
                 prec.preconditioners[i] = root
+        if self._group is not None:
+            self._group.refresh_roots()
 
     def precondition(self):
         if self.world_size > 1 and not self._grads_synced:
             self.reduce_scatter_grads()
+        group = self._ensure_group()
+        if group is not None:
+            group.precondition(restage=not group._staged)
+            group._staged = False
         for preconditioner in self.preconditioners:
-            preconditioner.precondition()
+            if id(preconditioner) not in self._group_members:
+                preconditioner.precondition()
         if self.world_size > 1:
             with nvtx_range('all_gather_grads'):
                 self.all_gather_grads()
@@ -178,7 +206,134 @@ class ShampooGradientMaker(PreconditionedGradientMaker):
                 for kind, target in (('stat', prec.statistics), ('root', prec.preconditioners)):
                     key = f'param{idx}.{kind}{i}'
                     if key in tensors:
-                        target[i] = tensors[key].to(prec.param.device)
+                        value = tensors[key].to(prec.param.device)
+                        if target[i].shape == value.shape and target[i].dtype == value.dtype:
+                            target[i].copy_(value)  # in place: grouped launches hold these addresses
+                        else:
+                            target[i] = value
+        if self._group is not None:
+            self._group.refresh_roots()
+
+
+class _MatrixBlockGroup:
+    """All blocks of all owned 2-D parameters, processed with grouped launches on CUDA: one staging
+    kernel splits every gradient block into bf16 hi/lo pairs, one grouped tcgen05 launch updates
+    every statistic (L += G G^T and R += G^T G, the moving average folded into the epilogue), and
+    two grouped launches apply the cached bf16 images of the roots (L^{-1/p} G, then times
+    R^{-1/p}).  Per step that is a handful of launches instead of several per block."""
+
+    def __init__(self, precs: List['Preconditioner'], ema):
+        ext = ops.extension()
+        self.ext = ext
+        self.precs = precs
+        dev = precs[0].param.device
+        self.device = dev
+        self.params = [prec.param for prec in precs]
+        self.regions = [torch.zeros(p.shape, device=dev, dtype=torch.float32) for p in self.params]
+        alpha, beta = (1.0, 1.0) if ema == _invalid else (float(ema), 1.0 - float(ema))
+        self.blocks = []   # (prec index, block index, row slice, col slice)
+        self.stat_plan, self.plan1, self.plan2 = ext.gemm_plan_new(), ext.gemm_plan_new(), ext.gemm_plan_new()
+        self.keep = []
+        bf16 = dict(device=dev, dtype=torch.bfloat16)
+        self.root_rows = []     # cast table rows of the roots: filled by refresh_roots
+        self.root_slots = []    # (prec, statistic index, hi, lo)
+        for pi, prec in enumerate(precs):
+            ncols = prec.param.shape[1]
+            for j, (rs, cs) in enumerate(prec._partitioner.block_slices()):
+                m, n = rs.stop - rs.start, cs.stop - cs.start
+                ld_n, ld_m = (max(n, 8) + 7) // 8 * 8, (max(m, 8) + 7) // 8 * 8
+                g_hi, g_lo = torch.zeros(m, ld_n, **bf16), torch.zeros(m, ld_n, **bf16)
+                t_hi, t_lo = torch.zeros(m, ld_n, **bf16), torch.zeros(m, ld_n, **bf16)
+                l_hi, l_lo = torch.zeros(m, ld_m, **bf16), torch.zeros(m, ld_m, **bf16)
+                r_hi, r_lo = torch.zeros(n, ld_n, **bf16), torch.zeros(n, ld_n, **bf16)
+                self.keep.append((g_hi, g_lo, t_hi, t_lo, l_hi, l_lo, r_hi, r_lo))
+                self.blocks.append((pi, j, rs, cs, g_hi, g_lo, m, n, ld_n))
+                self.root_slots += [(prec, 2 * j, l_hi, l_lo, m, ld_m), (prec, 2 * j + 1, r_hi, r_lo, n, ld_n)]
+                gh, gl = g_hi[:, :n], g_lo[:, :n]
+                stat_l, stat_r = prec.statistics[2 * j], prec.statistics[2 * j + 1]
+                # L (+)= G G^T: G as [M = m, K = n] K-major on both sides; R (+)= G^T G: G as [K = m, M = n]
+                ext.gemm_plan_add(self.stat_plan, [gh, gh, gl], [gh, gl, gh], True, True, stat_l, alpha, beta,
+                                  True, None, None, 0, 0, False, [], 1)
+                ext.gemm_plan_add(self.stat_plan, [gh, gh, gl], [gh, gl, gh], False, False, stat_r, alpha, beta,
+                                  True, None, None, 0, 0, False, [], 1)
+                lh, ll, rh, rl = l_hi[:, :m], l_lo[:, :m], r_hi[:, :n], r_lo[:, :n]
+                th, tl = t_hi[:, :n], t_lo[:, :n]
+                ext.gemm_plan_add(self.plan1, [lh, lh, ll], [gh, gl, gh], False, False, None, 1.0, 0.0, False,
+                                  t_hi, t_lo, 0, 0, False, [], 1)
+                dst = self.regions[pi].data_ptr() + 4 * (rs.start * ncols + cs.start)
+                ext.gemm_plan_add(self.plan2, [th, th, tl], [rh, rl, rh], True, False, None, 1.0, 0.0, False,
+                                  None, None, dst, ncols, False, [], 1)
+        for plan in (self.stat_plan, self.plan1, self.plan2):
+            ext.gemm_plan_finalize(plan)
+        self._grad_ptrs = None
+        self._grad_table = None
+        self._statistics_ids = None
+
+    @staticmethod
+    def supports(prec: 'Preconditioner') -> bool:
+        p = prec.param
+        if not (p.is_cuda and p.ndim == 2 and p.dtype == torch.float32
+                and tuple(prec._transformed_shape) == tuple(p.shape) and prec.exponent == 4):
+            return False
+        ncols = p.shape[1]
+        return all((rs.start * ncols + cs.start) % 4 == 0 for rs, cs in prec._partitioner.block_slices()) \
+            and ncols % 4 == 0
+
+    def _stage_grads(self):
+        grads = [p.grad for p in self.params]
+        for g in grads:
+            if g is None or not g.is_contiguous() or g.dtype != torch.float32:
+                raise RuntimeError('grouped Shampoo needs contiguous fp32 gradients')
+        ptrs = tuple(g.data_ptr() for g in grads)
+        if ptrs != self._grad_ptrs:  # autograd allocated new gradient tensors: re-point the staging table
+            rows = []
+            for pi, j, rs, cs, g_hi, g_lo, m, n, ld_n in self.blocks:
+                ncols = self.params[pi].shape[1]
+                src = ptrs[pi] + 4 * (rs.start * ncols + cs.start)
+                rows.append([src, g_hi.data_ptr(), g_lo.data_ptr(), m, n, ncols, ld_n])
+            self._grad_table = torch.tensor(rows, dtype=torch.int64, device=self.device)
+            self._grad_ptrs = ptrs
+        self.ext.cast_pad_bf16_grouped(self._grad_table, len(self.blocks))
+
+    def update_statistics(self):
+        ids = tuple(id(t) for prec in self.precs for t in prec.statistics)
+        if self._statistics_ids is None:
+            self._statistics_ids = ids
+        elif ids != self._statistics_ids:
+            raise RuntimeError('the statistics tensors were replaced; load state into them in place')
+        self._stage_grads()
+        self.ext.gemm_plan_run(self.stat_plan)
+        self._staged = True
+
+    def refresh_roots(self):
+        for prec, i, *_ in self.root_slots:
+            root = prec.preconditioners[i]
+            if not (root.is_contiguous() and root.dtype == torch.float32):
+                prec.preconditioners[i] = root.contiguous().float()
+        rows = [[prec.preconditioners[i].data_ptr(), hi.data_ptr(), lo.data_ptr(), n, n, n, ld]
+                for prec, i, hi, lo, n, ld in self.root_slots]
+        table = torch.tensor(rows, dtype=torch.int64, device=self.device)
+        self.ext.cast_pad_bf16_grouped(table, len(rows))
+        self._roots_ready = True
+
+    _roots_ready = False
+    _staged = False
+
+    def precondition(self, restage: bool):
+        if not self._roots_ready:
+            self.refresh_roots()
+        if restage:
+            self._stage_grads()
+        self.ext.gemm_plan_run(self.plan1)
+        self.ext.gemm_plan_run(self.plan2)
+        torch._foreach_copy_([p.grad for p in self.params], self.regions)
+
+    def __del__(self):
+        try:
+            for plan in (self.stat_plan, self.plan1, self.plan2):
+                self.ext.gemm_plan_free(plan)
+        except Exception:
+            pass
 
 
 class BlockPartitioner:

@@ -259,6 +259,39 @@ def test_batch_norm_train_kernels(ext, shape):
     ops.check_status()
 
 
+def test_shampoo_grouped_launches_match_per_block_path():
+    """Grouped statistics / root application on CUDA against the per-block PyTorch path on CPU."""
+    torch.manual_seed(0)
+    base = nn.Sequential(nn.Linear(40, 96), nn.Tanh(), nn.Linear(96, 72, bias=False), nn.Tanh(), nn.Linear(72, 8))
+    x, t = torch.randn(16, 40), torch.randint(0, 8, (16,))
+
+    def run(model, x, t, **kw):
+        cfg = asdl.PreconditioningConfig(damping=1e-4, preconditioner_upd_interval=2)
+        gm = asdl.ShampooGradientMaker(model, cfg, block_size=32, **kw)
+        opt = torch.optim.SGD(model.parameters(), lr=1e-3)
+        out = []
+        for _ in range(5):
+            opt.zero_grad(set_to_none=False)
+            d = gm.setup_model_call(model, x)
+            gm.setup_loss_call(F.cross_entropy, d, t)
+            gm.forward_and_backward()
+            out.append([p.grad.detach().cpu().clone() for p in model.parameters()])
+            opt.step()
+        return gm, out
+
+    _, ref = run(copy.deepcopy(base), x, t)
+    ext = ops.extension()
+    before = ext.launch_count()
+    gm, got = run(copy.deepcopy(base).to(DEV), x.to(DEV), t.to(DEV))
+    assert gm._group is not None and len(gm._group.blocks) == 2 * 3 + 3 * 3 + 3
+    # per step: 1 staging + 1 statistics + 2 application launches (+ root staging every 2nd step)
+    assert ext.launch_count() - before <= 5 * 4 + 3 + 2
+    for step, (g_ref, g_got) in enumerate(zip(ref, got)):
+        for a, b in zip(g_ref, g_got):
+            assert rel_err(b, a) < 5e-3, (step, rel_err(b, a), a.shape)
+    ops.check_status()
+
+
 def test_symmetric_segment_kernels_on_emulated_ranks(ext):
     """Pull-reduce, push-broadcast and decay kernels with three ranks emulated on one GPU."""
     from asdl_b200.parallel.symmetric import SymmetricArena

@@ -311,3 +311,43 @@ def test_hessian_shapes_and_tools():
     eig, _ = hm.hessian_eig(top_n=1, max_iters=300, tol=1e-9)
     top = torch.linalg.eigvalsh(H).abs().max().item()
     assert abs(abs(eig[0]) - top) / top < 1e-2
+
+
+def test_psgd_sparse_lu_fits_a_quadratic():
+    """P = Q^T Q with arrow-shaped LU factors: P g equals the dense product, and fitting on
+    (dx, H dx) pairs of a fixed SPD Hessian drives P H towards the identity on the criterion
+    E[dg^T P dg + dx^T P^-1 dx]."""
+    from asdl_b200.precondition.psgd import update_precond_splu, precond_grad_splu
+    torch.manual_seed(0)
+    n, r = 12, 4
+    L12 = torch.cat([torch.eye(r), torch.zeros(n - r, r)]).double()
+    U12 = torch.cat([torch.eye(r), torch.zeros(r, n - r)], dim=1).double()
+    l3, u3 = torch.ones(n - r, 1).double(), torch.ones(n - r, 1).double()
+    a = torch.randn(n, n).double()
+    H = a @ a.T / n + 0.5 * torch.eye(n).double()
+
+    def dense_P(L12, l3, U12, u3):
+        L = torch.zeros(n, n).double()
+        L[:, :r] = L12
+        L[r:, r:] = torch.diag(l3.reshape(-1))
+        U = torch.zeros(n, n).double()
+        U[:r] = U12
+        U[r:, r:] = torch.diag(u3.reshape(-1))
+        Q = L @ U
+        return Q.T @ Q
+
+    def criterion(P):
+        return (torch.trace(P @ H @ H) + torch.trace(torch.linalg.inv(P))).item()
+
+    start = criterion(dense_P(L12, l3, U12, u3))
+    for _ in range(400):
+        dx = torch.randn(n).double()
+        L12, l3, U12, u3 = update_precond_splu(L12, l3, U12, u3, [dx[:5].reshape(5, 1), dx[5:]],
+                                               [(H @ dx)[:5].reshape(5, 1), (H @ dx)[5:]], step=0.05)
+    P = dense_P(L12, l3, U12, u3)
+    assert criterion(P) < 0.8 * start
+    g = [torch.randn(3, 2).double(), torch.randn(6).double()]
+    out = precond_grad_splu(L12, l3, U12, u3, g)
+    flat = P @ torch.cat([t.reshape(-1) for t in g])
+    torch.testing.assert_close(torch.cat([t.reshape(-1) for t in out]), flat)
+    assert out[0].shape == (3, 2) and out[1].shape == (6,)
