@@ -10,7 +10,7 @@
 //              bn_bwd_finalize             -> dweight, dbias and the three dx coefficients
 //              bn_dx      (read x, dy, write dx)
 //
-// Partial sums are combined in double precision by the finalize kernels (one thread per channel),
+// Partial sums are combined in double precision by the finalize kernels (one warp per channel),
 // which keeps var = E[x^2] - E[x]^2 accurate.
 #include <cuda_bf16.h>
 
@@ -112,19 +112,32 @@ bn_sums(const __nv_bfloat16* __restrict__ x, float* __restrict__ part, long long
 }
 
 // coef layout (fp32, [5, c]): scale, shift (forward); k_dy, k_x, k_const (backward)
-__global__ void bn_fwd_finalize(const float* __restrict__ part, const float* __restrict__ weight,
-                                const float* __restrict__ bias, float* __restrict__ running_mean,
-                                float* __restrict__ running_var, float* __restrict__ mean_out,
-                                float* __restrict__ invstd_out, float* __restrict__ coef, int channels,
-                                int splits, long long rows, float momentum, float eps) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= channels) return;
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// One warp per channel: the lanes stride over the splits, combine in double precision.
+__global__ void __launch_bounds__(256)
+bn_fwd_finalize(const float* __restrict__ part, const float* __restrict__ weight,
+                const float* __restrict__ bias, float* __restrict__ running_mean,
+                float* __restrict__ running_var, float* __restrict__ mean_out,
+                float* __restrict__ invstd_out, float* __restrict__ coef, long long* __restrict__ tracked,
+                int channels, int splits, long long rows, float momentum, float eps) {
+  const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (c >= channels) return;  // whole warp
   double s = 0.0, q = 0.0;
-  for (int k = 0; k < splits; ++k) {
+  for (int k = lane; k < splits; k += 32) {
     const float2 v = *reinterpret_cast<const float2*>(part + (static_cast<size_t>(k) * channels + c) * 2);
     s += v.x;
     q += v.y;
   }
+  s = warp_sum(s);
+  q = warp_sum(q);
+  if (lane != 0) return;
+  if (c == 0 && tracked != nullptr) *tracked += 1;
   const double mean = s / static_cast<double>(rows);
   double var = q / static_cast<double>(rows) - mean * mean;
   var = var > 0.0 ? var : 0.0;
@@ -141,42 +154,76 @@ __global__ void bn_fwd_finalize(const float* __restrict__ part, const float* __r
   }
 }
 
-// out = in0 * ka[c] + in1 * kb[c] + kc[c]   (in1 / kb optional): the forward transform with
-// (x, -, scale, -, shift) and the input gradient with (dy, x, k_dy, k_x, k_const).
-template <bool TWO>
+__device__ __forceinline__ void load8(const float* p, float (&out)[8]) {
+  const float4 lo = *reinterpret_cast<const float4*>(p), hi = *reinterpret_cast<const float4*>(p + 4);
+  out[0] = lo.x; out[1] = lo.y; out[2] = lo.z; out[3] = lo.w;
+  out[4] = hi.x; out[5] = hi.y; out[6] = hi.z; out[7] = hi.w;
+}
+
+// y = act(x * scale[c] + shift[c] (+ residual))
+template <bool RES, bool RELU>
 __global__ void __launch_bounds__(256)
-bn_affine(const __nv_bfloat16* __restrict__ in0, const __nv_bfloat16* __restrict__ in1,
-          const float* __restrict__ ka, const float* __restrict__ kb, const float* __restrict__ kc,
-          __nv_bfloat16* __restrict__ out, long long vecs, int vec_per_row) {
+bn_apply(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+         const float* __restrict__ scale, const float* __restrict__ shift, __nv_bfloat16* __restrict__ y,
+         long long vecs, int vec_per_row) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < vecs; i += stride) {
     const int c0 = static_cast<int>(i % vec_per_row) * 8;
-    float a[8], v0[8], res[8];
-    unpack8(ld_stream(in0 + i * 8), v0);
-    const float4 a_lo = *reinterpret_cast<const float4*>(ka + c0), a_hi = *reinterpret_cast<const float4*>(ka + c0 + 4);
-    const float4 c_lo = *reinterpret_cast<const float4*>(kc + c0), c_hi = *reinterpret_cast<const float4*>(kc + c0 + 4);
-    a[0] = a_lo.x; a[1] = a_lo.y; a[2] = a_lo.z; a[3] = a_lo.w;
-    a[4] = a_hi.x; a[5] = a_hi.y; a[6] = a_hi.z; a[7] = a_hi.w;
-    res[0] = c_lo.x; res[1] = c_lo.y; res[2] = c_lo.z; res[3] = c_lo.w;
-    res[4] = c_hi.x; res[5] = c_hi.y; res[6] = c_hi.z; res[7] = c_hi.w;
+    float a[8], v[8], out[8];
+    unpack8(ld_stream(x + i * 8), v);
+    load8(scale + c0, a);
+    load8(shift + c0, out);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) res[k] = fmaf(v0[k], a[k], res[k]);
-    if (TWO) {
-      float v1[8];
-      unpack8(ld_stream(in1 + i * 8), v1);
-      const float4 b_lo = *reinterpret_cast<const float4*>(kb + c0), b_hi = *reinterpret_cast<const float4*>(kb + c0 + 4);
-      const float b[8] = {b_lo.x, b_lo.y, b_lo.z, b_lo.w, b_hi.x, b_hi.y, b_hi.z, b_hi.w};
+    for (int k = 0; k < 8; ++k) out[k] = fmaf(v[k], a[k], out[k]);
+    if (RES) {
+      float r[8];
+      unpack8(ld_stream(res + i * 8), r);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) res[k] = fmaf(v1[k], b[k], res[k]);
+      for (int k = 0; k < 8; ++k) out[k] += r[k];
     }
-    *reinterpret_cast<uint4*>(out + i * 8) = pack8(res);
+    if (RELU) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) out[k] = fmaxf(out[k], 0.f);
+    }
+    *reinterpret_cast<uint4*>(y + i * 8) = pack8(out);
   }
 }
 
+// g = RELU ? dy * (y > 0) : dy;   dx = g * k_dy[c] + x * k_x[c] + k_const[c];   dres = g (optional)
+template <bool RELU, bool DRES>
+__global__ void __launch_bounds__(256)
+bn_dx(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+      const __nv_bfloat16* __restrict__ y, const float* __restrict__ k_dy, const float* __restrict__ k_x,
+      const float* __restrict__ k_const, __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dres,
+      long long vecs, int vec_per_row) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < vecs; i += stride) {
+    const int c0 = static_cast<int>(i % vec_per_row) * 8;
+    float g[8], xv[8], a[8], b[8], out[8];
+    unpack8(ld_stream(dy + i * 8), g);
+    unpack8(ld_stream(x + i * 8), xv);
+    if (RELU) {
+      float yv[8];
+      unpack8(ld_stream(y + i * 8), yv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] = yv[k] > 0.f ? g[k] : 0.f;
+    }
+    load8(k_dy + c0, a);
+    load8(k_x + c0, b);
+    load8(k_const + c0, out);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) out[k] = fmaf(g[k], a[k], fmaf(xv[k], b[k], out[k]));
+    *reinterpret_cast<uint4*>(dx + i * 8) = pack8(out);
+    if (DRES) *reinterpret_cast<uint4*>(dres + i * 8) = pack8(g);
+  }
+}
+
+template <bool RELU>
 __global__ void __launch_bounds__(THREADS)
 bn_bwd_sums(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
-            const float* __restrict__ mean, const float* __restrict__ invstd, float* __restrict__ part,
-            long long rows, int channels, long long rows_per_split) {
+            const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
+            const float* __restrict__ invstd, float* __restrict__ part, long long rows, int channels,
+            long long rows_per_split) {
   const int group = threadIdx.x % GROUPS;
   const int lane = threadIdx.x / GROUPS;
   const int c0 = (blockIdx.x * GROUPS + group) * 8;
@@ -187,26 +234,32 @@ bn_bwd_sums(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
   for (int i = 0; i < 8; ++i) s_dy[i] = s_dyx[i] = 0.f;
   if (c0 < channels) {
     float mu[8], is[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      mu[i] = mean[c0 + i];
-      is[i] = invstd[c0 + i];
-    }
+    load8(mean + c0, mu);
+    load8(invstd + c0, is);
     const __nv_bfloat16* bx = x + c0;
     const __nv_bfloat16* bg = dy + c0;
+    const __nv_bfloat16* by = y + c0;
+    constexpr int U = RELU ? 2 : UNROLL;  // three tensors in flight when the mask is needed
     long long r = r_begin + lane;
-    for (; r + (UNROLL - 1) * LANES < r_end; r += UNROLL * LANES) {
-      uint4 rx[UNROLL], rg[UNROLL];
+    for (; r + (U - 1) * LANES < r_end; r += U * LANES) {
+      uint4 rx[U], rg[U], ry[U];
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
+      for (int u = 0; u < U; ++u) {
         rx[u] = ld_stream(bx + (r + u * LANES) * channels);
         rg[u] = ld_stream(bg + (r + u * LANES) * channels);
+        if (RELU) ry[u] = ld_stream(by + (r + u * LANES) * channels);
       }
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
+      for (int u = 0; u < U; ++u) {
         float xv[8], gv[8];
         unpack8(rx[u], xv);
         unpack8(rg[u], gv);
+        if (RELU) {
+          float yv[8];
+          unpack8(ry[u], yv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) gv[i] = yv[i] > 0.f ? gv[i] : 0.f;
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           s_dy[i] += gv[i];
@@ -218,6 +271,12 @@ bn_bwd_sums(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
       float xv[8], gv[8];
       unpack8(ld_stream(bx + r * channels), xv);
       unpack8(ld_stream(bg + r * channels), gv);
+      if (RELU) {
+        float yv[8];
+        unpack8(ld_stream(by + r * channels), yv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) gv[i] = yv[i] > 0.f ? gv[i] : 0.f;
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         s_dy[i] += gv[i];
@@ -231,18 +290,23 @@ bn_bwd_sums(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
 // dx = w*invstd * (dy - mean(dy) - xhat * mean(dy*xhat))
 //    = dy * k_dy + x * k_x + k_const  with
 //   k_dy = w*invstd, k_x = -k_dy * invstd * m2, k_const = -k_dy * (m1 - mean * invstd * m2)
-__global__ void bn_bwd_finalize(const float* __restrict__ part, const float* __restrict__ weight,
-                                const float* __restrict__ mean, const float* __restrict__ invstd,
-                                float* __restrict__ dweight, float* __restrict__ dbias,
-                                float* __restrict__ coef, int channels, int splits, long long rows) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= channels) return;
+__global__ void __launch_bounds__(256)
+bn_bwd_finalize(const float* __restrict__ part, const float* __restrict__ weight,
+                const float* __restrict__ mean, const float* __restrict__ invstd,
+                float* __restrict__ dweight, float* __restrict__ dbias,
+                float* __restrict__ coef, int channels, int splits, long long rows) {
+  const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (c >= channels) return;  // whole warp
   double s1 = 0.0, s2 = 0.0;
-  for (int k = 0; k < splits; ++k) {
+  for (int k = lane; k < splits; k += 32) {
     const float2 v = *reinterpret_cast<const float2*>(part + (static_cast<size_t>(k) * channels + c) * 2);
     s1 += v.x;
     s2 += v.y;
   }
+  s1 = warp_sum(s1);
+  s2 = warp_sum(s2);
+  if (lane != 0) return;
   dbias[c] = static_cast<float>(s1);
   dweight[c] = static_cast<float>(s2);
   const double m1 = s1 / static_cast<double>(rows), m2 = s2 / static_cast<double>(rows);
@@ -287,12 +351,22 @@ int affine_grid(long long vecs) {
   return static_cast<int>(std::min<long long>((vecs + 255) / 256, 148LL * 16));
 }
 
+void check_like(const at::Tensor& t, const at::Tensor& x, const char* name) {
+  TORCH_CHECK(t.sizes() == x.sizes() && t.scalar_type() == at::kBFloat16 && t.is_cuda() &&
+                  t.is_contiguous(at::MemoryFormat::ChannelsLast) &&
+                  (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0,
+              name, " must match x (channels_last bf16, 16-byte aligned)");
+}
+
 }  // namespace
 
-// Returns (y, mean, invstd).  running_mean / running_var are updated in place when given.
+// y = act(batch_norm(x) (+ residual)).  Returns (y, mean, invstd).  running_mean / running_var and
+// the batch counter are updated in place when given.
 std::vector<at::Tensor> bn_forward_train(at::Tensor x, at::Tensor weight, at::Tensor bias,
                                          c10::optional<at::Tensor> running_mean,
-                                         c10::optional<at::Tensor> running_var, double momentum, double eps) {
+                                         c10::optional<at::Tensor> running_var,
+                                         c10::optional<at::Tensor> num_batches_tracked, double momentum,
+                                         double eps, c10::optional<at::Tensor> residual, bool relu) {
   const Shape s = plan(x);
   check_vec(weight, s.channels, "weight");
   check_vec(bias, s.channels, "bias");
@@ -303,6 +377,17 @@ std::vector<at::Tensor> bn_forward_train(at::Tensor x, at::Tensor weight, at::Te
     rm = running_mean->data_ptr<float>();
     rv = running_var->data_ptr<float>();
   }
+  long long* tracked = nullptr;
+  if (num_batches_tracked.has_value()) {
+    TORCH_CHECK(num_batches_tracked->is_cuda() && num_batches_tracked->scalar_type() == at::kLong &&
+                    num_batches_tracked->numel() == 1, "num_batches_tracked must be a CUDA int64 scalar");
+    tracked = reinterpret_cast<long long*>(num_batches_tracked->data_ptr<int64_t>());
+  }
+  const __nv_bfloat16* rp = nullptr;
+  if (residual.has_value()) {
+    check_like(*residual, x, "residual");
+    rp = reinterpret_cast<const __nv_bfloat16*>(residual->data_ptr());
+  }
   const int dev = x.get_device();
   c10::cuda::CUDAGuard guard(dev);
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
@@ -312,34 +397,47 @@ std::vector<at::Tensor> bn_forward_train(at::Tensor x, at::Tensor weight, at::Te
   auto coef = at::empty({2, s.channels}, f32);
   auto y = at::empty_like(x);
   const auto* xp = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
+  auto* yp = reinterpret_cast<__nv_bfloat16*>(y.data_ptr());
   bn_sums<<<dim3(s.chunks, s.splits), THREADS, 0, stream>>>(xp, part.data_ptr<float>(), s.rows, s.channels,
                                                             s.rows_per_split);
-  bn_fwd_finalize<<<(s.channels + 127) / 128, 128, 0, stream>>>(
+  bn_fwd_finalize<<<(s.channels + 7) / 8, 256, 0, stream>>>(
       part.data_ptr<float>(), weight.data_ptr<float>(), bias.data_ptr<float>(), rm, rv, mean.data_ptr<float>(),
-      invstd.data_ptr<float>(), coef.data_ptr<float>(), s.channels, s.splits, s.rows,
+      invstd.data_ptr<float>(), coef.data_ptr<float>(), tracked, s.channels, s.splits, s.rows,
       static_cast<float>(momentum), static_cast<float>(eps));
   const long long vecs = s.rows * (s.channels / 8);
-  bn_affine<false><<<affine_grid(vecs), 256, 0, stream>>>(
-      xp, nullptr, coef.data_ptr<float>(), nullptr, coef.data_ptr<float>() + s.channels,
-      reinterpret_cast<__nv_bfloat16*>(y.data_ptr()), vecs, s.channels / 8);
+  const int grid = affine_grid(vecs), vpr = s.channels / 8;
+  const float* scale = coef.data_ptr<float>();
+  const float* shift = scale + s.channels;
+  if (rp != nullptr && relu)
+    bn_apply<true, true><<<grid, 256, 0, stream>>>(xp, rp, scale, shift, yp, vecs, vpr);
+  else if (rp != nullptr)
+    bn_apply<true, false><<<grid, 256, 0, stream>>>(xp, rp, scale, shift, yp, vecs, vpr);
+  else if (relu)
+    bn_apply<false, true><<<grid, 256, 0, stream>>>(xp, nullptr, scale, shift, yp, vecs, vpr);
+  else
+    bn_apply<false, false><<<grid, 256, 0, stream>>>(xp, nullptr, scale, shift, yp, vecs, vpr);
   B200_CUDA_CHECK(cudaGetLastError());
-  count_launch();
-  count_launch();
-  count_launch();
+  count_launch(3);
   return {y, mean, invstd};
 }
 
-// Returns (dx, dweight, dbias).
+// Backward of y = act(batch_norm(x) (+ residual)).  `y` is needed when the activation is a ReLU.
+// Returns (dx, dweight, dbias) and, with `want_dres`, the gradient of the residual (dy masked by
+// the activation; without an activation it is dy itself and is not returned).
 std::vector<at::Tensor> bn_backward_train(at::Tensor x, at::Tensor dy, at::Tensor weight, at::Tensor mean,
-                                          at::Tensor invstd) {
+                                          at::Tensor invstd, c10::optional<at::Tensor> y, bool want_dres) {
   const Shape s = plan(x);
-  TORCH_CHECK(dy.sizes() == x.sizes() && dy.scalar_type() == at::kBFloat16 && dy.is_cuda() &&
-                  dy.is_contiguous(at::MemoryFormat::ChannelsLast) &&
-                  (reinterpret_cast<uintptr_t>(dy.data_ptr()) & 15) == 0,
-              "dy must match x (channels_last bf16)");
+  check_like(dy, x, "dy");
   check_vec(weight, s.channels, "weight");
   check_vec(mean, s.channels, "mean");
   check_vec(invstd, s.channels, "invstd");
+  const bool relu = y.has_value();
+  const __nv_bfloat16* yp = nullptr;
+  if (relu) {
+    check_like(*y, x, "y");
+    yp = reinterpret_cast<const __nv_bfloat16*>(y->data_ptr());
+  }
+  const bool dres_out = want_dres && relu;
   const int dev = x.get_device();
   c10::cuda::CUDAGuard guard(dev);
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
@@ -348,24 +446,35 @@ std::vector<at::Tensor> bn_backward_train(at::Tensor x, at::Tensor dy, at::Tenso
   auto dweight = at::empty({s.channels}, f32), dbias = at::empty({s.channels}, f32);
   auto coef = at::empty({5, s.channels}, f32);
   auto dx = at::empty_like(x);
+  at::Tensor dres;
+  if (dres_out) dres = at::empty_like(x);
   const auto* xp = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
   const auto* gp = reinterpret_cast<const __nv_bfloat16*>(dy.data_ptr());
-  bn_bwd_sums<<<dim3(s.chunks, s.splits), THREADS, 0, stream>>>(
-      xp, gp, mean.data_ptr<float>(), invstd.data_ptr<float>(), part.data_ptr<float>(), s.rows, s.channels,
-      s.rows_per_split);
-  bn_bwd_finalize<<<(s.channels + 127) / 128, 128, 0, stream>>>(
+  auto* dxp = reinterpret_cast<__nv_bfloat16*>(dx.data_ptr());
+  auto* drp = dres_out ? reinterpret_cast<__nv_bfloat16*>(dres.data_ptr()) : nullptr;
+  const dim3 sgrid(s.chunks, s.splits);
+  if (relu)
+    bn_bwd_sums<true><<<sgrid, THREADS, 0, stream>>>(xp, gp, yp, mean.data_ptr<float>(), invstd.data_ptr<float>(),
+                                                     part.data_ptr<float>(), s.rows, s.channels, s.rows_per_split);
+  else
+    bn_bwd_sums<false><<<sgrid, THREADS, 0, stream>>>(xp, gp, xp, mean.data_ptr<float>(), invstd.data_ptr<float>(),
+                                                      part.data_ptr<float>(), s.rows, s.channels, s.rows_per_split);
+  bn_bwd_finalize<<<(s.channels + 7) / 8, 256, 0, stream>>>(
       part.data_ptr<float>(), weight.data_ptr<float>(), mean.data_ptr<float>(), invstd.data_ptr<float>(),
       dweight.data_ptr<float>(), dbias.data_ptr<float>(), coef.data_ptr<float>(), s.channels, s.splits, s.rows);
   const long long vecs = s.rows * (s.channels / 8);
-  float* k = coef.data_ptr<float>();
-  bn_affine<true><<<affine_grid(vecs), 256, 0, stream>>>(gp, xp, k + 2 * s.channels, k + 3 * s.channels,
-                                                         k + 4 * s.channels,
-                                                         reinterpret_cast<__nv_bfloat16*>(dx.data_ptr()), vecs,
-                                                         s.channels / 8);
+  const int grid = affine_grid(vecs), vpr = s.channels / 8;
+  const float* k = coef.data_ptr<float>();
+  const float *k_dy = k + 2 * s.channels, *k_x = k + 3 * s.channels, *k_c = k + 4 * s.channels;
+  if (relu && dres_out)
+    bn_dx<true, true><<<grid, 256, 0, stream>>>(gp, xp, yp, k_dy, k_x, k_c, dxp, drp, vecs, vpr);
+  else if (relu)
+    bn_dx<true, false><<<grid, 256, 0, stream>>>(gp, xp, yp, k_dy, k_x, k_c, dxp, nullptr, vecs, vpr);
+  else
+    bn_dx<false, false><<<grid, 256, 0, stream>>>(gp, xp, nullptr, k_dy, k_x, k_c, dxp, nullptr, vecs, vpr);
   B200_CUDA_CHECK(cudaGetLastError());
-  count_launch();
-  count_launch();
-  count_launch();
+  count_launch(3);
+  if (dres_out) return {dx, dweight, dbias, dres};
   return {dx, dweight, dbias};
 }
 

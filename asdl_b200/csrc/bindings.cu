@@ -29,9 +29,13 @@ void bn_unitwise_stats(at::Tensor y, at::Tensor g, at::Tensor weight, at::Tensor
                        double alpha, double beta);
 std::vector<at::Tensor> bn_forward_train(at::Tensor x, at::Tensor weight, at::Tensor bias,
                                          c10::optional<at::Tensor> running_mean,
-                                         c10::optional<at::Tensor> running_var, double momentum, double eps);
+                                         c10::optional<at::Tensor> running_var,
+                                         c10::optional<at::Tensor> num_batches_tracked, double momentum,
+                                         double eps, c10::optional<at::Tensor> residual, bool relu);
 std::vector<at::Tensor> bn_backward_train(at::Tensor x, at::Tensor dy, at::Tensor weight, at::Tensor mean,
-                                          at::Tensor invstd);
+                                          at::Tensor invstd, c10::optional<at::Tensor> y, bool want_dres);
+void bn_unitwise_stats_xhat(at::Tensor x, at::Tensor dy, c10::optional<at::Tensor> y, at::Tensor mean,
+                            at::Tensor invstd, at::Tensor stats, double alpha, double beta);
 void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot, int64_t wait_ms);
 void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale);
 void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs);
@@ -59,6 +63,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("bn_unitwise_stats", &b200::bn_unitwise_stats);
   m.def("bn_forward_train", &b200::bn_forward_train);
   m.def("bn_backward_train", &b200::bn_backward_train);
+  m.def("bn_unitwise_stats_xhat", &b200::bn_unitwise_stats_xhat);
   m.def("symm_barrier", &b200::symm_barrier);
   m.def("symm_reduce_segments", &b200::symm_reduce_segments);
   m.def("symm_bcast_segments", &b200::symm_bcast_segments);

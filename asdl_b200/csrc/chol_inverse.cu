@@ -103,24 +103,24 @@ __global__ void __launch_bounds__(256) chol_diag_kernel(const CholMat* mats, int
     S[r][c] = v;
   }
   __syncthreads();
+  // Left-looking factorisation by columns, one thread per row: entry (i, j) needs the dot product
+  // of rows i and j over the columns already done.  Row j is a shared-memory broadcast, row i is
+  // read with a conflict-free stride (the +1 padding), and there are two barriers per column.
   for (int j = 0; j < CB; ++j) {
-    if (tid == 0) {
-      float p = S[j][j];
-      if (!(p > 0.f)) {
+    float v = 0.f;
+    if (tid >= j && tid < CB) {
+      v = S[tid][j];
+      for (int k = 0; k < j; ++k) v = fmaf(-S[tid][k], S[j][k], v);
+    }
+    if (tid == j) {
+      if (!(v > 0.f)) {
         set_error(status, ERR_NOT_SPD);
-        p = 1.f;
+        v = 1.f;
       }
-      S[j][j] = sqrtf(p);
+      S[j][j] = sqrtf(v);
     }
     __syncthreads();
-    if (tid > j && tid < CB) S[tid][j] /= S[j][j];
-    __syncthreads();
-    // trailing update of the lower triangle: rows i > j, columns j < c <= i
-    const int m = CB - 1 - j;
-    for (int e = tid; e < m * m; e += 256) {
-      const int i = j + 1 + e / m, c = j + 1 + e % m;
-      if (c <= i) S[i][c] -= S[i][j] * S[c][j];
-    }
+    if (tid > j && tid < CB) S[tid][j] = v / S[j][j];
     __syncthreads();
   }
   // T = S^-1 (lower triangular): column c is a forward substitution; four neighbouring lanes of

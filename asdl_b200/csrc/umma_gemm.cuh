@@ -446,27 +446,39 @@ splitk_reduce_kernel(const __grid_constant__ GemmProblem single, const GemmProbl
   const int sub_r = blockIdx.y >> 2, sub_c = blockIdx.y & 3;  // 4x4 patches of 32x32
   if (diag_tile && sub_c > sub_r) return;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  // patches that lie completely outside the matrix (edge tiles of small problems) have no work
+  if (tm * G_BM + sub_r * 32 >= P.M || tn * G_BN + sub_c * 32 >= P.N) return;
   const float* base = P.ws + static_cast<size_t>(tile_id) * P.nsplit * (G_BM * G_BN);
   const int gc = tn * G_BN + sub_c * 32 + tx;
+  // sum the partials in split order; the loads of the four rows of a thread and of four splits are
+  // issued together (16 independent loads in flight per thread)
+  float accs[4] = {0.f, 0.f, 0.f, 0.f};
+  {
+    const float* p0 = base + static_cast<size_t>(sub_r * 32 + ty) * G_BN + sub_c * 32 + tx;
+    int s = 0;
+    for (; s + 4 <= P.nsplit; s += 4) {
+      float v[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          v[i][u] = __ldcg(p0 + static_cast<size_t>(8 * i) * G_BN + static_cast<size_t>(s + u) * (G_BM * G_BN));
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) accs[i] += v[i][u];
+    }
+    for (; s < P.nsplit; ++s)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        accs[i] += __ldcg(p0 + static_cast<size_t>(8 * i) * G_BN + static_cast<size_t>(s) * (G_BM * G_BN));
+  }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int lr = ty + 8 * i;
     const int row = sub_r * 32 + lr;
     const int gr = tm * G_BM + row;
-    const float* p = base + static_cast<size_t>(row) * G_BN + sub_c * 32 + tx;
-    float acc = 0.f;
-    int s = 0;
-    for (; s + 4 <= P.nsplit; s += 4) {
-      const float a0 = __ldcg(p + static_cast<size_t>(s) * (G_BM * G_BN));
-      const float a1 = __ldcg(p + static_cast<size_t>(s + 1) * (G_BM * G_BN));
-      const float a2 = __ldcg(p + static_cast<size_t>(s + 2) * (G_BM * G_BN));
-      const float a3 = __ldcg(p + static_cast<size_t>(s + 3) * (G_BM * G_BN));
-      acc += a0;
-      acc += a1;
-      acc += a2;
-      acc += a3;
-    }
-    for (; s < P.nsplit; ++s) acc += __ldcg(p + static_cast<size_t>(s) * (G_BM * G_BN));
+    const float acc = accs[i];
     float val = P.alpha * acc;
     const bool inb = gr < P.M && gc < P.N;
     if (inb && P.beta != 0.f) val += P.beta * P.Cin[static_cast<size_t>(gr) * P.ldc + gc];

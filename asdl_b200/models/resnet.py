@@ -13,19 +13,24 @@ __all__ = ['ResNet', 'Bottleneck', 'resnet50', 'resnet_tiny']
 class Bottleneck(nn.Module):
     expansion = 4
 
-    def __init__(self, inplanes, planes, stride=1, downsample=None):
+    def __init__(self, inplanes, planes, stride=1, downsample=None, fused=False):
         super().__init__()
+        act = 'relu' if fused else None
+        self.fused = fused
         self.conv1 = nn.Conv2d(inplanes, planes, 1, bias=False)
-        self.bn1 = FusedBatchNorm2d(planes)
+        self.bn1 = FusedBatchNorm2d(planes, act=act)
         self.conv2 = nn.Conv2d(planes, planes, 3, stride=stride, padding=1, bias=False)
-        self.bn2 = FusedBatchNorm2d(planes)
+        self.bn2 = FusedBatchNorm2d(planes, act=act)
         self.conv3 = nn.Conv2d(planes, planes * self.expansion, 1, bias=False)
-        self.bn3 = FusedBatchNorm2d(planes * self.expansion)
+        self.bn3 = FusedBatchNorm2d(planes * self.expansion, act=act)
         self.relu = nn.ReLU(inplace=False)
         self.downsample = downsample
 
     def forward(self, x):
         identity = x if self.downsample is None else self.downsample(x)
+        if self.fused:  # the ReLUs and the residual add run inside the normalisation kernels
+            out = self.bn2(self.conv2(self.bn1(self.conv1(x))))
+            return self.bn3(self.conv3(out), identity)
         out = self.relu(self.bn1(self.conv1(x)))
         out = self.relu(self.bn2(self.conv2(out)))
         out = self.bn3(self.conv3(out))
@@ -33,11 +38,16 @@ class Bottleneck(nn.Module):
 
 
 class ResNet(nn.Module):
-    def __init__(self, layers=(3, 4, 6, 3), num_classes=1000, width=64, in_channels=3):
+    """``fused=True`` folds every ReLU and residual add into the preceding normalisation layer
+    (:class:`FusedBatchNorm2d`); curvature of such layers is supported by
+    ``FusedKfacGradientMaker``, while the generic makers need ``fused=False``."""
+
+    def __init__(self, layers=(3, 4, 6, 3), num_classes=1000, width=64, in_channels=3, fused=False):
         super().__init__()
         self.inplanes = width
+        self.fused = fused
         self.conv1 = nn.Conv2d(in_channels, width, 7, stride=2, padding=3, bias=False)
-        self.bn1 = FusedBatchNorm2d(width)
+        self.bn1 = FusedBatchNorm2d(width, act='relu' if fused else None)
         self.relu = nn.ReLU(inplace=False)
         self.maxpool = nn.MaxPool2d(3, stride=2, padding=1)
         self.layer1 = self._make_layer(width, layers[0])
@@ -59,21 +69,22 @@ class ResNet(nn.Module):
             downsample = nn.Sequential(
                 nn.Conv2d(self.inplanes, planes * Bottleneck.expansion, 1, stride=stride, bias=False),
                 FusedBatchNorm2d(planes * Bottleneck.expansion))
-        layers = [Bottleneck(self.inplanes, planes, stride, downsample)]
+        layers = [Bottleneck(self.inplanes, planes, stride, downsample, fused=self.fused)]
         self.inplanes = planes * Bottleneck.expansion
-        layers += [Bottleneck(self.inplanes, planes) for _ in range(1, blocks)]
+        layers += [Bottleneck(self.inplanes, planes, fused=self.fused) for _ in range(1, blocks)]
         return nn.Sequential(*layers)
 
     def forward(self, x):
-        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        x = self.bn1(self.conv1(x))
+        x = self.maxpool(x if self.fused else self.relu(x))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         return self.fc(torch.flatten(self.avgpool(x), 1))
 
 
-def resnet50(num_classes=1000):
-    return ResNet((3, 4, 6, 3), num_classes=num_classes)
+def resnet50(num_classes=1000, fused=True):
+    return ResNet((3, 4, 6, 3), num_classes=num_classes, fused=fused)
 
 
-def resnet_tiny(num_classes=10, width=8):
+def resnet_tiny(num_classes=10, width=8, fused=False):
     """Two-stage miniature with the same block structure, for tests and smoke runs."""
-    return ResNet((1, 1, 1, 1), num_classes=num_classes, width=width)
+    return ResNet((1, 1, 1, 1), num_classes=num_classes, width=width, fused=fused)

@@ -31,6 +31,10 @@ class _BatchNormNd(Operation):
 
     @staticmethod
     def preprocess_in_data(module, in_data, out_data):
+        if getattr(module, 'fused_output', False):
+            raise ValueError(f'{module} fuses an activation or a residual add: its output does not determine '
+                             f'the normalised input.  Build the model without fusion for this gradient '
+                             f'maker, or use FusedKfacGradientMaker.')
         shape = (1, module.num_features) + (1,) * (out_data.ndim - 2)
         return (out_data - module.bias.view(shape)).div(module.weight.view(shape))
 

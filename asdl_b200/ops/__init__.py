@@ -19,7 +19,7 @@ import torch
 
 from . import _build
 
-__all__ = ['gram', 'matmul_tn', 'kron_apply', 'spd_inverse', 'spd_inverse_grouped', 'unitwise_inverse', 'batchnorm_unitwise_stats', 'batch_norm_train', 'conv_patch_gram',
+__all__ = ['gram', 'matmul_tn', 'kron_apply', 'spd_inverse', 'spd_inverse_grouped', 'unitwise_inverse', 'batchnorm_unitwise_stats', 'batch_norm_train', 'batchnorm_unitwise_stats_from_input', 'conv_patch_gram',
            'set_backend', 'get_backend', 'set_precision', 'get_precision', 'extension',
            'cuda_kernels_enabled', 'check_status']
 
@@ -321,40 +321,87 @@ def batchnorm_unitwise_stats(y: torch.Tensor, g: torch.Tensor, weight: torch.Ten
 
 
 class _BatchNormTrain(torch.autograd.Function):
-    """Training-mode batch normalisation on the library's NHWC bf16 kernels."""
+    """Training-mode batch normalisation (+ residual add, + ReLU) on the library's NHWC bf16 kernels."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, running_mean, running_var, momentum, eps):
+    def forward(ctx, x, weight, bias, running_mean, running_var, num_batches_tracked, momentum, eps,
+                residual, relu):
         y, mean, invstd = extension().bn_forward_train(x, weight.detach(), bias.detach(), running_mean,
-                                                       running_var, float(momentum), float(eps))
-        ctx.save_for_backward(x, weight, mean, invstd)
-        return y
+                                                       running_var, num_batches_tracked, float(momentum),
+                                                       float(eps), residual, bool(relu))
+        ctx.relu, ctx.has_residual = bool(relu), residual is not None
+        ctx.save_for_backward(x, weight, mean, invstd, *([y] if relu else []))
+        ctx.mark_non_differentiable(mean, invstd)
+        return y, mean, invstd
 
     @staticmethod
-    def backward(ctx, dy):
-        x, weight, mean, invstd = ctx.saved_tensors
+    def backward(ctx, dy, _dmean, _dinvstd):
+        x, weight, mean, invstd, *rest = ctx.saved_tensors
         if not dy.is_contiguous(memory_format=torch.channels_last):
             dy = dy.contiguous(memory_format=torch.channels_last)
-        dx, dweight, dbias = extension().bn_backward_train(x, dy, weight.detach(), mean, invstd)
-        return dx, dweight, dbias, None, None, None, None
+        y = rest[0] if ctx.relu else None
+        out = extension().bn_backward_train(x, dy, weight.detach(), mean, invstd, y, ctx.has_residual)
+        dx, dweight, dbias = out[:3]
+        dres = None
+        if ctx.has_residual:
+            dres = out[3] if ctx.relu else dy
+        return dx, dweight, dbias, None, None, None, None, None, dres, None
 
 
-def batch_norm_train_supported(x: torch.Tensor, weight, bias) -> bool:
+def batch_norm_train_supported(x: torch.Tensor, weight, bias, residual=None) -> bool:
     """True when :func:`batch_norm_train` runs on the library's kernels for this input."""
-    return (weight is not None and bias is not None and cuda_kernels_enabled(x) and x.ndim == 4
-            and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.numel() > 0
-            and weight.dtype == torch.float32 and bias.dtype == torch.float32
-            and x.is_contiguous(memory_format=torch.channels_last))
+    ok = (weight is not None and bias is not None and cuda_kernels_enabled(x) and x.ndim == 4
+          and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.numel() > 0
+          and weight.dtype == torch.float32 and bias.dtype == torch.float32
+          and x.is_contiguous(memory_format=torch.channels_last))
+    if ok and residual is not None:
+        ok = (residual.shape == x.shape and residual.dtype == torch.bfloat16
+              and residual.is_contiguous(memory_format=torch.channels_last))
+    return ok
 
 
-def batch_norm_train(x, weight, bias, running_mean=None, running_var=None, momentum=0.1, eps=1e-5):
-    """Batch normalisation with batch statistics (and the running statistics updated in place),
-    differentiable.  CUDA, channels_last bf16 activations with fp32 parameters: three kernels
-    forward (sums, finalize, transform) and three backward, each pass reading / writing every
-    activation exactly once with 16-byte accesses; anything else: ``F.batch_norm``."""
-    if batch_norm_train_supported(x, weight, bias):
-        return _BatchNormTrain.apply(x, weight, bias, running_mean, running_var, momentum, eps)
-    return torch.nn.functional.batch_norm(x, running_mean, running_var, weight, bias, True, momentum, eps)
+def batch_norm_train(x, weight, bias, running_mean=None, running_var=None, momentum=0.1, eps=1e-5,
+                     residual=None, relu=False, num_batches_tracked=None, return_stats=False):
+    """``act(batch_norm(x) + residual)`` with batch statistics (running statistics and the batch
+    counter updated in place), differentiable in x, weight, bias and residual.  CUDA, channels_last
+    bf16 activations with fp32 parameters: three kernels forward (sums, finalize, transform) and
+    three backward, each pass reading / writing every activation once with 16-byte accesses;
+    anything else: ``F.batch_norm`` followed by the add and the ReLU.  With ``return_stats`` the
+    result is ``(y, mean, invstd)`` (``None`` statistics on the PyTorch path)."""
+    if batch_norm_train_supported(x, weight, bias, residual):
+        y, mean, invstd = _BatchNormTrain.apply(x, weight, bias, running_mean, running_var,
+                                                num_batches_tracked, momentum, eps, residual, relu)
+        return (y, mean, invstd) if return_stats else y
+    if num_batches_tracked is not None:
+        num_batches_tracked.add_(1)
+    y = torch.nn.functional.batch_norm(x, running_mean, running_var, weight, bias, True, momentum, eps)
+    if residual is not None:
+        y = y + residual
+    if relu:
+        y = torch.relu(y)
+    return (y, None, None) if return_stats else y
+
+
+def batchnorm_unitwise_stats_from_input(x, dy, y, mean, invstd, out, alpha=1.0, beta=0.0):
+    """Unit-wise curvature blocks of a BatchNorm layer with a fused activation: the normalised
+    input is ``(x - mean) * invstd`` and the output gradient ``dy`` is masked by the ReLU that
+    produced ``y`` (``y=None``: no activation).  Same result layout as
+    :func:`batchnorm_unitwise_stats`."""
+    if (cuda_kernels_enabled(x, dy) and x.ndim == 4 and x.dtype == torch.bfloat16 and dy.dtype == torch.bfloat16
+            and x.shape[1] % 8 == 0 and x.is_contiguous(memory_format=torch.channels_last)
+            and (y is None or y.is_contiguous(memory_format=torch.channels_last)) and out.is_contiguous()):
+        if not dy.is_contiguous(memory_format=torch.channels_last):
+            dy = dy.contiguous(memory_format=torch.channels_last)
+        extension().bn_unitwise_stats_xhat(x, dy, y, mean, invstd, out, float(alpha), float(beta))
+        return out
+    shape = (1, -1) + (1,) * (x.ndim - 2)
+    xh = (x.float() - mean.view(shape)) * invstd.view(shape)
+    g = dy.float() if y is None else dy.float() * (y > 0)
+    dims = tuple(range(2, x.ndim))
+    gw, gb = (xh * g).sum(dim=dims), g.sum(dim=dims)
+    ww, wb, bb = gw.square().sum(dim=0), (gw * gb).sum(dim=0), gb.square().sum(dim=0)
+    new = torch.stack([torch.stack([ww, wb], dim=1), torch.stack([wb, bb], dim=1)], dim=1)
+    return out.mul_(beta).add_(new, alpha=alpha)
 
 
 def unitwise_inverse(blocks: torch.Tensor, damping: float = 0.0) -> torch.Tensor:

@@ -478,13 +478,18 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                     return
                 y = output.detach()
                 if output.requires_grad:
-                    saved = y.clone() if self.clone_norm_outputs else y
+                    fused = getattr(module, 'fused_output', False)
+                    if fused:  # (x, mean, invstd, y) of this forward pass
+                        saved = module.curvature_inputs
+                        module.curvature_inputs = None
+                    else:
+                        saved = y.clone() if self.clone_norm_outputs else y
 
                     def bwd(grad):
                         if not state['on']:
                             return
                         with torch.no_grad():
-                            self._norm_statistics(st, saved, grad.detach(), alpha, beta)
+                            self._norm_statistics(st, saved, grad.detach(), alpha, beta, fused)
                     output.register_hook(bwd)
             return fwd
 
@@ -492,6 +497,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             handles.append(st.module.register_forward_hook(kron_hook(st)))
         for st in self._norm:
             handles.append(st.module.register_forward_hook(norm_hook(st)))
+            if hasattr(st.module, 'keep_curvature_inputs'):
+                st.module.keep_curvature_inputs = True
         return handles, state
 
     def _push_factor(self, st: _KronState, t, output, alpha, is_A):
@@ -531,12 +538,16 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                              float(scale), True, True, [], 0)
 
     @staticmethod
-    def _norm_statistics(st: _NormState, y, g, alpha, beta):
+    def _norm_statistics(st: _NormState, y, g, alpha, beta, fused=False):
         module = st.module
         staged = getattr(st, 'stage', None) is not None  # reduced over ranks after the backward pass
         target = st.stage if staged else st.stats
         if staged:
             alpha, beta = 1.0, 0.0
+        if fused:
+            x, mean, invstd, out = y
+            ops.batchnorm_unitwise_stats_from_input(x, g, out, mean, invstd, target, alpha=alpha, beta=beta)
+            return
         if not isinstance(module, nn.LayerNorm):
             ops.batchnorm_unitwise_stats(y, g, module.weight, module.bias, out=target, alpha=alpha, beta=beta)
             return
@@ -613,6 +624,10 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             state['on'] = False
             for h in handles:
                 h.remove()
+            for st in self._norm:
+                if hasattr(st.module, 'keep_curvature_inputs'):
+                    st.module.keep_curvature_inputs = False
+                    st.module.curvature_inputs = None
         with torch.no_grad():
             grads = [p.grad for p in model.parameters() if p.grad is not None]
             if grads:

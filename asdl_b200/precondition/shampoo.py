@@ -511,6 +511,101 @@ def _power_iteration_batched(mats, num_iters=100, error_tolerance=1e-6, check_ev
     return value
 
 
+class _NewtonChainCuda:
+    """Coupled Newton iteration for a batch of equally sized matrices on the tensor cores.
+
+    Every product of an iteration (T^2, T^4, ..., T^p M and R T) is one grouped tcgen05 launch over
+    the whole batch, with fp32-grade accuracy from bf16 hi/lo operand splits.  All iterates are
+    polynomials in the (symmetric) input, hence symmetric, so the row-major buffers serve directly
+    as MN-major operands and nothing is transposed.  Buffers and launch plans are cached per
+    (batch, size, p) because Shampoo calls this with the same shapes at every root update."""
+
+    _cache: Dict[Tuple[int, int, int, int], '_NewtonChainCuda'] = {}
+
+    @classmethod
+    def get(cls, b, n, p, device):
+        key = (b, n, p, device.index or 0)
+        if key not in cls._cache:
+            cls._cache[key] = cls(b, n, p, device)
+        return cls._cache[key]
+
+    def __init__(self, b, n, p, device):
+        ext = ops.extension()
+        self.ext, self.b, self.n, self.p = ext, b, n, p
+        self.squarings = p.bit_length() - 1
+        ld = (n + 7) // 8 * 8
+        self.ld = ld
+        f32 = dict(device=device, dtype=torch.float32)
+        bf16 = dict(device=device, dtype=torch.bfloat16)
+        pair = lambda: (torch.zeros(b, n, ld, **bf16), torch.zeros(b, n, ld, **bf16))  # noqa: E731
+        self.M, self.R, self.T = (torch.zeros(b, n, n, **f32) for _ in range(3))
+        self.M_new, self.R_new = torch.zeros(b, n, n, **f32), torch.zeros(b, n, n, **f32)
+        self.M_s, self.R_s, self.T_s = pair(), pair(), pair()
+        self.P_s = [pair() for _ in range(self.squarings)]     # T^2, T^4, ...
+        self.plans = []
+
+        def product(a, bb, out_f32=None, out_pair=None):
+            plan = ext.gemm_plan_new()
+            for i in range(b):
+                ah, al = a[0][i][:, :n], a[1][i][:, :n]
+                bh, bl = bb[0][i][:, :n], bb[1][i][:, :n]
+                ext.gemm_plan_add(plan, [ah, ah, al], [bh, bl, bh], False, False,
+                                  None if out_f32 is None else out_f32[i], 1.0, 0.0, False,
+                                  None if out_pair is None else out_pair[0][i],
+                                  None if out_pair is None else out_pair[1][i], 0, 0, False, [], 1)
+            ext.gemm_plan_finalize(plan)
+            self.plans.append(plan)
+            return plan
+
+        prev = self.T_s
+        self.square_plans = []
+        for k in range(self.squarings):
+            self.square_plans.append(product(prev, prev, out_pair=self.P_s[k]))
+            prev = self.P_s[k]
+        self.plan_m = product(prev, self.M_s, out_f32=self.M_new)
+        self.plan_r = product(self.R_s, self.T_s, out_f32=self.R_new)
+
+    def _split(self, src, pair):
+        self.ext.cast_pad_bf16(src.view(self.b * self.n, self.n), pair[0].view(self.b * self.n, self.ld),
+                               pair[1].view(self.b * self.n, self.ld), 1.0)
+
+    def run(self, g, z, iter_count, error_tolerance, check_every=4):
+        """g: [b, n, n] damped matrices, z: [b] scaling; returns (g)^{-1/p} as a new tensor."""
+        b, n, p = self.b, self.n, self.p
+        alpha = -1.0 / p
+        eye = torch.eye(n, device=g.device, dtype=g.dtype)
+        torch.mul(g, z.view(b, 1, 1), out=self.M)
+        self.R.copy_(eye * z.pow(1.0 / p).view(b, 1, 1))
+        error = (self.M - eye).abs().amax(dim=(1, 2))
+        active = error > error_tolerance
+        self._split(self.M, self.M_s)
+        self._split(self.R, self.R_s)
+        for it in range(iter_count):
+            torch.mul(self.M, alpha, out=self.T)
+            self.T.diagonal(dim1=1, dim2=2).add_(1 - alpha)
+            self._split(self.T, self.T_s)
+            for plan in self.square_plans:
+                self.ext.gemm_plan_run(plan)
+            self.ext.gemm_plan_run(self.plan_m)
+            self.ext.gemm_plan_run(self.plan_r)
+            new_error = (self.M_new - eye).abs().amax(dim=(1, 2))
+            grew = (new_error > error * 1.2) if it > 0 else torch.zeros_like(active)
+            # the split products carry ~2^-17 relative error: once the residual is that small and
+            # no longer shrinking quadratically, the matrix is done
+            stalled = (new_error > 0.5 * error) & (error < 1e-3) if it > 0 else torch.zeros_like(active)
+            accept = active & ~grew
+            sel = accept.view(b, 1, 1)
+            torch.where(sel, self.M_new, self.M, out=self.M)
+            torch.where(sel, self.R_new, self.R, out=self.R)
+            error = torch.where(accept, new_error, error)
+            active = accept & ~stalled & (error > error_tolerance)
+            self._split(self.M, self.M_s)
+            self._split(self.R, self.R_s)
+            if (it + 1) % check_every == 0 and not bool(active.any()):
+                break
+        return self.R.clone()
+
+
 @torch.no_grad()
 def inverse_pth_root_batched(mats, p, iter_count=100, error_tolerance=1e-6, ridge_epsilon=1e-6,
                              check_every=4):
@@ -531,6 +626,12 @@ def inverse_pth_root_batched(mats, p, iter_count=100, error_tolerance=1e-6, ridg
     lam = _power_iteration_batched(mats)
     g = mats + (ridge_epsilon * lam).view(b, 1, 1) * eye
     z = (1 + p) / (2 * torch.linalg.matrix_norm(g))
+    # The split products of the tensor-core chain carry ~2^-17 relative error, which is only
+    # harmless while the ridge keeps the spectrum well above that; smaller ridges stay in fp32.
+    if (mats.is_cuda and dtype == torch.float32 and n >= 128 and p >= 2 and (p & (p - 1)) == 0
+            and ridge_epsilon >= 1e-4 and ops.get_backend() != 'torch'):
+        chain = _NewtonChainCuda.get(b, n, p, mats.device)
+        return chain.run(g, z, iter_count, max(error_tolerance, 2e-5), check_every)
     root = eye * z.pow(1.0 / p).view(b, 1, 1)
     m = g * z.view(b, 1, 1)
     error = (m - eye).abs().amax(dim=(1, 2))

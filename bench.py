@@ -142,7 +142,7 @@ def build_ours(args, device, world):
             return model(x)
 
     def step(x, t):
-        opt.zero_grad(set_to_none=False)
+        opt.zero_grad(set_to_none=True)
         dummy = gm.setup_model_call(model_fn, x)
         gm.setup_loss_call(F.cross_entropy, dummy, t)
         _, loss = gm.forward_and_backward()
@@ -180,7 +180,7 @@ def build_reference(args, device, world):
     opt = torch.optim.SGD(model.parameters(), lr=1e-4, momentum=0.9)
 
     def step(x, t):
-        opt.zero_grad(set_to_none=False)
+        opt.zero_grad(set_to_none=True)
         dummy = gm.setup_model_call(model, x)
         gm.setup_loss_call(F.cross_entropy, dummy, t)
         _, loss = gm.forward_and_backward()

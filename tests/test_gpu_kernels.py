@@ -292,6 +292,69 @@ def test_shampoo_grouped_launches_match_per_block_path():
     ops.check_status()
 
 
+@pytest.mark.parametrize('n,p', [(192, 4), (128, 2), (200, 8)])
+def test_inverse_root_chain_on_tensor_cores(n, p):
+    """Batched coupled Newton with grouped tcgen05 products against the exact root from an
+    eigendecomposition in fp64."""
+    from asdl_b200.precondition.shampoo import inverse_pth_root_batched
+    torch.manual_seed(0)
+    a = torch.randn(3, n, 2 * n, device=DEV)
+    mats = a @ a.transpose(1, 2) / (2 * n)
+    mats[1] *= 50.0                                  # different scales in one batch
+    ext = ops.extension()
+    before = ext.launch_count()
+    roots = inverse_pth_root_batched(mats, p, ridge_epsilon=1e-4)
+    assert ext.launch_count() > before               # ran on the library's kernels
+    for m, r in zip(mats.double(), roots.double()):
+        evals, evecs = torch.linalg.eigh(m)
+        evals = evals + 1e-4 * evals.max()
+        exact = (evecs * evals.pow(-1.0 / p)) @ evecs.T
+        assert rel_err(r, exact) < 2e-3, rel_err(r, exact)
+    ops.check_status()
+
+
+@pytest.mark.parametrize('relu,residual', [(True, False), (False, True), (True, True)])
+def test_batch_norm_train_fused_activation_and_residual(ext, relu, residual):
+    torch.manual_seed(0)
+    shape, c = (8, 64, 14, 14), 64
+    cl = dict(memory_format=torch.channels_last)
+    x = (torch.randn(shape, device=DEV) * 2 + 0.7).to(torch.bfloat16).contiguous(**cl)
+    r = torch.randn(shape, device=DEV).to(torch.bfloat16).contiguous(**cl) if residual else None
+    w = (torch.rand(c, device=DEV) + 0.5).requires_grad_(True)
+    b = torch.randn(c, device=DEV).requires_grad_(True)
+    dy = torch.randn(shape, device=DEV).to(torch.bfloat16).contiguous(**cl)
+    xr = x.detach().float().requires_grad_(True)
+    rr = r.detach().float().requires_grad_(True) if residual else None
+    wr, br = w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    y_ref = F.batch_norm(xr, None, None, wr, br, True, 0.1, 1e-5)
+    if residual:
+        y_ref = y_ref + rr
+    if relu:
+        y_ref = torch.relu(y_ref)
+    y_ref.backward(dy.float())
+    xk = x.detach().requires_grad_(True)
+    rk = r.detach().requires_grad_(True) if residual else None
+    tracked = torch.zeros((), dtype=torch.long, device=DEV)
+    y, mean, invstd = ops.batch_norm_train(xk, w, b, None, None, 0.1, 1e-5, residual=rk, relu=relu,
+                                           num_batches_tracked=tracked, return_stats=True)
+    y.backward(dy)
+    assert tracked.item() == 1
+    assert rel_err(y, y_ref) < 5e-3
+    assert rel_err(w.grad, wr.grad) < 2e-3 and rel_err(b.grad, br.grad) < 2e-3
+    assert rel_err(xk.grad, xr.grad) < 8e-3
+    if residual:
+        assert rel_err(rk.grad, rr.grad) < 5e-3
+    # unit-wise curvature from (x, mean, invstd, y) against the PyTorch formulation
+    stats = torch.zeros(c, 2, 2, device=DEV)
+    ops.batchnorm_unitwise_stats_from_input(xk.detach(), dy, y.detach() if relu else None, mean, invstd, stats)
+    ops.set_backend('torch')
+    ref = ops.batchnorm_unitwise_stats_from_input(xk.detach(), dy, y.detach() if relu else None, mean, invstd,
+                                                  torch.zeros(c, 2, 2, device=DEV))
+    ops.set_backend('auto')
+    assert rel_err(stats, ref) < 1e-4
+    ops.check_status()
+
+
 def test_symmetric_segment_kernels_on_emulated_ranks(ext):
     """Pull-reduce, push-broadcast and decay kernels with three ranks emulated on one GPU."""
     from asdl_b200.parallel.symmetric import SymmetricArena

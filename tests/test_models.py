@@ -65,3 +65,35 @@ def test_resnet_tiny_kfac_reference_maker():
     cfg = asdl.PreconditioningConfig(data_size=4, damping=1e-2)
     gm = asdl.KfacGradientMaker(model, cfg, fisher_type=asdl.FISHER_EMP)
     _steps(gm, model, x, F.cross_entropy, t, n=2)
+
+
+def test_fused_resnet_blocks_match_unfused_ones():
+    """ReLUs and residual adds folded into the normalisation layers: same loss, same gradients and
+    the same K-FAC preconditioned gradients as the model with separate layers."""
+    import copy
+    torch.manual_seed(0)
+    plain = resnet_tiny(fused=False)
+    fused = resnet_tiny(fused=True)
+    fused.load_state_dict(copy.deepcopy(plain.state_dict()))
+    x, t = torch.randn(6, 3, 32, 32), torch.randint(0, 10, (6,))
+    results = []
+    for model in (plain, fused):
+        cfg = asdl.PreconditioningConfig(data_size=6, damping=1e-2)
+        gm = asdl.FusedKfacGradientMaker(model, cfg, fisher_type=asdl.FISHER_EMP)
+        d = gm.setup_model_call(model, x)
+        gm.setup_loss_call(F.cross_entropy, d, t)
+        _, loss = gm.forward_and_backward()
+        results.append((loss.item(), [p.grad.clone() for p in model.parameters()],
+                        model.layer1[0].bn3.fisher.unit.data.clone(), model.bn1.running_mean.clone()))
+    assert abs(results[0][0] - results[1][0]) < 1e-6
+    for a, b in zip(results[0][1], results[1][1]):
+        torch.testing.assert_close(a, b, rtol=2e-4, atol=1e-6)
+    torch.testing.assert_close(results[0][2], results[1][2], rtol=1e-4, atol=1e-8)
+    torch.testing.assert_close(results[0][3], results[1][3])
+    generic = asdl.KfacGradientMaker(fused, asdl.PreconditioningConfig(data_size=6, damping=1e-2),
+                                     fisher_type=asdl.FISHER_EMP)
+    d = generic.setup_model_call(fused, x)
+    generic.setup_loss_call(F.cross_entropy, d, t)
+    import pytest
+    with pytest.raises(ValueError, match='fuses an activation'):
+        generic.forward_and_backward()
