@@ -13,7 +13,7 @@ void im2col_bf16(at::Tensor x, at::Tensor out, c10::optional<at::Tensor> out_lo,
                  std::vector<int64_t> kernel, std::vector<int64_t> stride,
                  std::vector<int64_t> padding, std::vector<int64_t> dilation, bool c_major);
 void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
-                      bool b_kmajor, int64_t dst_ptr, int64_t ldc, double alpha, bool sym, bool atomic,
+                      bool b_kmajor, int64_t dst_ptr, int64_t ldc, double alpha, bool sym, int64_t atomic,
                       std::vector<int64_t> extra_ptrs, int64_t nsplit);
 int64_t gemm_plan_new();
 void gemm_plan_free(int64_t id);
@@ -40,6 +40,7 @@ void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot, i
 void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale);
 void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs);
 void symm_scale_segments(at::Tensor local, at::Tensor segs, double beta);
+void symm_mirror_lower(at::Tensor local, at::Tensor mats, int64_t n_max);
 void chol_inverse(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs, at::Tensor damping);
 }  // namespace b200
 
@@ -68,5 +69,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_reduce_segments", &b200::symm_reduce_segments);
   m.def("symm_bcast_segments", &b200::symm_bcast_segments);
   m.def("symm_scale_segments", &b200::symm_scale_segments);
+  m.def("symm_mirror_lower", &b200::symm_mirror_lower);
   m.def("chol_inverse", &b200::chol_inverse, "grouped damped SPD inverse (fp32)");
 }

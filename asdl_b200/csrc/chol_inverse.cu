@@ -10,6 +10,8 @@
 // pivot sets the status word to ERR_NOT_SPD and the factorisation continues with pivot 1.
 //
 // Everything here is fp32 on the CUDA cores (64x64x64 shared-memory tiles, 4x4 register blocks).
+#include <cstring>
+
 #include "host_utils.h"
 #include "sm100_ptx.cuh"
 
@@ -68,6 +70,17 @@ __device__ __forceinline__ void load_tile(float (*dst)[CB + 1], const float* S, 
     else
       dst[lo][hi] = val;  // src(m = hi, k = lo)
   }
+}
+
+// ---- descriptor table of a call: cached table + this call's scratch bases ---------------------
+__global__ void chol_bind_scratch_kernel(const CholMat* cached, CholMat* out, int count, float* x_base,
+                                         float* d_base) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  CholMat M = cached[i];
+  M.X = x_base + reinterpret_cast<intptr_t>(M.X);
+  M.D = d_base + reinterpret_cast<intptr_t>(M.D);
+  out[i] = M;
 }
 
 // ---- phase 0: L = A + damping * I ------------------------------------------------------------
@@ -365,11 +378,58 @@ void chol_inverse(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs, at
     d_off += static_cast<size_t>(M.nb) * CB * CB;
     nb_max = std::max(nb_max, M.nb);
   }
-  at::Tensor desc = at::empty({static_cast<int64_t>(count * sizeof(CholMat))},
-                              at::TensorOptions().dtype(at::kByte).device(at::kCUDA, dev));
-  B200_CUDA_CHECK(cudaMemcpyAsync(desc.data_ptr(), host.data(), count * sizeof(CholMat),
-                                  cudaMemcpyHostToDevice, stream));
-  at::Tensor perm_t = at::tensor(perm, at::TensorOptions().dtype(at::kLong)).to(damping.device());
+  // The descriptor table and the sort permutation depend only on the addresses and sizes of the
+  // matrices.  Callers with persistent buffers (the K-FAC state) repeat the same call, so both are
+  // cached on the device: a repeated call issues no host-to-device copy and can be captured in a
+  // CUDA graph (the scratch buffers then come from the graph's memory pool).
+  struct Prepared {
+    std::vector<const void*> key;
+    at::Tensor desc_static;   // CholMat table without the per-call scratch pointers
+    at::Tensor perm;
+  };
+  static std::mutex cache_mutex;
+  static std::vector<Prepared> cache;
+  std::vector<const void*> key;
+  key.reserve(2 * count + 1);
+  key.push_back(reinterpret_cast<const void*>(static_cast<intptr_t>(dev)));
+  for (int i = 0; i < count; ++i) {
+    key.push_back(mats[i].data_ptr());
+    key.push_back(outs[i].data_ptr());
+    key.push_back(reinterpret_cast<const void*>(static_cast<intptr_t>(mats[i].size(0))));
+    key.push_back(reinterpret_cast<const void*>(static_cast<intptr_t>(mats[i].stride(0))));
+  }
+  at::Tensor desc, perm_t;
+  {
+    std::lock_guard<std::mutex> lock(cache_mutex);
+    for (auto& p : cache)
+      if (p.key == key) {
+        desc = p.desc_static;
+        perm_t = p.perm;
+      }
+    if (!desc.defined()) {
+      // X / D are stored as offsets (in floats) from the scratch bases; the prepare kernel turns them
+      // into pointers for this call
+      std::vector<CholMat> rel = host;
+      for (int s2 = 0; s2 < count; ++s2) {
+        rel[s2].X = reinterpret_cast<float*>(static_cast<intptr_t>(host[s2].X - x_buf.data_ptr<float>()));
+        rel[s2].D = reinterpret_cast<float*>(static_cast<intptr_t>(host[s2].D - d_buf.data_ptr<float>()));
+      }
+      at::Tensor staged = at::empty({static_cast<int64_t>(count * sizeof(CholMat))},
+                                    at::TensorOptions().dtype(at::kByte).pinned_memory(true));
+      std::memcpy(staged.data_ptr(), rel.data(), count * sizeof(CholMat));
+      desc = staged.to(at::Device(at::kCUDA, dev));
+      perm_t = at::tensor(perm, at::TensorOptions().dtype(at::kLong)).to(damping.device());
+      if (cache.size() >= 16) cache.erase(cache.begin());
+      cache.push_back({key, desc, perm_t});
+    }
+  }
+  // per-call table: the cached one with the scratch bases of this call added
+  at::Tensor desc_call = at::empty_like(desc);
+  chol_bind_scratch_kernel<<<(count + 127) / 128, 128, 0, stream>>>(
+      reinterpret_cast<const CholMat*>(desc.data_ptr()), reinterpret_cast<CholMat*>(desc_call.data_ptr()), count,
+      x_buf.data_ptr<float>(), d_buf.data_ptr<float>());
+  count_launch();
+  desc = desc_call;
   damp_sorted.copy_(damping.index_select(0, perm_t));
   const CholMat* dm = reinterpret_cast<const CholMat*>(desc.data_ptr());
   int* status = device_state(dev).status.data_ptr<int>();

@@ -130,6 +130,33 @@ __global__ void symm_scale_segments_kernel(float* base, const Seg* segs, float b
   }
 }
 
+
+// upper triangle <- transpose of the lower triangle for square matrices inside the buffer
+// (segment rows: offset, n).  One block per 32x32 tile on or below the diagonal.
+__global__ void symm_mirror_lower_kernel(float* base, const Seg* mats, int tiles_max) {
+  __shared__ float tile[32][33];
+  const Seg m = mats[blockIdx.y];
+  const int n = static_cast<int>(m.numel);
+  const int nt = (n + 31) / 32;
+  const int t = blockIdx.x;
+  if (t >= nt * (nt + 1) / 2) return;
+  int r = static_cast<int>((sqrtf(8.f * t + 1.f) - 1.f) * 0.5f);
+  while ((r + 1) * (r + 2) / 2 <= t) ++r;
+  while (r * (r + 1) / 2 > t) --r;
+  const int tr = r, tc = t - r * (r + 1) / 2;  // tile row >= tile column
+  float* a = base + m.off;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int i = ty; i < 32; i += 8) {
+    const int gr = tr * 32 + i, gc = tc * 32 + tx;
+    tile[i][tx] = (gr < n && gc < n) ? a[static_cast<size_t>(gr) * n + gc] : 0.f;
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int dr = tc * 32 + i, dc = tr * 32 + tx;  // destination (row, col) = source (col, row)
+    if (dr < n && dc < n && dc > dr) a[static_cast<size_t>(dr) * n + dc] = tile[tx][i];
+  }
+}
+
 // ---- host ------------------------------------------------------------------------------------
 static void check_table(const at::Tensor& peers, int world) {
   TORCH_CHECK(peers.is_cuda() && peers.scalar_type() == at::kLong && peers.is_contiguous() &&
@@ -199,6 +226,25 @@ void symm_scale_segments(at::Tensor local, at::Tensor segs, double beta) {
   symm_scale_segments_kernel<<<grid, 256, 0, stream>>>(
       local.data_ptr<float>(), reinterpret_cast<const Seg*>(segs.data_ptr<int64_t>()),
       static_cast<float>(beta));
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
+// mats: [k, 2] rows of (element offset inside `local`, matrix size n); n_max: the largest n (host value,
+// so that the call needs no device read and can be captured in a CUDA graph).
+void symm_mirror_lower(at::Tensor local, at::Tensor mats, int64_t n_max) {
+  TORCH_CHECK(local.is_cuda() && local.scalar_type() == at::kFloat && local.is_contiguous(),
+              "local must be a contiguous fp32 CUDA tensor");
+  check_segs(mats);
+  if (mats.size(0) == 0) return;
+  TORCH_CHECK(n_max > 0, "n_max must be the largest matrix size");
+  const int nt = static_cast<int>((n_max + 31) / 32);
+  const int dev = local.get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  dim3 grid(nt * (nt + 1) / 2, static_cast<unsigned>(mats.size(0)));
+  symm_mirror_lower_kernel<<<grid, 256, 0, stream>>>(local.data_ptr<float>(),
+                                                     reinterpret_cast<const Seg*>(mats.data_ptr<int64_t>()), nt);
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch();
 }

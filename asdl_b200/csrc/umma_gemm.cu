@@ -170,7 +170,7 @@ void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, b
 // this or another GPU.  `dst_ptr` receives the result (accumulated with reductions when `atomic`),
 // `extra_ptrs` receive plain copies of it (non-atomic mode only).  All destinations use `ldc`.
 void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
-                      bool b_kmajor, int64_t dst_ptr, int64_t ldc, double alpha, bool sym, bool atomic,
+                      bool b_kmajor, int64_t dst_ptr, int64_t ldc, double alpha, bool sym, int64_t atomic,
                       std::vector<int64_t> extra_ptrs, int64_t nsplit) {
   TORCH_CHECK(!a_segs.empty(), "no operands");
   TORCH_CHECK(dst_ptr != 0 && (dst_ptr & 15) == 0, "destination must be a 16-byte aligned device address");
@@ -188,6 +188,10 @@ void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_
   P.ldc = static_cast<int>(ldc);
   TORCH_CHECK(P.ldc >= P.N, "ldc is smaller than the number of columns");
   if (atomic) P.flags |= GF_ATOMIC;
+  if (atomic == 2) {
+    TORCH_CHECK(sym, "lower-triangle reductions need the symmetric mode");
+    P.flags |= GF_LOWER;
+  }
   P.n_extra = static_cast<int>(extra_ptrs.size());
   for (int e = 0; e < P.n_extra; ++e) {
     TORCH_CHECK((extra_ptrs[e] & 15) == 0, "destinations must be 16-byte aligned");

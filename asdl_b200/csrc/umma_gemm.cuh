@@ -39,6 +39,7 @@ enum : int {
   GF_B_KMAJOR = 4,   // B given as [N, K] row-major
   GF_SAME_AB = 8,    // A and B are the same matrix (diagonal tiles load once)
   GF_ATOMIC = 16,    // C += alpha * result with reductions (C may live on another GPU); beta unused
+  GF_LOWER = 32,     // with GF_SYM | GF_ATOMIC: add the lower triangle only (the owner mirrors it later)
 };
 
 constexpr int G_MAX_EXTRA = 7;  // additional destinations of the result (peer copies)
@@ -114,7 +115,7 @@ __device__ __forceinline__ void gemm_reduce_chunk(const GemmProblem& P, const fl
       if (gc < P.N && !(sym && diag_tile && gc > gr)) red_add_f32(c + j, alpha * v[j]);
     }
   }
-  if (sym) {
+  if (sym && !(P.flags & GF_LOWER)) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const int gc = gc0 + j;

@@ -116,5 +116,10 @@ class SymmetricArena:
         """every peer's [seg] <- local[seg] (push over NVLink)."""
         ops.extension().symm_bcast_segments(self.peers_dev, self.rank, self.world, segs)
 
+    def mirror_lower(self, mats: torch.Tensor, n_max: int):
+        """For every row (offset, n) of ``mats``: the n x n matrix at ``offset`` of the local buffer
+        gets its upper triangle from its lower one."""
+        ops.extension().symm_mirror_lower(self.buffer, mats, int(n_max))
+
     def scale_segments(self, segs: torch.Tensor, beta: float):
         ops.extension().symm_scale_segments(self.buffer, segs, float(beta))

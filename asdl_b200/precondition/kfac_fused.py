@@ -218,7 +218,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         total += sum(pad(p.numel()) for p in params)
         arena = self._arena = SymmetricArena(total, group=self.sync_group, device=self.device)
         rank = self.world_rank
-        factor_segs, stage_segs, grad_segs = [], [], []
+        factor_segs, stage_segs, grad_segs, mirror_rows = [], [], [], []
         for st in self._kron:
             st.A_off, st.A = arena.alloc(st.d_in, st.d_in)
             st.B_off, st.B = arena.alloc(st.d_out, st.d_out)
@@ -226,6 +226,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             st.owner = self._owner.get(st.module, 0)
             if st.owner == rank:
                 factor_segs += [(st.A_off, st.A.numel()), (st.B_off, st.B.numel())]
+                mirror_rows += [[st.A_off, st.d_in], [st.B_off, st.d_out]]
         for st in self._norm:
             st.stage_off, st.stage = arena.alloc(*st.stats.shape)
             st.owner = self._owner.get(st.module, 0)
@@ -249,20 +250,26 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         self._rest_segs = arena.segments(rest_segs)
         self._sym_params = params
         self._factor_segs = arena.segments(factor_segs)
+        self._mirror_mats = torch.tensor(mirror_rows, dtype=torch.int64, device=self.device).reshape(-1, 2)
+        self._mirror_n_max = max([r[1] for r in mirror_rows], default=0)
         self._stage_segs = arena.segments(stage_segs)
         self._grad_segs = arena.segments(grad_segs)
 
     def _bind_grads_to_arena(self):
         """Gradients live in the symmetric arena; anything autograd allocated elsewhere is moved."""
         with torch.no_grad():
+            moved_dst, moved_src = [], []
             for p in self._sym_params:
                 _, view = self._grad_slot[p]
                 g = p.grad
                 if g is None:
                     view.zero_()
                 elif g.data_ptr() != view.data_ptr():
-                    view.copy_(g)
+                    moved_dst.append(view)
+                    moved_src.append(g)
                 p.grad = view
+            if moved_dst:
+                torch._foreach_copy_(moved_dst, moved_src)
 
     # ------------------------------------------------------------------ CUDA-graph replay
     def _tensor_slots(self):
@@ -279,7 +286,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         step = self.state['step']
         curv, prec = self.do_update_curvature(step), self.do_update_preconditioner(step)
         plain = not curv and not prec
-        kind = 'plain' if plain else ('curvature' if curv and not prec else None)
+        kind = 'plain' if plain else ('curvature' if curv and not prec else ('update' if curv and prec else None))
         ready = all(st.has_inv for st in self._kron + self._norm
                     if self.is_module_for_inv_and_precondition(st.module))
         if not (self._graph_enabled and kind is not None and ready):
@@ -300,7 +307,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             for static, (_, _, value) in zip(self._static_inputs, slots):
                 if static.data_ptr() != value.data_ptr():
                     static.copy_(value, non_blocking=True)
-        with self._phase('plain_step_graph' if plain else 'curvature_step_graph'):
+        with self._phase({'plain': 'plain_step_graph', 'curvature': 'curvature_step_graph',
+                          'update': 'update_step_graph'}[kind]):
             captured['graph'].replay()
         self.replayed_launches += captured['launches']
         for p, g in zip(self._graph_params, captured['grads']):
@@ -315,7 +323,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
 
     def _capture(self, slots, key):
         """Capture the step without updates and, where possible, the step that also measures the
-        curvature.  Both run on fresh leaf views of the parameters: autograd's gradient
+        curvature and the step that measures it and inverts.  Both run on fresh leaf views of the parameters: autograd's gradient
         accumulators remember the stream they were created on - for the real parameters that may
         be the legacy default stream, which a capture must not touch, and they stay alive as long
         as anybody holds an output of an earlier step.  Views created inside the capture get their
@@ -373,12 +381,26 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             detach_results()
             self.precondition()
 
+        def update_step():  # curvature, inverses of the owned layers, preconditioning
+            for t in float_inputs:
+                t.requires_grad_(True)
+            try:
+                self.update_curvature(views=fresh_views(), names=names, through=float_inputs or None)
+            finally:
+                for t in float_inputs:
+                    t.requires_grad_(False)
+            detach_results()
+            self.update_preconditioner()
+            self.precondition()
+
         stream = torch.cuda.Stream()
         kinds = [('plain', plain_step)]
         if self.fisher_maker.config.seed is None:
-            kinds.append(('curvature', curvature_step))
+            kinds += [('curvature', curvature_step), ('update', update_step)]
         restore = [b for b in self.model.buffers()]
-        restore += [t for st in self._kron for t in (st.A, st.B)] + [st.stats for st in self._norm]
+        restore += [t for st in self._kron for t in (st.A, st.B, st.A_inv, st.B_inv)]
+        restore += [t for st in self._norm for t in (st.stats, st.inv)]
+        restore += [t for pair in self._bf16_cache.values() for t in pair if isinstance(t, torch.Tensor)]
         pool = None
         try:
             for kind, fn in kinds:
@@ -504,7 +526,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
     def _push_factor(self, st: _KronState, t, output, alpha, is_A):
         """Statistics product of this rank added into the owner's factor through NVLink: the SYRK
         epilogue issues reductions to the owner's symmetric buffer (scaled by 1/world so that the
-        owner ends up with the average over ranks)."""
+        owner ends up with the average over ranks).  Only lower-triangular tiles travel (as 16-byte
+        vector reductions); the owner mirrors them after the barrier."""
         ext = ops.extension()
         arena = self._arena
         module = st.module
@@ -535,7 +558,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         segs_b = [segs_a[0], segs_a[2], segs_a[0]] if len(segs_a) == 3 else segs_a
         off, n_dim = (st.A_off, st.d_in) if is_A else (st.B_off, st.d_out)
         ext.umma_gemm_to_ptr(segs_a, segs_b, False, False, arena.ptr(st.owner, off), n_dim,
-                             float(scale), True, True, [], 0)
+                             float(scale), True, 2, [], 0)  # lower triangle only; the owner mirrors
 
     @staticmethod
     def _norm_statistics(st: _NormState, y, g, alpha, beta, fused=False):
@@ -637,6 +660,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         if self._arena is not None:
             alpha, beta = self._stat_weights()
             self._arena.barrier()  # every rank's tiles have landed in the owners' factors
+            if self._mirror_n_max > 0:  # ranks add lower triangles only; the owner completes the matrices
+                self._arena.mirror_lower(self._mirror_mats, self._mirror_n_max)
             self._arena.reduce_segments(self._stage_segs, 1.0 / self.world_size)
             with torch.no_grad():
                 for st in self._norm:

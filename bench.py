@@ -208,6 +208,7 @@ def main():
         return
     rank, local, world = init_distributed(args.gpus)
     device = torch.device('cuda', local)
+    torch.backends.cudnn.benchmark = True  # both arms: fixed shapes, let cuDNN pick its kernels once
     build = build_ours if args.impl == 'ours' else build_reference
     step, launches, to_device, dtype = build(args, device, world)
 

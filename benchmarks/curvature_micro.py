@@ -93,6 +93,7 @@ def main():
         f_off = [arena.alloc(n, n) for _ in range(world)]   # factor r (only the copy on rank r is used)
         y_off = [arena.alloc(n, n) for _ in range(world)]   # preconditioned gradient r (replicated)
         mine = arena.segments([(f_off[rank][0], nn_)])
+        mine_mat = torch.tensor([[f_off[rank][0], n]], dtype=torch.int64, device=dev)
         inv = torch.empty(n, n, device=dev)
         ld = (n + 7) // 8 * 8
         mk = lambda: torch.empty(n, ld, device=dev, dtype=torch.bfloat16)  # noqa: E731
@@ -105,8 +106,9 @@ def main():
             arena.barrier()
             for r in range(world):
                 ext.umma_gemm_to_ptr([a], [a], False, False, arena.ptr(r, f_off[r][0]), n, 1.0 / (B * world),
-                                     True, True, [], 0)
+                                     True, 2, [], 0)   # lower triangle only over the wire
             arena.barrier()
+            arena.mirror_lower(mine_mat, n)
             ops.spd_inverse_grouped([f_off[rank][1]], [inv], damp)
             ext.cast_pad_bf16(inv, i_hi, i_lo, 1.0)
             ext.cast_pad_bf16(grad, g_hi, g_lo, 1.0)

@@ -397,6 +397,15 @@ def test_gemm_epilogue_reduces_into_and_replicates_to_other_buffers(ext):
     for _ in range(2):  # two ranks' contributions
         ext.umma_gemm_to_ptr([x], [x], False, False, target.data_ptr(), 200, 0.5, True, True, [], 0)
     assert rel_err(target, held + ref) < 1e-4
+    # lower-triangle-only reductions (what travels between GPUs) completed by a local mirror pass
+    from asdl_b200.parallel.symmetric import SymmetricArena
+    arena = SymmetricArena.local_group(200 * 200 + 64, 1)[0]
+    off, fac = arena.alloc(200, 200)
+    for _ in range(2):
+        ext.umma_gemm_to_ptr([x], [x], False, False, arena.ptr(0, off), 200, 0.5, True, 2, [], 0)
+    assert rel_err(torch.tril(fac), torch.tril(ref)) < 1e-4 and torch.triu(fac, 1).abs().max() == 0
+    arena.mirror_lower(torch.tensor([[off, 200]], dtype=torch.int64, device=DEV), 200)
+    assert rel_err(fac, ref) < 1e-4 and torch.equal(fac, fac.T)
     a = torch.randn(96, 160, device=DEV).to(torch.bfloat16)   # [K, M]
     b = torch.randn(96, 72, device=DEV).to(torch.bfloat16)    # [K, N]
     outs = [torch.zeros(160, 72, device=DEV) for _ in range(4)]
