@@ -4,7 +4,7 @@ import torch.nn as nn
 
 from .. import ops
 
-__all__ = ['FusedBatchNorm2d']
+__all__ = ['FusedBatchNorm2d', 'grouped_bf16_weights']
 
 
 class FusedBatchNorm2d(nn.BatchNorm2d):
@@ -71,3 +71,77 @@ class FusedBatchNorm2d(nn.BatchNorm2d):
 
     def extra_repr(self):
         return super().extra_repr() + (f', act={self.act}' if self.act else '')
+
+
+class _GroupedCast(torch.autograd.Function):
+    """fp32 parameters -> bf16 copies that live in one flat buffer (a few multi-tensor launches
+    instead of one cast kernel per parameter); the backward pass converts the bf16 gradients back to
+    fp32 the same way.  Every copy keeps the memory format of its parameter."""
+
+    @staticmethod
+    def forward(ctx, *weights):
+        total = sum((w.numel() + 7) // 8 * 8 for w in weights)
+        flat = torch.empty(total, device=weights[0].device, dtype=torch.bfloat16)
+        outs, off = [], 0
+        for w in weights:
+            chunk = flat[off:off + w.numel()]
+            off += (w.numel() + 7) // 8 * 8
+            outs.append(chunk.as_strided(w.shape, w.stride()) if w.is_contiguous() or _dense(w)
+                        else chunk.view(w.shape))
+        torch._foreach_copy_(outs, [w.detach() for w in weights])
+        ctx.meta = [(w.shape, w.stride()) for w in weights]
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        present = [(i, g) for i, g in enumerate(grads) if g is not None]
+        outs = [None] * len(grads)
+        if present:
+            dst = [torch.empty_strided(ctx.meta[i][0], ctx.meta[i][1], device=g.device, dtype=torch.float32)
+                   if _dense_meta(*ctx.meta[i]) else torch.empty(ctx.meta[i][0], device=g.device, dtype=torch.float32)
+                   for i, g in present]
+            torch._foreach_copy_(dst, [g for _, g in present])
+            for (i, _), d in zip(present, dst):
+                outs[i] = d
+        return tuple(outs)
+
+
+def _dense_meta(shape, stride):
+    """True when (shape, stride) covers exactly numel elements without gaps (any dimension order)."""
+    expected = 1
+    for size, st in sorted(((s, t) for s, t in zip(shape, stride) if s > 1), key=lambda p: p[1]):
+        if st != expected:
+            return False
+        expected *= size
+    return True
+
+
+def _dense(t):
+    return _dense_meta(t.shape, t.stride())
+
+
+class grouped_bf16_weights:
+    """Context manager: inside it, the ``weight`` of every Conv2d / Linear of ``model`` is a bf16 copy
+    made by one grouped cast (differentiable), so autocast finds nothing left to convert."""
+
+    def __init__(self, model):
+        self.model = model
+
+    def __enter__(self):
+        from torch.nn.utils.stateless import _reparametrize_module
+        names, weights = [], []
+        for name, module in self.model.named_modules():
+            if isinstance(module, (nn.Conv2d, nn.Linear)) and module.weight.dtype == torch.float32:
+                names.append(f'{name}.weight' if name else 'weight')
+                weights.append(module.weight)
+        self._ctx = None
+        if weights:
+            casts = _GroupedCast.apply(*weights)
+            self._ctx = _reparametrize_module(self.model, dict(zip(names, casts)))
+            self._ctx.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self._ctx is not None:
+            self._ctx.__exit__(*exc)
+        return False

@@ -5,7 +5,7 @@ and the module runs in channels_last / bf16 autocast without layout changes betw
 import torch
 import torch.nn as nn
 
-from .layers import FusedBatchNorm2d
+from .layers import FusedBatchNorm2d, grouped_bf16_weights
 
 __all__ = ['ResNet', 'Bottleneck', 'resnet50', 'resnet_tiny']
 
@@ -75,6 +75,12 @@ class ResNet(nn.Module):
         return nn.Sequential(*layers)
 
     def forward(self, x):
+        if self.fused and x.is_cuda and torch.is_autocast_enabled('cuda') and torch.get_autocast_dtype('cuda') == torch.bfloat16:
+            with grouped_bf16_weights(self):  # one grouped cast instead of one cast kernel per layer
+                return self._forward(x)
+        return self._forward(x)
+
+    def _forward(self, x):
         x = self.bn1(self.conv1(x))
         x = self.maxpool(x if self.fused else self.relu(x))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))

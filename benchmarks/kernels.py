@@ -133,9 +133,33 @@ def bench_im2col(timer, n, c, hw, k, stride, pad, hbm, flops_peak, src):
          gbs=round(by / ms / 1e6, 1), frac_of_peak_hbm=round(by / (ms * 1e-3) / hbm, 3), peak_source=src)
 
 
+def bench_batchnorm(timer, n, c, hw, hbm, flops_peak, src):
+    """Training BatchNorm forward + backward on NHWC bf16 (fused ReLU) against F.batch_norm + relu."""
+    import torch.nn.functional as F
+    cl = dict(memory_format=torch.channels_last)
+    x = torch.randn(n, c, hw, hw, device='cuda').to(torch.bfloat16).contiguous(**cl).requires_grad_(True)
+    dy = torch.randn(n, c, hw, hw, device='cuda').to(torch.bfloat16).contiguous(**cl)
+    w = torch.ones(c, device='cuda', requires_grad=True)
+    b = torch.zeros(c, device='cuda', requires_grad=True)
+
+    def ours():
+        y = ops.batch_norm_train(x, w, b, None, None, 0.1, 1e-5, relu=True)
+        torch.autograd.grad(y, (x, w, b), dy)
+
+    def lib():
+        y = torch.relu(F.batch_norm(x, None, None, w, b, True, 0.1, 1e-5))
+        torch.autograd.grad(y, (x, w, b), dy)
+    ms, ms_lib = timer(ours), timer(lib)
+    numel = n * c * hw * hw
+    by = 2.0 * numel * (3 + 7)           # fwd 3 passes; bwd sums (x, dy, y) + dx (dy, x, y, write)
+    emit(case='batchnorm_relu_train_fwd_bwd_nhwc_bf16', shape=[n, c, hw, hw], ms=round(ms, 4),
+         gbs=round(by / ms / 1e6, 1), frac_of_peak_hbm=round(by / (ms * 1e-3) / hbm, 3), peak_source=src,
+         torch_ms=round(ms_lib, 4), speedup_vs_torch=round(ms_lib / ms, 2))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--only', default=None, choices=['syrk', 'syrk_x3', 'precond', 'inverse', 'im2col'])
+    ap.add_argument('--only', default=None, choices=['syrk', 'syrk_x3', 'precond', 'inverse', 'im2col', 'batchnorm'])
     ap.add_argument('--rows', type=int, default=None)
     ap.add_argument('--n', type=int, default=None)
     ap.add_argument('--iters', type=int, default=10)
@@ -163,6 +187,9 @@ def main():
     if want('im2col'):
         bench_im2col(timer, 32, 64, 56, 3, 1, 1, hbm, fl, src)
         bench_im2col(timer, 32, 256, 14, 3, 1, 1, hbm, fl, src)
+    if want('batchnorm'):
+        for n, c, hw in [(32, 64, 112), (32, 256, 56), (32, 512, 28), (32, 1024, 14), (32, 2048, 7)]:
+            bench_batchnorm(timer, n, c, hw, hbm, fl, src)
     ops.check_status()
 
 

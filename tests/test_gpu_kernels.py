@@ -355,6 +355,36 @@ def test_batch_norm_train_fused_activation_and_residual(ext, relu, residual):
     ops.check_status()
 
 
+def test_fused_resnet_under_autocast_matches_unfused_model():
+    """Fused normalisation / activation / residual kernels plus the grouped weight cast against
+    the same network made of separate PyTorch layers (bf16 autocast, channels_last)."""
+    from asdl_b200.models import resnet_tiny
+    torch.manual_seed(0)
+    plain = resnet_tiny(width=16, fused=False).to(DEV).to(memory_format=torch.channels_last)
+    fused = resnet_tiny(width=16, fused=True).to(DEV).to(memory_format=torch.channels_last)
+    fused.load_state_dict(copy.deepcopy(plain.state_dict()))
+    x = torch.randn(8, 3, 64, 64, device=DEV).contiguous(memory_format=torch.channels_last)
+    t = torch.randint(0, 10, (8,), device=DEV)
+    grads = []
+    for model in (plain, fused):
+        with torch.autocast('cuda', dtype=torch.bfloat16):
+            loss = F.cross_entropy(model(x), t)
+        loss.backward()
+        grads.append((loss.item(), [p.grad.float().clone() for p in model.parameters()]))
+        assert all(p.grad.dtype == torch.float32 and p.grad.shape == p.shape for p in model.parameters())
+    assert abs(grads[0][0] - grads[1][0]) < 5e-2, (grads[0][0], grads[1][0])
+    # both networks round to bf16 at different places (the fused kernels round once after the
+    # residual add and the ReLU), so compare directions and overall size rather than digits
+    flat_a = torch.cat([g.flatten() for g in grads[0][1]])
+    flat_b = torch.cat([g.flatten() for g in grads[1][1]])
+    cosine = F.cosine_similarity(flat_a, flat_b, dim=0).item()
+    assert cosine > 0.98, cosine
+    assert 0.8 < (flat_b.norm() / flat_a.norm()).item() < 1.25
+    assert torch.allclose(plain.bn1.running_mean, fused.bn1.running_mean, atol=2e-3), \
+        (plain.bn1.running_mean - fused.bn1.running_mean).abs().max().item()
+    assert plain.bn1.num_batches_tracked.item() == fused.bn1.num_batches_tracked.item() == 1
+
+
 def test_symmetric_segment_kernels_on_emulated_ranks(ext):
     """Pull-reduce, push-broadcast and decay kernels with three ranks emulated on one GPU."""
     from asdl_b200.parallel.symmetric import SymmetricArena
