@@ -41,6 +41,8 @@ void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Ten
 void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs);
 void symm_scale_segments(at::Tensor local, at::Tensor segs, double beta);
 void symm_mirror_lower(at::Tensor local, at::Tensor mats, int64_t n_max);
+void symm_reduce_slots(at::Tensor local, at::Tensor table, int64_t world, int64_t slot_stride, int64_t n_max,
+                       double beta);
 void chol_inverse(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs, at::Tensor damping);
 }  // namespace b200
 
@@ -70,5 +72,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_bcast_segments", &b200::symm_bcast_segments);
   m.def("symm_scale_segments", &b200::symm_scale_segments);
   m.def("symm_mirror_lower", &b200::symm_mirror_lower);
+  m.def("symm_reduce_slots", &b200::symm_reduce_slots);
   m.def("chol_inverse", &b200::chol_inverse, "grouped damped SPD inverse (fp32)");
 }

@@ -12,6 +12,9 @@
 //   symm_bcast_segments   the calling rank stores the listed segments into every peer's copy
 //                         (broadcast-from-owner of preconditioned gradients).
 //   symm_scale_segments   local beta-scaling of segments (moving-average decay of owned factors).
+//   symm_reduce_slots     owner-side sum of the per-rank slots that the peers' SYRK epilogues stored
+//                         into (lower triangles), folded into the running factor and mirrored.
+//   symm_mirror_lower     upper triangle <- lower triangle of local matrices.
 //
 // The first SYMM_FLAG_WORDS 32-bit words of the symmetric buffer are reserved for the barrier
 // slots: word [s * 64 + r] of rank q is "rank r has reached epoch of barrier stream s"; word
@@ -157,6 +160,48 @@ __global__ void symm_mirror_lower_kernel(float* base, const Seg* mats, int tiles
   }
 }
 
+// Owner-side reduction of per-rank slots into a running factor, for square matrices:
+//   F <- beta * F + sum_r slot_r     on the lower triangle, mirrored into the upper one.
+// Row t of `table`: (offset of F, offset of slot 0, n); slot r starts `slot_stride` elements after
+// slot r-1.  Everything is local memory: the peers stored their lower-triangular tiles into the
+// slots with plain (coalesced) stores from their SYRK epilogues.
+struct SlotRow {
+  long long f_off, slot_off, n;
+};
+
+__global__ void symm_reduce_slots_kernel(float* base, const SlotRow* table, int world, long long slot_stride,
+                                         float beta) {
+  __shared__ float tile[32][33];
+  const SlotRow m = table[blockIdx.y];
+  const int n = static_cast<int>(m.n);
+  const int nt = (n + 31) / 32;
+  const int t = blockIdx.x;
+  if (t >= nt * (nt + 1) / 2) return;
+  int r = static_cast<int>((sqrtf(8.f * t + 1.f) - 1.f) * 0.5f);
+  while ((r + 1) * (r + 2) / 2 <= t) ++r;
+  while (r * (r + 1) / 2 > t) --r;
+  const int tr = r, tc = t - r * (r + 1) / 2;  // tile row >= tile column
+  float* f = base + m.f_off;
+  const float* slot0 = base + m.slot_off;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int i = ty; i < 32; i += 8) {
+    const int gr = tr * 32 + i, gc = tc * 32 + tx;
+    float v = 0.f;
+    if (gr < n && gc < n && gc <= gr) {
+      const size_t idx = static_cast<size_t>(gr) * n + gc;
+      for (int q = 0; q < world; ++q) v += slot0[q * slot_stride + idx];
+      if (beta != 0.f) v = fmaf(beta, f[idx], v);
+      f[idx] = v;
+    }
+    tile[i][tx] = v;
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int dr = tc * 32 + i, dc = tr * 32 + tx;  // destination (row, col) = source (col, row)
+    if (dr < n && dc < n && dc > dr) f[static_cast<size_t>(dr) * n + dc] = tile[tx][i];
+  }
+}
+
 // ---- host ------------------------------------------------------------------------------------
 static void check_table(const at::Tensor& peers, int world) {
   TORCH_CHECK(peers.is_cuda() && peers.scalar_type() == at::kLong && peers.is_contiguous() &&
@@ -245,6 +290,27 @@ void symm_mirror_lower(at::Tensor local, at::Tensor mats, int64_t n_max) {
   dim3 grid(nt * (nt + 1) / 2, static_cast<unsigned>(mats.size(0)));
   symm_mirror_lower_kernel<<<grid, 256, 0, stream>>>(local.data_ptr<float>(),
                                                      reinterpret_cast<const Seg*>(mats.data_ptr<int64_t>()), nt);
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
+// table: [k, 3] rows of (offset of the factor, offset of slot 0, n) inside `local`.
+void symm_reduce_slots(at::Tensor local, at::Tensor table, int64_t world, int64_t slot_stride, int64_t n_max,
+                       double beta) {
+  TORCH_CHECK(local.is_cuda() && local.scalar_type() == at::kFloat && local.is_contiguous(),
+              "local must be a contiguous fp32 CUDA tensor");
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.is_contiguous() && table.dim() == 2 &&
+                  table.size(1) == 3, "table must be a CUDA int64 [k, 3] tensor");
+  if (table.size(0) == 0) return;
+  TORCH_CHECK(n_max > 0 && world > 0, "bad arguments");
+  const int nt = static_cast<int>((n_max + 31) / 32);
+  const int dev = local.get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  dim3 grid(nt * (nt + 1) / 2, static_cast<unsigned>(table.size(0)));
+  symm_reduce_slots_kernel<<<grid, 256, 0, stream>>>(local.data_ptr<float>(),
+                                                     reinterpret_cast<const SlotRow*>(table.data_ptr<int64_t>()),
+                                                     static_cast<int>(world), slot_stride, static_cast<float>(beta));
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch();
 }

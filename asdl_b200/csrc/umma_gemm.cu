@@ -175,7 +175,8 @@ void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_
   TORCH_CHECK(!a_segs.empty(), "no operands");
   TORCH_CHECK(dst_ptr != 0 && (dst_ptr & 15) == 0, "destination must be a 16-byte aligned device address");
   TORCH_CHECK(static_cast<int>(extra_ptrs.size()) <= G_MAX_EXTRA, "too many extra destinations");
-  TORCH_CHECK(!(atomic && !extra_ptrs.empty()), "extra destinations are not supported in atomic mode");
+  TORCH_CHECK(!((atomic == 1 || atomic == 2) && !extra_ptrs.empty()),
+              "extra destinations are not supported in atomic mode");
   const int dev = a_segs[0].get_device();
   c10::cuda::CUDAGuard guard(dev);
   const int n_sms = at::cuda::getDeviceProperties(dev)->multiProcessorCount;
@@ -187,9 +188,9 @@ void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_
   P.Cin = P.C;
   P.ldc = static_cast<int>(ldc);
   TORCH_CHECK(P.ldc >= P.N, "ldc is smaller than the number of columns");
-  if (atomic) P.flags |= GF_ATOMIC;
-  if (atomic == 2) {
-    TORCH_CHECK(sym, "lower-triangle reductions need the symmetric mode");
+  if (atomic == 1 || atomic == 2) P.flags |= GF_ATOMIC;
+  if (atomic == 2 || atomic == 3) {
+    TORCH_CHECK(sym, "lower-triangle output needs the symmetric mode");
     P.flags |= GF_LOWER;
   }
   P.n_extra = static_cast<int>(extra_ptrs.size());

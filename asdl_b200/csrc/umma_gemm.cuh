@@ -39,7 +39,7 @@ enum : int {
   GF_B_KMAJOR = 4,   // B given as [N, K] row-major
   GF_SAME_AB = 8,    // A and B are the same matrix (diagonal tiles load once)
   GF_ATOMIC = 16,    // C += alpha * result with reductions (C may live on another GPU); beta unused
-  GF_LOWER = 32,     // with GF_SYM | GF_ATOMIC: add the lower triangle only (the owner mirrors it later)
+  GF_LOWER = 32,     // with GF_SYM: write / add the lower triangle only (the owner of the matrix mirrors it)
 };
 
 constexpr int G_MAX_EXTRA = 7;  // additional destinations of the result (peer copies)
@@ -179,9 +179,11 @@ __device__ __forceinline__ void gemm_store_chunk(const GemmProblem& P, const flo
         for (int j = 0; j < 32; ++j)
           if (gc0 + j < P.N) c[j] = out[j];
       }
+      if (!(P.flags & GF_LOWER)) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (gc0 + j < P.N) P.C[static_cast<size_t>(gc0 + j) * P.ldc + gr] = out[j];
+        for (int j = 0; j < 32; ++j)
+          if (gc0 + j < P.N) P.C[static_cast<size_t>(gc0 + j) * P.ldc + gr] = out[j];
+      }
     } else {
       // diagonal tile: keep the lower triangle, mirror it so the result is exactly symmetric
 #pragma unroll
@@ -189,7 +191,7 @@ __device__ __forceinline__ void gemm_store_chunk(const GemmProblem& P, const flo
         const int gc = gc0 + j;
         if (gc <= gr && gc < P.N) {
           c[j] = out[j];
-          if (gc < gr) P.C[static_cast<size_t>(gc) * P.ldc + gr] = out[j];
+          if (gc < gr && !(P.flags & GF_LOWER)) P.C[static_cast<size_t>(gc) * P.ldc + gr] = out[j];
         }
       }
     }
@@ -497,7 +499,7 @@ splitk_reduce_kernel(const __grid_constant__ GemmProblem single, const GemmProbl
       }
     }
   }
-  if (!sym || P.C == nullptr) return;
+  if (!sym || P.C == nullptr || (P.flags & GF_LOWER)) return;
   __syncthreads();
   // mirrored store: element (r, c) of the patch goes to C[c][r]
 #pragma unroll

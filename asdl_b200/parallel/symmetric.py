@@ -121,5 +121,12 @@ class SymmetricArena:
         gets its upper triangle from its lower one."""
         ops.extension().symm_mirror_lower(self.buffer, mats, int(n_max))
 
+    def reduce_slots(self, table: torch.Tensor, slot_stride: int, n_max: int, beta: float):
+        """For every row (factor offset, offset of slot 0, n) of ``table``: the local n x n factor
+        becomes ``beta * factor + sum over ranks of its slots`` (lower triangles, mirrored); slot r
+        lies ``r * slot_stride`` elements after slot 0.  Peers fill the slots with the stores of
+        their SYRK epilogues; this reduction reads local memory only."""
+        ops.extension().symm_reduce_slots(self.buffer, table, self.world, int(slot_stride), int(n_max), float(beta))
+
     def scale_segments(self, segs: torch.Tensor, beta: float):
         ops.extension().symm_scale_segments(self.buffer, segs, float(beta))

@@ -108,10 +108,11 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         grouped: apply the inverses of all layers with grouped launches (one staging kernel and
             two GEMM launches for the whole model) instead of a few launches per layer.
         comm: data-parallel transport.  ``'symmetric'`` keeps factors and gradients in NVLink
-            symmetric memory and uses the library's own kernels: the statistics SYRKs add their
-            tiles straight into the owner's factor (reductions over NVLink from the MMA
-            epilogue), owners pull-reduce the gradients of their layers, and the preconditioning
-            GEMM's epilogue stores its result into every rank's gradient buffer.  ``'torch'`` uses
+            symmetric memory and uses the library's own kernels: the statistics SYRKs store their
+            lower-triangular tiles straight into per-rank slots on the owner (peer stores from the
+            MMA epilogue; the owner sums its slots into the running factor), owners pull-reduce
+            the gradients of their layers, and the preconditioning GEMM's epilogue stores its
+            result into every rank's gradient buffer.  ``'torch'`` uses
             ``torch.distributed`` collectives (any backend).  ``'auto'`` picks ``'symmetric'``
             for multi-rank CUDA runs.
     Embedding layers are not handled here; list them in ``config.ignore_modules``.
@@ -216,9 +217,20 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         total = sum(pad(st.A.numel()) + pad(st.B.numel()) for st in self._kron)
         total += sum(pad(st.stats.numel()) for st in self._norm)
         total += sum(pad(p.numel()) for p in params)
+        # per-rank slots that the peers' SYRK epilogues store their (lower-triangular) statistics
+        # into: every owner needs world x (size of its factors); the symmetric region is sized for
+        # the largest owner and every rank can compute every owner's layout
+        owned_total = [0] * self.world_size
+        for st in self._kron:
+            o = self._owner.get(st.module, 0)
+            st.slot_rel = (owned_total[o], owned_total[o] + pad(st.A.numel()))
+            owned_total[o] += pad(st.A.numel()) + pad(st.B.numel())
+        self._slot_stride = max(owned_total + [64])
+        total += self.world_size * self._slot_stride + 64
         arena = self._arena = SymmetricArena(total, group=self.sync_group, device=self.device)
         rank = self.world_rank
-        factor_segs, stage_segs, grad_segs, mirror_rows = [], [], [], []
+        self._slots_off, _ = arena.alloc(self.world_size * self._slot_stride)
+        factor_segs, stage_segs, grad_segs, mirror_rows, slot_rows = [], [], [], [], []
         for st in self._kron:
             st.A_off, st.A = arena.alloc(st.d_in, st.d_in)
             st.B_off, st.B = arena.alloc(st.d_out, st.d_out)
@@ -227,6 +239,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             if st.owner == rank:
                 factor_segs += [(st.A_off, st.A.numel()), (st.B_off, st.B.numel())]
                 mirror_rows += [[st.A_off, st.d_in], [st.B_off, st.d_out]]
+                slot_rows += [[st.A_off, self._slots_off + st.slot_rel[0], st.d_in],
+                              [st.B_off, self._slots_off + st.slot_rel[1], st.d_out]]
         for st in self._norm:
             st.stage_off, st.stage = arena.alloc(*st.stats.shape)
             st.owner = self._owner.get(st.module, 0)
@@ -252,6 +266,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         self._factor_segs = arena.segments(factor_segs)
         self._mirror_mats = torch.tensor(mirror_rows, dtype=torch.int64, device=self.device).reshape(-1, 2)
         self._mirror_n_max = max([r[1] for r in mirror_rows], default=0)
+        self._slot_table = torch.tensor(slot_rows, dtype=torch.int64, device=self.device).reshape(-1, 3)
         self._stage_segs = arena.segments(stage_segs)
         self._grad_segs = arena.segments(grad_segs)
 
@@ -524,10 +539,11 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         return handles, state
 
     def _push_factor(self, st: _KronState, t, output, alpha, is_A):
-        """Statistics product of this rank added into the owner's factor through NVLink: the SYRK
-        epilogue issues reductions to the owner's symmetric buffer (scaled by 1/world so that the
-        owner ends up with the average over ranks).  Only lower-triangular tiles travel (as 16-byte
-        vector reductions); the owner mirrors them after the barrier."""
+        """Statistics product of this rank sent to the owner of the factor through NVLink: the SYRK
+        epilogue stores its lower-triangular tiles (scaled by 1/world) straight into this rank's
+        slot in the owner's symmetric buffer; after the barrier the owner sums its slots into the
+        running factor (moving average folded in) and mirrors the result.  Deterministic, and the
+        wire carries plain 16-byte stores."""
         ext = ops.extension()
         arena = self._arena
         module = st.module
@@ -556,9 +572,11 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             hi, lo = ops._stage_bf16(rows2d, ops._use_x3(rows2d.dtype))
             segs_a = [hi, hi, lo] if lo is not None else [hi]
         segs_b = [segs_a[0], segs_a[2], segs_a[0]] if len(segs_a) == 3 else segs_a
-        off, n_dim = (st.A_off, st.d_in) if is_A else (st.B_off, st.d_out)
+        n_dim = st.d_in if is_A else st.d_out
+        off = self._slots_off + self.world_rank * self._slot_stride + st.slot_rel[0 if is_A else 1]
+        # plain (coalesced) stores of the lower-triangular tiles into this rank's slot on the owner
         ext.umma_gemm_to_ptr(segs_a, segs_b, False, False, arena.ptr(st.owner, off), n_dim,
-                             float(scale), True, 2, [], 0)  # lower triangle only; the owner mirrors
+                             float(scale), True, 3, [], 0)
 
     @staticmethod
     def _norm_statistics(st: _NormState, y, g, alpha, beta, fused=False):
@@ -598,10 +616,6 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         handles, state = self._install_hooks()
         if cfg is not None and self.fisher_maker.config.seed is not None:
             torch.random.manual_seed(self.fisher_maker.config.seed)
-        if self._arena is not None:
-            # owners decay their factors; nobody may add before every owner has done so
-            self._arena.scale_segments(self._factor_segs, self._stat_weights()[1])
-            self._arena.barrier()
 
         def backward(loss_, retain=False):
             if views is None:
@@ -659,14 +673,15 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         self._loss = loss
         if self._arena is not None:
             alpha, beta = self._stat_weights()
-            self._arena.barrier()  # every rank's tiles have landed in the owners' factors
-            if self._mirror_n_max > 0:  # ranks add lower triangles only; the owner completes the matrices
-                self._arena.mirror_lower(self._mirror_mats, self._mirror_n_max)
+            self._arena.barrier()  # every rank's tiles have landed in the owners' slots
+            if self._mirror_n_max > 0:  # running factor <- beta * factor + sum of the slots, mirrored
+                self._arena.reduce_slots(self._slot_table, self._slot_stride, self._mirror_n_max, beta)
             self._arena.reduce_segments(self._stage_segs, 1.0 / self.world_size)
             with torch.no_grad():
-                for st in self._norm:
-                    if st.owner == self.world_rank:
-                        st.stats.mul_(beta).add_(st.stage, alpha=alpha)
+                mine = [st for st in self._norm if st.owner == self.world_rank]
+                if mine:
+                    torch._foreach_mul_([st.stats for st in mine], beta)
+                    torch._foreach_add_([st.stats for st in mine], [st.stage for st in mine], alpha=alpha)
         elif self.world_size > 1:
             self._reduce_staged_statistics()
 

@@ -8,8 +8,9 @@ rank holds activations a [B, n] (bf16, N(0,1)) and contributes a^T a / (B W) to 
 owner adds damping, inverts in fp32 and applies the inverse to an n x n gradient; every rank ends
 up with all W preconditioned gradients.
 
-  fused    SYRK whose epilogue adds its tiles into the owner's factor over NVLink (compute +
-           reduce-to-owner in one kernel), bounded flag barrier, grouped Cholesky inverse,
+  fused    SYRK whose epilogue stores its lower-triangular tiles into this rank's slot on the
+           owner over NVLink (compute + send in one kernel), bounded flag barrier, owner-side sum
+           of the slots, grouped Cholesky inverse,
            tcgen05 GEMM whose epilogue stores the result into every rank's buffer (compute +
            all-gather in one kernel).
   library  torch.matmul (cuBLAS, fp32 output) + dist.all_reduce (NCCL) + torch.linalg.cholesky /
@@ -89,11 +90,11 @@ def main():
         a = torch.randn(B, n, device=dev).to(torch.bfloat16)
         grad = torch.randn(n, n, device=dev)
         nn_ = n * n
-        arena = SymmetricArena(2 * world * nn_ + 1024) if world > 1 else SymmetricArena.local_group(2 * nn_ + 1024, 1)[0]
+        arena = SymmetricArena(3 * world * nn_ + 1024) if world > 1 else SymmetricArena.local_group(3 * nn_ + 1024, 1)[0]
         f_off = [arena.alloc(n, n) for _ in range(world)]   # factor r (only the copy on rank r is used)
+        slots_off, _ = arena.alloc(world, n, n)             # slot q: the statistics that rank q stored here
         y_off = [arena.alloc(n, n) for _ in range(world)]   # preconditioned gradient r (replicated)
-        mine = arena.segments([(f_off[rank][0], nn_)])
-        mine_mat = torch.tensor([[f_off[rank][0], n]], dtype=torch.int64, device=dev)
+        slot_table = torch.tensor([[f_off[rank][0], slots_off, n]], dtype=torch.int64, device=dev)
         inv = torch.empty(n, n, device=dev)
         ld = (n + 7) // 8 * 8
         mk = lambda: torch.empty(n, ld, device=dev, dtype=torch.bfloat16)  # noqa: E731
@@ -102,13 +103,12 @@ def main():
         peers_y = [arena.ptr(r, y_off[rank][0]) for r in range(world) if r != rank]
 
         def fused():
-            arena.scale_segments(mine, 0.0)
+            for k in range(world):  # staggered: at any time every owner receives from one peer
+                r = (rank + 1 + k) % world
+                ext.umma_gemm_to_ptr([a], [a], False, False, arena.ptr(r, slots_off + rank * nn_), n,
+                                     1.0 / (B * world), True, 3, [], 0)   # lower-triangular tiles, plain stores
             arena.barrier()
-            for r in range(world):
-                ext.umma_gemm_to_ptr([a], [a], False, False, arena.ptr(r, f_off[r][0]), n, 1.0 / (B * world),
-                                     True, 2, [], 0)   # lower triangle only over the wire
-            arena.barrier()
-            arena.mirror_lower(mine_mat, n)
+            arena.reduce_slots(slot_table, nn_, n, 0.0)
             ops.spd_inverse_grouped([f_off[rank][1]], [inv], damp)
             ext.cast_pad_bf16(inv, i_hi, i_lo, 1.0)
             ext.cast_pad_bf16(grad, g_hi, g_lo, 1.0)
