@@ -287,6 +287,9 @@ def main():
     barrier(world)
     e2e_s = time.perf_counter() - t0
 
+    if args.impl == 'ours':  # a kernel that gave up on a wait (peer barrier, pipeline stage) reports it here
+        import asdl_b200
+        asdl_b200.ops.check_status()
     times = torch.tensor([ms, e2e_s * 1e3], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)

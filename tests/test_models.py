@@ -97,3 +97,26 @@ def test_fused_resnet_blocks_match_unfused_ones():
     import pytest
     with pytest.raises(ValueError, match='fuses an activation'):
         generic.forward_and_backward()
+
+
+def test_grouped_bf16_weight_cast_is_transparent():
+    """One grouped cast of all Conv2d / Linear weights gives the same outputs and fp32 gradients
+    (in the parameters' own memory format) as autocast's per-layer casts."""
+    import copy
+    from asdl_b200.models.layers import grouped_bf16_weights
+    torch.manual_seed(0)
+    a = resnet_tiny(fused=True).to(memory_format=torch.channels_last)
+    b = copy.deepcopy(a)
+    x = torch.randn(2, 3, 32, 32)
+    with torch.autocast('cpu', dtype=torch.bfloat16):
+        with grouped_bf16_weights(a):
+            assert a.conv1.weight.dtype == torch.bfloat16 and a.conv1.weight.stride() == b.conv1.weight.stride()
+            ya = a._forward(x)
+        yb = b._forward(x)
+    assert a.conv1.weight.dtype == torch.float32          # restored
+    torch.testing.assert_close(ya, yb)
+    ya.float().sum().backward()
+    yb.float().sum().backward()
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        assert pa.grad.dtype == torch.float32 and pa.grad.stride() == pb.grad.stride()
+        torch.testing.assert_close(pa.grad, pb.grad, rtol=2e-2, atol=1e-3 * pb.grad.abs().max().item())
