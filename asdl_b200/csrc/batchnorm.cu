@@ -23,7 +23,7 @@ namespace {
 constexpr int GROUPS = 8;    // channel groups of 8 channels per CTA -> 64 channels
 constexpr int LANES = 32;    // row lanes per CTA
 constexpr int THREADS = GROUPS * LANES;
-constexpr int UNROLL = 4;    // independent 16-byte loads in flight per thread and tensor
+constexpr int UNROLL = 8;    // independent 16-byte loads in flight per thread (forward sums)
 
 __device__ __forceinline__ void unpack8(const uint4& raw, float (&out)[8]) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -167,6 +167,7 @@ bn_apply(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ 
          const float* __restrict__ scale, const float* __restrict__ shift, __nv_bfloat16* __restrict__ y,
          long long vecs, int vec_per_row) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+#pragma unroll 4
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < vecs; i += stride) {
     const int c0 = static_cast<int>(i % vec_per_row) * 8;
     float a[8], v[8], out[8];
@@ -197,6 +198,7 @@ bn_dx(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
       const float* __restrict__ k_const, __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dres,
       long long vecs, int vec_per_row) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+#pragma unroll 2
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < vecs; i += stride) {
     const int c0 = static_cast<int>(i % vec_per_row) * 8;
     float g[8], xv[8], a[8], b[8], out[8];
@@ -239,7 +241,7 @@ bn_bwd_sums(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
     const __nv_bfloat16* bx = x + c0;
     const __nv_bfloat16* bg = dy + c0;
     const __nv_bfloat16* by = y + c0;
-    constexpr int U = RELU ? 2 : UNROLL;  // three tensors in flight when the mask is needed
+    constexpr int U = RELU ? 2 : 4;  // two or three tensors in flight per row
     long long r = r_begin + lane;
     for (; r + (U - 1) * LANES < r_end; r += U * LANES) {
       uint4 rx[U], rg[U], ry[U];
