@@ -120,3 +120,18 @@ def test_grouped_bf16_weight_cast_is_transparent():
     for pa, pb in zip(a.parameters(), b.parameters()):
         assert pa.grad.dtype == torch.float32 and pa.grad.stride() == pb.grad.stride()
         torch.testing.assert_close(pa.grad, pb.grad, rtol=2e-2, atol=1e-3 * pb.grad.abs().max().item())
+
+
+def test_wideresnet_and_mixer_step_through_their_makers():
+    from asdl_b200.models import wideresnet_tiny, mixer_tiny
+    torch.manual_seed(0)
+    x, t = torch.randn(4, 3, 32, 32), torch.randint(0, 10, (4,))
+    wrn = wideresnet_tiny()
+    cfg = asdl.PreconditioningConfig(data_size=4, damping=1e-2)
+    _steps(asdl.FusedKfacGradientMaker(wrn, cfg, fisher_type=asdl.FISHER_EMP), wrn, x, F.cross_entropy, t, n=2)
+    assert wrn.blocks[1].shortcut.fisher.kron.B.shape == (32, 32)
+    mixer = mixer_tiny()
+    _steps(asdl.KfacGradientMaker(mixer, cfg, fisher_type=asdl.FISHER_EMP), mixer, x, F.cross_entropy, t, n=2)
+    assert mixer.blocks[0].token_fc1.fisher.kron.A_inv.shape == (16, 16)    # 16 patches of 8 x 8
+    shampoo = asdl.ShampooGradientMaker(mixer, asdl.PreconditioningConfig(damping=1e-6), block_size=16)
+    _steps(shampoo, mixer, x, F.cross_entropy, t, n=2, lr=1e-3)
