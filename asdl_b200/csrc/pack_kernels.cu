@@ -104,6 +104,52 @@ void cast_pad_bf16_grouped(at::Tensor table, int64_t count) {
   count_launch();
 }
 
+// Transposing cast bf16 -> fp32: dst[i][j] = float(src[j * src_ld + i]) for i < rows, j < cols.
+// Weight gradients of linear layers leave autograd as transposed (column-major) bf16 tensors; this
+// brings one into the row-major fp32 layout of the parameter in one coalesced pass (32 x 32 tiles
+// through shared memory).  All arguments are kernel parameters, so the launch can be captured in a
+// CUDA graph.
+__global__ void transpose_cast_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst,
+                                      long long rows, long long cols, long long lds, long long ldd) {
+  __shared__ float tile[32][33];
+  const long long tiles_r = (rows + 31) / 32, tiles_c = (cols + 31) / 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (long long t = blockIdx.x; t < tiles_r * tiles_c; t += gridDim.x) {
+    const long long tr = t / tiles_c, tc = t - tr * tiles_c;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const long long j = tc * 32 + ty + 8 * k, i = tr * 32 + tx;
+      tile[ty + 8 * k][tx] = (i < rows && j < cols) ? __bfloat162float(src[j * lds + i]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const long long i = tr * 32 + ty + 8 * k, j = tc * 32 + tx;
+      if (i < rows && j < cols) dst[i * ldd + j] = tile[tx][ty + 8 * k];
+    }
+    __syncthreads();
+  }
+}
+
+// src: bf16 [rows, cols] tensor with strides (1, ld) (a transposed matrix); dst: fp32 [rows, cols] row-major.
+void transpose_cast(at::Tensor src, at::Tensor dst) {
+  TORCH_CHECK(src.is_cuda() && dst.is_cuda() && src.dim() == 2 && dst.dim() == 2 && src.sizes() == dst.sizes(),
+              "src and dst must be CUDA matrices of the same shape");
+  TORCH_CHECK(src.scalar_type() == at::kBFloat16 && dst.scalar_type() == at::kFloat, "bf16 -> fp32 only");
+  TORCH_CHECK(src.stride(0) == 1 && src.stride(1) >= src.size(0) && dst.stride(1) == 1 && dst.stride(0) >= dst.size(1),
+              "src must be column-major and dst row-major");
+  const long long rows = src.size(0), cols = src.size(1);
+  if (rows == 0 || cols == 0) return;
+  c10::cuda::CUDAGuard guard(src.get_device());
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  const long long tiles = ((rows + 31) / 32) * ((cols + 31) / 32);
+  const int grid = static_cast<int>(std::min<long long>(tiles, 148LL * 8));
+  transpose_cast_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(src.data_ptr()),
+                                                  dst.data_ptr<float>(), rows, cols, src.stride(1), dst.stride(0));
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
 struct Im2colParams {
   long long sN, sC, sH, sW;  // input strides in elements
   int N, C, H, W;

@@ -6,6 +6,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .layers import grouped_bf16_weights
 from .vit import SelfAttention
 
 __all__ = ['GPT2', 'gpt2_medium', 'gpt2_tiny']
@@ -26,13 +27,24 @@ class Block(nn.Module):
 
 
 class GPT2(nn.Module):
-    def __init__(self, vocab_size=50257, n_positions=1024, n_layer=24, n_head=16, n_embd=1024):
+    def __init__(self, vocab_size=50257, n_positions=1024, n_layer=24, n_head=16, n_embd=1024,
+                 pad_vocab_to_multiple_of=64):
         super().__init__()
-        self.wte = nn.Embedding(vocab_size, n_embd)
+        # The embedding / output matrix is stored with its row count rounded up: an odd vocabulary
+        # size (50257) makes the rows of the logits unaligned and pushes the output GEMMs onto slow
+        # unaligned kernels.  The extra logits are forced to -inf, so losses and sampled labels are
+        # those of the unpadded vocabulary.
+        self.vocab_size = vocab_size
+        m = max(1, pad_vocab_to_multiple_of)
+        padded = (vocab_size + m - 1) // m * m
+        mask = torch.zeros(padded)
+        mask[vocab_size:] = float('-inf')
+        self.register_buffer('vocab_mask', mask, persistent=False)
+        self.wte = nn.Embedding(padded, n_embd)
         self.wpe = nn.Embedding(n_positions, n_embd)
         self.blocks = nn.ModuleList(Block(n_embd, n_head) for _ in range(n_layer))
         self.ln_f = nn.LayerNorm(n_embd)
-        self.lm_head = nn.Linear(n_embd, vocab_size, bias=False)
+        self.lm_head = nn.Linear(n_embd, padded, bias=False)
         self.lm_head.weight = self.wte.weight  # tied
         for m in self.modules():
             if isinstance(m, (nn.Linear, nn.Embedding)):
@@ -44,11 +56,20 @@ class GPT2(nn.Module):
             nn.init.normal_(blk.attn.proj.weight, std=0.02 / (2 * n_layer) ** 0.5)
 
     def forward(self, tokens):
+        if tokens.is_cuda and torch.is_autocast_enabled('cuda') and torch.get_autocast_dtype('cuda') == torch.bfloat16:
+            with grouped_bf16_weights(self):  # one grouped cast instead of one cast kernel per layer
+                return self._forward(tokens)
+        return self._forward(tokens)
+
+    def _forward(self, tokens):
         pos = torch.arange(tokens.shape[1], device=tokens.device)
         x = self.wte(tokens) + self.wpe(pos)
         for blk in self.blocks:
             x = blk(x)
-        return self.lm_head(self.ln_f(x))
+        logits = self.lm_head(self.ln_f(x))
+        if logits.shape[-1] != self.vocab_size:
+            logits = logits + self.vocab_mask.to(logits.dtype)
+        return logits
 
     def ignore_for_kfac(self):
         """Modules that K-FAC leaves to the plain gradient on this model."""

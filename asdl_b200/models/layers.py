@@ -100,7 +100,19 @@ class _GroupedCast(torch.autograd.Function):
             dst = [torch.empty_strided(ctx.meta[i][0], ctx.meta[i][1], device=g.device, dtype=torch.float32)
                    if _dense_meta(*ctx.meta[i]) else torch.empty(ctx.meta[i][0], device=g.device, dtype=torch.float32)
                    for i, g in present]
-            torch._foreach_copy_(dst, [g for _, g in present])
+            same, same_dst = [], []
+            kernels = present[0][1].is_cuda and ops.cuda_kernels_enabled(present[0][1])
+            for (i, g), d in zip(present, dst):
+                # autograd hands the weight gradient of a linear layer over as a transposed tensor: a
+                # tiled transposing cast instead of a strided element-wise copy
+                if (kernels and g.ndim == 2 and g.dtype == torch.bfloat16 and d.is_contiguous()
+                        and g.stride(0) == 1 and g.stride(1) >= g.shape[0] and g.shape[0] > 1):
+                    ops.extension().transpose_cast(g, d)
+                else:
+                    same.append(g)
+                    same_dst.append(d)
+            if same:
+                torch._foreach_copy_(same_dst, same)
             for (i, _), d in zip(present, dst):
                 outs[i] = d
         return tuple(outs)

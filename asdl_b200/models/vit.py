@@ -6,6 +6,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .layers import grouped_bf16_weights
+
 __all__ = ['VisionTransformer', 'vit_b_16', 'vit_tiny']
 
 
@@ -56,6 +58,12 @@ class VisionTransformer(nn.Module):
                 nn.init.zeros_(m.bias)
 
     def forward(self, x):
+        if x.is_cuda and torch.is_autocast_enabled('cuda') and torch.get_autocast_dtype('cuda') == torch.bfloat16:
+            with grouped_bf16_weights(self):  # one grouped cast instead of one cast kernel per layer
+                return self._forward(x)
+        return self._forward(x)
+
+    def _forward(self, x):
         x = self.conv_proj(x).flatten(2).transpose(1, 2)
         x = torch.cat([self.class_token.expand(x.shape[0], -1, -1).to(x.dtype), x], dim=1)
         x = x + self.pos_embedding.to(x.dtype)

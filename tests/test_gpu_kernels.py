@@ -385,6 +385,31 @@ def test_fused_resnet_under_autocast_matches_unfused_model():
     assert plain.bn1.num_batches_tracked.item() == fused.bn1.num_batches_tracked.item() == 1
 
 
+@pytest.mark.parametrize('rows,cols', [(96, 40), (1000, 768), (33, 65), (4096, 1024)])
+def test_transposing_cast_kernel(ext, rows, cols):
+    """Column-major bf16 gradient -> row-major fp32 tensor (what autograd hands over for linear layers)."""
+    torch.manual_seed(0)
+    base = torch.randn(cols, rows, device=DEV).to(torch.bfloat16)   # storage of the transposed matrix
+    src = base.t()                                                  # [rows, cols], strides (1, rows)
+    dst = torch.full((rows, cols), float('nan'), device=DEV)
+    ext.transpose_cast(src, dst)
+    assert torch.equal(dst, src.float())
+    # through the grouped weight cast: a linear layer under autocast gets an fp32 gradient in its own layout
+    from asdl_b200.models.layers import grouped_bf16_weights
+    lin_a, lin_b = nn.Linear(cols, 24).to(DEV), nn.Linear(cols, 24).to(DEV)
+    lin_b.load_state_dict(lin_a.state_dict())
+    x = torch.randn(rows, cols, device=DEV)
+    with torch.autocast('cuda', dtype=torch.bfloat16):
+        with grouped_bf16_weights(lin_a):
+            ya = lin_a(x)
+        yb = lin_b(x)
+    ya.float().square().sum().backward()
+    yb.float().square().sum().backward()
+    assert lin_a.weight.grad.dtype == torch.float32 and lin_a.weight.grad.is_contiguous()
+    assert rel_err(lin_a.weight.grad, lin_b.weight.grad) < 1e-2
+    ops.check_status()
+
+
 def test_symmetric_segment_kernels_on_emulated_ranks(ext):
     """Pull-reduce, push-broadcast and decay kernels with three ranks emulated on one GPU."""
     from asdl_b200.parallel.symmetric import SymmetricArena
