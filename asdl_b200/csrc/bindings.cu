@@ -37,6 +37,10 @@ std::vector<at::Tensor> bn_backward_train(at::Tensor x, at::Tensor dy, at::Tenso
                                           at::Tensor invstd, c10::optional<at::Tensor> y, bool want_dres);
 void bn_unitwise_stats_xhat(at::Tensor x, at::Tensor dy, c10::optional<at::Tensor> y, at::Tensor mean,
                             at::Tensor invstd, at::Tensor stats, double alpha, double beta);
+bool ln_supported_size(int64_t d);
+std::vector<at::Tensor> ln_forward(at::Tensor x, at::Tensor weight, at::Tensor bias, double eps);
+std::vector<at::Tensor> ln_backward(at::Tensor x, at::Tensor dy, at::Tensor weight, at::Tensor mean,
+                                    at::Tensor rstd);
 void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot, int64_t wait_ms);
 void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale);
 void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs);
@@ -69,6 +73,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("bn_forward_train", &b200::bn_forward_train);
   m.def("bn_backward_train", &b200::bn_backward_train);
   m.def("bn_unitwise_stats_xhat", &b200::bn_unitwise_stats_xhat);
+  m.def("ln_supported_size", &b200::ln_supported_size);
+  m.def("ln_forward", &b200::ln_forward);
+  m.def("ln_backward", &b200::ln_backward);
   m.def("symm_barrier", &b200::symm_barrier);
   m.def("symm_reduce_segments", &b200::symm_reduce_segments);
   m.def("symm_bcast_segments", &b200::symm_bcast_segments);

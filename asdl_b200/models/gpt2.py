@@ -6,7 +6,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .layers import grouped_bf16_weights
+from .layers import FusedLayerNorm, grouped_bf16_weights
 from .vit import SelfAttention
 
 __all__ = ['GPT2', 'gpt2_medium', 'gpt2_tiny']
@@ -15,9 +15,9 @@ __all__ = ['GPT2', 'gpt2_medium', 'gpt2_tiny']
 class Block(nn.Module):
     def __init__(self, dim, heads):
         super().__init__()
-        self.ln_1 = nn.LayerNorm(dim)
+        self.ln_1 = FusedLayerNorm(dim)
         self.attn = SelfAttention(dim, heads, causal=True)
-        self.ln_2 = nn.LayerNorm(dim)
+        self.ln_2 = FusedLayerNorm(dim)
         self.fc = nn.Linear(dim, 4 * dim)
         self.proj = nn.Linear(4 * dim, dim)
 
@@ -43,7 +43,7 @@ class GPT2(nn.Module):
         self.wte = nn.Embedding(padded, n_embd)
         self.wpe = nn.Embedding(n_positions, n_embd)
         self.blocks = nn.ModuleList(Block(n_embd, n_head) for _ in range(n_layer))
-        self.ln_f = nn.LayerNorm(n_embd)
+        self.ln_f = FusedLayerNorm(n_embd)
         self.lm_head = nn.Linear(n_embd, padded, bias=False)
         self.lm_head.weight = self.wte.weight  # tied
         for m in self.modules():

@@ -4,7 +4,7 @@ import torch.nn as nn
 
 from .. import ops
 
-__all__ = ['FusedBatchNorm2d', 'grouped_bf16_weights']
+__all__ = ['FusedBatchNorm2d', 'FusedLayerNorm', 'grouped_bf16_weights']
 
 
 class FusedBatchNorm2d(nn.BatchNorm2d):
@@ -71,6 +71,23 @@ class FusedBatchNorm2d(nn.BatchNorm2d):
 
     def extra_repr(self):
         return super().extra_repr() + (f', act={self.act}' if self.act else '')
+
+
+class FusedLayerNorm(nn.LayerNorm):
+    """``nn.LayerNorm`` over the last dimension whose forward / backward run on the library's bf16
+    kernels (:func:`asdl_b200.ops.layer_norm`) for contiguous bf16 CUDA inputs of a supported
+    feature size, and exactly like the parent otherwise.  Under autocast the parent computes in
+    fp32 and returns fp32; this layer keeps the activation in bf16 (statistics in fp32)."""
+
+    def forward(self, x):
+        if (len(self.normalized_shape) == 1 and self.elementwise_affine and self.bias is not None
+                and x.is_cuda and torch.is_autocast_enabled('cuda')
+                and torch.get_autocast_dtype('cuda') == torch.bfloat16):
+            xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+            xb = xb if xb.is_contiguous() else xb.contiguous()
+            if ops.layer_norm_supported(xb, self.weight, self.bias):
+                return ops.layer_norm(xb, self.weight, self.bias, self.eps)
+        return super().forward(x)
 
 
 class _GroupedCast(torch.autograd.Function):

@@ -6,7 +6,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .layers import grouped_bf16_weights
+from .layers import FusedLayerNorm, grouped_bf16_weights
 
 __all__ = ['VisionTransformer', 'vit_b_16', 'vit_tiny']
 
@@ -29,9 +29,9 @@ class SelfAttention(nn.Module):
 class EncoderBlock(nn.Module):
     def __init__(self, dim, heads, mlp_dim, causal=False):
         super().__init__()
-        self.ln_1 = nn.LayerNorm(dim, eps=1e-6)
+        self.ln_1 = FusedLayerNorm(dim, eps=1e-6)
         self.attn = SelfAttention(dim, heads, causal)
-        self.ln_2 = nn.LayerNorm(dim, eps=1e-6)
+        self.ln_2 = FusedLayerNorm(dim, eps=1e-6)
         self.fc1 = nn.Linear(dim, mlp_dim)
         self.fc2 = nn.Linear(mlp_dim, dim)
 
@@ -50,7 +50,7 @@ class VisionTransformer(nn.Module):
         self.class_token = nn.Parameter(torch.zeros(1, 1, hidden_dim))
         self.pos_embedding = nn.Parameter(torch.empty(1, seq, hidden_dim).normal_(std=0.02))
         self.layers = nn.ModuleList(EncoderBlock(hidden_dim, num_heads, mlp_dim) for _ in range(num_layers))
-        self.ln = nn.LayerNorm(hidden_dim, eps=1e-6)
+        self.ln = FusedLayerNorm(hidden_dim, eps=1e-6)
         self.head = nn.Linear(hidden_dim, num_classes)
         for m in self.modules():
             if isinstance(m, nn.Linear):

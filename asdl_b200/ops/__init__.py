@@ -19,7 +19,7 @@ import torch
 
 from . import _build
 
-__all__ = ['gram', 'matmul_tn', 'kron_apply', 'spd_inverse', 'spd_inverse_grouped', 'unitwise_inverse', 'batchnorm_unitwise_stats', 'batch_norm_train', 'batchnorm_unitwise_stats_from_input', 'conv_patch_gram',
+__all__ = ['gram', 'matmul_tn', 'kron_apply', 'spd_inverse', 'spd_inverse_grouped', 'unitwise_inverse', 'batchnorm_unitwise_stats', 'batch_norm_train', 'batchnorm_unitwise_stats_from_input', 'layer_norm', 'conv_patch_gram',
            'set_backend', 'get_backend', 'set_precision', 'get_precision', 'extension',
            'cuda_kernels_enabled', 'check_status']
 
@@ -402,6 +402,43 @@ def batchnorm_unitwise_stats_from_input(x, dy, y, mean, invstd, out, alpha=1.0, 
     ww, wb, bb = gw.square().sum(dim=0), (gw * gb).sum(dim=0), gb.square().sum(dim=0)
     new = torch.stack([torch.stack([ww, wb], dim=1), torch.stack([wb, bb], dim=1)], dim=1)
     return out.mul_(beta).add_(new, alpha=alpha)
+
+
+class _LayerNormFn(torch.autograd.Function):
+    """LayerNorm over the last dimension on the library's bf16 kernels."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        y, mean, rstd = extension().ln_forward(x, weight.detach(), bias.detach(), float(eps))
+        ctx.save_for_backward(x, weight, mean, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, mean, rstd = ctx.saved_tensors
+        dx, dweight, dbias = extension().ln_backward(x, dy.contiguous(), weight.detach(), mean, rstd)
+        return dx, dweight, dbias, None
+
+
+_LN_SIZES = {256 * v for v in (1, 2, 3, 4, 6, 8, 12, 16)}
+
+
+def layer_norm_supported(x: torch.Tensor, weight, bias) -> bool:
+    return (weight is not None and bias is not None and weight.ndim == 1 and cuda_kernels_enabled(x)
+            and x.dtype == torch.bfloat16 and x.is_contiguous() and x.numel() > 0
+            and x.shape[-1] == weight.numel() and weight.numel() in _LN_SIZES
+            and weight.dtype == torch.float32 and bias.dtype == torch.float32)
+
+
+def layer_norm(x, weight, bias, eps=1e-5):
+    """LayerNorm over the last dimension, differentiable.  CUDA, contiguous bf16 input with fp32
+    parameters and a feature size of 256 * {1, 2, 3, 4, 6, 8, 12, 16}: one kernel forward, two
+    backward (the input gradient and the weight / bias gradients come out of one pass over dy and
+    x); anything else: ``F.layer_norm``."""
+    if layer_norm_supported(x, weight, bias):
+        return _LayerNormFn.apply(x, weight, bias, eps)
+    return torch.nn.functional.layer_norm(x, (weight.numel(),) if weight is not None else x.shape[-1:],
+                                          weight, bias, eps)
 
 
 def unitwise_inverse(blocks: torch.Tensor, damping: float = 0.0) -> torch.Tensor:

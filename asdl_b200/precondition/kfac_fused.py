@@ -86,7 +86,6 @@ class _NormState:
         self.has_inv = False
         self.unit = UnitWise(self.stats)
         module.fisher = SymMatrix(unit=self.unit)
-        self.saved_out = None
 
 
 class FusedKfacGradientMaker(KfacGradientMaker):
@@ -230,14 +229,13 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         arena = self._arena = SymmetricArena(total, group=self.sync_group, device=self.device)
         rank = self.world_rank
         self._slots_off, _ = arena.alloc(self.world_size * self._slot_stride)
-        factor_segs, stage_segs, grad_segs, mirror_rows, slot_rows = [], [], [], [], []
+        stage_segs, grad_segs, mirror_rows, slot_rows = [], [], [], []
         for st in self._kron:
             st.A_off, st.A = arena.alloc(st.d_in, st.d_in)
             st.B_off, st.B = arena.alloc(st.d_out, st.d_out)
             st.kron.A, st.kron.B = st.A, st.B
             st.owner = self._owner.get(st.module, 0)
             if st.owner == rank:
-                factor_segs += [(st.A_off, st.A.numel()), (st.B_off, st.B.numel())]
                 mirror_rows += [[st.A_off, st.d_in], [st.B_off, st.d_out]]
                 slot_rows += [[st.A_off, self._slots_off + st.slot_rel[0], st.d_in],
                               [st.B_off, self._slots_off + st.slot_rel[1], st.d_out]]
@@ -263,8 +261,6 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                     rest_segs.append((off, p.numel()))
         self._rest_segs = arena.segments(rest_segs)
         self._sym_params = params
-        self._factor_segs = arena.segments(factor_segs)
-        self._mirror_mats = torch.tensor(mirror_rows, dtype=torch.int64, device=self.device).reshape(-1, 2)
         self._mirror_n_max = max([r[1] for r in mirror_rows], default=0)
         self._slot_table = torch.tensor(slot_rows, dtype=torch.int64, device=self.device).reshape(-1, 3)
         self._stage_segs = arena.segments(stage_segs)

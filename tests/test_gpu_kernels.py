@@ -410,6 +410,38 @@ def test_transposing_cast_kernel(ext, rows, cols):
     ops.check_status()
 
 
+@pytest.mark.parametrize('rows,d', [(64, 256), (197 * 3, 768), (1000, 1024), (9, 4096), (33, 1536)])
+def test_layer_norm_kernels(ext, rows, d):
+    """Forward and backward (input, weight, bias gradients) against F.layer_norm in fp32."""
+    torch.manual_seed(0)
+    x = (torch.randn(rows, d, device=DEV) * 1.5 + 0.3).to(torch.bfloat16)
+    w = (torch.rand(d, device=DEV) + 0.5).requires_grad_(True)
+    b = torch.randn(d, device=DEV).requires_grad_(True)
+    dy = torch.randn(rows, d, device=DEV).to(torch.bfloat16)
+    xr = x.float().requires_grad_(True)
+    wr, br = w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    F.layer_norm(xr, (d,), wr, br, 1e-5).backward(dy.float())
+    xk = x.detach().requires_grad_(True)
+    assert ops.layer_norm_supported(xk, w, b)
+    before = ext.launch_count()
+    y = ops.layer_norm(xk, w, b, 1e-5)
+    y.backward(dy)
+    assert ext.launch_count() == before + 3
+    assert rel_err(y, F.layer_norm(x.float(), (d,), w, b, 1e-5)) < 4e-3
+    assert rel_err(xk.grad, xr.grad) < 6e-3
+    assert rel_err(w.grad, wr.grad) < 1e-4 and rel_err(b.grad, br.grad) < 1e-4
+    # a 3-d input and the module wrapper under autocast
+    from asdl_b200.models.layers import FusedLayerNorm
+    ln = FusedLayerNorm(d).to(DEV)
+    x3 = torch.randn(2, 5, d, device=DEV, requires_grad=True)
+    with torch.autocast('cuda', dtype=torch.bfloat16):
+        out = ln(x3)
+    assert out.dtype == torch.bfloat16 and out.shape == x3.shape
+    out.float().sum().backward()
+    assert x3.grad is not None and ln.weight.grad.shape == (d,)
+    ops.check_status()
+
+
 def test_symmetric_segment_kernels_on_emulated_ranks(ext):
     """Pull-reduce, push-broadcast and decay kernels with three ranks emulated on one GPU."""
     from asdl_b200.parallel.symmetric import SymmetricArena
