@@ -117,6 +117,10 @@ class FusedKfacGradientMaker(KfacGradientMaker):
     Embedding layers are not handled here; list them in ``config.ignore_modules``.
     """
 
+    #: plain steps that run eagerly before the CUDA graphs are captured (the capture itself warms
+    #: every step kind up twice, so none are needed)
+    eager_plain_steps_before_capture = 0
+
     def __init__(self, model, config: PreconditioningConfig, fisher_type: str = FISHER_MC,
                  loss_type: str = LOSS_CROSS_ENTROPY, scale: float = 1, grad_scale: float = 1,
                  n_mc_samples: int = 1, var: float = 1., seed: int = None,
@@ -308,9 +312,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             if kind != 'plain':
                 return self._eager_step(step, plain)
             self._plain_steps_seen += 1
-            if self._plain_steps_seen <= 2:  # let lazy initialisation happen eagerly first
+            if self._plain_steps_seen <= self.eager_plain_steps_before_capture:
                 return self._eager_step(step, plain)
-            self._capture(slots, key)
+            self._capture(slots, key)  # runs its own warm-up rounds before recording
         if key != self._graph_key or kind not in self._graphs:
             return self._eager_step(step, plain)
         captured = self._graphs[kind]

@@ -203,6 +203,7 @@ def barrier(world):
 
 def main():
     args = parse_args()
+    args.warmup = max(args.warmup, 3)  # the step graphs are captured at the second step
     if args.impl == 'reference' and not os.path.isdir(os.path.join(ROOT, 'baseline', '_ref', 'asdl')):
         if int(os.environ.get('RANK', '0')) == 0:
             print(json.dumps({'impl': 'reference',

@@ -135,3 +135,13 @@ def test_wideresnet_and_mixer_step_through_their_makers():
     assert mixer.blocks[0].token_fc1.fisher.kron.A_inv.shape == (16, 16)    # 16 patches of 8 x 8
     shampoo = asdl.ShampooGradientMaker(mixer, asdl.PreconditioningConfig(damping=1e-6), block_size=16)
     _steps(shampoo, mixer, x, F.cross_entropy, t, n=2, lr=1e-3)
+
+
+def test_fused_layer_norm_is_layer_norm_on_cpu():
+    from asdl_b200.models.layers import FusedLayerNorm
+    torch.manual_seed(0)
+    a, b = FusedLayerNorm(48), nn.LayerNorm(48)
+    b.load_state_dict(a.state_dict())
+    x = torch.randn(3, 7, 48)
+    torch.testing.assert_close(a(x), b(x))
+    assert isinstance(a, nn.LayerNorm)
