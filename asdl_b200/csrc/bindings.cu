@@ -25,6 +25,7 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
 void gemm_plan_finalize(int64_t id);
 void gemm_plan_run(int64_t id);
 void cast_pad_bf16_grouped(at::Tensor table, int64_t count);
+void cast_split3(at::Tensor src, at::Tensor hi, at::Tensor mid, at::Tensor lo);
 void transpose_cast(at::Tensor src, at::Tensor dst);
 void bn_unitwise_stats(at::Tensor y, at::Tensor g, at::Tensor weight, at::Tensor bias, at::Tensor stats,
                        double alpha, double beta);
@@ -68,6 +69,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_plan_finalize", &b200::gemm_plan_finalize);
   m.def("gemm_plan_run", &b200::gemm_plan_run);
   m.def("cast_pad_bf16_grouped", &b200::cast_pad_bf16_grouped);
+  m.def("cast_split3", &b200::cast_split3);
   m.def("transpose_cast", &b200::transpose_cast);
   m.def("bn_unitwise_stats", &b200::bn_unitwise_stats);
   m.def("bn_forward_train", &b200::bn_forward_train);

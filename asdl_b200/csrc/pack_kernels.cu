@@ -72,6 +72,49 @@ void cast_pad_bf16(at::Tensor src, at::Tensor hi, c10::optional<at::Tensor> lo, 
   count_launch();
 }
 
+// Three-way split of an fp32 matrix: v = hi + mid + lo with every part a bf16 number, which carries
+// the full 24-bit significand of v.  Six tensor-core products of such parts (hi*hi, hi*mid, mid*hi,
+// hi*lo, mid*mid, lo*hi) reproduce an fp32 product to ~2^-24.
+__global__ void cast_split3_kernel(const float* __restrict__ src, long long lds, __nv_bfloat16* __restrict__ hi,
+                                   __nv_bfloat16* __restrict__ mid, __nv_bfloat16* __restrict__ lo,
+                                   long long ldo, long long rows, int n) {
+  const long long total = rows * ldo;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / ldo;
+    const int c = static_cast<int>(i - r * ldo);
+    const float v = (c < n) ? src[r * lds + c] : 0.f;
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(h);
+    const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+    hi[i] = h;
+    mid[i] = m;
+    lo[i] = __float2bfloat16_rn(r1 - __bfloat162float(m));
+  }
+}
+
+void cast_split3(at::Tensor src, at::Tensor hi, at::Tensor mid, at::Tensor lo) {
+  TORCH_CHECK(src.is_cuda() && src.dim() == 2 && src.stride(1) == 1 && src.scalar_type() == at::kFloat,
+              "src must be a 2-D fp32 CUDA tensor with unit column stride");
+  for (const at::Tensor* t : {&hi, &mid, &lo})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kBFloat16 && t->dim() == 2 && t->is_contiguous() &&
+                    t->size(0) == src.size(0) && t->size(1) >= src.size(1) && t->sizes() == hi.sizes(),
+                "outputs must be contiguous bf16 [rows, >= n] tensors of one shape");
+  c10::cuda::CUDAGuard guard(src.get_device());
+  const long long rows = src.size(0);
+  const long long ldo = hi.size(1);
+  if (rows == 0) return;
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  const long long total = rows * ldo;
+  const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148LL * 16));
+  cast_split3_kernel<<<blocks, 256, 0, stream>>>(
+      src.data_ptr<float>(), src.stride(0), reinterpret_cast<__nv_bfloat16*>(hi.data_ptr()),
+      reinterpret_cast<__nv_bfloat16*>(mid.data_ptr()), reinterpret_cast<__nv_bfloat16*>(lo.data_ptr()), ldo, rows,
+      static_cast<int>(src.size(1)));
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
 // Grouped fp32 -> bf16 hi/lo staging: one launch converts many matrices.  Each table row holds
 // (src fp32 ptr, hi ptr, lo ptr or 0, rows, n, src pitch, dst pitch) as int64.
 __global__ void cast_pad_grouped_kernel(const long long* __restrict__ table) {

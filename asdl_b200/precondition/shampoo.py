@@ -35,6 +35,11 @@ __all__ = ['ShampooGradientMaker', 'Preconditioner', 'BlockPartitioner', 'Comput
 
 _invalid = -1
 
+#: Which batches of statistics take the grouped tensor-core chain for their inverse roots:
+#: 'auto' (well-damped ones: ridge >= 1e-4 of the largest eigenvalue), 'always', or 'never'
+#: (batched fp32 matrix products of PyTorch).
+TENSOR_CORE_ROOTS = 'auto'
+
 
 class ShampooGradientMaker(PreconditionedGradientMaker):
     """GradientMaker for `Shampoo <https://arxiv.org/abs/1802.09568>`_.
@@ -514,8 +519,11 @@ def _power_iteration_batched(mats, num_iters=100, error_tolerance=1e-6, check_ev
 class _NewtonChainCuda:
     """Coupled Newton iteration for a batch of equally sized matrices on the tensor cores.
 
-    Every product of an iteration (T^2, T^4, ..., T^p M and R T) is one grouped tcgen05 launch over
-    the whole batch, with fp32-grade accuracy from bf16 hi/lo operand splits.  All iterates are
+    Every product of an iteration (T^2, T^4, ..., T^p M and R T) runs as two grouped tcgen05
+    launches over the whole batch: the operands are split three ways into bf16 parts
+    (v = hi + mid + lo carries the full fp32 significand) and the six significant part products
+    hi*hi, hi*mid, mid*hi, hi*lo, mid*mid, lo*hi are accumulated in fp32, which reproduces an fp32
+    product to ~2^-24 - enough for ridges of 1e-6 times the largest eigenvalue.  All iterates are
     polynomials in the (symmetric) input, hence symmetric, so the row-major buffers serve directly
     as MN-major operands and nothing is transposed.  Buffers and launch plans are cached per
     (batch, size, p) because Shampoo calls this with the same shapes at every root update."""
@@ -529,6 +537,11 @@ class _NewtonChainCuda:
             cls._cache[key] = cls(b, n, p, device)
         return cls._cache[key]
 
+    @classmethod
+    def clear_cache(cls):
+        """Release the cached buffers and launch plans."""
+        cls._cache.clear()
+
     def __init__(self, b, n, p, device):
         ext = ops.extension()
         self.ext, self.b, self.n, self.p = ext, b, n, p
@@ -537,37 +550,44 @@ class _NewtonChainCuda:
         self.ld = ld
         f32 = dict(device=device, dtype=torch.float32)
         bf16 = dict(device=device, dtype=torch.bfloat16)
-        pair = lambda: (torch.zeros(b, n, ld, **bf16), torch.zeros(b, n, ld, **bf16))  # noqa: E731
+        triple = lambda: tuple(torch.zeros(b, n, ld, **bf16) for _ in range(3))  # noqa: E731
         self.M, self.R, self.T = (torch.zeros(b, n, n, **f32) for _ in range(3))
         self.M_new, self.R_new = torch.zeros(b, n, n, **f32), torch.zeros(b, n, n, **f32)
-        self.M_s, self.R_s, self.T_s = pair(), pair(), pair()
-        self.P_s = [pair() for _ in range(self.squarings)]     # T^2, T^4, ...
+        self.P = [torch.zeros(b, n, n, **f32) for _ in range(self.squarings)]   # T^2, T^4, ... in fp32
+        self.M_s, self.R_s, self.T_s = triple(), triple(), triple()
+        self.P_s = [triple() for _ in range(self.squarings)]
         self.plans = []
 
-        def product(a, bb, out_f32=None, out_pair=None):
-            plan = ext.gemm_plan_new()
+        def product(a, bb, out):
+            """Two plans: out = a1 b1 + a1 b2 + a2 b1, then out += a1 b3 + a2 b2 + a3 b1."""
+            first, second = ext.gemm_plan_new(), ext.gemm_plan_new()
             for i in range(b):
-                ah, al = a[0][i][:, :n], a[1][i][:, :n]
-                bh, bl = bb[0][i][:, :n], bb[1][i][:, :n]
-                ext.gemm_plan_add(plan, [ah, ah, al], [bh, bl, bh], False, False,
-                                  None if out_f32 is None else out_f32[i], 1.0, 0.0, False,
-                                  None if out_pair is None else out_pair[0][i],
-                                  None if out_pair is None else out_pair[1][i], 0, 0, False, [], 1)
-            ext.gemm_plan_finalize(plan)
-            self.plans.append(plan)
-            return plan
+                a1, a2, a3 = (t[i][:, :n] for t in a)
+                b1, b2, b3 = (t[i][:, :n] for t in bb)
+                ext.gemm_plan_add(first, [a1, a1, a2], [b1, b2, b1], False, False, out[i], 1.0, 0.0, False,
+                                  None, None, 0, 0, False, [], 1)
+                ext.gemm_plan_add(second, [a1, a2, a3], [b3, b2, b1], False, False, out[i], 1.0, 1.0, False,
+                                  None, None, 0, 0, False, [], 1)
+            ext.gemm_plan_finalize(first)
+            ext.gemm_plan_finalize(second)
+            self.plans += [first, second]
+            return first, second
 
         prev = self.T_s
         self.square_plans = []
         for k in range(self.squarings):
-            self.square_plans.append(product(prev, prev, out_pair=self.P_s[k]))
+            self.square_plans.append(product(prev, prev, self.P[k]))
             prev = self.P_s[k]
-        self.plan_m = product(prev, self.M_s, out_f32=self.M_new)
-        self.plan_r = product(self.R_s, self.T_s, out_f32=self.R_new)
+        self.plan_m = product(prev, self.M_s, self.M_new)
+        self.plan_r = product(self.R_s, self.T_s, self.R_new)
 
-    def _split(self, src, pair):
-        self.ext.cast_pad_bf16(src.view(self.b * self.n, self.n), pair[0].view(self.b * self.n, self.ld),
-                               pair[1].view(self.b * self.n, self.ld), 1.0)
+    def _split(self, src, parts):
+        rows = self.b * self.n
+        self.ext.cast_split3(src.view(rows, self.n), *(t.view(rows, self.ld) for t in parts))
+
+    def _run(self, plans):
+        self.ext.gemm_plan_run(plans[0])
+        self.ext.gemm_plan_run(plans[1])
 
     def run(self, g, z, iter_count, error_tolerance, check_every=4):
         """g: [b, n, n] damped matrices, z: [b] scaling; returns (g)^{-1/p} as a new tensor."""
@@ -584,15 +604,16 @@ class _NewtonChainCuda:
             torch.mul(self.M, alpha, out=self.T)
             self.T.diagonal(dim1=1, dim2=2).add_(1 - alpha)
             self._split(self.T, self.T_s)
-            for plan in self.square_plans:
-                self.ext.gemm_plan_run(plan)
-            self.ext.gemm_plan_run(self.plan_m)
-            self.ext.gemm_plan_run(self.plan_r)
+            for k, plans in enumerate(self.square_plans):
+                self._run(plans)
+                self._split(self.P[k], self.P_s[k])
+            self._run(self.plan_m)
+            self._run(self.plan_r)
             new_error = (self.M_new - eye).abs().amax(dim=(1, 2))
             grew = (new_error > error * 1.2) if it > 0 else torch.zeros_like(active)
-            # the split products carry ~2^-17 relative error: once the residual is that small and
-            # no longer shrinking quadratically, the matrix is done
-            stalled = (new_error > 0.5 * error) & (error < 1e-3) if it > 0 else torch.zeros_like(active)
+            # rounding puts a floor of a few 1e-7 * sqrt(n) under the residual: a matrix whose small
+            # residual has stopped shrinking quadratically is done
+            stalled = ((new_error > 0.5 * error) & (error < 1e-4)) if it > 0 else torch.zeros_like(active)
             accept = active & ~grew
             sel = accept.view(b, 1, 1)
             torch.where(sel, self.M_new, self.M, out=self.M)
@@ -626,12 +647,11 @@ def inverse_pth_root_batched(mats, p, iter_count=100, error_tolerance=1e-6, ridg
     lam = _power_iteration_batched(mats)
     g = mats + (ridge_epsilon * lam).view(b, 1, 1) * eye
     z = (1 + p) / (2 * torch.linalg.matrix_norm(g))
-    # The split products of the tensor-core chain carry ~2^-17 relative error, which is only
-    # harmless while the ridge keeps the spectrum well above that; smaller ridges stay in fp32.
     if (mats.is_cuda and dtype == torch.float32 and n >= 128 and p >= 2 and (p & (p - 1)) == 0
-            and ridge_epsilon >= 1e-4 and ops.get_backend() != 'torch'):
+            and ops.get_backend() != 'torch'
+            and (TENSOR_CORE_ROOTS == 'always' or (TENSOR_CORE_ROOTS == 'auto' and ridge_epsilon >= 1e-4))):
         chain = _NewtonChainCuda.get(b, n, p, mats.device)
-        return chain.run(g, z, iter_count, max(error_tolerance, 2e-5), check_every)
+        return chain.run(g, z, iter_count, error_tolerance, check_every)
     root = eye * z.pow(1.0 / p).view(b, 1, 1)
     m = g * z.view(b, 1, 1)
     error = (m - eye).abs().amax(dim=(1, 2))

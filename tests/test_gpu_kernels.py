@@ -292,6 +292,15 @@ def test_shampoo_grouped_launches_match_per_block_path():
     ops.check_status()
 
 
+def test_three_way_split_reproduces_fp32(ext):
+    torch.manual_seed(0)
+    x = torch.randn(300, 200, device=DEV) * torch.logspace(-6, 3, 200, device=DEV)
+    parts = [torch.empty(300, 200, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
+    ext.cast_split3(x, *parts)
+    total = parts[0].double() + parts[1].double() + parts[2].double()
+    assert ((total - x.double()).abs() <= x.double().abs() * 2.0 ** -23).all()
+
+
 @pytest.mark.parametrize('n,p', [(192, 4), (128, 2), (200, 8)])
 def test_inverse_root_chain_on_tensor_cores(n, p):
     """Batched coupled Newton with grouped tcgen05 products against the exact root from an
