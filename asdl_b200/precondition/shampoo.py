@@ -525,7 +525,8 @@ class _NewtonChainCuda:
     hi*hi, hi*mid, mid*hi, hi*lo, mid*mid, lo*hi are accumulated in fp32, which reproduces an fp32
     product to ~2^-24 - enough for ridges of 1e-6 times the largest eigenvalue.  All iterates are
     polynomials in the (symmetric) input, hence symmetric, so the row-major buffers serve directly
-    as MN-major operands and nothing is transposed.  Buffers and launch plans are cached per
+    as MN-major operands and nothing is transposed; the products run in the GEMM's symmetric mode
+    (lower tiles, mirrored), which keeps the iterates exactly symmetric at half the work.  Buffers and launch plans are cached per
     (batch, size, p) because Shampoo calls this with the same shapes at every root update."""
 
     _cache: Dict[Tuple[int, int, int, int], '_NewtonChainCuda'] = {}
@@ -564,9 +565,11 @@ class _NewtonChainCuda:
             for i in range(b):
                 a1, a2, a3 = (t[i][:, :n] for t in a)
                 b1, b2, b3 = (t[i][:, :n] for t in bb)
-                ext.gemm_plan_add(first, [a1, a1, a2], [b1, b2, b1], False, False, out[i], 1.0, 0.0, False,
+                # symmetric mode: lower-triangular tiles only, mirrored (half the work, and the iterates
+                # stay exactly symmetric, which the transposed operand reads rely on)
+                ext.gemm_plan_add(first, [a1, a1, a2], [b1, b2, b1], False, False, out[i], 1.0, 0.0, True,
                                   None, None, 0, 0, False, [], 1)
-                ext.gemm_plan_add(second, [a1, a2, a3], [b3, b2, b1], False, False, out[i], 1.0, 1.0, False,
+                ext.gemm_plan_add(second, [a1, a2, a3], [b3, b2, b1], False, False, out[i], 1.0, 1.0, True,
                                   None, None, 0, 0, False, [], 1)
             ext.gemm_plan_finalize(first)
             ext.gemm_plan_finalize(second)
@@ -594,7 +597,13 @@ class _NewtonChainCuda:
         b, n, p = self.b, self.n, self.p
         alpha = -1.0 / p
         eye = torch.eye(n, device=g.device, dtype=g.dtype)
-        torch.mul(g, z.view(b, 1, 1), out=self.M)
+        # The kernels read every operand as its own transpose.  That is only the same iteration while
+        # the iterates are exactly symmetric: an antisymmetric part (the input may carry one at
+        # rounding level) is amplified together with the small eigenvalues and moves the fixed point
+        # away from the identity.  So the input is symmetrised and every product is formed in the
+        # symmetric mode of the GEMM.
+        torch.add(g, g.transpose(1, 2), out=self.M)
+        self.M.mul_((0.5 * z).view(b, 1, 1))
         self.R.copy_(eye * z.pow(1.0 / p).view(b, 1, 1))
         error = (self.M - eye).abs().amax(dim=(1, 2))
         active = error > error_tolerance
