@@ -150,3 +150,42 @@ def test_matrix_manager_accumulates_and_measures():
     torch.testing.assert_close(acc, 2 * single, rtol=1e-5, atol=1e-7)
     trace = mm.get_trace(asdl.FISHER_EMP, asdl.SHAPE_LAYER_WISE, 'run')
     assert trace is not None
+
+
+def test_gradient_utilities_against_autograd():
+    model = _mlp()
+    x, t = torch.randn(6, 6), torch.randint(0, 3, (6,))
+    params = list(model.parameters())
+
+    def per_example():
+        rows = []
+        for i in range(6):
+            loss = F.cross_entropy(model(x[i:i + 1]), t[i:i + 1], reduction='sum')
+            rows.append(torch.cat([g.flatten() for g in torch.autograd.grad(loss, params)]))
+        return torch.stack(rows)
+    oracle = per_example()
+
+    def closure():
+        loss = F.cross_entropy(model(x), t, reduction='sum')
+        loss.backward()
+        return loss
+    model.zero_grad()
+    grads = asdl.batch_gradient(model, closure)
+    # per-example gradients are listed module by module (weight, then bias): the parameter order here
+    torch.testing.assert_close(grads, oracle, rtol=1e-4, atol=1e-6)
+    model.zero_grad()
+    asdl.save_batch_gradient(model, closure)
+    torch.testing.assert_close(model[0].weight.batch_grad.sum(0), model[0].weight.grad, rtol=1e-4, atol=1e-6)
+    jac = asdl.jacobian(model, x)
+    assert jac.shape == (6, 3, sum(p.numel() for p in params))
+    out0 = model(x)[2, 1]
+    g = torch.cat([v.flatten() for v in torch.autograd.grad(out0, params)])
+    torch.testing.assert_close(jac[2, 1], g, rtol=1e-4, atol=1e-6)
+    model.zero_grad()
+    loader = DataLoader(TensorDataset(x, t), batch_size=2)
+    mean_loss = asdl.data_loader_gradient(model, lambda y, tt: F.cross_entropy(y, tt, reduction='sum'), loader)
+    ref_loss = F.cross_entropy(model(x), t)
+    assert abs(mean_loss - ref_loss.item()) < 1e-5
+    ref = torch.autograd.grad(ref_loss, params)
+    for p, r in zip(params, ref):
+        torch.testing.assert_close(p.grad, r, rtol=1e-4, atol=1e-6)
