@@ -97,8 +97,11 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             that apply the inverses.
         clone_norm_outputs: copy normalisation-layer outputs in the statistics hook (needed only
             if the model modifies them in place afterwards, e.g. ``ReLU(inplace=True)``).
-        cuda_graph: replay steps that update neither curvature nor inverses (forward, loss,
-            backward and preconditioning) from a CUDA graph.  The registered tensor arguments are
+        cuda_graph: replay whole steps from CUDA graphs: the plain step (forward, loss, backward,
+            preconditioning), the step that also measures the curvature, and the step that measures
+            it and inverts (the last two unless a sampling seed is configured).  They are captured
+            at the first plain step after the first inverses exist; hyper-parameters (damping,
+            moving-average weights) are read at capture time.  The registered tensor arguments are
             copied into static buffers before every replay, ``param.grad`` is (re)bound to static
             gradient tensors that each replay overwrites (so gradients are not accumulated across
             calls in this mode), and the returned output / loss are static tensors as well.
@@ -169,7 +172,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         # barriers keep their epochs on the device, so a replay needs no per-step host arguments
         self._graph_enabled = (bool(cuda_graph) and device.type == 'cuda'
                                and (self.world_size == 1 or self.comm == 'symmetric'))
-        self._graphs = {}              # 'plain' / 'curvature' -> captured step
+        self._graphs = {}              # 'plain' / 'curvature' / 'update' -> captured step
         self._graph_key = None
         self._plain_steps_seen = 0
         self.replayed_launches = 0     # ... summed over all replays so far
@@ -181,7 +184,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
     def enable_phase_timing(self, enabled=True):
         """Record CUDA events around the phases of every step (plain step, curvature update,
         inverse update, preconditioning).  Read the result with :meth:`phase_times`."""
-        self._timing = {} if enabled else None
+        self._timing = {} if (enabled and self.device.type == 'cuda') else None
 
     def _phase(self, name):
         maker = self
