@@ -114,3 +114,27 @@ class SengGradientMaker(PreconditionedGradientMaker):
     def _teardown(self):
         with torch.no_grad():
             self._loss /= self.config.data_size
+
+    # ------------------------------------------------------------------ checkpointing
+    _INFO_FIELDS = ('in_data', 'out_grads', 'sub_in_data', 'sub_out_grads', 'in_indices', 'out_indices', 'gram_inv')
+
+    def _curvature_state(self):
+        out = {}
+        names = {module: name for name, module in self.module_dict.items()}
+        for module, info in self._curvature_info.items():
+            for field in self._INFO_FIELDS:
+                value = getattr(info, field)
+                if value is not None:
+                    out[f'{names[module]}.seng.{field}'] = value
+        return out
+
+    def _load_curvature_state(self, tensors):
+        grouped: Dict[str, Dict[str, Tensor]] = {}
+        for key, value in tensors.items():
+            name, _, field = key.rsplit('.', 2)
+            grouped.setdefault(name, {})[field] = value
+        for name, module in self.module_dict.items():
+            if name in grouped:
+                fields = {f: grouped[name].get(f) for f in self._INFO_FIELDS}
+                fields = {f: (v.to(self.device) if v is not None else None) for f, v in fields.items()}
+                self._curvature_info[module] = SketchedEmpFisherInfo(**fields)

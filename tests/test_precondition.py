@@ -351,3 +351,30 @@ def test_psgd_sparse_lu_fits_a_quadratic():
     flat = P @ torch.cat([t.reshape(-1) for t in g])
     torch.testing.assert_close(torch.cat([t.reshape(-1) for t in out]), flat)
     assert out[0].shape == (3, 2) and out[1].shape == (6,)
+
+
+def test_seng_state_roundtrip():
+    """The sketched curvature of SENG travels through state_dict: a fresh maker that loads it
+    preconditions a given gradient exactly like the original."""
+    import copy
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(6, 5), nn.ReLU(), nn.Linear(5, 3))
+    x, t = torch.randn(8, 6), torch.randint(0, 3, (8,))
+    cfg = asdl.PreconditioningConfig(data_size=8, damping=1e-2, curvature_upd_interval=100)
+    gm = asdl.SengGradientMaker(model, cfg, sketching_size=4)
+    d = gm.setup_model_call(model, x)
+    gm.setup_loss_call(F.cross_entropy, d, t)
+    gm.forward_and_backward()
+    state = copy.deepcopy(gm.state_dict())
+    assert any(k.endswith('seng.gram_inv') for k in state['curvature'])
+    fresh = asdl.SengGradientMaker(model, cfg, sketching_size=4)
+    fresh.load_state_dict(state)
+    grads = [torch.randn_like(p) for p in model.parameters()]
+    results = []
+    for maker in (gm, fresh):
+        for p, g in zip(model.parameters(), grads):
+            p.grad = g.clone()
+        maker.precondition()
+        results.append([p.grad.clone() for p in model.parameters()])
+    for a, b in zip(*results):
+        torch.testing.assert_close(a, b)

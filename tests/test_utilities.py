@@ -29,9 +29,16 @@ def test_tril_roundtrip_and_symmatrix_files(tmp_path):
     paths = sym.save(str(tmp_path), 'layer0')
     files = [os.path.join(dp, f) for dp, _, fs in os.walk(tmp_path) for f in fs]
     assert files and all(f.endswith('.npy') for f in files)
-    stored = np.load(sorted(f for f in files if 'tril' in os.path.basename(f) or True)[0])
-    assert stored.ndim == 1                                   # lower triangles only
-    assert paths is not None
+    assert paths == {'tril': 'layer0/tril.npy',
+                     'kron': {'A_tril': 'layer0/kron/A_tril.npy', 'B_tril': 'layer0/kron/B_tril.npy'}}
+    stored = np.load(os.path.join(tmp_path, paths['tril']))
+    assert stored.ndim == 1 and stored.dtype == np.float32 and stored.size == 28   # row-major lower triangle
+    loaded = asdl.SymMatrix()
+    loaded.load(path=os.path.join(tmp_path, paths['tril']),
+                kron_path={k: os.path.join(tmp_path, v) for k, v in paths['kron'].items()})
+    torch.testing.assert_close(loaded.data, a)
+    torch.testing.assert_close(loaded.kron.A, kron.A)
+    torch.testing.assert_close(loaded.kron.B, kron.B)
 
 
 def test_param_vector_algebra():
