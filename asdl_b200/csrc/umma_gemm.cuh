@@ -18,6 +18,14 @@
 // Split-K partial tiles go to a scratch buffer; `splitk_reduce_kernel` then sums the partials
 // in split order (deterministic) and runs the same epilogue with fully coalesced traffic.
 // SYM mode (SYRK) schedules only tiles on or below the diagonal and mirrors them.
+//
+// Epilogue variants for destinations in other GPUs' memory (peer pointers from a symmetric
+// allocation): plain stores of the lower-triangular tiles only (GF_LOWER: the owner of the matrix
+// sums and mirrors what the ranks sent), `red.global.add` reductions (GF_ATOMIC, optionally
+// lower-only), and up to G_MAX_EXTRA additional plain copies of the result (C_extra: the
+// preconditioned gradient replicated to every rank).  Peer memory is only ever written with
+// per-thread stores / reductions from the epilogue; TMA loads always read local memory.
+// A grouped launch (`work` != nullptr) runs one tile of one problem of a plan per CTA.
 #pragma once
 #include "sm100_ptx.cuh"
 
