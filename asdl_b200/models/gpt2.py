@@ -1,7 +1,9 @@
 """GPT-2 (decoder-only transformer, learned token and position embeddings, pre-norm blocks, tied
 output head) with ``nn.Linear`` projections, so that K-FAC's Linear hooks see every weight matrix
 of the blocks.  ``ignore_for_kfac`` lists the modules that K-FAC must skip on this model: the
-embeddings and the output head (a vocabulary-sized factor is 50257 x 50257) and the LayerNorms."""
+embeddings and the output head (a vocabulary-sized factor is 50257 x 50257) and the LayerNorms.
+The reference only has layer-shape tables of such models for its cost model
+(examples/prof/models/transformer.py:27-42); its Embedding operation is asdl/operations/embedding.py."""
 import torch
 import torch.nn as nn
 import torch.nn.functional as F

@@ -1,7 +1,8 @@
 """MLP-Mixer (patch embedding convolution, blocks of a token-mixing MLP across patches and a
 channel-mixing MLP across features, global average pooling, linear head).  Every weight matrix is an
 ``nn.Linear`` (the token-mixing MLP acts on the transposed activation), so K-FAC hooks and
-per-parameter methods see all of them."""
+per-parameter methods see all of them.  Reference counterpart: the timm Mixer-B of
+examples/arxiv_results/configs/mixer/*.json."""
 import torch.nn as nn
 import torch.nn.functional as F
 

@@ -1,7 +1,9 @@
 """ResNet-50 with the torchvision topology (stem 7x7/2 + max-pool, bottleneck stages
 [3, 4, 6, 3] with the stride on the 3x3 convolution, global average pool, linear head), written
 for curvature capture: activations that the statistics hooks read are never overwritten in place,
-and the module runs in channels_last / bf16 autocast without layout changes between layers."""
+and the module runs in channels_last / bf16 autocast without layout changes between layers.
+The reference trains the torchvision model (examples/train_resnet50_with_kfac.py:144-154) and CIFAR
+ResNets of its own (examples/arxiv_results/models/resnet.py)."""
 import torch
 import torch.nn as nn
 

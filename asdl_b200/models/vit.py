@@ -1,7 +1,9 @@
 """Vision Transformer (ViT-B/16 topology: patch-embedding convolution, class token, learned position
 embedding, pre-norm encoder blocks, linear head) written so that every weight matrix is visible to
 the curvature hooks: the attention projections are plain ``nn.Linear`` modules (a fused
-``nn.MultiheadAttention`` keeps q/k/v in one bare parameter that module hooks never see)."""
+``nn.MultiheadAttention`` keeps q/k/v in one bare parameter that module hooks never see).  The
+reference takes its ViT / Mixer models from timm (examples/arxiv_results/train.py:349,
+configs/vit/*.json)."""
 import torch
 import torch.nn as nn
 import torch.nn.functional as F

@@ -1,6 +1,7 @@
 """Wide residual network for 32 x 32 images (WRN-d-k: three stages of pre-activation basic blocks,
 widths 16k / 32k / 64k, depth d = 6n + 4), the CIFAR model family of the reference's training
-recipes.  Activations read by curvature hooks are never modified in place."""
+recipes (examples/arxiv_results/models/wideresnet.py, configs/wideresnet28/*.json).  Activations read by
+curvature hooks are never modified in place."""
 import torch
 import torch.nn as nn
 import torch.nn.functional as F

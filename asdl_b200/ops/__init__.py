@@ -8,6 +8,17 @@ The CUDA path never falls back silently: if a CUDA tensor is passed and the exte
 loaded an ImportError is raised.  ``set_backend('torch')`` selects the PyTorch implementation
 explicitly (used to build reference results on the GPU).
 
+What each primitive stands in for in the reference (file:line inside its project):
+  * ``gram`` / ``matmul_tn``: asdl/operations/linear.py:77,89 (A = a^T a, B = g^T g),
+    asdl/precondition/shampoo.py:335-339 (mode statistics);
+  * ``conv_patch_gram``: asdl/utils.py:51-88 (im2col) + asdl/operations/conv.py:80-88;
+  * ``kron_apply``: asdl/symmatrix.py:536-548 (B W A) and asdl/precondition/shampoo.py:351-367;
+  * ``spd_inverse`` / ``spd_inverse_grouped``: asdl/utils.py:91-96 (cholesky_inv);
+  * ``unitwise_inverse``: asdl/symmatrix.py:687-698;
+  * ``batchnorm_unitwise_stats``: asdl/operations/batchnorm.py:11-55;
+  * ``batch_norm_train`` / ``layer_norm``: the models' own normalisation layers (no reference
+    counterpart; PyTorch's kernels were the hot spot of the benchmark models).
+
 Precision policy of the tensor-core products (``set_precision``):
   * ``'auto'``   : bf16/fp16 inputs -> one bf16 pass (fp32 accumulation);
                    fp32 inputs      -> three bf16 passes on hi/lo splits ("bf16x3", ~2^-16 relative);
@@ -19,7 +30,9 @@ import torch
 
 from . import _build
 
-__all__ = ['gram', 'matmul_tn', 'kron_apply', 'spd_inverse', 'spd_inverse_grouped', 'unitwise_inverse', 'batchnorm_unitwise_stats', 'batch_norm_train', 'batchnorm_unitwise_stats_from_input', 'layer_norm', 'conv_patch_gram',
+__all__ = ['gram', 'matmul_tn', 'kron_apply', 'conv_patch_gram', 'spd_inverse', 'spd_inverse_grouped',
+           'unitwise_inverse', 'batchnorm_unitwise_stats', 'batchnorm_unitwise_stats_from_input',
+           'batch_norm_train', 'layer_norm',
            'set_backend', 'get_backend', 'set_precision', 'get_precision', 'extension',
            'cuda_kernels_enabled', 'check_status']
 
