@@ -657,7 +657,12 @@ class EkfacGradientMaker(NaturalGradientMaker):
     measured in that basis.  Empirical Fisher only."""
 
     def __init__(self, model, config: PreconditioningConfig, *args, **kwargs):
-        super().__init__(model, config, *args, **kwargs, fisher_shape=SHAPE_KFE)
+        if not args:
+            kwargs.setdefault('fisher_type', FISHER_EMP)
+        # normalisation layers have no Kronecker eigenbasis: unit-wise blocks as in K-FAC
+        fisher_shape = [SHAPE_KFE, (nn.BatchNorm1d, SHAPE_UNIT_WISE), (nn.BatchNorm2d, SHAPE_UNIT_WISE),
+                        (nn.LayerNorm, SHAPE_UNIT_WISE)]
+        super().__init__(model, config, *args, **kwargs, fisher_shape=fisher_shape)
         if self.fisher_type != FISHER_EMP:
             raise ValueError(f'{EkfacGradientMaker} supports only {FISHER_EMP}.')
 

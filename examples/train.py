@@ -120,7 +120,7 @@ def make_grad_maker(args, model):
     if name == 'kfac_fused':
         return asdl.FusedKfacGradientMaker(model, cfg, cuda_graph=args.cuda_graph)
     if name == 'ekfac':
-        return asdl.EkfacGradientMaker(model, cfg)
+        return asdl.EkfacGradientMaker(model, cfg, fisher_type=asdl.FISHER_EMP)
     if name == 'unit_wise':
         return asdl.UnitWiseNaturalGradientMaker(model, cfg)
     if name == 'diag':
