@@ -33,3 +33,11 @@ def test_other_examples():
     assert 'reshape' in _run('examples/grad_maker_demo.py')
     assert 'epoch 1' in _run('examples/pseudo_batch_train.py', '--epochs', '1')
     assert 'GFLOP' in _run('benchmarks/flops_memory.py', '--model', 'resnet_tiny')
+
+
+@pytest.mark.parametrize('impl', ['ours', 'fused'])
+def test_cpu_mlp_kfac_benchmark_matches_dense_oracle(impl):
+    import json
+    rec = json.loads(_run('benchmarks/cpu_mlp_kfac.py', '--impl', impl, '--steps', '2').strip().splitlines()[-1])
+    assert rec['max_rel_err_vs_dense_oracle'] < 1e-5
+    assert rec['last_loss'] < rec['first_loss']
