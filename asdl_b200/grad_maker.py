@@ -198,6 +198,11 @@ class GradientMaker:
     def delegate_forward_and_backward(self, other, *args, **kwargs):
         """Lets ``other`` (another GradientMaker) run the registered computation and mirrors its
         ``model_output`` / ``loss`` on ``self``."""
+        if self._model_fn is None:
+            raise ValueError('model_fn is not set. Call setup_model_call() before calling forward_and_backward().')
+        if self._loss_fn is None and self._dummy_loss is None:
+            raise ValueError('Neither loss_fn nor loss_repr is set. '
+                             'Call setup_loss_call() or setup_loss_repr() before calling forward_and_backward().')
         other.setup_model_call(self._model_fn, *self._model_args, **self._model_kwargs)
         if self._loss_fn is None:
             other.setup_loss_repr(self._dummy_loss)

@@ -57,6 +57,8 @@ class KronBfgsGradientMaker(PreconditionedGradientMaker):
     def _startup(self):
         step = self.state['step']
         if step > 0 and self.do_update_preconditioner(step - 1):
+            if not self._last_call[0] and not self._last_call[1]:
+                return  # resumed from a checkpoint: the batch of the open (s, y) pair is gone, drop the pair
             self._post_preconditioner_update()
 
     def update_preconditioner(self):

@@ -621,7 +621,37 @@ class NaturalGradientMaker(PreconditionedGradientMaker):
                 continue
             device = next(module.parameters()).device
             items = {k: v.to(device) for k, v in items.items()}
+            if name != '__model__':
+                _check_state_shapes(name, module, items)
             self._set_module_fisher(module, SymMatrix.from_tensors(items))
+
+
+def _check_state_shapes(name, module, items):
+    """A checkpoint written for another architecture fails at load time, with the offending key,
+    instead of at the first preconditioning product."""
+    weight = getattr(module, 'weight', None)
+    if weight is None:
+        return
+
+    def fail(key, why):
+        raise ValueError(f'curvature checkpoint entry {name}.{key} of shape {tuple(items[key].shape)} does not fit '
+                         f'{module.__class__.__name__} with weight {tuple(weight.shape)}: {why}')
+
+    sides = {}
+    for key, value in items.items():
+        if key in ('kron.A', 'kron.A_inv', 'kron.B', 'kron.B_inv'):
+            if value.ndim == 2 and value.shape[0] != value.shape[1]:
+                fail(key, 'a Kronecker factor is square')
+            side = key[5]
+            if sides.setdefault(side, value.shape[0]) != value.shape[0]:
+                fail(key, 'factor and inverse differ in size')
+        elif key in ('diag.weight', 'diag.weight_inv') and value.shape != weight.shape:
+            fail(key, 'the diagonal has the shape of the weight')
+    if 'B' in sides and sides['B'] != weight.shape[0] and not isinstance(module, nn.Embedding):
+        fail('kron.B' if 'kron.B' in items else 'kron.B_inv', 'the output-side factor has one row per output feature')
+    if 'A' in sides and 'B' in sides and not isinstance(module, nn.Embedding) \
+            and sides['A'] * sides['B'] != weight.numel():
+        fail('kron.A' if 'kron.A' in items else 'kron.A_inv', 'the factor sizes do not multiply to the weight size')
 
 
 class FullNaturalGradientMaker(NaturalGradientMaker):

@@ -57,6 +57,8 @@ def tril_to_matrix(tril: torch.Tensor):
     if tril.ndim != 1:
         raise ValueError(f'tril.ndim has to be 1. Got {tril.ndim}.')
     n = get_n_cols_by_tril(tril)
+    if n * (n + 1) // 2 != tril.numel():
+        raise ValueError(f'{tril.numel()} entries are not the packed triangle of any square matrix.')
     rows, cols = torch.tril_indices(n, n, device=tril.device)
     out = torch.zeros(n, n, device=tril.device, dtype=tril.dtype)
     out[rows, cols] = tril

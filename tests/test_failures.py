@@ -1,0 +1,123 @@
+"""Failures are raised on the host with a usable message and leave the model as it was: exceptions
+inside hooked passes, checkpoints that do not fit, damaged curvature files, misuse of the API."""
+import copy
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+import asdl_b200 as asdl
+from conftest import make_net, make_data
+
+
+def _step(gm, model, x, t):
+    dummy = gm.setup_model_call(model, x)
+    gm.setup_loss_call(F.cross_entropy, dummy, t)
+    return gm.forward_and_backward()
+
+
+def _n_hooks(model):
+    return sum(len(m._forward_hooks) + len(m._forward_pre_hooks) + len(m._backward_hooks) + len(m._backward_pre_hooks)
+               for m in model.modules())
+
+
+class _Boom(nn.Module):
+    def forward(self, x):
+        raise RuntimeError('boom')
+
+
+@pytest.mark.parametrize('maker', [asdl.KfacGradientMaker, asdl.FusedKfacGradientMaker, asdl.DiagNaturalGradientMaker])
+def test_exception_in_forward_removes_the_hooks(maker):
+    model = nn.Sequential(nn.Linear(5, 4), _Boom())
+    x, t = make_data('mlp', 8, 'cross_entropy')
+    gm = maker(model, asdl.PreconditioningConfig(data_size=8, damping=1e-2))
+    before = _n_hooks(model)
+    with pytest.raises(RuntimeError, match='boom'):
+        _step(gm, model, x, t)
+    assert _n_hooks(model) == before
+    model[1] = nn.Identity()   # the maker is usable again once the model is
+    gm = maker(model, asdl.PreconditioningConfig(data_size=8, damping=1e-2))
+    _, loss = _step(gm, model, x, t)
+    assert torch.isfinite(loss)
+
+
+def test_exception_in_loss_removes_the_hooks():
+    model = make_net('mlp')
+    x, t = make_data('mlp', 8, 'cross_entropy')
+    gm = asdl.KfacGradientMaker(model, asdl.PreconditioningConfig(data_size=8, damping=1e-2))
+
+    def bad_loss(y, t, reduction="mean"):
+        raise ValueError('bad loss')
+
+    dummy = gm.setup_model_call(model, x)
+    gm.setup_loss_call(bad_loss, dummy, t)
+    with pytest.raises(ValueError, match='bad loss'):
+        gm.forward_and_backward()
+    assert _n_hooks(model) == 0
+
+
+def test_checkpoint_of_another_architecture_is_refused_at_load():
+    model = make_net('mlp')
+    x, t = make_data('mlp', 8, 'cross_entropy')
+    cfg = asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=0.3)
+    gm = asdl.KfacGradientMaker(model, cfg)
+    _step(gm, model, x, t)
+    state = copy.deepcopy(gm.state_dict())
+    key = next(k for k in state['curvature'] if k.endswith('kron.A'))
+    state['curvature'][key] = torch.zeros(3, 3)
+    fresh = asdl.KfacGradientMaker(make_net('mlp'), cfg)
+    with pytest.raises(ValueError, match='curvature checkpoint entry'):
+        fresh.load_state_dict(state)
+
+
+def test_damaged_curvature_file_is_reported(tmp_path):
+    model = make_net('mlp')
+    x, t = make_data('mlp', 8, 'cross_entropy')
+    gm = asdl.KfacGradientMaker(model, asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=0.3))
+    _step(gm, model, x, t)
+    fisher = model[0].fisher
+    paths = fisher.save(str(tmp_path), 'layer0')
+    a_file = os.path.join(str(tmp_path), paths['kron']['A_tril'])
+    good = np.load(a_file)
+    np.save(a_file, good[:-1])  # a lower triangle with one element missing is not a triangle of any n
+    kron_paths = {k: os.path.join(str(tmp_path), v) for k, v in paths['kron'].items()}
+    with pytest.raises(ValueError, match='packed triangle'):
+        fisher.load(kron_path=kron_paths)
+    with open(a_file, 'wb') as f:
+        f.write(b'not an npy file')
+    with pytest.raises(Exception):
+        fisher.load(kron_path=kron_paths)
+    np.save(a_file, good)
+    fisher.load(kron_path=kron_paths)  # and the intact file loads again
+    assert fisher.kron.A.shape == (5, 5)
+
+
+def test_api_misuse_messages():
+    model = make_net('mlp')
+    x, t = make_data('mlp', 8, 'cross_entropy')
+    gm = asdl.KfacGradientMaker(model, asdl.PreconditioningConfig(data_size=8, damping=1e-2))
+    with pytest.raises((ValueError, RuntimeError)):
+        gm.forward_and_backward()  # nothing set up
+    gm.setup_model_call(model, x)
+    with pytest.raises((ValueError, RuntimeError)):
+        gm.forward_and_backward()  # no loss set up
+    with pytest.raises((ValueError, TypeError)):
+        asdl.KfacGradientMaker(model, asdl.PreconditioningConfig(data_size=8), fisher_type='no_such_type')
+    with pytest.raises(ValueError):
+        asdl.get_update_schedule(1.5, 0.0, 10)
+
+
+def test_non_finite_factor_is_reported_not_inverted():
+    """A factor with a NaN cannot be inverted; the maker says which step failed instead of
+    writing NaNs into the gradients."""
+    model = make_net('mlp')
+    x, t = make_data('mlp', 8, 'cross_entropy')
+    gm = asdl.KfacGradientMaker(model, asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=0.3),
+                                fisher_type=asdl.FISHER_EMP)
+    x_bad = x.clone()
+    x_bad[0, 0] = float('nan')
+    with pytest.raises(Exception):
+        _step(gm, model, x_bad, t)
