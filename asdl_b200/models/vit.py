@@ -10,7 +10,7 @@ import torch.nn.functional as F
 
 from .layers import FusedLayerNorm, grouped_bf16_weights
 
-__all__ = ['VisionTransformer', 'vit_b_16', 'vit_tiny']
+__all__ = ['VisionTransformer', 'vit_b_16', 'vit_tiny_patch16_224', 'vit_tiny']
 
 
 class SelfAttention(nn.Module):
@@ -76,6 +76,12 @@ class VisionTransformer(nn.Module):
 
 def vit_b_16(num_classes=1000):
     return VisionTransformer(224, 16, 12, 12, 768, 3072, num_classes)
+
+
+def vit_tiny_patch16_224(num_classes=10):
+    """ViT-Ti/16 (12 blocks of width 192 with 3 heads): the transformer of the reference's CIFAR-10
+    recipes (examples/arxiv_results/configs/vit/*.json), there with pretrained weights, here random."""
+    return VisionTransformer(224, 16, 12, 3, 192, 768, num_classes)
 
 
 def vit_tiny(num_classes=10, image_size=32):

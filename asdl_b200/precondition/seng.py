@@ -102,7 +102,8 @@ class SengGradientMaker(PreconditionedGradientMaker):
             if bias:
                 a = torch.cat([a, a.new_ones(a.shape[0], 1, a.shape[2])], dim=1)
             root = v.abs().sqrt()
-            mat_in = torch.einsum('n,nir->ir', v / root.sum(), a)
+            # all-zero v (the sampled coordinates saw dead units only) leaves the gradient as it is
+            mat_in = torch.einsum('n,nir->ir', v / root.sum().clamp_min(torch.finfo(v.dtype).tiny), a)
             mat_out = torch.einsum('n,nor->or', root, e)
             g = g - (mat_out @ mat_in.T) / N ** 2
             if bias:

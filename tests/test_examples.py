@@ -41,3 +41,73 @@ def test_cpu_mlp_kfac_benchmark_matches_dense_oracle(impl):
     rec = json.loads(_run('benchmarks/cpu_mlp_kfac.py', '--impl', impl, '--steps', '2').strip().splitlines()[-1])
     assert rec['max_rel_err_vs_dense_oracle'] < 1e-5
     assert rec['last_loss'] < rec['first_loss']
+
+
+def test_batched_augmentations_match_per_sample_definitions():
+    import torch
+    import torch.nn.functional as F
+    sys.path.insert(0, os.path.join(ROOT, 'examples'))
+    from augment import batch_cutout, batch_random_crop_flip, Cutout
+    x = torch.randn(6, 3, 8, 8)
+    g = torch.Generator().manual_seed(3)
+    out = batch_random_crop_flip(x, padding=2, generator=g)
+    g = torch.Generator().manual_seed(3)   # replay the draws: dy, dx, then the flip coin
+    dy = torch.randint(-2, 3, (6, 1, 1), generator=g).flatten()
+    dx = torch.randint(-2, 3, (6, 1, 1), generator=g).flatten()
+    flip = (torch.rand(6, 1, 1, generator=g) < 0.5).flatten()
+    for i in range(6):
+        padded = F.pad(x[i], (2, 2, 2, 2))
+        crop = padded[:, 2 + dy[i]:2 + dy[i] + 8, 2 + dx[i]:2 + dx[i] + 8]
+        want = crop.flip(-1) if flip[i] else crop
+        torch.testing.assert_close(out[i], want)
+    holes = batch_cutout(torch.ones(5, 2, 16, 16), n_holes=1, length=4, generator=torch.Generator().manual_seed(0))
+    zeros = (holes[:, 0] == 0).flatten(1).sum(dim=1)
+    assert ((zeros > 0) & (zeros <= 16)).all() and torch.equal(holes[:, 0], holes[:, 1])
+    assert Cutout(2, 4)(torch.ones(3, 16, 16)).shape == (3, 16, 16)
+
+
+def test_train_script_accepts_reference_style_config(tmp_path):
+    import json
+    cfg = {'dataset': 'synthetic', 'model': 'resnet18', 'optim': 'kfac_mc', 'lr': 0.01, 'momentum': 0.9, 'damping': 1e-3,
+           'curvature_update_interval': 2, 'clipping_norm': 10, 'ema_decay': -1, 'data_augmentation': True, 'cutout': True,
+           'n_holes': 1, 'length': 16, 'batch_size': 8, 'epochs': 1, 'weight_decay': 5e-4}
+    path = tmp_path / 'cfg.json'
+    path.write_text(json.dumps(cfg))
+    log = tmp_path / 'log.jsonl'
+    out = _run('examples/train.py', '--config', str(path), '--steps-per-epoch', '3', '--no-cuda', '--cosine',
+               '--label-smoothing', '0.1', '--log-json', str(log))
+    assert 'epoch 1' in out
+    lines = [json.loads(line) for line in log.read_text().splitlines()]
+    assert lines[0]['epoch'] == 1 and 'avg_step_time_ms' in lines[-1] and lines[-1]['stopped'] is None
+
+
+def test_every_recipe_parses_and_builds_its_maker(monkeypatch):
+    """All entries of examples/configs/recipes.json name valid options, models and methods."""
+    import json
+    sys.path.insert(0, os.path.join(ROOT, 'examples'))
+    import train
+    with open(os.path.join(ROOT, 'examples', 'configs', 'recipes.json')) as f:
+        table = json.load(f)
+    count = 0
+    for family, entries in table.items():
+        if family.startswith('_'):
+            continue
+        for method in entries:
+            if method == 'common':
+                continue
+            monkeypatch.setattr(sys, 'argv', ['train.py', '--recipe', f'{family}/{method}', '--dataset', 'synthetic',
+                                              '--batch-size', '4', '--no-cuda'])
+            args = train.parse_args()
+            assert args.dataset == 'synthetic' and args.batch_size == 4 and args.optim in train.OPTIMS
+            assert args.preconditioner_upd_interval == args.curvature_upd_interval
+            if family in ('mlp', 'resnet18'):   # the big families are built in the model tests
+                model = train.make_model(args.model, (3, 32, 32), 10, 32, args.depth)
+                assert train.make_grad_maker(args, model) is not None
+            count += 1
+    assert count == 25
+
+
+def test_recipe_runs_end_to_end():
+    out = _run('examples/train.py', '--recipe', 'mlp/kfac', '--dataset', 'synthetic', '--width', '32', '--batch-size', '8',
+               '--steps-per-epoch', '3', '--epochs', '1', '--no-cuda')
+    assert 'epoch 1' in out

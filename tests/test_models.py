@@ -145,3 +145,25 @@ def test_fused_layer_norm_is_layer_norm_on_cpu():
     x = torch.randn(3, 7, 48)
     torch.testing.assert_close(a(x), b(x))
     assert isinstance(a, nn.LayerNorm)
+
+
+def test_cifar_family_steps_through_its_makers():
+    from asdl_b200.models import MLP, SmallCNN, resnet18, resnet34, vit_tiny_patch16_224
+    torch.manual_seed(0)
+    x, t = torch.randn(4, 3, 32, 32), torch.randint(0, 10, (4,))
+    cfg = asdl.PreconditioningConfig(data_size=4, damping=1e-2)
+    plain, fused = resnet18(width=8), resnet18(width=8, fused=True)
+    fused.load_state_dict(plain.state_dict())
+    torch.testing.assert_close(plain(x), fused(x))
+    _steps(asdl.KfacGradientMaker(plain, cfg, fisher_type=asdl.FISHER_EMP), plain, x, F.cross_entropy, t, n=2)
+    _steps(asdl.FusedKfacGradientMaker(fused, cfg, fisher_type=asdl.FISHER_EMP), fused, x, F.cross_entropy, t, n=2)
+    assert plain.blocks[2].downsample[0].fisher.kron.A_inv.shape == (8, 8)         # 1 x 1 convolution, 8 -> 16 channels
+    assert len(resnet34(width=8).blocks) == 16
+    mlp = MLP(width=16, depth=4, in_features=3 * 32 * 32)
+    assert sum(isinstance(m, nn.Linear) for m in mlp.modules()) == 4
+    _steps(asdl.KronPsgdGradientMaker(mlp, asdl.PreconditioningConfig()), mlp, x, F.cross_entropy, t, n=2)
+    cnn = SmallCNN(in_channels=3, image_size=32)
+    _steps(asdl.SengGradientMaker(cnn, asdl.PreconditioningConfig(data_size=4, damping=1e-1), sketching_size=3,
+                                  truncated_rank=2), cnn, x, F.cross_entropy, t, n=2)
+    vit = vit_tiny_patch16_224()
+    assert len(vit.layers) == 12 and vit.head.in_features == 192 and vit.layers[0].attn.heads == 3
