@@ -192,7 +192,8 @@ class Operation:
             return
         a = self.preprocess_in_data(self._module, in_data, out_data)
         for name in todo:
-            _FWD_HANDLERS[name](self, a, out_data)
+            with nvtx_range(_RANGE_NAMES_FWD.get(name, name)):
+                _FWD_HANDLERS[name](self, a, out_data)
 
     def _fwd_kron(self, a, out_data):
         self.accumulate_result(self.cov_kron_A(self._module, a).mul_(self._cov_scale), OP_COV_KRON, 'A')
@@ -227,7 +228,8 @@ class Operation:
         for name in list(names):
             handler = _BWD_HANDLERS.get(name)
             if handler is not None:
-                handler(self, name, a, g, vector)
+                with nvtx_range(_RANGE_NAMES_BWD.get(name, name)):
+                    handler(self, name, a, g, vector)
 
     def _bwd_cov(self, name, a, g, vector):
         _, _, bg = self.collect_batch_grads(a, g)
@@ -465,6 +467,10 @@ _BWD_HANDLERS = {
     OP_SPATIAL_MEAN_OUTGRADS: Operation._bwd_mean_outgrads,
     OP_SKETCHED_GRAM: Operation._bwd_sketched_gram,
 }
+#: range names of the hook-time work (NVTX and phase profiles); the Kronecker ops have a forward and a backward half
+_RANGE_NAMES_FWD = {OP_COV_KRON: 'cov_kron_A', OP_COV_SWIFT_KRON: 'cov_swift_kron_A'}
+_RANGE_NAMES_BWD = {OP_COV_KRON: 'cov_kron_B', OP_COV_SWIFT_KRON: 'cov_swift_kron_B',
+                    OP_COV_KRON_INV: 'cov_kron_inv', OP_COV_SWIFT_KRON_INV: 'cov_swift_kron_inv'}
 
 
 class OperationContext:

@@ -18,6 +18,7 @@ import torch
 import torch.nn as nn
 
 from ..grad_maker import GradientMaker
+from ..utils import nvtx_range
 
 __all__ = ['PreconditionedGradientMaker', 'PreconditioningConfig', 'get_update_schedule',
            'INTERVAL_CONSTANT', 'INTERVAL_STEP', 'INTERVAL_LINEAR', 'INTERVAL_TYPES']
@@ -147,13 +148,17 @@ class PreconditionedGradientMaker(GradientMaker):
         step = self.state['step']
         self._startup()
         if self.do_forward_and_backward(step):
-            self.forward()
-            self.backward()
+            with nvtx_range('forward_and_backward'):
+                self.forward()
+                self.backward()
         if self.do_update_curvature(step):
-            self.update_curvature()
+            with nvtx_range('update_curvature'):
+                self.update_curvature()
         if self.do_update_preconditioner(step):
-            self.update_preconditioner()
-        self.precondition()
+            with nvtx_range('update_preconditioner'):
+                self.update_preconditioner()
+        with nvtx_range('precondition'):
+            self.precondition()
         self._teardown()
         self.state['step'] += 1
         return self._model_output, self._loss

@@ -20,11 +20,14 @@ from torch import nn
 import torch.nn.functional as F
 from torch.utils.data import BatchSampler, DataLoader, Subset
 
+from . import profiling
+from .profiling import PhaseProfile, time_funcs
+
 __all__ = [
     'original_requires_grad', 'record_original_requires_grad',
     'restore_original_requires_grad', 'skip_param_grad', 'im2col_2d',
     'im2col_2d_slow', 'cholesky_inv', 'cholesky_solve', 'smw_inv',
-    'PseudoBatchLoaderGenerator', 'nvtx_range', 'has_reduction'
+    'PseudoBatchLoaderGenerator', 'nvtx_range', 'has_reduction', 'PhaseProfile', 'time_funcs'
 ]
 
 _FLAG = '_original_requires_grad'
@@ -178,12 +181,15 @@ class PseudoBatchLoaderGenerator:
 
 @contextmanager
 def nvtx_range(msg, *args, **kwargs):
-    """NVTX range when CUDA is present, no-op otherwise."""
+    """NVTX range when CUDA is present; while a :class:`~asdl_b200.utils.profiling.PhaseProfile`
+    is active the range is also timed (CUDA events, or the wall clock on CPU) under the same name."""
+    profile = profiling.active_profile()
+    timed = profile.range(msg) if profile is not None else nullcontext()
     if torch.cuda.is_available():
-        with torch.cuda.nvtx.range(msg, *args, **kwargs):
+        with torch.cuda.nvtx.range(msg, *args, **kwargs), timed:
             yield
     else:
-        with nullcontext():
+        with timed:
             yield
 
 

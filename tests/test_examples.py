@@ -111,3 +111,45 @@ def test_recipe_runs_end_to_end():
     out = _run('examples/train.py', '--recipe', 'mlp/kfac', '--dataset', 'synthetic', '--width', '32', '--batch-size', '8',
                '--steps-per-epoch', '3', '--epochs', '1', '--no-cuda')
     assert 'epoch 1' in out
+
+
+def test_nsys_report_attributes_kernels_to_ranges(tmp_path):
+    """A hand-made export: two occurrences of range 'cov' with kernels of 30 + 20 and 50 ns launched
+    inside them, one 'inv' range with a memcpy, and a kernel launched outside every range."""
+    import sqlite3
+    sys.path.insert(0, os.path.join(ROOT, 'benchmarks'))
+    import nsys_nvtx_report as report
+    db = str(tmp_path / 'trace.sqlite')
+    con = sqlite3.connect(db)
+    con.execute('CREATE TABLE NVTX_EVENTS (start INTEGER, end INTEGER, text TEXT)')
+    con.executemany('INSERT INTO NVTX_EVENTS VALUES (?, ?, ?)', [(100, 200, 'cov'), (300, 420, 'cov'), (500, 600, 'inv'),
+                                                                 (700, None, 'open')])
+    con.execute('CREATE TABLE CUPTI_ACTIVITY_KIND_RUNTIME (start INTEGER, end INTEGER, correlationId INTEGER)')
+    con.executemany('INSERT INTO CUPTI_ACTIVITY_KIND_RUNTIME VALUES (?, ?, ?)',
+                    [(110, 115, 1), (150, 155, 2), (310, 315, 3), (510, 515, 4), (650, 655, 5)])
+    con.execute('CREATE TABLE CUPTI_ACTIVITY_KIND_KERNEL (start INTEGER, end INTEGER, correlationId INTEGER)')
+    con.executemany('INSERT INTO CUPTI_ACTIVITY_KIND_KERNEL VALUES (?, ?, ?)',
+                    [(1000, 1030, 1), (1030, 1050, 2), (1100, 1150, 3), (1300, 1400, 5)])
+    con.execute('CREATE TABLE CUPTI_ACTIVITY_KIND_MEMCPY (start INTEGER, end INTEGER, correlationId INTEGER)')
+    con.execute('INSERT INTO CUPTI_ACTIVITY_KIND_MEMCPY VALUES (1200, 1207, 4)')
+    con.commit()
+    con.close()
+    table = report.collect(db)
+    assert set(table) == {'cov', 'inv'}
+    assert table['cov']['ncalls'] == 2 and table['cov']['kernel'] == 50 and table['cov']['runtime'] == 110
+    assert table['cov']['kernel_stdev'] == 0 and abs(table['cov']['runtime_stdev'] - 200 ** 0.5) < 1e-9
+    assert table['inv']['kernel'] == 0 and table['inv']['memcpy'] == 7 and table['inv']['sync'] == 0
+    assert report.collect(db, ignore_first=True)['cov']['ncalls'] == 1
+    assert set(report.collect(db, keywords=['in'])) == {'inv'}
+    assert 'cov' in _run('benchmarks/nsys_nvtx_report.py', db, '--json', str(tmp_path / 'out.json'))
+
+
+def test_time_step_reports_phases(tmp_path):
+    import json
+    cfg = tmp_path / 'cfg.yaml'
+    cfg.write_text('optim: kfac\nmodel: cnn\nbatch_size: 8\nema_decay: 0.1\niters: 3\nwarmup: 1\n')
+    out = _run('benchmarks/time_step.py', '--config', str(cfg), '--no-cuda', '--json')
+    ranges = json.loads(out.strip().splitlines()[-1])['ranges']
+    assert ranges['step']['ncalls'] == 3 and ranges['optimizer_step']['ncalls'] == 3
+    assert ranges['step']['mean_ms'] >= ranges['update_curvature']['mean_ms'] > 0
+    assert 'cov_kron_A' in ranges and 'precondition' in ranges

@@ -196,3 +196,42 @@ def test_gradient_utilities_against_autograd():
     ref = torch.autograd.grad(ref_loss, params)
     for p, r in zip(params, ref):
         torch.testing.assert_close(p.grad, r, rtol=1e-4, atol=1e-6)
+
+
+def test_phase_profile_times_library_and_user_ranges():
+    from asdl_b200.utils import PhaseProfile, nvtx_range, time_funcs
+    from asdl_b200.utils.profiling import active_profile
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(6, 5), nn.ReLU(), nn.Linear(5, 3))
+    x, t = torch.randn(8, 6), torch.randint(0, 3, (8,))
+    gm = asdl.KfacGradientMaker(model, asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=0.5,
+                                                                  preconditioner_upd_interval=2,
+                                                                  curvature_upd_interval=1))
+
+    def step():
+        d = gm.setup_model_call(model, x)
+        gm.setup_loss_call(F.cross_entropy, d, t)
+        gm.forward_and_backward()
+
+    assert active_profile() is None
+    with PhaseProfile(cuda=False) as prof:
+        assert active_profile() is prof
+        for _ in range(4):
+            with nvtx_range('user_step'):
+                step()
+    assert active_profile() is None
+    table = prof.table()
+    assert table['user_step']['ncalls'] == 4 and table['update_curvature']['ncalls'] == 4
+    assert table['update_preconditioner']['ncalls'] == 2          # every second step
+    assert table['cov_kron_A']['ncalls'] == 8 and table['cov_kron_B']['ncalls'] == 8   # two layers, four steps
+    assert table['user_step']['total_ms'] >= table['update_curvature']['total_ms'] > 0
+    assert any(name.startswith('inv_kron') for name in table)
+    assert 'user_step' in prof.report().splitlines()[1]            # sorted by total time: the enclosing range first
+    with PhaseProfile(cuda=False, skip_first=3) as prof:
+        for _ in range(4):
+            with nvtx_range('user_step'):
+                step()
+    assert prof.table()['user_step']['ncalls'] == 1 and prof.reduce_max()['user_step']['ncalls'] == 1
+    table = time_funcs([step, lambda: None], name='kfac_', func_names=['step', 'noop'], num_iters=3, num_warmups=1)
+    assert table['kfac_step']['ncalls'] == 3 and table['kfac_Iter']['mean_ms'] >= table['kfac_step']['mean_ms']
+    assert table['kfac_noop']['mean_ms'] < table['kfac_step']['mean_ms']
