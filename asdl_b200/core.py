@@ -133,14 +133,17 @@ def _save_context(model, ops_to_save, targets, ignore_modules):
 
 
 def save_inputs_outgrads(model: nn.Module, targets=None, ignore_modules=None) -> OperationContext:
+    """Context in which hooks keep every supported layer's inputs and output gradients (``cxt.in_data(module)``, ``cxt.out_grads(module)``)."""
     return _save_context(model, (OP_SAVE_INPUTS, OP_SAVE_OUTGRADS), targets, ignore_modules)
 
 
 def save_inputs(model: nn.Module, targets=None, ignore_modules=None) -> OperationContext:
+    """Context in which hooks keep every supported layer's inputs."""
     return _save_context(model, (OP_SAVE_INPUTS,), targets, ignore_modules)
 
 
 def save_outgrads(model: nn.Module, targets=None, ignore_modules=None) -> OperationContext:
+    """Context in which hooks keep every supported layer's output gradients."""
     return _save_context(model, (OP_SAVE_OUTGRADS,), targets, ignore_modules)
 
 

@@ -48,6 +48,11 @@ def roofline_ms(flop: float, n_bytes: float, peak_tflops: float = 1413.5, peak_g
 
 
 class Counter:
+    """Base of the analytic cost models: ``count_flop_numel(module, ...)`` returns the floating-point
+    operations and the number of stored values one phase of a method costs on ``module`` (Linear, Conv2d or
+    MultiheadAttention); subclasses define ``cost`` (and ``attn``).  Reference: asdl/counter.py:15-120.
+    """
+
     supported_types = (nn.Linear, nn.Conv2d, nn.MultiheadAttention)
 
     def count_flop_numel(self, module: nn.Module, inputs: Optional[Tensor] = None,
@@ -125,6 +130,8 @@ def _conv_or_linear_macs(d: LayerDims):
 
 
 class Forward(Counter):
+    """Forward pass: one multiply-add per weight and output position; stores the outputs."""
+
     def cost(self, d):
         return _conv_or_linear_macs(d), d.batch_size * d.d_out * d.out_positions
 
@@ -142,6 +149,8 @@ class Forward(Counter):
 
 
 class BackwardWeight(Counter):
+    """Weight gradient: the same multiply-adds as the forward pass; stores one value per parameter."""
+
     def cost(self, d):
         return _conv_or_linear_macs(d), d.n_params
 
@@ -152,6 +161,8 @@ class BackwardWeight(Counter):
 
 
 class BackwardInput(Counter):
+    """Input gradient: the same multiply-adds as the forward pass; stores one value per input element."""
+
     def cost(self, d):
         return _conv_or_linear_macs(d), d.batch_size * (d.c_in * d.in_positions if d.is_conv else d.d_in)
 
@@ -191,17 +202,24 @@ def _im2col_flop(d: LayerDims):
 
 
 class KFACStats(Counter):
+    """K-FAC statistics: patch extraction for convolutions plus the two Gram products ``a^T a`` (d_in^2 per
+    sample) and ``g^T g`` (d_out^2 per sample); stores both factors."""
+
     def cost(self, d):
         a, b = d.d_in ** 2, d.d_out ** 2
         return _im2col_flop(d) + d.batch_size * (a + b) * 2, a + b
 
 
 class KFACInv(Counter):
+    """K-FAC inverses: n^3 per factor (Cholesky factorisation, triangular inverse and product)."""
+
     def cost(self, d):
         return d.d_in ** 3 + d.d_out ** 3, d.d_in ** 2 + d.d_out ** 2
 
 
 class KFACPrecond(Counter):
+    """K-FAC preconditioning ``B^-1 G A^-1``: two matrix products per layer."""
+
     def cost(self, d):
         return d.d_in * d.d_in * d.d_out * 2 + d.d_in * d.d_out * d.d_out * 2, 0
 
@@ -214,6 +232,9 @@ def _prod(shape):
 
 
 class ShampooStats(Counter):
+    """Shampoo statistics: for every tensor mode of size s the contraction of the gradient with itself over
+    the other modes (2 * numel * s operations, s^2 stored values)."""
+
     @staticmethod
     def flop(*shape):
         return sum(_prod(shape) * s * 2 for s in shape)
@@ -242,6 +263,8 @@ class ShampooInv(Counter):
 
 
 class ShampooPrecond(Counter):
+    """Shampoo preconditioning: one mode product with an s x s root per tensor mode."""
+
     @staticmethod
     def flop(*shape):
         return sum(_prod(shape) * s * 2 for s in shape)
@@ -267,6 +290,9 @@ class LBFGSPrecond(Counter):
 
 
 class SMWNGStats(Counter):
+    """Sherman-Morrison-Woodbury natural gradient statistics: the n x n Gram matrices of inputs and
+    output gradients (n = batch size) and their element-wise product."""
+
     def cost(self, d):
         n2 = d.batch_size ** 2
         if d.is_conv:
@@ -275,6 +301,8 @@ class SMWNGStats(Counter):
 
 
 class SMWNGPrecond(Counter):
+    """SMW natural gradient solve: Cholesky solve of the n x n kernel and the two reductions around it."""
+
     @staticmethod
     def flop(n):
         return n ** 2 + 1 / 3 * n ** 3 + n ** 2  # Gram row sums + Cholesky solve

@@ -435,6 +435,9 @@ class FisherEmp(FisherMaker):
 
 
 def get_fisher_maker(model: nn.Module, config: FisherConfig):
+    """The FisherMaker subclass for ``config.fisher_type`` (exact / Monte-Carlo / empirical) and
+    ``config.loss_type`` (cross-entropy / MSE).  Reference: asdl/fisher.py:500-521.
+    """
     fisher_type, loss_type = config.fisher_type, config.loss_type
     if fisher_type not in _supported_types:
         raise ValueError(f'Invalid fisher_type: {fisher_type}. {_supported_types} are supported.')

@@ -35,6 +35,10 @@ class HessianConfig:
 
 
 class HessianMaker(GradientMaker):
+    """Hessian of the loss in the shapes full / layer_wise / diag (row-by-row double backward), stored as
+    ``module.hessian`` (``SymMatrix``), Hessian-vector products as ``module.hvp``, and the matrix-free tools
+    ``hessian_eig`` / ``hessian_free`` / ``hessian_quadratic_form``.  Reference: asdl/hessian.py:27-289.
+    """
     def __init__(self, model: nn.Module, config):
         super().__init__(model)
         self.config = config

@@ -234,14 +234,17 @@ def empirical_implicit_ntk(model, x1, x2=None, precond=None):
 
 
 def get_preconditioned_kernel_fn(kernel_fn, precond):
+    """``kernel_fn`` with its ``precond`` argument bound to a gradient maker whose ``precondition`` is applied to one side's Jacobian."""
     return partial(kernel_fn, precond=precond)
 
 
 def empirical_class_wise_direct_ntk(model, x1, x2=None, precond=None):
+    """Empirical NTK per output class, c x n1 x n2, from per-example gradients of each logit."""
     return _empirical_class_wise_ntk(model, x1, x2, hadamard=False, precond=precond)
 
 
 def empirical_class_wise_hadamard_ntk(model, x1, x2=None, precond=None):
+    """Empirical NTK per output class, c x n1 x n2, from layer-wise Hadamard products of input and output-gradient Gram matrices."""
     return _empirical_class_wise_ntk(model, x1, x2, hadamard=True, precond=precond)
 
 

@@ -14,6 +14,7 @@ _OPS = set(BASIC_OPS + [OP_COV_KRON, OP_COV_SWIFT_KRON, OP_COV_DIAG, OP_COV_DIAG
 
 
 class Bias(nn.Module):
+    """Learnable scalar added to its input (Fixup-style networks).  Reference: asdl/operations/bias.py:8-24."""
     supported_operations = _OPS
 
     def __init__(self):

@@ -23,6 +23,10 @@ def _rows(t):
 
 
 class Conv2d(Operation):
+    """Statistics of ``nn.Conv2d``.  in_data becomes the patch matrix n x (c_in kh kw) x (h_out w_out),
+    out_grads n x c_out x (h_out w_out); the input-side Kronecker factor is divided by the number of output
+    positions.  Everything but the rFIM operations.  Reference: asdl/operations/conv.py:9-225.
+    """
     supported_operations = set(ALL_OPS) - {OP_RFIM_RELU, OP_RFIM_SOFTMAX}
 
     @staticmethod

@@ -28,6 +28,10 @@ def _eigenbasis(x, gram_fn):
 
 
 class Linear(Operation):
+    """Statistics of ``nn.Linear``.  module.weight: f_out x f_in, module.bias: f_out; in_data: n x f_in and
+    out_grads: n x f_out after leading dimensions (sequence positions) are folded into n.  Supports every
+    operation.  Reference: asdl/operations/linear.py:9-190.
+    """
     supported_operations = set(ALL_OPS)
 
     @staticmethod

@@ -10,6 +10,7 @@ __all__ = ['Scale', 'ScaleExt']
 
 
 class Scale(nn.Module):
+    """Learnable scalar that multiplies its input (Fixup-style networks).  Reference: asdl/operations/scale.py:7-20."""
     def __init__(self):
         super().__init__()
         self.weight = nn.Parameter(torch.ones(1))

@@ -655,11 +655,13 @@ def _check_state_shapes(name, module, items):
 
 
 class FullNaturalGradientMaker(NaturalGradientMaker):
+    """Natural gradient with one dense Fisher matrix over all parameters."""
     def __init__(self, model, config: PreconditioningConfig, *args, **kwargs):
         super().__init__(model, config, *args, **kwargs, fisher_shape=SHAPE_FULL)
 
 
 class LayerWiseNaturalGradientMaker(NaturalGradientMaker):
+    """Natural gradient with one dense Fisher block per layer."""
     def __init__(self, model, config: PreconditioningConfig, *args, **kwargs):
         super().__init__(model, config, *args, **kwargs, fisher_shape=SHAPE_LAYER_WISE)
 
@@ -698,15 +700,18 @@ class EkfacGradientMaker(NaturalGradientMaker):
 
 
 class UnitWiseNaturalGradientMaker(NaturalGradientMaker):
+    """Natural gradient with one small Fisher block per output unit (2 x 2 per feature for normalisation layers)."""
     def __init__(self, model, config: PreconditioningConfig, *args, **kwargs):
         super().__init__(model, config, *args, **kwargs, fisher_shape=SHAPE_UNIT_WISE)
 
 
 class DiagNaturalGradientMaker(NaturalGradientMaker):
+    """Natural gradient with the diagonal of the Fisher matrix."""
     def __init__(self, model, config: PreconditioningConfig, *args, **kwargs):
         super().__init__(model, config, *args, **kwargs, fisher_shape=SHAPE_DIAG)
 
 
 class EmpNaturalGradientMaker(NaturalGradientMaker):
+    """Natural gradient with the empirical Fisher (gradients of the observed labels) in the given shape."""
     def __init__(self, model, config: PreconditioningConfig, *args, **kwargs):
         super().__init__(model, config, *args, **kwargs, fisher_type=FISHER_EMP)

@@ -70,6 +70,11 @@ class PreconditioningConfig:
 
 
 class PreconditionedGradientMaker(GradientMaker):
+    """Template of every preconditioned gradient maker: ``forward_and_backward()`` runs the pass, then
+    ``update_curvature`` / ``update_preconditioner`` when their schedules say so, then ``precondition`` (which
+    rewrites ``param.grad`` in place), and counts the step.  ``state_dict()`` holds the step and the curvature
+    state of the subclass.  Reference: asdl/precondition/prec_grad_maker.py:78-201.
+    """
     _supported_classes = None
 
     def __init__(self, model: nn.Module, config: PreconditioningConfig):

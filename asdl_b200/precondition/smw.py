@@ -39,6 +39,11 @@ class SmwEmpNaturalGradientConfig:
 
 
 class SmwEmpNaturalGradientMaker(GradientMaker):
+    """Exact empirical-Fisher natural gradient of a mini-batch through the n x n Gram matrix of per-example
+    gradients (Sherman-Morrison-Woodbury): the kernel ``sum_l (a a^T) * (g g^T)`` is accumulated in hooks, one
+    Cholesky solve re-weights the per-example losses and a second backward pass forms the gradient.
+    Reference: asdl/precondition/smw.py:36-69.
+    """
     _loss_reduction = 'none'
 
     def __init__(self, model, config):

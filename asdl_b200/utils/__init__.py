@@ -39,6 +39,7 @@ def record_original_requires_grad(param):
 
 
 def restore_original_requires_grad(param):
+    """Puts back the ``requires_grad`` value that :func:`record_original_requires_grad` stored on ``param``."""
     param.requires_grad = getattr(param, _FLAG, param.requires_grad)
 
 

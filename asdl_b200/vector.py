@@ -17,6 +17,10 @@ __all__ = ['ParamVector', 'reduce_vectors', 'normalization', 'orthnormal']
 
 
 class ParamVector:
+    """Ordered map parameter -> tensor of the same shape with vector-space arithmetic (``+``, ``add_``, ``mul_``,
+    ``dot``, ``norm``), slicing by module or parameter, and a flat view for collectives and dense algebra.
+    Reference: asdl/vector.py:11-102.
+    """
     def __init__(self, params: Iterable[torch.Tensor],
                  values: Union[torch.Tensor, Iterable[torch.Tensor]]):
         params = list(params)

@@ -153,3 +153,25 @@ def test_time_step_reports_phases(tmp_path):
     assert ranges['step']['ncalls'] == 3 and ranges['optimizer_step']['ncalls'] == 3
     assert ranges['step']['mean_ms'] >= ranges['update_curvature']['mean_ms'] > 0
     assert 'cov_kron_A' in ranges and 'precondition' in ranges
+
+
+def test_api_reference_is_current(tmp_path):
+    """docs/api.md is what docs/build_api.py writes from the present docstrings, and every public
+    class and function has a docstring."""
+    import inspect
+    import asdl_b200
+    missing = [n for n in dir(asdl_b200) if not n.startswith('_')
+               and (inspect.isclass(getattr(asdl_b200, n)) or inspect.isfunction(getattr(asdl_b200, n)))
+               and not (getattr(asdl_b200, n).__doc__ or '').strip()]
+    assert not missing, missing
+    path = os.path.join(ROOT, 'docs', 'api.md')
+    with open(path) as f:
+        before = f.read()
+    try:
+        _run('docs/build_api.py')
+        with open(path) as f:
+            after = f.read()
+    finally:
+        with open(path, 'w') as f:
+            f.write(before)
+    assert before == after, 'run python docs/build_api.py'
