@@ -46,6 +46,15 @@ def _fisher(model, x, t, shape, **kw):
     return fm
 
 
+def _manager_fisher(model, x, t, data_size):
+    cfg = asdl.FisherConfig(fisher_type=asdl.FISHER_EMP, fisher_shapes=[asdl.SHAPE_LAYER_WISE], data_size=data_size,
+                            loss_type=asdl.LOSS_CROSS_ENTROPY, fisher_attr=asdl.FISHER_EMP)
+    fm = asdl.get_fisher_maker(model, cfg)
+    dummy = fm.setup_model_call(model, x)
+    fm.setup_loss_call(F.cross_entropy, dummy, t)
+    fm.forward_and_backward()
+
+
 def _probe(model):
     g = torch.Generator().manual_seed(9)
     return asdl.ParamVector(list(model.parameters()), [torch.randn(p.shape, generator=g) for p in model.parameters()])
@@ -108,6 +117,24 @@ def _worker(rank, world, port, out_dir):
 
         eigvals, _ = asdl.power_method(summed_fvp, model, top_n=1, max_iters=300, tol=1e-9, is_distributed=True)
         out['top_eig'] = float(eigvals[0])
+        xs, ts = x[rank * n:(rank + 1) * n], t[rank * n:(rank + 1) * n]
+        # MatrixManager: per-rank means, one packed message, average over ranks
+        mm = asdl.MatrixManager(model, asdl.FISHER_EMP)
+        _manager_fisher(model, xs, ts, n)
+        mm.accumulate_matrices('run')
+        mm.reduce_matrices('run', all_reduce=True)
+        out['manager'] = mm.get_matrix(model[0], asdl.FISHER_EMP, 'run').data.clone()
+        # function-space solvers
+        torch.manual_seed(7)
+        K.kernel_free_cross_entropy(model, xs, ts, damping=1e-2, tol=1e-8, is_distributed=True)
+        out['kernel_free'] = torch.cat([p.grad.flatten() for p in model.parameters()]).clone()
+        torch.manual_seed(11 + rank)
+        out['kernel_eig'] = float(K.kernel_eigenvalues(model, xs, top_n=1, max_iters=500, tol=1e-10, is_distributed=True)[0])
+        class_kernels = K.batch(K.empirical_class_wise_direct_ntk, model, x, batch_size=2).permute(2, 0, 1).contiguous()
+        split = [[0, 1], [2]][rank]                      # 3 classes over 2 ranks
+        damped = class_kernels[split] / x.shape[0] + 1e-2 * torch.eye(x.shape[0])
+        K.parallel_efficient_natural_gradient_cross_entropy(model, xs, ts, damped, damping=1e-2)
+        out['parallel_ngd'] = torch.cat([p.grad.flatten() for p in model.parameters()]).clone()
         torch.save(out, os.path.join(out_dir, f'rank{rank}.pt'))
     finally:
         dist.destroy_process_group()
@@ -135,3 +162,18 @@ def test_distributed_entry_points_match_single_process():
     assert abs(ranks[0]['top_eig'] - ranks[1]['top_eig']) < 1e-6 * top
     assert abs(ranks[0]['top_eig'] - top) < 1e-3 * top
     del full
+    fresh = _net()
+    _manager_fisher(fresh, x, t, x.shape[0])
+    K.kernel_free_cross_entropy(model, x, t, damping=1e-2, tol=1e-8)
+    kernel_free = torch.cat([p.grad.flatten() for p in model.parameters()]).clone()
+    jac_kernel = K.batch(K.empirical_direct_ntk, model, x, batch_size=2)           # n x n x c x c
+    n, c = x.shape[0], 3
+    top_kernel = torch.linalg.eigvalsh(jac_kernel.permute(0, 2, 1, 3).reshape(n * c, n * c))[-1].item()
+    class_kernels = K.batch(K.empirical_class_wise_direct_ntk, model, x, batch_size=2).permute(2, 0, 1).contiguous()
+    K.efficient_natural_gradient_cross_entropy(model, x, t, class_kernels / n + 1e-2 * torch.eye(n), damping=1e-2)
+    ngd = torch.cat([p.grad.flatten() for p in model.parameters()]).clone()
+    for r in ranks:
+        torch.testing.assert_close(r['manager'], getattr(fresh[0], asdl.FISHER_EMP).data, rtol=1e-4, atol=1e-6)
+        torch.testing.assert_close(r['kernel_free'], kernel_free, rtol=1e-3, atol=1e-5)
+        assert abs(r['kernel_eig'] - top_kernel) < 1e-3 * top_kernel
+        torch.testing.assert_close(r['parallel_ngd'], ngd, rtol=1e-3, atol=1e-5)
