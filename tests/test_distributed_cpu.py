@@ -72,7 +72,7 @@ def _worker(rank, world, port, kind, out_dir):
     dist.init_process_group('gloo', init_method=f'tcp://127.0.0.1:{port}', rank=rank, world_size=world,
                             timeout=timedelta(seconds=60))
     try:
-        x, t = _data()
+        x, t = _data(4 * world)
         n = x.shape[0] // world
         xs, ts = x[rank * n:(rank + 1) * n], t[rank * n:(rank + 1) * n]
         model = _net()
@@ -83,14 +83,15 @@ def _worker(rank, world, port, kind, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize('kind', ['kfac', 'kfac_noema', 'fused', 'shampoo'])
-def test_data_parallel_matches_single_process(kind):
-    world = 2
+@pytest.mark.parametrize('kind,world', [('kfac', 2), ('kfac_noema', 2), ('fused', 2), ('shampoo', 2),
+                                        ('kfac', 3), ('fused', 3), ('shampoo', 3)])
+def test_data_parallel_matches_single_process(kind, world):
     with tempfile.TemporaryDirectory() as out_dir:
         mp.spawn(_worker, args=(world, _free_port(), kind, out_dir), nprocs=world, join=True)
         results = [torch.load(os.path.join(out_dir, f'rank{r}.pt'), weights_only=False) for r in range(world)]
-    torch.testing.assert_close(results[0]['grads'], results[1]['grads'])  # ranks agree on every gradient
-    x, t = _data()
+    for other in results[1:]:
+        torch.testing.assert_close(results[0]['grads'], other['grads'])  # ranks agree on every gradient
+    x, t = _data(4 * world)
     _, single = _train(kind, _net(), x, t, data_size=x.shape[0])
     if kind == 'shampoo':
         # the statistic of the averaged gradient is what the owner sees: identical to single process
@@ -104,7 +105,7 @@ def test_data_parallel_matches_single_process(kind):
             merged['curvature'].update(r['state']['curvature'])
         model = _net()
         model.load_state_dict(results[0]['weights'])
-        gm = _make('kfac', model, 8)
+        gm = _make('kfac', model, 4 * world)
         gm.load_state_dict(merged)
         assert gm.state['step'] == 4
         assert model[0].fisher.kron.A is not None
