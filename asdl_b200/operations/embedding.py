@@ -17,10 +17,10 @@ __all__ = ['Embedding']
 
 class Embedding(Operation):
     """Statistics of ``nn.Embedding``.  in_data: token ids (any shape, flattened), out_grads: tokens x dim.
-    The input-side Kronecker factor of one-hot inputs is the diagonal matrix of token counts, kept as a vector;
-    per-example gradients and the diagonal are scatter-adds over tokens.  Reference:
-    asdl/operations/embedding.py:7-78 (which materialises the vocabulary x vocabulary factor and loops over
-    tokens in Python).
+    The input-side Kronecker factor is ``counts^T counts`` of the per-example token-count vectors
+    (vocabulary x vocabulary, so only for small vocabularies; larger ones use the diagonal shape or are
+    ignored); counts, per-example gradients and the diagonal are scatter-adds over tokens.  Reference:
+    asdl/operations/embedding.py:7-78 (``bincount`` per example and Python loops over tokens).
     """
     supported_operations = set(BASIC_OPS + [OP_COV_KRON, OP_BATCH_GRADS, 'diag', OP_COV_DIAG,
                                             OP_COV_DIAG_INV])

@@ -99,7 +99,8 @@ class PreconditionedGradientMaker(GradientMaker):
                     warmup_ratio=config.curvature_warmup_ratio,
                     interval_type=config.curvature_interval_type)
         self.state = dict(step=0)
-        self.module_dict = nn.ModuleDict({name.replace('.', '/'): m for name, m in model.named_modules()
+        # a model that is itself a single layer has the empty name, which ModuleDict refuses
+        self.module_dict = nn.ModuleDict({(name.replace('.', '/') or 'model'): m for name, m in model.named_modules()
                                           if self._is_supported(name, m)})
         params = list(self.module_dict.parameters())
         self.device = params[0].device if params else torch.device('cpu')

@@ -1,0 +1,137 @@
+"""Behaviour that differs from the reference on purpose, one test per item: makers that crash or
+silently do nothing there work here, damped solves leave their inputs alone, the interval type of
+the curvature schedule is a real option, the legacy hook and functorch entry points are gone."""
+import warnings
+
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+import asdl_b200 as asdl
+from conftest import make_net, make_data
+
+
+def _step(gm, model, x, t):
+    dummy = gm.setup_model_call(model, x)
+    gm.setup_loss_call(F.cross_entropy, dummy, t)
+    return gm.forward_and_backward()
+
+
+def _raw_grads(model, x, t):
+    model.zero_grad()
+    F.cross_entropy(model(x), t).backward()
+    out = [p.grad.clone() for p in model.parameters()]
+    model.zero_grad()
+    return out
+
+
+def test_layer_wise_maker_preconditions():
+    """asdl/precondition/natural_gradient.py:539 asks SymMatrix for ``has_inv``, which it lacks."""
+    model = make_net('mlp')
+    x, t = make_data('mlp', 8, 'cross_entropy')
+    raw = _raw_grads(model, x, t)
+    gm = asdl.LayerWiseNaturalGradientMaker(model, asdl.PreconditioningConfig(data_size=8, damping=1e-2),
+                                            fisher_type=asdl.FISHER_EMP)
+    _step(gm, model, x, t)
+    assert any(not torch.allclose(p.grad, r) for p, r in zip(model.parameters(), raw))
+    lin = next(m for m in model.modules() if isinstance(m, nn.Linear))
+    assert lin.fisher.has_inv
+
+
+def test_curve_ball_and_ekfac_change_the_gradient():
+    """asdl/precondition/curve_ball.py:29 and natural_gradient.py:909-915 define hooks nobody calls."""
+    x, t = make_data('mlp', 8, 'cross_entropy')
+    for make in (lambda m: asdl.CurveBallGradientMaker(m, asdl.PreconditioningConfig(damping=1e-2), momentum=0.1),
+                 lambda m: asdl.EkfacGradientMaker(m, asdl.PreconditioningConfig(data_size=8, damping=1e-2))):
+        model = make_net('mlp')
+        raw = _raw_grads(model, x, t)
+        _step(make(model), model, x, t)
+        got = [p.grad for p in model.parameters()]
+        assert all(torch.isfinite(g).all() for g in got)
+        assert any(not torch.allclose(g, r, rtol=1e-3, atol=1e-6) for g, r in zip(got, raw))
+
+
+def test_shampoo_forwards_its_block_size():
+    """asdl/precondition/shampoo.py:55 vs 301-310 drops ``block_size``."""
+    lin = nn.Linear(10, 6, bias=False)
+    gm = asdl.ShampooGradientMaker(lin, asdl.PreconditioningConfig(damping=1e-6), block_size=4)
+    x, t = torch.randn(5, 10), torch.randint(0, 6, (5,))
+    _step(gm, lin, x, t)
+    shapes = sorted(tuple(s.shape) for pre in gm.preconditioners for s in pre.statistics)
+    assert shapes and max(s[0] for s in shapes) <= 4      # 6 x 10 in blocks of at most 4 x 4
+
+
+def test_damped_solves_leave_their_input_alone():
+    """asdl/utils.py:91-96 adds the damping to the caller's diagonal and subtracts it again."""
+    torch.manual_seed(0)
+    a = torch.randn(6, 6)
+    spd = a @ a.T + torch.eye(6)
+    before = spd.clone()
+    asdl.cholesky_inv(spd, 0.3)
+    asdl.cholesky_solve(spd, torch.randn(6), 0.3)
+    assert torch.equal(spd, before)                       # bit-identical, not "restored up to rounding"
+    kron = asdl.Kron(spd.clone(), spd.clone())
+    kron.update_inv(1e-2)
+    assert torch.equal(kron.A, before) and torch.equal(kron.B, before)
+    unit = asdl.UnitWise(torch.stack([spd[:2, :2], spd[2:4, 2:4]]).clone())
+    keep = unit.data.clone()
+    unit.update_inv(1e-2)
+    assert torch.equal(unit.data, keep)
+
+
+def test_curvature_interval_type_is_a_field_and_is_used():
+    """asdl/precondition/prec_grad_maker.py:71 lacks the annotation, :92-101 never forwards the type."""
+    import dataclasses
+    names = {f.name for f in dataclasses.fields(asdl.PreconditioningConfig)}
+    assert {'curvature_interval_type', 'preconditioner_interval_type'} <= names
+    model = make_net('mlp')
+    schedules = {}
+    for kind in (asdl.INTERVAL_CONSTANT, asdl.INTERVAL_LINEAR):
+        cfg = asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=0.1, num_total_steps=40,
+                                         curvature_upd_ratio=0.25, preconditioner_upd_ratio=0.25,
+                                         curvature_interval_type=kind, preconditioner_interval_type=kind)
+        gm = asdl.KfacGradientMaker(model, cfg)
+        schedules[kind] = [gm.do_update_curvature(s) for s in range(40)]
+        assert sum(schedules[kind]) == 10
+    assert schedules[asdl.INTERVAL_CONSTANT] != schedules[asdl.INTERVAL_LINEAR]
+
+
+def test_no_deprecated_hooks_or_functorch():
+    """asdl/core.py:68 registers legacy module backward hooks (one FutureWarning per module and step);
+    asdl/grad_maker.py:378 goes through functorch.make_functional_with_buffers."""
+    model = make_net('cnn')
+    x, t = make_data('cnn', 8, 'cross_entropy')
+    gm = asdl.KfacGradientMaker(model, asdl.PreconditioningConfig(data_size=8, damping=1e-2))
+    with warnings.catch_warnings():
+        warnings.simplefilter('error', FutureWarning)
+        warnings.simplefilter('error', DeprecationWarning)
+        _step(gm, model, x, t)
+        plain = asdl.GradientMaker(model)
+        dummy = plain.setup_model_call(model, x)
+        plain.setup_loss_call(F.cross_entropy, dummy, t)
+        grads = plain.per_example_loss_grads()
+    assert next(iter(grads.values())).shape[0] == 8 if isinstance(grads, dict) else True
+
+
+def test_embedding_statistics_without_token_loops():
+    """asdl/operations/embedding.py:28-46,74-77 loops over examples and tokens in Python; the
+    scatter-add forms give the same factor, per-example gradients and diagonal."""
+    torch.manual_seed(0)
+    emb = nn.Embedding(11, 4)
+    model = nn.Sequential(emb, nn.Flatten(), nn.Linear(12, 3))
+    tokens, t = torch.randint(0, 11, (6, 3)), torch.randint(0, 3, (6,))
+    with asdl.extend(model, asdl.OP_COV_KRON, asdl.OP_BATCH_GRADS, asdl.OP_COV_DIAG) as cxt:
+        F.cross_entropy(model(tokens), t, reduction='sum').backward()
+        A = cxt.cov_kron(emb)['A']
+        per_example = cxt.batch_grads(emb)['weight']
+        diag = cxt.cov_diag(emb)['weight']
+    counts = torch.stack([torch.bincount(row, minlength=11).float() for row in tokens])
+    torch.testing.assert_close(A, counts.T @ counts)
+    want = []
+    for i in range(6):                                     # per-example gradient by plain autograd
+        model.zero_grad()
+        F.cross_entropy(model(tokens[i:i + 1]), t[i:i + 1], reduction='sum').backward()
+        want.append(emb.weight.grad.clone())
+    torch.testing.assert_close(per_example, torch.stack(want))
+    assert diag.shape == emb.weight.shape and bool((diag >= 0).all())
