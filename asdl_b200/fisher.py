@@ -181,7 +181,20 @@ class FisherMaker(GradientMaker):
                 if value is not None:
                     setattr(module, attr, value)
 
+        def adopt_promoted_factors(module):
+            # a wide swift factor that received a second contribution was replaced by the square matrix it
+            # stands for (it cannot be updated in place): hand the new tensor to the stored Kron
+            stored = getattr(module, fisher_attr, None)
+            if stored is None or not stored.has_kron or not cxt.is_operation_registered(module):
+                return
+            results = cxt.cov_kron(module) or {}
+            for key in ('A', 'B'):
+                value = results.get(key)
+                if value is not None and value is not getattr(stored.kron, key):
+                    setattr(stored.kron, key, value)
+
         for module in model.modules():
+            adopt_promoted_factors(module)
             extract(module, cxt.cov_symmatrix, fisher_attr)
             extract(module, cxt.cvp_paramvector, fvp_attr)
         extract(model, cxt.full_cov_symmatrix, fisher_attr)

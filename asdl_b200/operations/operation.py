@@ -16,6 +16,8 @@ Kronecker factor GEMMs are issued through :mod:`asdl_b200.ops` (tcgen05 SYRK on 
 """
 from typing import Dict, List, Tuple
 
+import math
+
 import torch
 import torch.nn as nn
 
@@ -199,8 +201,27 @@ class Operation:
         self.accumulate_result(self.cov_kron_A(self._module, a).mul_(self._cov_scale), OP_COV_KRON, 'A')
 
     def _fwd_swift_kron(self, a, out_data):
-        self.accumulate_result(self.cov_swift_kron_A(self._module, a).mul_(self._cov_scale),
-                               OP_COV_KRON, 'A')
+        self._accumulate_swift(self.cov_swift_kron_A(self._module, a), 'A')
+
+    def _accumulate_swift(self, mat, key):
+        """A swift factor is either the square statistic or, with fewer samples than features, the raw
+        n x d matrix x itself, which stands for ``x^T x / n`` (what ``smw_inv`` inverts).  A raw factor is
+        stored as ``x * sqrt(cov_scale * n)`` so that it stands for ``cov_scale * x^T x``, out of place
+        (x is the layer input or the output gradient that autograd still uses).  Anything that has to be
+        added to an existing entry (moving averages, several backward passes) is added as the square
+        matrix it stands for: raw matrices of different passes have no meaningful sum."""
+        scale = self._cov_scale
+        node = self._walk((OP_COV_KRON,), create=True)
+        old = node.get(key)
+        raw = mat.shape[0] != mat.shape[1]
+        if old is None:
+            node[key] = mat * (math.sqrt(scale * mat.shape[0]) if raw else scale)
+            return
+        new = (mat.T @ mat if raw else mat) * scale
+        if old.shape[0] == old.shape[1]:
+            old += new          # in place: a registered accumulator keeps its identity
+        else:
+            node[key] = old.T @ old / old.shape[0] + new
 
     def _fwd_simple(name, fn_name, needs_out):  # noqa: N805  (builder, not a method)
         def handler(self, a, out_data):
@@ -259,8 +280,10 @@ class Operation:
             self.accumulate_result(cvp.view_as(module.bias), OP_CVP, 'bias')
 
     def _bwd_kron(self, name, a, g, vector):
-        fn = self.cov_kron_B if name == OP_COV_KRON else self.cov_swift_kron_B
-        self.accumulate_result(fn(self._module, g).mul_(self._cov_scale), OP_COV_KRON, 'B')
+        if name == OP_COV_KRON:
+            self.accumulate_result(self.cov_kron_B(self._module, g).mul_(self._cov_scale), OP_COV_KRON, 'B')
+        else:
+            self._accumulate_swift(self.cov_swift_kron_B(self._module, g), 'B')
 
     def _bwd_kron_inv(self, name, a, g, vector):
         module, scale = self._module, self._cov_scale
@@ -272,14 +295,16 @@ class Operation:
 
     def _bwd_swift_kron_inv(self, name, a, g, vector):
         module, scale = self._module, self._cov_scale
-        A = self.cov_swift_kron_A(module, a)
-        B = self.cov_swift_kron_B(module, g)
+
+        def scaled(mat):  # same convention as _accumulate_swift: a raw n x d factor stands for x^T x / n
+            return mat * (scale if mat.shape[0] == mat.shape[1] else math.sqrt(scale * mat.shape[0]))
+
+        A = scaled(self.cov_swift_kron_A(module, a))
+        B = scaled(self.cov_swift_kron_B(module, g))
         damping_A, damping_B = self.cov_kron_damping(A, B)
 
         def invert(mat, damp):
-            if mat.shape[0] == mat.shape[1]:
-                return cholesky_inv(mat * scale, damp)
-            return smw_inv(mat, damp)
+            return cholesky_inv(mat, damp) if mat.shape[0] == mat.shape[1] else smw_inv(mat, damp)
 
         self.accumulate_result(invert(A, damping_A), OP_COV_KRON, 'A_inv')
         self.accumulate_result(invert(B, damping_B), OP_COV_KRON, 'B_inv')

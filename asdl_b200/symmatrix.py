@@ -98,6 +98,22 @@ def _merge(a: Optional[Tensor], b: Optional[Tensor], inplace: bool):
     return a + b
 
 
+def swift_gram(x: Tensor) -> Tensor:
+    """The square matrix a "swift" factor stands for: a wide n x d factor x (n < d) represents
+    ``x^T x / n`` (the Woodbury inverse in :func:`asdl_b200.utils.smw_inv` is the inverse of exactly that
+    plus damping); a square factor is itself."""
+    return x if x.shape[0] == x.shape[1] else x.T @ x / x.shape[0]
+
+
+def _merge_factor(a: Optional[Tensor], b: Optional[Tensor], inplace: bool):
+    """Sum of two Kronecker factors; wide swift factors of different batches cannot be added as they
+    are, so a sum involving one is formed from the square matrices they stand for."""
+    if a is None or b is None or (a.shape[0] == a.shape[1] and b.shape[0] == b.shape[1]):
+        return _merge(a, b, inplace)
+    a, b = swift_gram(a), swift_gram(b)
+    return a.add_(b) if inplace and a.shape == b.shape and a.shape[0] == a.shape[1] and a.is_leaf else a + b
+
+
 # ----------------------------------------------------------------------------------------------
 # containers
 # ----------------------------------------------------------------------------------------------
@@ -155,18 +171,19 @@ class Kron:
     def __add__(self, other):  # inverses are dropped
         if not other.has_data:
             return self
-        return Kron(_merge(self.A, other.A, False), _merge(self.B, other.B, False))
+        return Kron(_merge_factor(self.A, other.A, False), _merge_factor(self.B, other.B, False))
 
     def __iadd__(self, other):
         if other.has_data:
-            self.A = _merge(self.A, other.A, True)
-            self.B = _merge(self.B, other.B, True)
+            self.A = _merge_factor(self.A, other.A, True)
+            self.B = _merge_factor(self.B, other.B, True)
         return self
 
     def mul_(self, value):
         for t in (self.A, self.B):
             if t is not None:
-                t.mul_(value)
+                # a wide swift factor x stands for x^T x / n: scaling that by v scales x by sqrt(v)
+                t.mul_(value if t.shape[0] == t.shape[1] else math.sqrt(value))
         return self
 
     def eigenvalues(self):
@@ -215,8 +232,8 @@ class Kron:
         if not (self.has_A and self.has_B):
             return damping, damping
 
-        def mean_eig(mat):
-            total = mat.trace() if mat.shape[0] == mat.shape[1] else (mat ** 2).sum()
+        def mean_eig(mat):  # a wide swift factor x stands for x^T x / n
+            total = mat.trace() if mat.shape[0] == mat.shape[1] else (mat ** 2).sum() / mat.shape[0]
             return total / mat.shape[-1]
 
         pi = float(torch.sqrt(mean_eig(self.A) / mean_eig(self.B)))

@@ -424,3 +424,31 @@ def test_seng_state_roundtrip():
         results.append([p.grad.clone() for p in model.parameters()])
     for a, b in zip(*results):
         torch.testing.assert_close(a, b)
+
+
+@pytest.mark.parametrize('ema,fisher_type,steps,kwargs', [
+    (-1, asdl.FISHER_EMP, 1, {}), (1.0, asdl.FISHER_EMP, 1, {}), (0.3, asdl.FISHER_EMP, 3, {}),
+    (-1, asdl.FISHER_MC, 1, {'n_mc_samples': 2}), (0.3, asdl.FISHER_MC, 3, {'n_mc_samples': 2}),
+    (-1, asdl.FISHER_EXACT, 1, {})])
+def test_swift_kfac_equals_kfac(ema, fisher_type, steps, kwargs):
+    """With fewer samples than features the swift factors are the raw n x d matrices and the inverse
+    is taken by Woodbury: exact, so the preconditioned gradients equal those of ordinary K-FAC in
+    every mode (inverse in the hooks, moving average, several backward passes per step)."""
+    def run(swift):
+        torch.manual_seed(0)
+        model = nn.Sequential(nn.Linear(12, 9), nn.Tanh(), nn.Linear(9, 3))
+        x, t = torch.randn(4, 12), torch.randint(0, 3, (4,))
+        cfg = asdl.PreconditioningConfig(data_size=4, damping=1e-2, ema_decay=ema)
+        gm = asdl.KfacGradientMaker(model, cfg, fisher_type=fisher_type, swift=swift, **kwargs)
+        opt = torch.optim.SGD(model.parameters(), lr=0.05)
+        for s in range(steps):
+            opt.zero_grad()
+            torch.manual_seed(100 + s)           # the same sampled labels in both runs
+            step(gm, model, x, t)
+            grads = torch.cat([p.grad.flatten() for p in model.parameters()])
+            opt.step()
+        if swift and ema == -1:
+            assert model[0].fisher.kron.A_inv.shape == (12, 12)
+        return grads
+
+    torch.testing.assert_close(run(True), run(False), rtol=1e-4, atol=1e-6)
