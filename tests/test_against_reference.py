@@ -1,0 +1,193 @@
+"""Differential check against the reference package where it is installed beside the repository
+(``baseline/_ref``; skipped otherwise): the same model, data and seeds go through both libraries'
+gradient makers for three optimizer steps and the preconditioned gradients are compared."""
+import os
+import sys
+import warnings
+
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+import asdl_b200 as ours
+
+REF_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 'baseline', '_ref')
+
+
+@pytest.fixture(scope='module')
+def reference():
+    if not os.path.isdir(os.path.join(REF_DIR, 'asdl')):
+        pytest.skip('reference package not installed under baseline/_ref')
+    sys.path.insert(0, REF_DIR)
+    try:
+        import asdl
+    except Exception as exc:  # an environment without the reference's imports
+        pytest.skip(f'reference package not importable: {exc}')
+    finally:
+        sys.path.remove(REF_DIR)
+    return asdl
+
+
+def _net(kind):
+    torch.manual_seed(0)
+    if kind == 'mlp':
+        return nn.Sequential(nn.Linear(6, 5), nn.Tanh(), nn.Linear(5, 3)), torch.randn(8, 6), torch.randint(0, 3, (8,))
+    model = nn.Sequential(nn.Conv2d(2, 3, 3, padding=1), nn.Tanh(), nn.Conv2d(3, 4, 2, stride=2), nn.Flatten(),
+                          nn.Linear(36, 3))
+    return model, torch.randn(8, 2, 6, 6), torch.randint(0, 3, (8,))
+
+
+def _run(lib, make, kind, steps=3):
+    model, x, t = _net(kind)
+    gm = make(lib, model)
+    opt = torch.optim.SGD(model.parameters(), lr=0.01)
+    out = []
+    with warnings.catch_warnings():
+        warnings.simplefilter('ignore')
+        for s in range(steps):
+            opt.zero_grad()
+            torch.manual_seed(50 + s)      # sampled labels and random probes agree between the libraries
+            dummy = gm.setup_model_call(model, x)
+            gm.setup_loss_call(F.cross_entropy, dummy, t)
+            gm.forward_and_backward()
+            out.append(torch.cat([p.grad.flatten() for p in model.parameters()]).clone())
+            opt.step()
+    return out
+
+
+def _cfg(lib, **kw):
+    return lib.PreconditioningConfig(**kw)
+
+
+#: name -> (constructor, relative tolerance, steps compared)
+CASES = {
+    'kfac_emp': (lambda L, m: L.KfacGradientMaker(m, _cfg(L, data_size=8, damping=1e-2), fisher_type='fisher_emp'), 1e-4, 3),
+    'kfac_mc': (lambda L, m: L.KfacGradientMaker(m, _cfg(L, data_size=8, damping=1e-2)), 1e-4, 3),
+    'kfac_ema': (lambda L, m: L.KfacGradientMaker(m, _cfg(L, data_size=8, damping=1e-2, ema_decay=0.3),
+                                                  fisher_type='fisher_emp'), 1e-4, 3),
+    'diag': (lambda L, m: L.DiagNaturalGradientMaker(m, _cfg(L, data_size=8, damping=1e-2), fisher_type='fisher_emp'), 1e-5, 3),
+    'full': (lambda L, m: L.FullNaturalGradientMaker(m, _cfg(L, data_size=8, damping=1e-2), fisher_type='fisher_emp'), 1e-4, 3),
+    # inverse roots come from different iterations (batched here), probes pass through different triangular solves
+    'shampoo': (lambda L, m: L.ShampooGradientMaker(m, _cfg(L, damping=1e-6)), 1e-2, 3),
+    'kron_psgd': (lambda L, m: L.KronPsgdGradientMaker(m, _cfg(L)), 5e-3, 3),
+    'psgd': (lambda L, m: L.PsgdGradientMaker(m, _cfg(L)), 1e-5, 3),
+    # the first K-BFGS step is plain; afterwards this library updates the stored inverse, the reference a temporary
+    'kbfgs': (lambda L, m: L.KronBfgsGradientMaker(m, _cfg(L, data_size=8, damping=1e-2, ema_decay=0.1)), 1e-6, 1),
+    'seng': (lambda L, m: L.SengGradientMaker(m, _cfg(L, data_size=8, damping=1e-1), sketching_size=256,
+                                              truncated_rank=16), 1e-5, 3),
+    'smw': (lambda L, m: L.SmwEmpNaturalGradientMaker(m, L.SmwEmpNaturalGradientConfig(data_size=8, damping=1e-2)), 1e-5, 3),
+    'newton': (lambda L, m: L.NewtonGradientMaker(m, L.NewtonGradientConfig(damping=1e-1)), 1e-4, 3),
+}
+
+
+@pytest.mark.parametrize('kind', ['mlp', 'cnn'])
+@pytest.mark.parametrize('name', sorted(CASES))
+def test_same_gradients_as_the_reference(reference, name, kind):
+    make, rtol, steps = CASES[name]
+    want = _run(reference, make, kind)
+    got = _run(ours, make, kind)
+    for w, g in list(zip(want, got))[:steps]:
+        assert ((w - g).norm() / w.norm()).item() < rtol
+
+
+def test_unit_wise_on_a_linear_network(reference):
+    """(The reference's unit-wise maker fails on convolutions: it concatenates a 4-D and a 2-D tensor.)"""
+    def make(L, m):
+        return L.UnitWiseNaturalGradientMaker(m, _cfg(L, data_size=8, damping=1e-2), fisher_type='fisher_emp')
+    for w, g in zip(_run(reference, make, 'mlp'), _run(ours, make, 'mlp')):
+        assert ((w - g).norm() / w.norm()).item() < 1e-5
+    assert all(torch.isfinite(g).all() for g in _run(ours, make, 'cnn'))
+
+
+def _mlp():
+    return _net('mlp')
+
+
+def _fisher_maker(L, **kw):
+    model, x, t = _mlp()
+    fm = L.get_fisher_maker(model, L.FisherConfig(fisher_type='fisher_emp', fisher_shapes=['full'],
+                                                  loss_type='cross_entropy', data_size=8, **kw))
+    dummy = fm.setup_model_call(model, x)
+    fm.setup_loss_call(F.cross_entropy, dummy, t)
+    return model, fm
+
+
+def _ones(L, model):
+    return L.ParamVector(list(model.parameters()), [torch.ones_like(p) for p in model.parameters()])
+
+
+def _fisher_eig(L):
+    _, fm = _fisher_maker(L)
+    fm.forward_and_backward()
+    return torch.tensor([float(v) for v in fm.fisher_eig(top_n=2, max_iters=300, tol=1e-9)[0]])
+
+
+def _fisher_free(L):
+    model, fm = _fisher_maker(L)
+    return fm.fisher_free(_ones(L, model), damping=1e-2, max_iters=200, tol=1e-10).get_flatten_vector()
+
+
+def _fisher_quadratic_form(L):
+    model, fm = _fisher_maker(L)
+    return torch.tensor(float(fm.fisher_quadratic_form(_ones(L, model))))
+
+
+def _hessian(shape):
+    def run(L):
+        model, x, t = _mlp()
+        hm = L.HessianMaker(model, L.HessianConfig(hessian_shapes=[shape]))
+        dummy = hm.setup_model_call(model, x)
+        hm.setup_loss_call(F.cross_entropy, dummy, t)
+        hm.forward_and_backward()
+        if shape == 'full':
+            return model.hessian.data
+        return model[0].hessian.data if shape == 'layer_wise' else model[0].hessian.diag.weight
+    return run
+
+
+def _hessian_eig(L):
+    model, x, t = _mlp()
+    hm = L.HessianMaker(model, L.HessianConfig(hessian_shapes=['full']))
+    dummy = hm.setup_model_call(model, x)
+    hm.setup_loss_call(F.cross_entropy, dummy, t)
+    return torch.tensor([float(v) for v in hm.hessian_eig(top_n=1, max_iters=500, tol=1e-10)[0]])
+
+
+def _ntk(name):
+    def run(L):
+        model, x, _ = _mlp()
+        return getattr(L, name)(model, x)
+    return run
+
+
+def _gradient_after(call):
+    def run(L):
+        model, x, t = _mlp()
+        call(L, model, x, t)
+        return torch.cat([p.grad.flatten() for p in model.parameters()])
+    return run
+
+
+ANALYSES = {
+    'fisher_eig': _fisher_eig, 'fisher_free': _fisher_free, 'fisher_quadratic_form': _fisher_quadratic_form,
+    'hessian_full': _hessian('full'), 'hessian_layer_wise': _hessian('layer_wise'), 'hessian_diag': _hessian('diag'),
+    'hessian_eig': _hessian_eig,
+    'ntk_implicit': _ntk('empirical_implicit_ntk'), 'ntk_class_wise_direct': _ntk('empirical_class_wise_direct_ntk'),
+    'ntk_class_wise_hadamard': _ntk('empirical_class_wise_hadamard_ntk'),
+    'kernel_free': _gradient_after(lambda L, m, x, t: L.kernel_free_cross_entropy(m, x, t, damping=1e-2, tol=1e-9)),
+    'kernel_eigenvalues': lambda L: torch.tensor([float(v) for v in L.kernel_eigenvalues(
+        _mlp()[0], _mlp()[1], top_n=2, max_iters=500, tol=1e-10)]),
+    'empirical_natural_gradient': _gradient_after(lambda L, m, x, t: L.empirical_natural_gradient(m, x, t, damping=1e-2)),
+}
+
+
+@pytest.mark.parametrize('name', sorted(ANALYSES))
+def test_same_analysis_results_as_the_reference(reference, name):
+    with warnings.catch_warnings():
+        warnings.simplefilter('ignore')
+        torch.manual_seed(3)
+        want = torch.as_tensor(ANALYSES[name](reference)).double().flatten()
+        torch.manual_seed(3)
+        got = torch.as_tensor(ANALYSES[name](ours)).double().flatten()
+    assert ((want - got).norm() / want.norm()).item() < 1e-5
