@@ -9,7 +9,7 @@ import torch
 from torch import nn
 
 from .. import ops
-from .operation import (Operation, BASIC_OPS, OP_COV_KRON, OP_BATCH_GRADS, OP_COV_DIAG,
+from .operation import (Operation, BASIC_OPS, OP_COV_KRON, OP_COV_KRON_INV, OP_BATCH_GRADS, OP_COV_DIAG,
                         OP_COV_DIAG_INV)
 
 __all__ = ['Embedding']
@@ -22,7 +22,9 @@ class Embedding(Operation):
     ignored); counts, per-example gradients and the diagonal are scatter-adds over tokens.  Reference:
     asdl/operations/embedding.py:7-78 (``bincount`` per example and Python loops over tokens).
     """
-    supported_operations = set(BASIC_OPS + [OP_COV_KRON, OP_BATCH_GRADS, 'diag', OP_COV_DIAG,
+    # the reference leaves out the fused "statistic + inverse" op, so K-FAC without a moving average
+    # (which inverts inside the hooks) finds no curvature for an embedding and raises
+    supported_operations = set(BASIC_OPS + [OP_COV_KRON, OP_COV_KRON_INV, OP_BATCH_GRADS, 'diag', OP_COV_DIAG,
                                             OP_COV_DIAG_INV])
 
     @staticmethod

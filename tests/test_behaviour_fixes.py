@@ -135,3 +135,17 @@ def test_embedding_statistics_without_token_loops():
         want.append(emb.weight.grad.clone())
     torch.testing.assert_close(per_example, torch.stack(want))
     assert diag.shape == emb.weight.shape and bool((diag >= 0).all())
+
+
+def test_kfac_without_moving_average_handles_embeddings():
+    """asdl/operations/embedding.py:8-9 lacks the fused statistic + inverse op, so the reference's K-FAC
+    without ``ema_decay`` raises "Matrix of shape kron ... has not been calculated" on an embedding."""
+    def run(ema):
+        torch.manual_seed(0)
+        model = nn.Sequential(nn.Embedding(11, 4), nn.Flatten(), nn.Linear(12, 3))
+        tokens, t = torch.randint(0, 11, (8, 3)), torch.randint(0, 3, (8,))
+        gm = asdl.KfacGradientMaker(model, asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=ema),
+                                    fisher_type=asdl.FISHER_EMP)
+        _step(gm, model, tokens, t)
+        return torch.cat([p.grad.flatten() for p in model.parameters()])
+    torch.testing.assert_close(run(-1), run(1.0), rtol=1e-4, atol=1e-6)   # keeping only the newest statistics is the same
