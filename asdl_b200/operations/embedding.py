@@ -27,22 +27,18 @@ class Embedding(Operation):
     supported_operations = set(BASIC_OPS + [OP_COV_KRON, OP_COV_KRON_INV, OP_BATCH_GRADS, 'diag', OP_COV_DIAG,
                                             OP_COV_DIAG_INV])
 
-    @staticmethod
-    def _per_example(in_data, out_grads):
-        n = in_data.shape[0]
-        idx = in_data.reshape(n, -1)
-        g = out_grads.reshape(n, idx.shape[1], -1)
-        return idx, g
-
     @classmethod
     def batch_grads_weight(cls, module, in_data, out_grads):
-        """n x num_embeddings x embedding_dim (dense; intended for small vocabularies)."""
-        idx, g = cls._per_example(in_data, out_grads)
-        n, t = idx.shape
-        out = g.new_zeros(n * module.num_embeddings, module.embedding_dim)
-        rows = (idx + torch.arange(n, device=idx.device).unsqueeze(1) * module.num_embeddings)
-        out.index_add_(0, rows.reshape(-1), g.reshape(n * t, -1))
-        out = out.view(n, module.num_embeddings, module.embedding_dim)
+        """tokens x num_embeddings x embedding_dim (dense; intended for small vocabularies).  Every token
+        is a row of its own, the convention of every layer for inputs with extra leading dimensions
+        (a Linear layer after the embedding flattens n x sequence x features to (n sequence) x features),
+        so the rows of all layers of a token-level model line up."""
+        idx = in_data.reshape(-1).long()
+        g = out_grads.reshape(idx.shape[0], -1)
+        rows = idx.shape[0]
+        out = g.new_zeros(rows * module.num_embeddings, module.embedding_dim)
+        out.index_add_(0, idx + torch.arange(rows, device=idx.device) * module.num_embeddings, g)
+        out = out.view(rows, module.num_embeddings, module.embedding_dim)
         if module.padding_idx is not None:
             out[:, module.padding_idx].zero_()
         return out

@@ -78,9 +78,12 @@ BWD_OPS_WITH_INPUTS = [OP_COV, OP_COV_INV, OP_CVP, OP_COV_KRON_INV, OP_COV_SWIFT
 # everything that needs the backward pass
 BWD_OPS = [OP_SAVE_OUTGRADS, OP_COV_KRON, OP_COV_SWIFT_KRON, OP_RFIM_RELU, OP_RFIM_SOFTMAX,
            OP_MEAN_OUTGRADS, OP_SPATIAL_MEAN_OUTGRADS] + BWD_OPS_WITH_INPUTS
+# what every layer type supports: saved tensors and means, and everything that follows from per-example
+# gradients alone (layer-wise blocks and their inverses, matrix-free products, the model-wide matrix, Gram rows)
 BASIC_OPS = [OP_SAVE_INPUTS, OP_SAVE_OUTPUTS, OP_SAVE_OUTGRADS,
              OP_MEAN_INPUTS, OP_MEAN_OUTPUTS, OP_SPATIAL_MEAN_OUTPUTS, OP_OUT_SPATIAL_SIZE,
-             OP_MEAN_OUTGRADS, OP_SPATIAL_MEAN_OUTGRADS]
+             OP_MEAN_OUTGRADS, OP_SPATIAL_MEAN_OUTGRADS,
+             OP_FULL_COV, OP_FULL_CVP, OP_COV, OP_COV_INV, OP_CVP, OP_GRAM_DIRECT]
 
 # local copies of the shape names (the canonical definitions live in asdl_b200.matrices)
 SHAPE_LAYER_WISE = 'layer_wise'

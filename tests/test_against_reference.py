@@ -216,3 +216,65 @@ def test_same_analysis_results_as_the_reference(reference, name):
         torch.manual_seed(3)
         got = torch.as_tensor(ANALYSES[name](ours)).double().flatten()
     assert ((want - got).norm() / want.norm()).item() < 1e-5
+
+
+def _fisher_tensors(model):
+    out = {}
+    for name, module in model.named_modules():
+        fisher = getattr(module, 'fisher', None)
+        if fisher is None:
+            continue
+        parts = {'': fisher, 'kron.': getattr(fisher, 'kron', None), 'unit.': getattr(fisher, 'unit', None),
+                 'diag.': getattr(fisher, 'diag', None)}
+        for prefix, part in parts.items():
+            if part is None:
+                continue
+            for attr in ('data', 'inv', 'A', 'B', 'A_inv', 'B_inv', 'weight', 'bias', 'weight_inv', 'bias_inv'):
+                value = getattr(part, attr, None)
+                if isinstance(value, torch.Tensor):
+                    out[f'{name}.{prefix}{attr}'] = value
+    return out
+
+
+def _fisher_net(kind):
+    torch.manual_seed(0)
+    if kind == 'mlp':
+        return nn.Sequential(nn.Linear(6, 5), nn.Tanh(), nn.Linear(5, 3)), torch.randn(8, 6)
+    if kind == 'cnn_bn':
+        return (nn.Sequential(nn.Conv2d(2, 3, 3, padding=1), nn.BatchNorm2d(3), nn.Tanh(), nn.Flatten(), nn.Linear(108, 3)),
+                torch.randn(8, 2, 6, 6))
+    # token-level model: every layer sees (examples x tokens) rows
+    return nn.Sequential(nn.Embedding(11, 4), nn.LayerNorm(4), nn.Linear(4, 3)), torch.randint(0, 11, (8, 3))
+
+
+@pytest.mark.parametrize('kind', ['mlp', 'cnn_bn', 'embedding_ln'])
+@pytest.mark.parametrize('fisher_type', ['fisher_exact', 'fisher_mc', 'fisher_emp'])
+@pytest.mark.parametrize('loss', ['cross_entropy', 'mse'])
+def test_same_fisher_tensors_as_the_reference(reference, kind, fisher_type, loss):
+    """Every shape, with and without the fused inverse: the same tensors under the same names."""
+    shapes = ['full', 'layer_wise', 'kron', 'unit_wise', 'diag']
+    if kind == 'embedding_ln' and fisher_type == 'fisher_exact':
+        pytest.skip('on n x tokens x classes outputs the reference raises (cross-entropy) or loops over the wrong '
+                    'dimension (MSE); tests/test_fisher.py checks this library against J^T J there')
+    if kind == 'embedding_ln':
+        shapes = ['full', 'layer_wise', 'diag']   # no unit-wise blocks for embeddings, no Kronecker factors for LayerNorm
+    for shape in shapes:
+        for calc_inv in (False, True):
+            results = []
+            for lib in (reference, ours):
+                model, x = _fisher_net(kind)
+                rows = 24 if kind == 'embedding_ln' else 8
+                t = torch.randint(0, 3, (rows,)) if loss == 'cross_entropy' else torch.randn(rows, 3)
+                fm = lib.get_fisher_maker(model, lib.FisherConfig(fisher_type=fisher_type, fisher_shapes=[shape],
+                                                                  loss_type=loss, data_size=8, seed=1, n_mc_samples=2))
+                dummy = fm.setup_model_call(model, x)
+                fm.setup_loss_call(F.cross_entropy if loss == 'cross_entropy' else F.mse_loss,
+                                   dummy.view(-1, 3) if kind == 'embedding_ln' else dummy, t)
+                with warnings.catch_warnings():
+                    warnings.simplefilter('ignore')
+                    fm.forward_and_backward(calc_inv=calc_inv, damping=1e-2)
+                results.append(_fisher_tensors(model))
+            want, got = results
+            assert set(want) == set(got), (shape, calc_inv, sorted(set(want) ^ set(got)))
+            for key in want:
+                assert ((want[key] - got[key]).norm() / (want[key].norm() + 1e-30)).item() < 1e-4, (shape, calc_inv, key)

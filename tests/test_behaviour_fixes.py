@@ -133,7 +133,8 @@ def test_embedding_statistics_without_token_loops():
         model.zero_grad()
         F.cross_entropy(model(tokens[i:i + 1]), t[i:i + 1], reduction='sum').backward()
         want.append(emb.weight.grad.clone())
-    torch.testing.assert_close(per_example, torch.stack(want))
+    assert per_example.shape == (18, 11, 4)                # one row per token, like every layer on sequence inputs
+    torch.testing.assert_close(per_example.view(6, 3, 11, 4).sum(dim=1), torch.stack(want))
     assert diag.shape == emb.weight.shape and bool((diag >= 0).all())
 
 

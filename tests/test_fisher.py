@@ -322,3 +322,34 @@ def test_norm_embedding_layers():
     F.cross_entropy(emb(idx), t, reduction='sum').backward()
     torch.testing.assert_close(bg.sum(0), emb[0].weight.grad, rtol=1e-4, atol=1e-6)
     assert kron['A'].shape == (11, 11) and kron['B'].shape == (4, 4)
+
+
+@pytest.mark.parametrize('loss_type', LOSSES)
+def test_exact_fisher_of_a_token_level_model_is_the_ggn(loss_type):
+    """Outputs n x tokens x classes: every token is an example; the exact Fisher is J^T H J / data_size
+    over all (example, token) rows."""
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Embedding(11, 4), nn.LayerNorm(4), nn.Linear(4, 3))
+    tokens = torch.randint(0, 11, (8, 3))
+    ce = loss_type == asdl.LOSS_CROSS_ENTROPY
+    t = torch.randint(0, 3, (24,)) if ce else torch.randn(24, 3)
+    fm = asdl.get_fisher_maker(model, asdl.FisherConfig(fisher_type=FISHER_EXACT, fisher_shapes=[SHAPE_FULL],
+                                                        loss_type=loss_type, data_size=8))
+    dummy = fm.setup_model_call(model, tokens)
+    fm.setup_loss_call(F.cross_entropy if ce else F.mse_loss, dummy.view(-1, 3), t)
+    fm.forward_and_backward()
+    y = model(tokens).view(-1, 3)
+    params = list(model.parameters())
+    rows = []
+    for i in range(24):
+        for c in range(3):
+            grads = torch.autograd.grad(y[i, c], params, retain_graph=True)
+            rows.append(torch.cat([g.flatten() for g in grads]))
+    J = torch.stack(rows).view(24, 3, -1)
+    if ce:
+        p = y.softmax(dim=1).detach()
+        H = torch.diag_embed(p) - p.unsqueeze(2) * p.unsqueeze(1)
+    else:
+        H = torch.eye(3).expand(24, 3, 3)
+    want = torch.einsum('ncp,ncd,ndq->pq', J, H, J) / 8
+    torch.testing.assert_close(model.fisher.data, want, rtol=1e-4, atol=1e-6)
