@@ -278,3 +278,112 @@ def test_same_fisher_tensors_as_the_reference(reference, kind, fisher_type, loss
             assert set(want) == set(got), (shape, calc_inv, sorted(set(want) ^ set(got)))
             for key in want:
                 assert ((want[key] - got[key]).norm() / (want[key].norm() + 1e-30)).item() < 1e-4, (shape, calc_inv, key)
+
+
+def _conv_net():
+    torch.manual_seed(0)
+    return (nn.Sequential(nn.Conv2d(2, 3, 3, padding=1), nn.Tanh(), nn.Flatten(), nn.Linear(108, 3)), torch.randn(8, 2, 6, 6),
+            torch.randint(0, 3, (8,)))
+
+
+def _leaves(value):
+    if isinstance(value, torch.Tensor):
+        return [value.double().flatten()]
+    if isinstance(value, dict):
+        value = list(value.values())
+    if isinstance(value, (list, tuple)):
+        return [leaf for v in value for leaf in _leaves(v)]
+    return [torch.as_tensor(value).double().flatten()]
+
+
+def _counters(L):
+    model, x, _ = _conv_net()
+    flat = torch.randn(8, 108)
+    out = []
+    for cls in ('Forward', 'BackwardWeight', 'BackwardInput', 'AdamStats', 'AdamPrecond', 'KFACStats', 'KFACInv',
+                'KFACPrecond', 'ShampooStats', 'ShampooInv', 'ShampooPrecond', 'SMWNGStats'):
+        counter = getattr(L, cls)()
+        for module, inputs in ((model[0], x), (model[3], flat)):
+            out += list(counter.count_flop_numel(module, inputs, module(inputs), batch_size=8))
+    return [float(v) for v in out]
+
+
+def _loader_gradient(L):
+    model, x, t = _conv_net()
+    loader = torch.utils.data.DataLoader(torch.utils.data.TensorDataset(x, t), batch_size=4)
+    loss = L.data_loader_gradient(model, lambda y, tt: F.cross_entropy(y, tt, reduction='sum'), loader)
+    return [loss] + [p.grad for p in model.parameters()]
+
+
+def _functional(name):
+    def run(L):
+        model, x, t = _conv_net()
+        gm = L.GradientMaker(model)
+        dummy = gm.setup_model_call(model, x)
+        gm.setup_loss_call(F.cross_entropy, dummy, t)
+        return getattr(gm, name)()
+    return run
+
+
+def _esd(L):
+    model, x, t = _conv_net()
+    fm = L.get_fisher_maker(model, L.FisherConfig(fisher_type='fisher_emp', fisher_shapes=['full'],
+                                                  loss_type='cross_entropy', data_size=8))
+    dummy = fm.setup_model_call(model, x)
+    fm.setup_loss_call(F.cross_entropy, dummy, t)
+    return list(fm.fisher_esd(n_v=2, num_iter=10)[:2])
+
+
+def _schedules(L):
+    out = []
+    for ratio, warmup in ((0.1, 0.0), (0.5, 0.0), (0.5, 0.2), (1.0, 0.2)):
+        for kind in ('constant', 'step', 'linear'):
+            out += [float(v) for v in L.get_update_schedule(num_total_steps=50, update_ratio=ratio, warmup_ratio=warmup,
+                                                            interval_type=kind)]
+    return out
+
+
+UTILITIES = {
+    'schedules': _schedules, 'counters': _counters, 'data_loader_gradient': _loader_gradient, 'fisher_esd': _esd,
+    'batch_gradient': lambda L: _batch_gradient(L),
+    'loss_grad': _functional('loss_grad'), 'per_example_loss_grads': _functional('per_example_loss_grads'),
+    'loss_hessian': _functional('loss_hessian'), 'logit_jacobian': _functional('logit_jacobian'),
+}
+
+
+def _batch_gradient(L):
+    model, x, t = _conv_net()
+    return L.batch_gradient(model, lambda: F.cross_entropy(model(x), t, reduction='sum').backward())
+
+
+@pytest.mark.parametrize('name', sorted(UTILITIES))
+def test_same_utility_results_as_the_reference(reference, name):
+    with warnings.catch_warnings():
+        warnings.simplefilter('ignore')
+        torch.manual_seed(3)
+        want = torch.cat(_leaves(UTILITIES[name](reference)))
+        torch.manual_seed(3)
+        got = torch.cat(_leaves(UTILITIES[name](ours)))
+    assert want.shape == got.shape
+    assert ((want - got).norm() / (want.norm() + 1e-30)).item() < 1e-4
+
+
+def test_curvature_files_interchange_with_the_reference(reference, tmp_path):
+    """Lower-triangle ``.npy`` files written by either library load in the other."""
+    for writer, reader in ((reference, ours), (ours, reference)):
+        model, x, t = _conv_net()
+        fm = writer.get_fisher_maker(model, writer.FisherConfig(fisher_type='fisher_emp', fisher_shapes=['kron', 'diag'],
+                                                                loss_type='cross_entropy', data_size=8))
+        dummy = fm.setup_model_call(model, x)
+        fm.setup_loss_call(F.cross_entropy, dummy, t)
+        fm.forward_and_backward()
+        root = str(tmp_path / writer.__name__)
+        paths = model[0].fisher.save(root, 'conv')
+        assert paths['kron']['A_tril'].replace(os.sep, '/') == 'conv/kron/A_tril.npy'
+        assert paths['diag']['weight'].replace(os.sep, '/') == 'conv/diag/weight.npy'
+        loaded = reader.SymMatrix()
+        loaded.load(kron_path={k: os.path.join(root, v) for k, v in paths['kron'].items()},
+                    diag_path={k: os.path.join(root, v) for k, v in paths['diag'].items()})
+        torch.testing.assert_close(loaded.kron.A, model[0].fisher.kron.A)
+        torch.testing.assert_close(loaded.kron.B, model[0].fisher.kron.B)
+        torch.testing.assert_close(loaded.diag.weight, model[0].fisher.diag.weight)
