@@ -387,3 +387,69 @@ def test_curvature_files_interchange_with_the_reference(reference, tmp_path):
         torch.testing.assert_close(loaded.kron.A, model[0].fisher.kron.A)
         torch.testing.assert_close(loaded.kron.B, model[0].fisher.kron.B)
         torch.testing.assert_close(loaded.diag.weight, model[0].fisher.diag.weight)
+
+
+class _LossInside(nn.Module):
+    """Returns logits, or ``(logits, loss)`` / ``{'loss', 'logits'}`` when given targets."""
+
+    def __init__(self):
+        super().__init__()
+        torch.manual_seed(0)
+        self.body = nn.Sequential(nn.Linear(6, 5), nn.BatchNorm1d(5), nn.ReLU(), nn.Linear(5, 3))
+
+    def forward(self, x, t=None, as_dict=False):
+        y = self.body(x)
+        if t is None:
+            return y
+        loss = F.cross_entropy(y, t)
+        return {'loss': loss, 'logits': y} if as_dict else (y, loss)
+
+
+SCHEDULED = {
+    'intervals_and_warmup': lambda L, m: L.KfacGradientMaker(m, _cfg(
+        L, data_size=8, damping=1e-2, ema_decay=0.2, curvature_upd_interval=2, preconditioner_upd_interval=3,
+        preconditioner_warmup_steps=2), fisher_type='fisher_emp'),
+    'ratios': lambda L, m: L.KfacGradientMaker(m, _cfg(
+        L, data_size=8, damping=1e-2, ema_decay=0.2, num_total_steps=6, preconditioner_upd_ratio=0.5,
+        curvature_upd_ratio=0.5), fisher_type='fisher_emp'),
+    'ignore_class': lambda L, m: L.KfacGradientMaker(m, _cfg(L, data_size=8, damping=1e-2, ignore_modules=[nn.BatchNorm1d]),
+                                                     fisher_type='fisher_emp'),
+    'ignore_name': lambda L, m: L.KfacGradientMaker(m, _cfg(L, data_size=8, damping=1e-2, ignore_modules=['body.0']),
+                                                    fisher_type='fisher_emp'),
+    'sampled_labels': lambda L, m: L.KfacGradientMaker(m, _cfg(L, data_size=8, damping=1e-2)),
+}
+
+
+@pytest.mark.parametrize('convention', ['tensor', 'tuple', 'dict'])
+@pytest.mark.parametrize('name', sorted(SCHEDULED))
+def test_same_gradients_for_every_output_convention_and_schedule(reference, name, convention):
+    runs = []
+    for lib in (reference, ours):
+        model = _LossInside()
+        torch.manual_seed(1)
+        x, t = torch.randn(8, 6), torch.randint(0, 3, (8,))
+        gm = SCHEDULED[name](lib, model)
+        opt = torch.optim.SGD(model.parameters(), lr=0.05)
+        grads = []
+        with warnings.catch_warnings():
+            warnings.simplefilter('ignore')
+            for s in range(6):
+                opt.zero_grad()
+                torch.manual_seed(20 + s)
+                if convention == 'tuple':
+                    dummy = gm.setup_model_call(model, x, t)
+                    gm.setup_logits_repr(dummy[0])
+                    gm.setup_loss_repr(dummy[1])
+                elif convention == 'dict':
+                    dummy = gm.setup_model_call(model, x, t, as_dict=True)
+                    gm.setup_logits_repr(dummy['logits'])
+                    gm.setup_loss_repr(dummy['loss'])
+                else:
+                    dummy = gm.setup_model_call(model, x)
+                    gm.setup_loss_call(F.cross_entropy, dummy, t)
+                gm.forward_and_backward()
+                grads.append(torch.cat([p.grad.flatten() for p in model.parameters()]).clone())
+                opt.step()
+        runs.append(grads)
+    for want, got in zip(*runs):
+        assert ((want - got).norm() / want.norm()).item() < 1e-4
