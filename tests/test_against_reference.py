@@ -453,3 +453,68 @@ def test_same_gradients_for_every_output_convention_and_schedule(reference, name
         runs.append(grads)
     for want, got in zip(*runs):
         assert ((want - got).norm() / want.norm()).item() < 1e-4
+
+
+def _plain_norm_layers(module):
+    """The library's normalisation subclasses replaced by their parents (the reference matches layer
+    types exactly and refuses subclasses); same parameters and buffers."""
+    for name, child in list(module.named_children()):
+        kind = type(child).__name__
+        if kind == 'FusedLayerNorm':
+            new = nn.LayerNorm(child.normalized_shape, eps=child.eps)
+        elif kind == 'FusedBatchNorm2d':
+            assert child.act is None
+            new = nn.BatchNorm2d(child.num_features, eps=child.eps, momentum=child.momentum)
+        else:
+            _plain_norm_layers(child)
+            continue
+        new.load_state_dict(child.state_dict())
+        setattr(module, name, new)
+    return module
+
+
+def _family(kind, plain):
+    from asdl_b200 import models
+    torch.manual_seed(0)
+    images, labels = torch.randn(4, 3, 32, 32), torch.randint(0, 10, (4,))
+    if kind == 'gpt2':
+        model = models.gpt2_tiny()
+        tokens = torch.randint(0, 97, (4, 16))
+        images, labels = tokens, tokens
+    else:
+        model = {'resnet_bottleneck': models.resnet_tiny, 'resnet18': lambda: models.resnet18(width=8),
+                 'wideresnet': models.wideresnet_tiny, 'vit': models.vit_tiny, 'mixer': models.mixer_tiny}[kind]()
+    return (_plain_norm_layers(model) if plain else model), images, labels
+
+
+@pytest.mark.parametrize('kind', ['resnet_bottleneck', 'resnet18', 'wideresnet', 'vit', 'mixer', 'gpt2'])
+@pytest.mark.parametrize('fisher_type,ema', [('fisher_emp', 0.3), ('fisher_mc', -1)])
+def test_model_families_generic_and_fused_kfac(reference, kind, fisher_type, ema):
+    """Two K-FAC steps on the tiny version of every model family: the reference's maker, this library's
+    generic maker and its fused maker give the same gradients."""
+    def run(lib, maker_name, plain):
+        model, x, t = _family(kind, plain)
+        ignore = [nn.Embedding] if kind == 'gpt2' else None
+        gm = getattr(lib, maker_name)(model, _cfg(lib, data_size=4, damping=1e-2, ema_decay=ema, ignore_modules=ignore),
+                                      fisher_type=fisher_type)
+        opt = torch.optim.SGD(model.parameters(), lr=0.01)
+        grads = []
+        with warnings.catch_warnings():
+            warnings.simplefilter('ignore')
+            for s in range(2):
+                opt.zero_grad()
+                torch.manual_seed(9 + s)
+                dummy = gm.setup_model_call(model, x)
+                if kind == 'gpt2':
+                    gm.setup_loss_call(F.cross_entropy, dummy.view(-1, model(x).shape[-1]), t.view(-1))
+                else:
+                    gm.setup_loss_call(F.cross_entropy, dummy, t)
+                gm.forward_and_backward()
+                grads.append(torch.cat([p.grad.flatten() for p in model.parameters() if p.grad is not None]).clone())
+                opt.step()
+        return grads
+
+    want = run(reference, 'KfacGradientMaker', True)
+    for maker_name in ('KfacGradientMaker', 'FusedKfacGradientMaker'):
+        for w, g in zip(want, run(ours, maker_name, False)):
+            assert ((w - g).norm() / w.norm()).item() < 2e-4, maker_name
