@@ -25,6 +25,7 @@ def main():
     ap.add_argument('--model', default='resnet50', choices=['resnet50', 'resnet_tiny', 'vit_b_16', 'gpt2_medium'])
     ap.add_argument('--batch-size', type=int, default=32)
     ap.add_argument('--seq-len', type=int, default=128)
+    ap.add_argument('--json', default=None, help='also write {phase: {flop, numel, roofline_ms}} to this file')
     args = ap.parse_args()
     if args.model == 'resnet50':
         model, x = resnet50(), torch.randn(1, 3, 224, 224)
@@ -48,6 +49,15 @@ def main():
         name = type(c).__name__
         flop, numel = counts[name]['flop'], counts[name]['numel']
         print(f'{name:<16}{flop / 1e9:>12.2f}{numel / 1e6:>12.2f}{C.roofline_ms(flop, 4 * numel):>14.4f}')
+    if args.json:
+        import json
+        with open(args.json, 'w') as f:
+            json.dump({'model': args.model, 'rows': rows,
+                       'phases': {type(c).__name__: {'flop': counts[type(c).__name__]['flop'],
+                                                     'numel': counts[type(c).__name__]['numel'],
+                                                     'roofline_ms': C.roofline_ms(counts[type(c).__name__]['flop'],
+                                                                                  4 * counts[type(c).__name__]['numel'])}
+                                  for c in counters}}, f, indent=1)
 
 
 if __name__ == '__main__':

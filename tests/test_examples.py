@@ -175,3 +175,15 @@ def test_api_reference_is_current(tmp_path):
         with open(path, 'w') as f:
             f.write(before)
     assert before == after, 'run python docs/build_api.py'
+
+
+def test_plot_report_renders_both_formats(tmp_path):
+    phases = tmp_path / 'phases.json'
+    phases.write_text(_run('benchmarks/time_step.py', '--optim', 'kfac', '--model', 'cnn', '--batch-size', '8',
+                           '--iters', '2', '--warmup', '1', '--no-cuda', '--json'))
+    out = _run('benchmarks/plot_report.py', 'phases', str(phases))
+    assert 'kfac / cnn' in out and 'C=update_curvature' in out and 'ms / step' in out
+    cost = tmp_path / 'cost.json'
+    _run('benchmarks/flops_memory.py', '--model', 'resnet_tiny', '--json', str(cost))
+    out = _run('benchmarks/plot_report.py', 'cost', str(cost))
+    assert 'K-FAC' in out and 'Shampoo' in out and 'stored numbers' in out
