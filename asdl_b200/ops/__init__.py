@@ -30,7 +30,7 @@ import torch
 
 from . import _build
 
-__all__ = ['gram', 'matmul_tn', 'kron_apply', 'conv_patch_gram', 'spd_inverse', 'spd_inverse_grouped',
+__all__ = ['gram', 'matmul_tn', 'kron_apply', 'conv_patch_gram', 'spd_inverse', 'spd_inverse_grouped', 'damped_cholesky',
            'unitwise_inverse', 'batchnorm_unitwise_stats', 'batchnorm_unitwise_stats_from_input',
            'batch_norm_train', 'layer_norm',
            'set_backend', 'get_backend', 'set_precision', 'get_precision', 'extension',
@@ -260,6 +260,36 @@ def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
 # --------------------------------------------------------------------------------------------
 # inverses
 # --------------------------------------------------------------------------------------------
+#: a factorisation that breaks down is retried with the damping multiplied by this, this many times
+DAMPING_ESCALATION, DAMPING_ESCALATION_TRIES = 10.0, 6
+
+
+def damped_cholesky(mat: torch.Tensor, damping) -> torch.Tensor:
+    """Lower Cholesky factor of ``mat + damping*I`` (PyTorch path).  A matrix that is not positive
+    definite at that damping (rounding in an ill-conditioned factor, a negative curvature estimate) is
+    retried with 10x the damping, up to six times, with a warning that names the damping finally used;
+    non-finite entries raise at once, since no damping repairs them."""
+    eye = torch.eye(mat.shape[-1], device=mat.device, dtype=mat.dtype)
+    damping = damping.to(mat.dtype) if isinstance(damping, torch.Tensor) else damping
+    chol, info = torch.linalg.cholesky_ex(mat + damping * eye)
+    if not bool(info.any()):
+        return chol
+    if not bool(torch.isfinite(mat).all()):
+        raise torch.linalg.LinAlgError(f'a {tuple(mat.shape)} curvature matrix has non-finite entries and cannot be '
+                                       f'factorised (non-finite activations or gradients in the statistics pass)')
+    used = float(damping) if float(damping) > 0 else 1e-8 * float(mat.diagonal(dim1=-2, dim2=-1).abs().max() + 1e-30)
+    for _ in range(DAMPING_ESCALATION_TRIES):
+        used *= DAMPING_ESCALATION
+        chol, info = torch.linalg.cholesky_ex(mat + used * eye)
+        if not bool(info.any()):
+            import warnings
+            warnings.warn(f'a {tuple(mat.shape)} curvature matrix is not positive definite with damping '
+                          f'{float(damping):.3g}; factorised with damping {used:.3g} instead.')
+            return chol
+    raise torch.linalg.LinAlgError(f'a {tuple(mat.shape)} curvature matrix is not positive definite even with damping '
+                                   f'{used:.3g} (asked for {float(damping):.3g})')
+
+
 def spd_inverse(mat: torch.Tensor, damping=0.0) -> torch.Tensor:
     """``(mat + damping*I)^-1`` for symmetric positive (semi-)definite ``mat``; the input is left
     untouched.  ``damping`` may be a Python number or a 0-d / 1-element tensor (kept on the
@@ -268,10 +298,7 @@ def spd_inverse(mat: torch.Tensor, damping=0.0) -> torch.Tensor:
         out = torch.empty(mat.shape, device=mat.device, dtype=torch.float32)
         spd_inverse_grouped([mat], [out], damping)
         return out
-    n = mat.shape[-1]
-    eye = torch.eye(n, device=mat.device, dtype=mat.dtype)
-    chol = torch.linalg.cholesky(mat + damping * eye)
-    return torch.cholesky_inverse(chol)
+    return torch.cholesky_inverse(damped_cholesky(mat, damping))
 
 
 def spd_inverse_grouped(mats, outs, damping):
@@ -297,8 +324,7 @@ def spd_inverse_grouped(mats, outs, damping):
         extension().chol_inverse(list(mats), list(outs), damp)
         return outs
     for m, o, d in zip(mats, outs, damp):
-        eye = torch.eye(m.shape[-1], device=m.device, dtype=m.dtype)
-        o.copy_(torch.cholesky_inverse(torch.linalg.cholesky(m + d.to(m.dtype) * eye)))
+        o.copy_(torch.cholesky_inverse(damped_cholesky(m, d)))
     return outs
 
 

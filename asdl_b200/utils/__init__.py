@@ -120,8 +120,8 @@ def cholesky_inv(X, damping=1e-7):
 
 def cholesky_solve(X, b, damping=1e-7):
     """Solve (X + damping*I) y = b.  X is not modified."""
-    eye = torch.eye(X.shape[-1], device=X.device, dtype=X.dtype)
-    chol = torch.linalg.cholesky(X + damping * eye)
+    from .. import ops
+    chol = ops.damped_cholesky(X, damping)
     if b.ndim == 1:
         return torch.cholesky_solve(b.unsqueeze(-1), chol).squeeze(-1)
     return torch.cholesky_solve(b, chol)

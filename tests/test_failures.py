@@ -121,3 +121,31 @@ def test_non_finite_factor_is_reported_not_inverted():
     x_bad[0, 0] = float('nan')
     with pytest.raises(Exception):
         _step(gm, model, x_bad, t)
+
+
+def test_indefinite_factor_is_factorised_with_more_damping_and_a_warning():
+    """Cholesky breakdown does not end the run: the damping is raised tenfold until the factor is
+    positive definite, and the warning names the damping that was used."""
+    torch.manual_seed(0)
+    q = torch.linalg.qr(torch.randn(6, 6))[0]
+    mat = (q * torch.tensor([2.0, 1.0, 0.5, 0.1, 0.0, -3e-4])) @ q.T          # one slightly negative eigenvalue
+    mat = (mat + mat.T) / 2
+    with pytest.warns(UserWarning, match='not positive definite with damping 1e-05'):
+        inv = asdl.cholesky_inv(mat, 1e-5)
+    assert torch.isfinite(inv).all()
+    used = 1e-3                                                               # 1e-5 -> 1e-4 (still < 3e-4) -> 1e-3
+    torch.testing.assert_close(inv, torch.linalg.inv(mat + used * torch.eye(6)), rtol=1e-3, atol=1e-3)
+    with pytest.warns(UserWarning):
+        y = asdl.cholesky_solve(mat, torch.ones(6), 1e-5)
+    torch.testing.assert_close((mat + used * torch.eye(6)) @ y, torch.ones(6), rtol=1e-3, atol=1e-3)
+    bad = mat.clone()
+    bad[0, 0] = float('nan')
+    with pytest.raises(torch.linalg.LinAlgError, match='non-finite'):
+        asdl.cholesky_inv(bad, 1e-5)
+    with pytest.raises(torch.linalg.LinAlgError, match='even with damping'):
+        asdl.cholesky_inv(-1e6 * torch.eye(4), 1e-5)
+    spd = q @ q.T + torch.eye(6)
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter('error')
+        asdl.cholesky_inv(spd, 1e-5)                                          # the normal case stays silent
