@@ -22,7 +22,7 @@ import torch.nn.functional as F
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import asdl_b200 as asdl  # noqa: E402
-from asdl_b200.models import resnet50  # noqa: E402
+from asdl_b200.models import resnet50, resnet_tiny  # noqa: E402
 
 
 def parse_args():
@@ -41,13 +41,18 @@ def parse_args():
     ap.add_argument('--ema-decay', type=float, default=0.05)
     ap.add_argument('--kl-clip', type=float, default=1e-3)
     ap.add_argument('--no-graph', action='store_true')
+    ap.add_argument('--cpu-smoke', action='store_true',
+                    help='run the same loop on the CPU with the tiny bottleneck ResNet and 32 x 32 images (checks the script)')
     return ap.parse_args()
 
 
-def synthetic_batches(batch_size, count, seed):
+def synthetic_batches(batch_size, count, seed, side=224, classes=1000, pin=True):
     g = torch.Generator().manual_seed(seed)
-    data = [(torch.randn(batch_size, 3, 224, 224, generator=g).contiguous(memory_format=torch.channels_last).pin_memory(),
-             torch.randint(0, 1000, (batch_size,), generator=g).pin_memory()) for _ in range(8)]
+    data = []
+    for _ in range(8):
+        x = torch.randn(batch_size, 3, side, side, generator=g).contiguous(memory_format=torch.channels_last)
+        t = torch.randint(0, classes, (batch_size,), generator=g)
+        data.append((x.pin_memory(), t.pin_memory()) if pin else (x, t))
     for i in range(count):
         yield data[i % len(data)]
 
@@ -55,18 +60,20 @@ def synthetic_batches(batch_size, count, seed):
 def main():
     args = parse_args()
     rank, local, world = (int(os.environ.get(k, d)) for k, d in (('RANK', 0), ('LOCAL_RANK', 0), ('WORLD_SIZE', 1)))
-    if not torch.cuda.is_available():
-        raise SystemExit('this example needs a CUDA device')
-    torch.cuda.set_device(local)
-    device = torch.device('cuda', local)
+    cuda = not args.cpu_smoke
+    if cuda and not torch.cuda.is_available():
+        raise SystemExit('this example needs a CUDA device (or --cpu-smoke)')
+    if cuda:
+        torch.cuda.set_device(local)
+    device = torch.device('cuda', local) if cuda else torch.device('cpu')
     if world > 1:
-        dist.init_process_group('nccl', device_id=device)
+        dist.init_process_group('nccl', device_id=device) if cuda else dist.init_process_group('gloo')
     torch.manual_seed(0)
-    model = resnet50().to(device).to(memory_format=torch.channels_last)
+    model = (resnet50() if cuda else resnet_tiny()).to(device).to(memory_format=torch.channels_last)
     config = asdl.PreconditioningConfig(data_size=args.batch_size, damping=args.damping, ema_decay=args.ema_decay,
                                         curvature_upd_interval=args.cov_update_freq,
                                         preconditioner_upd_interval=args.inv_update_freq)
-    grad_maker = asdl.FusedKfacGradientMaker(model, config, cuda_graph=not args.no_graph)
+    grad_maker = asdl.FusedKfacGradientMaker(model, config, cuda_graph=cuda and not args.no_graph)
     decay, no_decay = [], []
     for p in model.parameters():
         (decay if p.ndim > 1 else no_decay).append(p)
@@ -87,12 +94,13 @@ def main():
     total_steps = args.steps or args.epochs * steps_per_epoch
 
     def model_fn(x):
-        with torch.autocast('cuda', dtype=torch.bfloat16):
+        with torch.autocast(device.type, dtype=torch.bfloat16, enabled=cuda):
             return model(x)
 
     step, t0 = 0, time.time()
     for epoch in range(args.epochs):
-        batches = loader if loader is not None else synthetic_batches(args.batch_size, steps_per_epoch, seed=rank)
+        batches = loader if loader is not None else synthetic_batches(
+            args.batch_size, steps_per_epoch, seed=rank, side=224 if cuda else 32, classes=1000 if cuda else 10, pin=cuda)
         if loader is not None and world > 1:
             loader.sampler.set_epoch(epoch)
         for x, t in batches:
@@ -115,10 +123,12 @@ def main():
             optimizer.step()
             step += 1
             if rank == 0 and (step % 50 == 0 or step == total_steps):
-                torch.cuda.synchronize()
+                if cuda:
+                    torch.cuda.synchronize()
                 rate = step * args.batch_size * world / (time.time() - t0)
-                print(f'step {step}/{total_steps} lr {lr:.4f} loss {float(loss):.4f} {rate:.0f} images/s', flush=True)
-    asdl.ops.check_status()
+                print(f'step {step}/{total_steps} lr {lr:.4f} loss {float(loss.detach()):.4f} {rate:.0f} images/s', flush=True)
+    if cuda:
+        asdl.ops.check_status()
     if world > 1:
         dist.destroy_process_group()
 

@@ -187,3 +187,9 @@ def test_plot_report_renders_both_formats(tmp_path):
     _run('benchmarks/flops_memory.py', '--model', 'resnet_tiny', '--json', str(cost))
     out = _run('benchmarks/plot_report.py', 'cost', str(cost))
     assert 'K-FAC' in out and 'Shampoo' in out and 'stored numbers' in out
+
+
+def test_resnet50_example_loop_on_cpu():
+    out = _run('examples/train_resnet50_with_kfac.py', '--cpu-smoke', '--steps', '8', '--batch-size', '4',
+               '--cov-update-freq', '2', '--inv-update-freq', '4', '--warmup-steps', '3')
+    assert 'step 8/8' in out and 'nan' not in out.lower()
