@@ -33,6 +33,7 @@ def test_other_examples():
     assert 'reshape' in _run('examples/grad_maker_demo.py')
     assert 'epoch 1' in _run('examples/pseudo_batch_train.py', '--epochs', '1')
     assert 'GFLOP' in _run('benchmarks/flops_memory.py', '--model', 'resnet_tiny')
+    assert 'K-FAC OBS pruning' in _run('examples/one_shot_pruning.py', '--rounds', '2')
 
 
 @pytest.mark.parametrize('impl', ['ours', 'fused'])
