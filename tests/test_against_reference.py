@@ -518,3 +518,30 @@ def test_model_families_generic_and_fused_kfac(reference, kind, fisher_type, ema
     for maker_name in ('KfacGradientMaker', 'FusedKfacGradientMaker'):
         for w, g in zip(want, run(ours, maker_name, False)):
             assert ((w - g).norm() / w.norm()).item() < 2e-4, maker_name
+
+
+def test_mixed_shape_rules_on_a_language_model(reference):
+    """Shape assignment by class and by name substring: Kronecker factors for the Linear layers, the
+    diagonal for the embeddings and the output head, unit-wise blocks for LayerNorm."""
+    runs = []
+    for lib, plain in ((reference, True), (ours, False)):
+        model, tokens, _ = _family('gpt2', plain)
+        rules = ['kron', (nn.Embedding, 'diag'), (nn.LayerNorm, 'unit_wise'), ('lm_head', 'diag')]
+        gm = lib.NaturalGradientMaker(model, _cfg(lib, data_size=4, damping=1e-2, ema_decay=0.3), fisher_type='fisher_emp',
+                                      fisher_shape=rules)
+        grads = []
+        with warnings.catch_warnings():
+            warnings.simplefilter('ignore')
+            for _ in range(2):
+                model.zero_grad()
+                dummy = gm.setup_model_call(model, tokens)
+                gm.setup_loss_call(F.cross_entropy, dummy.view(-1, model(tokens).shape[-1]), tokens.view(-1))
+                gm.forward_and_backward()
+                grads.append(torch.cat([p.grad.flatten() for p in model.parameters() if p.grad is not None]).clone())
+                with torch.no_grad():
+                    for p in model.parameters():
+                        if p.grad is not None:
+                            p -= 0.01 * p.grad
+        runs.append(grads)
+    for want, got in zip(*runs):
+        assert ((want - got).norm() / want.norm()).item() < 1e-4
