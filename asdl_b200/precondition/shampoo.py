@@ -664,6 +664,8 @@ def inverse_pth_root_batched(mats, p, iter_count=100, error_tolerance=1e-6, ridg
     root = eye * z.pow(1.0 / p).view(b, 1, 1)
     m = g * z.view(b, 1, 1)
     error = (m - eye).abs().amax(dim=(1, 2))
+    if not mats.is_cuda:
+        return _coupled_newton_compacting(root, m, error, p, iter_count, error_tolerance)
     active = error > error_tolerance
     for it in range(iter_count):
         t = (1 - alpha) * eye + alpha * m
@@ -680,6 +682,40 @@ def inverse_pth_root_batched(mats, p, iter_count=100, error_tolerance=1e-6, ridg
         if (it + 1) % check_every == 0 and not bool(active.any()):
             break
     return root
+
+
+def _coupled_newton_compacting(root, m, error, p, iter_count, error_tolerance):
+    """The same iteration for host tensors, where reading the errors costs nothing: matrices leave
+    the batch as soon as they converge (or their error grows), so every product runs on the
+    matrices that still need it, and nothing is copied while the batch stays as it is."""
+    alpha = -1.0 / p
+    n = m.shape[-1]
+    eye = torch.eye(n, dtype=m.dtype)
+    out = root.clone()
+    index = torch.nonzero(error > error_tolerance).flatten()
+    if index.numel() < root.shape[0]:
+        root, m, error = root[index], m[index], error[index]
+    for it in range(iter_count):
+        if index.numel() == 0:
+            break
+        t = m * alpha
+        t.diagonal(dim1=1, dim2=2).add_(1 - alpha)
+        new_root = _bmm(root, t)
+        new_m = _bmm(_mat_power_batched(t, p), m)
+        new_error = (new_m - eye).abs_().amax(dim=(1, 2))
+        grew = (new_error > error * 1.2) if it > 0 else torch.zeros_like(new_error, dtype=torch.bool)
+        done = ~grew & (new_error <= error_tolerance)
+        leaving = grew | done
+        if bool(leaving.any()):
+            out[index[done]] = new_root[done]
+            out[index[grew]] = root[grew]        # a step whose error grew is discarded
+            keep = ~leaving
+            index, root, m, error = index[keep], new_root[keep], new_m[keep], new_error[keep]
+        else:
+            root, m, error = new_root, new_m, new_error
+    if index.numel():
+        out[index] = root                        # iteration limit reached
+    return out
 
 
 @torch.no_grad()
