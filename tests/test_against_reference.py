@@ -545,3 +545,34 @@ def test_mixed_shape_rules_on_a_language_model(reference):
         runs.append(grads)
     for want, got in zip(*runs):
         assert ((want - got).norm() / want.norm()).item() < 1e-4
+
+
+@pytest.mark.parametrize('options', [
+    {'fisher_type': 'fisher_emp'}, {'fisher_type': 'fisher_mc'}, {'fisher_type': 'fisher_exact'},
+    {'fisher_type': 'fisher_mc', 'n_mc_samples': 3}, {'fisher_type': 'fisher_mc', 'var': 0.5},
+    {'fisher_type': 'fisher_exact', 'ema': 0.3}, {'fisher_type': 'fisher_mc', 'scale': 2.0},
+    {'fisher_type': 'fisher_emp', 'grad_scale': 0.5}], ids=lambda o: '-'.join(f'{k}={v}' for k, v in o.items()))
+def test_same_gradients_with_a_regression_loss_and_every_constructor_option(reference, options):
+    runs = []
+    for lib in (reference, ours):
+        kw = dict(options)
+        model, x, _ = _conv_net()
+        torch.manual_seed(4)
+        t = torch.randn(8, 3)
+        gm = lib.KfacGradientMaker(model, _cfg(lib, data_size=8, damping=1e-2, ema_decay=kw.pop('ema', -1)),
+                                   loss_type='mse', **kw)
+        opt = torch.optim.SGD(model.parameters(), lr=0.01)
+        grads = []
+        with warnings.catch_warnings():
+            warnings.simplefilter('ignore')
+            for s in range(3):
+                opt.zero_grad()
+                torch.manual_seed(9 + s)
+                dummy = gm.setup_model_call(model, x)
+                gm.setup_loss_call(F.mse_loss, dummy, t)
+                gm.forward_and_backward()
+                grads.append(torch.cat([p.grad.flatten() for p in model.parameters()]).clone())
+                opt.step()
+        runs.append(grads)
+    for want, got in zip(*runs):
+        assert ((want - got).norm() / want.norm()).item() < 1e-4
