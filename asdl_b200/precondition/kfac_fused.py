@@ -129,10 +129,6 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                  n_mc_samples: int = 1, var: float = 1., seed: int = None,
                  precond_precision: str = 'bf16x3', clone_norm_outputs: bool = False,
                  cuda_graph: bool = False, comm: str = 'auto', grouped: bool = True, **kwargs):
-        if fisher_type not in (FISHER_MC, FISHER_EMP):
-            raise ValueError('FusedKfacGradientMaker supports fisher_mc and fisher_emp.')
-        if loss_type != LOSS_CROSS_ENTROPY and fisher_type == FISHER_MC:
-            raise ValueError('Monte-Carlo sampling is implemented for cross-entropy only.')
         super().__init__(model, config, fisher_type=fisher_type, loss_type=loss_type, scale=scale,
                          grad_scale=grad_scale, n_mc_samples=n_mc_samples, var=var, seed=seed, **kwargs)
         self.precond_precision = precond_precision
@@ -473,7 +469,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         if staged:
             beta = 0.0
         handles = []
-        state = {'on': True}
+        # 'seen': layers whose output-gradient statistics were already written in this curvature pass; further
+        # backward passes of the same pass (several Monte-Carlo samples) add to them instead of starting over
+        state = {'on': True, 'seen': set()}
 
         def kron_hook(st: _KronState):
             module = st.module
@@ -498,15 +496,17 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                         if not state['on']:
                             return
                         g = grad.detach()
+                        again = st in state['seen']
+                        state['seen'].add(st)
                         with torch.no_grad():
                             if self._arena is not None:
-                                self._push_factor(st, g, None, alpha, is_A=False)
+                                self._push_factor(st, g, None, alpha, is_A=False, accumulate=again)
                                 return
                             if g.ndim == 4:
                                 rows = g.permute(0, 2, 3, 1).reshape(-1, g.shape[1])
                             else:
                                 rows = g.reshape(-1, g.shape[-1])
-                            ops.gram(rows, scale=alpha, out=st.B_new if staged else st.B, beta=beta)
+                            ops.gram(rows, scale=alpha, out=st.B_new if staged else st.B, beta=1.0 if again else beta)
                     output.register_hook(bwd)
             return fwd
 
@@ -528,8 +528,10 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                     def bwd(grad):
                         if not state['on']:
                             return
+                        again = st in state['seen']
+                        state['seen'].add(st)
                         with torch.no_grad():
-                            self._norm_statistics(st, saved, grad.detach(), alpha, beta, fused)
+                            self._norm_statistics(st, saved, grad.detach(), alpha, beta, fused, accumulate=again)
                     output.register_hook(bwd)
             return fwd
 
@@ -541,7 +543,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                 st.module.keep_curvature_inputs = True
         return handles, state
 
-    def _push_factor(self, st: _KronState, t, output, alpha, is_A):
+    def _push_factor(self, st: _KronState, t, output, alpha, is_A, accumulate=False):
         """Statistics product of this rank sent to the owner of the factor through NVLink: the SYRK
         epilogue stores its lower-triangular tiles (scaled by 1/world) straight into this rank's
         slot in the owner's symmetric buffer; after the barrier the owner sums its slots into the
@@ -577,17 +579,20 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         segs_b = [segs_a[0], segs_a[2], segs_a[0]] if len(segs_a) == 3 else segs_a
         n_dim = st.d_in if is_A else st.d_out
         off = self._slots_off + self.world_rank * self._slot_stride + st.slot_rel[0 if is_A else 1]
-        # plain (coalesced) stores of the lower-triangular tiles into this rank's slot on the owner
+        # plain (coalesced) stores of the lower-triangular tiles into this rank's slot on the owner; a further
+        # backward pass of the same curvature pass adds to the slot (the slot has one writer, this rank)
         ext.umma_gemm_to_ptr(segs_a, segs_b, False, False, arena.ptr(st.owner, off), n_dim,
-                             float(scale), True, 3, [], 0)
+                             float(scale), True, 2 if accumulate else 3, [], 0)
 
     @staticmethod
-    def _norm_statistics(st: _NormState, y, g, alpha, beta, fused=False):
+    def _norm_statistics(st: _NormState, y, g, alpha, beta, fused=False, accumulate=False):
         module = st.module
         staged = getattr(st, 'stage', None) is not None  # reduced over ranks after the backward pass
         target = st.stage if staged else st.stats
         if staged:
             alpha, beta = 1.0, 0.0
+        if accumulate:  # a further backward pass of the same curvature pass
+            beta = 1.0
         if fused:
             x, mean, invstd, out = y
             ops.batchnorm_unitwise_stats_from_input(x, g, out, mean, invstd, target, alpha=alpha, beta=beta)
@@ -604,6 +609,37 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         bb = gb.square().sum(dim=0)
         new = torch.stack([torch.stack([ww, wb], dim=1), torch.stack([wb, bb], dim=1)], dim=1)
         target.mul_(beta).add_(new, alpha=alpha)
+
+    def _sampling_losses(self, logits):
+        """The scalar losses whose backward passes (activation gradients only) measure the output-side
+        statistics of the Monte-Carlo and the exact Fisher, as in asdl/fisher.py:419-490: labels sampled
+        from the model (cross-entropy) or Gaussian targets around the output (squared error), each
+        divided by the number of samples; or one pass per class weighted by sqrt(p) / one per output."""
+        cfg = self.fisher_maker.config
+        cross_entropy = cfg.loss_type == LOSS_CROSS_ENTROPY
+        if self.fisher_type == FISHER_MC:
+            n_mc = cfg.n_mc_samples
+            if cross_entropy:
+                log_probs = F.log_softmax(logits.float(), dim=-1).reshape(-1, logits.shape[-1])
+                for _ in range(n_mc):
+                    with torch.no_grad():
+                        targets = torch.multinomial(log_probs.exp(), 1).squeeze(1)
+                    yield F.nll_loss(log_probs, targets, reduction='sum') / n_mc
+            else:
+                std = float(cfg.var) ** 0.5
+                for _ in range(n_mc):
+                    with torch.no_grad():
+                        targets = logits + std * torch.randn_like(logits)
+                    yield 0.5 * F.mse_loss(logits, targets, reduction='sum') / n_mc
+        elif cross_entropy:
+            log_probs = F.log_softmax(logits, dim=-1).reshape(-1, logits.shape[-1])
+            with torch.no_grad():
+                sqrt_probs = log_probs.exp().sqrt()
+            for c in range(log_probs.shape[1]):
+                yield -(log_probs[:, c] * sqrt_probs[:, c]).sum()
+        else:
+            for d in range(logits.shape[-1]):
+                yield logits[..., d].sum()
 
     def update_curvature(self, views=None, names=None, through=None):
         """One pass that measures the statistics and leaves the (averaged) loss gradient in
@@ -645,13 +681,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                 if self.fisher_type == FISHER_EMP:
                     backward(loss)
                 else:
-                    logits = self._logits
-                    n_mc = self.fisher_maker.config.n_mc_samples
-                    log_probs = F.log_softmax(logits.float(), dim=-1).reshape(-1, logits.shape[-1])
-                    for _ in range(n_mc):
-                        with torch.no_grad():
-                            targets = torch.multinomial(log_probs.exp(), 1).squeeze(1)
-                        nll = F.nll_loss(log_probs, targets, reduction='sum') / n_mc
+                    for nll in self._sampling_losses(self._logits):
                         if views is None:
                             with skip_param_grad(model):
                                 nll.backward(retain_graph=True)

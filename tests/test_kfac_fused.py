@@ -73,3 +73,39 @@ def test_fused_mc_fisher_trains():
         opt.step()
         losses.append(loss.item())
     assert losses[-1] < losses[0]
+
+
+@pytest.mark.parametrize('loss', ['cross_entropy', 'mse'])
+@pytest.mark.parametrize('options', [
+    {'fisher_type': 'fisher_mc'}, {'fisher_type': 'fisher_exact'}, {'fisher_type': 'fisher_mc', 'n_mc_samples': 3},
+    {'fisher_type': 'fisher_mc', 'var': 0.5}, {'fisher_type': 'fisher_exact', 'ema': 0.3},
+    {'fisher_type': 'fisher_mc', 'scale': 2.0}, {'fisher_type': 'fisher_emp', 'grad_scale': 0.5},
+    {'fisher_type': 'fisher_mc', 'seed': 3}], ids=lambda o: '-'.join(f'{k}={v}' for k, v in o.items()))
+def test_fused_follows_the_generic_maker_for_every_fisher_type_and_option(options, loss):
+    """Sampled labels / Gaussian targets, several samples per step (statistics of the passes add up),
+    one pass per class or output for the exact Fisher, scales and seeds."""
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    def run(maker_cls):
+        kw = dict(options)
+        torch.manual_seed(0)
+        model = nn.Sequential(nn.Conv2d(2, 3, 3, padding=1), nn.BatchNorm2d(3), nn.Tanh(), nn.Flatten(), nn.Linear(108, 3))
+        x = torch.randn(8, 2, 6, 6)
+        t = torch.randn(8, 3) if loss == 'mse' else torch.randint(0, 3, (8,))
+        cfg = asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=kw.pop('ema', -1))
+        gm = maker_cls(model, cfg, loss_type=loss, **kw)
+        opt = torch.optim.SGD(model.parameters(), lr=0.01)
+        grads = []
+        for s in range(3):
+            opt.zero_grad()
+            torch.manual_seed(9 + s)
+            dummy = gm.setup_model_call(model, x)
+            gm.setup_loss_call(F.mse_loss if loss == 'mse' else F.cross_entropy, dummy, t)
+            gm.forward_and_backward()
+            grads.append(torch.cat([p.grad.flatten() for p in model.parameters()]).clone())
+            opt.step()
+        return grads
+
+    for want, got in zip(run(asdl.KfacGradientMaker), run(asdl.FusedKfacGradientMaker)):
+        assert ((want - got).norm() / want.norm()).item() < 1e-4
