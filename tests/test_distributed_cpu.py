@@ -46,10 +46,11 @@ def _make(kind, model, data_size):
     if kind == 'kfac_noema':
         cfg = asdl.PreconditioningConfig(data_size=data_size, damping=1e-2)
         return asdl.KfacGradientMaker(model, cfg, fisher_type=asdl.FISHER_EMP)
-    if kind == 'fused':
+    if kind in ('fused', 'fused_exact'):   # the exact Fisher takes one backward pass per class: statistics add up
         cfg = asdl.PreconditioningConfig(data_size=data_size, damping=1e-2, ema_decay=0.5,
                                          curvature_upd_interval=2, preconditioner_upd_interval=2)
-        return asdl.FusedKfacGradientMaker(model, cfg, fisher_type=asdl.FISHER_EMP, comm='torch')
+        fisher_type = asdl.FISHER_EMP if kind == 'fused' else asdl.FISHER_EXACT
+        return asdl.FusedKfacGradientMaker(model, cfg, fisher_type=fisher_type, comm='torch')
     cfg = asdl.PreconditioningConfig(damping=1e-3, preconditioner_upd_interval=2)
     return asdl.ShampooGradientMaker(model, cfg, block_size=8)
 
@@ -84,7 +85,7 @@ def _worker(rank, world, port, kind, out_dir):
 
 
 @pytest.mark.parametrize('kind,world', [('kfac', 2), ('kfac_noema', 2), ('fused', 2), ('shampoo', 2),
-                                        ('kfac', 3), ('fused', 3), ('shampoo', 3)])
+                                        ('kfac', 3), ('fused', 3), ('shampoo', 3), ('fused_exact', 2)])
 def test_data_parallel_matches_single_process(kind, world):
     with tempfile.TemporaryDirectory() as out_dir:
         mp.spawn(_worker, args=(world, _free_port(), kind, out_dir), nprocs=world, join=True)
