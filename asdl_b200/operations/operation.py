@@ -123,6 +123,8 @@ class Operation:
         self._model_for_kernel = model_for_kernel
         self._op_names = names
         self._op_results = {}
+        self._bwd_calls = 0           # backward hook calls so far (pairs each one with its forward call)
+        self._kron_inv_sums = None    # (A, B) behind the hook-time inverses, for layers applied more than once
         self._damping = 1.e-7
         self._cov_scale = 1.
         self._sketching_size = 256
@@ -165,6 +167,8 @@ class Operation:
 
     def clear_results(self):
         self._op_results = {}
+        self._bwd_calls = 0
+        self._kron_inv_sums = None
 
     # ------------------------------------------------------------------ knobs
     def add_op_name(self, op_name):
@@ -247,8 +251,12 @@ class Operation:
             self.accumulate_result([g], OP_SAVE_OUTGRADS, extend=True)
         a = None
         if any(n in BWD_OPS_WITH_INPUTS for n in names):
-            a = self.preprocess_in_data(module, self.get_result(OP_SAVE_INPUTS)[-1],
-                                        self.get_result(OP_SAVE_OUTPUTS)[-1])
+            # a layer applied k times in the forward pass saved k inputs; its output gradients arrive in
+            # reverse order (and again in that order in every further backward pass of the same graph)
+            saved_in, saved_out = self.get_result(OP_SAVE_INPUTS), self.get_result(OP_SAVE_OUTPUTS)
+            use = -1 - self._bwd_calls % len(saved_in)
+            self._bwd_calls += 1
+            a = self.preprocess_in_data(module, saved_in[use], saved_out[use])
         for name in list(names):
             handler = _BWD_HANDLERS.get(name)
             if handler is not None:
@@ -292,9 +300,14 @@ class Operation:
         module, scale = self._module, self._cov_scale
         A = self.cov_kron_A(module, a).mul_(scale)
         B = self.cov_kron_B(module, g).mul_(scale)
+        if self._kron_inv_sums is not None:   # the layer was applied before in this pass: invert the sums
+            A += self._kron_inv_sums[0]
+            B += self._kron_inv_sums[1]
+        self._kron_inv_sums = (A, B)
         damping_A, damping_B = self.cov_kron_damping(A, B)
-        self.accumulate_result(cholesky_inv(A, damping_A), OP_COV_KRON, 'A_inv')
-        self.accumulate_result(cholesky_inv(B, damping_B), OP_COV_KRON, 'B_inv')
+        node = self._walk((OP_COV_KRON,), create=True)
+        node['A_inv'] = cholesky_inv(A, damping_A)
+        node['B_inv'] = cholesky_inv(B, damping_B)
 
     def _bwd_swift_kron_inv(self, name, a, g, vector):
         module, scale = self._module, self._cov_scale

@@ -471,7 +471,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         handles = []
         # 'seen': layers whose output-gradient statistics were already written in this curvature pass; further
         # backward passes of the same pass (several Monte-Carlo samples) add to them instead of starting over
-        state = {'on': True, 'seen': set()}
+        state = {'on': True, 'seen': set(), 'seen_inputs': set()}
 
         def kron_hook(st: _KronState):
             module = st.module
@@ -480,17 +480,20 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                 if not state['on']:
                     return
                 x = inputs[0].detach()
+                reused = st in state['seen_inputs']   # a layer applied more than once in one forward pass
+                state['seen_inputs'].add(st)
+                beta_a = 1.0 if reused else beta
                 with torch.no_grad():
                     if self._arena is not None:
-                        self._push_factor(st, x, output, alpha, is_A=True)
+                        self._push_factor(st, x, output, alpha, is_A=True, accumulate=reused)
                     elif isinstance(module, nn.Conv2d):
                         out_size = output.shape[-2] * output.shape[-1]
                         ops.conv_patch_gram(x, module, scale=alpha / out_size,
-                                            out=st.A_new if staged else st.A, beta=beta,
+                                            out=st.A_new if staged else st.A, beta=beta_a,
                                             channels_last_order=st.khwc)
                     else:
                         ops.gram(x.reshape(-1, x.shape[-1]), scale=alpha,
-                                 out=st.A_new if staged else st.A, beta=beta)
+                                 out=st.A_new if staged else st.A, beta=beta_a)
                 if output.requires_grad:
                     def bwd(grad):
                         if not state['on']:

@@ -150,3 +150,48 @@ def test_kfac_without_moving_average_handles_embeddings():
         _step(gm, model, tokens, t)
         return torch.cat([p.grad.flatten() for p in model.parameters()])
     torch.testing.assert_close(run(-1), run(1.0), rtol=1e-4, atol=1e-6)   # keeping only the newest statistics is the same
+
+
+class _Reused(nn.Module):
+    """One layer applied twice, one frozen layer, one layer without bias."""
+
+    def __init__(self):
+        super().__init__()
+        torch.manual_seed(0)
+        self.inp, self.mid, self.out = nn.Linear(6, 5), nn.Linear(5, 5, bias=False), nn.Linear(5, 3)
+        self.frozen = nn.Linear(5, 5)
+        for p in self.frozen.parameters():
+            p.requires_grad_(False)
+
+    def forward(self, x):
+        h = torch.tanh(self.inp(x))
+        h = torch.tanh(self.mid(torch.tanh(self.mid(h))))
+        return self.out(self.frozen(h))
+
+
+def test_kfac_on_a_layer_that_is_applied_twice():
+    """Statistics of both applications add up: A = a1^T a1 + a2^T a2, B likewise, and the inverse is
+    taken of the sums.  (Without a moving average the reference inverts inside the backward hook, pairs
+    both output gradients with the last input and adds the two inverses: asdl/operations/operation.py:267-278.)"""
+    def run(maker, ema):
+        model = _Reused()
+        torch.manual_seed(1)
+        x, t = torch.randn(8, 6), torch.randint(0, 3, (8,))
+        gm = maker(model, asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=ema), fisher_type=asdl.FISHER_EMP)
+        _step(gm, model, x, t)
+        assert model.frozen.weight.grad is None
+        return torch.cat([p.grad.flatten() for p in model.parameters() if p.grad is not None]), model
+
+    keep_newest, model = run(asdl.KfacGradientMaker, 1.0)
+    with asdl.save_inputs_outgrads(model) as cxt:
+        torch.manual_seed(1)
+        x, t = torch.randn(8, 6), torch.randint(0, 3, (8,))
+        F.cross_entropy(model(x), t, reduction='sum').backward()
+        inputs, grads = cxt.in_data(model.mid), cxt.out_grads(model.mid)
+    model.zero_grad()
+    assert len(inputs) == 2 and len(grads) == 2
+    want_A = sum(a.T @ a for a in inputs) / 8
+    torch.testing.assert_close(model.mid.fisher.kron.A, want_A, rtol=1e-4, atol=1e-6)
+    for maker in (asdl.KfacGradientMaker, asdl.FusedKfacGradientMaker):
+        for ema in (-1, 1.0):
+            torch.testing.assert_close(run(maker, ema)[0], keep_newest, rtol=1e-4, atol=1e-6)
