@@ -29,6 +29,12 @@ class Conv2d(Operation):
     """
     supported_operations = set(ALL_OPS) - {OP_RFIM_RELU, OP_RFIM_SOFTMAX}
 
+    def __init__(self, module, op_names, model_for_kernel=None):
+        if getattr(module, 'groups', 1) != 1:
+            raise ValueError(f'{module}: convolutions with groups > 1 are not supported (every group has its own '
+                             f'patch matrix); list the layer in ignore_modules.')
+        super().__init__(module, op_names, model_for_kernel)
+
     @staticmethod
     def preprocess_in_data(module, in_data, out_data):
         return im2col_2d(in_data, module)

@@ -222,8 +222,8 @@ def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
     CUDA: a bf16 im2col kernel (vectorised for channels_last inputs) feeds the tcgen05 SYRK; 1x1
     stride-1 convolutions on channels_last activations need no staging at all.  fp32 inputs are
     staged as bf16 hi/lo patch pairs and multiplied in three passes (precision policy 'auto')."""
-    from ..utils import im2col_2d, _conv_geometry
-    (kh, kw), (sh, sw), (ph, pw), (dh, dw) = _conv_geometry(conv)
+    from ..utils import im2col_2d, _conv_geometry, _explicit_padding
+    (kh, kw), (sh, sw), _, (dh, dw) = _conv_geometry(conv)
     if not cuda_kernels_enabled(x):
         patches = im2col_2d(x, conv)  # n x (c kh kw) x L
         if channels_last_order:
@@ -231,6 +231,7 @@ def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
             patches = patches.view(n, x.shape[1], kh * kw, L).permute(0, 2, 1, 3).reshape(n, -1, L)
         rows = patches.permute(0, 2, 1).reshape(-1, patches.shape[1])
         return gram(rows, scale=scale, out=out, beta=beta)
+    x, (ph, pw) = _explicit_padding(x, conv)   # reflect / replicate / circular padding becomes part of the input
     n, c, h, w = x.shape
     ho = (h + 2 * ph - dh * (kh - 1) - 1) // sh + 1
     wo = (w + 2 * pw - dw * (kw - 1) - 1) // sw + 1

@@ -139,6 +139,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         for name, module in self.named_modules_for_curvature:
             shape = self.shape_for[module]
             if shape == SHAPE_KRON and isinstance(module, (nn.Linear, nn.Conv2d)):
+                if getattr(module, 'groups', 1) != 1:
+                    raise ValueError(f'{name}: convolutions with groups > 1 are not supported (every group has its '
+                                     f'own patch matrix); list the layer in config.ignore_modules.')
                 self._kron.append(_KronState(name, module, device))
             elif shape == SHAPE_UNIT_WISE and isinstance(module, _NORMS):
                 self._norm.append(_NormState(name, module, device))
@@ -557,8 +560,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         module = st.module
         scale = alpha / self.world_size
         if is_A and isinstance(module, nn.Conv2d):
-            from ..utils import _conv_geometry
-            (kh, kw), (sh, sw), (ph, pw), (dh, dw) = _conv_geometry(module)
+            from ..utils import _conv_geometry, _explicit_padding
+            (kh, kw), (sh, sw), _, (dh, dw) = _conv_geometry(module)
+            t, (ph, pw) = _explicit_padding(t, module)
             n, c, h, w = t.shape
             scale = scale / (output.shape[-2] * output.shape[-1])
             pointwise = kh == kw == sh == sw == 1 and ph == pw == 0

@@ -82,6 +82,16 @@ def _conv_geometry(conv2d):
     return tuple(conv2d.kernel_size), tuple(conv2d.stride), tuple(pad), tuple(conv2d.dilation)
 
 
+def _explicit_padding(x: torch.Tensor, conv2d):
+    """(input, (pad_h, pad_w)) for patch extraction: reflect / replicate / circular padding is applied to
+    the input here (patch extraction itself pads with zeros), zero padding is left to the caller."""
+    _, _, (ph, pw), _ = _conv_geometry(conv2d)
+    mode = getattr(conv2d, 'padding_mode', 'zeros')
+    if mode == 'zeros' or (ph == 0 and pw == 0):
+        return x, (ph, pw)
+    return F.pad(x, (pw, pw, ph, ph), mode=mode), (0, 0)
+
+
 def im2col_2d(x: torch.Tensor, conv2d: nn.Module):
     """Patch matrix of a conv input: ``n x c x h x w -> n x (c*kh*kw) x (h_out*w_out)`` with the
     column order (c, kh, kw) of ``conv2d.weight.view(c_out, -1)``."""
@@ -89,7 +99,8 @@ def im2col_2d(x: torch.Tensor, conv2d: nn.Module):
         raise ValueError(f'x.ndim has to be 4. Got {x.ndim}.')
     if not isinstance(conv2d, (nn.Conv2d, nn.ConvTranspose2d)):
         raise TypeError(f'conv2d has to be {nn.Conv2d} or {nn.ConvTranspose2d}. Got {type(conv2d)}.')
-    (kh, kw), (sh, sw), (ph, pw), (dh, dw) = _conv_geometry(conv2d)
+    (kh, kw), (sh, sw), _, (dh, dw) = _conv_geometry(conv2d)
+    x, (ph, pw) = _explicit_padding(x, conv2d)
     if ph or pw:
         x = F.pad(x, (pw, pw, ph, ph))
     n, c, h, w = x.shape
@@ -108,7 +119,8 @@ def im2col_2d_slow(x: torch.Tensor, conv2d: nn.Module):
         raise ValueError(f'x.ndim has to be 4. Got {x.ndim}.')
     if not isinstance(conv2d, (nn.Conv2d, nn.ConvTranspose2d)):
         raise TypeError(f'conv2d has to be {nn.Conv2d} or {nn.ConvTranspose2d}. Got {type(conv2d)}.')
-    k, s, p, d = _conv_geometry(conv2d)
+    k, s, _, d = _conv_geometry(conv2d)
+    x, p = _explicit_padding(x, conv2d)
     return F.unfold(x, k, dilation=d, padding=p, stride=s)
 
 

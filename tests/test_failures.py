@@ -149,3 +149,17 @@ def test_indefinite_factor_is_factorised_with_more_damping_and_a_warning():
     with warnings.catch_warnings():
         warnings.simplefilter('error')
         asdl.cholesky_inv(spd, 1e-5)                                          # the normal case stays silent
+
+
+def test_grouped_convolution_is_refused_with_advice():
+    model = nn.Sequential(nn.Conv2d(4, 6, 3, groups=2), nn.Flatten(), nn.Linear(6 * 4 * 4, 3))
+    x, t = torch.randn(4, 4, 6, 6), torch.randint(0, 3, (4,))
+    cfg = asdl.PreconditioningConfig(data_size=4, damping=1e-2)
+    with pytest.raises(ValueError, match='groups > 1'):
+        asdl.FusedKfacGradientMaker(model, cfg)
+    with pytest.raises(ValueError, match='groups > 1'):
+        _step(asdl.KfacGradientMaker(model, cfg), model, x, t)
+    ok = asdl.PreconditioningConfig(data_size=4, damping=1e-2, ignore_modules=[model[0]])
+    for maker in (asdl.KfacGradientMaker, asdl.FusedKfacGradientMaker):   # the advice works
+        _, loss = _step(maker(model, ok), model, x, t)
+        assert torch.isfinite(loss) and model[0].weight.grad is not None

@@ -167,3 +167,17 @@ def test_post_hoc_calculators_agree_with_hooks(kind, shape):
         post = cxt.cov_symmatrix(layer)
     for key, value in hooked.tensors().items():
         torch.testing.assert_close(post.tensors()[key], value, rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize('mode', ['zeros', 'reflect', 'replicate', 'circular'])
+def test_convolution_statistics_honour_the_padding_mode(mode):
+    """Patches are taken from the input padded the way the layer pads it (the reference pads with
+    zeros whatever the mode: asdl/utils.py:51-70)."""
+    torch.manual_seed(0)
+    conv = nn.Conv2d(2, 3, 3, padding=1, padding_mode=mode)
+    model = nn.Sequential(conv, nn.Flatten(), nn.Linear(3 * 36, 3))
+    x, t = torch.randn(4, 2, 6, 6), torch.randint(0, 3, (4,))
+    want = _per_example_grads(model, conv, x, t)
+    got = _run(model, x, t, OP_BATCH_GRADS, read=lambda c: dict(c.batch_grads(conv)))
+    torch.testing.assert_close(torch.cat([got['weight'].flatten(1), got['bias'].flatten(1)], dim=1), want)
+    torch.testing.assert_close(asdl.im2col_2d(x, conv), asdl.im2col_2d_slow(x, conv))
