@@ -75,18 +75,23 @@ def skip_param_grad(model, disable=False):
 def _conv_geometry(conv2d):
     pad = conv2d.padding
     if isinstance(pad, str):
-        if pad == 'valid':
-            pad = (0, 0)
-        else:
+        if pad not in ('valid', 'same'):
             raise ValueError(f'padding="{pad}" is not supported.')
+        pad = (0, 0)   # 'same' is applied to the input by _explicit_padding (it may be asymmetric)
     return tuple(conv2d.kernel_size), tuple(conv2d.stride), tuple(pad), tuple(conv2d.dilation)
 
 
 def _explicit_padding(x: torch.Tensor, conv2d):
     """(input, (pad_h, pad_w)) for patch extraction: reflect / replicate / circular padding is applied to
     the input here (patch extraction itself pads with zeros), zero padding is left to the caller."""
-    _, _, (ph, pw), _ = _conv_geometry(conv2d)
+    (kh, kw), _, (ph, pw), (dh, dw) = _conv_geometry(conv2d)
     mode = getattr(conv2d, 'padding_mode', 'zeros')
+    if conv2d.padding == 'same':   # stride 1: total padding d * (k - 1), the extra element on the right / bottom
+        th, tw = dh * (kh - 1), dw * (kw - 1)
+        pads = (tw // 2, tw - tw // 2, th // 2, th - th // 2)
+        if not any(pads):
+            return x, (0, 0)
+        return F.pad(x, pads, mode='constant' if mode == 'zeros' else mode), (0, 0)
     if mode == 'zeros' or (ph == 0 and pw == 0):
         return x, (ph, pw)
     return F.pad(x, (pw, pw, ph, ph), mode=mode), (0, 0)

@@ -181,3 +181,20 @@ def test_convolution_statistics_honour_the_padding_mode(mode):
     got = _run(model, x, t, OP_BATCH_GRADS, read=lambda c: dict(c.batch_grads(conv)))
     torch.testing.assert_close(torch.cat([got['weight'].flatten(1), got['bias'].flatten(1)], dim=1), want)
     torch.testing.assert_close(asdl.im2col_2d(x, conv), asdl.im2col_2d_slow(x, conv))
+
+
+@pytest.mark.parametrize('kernel', [3, (2, 4)])
+def test_convolution_with_same_padding(kernel):
+    torch.manual_seed(0)
+    conv = nn.Conv2d(2, 3, kernel, padding='same')
+    model = nn.Sequential(conv, nn.Flatten(), nn.Linear(3 * 36, 3))
+    x, t = torch.randn(4, 2, 6, 6), torch.randint(0, 3, (4,))
+    want = _per_example_grads(model, conv, x, t)
+    got = _run(model, x, t, OP_BATCH_GRADS, read=lambda c: dict(c.batch_grads(conv)))
+    torch.testing.assert_close(torch.cat([got['weight'].flatten(1), got['bias'].flatten(1)], dim=1), want)
+    for maker in (asdl.KfacGradientMaker, asdl.FusedKfacGradientMaker):
+        gm = maker(model, asdl.PreconditioningConfig(data_size=4, damping=1e-2), fisher_type=asdl.FISHER_EMP)
+        dummy = gm.setup_model_call(model, x)
+        gm.setup_loss_call(F.cross_entropy, dummy, t)
+        gm.forward_and_backward()
+        assert torch.isfinite(conv.weight.grad).all()
