@@ -134,6 +134,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         self.precond_precision = precond_precision
         self.clone_norm_outputs = clone_norm_outputs
         device = self.device
+        if any(p.dtype == torch.float64 for p in model.parameters()):
+            raise ValueError('FusedKfacGradientMaker keeps its factors and inverses in fp32 buffers; '
+                             'use KfacGradientMaker for a float64 model.')
         self._kron: List[_KronState] = []
         self._norm: List[_NormState] = []
         for name, module in self.named_modules_for_curvature:

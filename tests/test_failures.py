@@ -163,3 +163,9 @@ def test_grouped_convolution_is_refused_with_advice():
     for maker in (asdl.KfacGradientMaker, asdl.FusedKfacGradientMaker):   # the advice works
         _, loss = _step(maker(model, ok), model, x, t)
         assert torch.isfinite(loss) and model[0].weight.grad is not None
+
+
+def test_fused_maker_refuses_float64_models():
+    model = nn.Sequential(nn.Linear(5, 3)).double()
+    with pytest.raises(ValueError, match='float64'):
+        asdl.FusedKfacGradientMaker(model, asdl.PreconditioningConfig(data_size=4, damping=1e-2))
