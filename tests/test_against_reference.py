@@ -576,3 +576,24 @@ def test_same_gradients_with_a_regression_loss_and_every_constructor_option(refe
         runs.append(grads)
     for want, got in zip(*runs):
         assert ((want - got).norm() / want.norm()).item() < 1e-4
+
+
+@pytest.mark.parametrize('name,loss', [('loss_hvp', 'cross_entropy'), ('logit_jvp', 'cross_entropy'),
+                                       ('fvp', 'cross_entropy'), ('fvp', 'mse')])
+def test_same_functional_products_as_the_reference(reference, name, loss):
+    results = []
+    for lib in (reference, ours):
+        model, x, t = _mlp()
+        if loss == 'mse':
+            torch.manual_seed(2)
+            t = torch.randn(8, 3)
+        gm = lib.GradientMaker(model)
+        dummy = gm.setup_model_call(model, x)
+        gm.setup_loss_call(F.cross_entropy if loss == 'cross_entropy' else F.mse_loss, dummy, t)
+        tangents = tuple(torch.ones_like(p) for p in model.parameters())
+        kwargs = {'tangents': tangents, **({'loss_type': loss} if name == 'fvp' else {})}
+        with warnings.catch_warnings():
+            warnings.simplefilter('ignore')
+            results.append(torch.cat(_leaves(getattr(gm, name)(**kwargs))))
+    want, got = results
+    assert want.shape == got.shape and ((want - got).norm() / want.norm()).item() < 1e-5
