@@ -582,6 +582,94 @@ class NaturalGradientMaker(PreconditionedGradientMaker):
         with nvtx_range('all_reduce_all_grad'):
             self._reduce_avg([p.grad for p in self.model.parameters() if p.grad is not None])
 
+    # -- members of the reference's explicit-partition interface (asdl/precondition/natural_gradient.py:288-320,
+    #    587-700, 802-811), kept so that code written against them keeps running --------------------------
+    def computational_cost(self, shape, module):
+        """Cost that the owner assignment attributes to ``module`` with curvature ``shape`` (inverse and
+        preconditioning, cubic in the factor sizes); 0 for modules this rank does not own."""
+        from ..parallel.partition import curvature_cost
+        return curvature_cost(module, shape) if self.is_module_for_inv_and_precondition(module) else 0
+
+    @staticmethod
+    def next_split(subset_partitions):
+        """Index at which a list of costs is cut into two parts of nearly equal sums (the first part is
+        the shortest prefix reaching half of the total, and never the whole list)."""
+        if len(subset_partitions) < 2:
+            raise ValueError('at least two costs are needed for a split.')
+        half, running = sum(subset_partitions) / 2, 0.0
+        for index, cost in enumerate(subset_partitions):
+            running += cost
+            if running >= half:
+                return min(index + 1, len(subset_partitions) - 1)
+        return len(subset_partitions) - 1
+
+    def _modules_outside_partitions(self, module_name=None):
+        return [m for name, m in self.named_modules_for_curvature
+                if m not in self.partitioned_modules and (module_name is None or name == module_name)]
+
+    def reduce_scatter_curvature_module_partitions(self, kron=None, diag=None, with_grad=False):
+        """Sum the curvature of ``module_partitions[r]`` onto rank r (explicit partitions only)."""
+        if self.module_partitions is None:
+            raise ValueError('module_partitions is not set.')
+        handles = []
+        for shape in _module_level_shapes:
+            for keys in self._keys_list_from_shape(shape, kron=kron, diag=diag):
+                handles += self.fisher_maker.reduce_scatter_fisher(self.module_partitions, *keys, with_grad=with_grad,
+                                                                   group=self.sync_group, async_op=True)
+        self.curvature_sync_handles += [h for h in handles if h is not None]
+        return handles
+
+    def reduce_curvature(self, module_name, kron=None, diag=None, with_grad=False):
+        """Sum the curvature of the named module onto the rank whose explicit partition holds it."""
+        if self.module_partitions is None:
+            raise ValueError('module_partitions is not set.')
+        module = dict(self.named_modules_for_curvature).get(module_name)
+        if module is None or module not in self.partitioned_modules:
+            return []
+        dst = next(i for i, part in enumerate(self.module_partitions) if module in part)
+        if self.sync_group is not None and self.sync_group_ranks is not None:
+            dst = self.sync_group_ranks[dst]
+        handles = []
+        for keys in self._keys_list_from_shape(self.shape_for[module], kron=kron, diag=diag):
+            handles += self.fisher_maker.reduce_fisher([module], *keys, all_reduce=False, dst=dst, with_grad=with_grad,
+                                                       group=self.sync_group, async_op=True)
+        self.curvature_sync_handles += [h for h in handles if h is not None]
+        return handles
+
+    def all_reduce_undivided_curvature(self, module_name=None, kron=None, diag=None, with_grad=False):
+        """Sum over ranks the curvature of the modules that no explicit partition holds."""
+        modules = self._modules_outside_partitions(module_name)
+        handles = []
+        for shape in _module_level_shapes:
+            for keys in self._keys_list_from_shape(shape, kron=kron, diag=diag):
+                handles += self.fisher_maker.reduce_fisher(modules, *keys, all_reduce=True, with_grad=with_grad,
+                                                           group=self.sync_group, async_op=True)
+        self.curvature_sync_handles += [h for h in handles if h is not None]
+        return handles
+
+    def _all_reduce_sum(self, grads):
+        grads = [g for g in grads if g is not None]
+        if not grads or not dist.is_initialized():
+            return
+        packed = torch.cat([g.reshape(-1) for g in grads])
+        dist.all_reduce(packed, group=self.sync_group)
+        offset = 0
+        for g in grads:
+            g.copy_(packed[offset:offset + g.numel()].view_as(g))
+            offset += g.numel()
+
+    def all_reduce_undivided_grad(self, async_op=False):
+        """Sum over ranks the gradients of the curvature modules that no explicit partition holds."""
+        if not dist.is_initialized():
+            raise EnvironmentError('torch.distributed is not initialized.')
+        self._all_reduce_sum([p.grad for m in self._modules_outside_partitions() for p in m.parameters()])
+
+    def all_reduce_no_curvature_grad(self, async_op=False):
+        """Sum over ranks the gradients of the leaf modules without curvature."""
+        with_curvature = set(self.modules_for_curvature)
+        self._all_reduce_sum([p.grad for m in self.model.modules()
+                              if len(list(m.children())) == 0 and m not in with_curvature for p in m.parameters()])
+
     def reduce_scatter_grad(self, async_op=False):
         self._owned_grads_synced = False
         self.sync_grad_pre_precondition()

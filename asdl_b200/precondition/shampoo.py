@@ -86,6 +86,23 @@ class ShampooGradientMaker(PreconditionedGradientMaker):
         splits = [i for i in range(1, len(owners)) if owners[i] != owners[i - 1]]
         return splits, owners
 
+    @staticmethod
+    def computational_cost(shapes):
+        """Cost of the inverse roots of a list of square factor shapes ``[[n, n], ...]`` (cubic; the
+        reference's heuristic is n ** 0.4, asdl/precondition/shampoo.py:166-179)."""
+        total = 0.0
+        for shape in shapes:
+            if len(shape) != 2 or shape[0] != shape[1]:
+                raise ValueError(f'square factor shapes are expected. Got {shape}.')
+            total += float(shape[0]) ** 3
+        return total
+
+    @staticmethod
+    def next_split(subset_partitions):
+        """Index at which a list of costs is cut into two parts of nearly equal sums."""
+        from .natural_gradient import NaturalGradientMaker
+        return NaturalGradientMaker.next_split(subset_partitions)
+
     def do_forward_and_backward(self, step=None):
         return True
 

@@ -597,3 +597,33 @@ def test_same_functional_products_as_the_reference(reference, name, loss):
             results.append(torch.cat(_leaves(getattr(gm, name)(**kwargs))))
     want, got = results
     assert want.shape == got.shape and ((want - got).norm() / want.norm()).item() < 1e-5
+
+
+def test_public_surface_covers_the_reference(reference):
+    """Every public name of the reference's flat namespace exists here; every public member of its
+    classes and every parameter of its functions and constructors is accepted."""
+    import inspect
+    problems = []
+    for name in dir(reference):
+        if name.startswith('_'):
+            continue
+        if not hasattr(ours, name):
+            problems.append(f'missing name {name}')
+            continue
+        theirs, mine = getattr(reference, name), getattr(ours, name)
+        if inspect.isclass(theirs) and inspect.isclass(mine):
+            problems += [f'{name}.{m}' for m in dir(theirs) if not m.startswith('_') and not hasattr(mine, m)]
+            pairs = [(theirs.__init__, mine.__init__)]
+        elif inspect.isfunction(theirs) and inspect.isfunction(mine):
+            pairs = [(theirs, mine)]
+        else:
+            continue
+        for f_theirs, f_mine in pairs:
+            try:
+                wanted, have = inspect.signature(f_theirs).parameters, inspect.signature(f_mine).parameters
+            except (TypeError, ValueError):
+                continue
+            if any(p.kind == p.VAR_KEYWORD for p in have.values()):
+                continue
+            problems += [f'{name}({p})' for p in wanted if p not in have]
+    assert not problems, problems

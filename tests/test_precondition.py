@@ -452,3 +452,20 @@ def test_swift_kfac_equals_kfac(ema, fisher_type, steps, kwargs):
         return grads
 
     torch.testing.assert_close(run(True), run(False), rtol=1e-4, atol=1e-6)
+
+
+def test_members_of_the_explicit_partition_interface():
+    model = make_net('mlp')
+    gm = asdl.KfacGradientMaker(model, asdl.PreconditioningConfig(data_size=8, damping=1e-2))
+    linears = [m for m in model.modules() if isinstance(m, nn.Linear)]
+    assert gm.computational_cost(asdl.SHAPE_KRON, linears[0]) > 0
+    assert gm.next_split([1, 1, 1, 1]) == 2 and gm.next_split([10, 1, 1]) == 1 and gm.next_split([1, 1, 10]) == 2
+    with pytest.raises(ValueError):
+        gm.next_split([1])
+    with pytest.raises(ValueError, match='module_partitions'):
+        gm.reduce_scatter_curvature_module_partitions()
+    with pytest.raises(ValueError, match='module_partitions'):
+        gm.reduce_curvature('0')
+    gm.all_reduce_no_curvature_grad()       # no process group: nothing to do
+    shampoo = asdl.ShampooGradientMaker(model, asdl.PreconditioningConfig(damping=1e-6))
+    assert shampoo.computational_cost([[4, 4], [2, 2]]) == 72 and shampoo.next_split([3, 1, 1, 1]) == 1
