@@ -228,6 +228,11 @@ def module_wise_assignments(model, *assign_rules, ignore_modules=None, map_rule=
         yield (name, module, values) if named else (module, values)
 
 
+def named_modules_to_assign(model, value, *assign_rules, ignore_modules=None):
+    """``(name, module)`` pairs whose assigned values contain ``value``."""
+    return modules_to_assign(model, value, *assign_rules, ignore_modules=ignore_modules, named=True)
+
+
 def modules_to_assign(model, value, *assign_rules, ignore_modules=None, named=False):
     """Modules whose assigned values contain ``value``."""
     for item in module_wise_assignments(model, *assign_rules, ignore_modules=ignore_modules, named=True):

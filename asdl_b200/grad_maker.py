@@ -42,6 +42,27 @@ class GetFirstItem:
         return 'GetFirstItem()'
 
 
+class GetItem(tuple):
+    """``value[item]`` as an element of a DummyObject's operator list (``DummyObject([GetItem(0)])``)."""
+
+    def __new__(cls, item):
+        return tuple.__new__(cls, (_OP_ITEM, item))
+
+
+class GetAttr(tuple):
+    """``value.item`` as an element of a DummyObject's operator list."""
+
+    def __new__(cls, item):
+        return tuple.__new__(cls, (_OP_ATTR, item))
+
+
+class Call(tuple):
+    """``value(*args, **kwargs)`` as an element of a DummyObject's operator list."""
+
+    def __new__(cls, args=(), kwargs=None):
+        return tuple.__new__(cls, (_OP_CALL, tuple(args), dict(kwargs or {})))
+
+
 class DummyObject:
     """Recorder of a chain of ``[]`` / ``.attr`` / ``()`` operations on a value that does not exist
     yet.  ``eval(base)`` replays the chain on ``base``; DummyObjects appearing inside call

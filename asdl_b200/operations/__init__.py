@@ -6,6 +6,8 @@ from torch import nn
 
 from .operation import *  # noqa: F401,F403
 from .operation import __all__ as _operation_all
+from .operation import (SHAPE_FULL, SHAPE_LAYER_WISE, SHAPE_KRON, SHAPE_SWIFT_KRON, SHAPE_KFE, SHAPE_UNIT_WISE,  # noqa: F401
+                        SHAPE_DIAG, HESSIAN, FISHER_EXACT, FISHER_MC, FISHER_EMP)
 from .linear import Linear
 from .conv import Conv2d
 from .batchnorm import BatchNorm1d, BatchNorm2d

@@ -10,7 +10,7 @@ from torch import nn
 
 from .. import ops
 from .operation import (Operation, BASIC_OPS, OP_COV_KRON, OP_COV_KRON_INV, OP_BATCH_GRADS, OP_COV_DIAG,
-                        OP_COV_DIAG_INV)
+                        OP_COV_DIAG_INV, SHAPE_DIAG)
 
 __all__ = ['Embedding']
 
@@ -24,7 +24,7 @@ class Embedding(Operation):
     """
     # the reference leaves out the fused "statistic + inverse" op, so K-FAC without a moving average
     # (which inverts inside the hooks) finds no curvature for an embedding and raises
-    supported_operations = set(BASIC_OPS + [OP_COV_KRON, OP_COV_KRON_INV, OP_BATCH_GRADS, 'diag', OP_COV_DIAG,
+    supported_operations = set(BASIC_OPS + [OP_COV_KRON, OP_COV_KRON_INV, OP_BATCH_GRADS, SHAPE_DIAG, OP_COV_DIAG,
                                             OP_COV_DIAG_INV])
 
     @classmethod

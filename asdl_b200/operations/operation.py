@@ -86,10 +86,17 @@ BASIC_OPS = [OP_SAVE_INPUTS, OP_SAVE_OUTPUTS, OP_SAVE_OUTGRADS,
              OP_FULL_COV, OP_FULL_CVP, OP_COV, OP_COV_INV, OP_CVP, OP_GRAM_DIRECT]
 
 # local copies of the shape names (the canonical definitions live in asdl_b200.matrices)
+SHAPE_FULL = 'full'
 SHAPE_LAYER_WISE = 'layer_wise'
 SHAPE_KRON = 'kron'
+SHAPE_SWIFT_KRON = 'swift_kron'
+SHAPE_KFE = 'kfe'
 SHAPE_UNIT_WISE = 'unit_wise'
 SHAPE_DIAG = 'diag'
+HESSIAN = 'hessian'
+FISHER_EXACT = 'fisher_exact'
+FISHER_MC = 'fisher_mc'
+FISHER_EMP = 'fisher_emp'
 
 __all__ = ['Operation', 'OperationContext', 'ALL_OPS', 'FWD_OPS', 'BWD_OPS', 'BWD_OPS_WITH_INPUTS',
            'BASIC_OPS'] + [name for name in list(globals()) if name.startswith('OP_')]

@@ -39,6 +39,16 @@ def _as_3d(t: Tensor):
     return t.unsqueeze(-1) if t.ndim == 2 else t
 
 
+def maybe_unsqueeze_to_3d(t: Tensor):
+    """n x d -> n x d x 1; three-dimensional tensors pass through."""
+    return _as_3d(t)
+
+
+def maybe_flatten_to_2d(t: Tensor):
+    """n x d x 1 -> n x d; two-dimensional tensors pass through."""
+    return t.flatten(start_dim=1) if t.ndim == 3 and t.shape[-1] == 1 else t
+
+
 class SengGradientMaker(PreconditionedGradientMaker):
     r"""GradientMaker for SENG.
 

@@ -70,6 +70,16 @@ def _eigvalsh(mat: torch.Tensor):
     return torch.linalg.eigvalsh(mat, UPLO='U')
 
 
+def symeig(A: torch.Tensor, upper=True):
+    """Eigenvalues of a symmetric matrix from its upper (default) or lower triangle, ascending."""
+    return torch.linalg.eigvalsh(A, UPLO='U' if upper else 'L')
+
+
+def is_all_none(items: Iterable):
+    """Whether every item is None."""
+    return all(item is None for item in items)
+
+
 def _npy_save(path, tensor):
     os.makedirs(os.path.dirname(path), exist_ok=True)
     np.save(path, tensor.detach().cpu().numpy().astype('float32'))

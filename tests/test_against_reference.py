@@ -627,3 +627,21 @@ def test_public_surface_covers_the_reference(reference):
                 continue
             problems += [f'{name}({p})' for p in wanted if p not in have]
     assert not problems, problems
+
+
+def test_every_submodule_name_of_the_reference_exists(reference):
+    """``from asdl.<module> import <name>`` keeps working with ``asdl_b200.<module>``."""
+    import importlib
+    import inspect
+    import pkgutil
+    missing = []
+    for info in pkgutil.walk_packages(reference.__path__, 'asdl.'):
+        theirs = importlib.import_module(info.name)
+        mine = importlib.import_module(info.name.replace('asdl.', 'asdl_b200.', 1))
+        for name, obj in vars(theirs).items():
+            if name.startswith('_') or inspect.ismodule(obj):
+                continue
+            defined_here = getattr(obj, '__module__', info.name) == info.name or isinstance(obj, (str, int, float, list, tuple))
+            if defined_here and not hasattr(mine, name):
+                missing.append(f'{mine.__name__}.{name}')
+    assert not missing, missing
