@@ -644,4 +644,7 @@ def test_every_submodule_name_of_the_reference_exists(reference):
             defined_here = getattr(obj, '__module__', info.name) == info.name or isinstance(obj, (str, int, float, list, tuple))
             if defined_here and not hasattr(mine, name):
                 missing.append(f'{mine.__name__}.{name}')
+            elif inspect.isclass(obj) and obj.__module__ == info.name:      # and every public member of its classes
+                missing += [f'{mine.__name__}.{name}.{member}' for member in dir(obj)
+                            if not member.startswith('_') and not hasattr(getattr(mine, name), member)]
     assert not missing, missing
