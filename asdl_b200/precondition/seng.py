@@ -39,14 +39,14 @@ def _as_3d(t: Tensor):
     return t.unsqueeze(-1) if t.ndim == 2 else t
 
 
-def maybe_unsqueeze_to_3d(t: Tensor):
+def maybe_unsqueeze_to_3d(tensor: Tensor):
     """n x d -> n x d x 1; three-dimensional tensors pass through."""
-    return _as_3d(t)
+    return _as_3d(tensor)
 
 
-def maybe_flatten_to_2d(t: Tensor):
+def maybe_flatten_to_2d(tensor: Tensor):
     """n x d x 1 -> n x d; two-dimensional tensors pass through."""
-    return t.flatten(start_dim=1) if t.ndim == 3 and t.shape[-1] == 1 else t
+    return tensor.flatten(start_dim=1) if tensor.ndim == 3 and tensor.shape[-1] == 1 else tensor
 
 
 class SengGradientMaker(PreconditionedGradientMaker):

@@ -75,9 +75,9 @@ def symeig(A: torch.Tensor, upper=True):
     return torch.linalg.eigvalsh(A, UPLO='U' if upper else 'L')
 
 
-def is_all_none(items: Iterable):
+def is_all_none(xs: Iterable):
     """Whether every item is None."""
-    return all(item is None for item in items)
+    return all(x is None for x in xs)
 
 
 def _npy_save(path, tensor):
