@@ -603,6 +603,15 @@ class NaturalGradientMaker(PreconditionedGradientMaker):
                 return min(index + 1, len(subset_partitions) - 1)
         return len(subset_partitions) - 1
 
+    def _distinct_keys(self, kron=None, diag=None):
+        """Key paths of every module-level shape, each once (kron and swift_kron share theirs)."""
+        out = []
+        for shape in _module_level_shapes:
+            for keys in self._keys_list_from_shape(shape, kron=kron, diag=diag):
+                if keys not in out:
+                    out.append(keys)
+        return out
+
     def _modules_outside_partitions(self, module_name=None):
         return [m for name, m in self.named_modules_for_curvature
                 if m not in self.partitioned_modules and (module_name is None or name == module_name)]
@@ -612,10 +621,9 @@ class NaturalGradientMaker(PreconditionedGradientMaker):
         if self.module_partitions is None:
             raise ValueError('module_partitions is not set.')
         handles = []
-        for shape in _module_level_shapes:
-            for keys in self._keys_list_from_shape(shape, kron=kron, diag=diag):
-                handles += self.fisher_maker.reduce_scatter_fisher(self.module_partitions, *keys, with_grad=with_grad,
-                                                                   group=self.sync_group, async_op=True)
+        for keys in self._distinct_keys(kron, diag):
+            handles += self.fisher_maker.reduce_scatter_fisher(self.module_partitions, *keys, with_grad=with_grad,
+                                                               group=self.sync_group, async_op=True)
         self.curvature_sync_handles += [h for h in handles if h is not None]
         return handles
 
@@ -640,10 +648,9 @@ class NaturalGradientMaker(PreconditionedGradientMaker):
         """Sum over ranks the curvature of the modules that no explicit partition holds."""
         modules = self._modules_outside_partitions(module_name)
         handles = []
-        for shape in _module_level_shapes:
-            for keys in self._keys_list_from_shape(shape, kron=kron, diag=diag):
-                handles += self.fisher_maker.reduce_fisher(modules, *keys, all_reduce=True, with_grad=with_grad,
-                                                           group=self.sync_group, async_op=True)
+        for keys in self._distinct_keys(kron, diag):
+            handles += self.fisher_maker.reduce_fisher(modules, *keys, all_reduce=True, with_grad=with_grad,
+                                                       group=self.sync_group, async_op=True)
         self.curvature_sync_handles += [h for h in handles if h is not None]
         return handles
 

@@ -72,6 +72,7 @@ def _results(model, x, t, world, rank=0, distributed=False):
         fm.reduce_fisher(linears, 'kron', 'B', all_reduce=True)
     out['kron_A'] = linears[0].fisher.kron.A.clone()
     out['kron_B'] = linears[1].fisher.kron.B.clone()
+    out['kron_A_of'] = [m.fisher.kron.A.clone() for m in linears]
     # partitioned reduction: module i is complete on rank i only
     fm = _fisher(model, x, t, asdl.SHAPE_LAYER_WISE, data_size=1)
     if distributed:
@@ -135,6 +136,17 @@ def _worker(rank, world, port, out_dir):
         damped = class_kernels[split] / x.shape[0] + 1e-2 * torch.eye(x.shape[0])
         K.parallel_efficient_natural_gradient_cross_entropy(model, xs, ts, damped, damping=1e-2)
         out['parallel_ngd'] = torch.cat([p.grad.flatten() for p in model.parameters()]).clone()
+        # explicit partitions (the reference's older interface): module r is summed onto rank r
+        linears = [m for m in model if isinstance(m, nn.Linear)]
+        gm = asdl.KfacGradientMaker(model, asdl.PreconditioningConfig(data_size=n, damping=1e-2, ema_decay=0.5),
+                                    fisher_type=asdl.FISHER_EMP, module_partitions=[[m] for m in linears])
+        dummy = gm.setup_model_call(model, xs)
+        gm.setup_loss_call(F.cross_entropy, dummy, ts)
+        gm.delegate_forward_and_backward(gm.fisher_maker, data_size=1, scale=1., accumulate=False)
+        gm.reduce_scatter_curvature_module_partitions()
+        gm.wait_all_curvature_sync()
+        out['partition_A'] = linears[rank].fisher.kron.A.clone()
+        assert gm.reduce_curvature('no_such_module') == [] and gm.computational_cost(asdl.SHAPE_KRON, linears[rank]) > 0
         torch.save(out, os.path.join(out_dir, f'rank{rank}.pt'))
     finally:
         dist.destroy_process_group()
@@ -154,6 +166,7 @@ def test_distributed_entry_points_match_single_process():
         assert abs(r['loader_loss'] - single['loader_loss']) < 1e-5
     for rank, r in enumerate(ranks):
         torch.testing.assert_close(r['layer_block'], single['layer_blocks'][rank], rtol=1e-4, atol=1e-6)
+        torch.testing.assert_close(r['partition_A'], single['kron_A_of'][rank], rtol=1e-4, atol=1e-6)
     ntk = K.batch(K.empirical_direct_ntk, model, x, batch_size=2)
     for r in ranks:
         torch.testing.assert_close(r['ntk'], ntk, rtol=1e-4, atol=1e-6)
