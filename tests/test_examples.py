@@ -8,11 +8,38 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(*args, timeout=600):
+def _run_process(*args, timeout=600):
+    """The script as its own process (what a user types)."""
     env = dict(os.environ, CUDA_VISIBLE_DEVICES='')
     result = subprocess.run([sys.executable, *args], cwd=ROOT, capture_output=True, text=True, timeout=timeout, env=env)
     assert result.returncode == 0, result.stderr[-2000:]
     return result.stdout
+
+
+def _run(script, *args):
+    """The script's ``__main__`` inside this process (saves an interpreter start and a torch import per
+    call); returns what it printed."""
+    import contextlib
+    import io
+    import runpy
+    import torch
+    out = io.StringIO()
+    old_argv, old_path, old_cwd, rng = sys.argv, list(sys.path), os.getcwd(), torch.get_rng_state()
+    sys.argv = [os.path.join(ROOT, script), *map(str, args)]
+    os.chdir(ROOT)
+    try:
+        with contextlib.redirect_stdout(out):
+            try:
+                runpy.run_path(sys.argv[0], run_name='__main__')
+            except SystemExit as exc:
+                assert exc.code in (None, 0), f'{script} exited with {exc.code}: {out.getvalue()[-2000:]}'
+    finally:
+        sys.argv, sys.path[:] = old_argv, old_path
+        os.chdir(old_cwd)
+        torch.set_rng_state(rng)
+        for name in ('train', 'augment'):     # modules the scripts import from their own folder
+            sys.modules.pop(name, None)
+    return out.getvalue()
 
 
 @pytest.mark.parametrize('optim', ['kfac_fused', 'shampoo', 'kron_psgd', 'kbfgs', 'ekfac'])
@@ -23,7 +50,7 @@ def test_train_script_with_every_family(optim):
 
 
 def test_train_script_reads_json_config():
-    out = _run('examples/train.py', '--config', 'examples/configs/cnn_shampoo.json', '--steps-per-epoch', '2',
+    out = _run_process('examples/train.py', '--config', 'examples/configs/cnn_shampoo.json', '--steps-per-epoch', '2',
                '--epochs', '1', '--no-cuda')
     assert 'epoch 1' in out
 
