@@ -648,3 +648,50 @@ def test_every_submodule_name_of_the_reference_exists(reference):
                 missing += [f'{mine.__name__}.{name}.{member}' for member in dir(obj)
                             if not member.startswith('_') and not hasattr(getattr(mine, name), member)]
     assert not missing, missing
+
+
+def test_psgd_factor_formats_and_sparse_lu_match_the_reference(reference):
+    import importlib
+    theirs = importlib.import_module('asdl.precondition.psgd')
+    mine = importlib.import_module('asdl_b200.precondition.psgd')
+    torch.manual_seed(0)
+    m, n = 5, 7
+    dX, dG, G = torch.randn(m, n), torch.randn(m, n), torch.randn(m, n)
+
+    def dense(k):
+        return torch.triu(torch.randn(k, k)) * 0.3 + torch.eye(k)
+
+    def scale(k):
+        return 1 + 0.1 * torch.rand(1, k)
+
+    def norm(k):      # row 0: diagonal, row 1: last column without its last entry
+        q = torch.cat([1 + 0.1 * torch.rand(1, k), 0.1 * torch.randn(1, k)], dim=0)
+        q[1, -1] = 0
+        return q
+
+    formats = {'scale,dense': (scale(m), dense(n)), 'dense,scale': (dense(m), scale(n)), 'norm,dense': (norm(m), dense(n)),
+               'norm,scale': (norm(m), scale(n)), 'dense,norm': (dense(m), norm(n)), 'scale,norm': (scale(m), norm(n))}
+    for name, (Ql, Qr) in formats.items():
+        results = []
+        for lib in (theirs, mine):
+            a, b = lib.update_precond_kron(Ql.clone(), Qr.clone(), dX, dG)
+            results.append((a, b, lib.precond_grad_kron(a, b, G)))
+        for want, got in zip(*results):
+            assert ((want - got).norm() / want.norm()).item() < 1e-5, name
+    # (dense, dense) and (scale, scale): the reference's dispatcher does not reach them; this library's do something sensible
+    a, b = mine.update_precond_kron(dense(m), dense(n), dX, dG)
+    assert torch.isfinite(mine.precond_grad_kron(a, b, G)).all()
+    a, b = mine.update_precond_kron(scale(m), scale(n), dX, dG)
+    assert torch.isfinite(mine.precond_grad_kron(a, b, G)).all()
+
+    r, size = 2, 9
+    L12 = torch.cat([torch.eye(r), torch.zeros(size - r, r)], 0) + 0.1 * torch.tril(torch.randn(size, r))
+    U12 = torch.cat([torch.eye(r), torch.zeros(r, size - r)], 1) + 0.1 * torch.triu(torch.randn(r, size))
+    l3, u3 = 1 + 0.1 * torch.rand(size - r, 1), 1 + 0.1 * torch.rand(size - r, 1)
+    dxs, dgs, grads = ([torch.randn(3, 2), torch.randn(3)] for _ in range(3))
+    results = []
+    for lib in (theirs, mine):
+        state = lib.update_precond_splu(L12.clone(), l3.clone(), U12.clone(), u3.clone(), dxs, dgs)
+        results.append(list(state) + list(lib.precond_grad_splu(*state, grads)))
+    for want, got in zip(*results):
+        assert ((want - got).norm() / want.norm()).item() < 1e-5
