@@ -184,24 +184,33 @@ def _parallel(kernel_fn, model, loader1, loader2=None, store_on_device=True, gat
 # ----------------------------------------------------------------------------------------------
 # empirical NTKs
 # ----------------------------------------------------------------------------------------------
-def empirical_direct_ntk(model, x1, x2=None):
-    """J1 J2^T from explicit per-example logit Jacobians: n1 x n2 x c x c."""
+def empirical_direct_ntk(model, x1, x2=None, precond=None):
+    """J1 J2^T from explicit per-example logit Jacobians: n1 x n2 x c x c.  With ``precond`` (a gradient maker
+    with curvature) the kernel is J1 F^-1 J2^T: the second Jacobian's rows are preconditioned layer by layer."""
     n1 = x1.shape[0]
     inputs = x1 if x2 is None else torch.cat([x1, x2], dim=0)
     with extend(model, OP_BATCH_GRADS) as cxt:
         outputs = model(inputs)
         n_classes = outputs.shape[1]
         params = [p for p in model.parameters() if p.requires_grad]
-        rows = []
+        rows, right_rows = [], []
         for k in range(n_classes):
             cxt.clear_batch_grads()
             torch.autograd.grad(outputs[:, k].sum(), params, retain_graph=k < n_classes - 1,
                                 allow_unused=True)
             parts = [cxt.batch_grads(m, flatten=True) for m in model.modules()]
             rows.append(torch.cat([p for p in parts if p is not None], dim=1))
+            if precond is not None:
+                for m in model.modules():
+                    grads = cxt.batch_grads(m)
+                    if grads is not None:   # in place on the stored per-example gradients
+                        precond.precondition_module(m, vec_weight=grads.get('weight'), vec_bias=grads.get('bias'))
+                parts = [cxt.batch_grads(m, flatten=True) for m in model.modules()]
+                right_rows.append(torch.cat([p for p in parts if p is not None], dim=1))
     jac = torch.stack(rows, dim=1)  # n x c x p
     j1 = jac[:n1]
-    j2 = j1 if x2 is None else jac[n1:]
+    right = jac if precond is None else torch.stack(right_rows, dim=1)
+    j2 = right[:n1] if x2 is None else right[n1:]
     return torch.einsum('ncp,mdp->nmcd', j1, j2)
 
 

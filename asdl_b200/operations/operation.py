@@ -394,6 +394,10 @@ class Operation:
         bg_w, bg_b, bg = self.collect_batch_grads(a, g)
         precond = getattr(module, 'gram_precond', None)
         if precond is not None:
+            # copies: the per-example bias gradient of a Linear layer is the output gradient itself, which
+            # autograd still propagates
+            bg_w = None if bg_w is None else bg_w.clone()
+            bg_b = None if bg_b is None else bg_b.clone()
             precond.precondition_module(module, vec_weight=bg_w, vec_bias=bg_b)
             bg2 = torch.cat([t.flatten(start_dim=1) for t in (bg_w, bg_b) if t is not None], dim=1)
         else:

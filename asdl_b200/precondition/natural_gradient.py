@@ -427,8 +427,32 @@ class NaturalGradientMaker(PreconditionedGradientMaker):
     def precondition_module(self, module, vec_weight=None, vec_bias=None, use_inv=True):
         """Precondition explicit weight/bias-shaped tensors with ``module``'s curvature (used by
         the kernel utilities for per-example gradients)."""
+        weight = getattr(module, 'weight', None)
+        if vec_weight is not None and weight is not None and vec_weight.ndim == weight.ndim + 1:
+            for i in range(vec_weight.shape[0]):   # a batch of per-example gradients: one at a time, in place
+                self._precondition_module(module, vec_weight=vec_weight[i],
+                                          vec_bias=None if vec_bias is None else vec_bias[i], grad_scale=1,
+                                          use_inv=use_inv)
+            return
         self._precondition_module(module, vec_weight=vec_weight, vec_bias=vec_bias, grad_scale=1,
                                   use_inv=use_inv)
+
+    def precondition_vector(self, vectors, use_inv=True):
+        """``F^-1`` applied in place to a list of tensors aligned with ``model.parameters()`` (used by the
+        kernel utilities between two Jacobians).  Runs on plain PyTorch operations, so the result stays
+        differentiable with respect to what the tensors were computed from."""
+        from .. import ops
+        vectors = list(vectors)
+        params = list(self.model.parameters())
+        if len(vectors) != len(params):
+            raise ValueError(f'{len(params)} tensors are expected, one per parameter. Got {len(vectors)}.')
+        backend = ops.get_backend()
+        ops.set_backend('torch')
+        try:
+            self.precondition(vectors=ParamVector(params, vectors), grad_scale=1, use_inv=use_inv)
+        finally:
+            ops.set_backend(backend)
+        return vectors
 
     def _precondition_module(self, module, shape=None, vectors: ParamVector = None,
                              vec_weight: torch.Tensor = None, vec_bias: torch.Tensor = None,

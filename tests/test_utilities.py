@@ -235,3 +235,36 @@ def test_phase_profile_times_library_and_user_ranges():
     table = time_funcs([step, lambda: None], name='kfac_', func_names=['step', 'noop'], num_iters=3, num_warmups=1)
     assert table['kfac_step']['ncalls'] == 3 and table['kfac_Iter']['mean_ms'] >= table['kfac_step']['mean_ms']
     assert table['kfac_noop']['mean_ms'] < table['kfac_step']['mean_ms']
+
+
+def test_preconditioned_ntk_is_jacobian_inverse_fisher_jacobian():
+    """``get_preconditioned_kernel_fn``: J1 F^-1 J2^T with the K-FAC inverse of a gradient maker, for the
+    direct, the implicit and the class-wise direct kernel."""
+    from asdl_b200 import kernel as K
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(6, 5), nn.Tanh(), nn.Linear(5, 3))
+    x, t = torch.randn(4, 6), torch.randint(0, 3, (4,))
+    gm = asdl.KfacGradientMaker(model, asdl.PreconditioningConfig(data_size=4, damping=1e-2), fisher_type=asdl.FISHER_EMP)
+    dummy = gm.setup_model_call(model, x)
+    gm.setup_loss_call(F.cross_entropy, dummy, t)
+    gm.forward_and_backward()
+    model.zero_grad()
+    params = list(model.parameters())
+    y = model(x)
+    jac, right = [], []
+    for i in range(4):
+        for c in range(3):
+            grads = torch.autograd.grad(y[i, c], params, retain_graph=True)
+            jac.append(torch.cat([g.flatten() for g in grads]))
+            vec = asdl.ParamVector(params, [g.clone() for g in grads])
+            gm.precondition(vectors=vec, grad_scale=1)
+            right.append(vec.get_flatten_vector())
+    jac, right = torch.stack(jac).view(4, 3, -1), torch.stack(right).view(4, 3, -1)
+    want = torch.einsum('ncp,mdp->nmcd', jac, right)
+    plain = torch.einsum('ncp,mdp->nmcd', jac, jac)
+    for fn in (K.empirical_direct_ntk, K.empirical_implicit_ntk):
+        torch.testing.assert_close(K.batch(fn, model, x, batch_size=2), plain, rtol=1e-4, atol=1e-5)
+        got = K.batch(K.get_preconditioned_kernel_fn(fn, gm), model, x, batch_size=4)
+        torch.testing.assert_close(got, want, rtol=1e-3, atol=1e-4)
+    class_wise = K.batch(K.get_preconditioned_kernel_fn(K.empirical_class_wise_direct_ntk, gm), model, x, batch_size=4)
+    torch.testing.assert_close(class_wise, torch.einsum('ncp,mcp->nmc', jac, right), rtol=1e-3, atol=1e-4)
