@@ -57,12 +57,15 @@ def extend(model, *op_names, ignore_modules=None, map_rule=None, vectors: ParamV
             x = inputs[0].detach()
             y = output.detach()
             if needs_fwd:
-                on_side_stream(lambda: cxt.call_operations_in_forward(module, x, y))
+                # the forward pass may run inside the user's autocast region: statistics are not to be autocast
+                with torch.autocast(x.device.type, enabled=False):
+                    on_side_stream(lambda: cxt.call_operations_in_forward(module, x, y))
             if needs_bwd and output.requires_grad:
                 def grad_hook(grad):
                     if state['alive'] and cxt.is_operation_registered(module):
                         g = grad.detach()
-                        on_side_stream(lambda: cxt.call_operations_in_backward(module, g))
+                        with torch.autocast(g.device.type, enabled=False):
+                            on_side_stream(lambda: cxt.call_operations_in_backward(module, g))
                 output.register_hook(grad_hook)
         return forward_hook
 

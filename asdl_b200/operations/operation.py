@@ -207,9 +207,15 @@ class Operation:
         if not todo:
             return
         a = self.preprocess_in_data(self._module, in_data, out_data)
+        a32 = out32 = None
         for name in todo:
             with nvtx_range(_RANGE_NAMES_FWD.get(name, name)):
-                _FWD_HANDLERS[name](self, a, out_data)
+                if name in _HALF_PRECISION_OK:
+                    _FWD_HANDLERS[name](self, a, out_data)
+                else:   # everything but the Gram products computes in fp32 (activations may be bf16 under autocast)
+                    a32 = _as_fp32(a) if a32 is None else a32
+                    out32 = _as_fp32(out_data) if out32 is None else out32
+                    _FWD_HANDLERS[name](self, a32, out32)
 
     def _fwd_kron(self, a, out_data):
         self.accumulate_result(self.cov_kron_A(self._module, a).mul_(self._cov_scale), OP_COV_KRON, 'A')
@@ -264,11 +270,17 @@ class Operation:
             use = -1 - self._bwd_calls % len(saved_in)
             self._bwd_calls += 1
             a = self.preprocess_in_data(module, saved_in[use], saved_out[use])
+        a32 = g32 = None
         for name in list(names):
             handler = _BWD_HANDLERS.get(name)
             if handler is not None:
                 with nvtx_range(_RANGE_NAMES_BWD.get(name, name)):
-                    handler(self, name, a, g, vector)
+                    if name in _HALF_PRECISION_OK:
+                        handler(self, name, a, g, vector)
+                    else:
+                        a32 = _as_fp32(a) if a32 is None and a is not None else a32
+                        g32 = _as_fp32(g) if g32 is None else g32
+                        handler(self, name, a32, g32, vector)
 
     def _bwd_cov(self, name, a, g, vector):
         _, _, bg = self.collect_batch_grads(a, g)
@@ -519,6 +531,17 @@ _BWD_HANDLERS = {
     OP_SPATIAL_MEAN_OUTGRADS: Operation._bwd_mean_outgrads,
     OP_SKETCHED_GRAM: Operation._bwd_sketched_gram,
 }
+#: operations whose primitives take bf16 / fp16 activations as they are (Gram products with fp32 accumulation:
+#: tensor-core kernels on CUDA, an fp32 product elsewhere); every other operation gets fp32 copies
+_HALF_PRECISION_OK = {OP_COV_KRON, OP_COV_KRON_INV}
+
+
+def _as_fp32(t):
+    if isinstance(t, torch.Tensor) and t.dtype in (torch.bfloat16, torch.float16):
+        return t.float()
+    return t
+
+
 #: range names of the hook-time work (NVTX and phase profiles); the Kronecker ops have a forward and a backward half
 _RANGE_NAMES_FWD = {OP_COV_KRON: 'cov_kron_A', OP_COV_SWIFT_KRON: 'cov_swift_kron_A'}
 _RANGE_NAMES_BWD = {OP_COV_KRON: 'cov_kron_B', OP_COV_SWIFT_KRON: 'cov_swift_kron_B',

@@ -132,6 +132,11 @@ def _segments(a_hi, a_lo, b_hi, b_lo):
 # --------------------------------------------------------------------------------------------
 # products
 # --------------------------------------------------------------------------------------------
+def _f32(t: torch.Tensor) -> torch.Tensor:
+    """Half-precision tensors as fp32 (the PyTorch paths accumulate and return fp32, like the kernels do)."""
+    return t.float() if t.dtype in (torch.bfloat16, torch.float16) else t
+
+
 def gram(x: torch.Tensor, scale: float = 1.0, out: Optional[torch.Tensor] = None,
          beta: float = 0.0) -> torch.Tensor:
     """``scale * x^T x (+ beta * out)`` for a sample matrix x [rows, n] -> [n, n].
@@ -142,6 +147,7 @@ def gram(x: torch.Tensor, scale: float = 1.0, out: Optional[torch.Tensor] = None
     if x.ndim != 2:
         raise ValueError(f'x has to be 2-D. Got {x.ndim}-D.')
     if not cuda_kernels_enabled(x) or x.shape[0] == 0:
+        x = _f32(x)
         prod = (x.T @ x) * scale if scale != 1.0 else x.T @ x
         if out is None:
             return prod
@@ -165,7 +171,7 @@ def matmul_tn(a: torch.Tensor, b: torch.Tensor, scale: float = 1.0,
               out: Optional[torch.Tensor] = None, beta: float = 0.0) -> torch.Tensor:
     """``scale * a^T b (+ beta*out)`` with a: [k, m], b: [k, n] (both "sample-major")."""
     if not cuda_kernels_enabled(a, b) or a.shape[0] == 0:
-        prod = (a.T @ b) * scale
+        prod = (_f32(a).T @ _f32(b)) * scale
         if out is None:
             return prod
         return out.mul_(beta).add_(prod.to(out.dtype)) if beta != 0.0 else out.copy_(prod)
@@ -225,7 +231,7 @@ def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
     from ..utils import im2col_2d, _conv_geometry, _explicit_padding
     (kh, kw), (sh, sw), _, (dh, dw) = _conv_geometry(conv)
     if not cuda_kernels_enabled(x):
-        patches = im2col_2d(x, conv)  # n x (c kh kw) x L
+        patches = im2col_2d(_f32(x), conv)  # n x (c kh kw) x L
         if channels_last_order:
             n, _, L = patches.shape
             patches = patches.view(n, x.shape[1], kh * kw, L).permute(0, 2, 1, 3).reshape(n, -1, L)

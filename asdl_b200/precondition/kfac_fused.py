@@ -489,7 +489,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                 reused = st in state['seen_inputs']   # a layer applied more than once in one forward pass
                 state['seen_inputs'].add(st)
                 beta_a = 1.0 if reused else beta
-                with torch.no_grad():
+                # the forward pass may run inside an autocast region: the statistics are not to be autocast
+                with torch.no_grad(), torch.autocast(x.device.type, enabled=False):
                     if self._arena is not None:
                         self._push_factor(st, x, output, alpha, is_A=True, accumulate=reused)
                     elif isinstance(module, nn.Conv2d):

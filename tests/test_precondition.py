@@ -469,3 +469,55 @@ def test_members_of_the_explicit_partition_interface():
     gm.all_reduce_no_curvature_grad()       # no process group: nothing to do
     shampoo = asdl.ShampooGradientMaker(model, asdl.PreconditioningConfig(damping=1e-6))
     assert shampoo.computational_cost([[4, 4], [2, 2]]) == 72 and shampoo.next_split([3, 1, 1, 1]) == 1
+
+
+AUTOCAST_MAKERS = {
+    'kfac': lambda m: asdl.KfacGradientMaker(m, asdl.PreconditioningConfig(data_size=16, damping=1e-2, ema_decay=0.3),
+                                             fisher_type=asdl.FISHER_EMP),
+    'kfac_mc_inv_in_hooks': lambda m: asdl.KfacGradientMaker(m, asdl.PreconditioningConfig(data_size=16, damping=1e-2), seed=1),
+    'kfac_fused': lambda m: asdl.FusedKfacGradientMaker(m, asdl.PreconditioningConfig(data_size=16, damping=1e-2, ema_decay=0.3),
+                                                        fisher_type=asdl.FISHER_EMP),
+    'ekfac': lambda m: asdl.EkfacGradientMaker(m, asdl.PreconditioningConfig(data_size=16, damping=1e-2)),
+    'unit_wise': lambda m: asdl.UnitWiseNaturalGradientMaker(m, asdl.PreconditioningConfig(data_size=16, damping=1e-2),
+                                                             fisher_type=asdl.FISHER_EMP),
+    'diag': lambda m: asdl.DiagNaturalGradientMaker(m, asdl.PreconditioningConfig(data_size=16, damping=1e-2),
+                                                    fisher_type=asdl.FISHER_EMP),
+    'layer_wise': lambda m: asdl.LayerWiseNaturalGradientMaker(m, asdl.PreconditioningConfig(data_size=16, damping=1e-2),
+                                                               fisher_type=asdl.FISHER_EMP),
+    'shampoo': lambda m: asdl.ShampooGradientMaker(m, asdl.PreconditioningConfig(damping=1e-4)),
+    'kron_psgd': lambda m: asdl.KronPsgdGradientMaker(m, asdl.PreconditioningConfig()),
+    'kbfgs': lambda m: asdl.KronBfgsGradientMaker(m, asdl.PreconditioningConfig(data_size=16, damping=1e-2, ema_decay=0.1)),
+    'seng': lambda m: asdl.SengGradientMaker(m, asdl.PreconditioningConfig(data_size=16, damping=1e-1)),
+    'smw': lambda m: asdl.SmwEmpNaturalGradientMaker(m, asdl.SmwEmpNaturalGradientConfig(data_size=16, damping=1e-2)),
+}
+
+
+@pytest.mark.parametrize('name', sorted(AUTOCAST_MAKERS))
+def test_makers_under_bf16_autocast(name):
+    """The model may run under bf16 autocast: hooks see bf16 activations and run inside the autocast
+    region, statistics and factors stay fp32, and the result stays close to the fp32 run."""
+    def run(bf16):
+        torch.manual_seed(0)
+        norm_layers = name not in ('kbfgs', 'seng', 'kron_psgd')     # those makers handle Linear / Conv2d only
+        layers = ([nn.Conv2d(2, 4, 3, padding=1)] + ([nn.BatchNorm2d(4)] if norm_layers else [])
+                  + [nn.Tanh(), nn.Flatten(), nn.Linear(4 * 36, 8)] + ([nn.LayerNorm(8)] if norm_layers else [])
+                  + [nn.Linear(8, 3)])
+        model = nn.Sequential(*layers)
+        x, t = torch.randn(16, 2, 6, 6), torch.randint(0, 3, (16,))
+        gm = AUTOCAST_MAKERS[name](model)
+
+        def model_fn(inp):
+            with torch.autocast('cpu', dtype=torch.bfloat16, enabled=bf16):
+                return model(inp)
+
+        for _ in range(2):
+            model.zero_grad()
+            dummy = gm.setup_model_call(model_fn, x)
+            gm.setup_loss_call(F.cross_entropy, dummy, t)
+            gm.forward_and_backward()
+        assert all(p.grad.dtype == torch.float32 for p in model.parameters())
+        return torch.cat([p.grad.flatten() for p in model.parameters()])
+
+    full, mixed = run(False), run(True)
+    assert torch.isfinite(mixed).all()
+    assert F.cosine_similarity(full, mixed, dim=0) > 0.98
