@@ -211,3 +211,23 @@ def test_inverse_roots_survive_an_error_that_rises_in_the_first_iteration():
         exact = (v * (w + 1e-4 * w.max()).pow(-0.25)) @ v.T
         got = ComputePower(mat.clone(), 4, ridge_epsilon=1e-4).double()
         assert ((got - exact).norm() / exact.norm()).item() < 1e-3
+
+
+def test_convolution_diagonal_is_exact_for_small_outputs():
+    """For few output positions the reference switches to ``sum_{n,pos} g^2 a^2`` (asdl/operations/conv.py:64-69),
+    which is not the diagonal ``sum_n (sum_pos g a)^2`` of the Fisher; here the diagonal is always the latter."""
+    torch.manual_seed(0)
+    conv = nn.Conv2d(6, 6, 3)
+    model = nn.Sequential(conv, nn.Tanh(), nn.Flatten(), nn.Linear(6 * 2 * 2, 3))
+    x, t = torch.randn(5, 6, 4, 4), torch.randint(0, 3, (5,))         # 2 x 2 output positions
+    rows = []
+    for i in range(5):
+        model.zero_grad()
+        F.cross_entropy(model(x[i:i + 1]), t[i:i + 1], reduction='sum').backward()
+        rows.append(conv.weight.grad.flatten().clone())
+    model.zero_grad()
+    want = torch.stack(rows).square().sum(dim=0)
+    with asdl.extend(model, asdl.OP_COV_DIAG) as cxt:
+        F.cross_entropy(model(x), t, reduction='sum').backward()
+        got = cxt.cov_diag(conv)['weight'].flatten()
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-7)
