@@ -695,3 +695,102 @@ def test_psgd_factor_formats_and_sparse_lu_match_the_reference(reference):
         results.append(list(state) + list(lib.precond_grad_splu(*state, grads)))
     for want, got in zip(*results):
         assert ((want - got).norm() / want.norm()).item() < 1e-5
+
+
+def _random_network(rng):
+    """A random small classifier: 0-3 convolutions (random kernel / stride / padding / bias, optional BatchNorm2d),
+    0-2 hidden Linear layers (optional LayerNorm / BatchNorm1d), random activations."""
+    layers = []
+    if rng.random() < 0.6:
+        channels, side = 2, 8
+        for _ in range(rng.randint(1, 3)):
+            out_channels, k, stride = rng.choice([3, 4, 6]), rng.choice([1, 2, 3]), rng.choice([1, 1, 2])
+            pad = rng.choice([0, 1]) if k > 1 else 0
+            new_side = (side + 2 * pad - k) // stride + 1
+            if new_side < 2:
+                continue
+            layers.append(nn.Conv2d(channels, out_channels, k, stride=stride, padding=pad, bias=rng.random() < 0.7))
+            channels, side = out_channels, new_side
+            if rng.random() < 0.5:
+                layers.append(nn.BatchNorm2d(channels))
+            layers.append(rng.choice([nn.Tanh, nn.ReLU, nn.Sigmoid])())
+        layers.append(nn.Flatten())
+        width, x = channels * side * side, torch.randn(8, 2, 8, 8)
+    else:
+        width, x = 7, torch.randn(8, 7)
+    for _ in range(rng.randint(0, 2)):
+        new_width = rng.choice([4, 5, 9])
+        layers.append(nn.Linear(width, new_width, bias=rng.random() < 0.7))
+        width = new_width
+        draw = rng.random()
+        if draw < 0.3:
+            layers.append(nn.LayerNorm(width))
+        elif draw < 0.5:
+            layers.append(nn.BatchNorm1d(width))
+        layers.append(rng.choice([nn.Tanh, nn.ReLU])())
+    layers.append(nn.Linear(width, 3))
+    return nn.Sequential(*layers), x
+
+
+@pytest.mark.parametrize('seed', range(12))
+def test_random_networks_kfac_generic_and_fused(reference, seed):
+    import random
+    rng = random.Random(seed)
+    ema, fisher_type = rng.choice([-1, 0.3, 1.0]), rng.choice(['fisher_emp', 'fisher_mc', 'fisher_exact'])
+    damping = rng.choice([1e-1, 1e-2, 1e-3])
+    runs = []
+    for lib, maker in ((reference, 'KfacGradientMaker'), (ours, 'KfacGradientMaker'), (ours, 'FusedKfacGradientMaker')):
+        torch.manual_seed(seed)
+        model, x = _random_network(random.Random(seed))
+        t = torch.randint(0, 3, (8,))
+        gm = getattr(lib, maker)(model, _cfg(lib, data_size=8, damping=damping, ema_decay=ema), fisher_type=fisher_type)
+        opt = torch.optim.SGD(model.parameters(), lr=0.01)
+        grads = []
+        with warnings.catch_warnings():
+            warnings.simplefilter('ignore')
+            for s in range(2):
+                opt.zero_grad()
+                torch.manual_seed(100 + s)
+                dummy = gm.setup_model_call(model, x)
+                gm.setup_loss_call(F.cross_entropy, dummy, t)
+                gm.forward_and_backward()
+                grads.append(torch.cat([p.grad.flatten() for p in model.parameters()]).clone())
+                opt.step()
+        runs.append(grads)
+    for other in runs[1:]:
+        for want, got in zip(runs[0], other):
+            assert ((want - got).norm() / want.norm()).item() < 1e-3
+
+
+@pytest.mark.parametrize('seed', range(12))
+def test_random_networks_fisher_flags(reference, seed):
+    import random
+    rng = random.Random(seed + 500)
+    shape = rng.choice(['full', 'layer_wise', 'kron', 'unit_wise', 'diag'])
+    fisher_type = rng.choice(['fisher_exact', 'fisher_mc', 'fisher_emp'])
+    loss = rng.choice(['cross_entropy', 'mse'])
+    flags = dict(accumulate=rng.random() < 0.4, calc_loss_grad=rng.random() < 0.5, scale=rng.choice([1.0, 0.5, 3.0]))
+    if not flags['accumulate'] and rng.random() < 0.4:
+        flags.update(calc_inv=True, damping=rng.choice([1e-1, 1e-2]))
+    results = []
+    for lib in (reference, ours):
+        torch.manual_seed(seed)
+        model, x = _random_network(random.Random(seed))
+        t = torch.randint(0, 3, (8,)) if loss == 'cross_entropy' else torch.randn(8, 3)
+        fm = lib.get_fisher_maker(model, lib.FisherConfig(fisher_type=fisher_type, fisher_shapes=[shape], loss_type=loss,
+                                                          data_size=8, seed=2))
+        with warnings.catch_warnings():
+            warnings.simplefilter('ignore')
+            for _ in range(2 if flags['accumulate'] else 1):
+                dummy = fm.setup_model_call(model, x)
+                fm.setup_loss_call(F.cross_entropy if loss == 'cross_entropy' else F.mse_loss, dummy, t)
+                out = fm.forward_and_backward(**flags)
+        tensors = _fisher_tensors(model)
+        if flags['calc_loss_grad']:
+            tensors.update({'grad.' + n: p.grad for n, p in model.named_parameters() if p.grad is not None})
+            tensors['loss'] = torch.as_tensor(float(out[1]))
+        results.append(tensors)
+    want, got = results
+    assert set(want) == set(got)
+    for key in want:
+        assert ((want[key] - got[key]).norm() / (want[key].norm() + 1e-30)).item() < 1e-3, key
