@@ -417,15 +417,8 @@ def empirical_natural_gradient(model, inputs, targets, loss_fn=F.cross_entropy, 
         batch_loss = loss_fn(outputs, targets, reduction='none')
         params = [p for p in model.parameters() if p.requires_grad]
         torch.autograd.grad(batch_loss.sum(), params, retain_graph=True)
-    UtU = model.kernel
-    Utg = UtU.sum(dim=1)
-    if data_average:
-        UtU = UtU / n
-    b = _cholesky_solve(UtU, Utg, damping)
-    ones = torch.ones_like(b)
-    if data_average:
-        b, ones = b / n ** 2, ones / n
-    batch_loss.backward(gradient=(ones - b) / damping)
+    from .precondition.smw import woodbury_example_weights
+    batch_loss.backward(gradient=woodbury_example_weights(model.kernel, damping, data_average))
     return batch_loss.mean() if data_average else batch_loss.sum()
 
 
@@ -445,16 +438,11 @@ def empirical_natural_gradient2(model, inputs, targets, loss_fn=F.cross_entropy,
 def empirical_natural_gradient_by_context(cxt: OperationContext, damping=1e-5, data_average_n=None):
     """Re-weights every example by (1 - b)/damping with (K + damping*I) b = K 1 and rebuilds the
     parameter gradients from the saved tensors of ``cxt`` (sum-reduced output-gradients)."""
-    UtU = cxt.calc_kernel()
-    Utg = UtU.sum(dim=1)
-    n = data_average_n
-    if n:
-        UtU = UtU / n
-    b = _cholesky_solve(UtU, Utg, damping)
-    ones = torch.ones_like(b)
-    if n:
-        b, ones = b / n ** 2, ones / n
-    cxt.calc_grads((ones - b) / damping)
+    from .precondition.smw import woodbury_example_weights
+    gram = cxt.calc_kernel()
+    if data_average_n and data_average_n != gram.shape[0]:
+        raise ValueError(f'data_average_n ({data_average_n}) has to be the batch size ({gram.shape[0]}).')
+    cxt.calc_grads(woodbury_example_weights(gram, damping, bool(data_average_n)))
 
 
 def kernel_vector_product(model, inputs, vec):

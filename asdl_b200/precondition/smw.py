@@ -21,15 +21,33 @@ __all__ = ['SmwEmpNaturalGradientConfig', 'SmwEmpNaturalGradientMaker']
 
 
 def zero_kernel(model: nn.Module, n_data1: int, n_data2: int):
-    p = next(iter(model.parameters()))
-    model.kernel = torch.zeros(n_data1, n_data2, device=p.device, dtype=p.dtype)
+    """Fresh ``model.kernel`` (n_data1 x n_data2) for the Gram hooks to add into."""
+    like = next(iter(model.parameters()))
+    model.kernel = like.new_zeros(n_data1, n_data2)
 
 
 def cholesky_solve(A, b, eps=1e-8):
-    """(A + eps*I)^-1 b without touching A."""
-    eye = torch.eye(A.shape[-1], device=A.device, dtype=A.dtype)
-    chol = torch.linalg.cholesky(A + eps * eye)
-    return torch.cholesky_solve(b.unsqueeze(-1), chol).squeeze(-1)
+    """(A + eps*I)^-1 b without touching A (a breakdown of the factorisation raises the damping, see
+    :func:`asdl_b200.ops.damped_cholesky`)."""
+    from .. import ops
+    return torch.cholesky_solve(b.unsqueeze(-1), ops.damped_cholesky(A, eps)).squeeze(-1)
+
+
+def woodbury_example_weights(gram: Tensor, damping: float, data_average: bool) -> Tensor:
+    """Per-example loss weights w such that back-propagating ``sum_i w_i loss_i`` leaves
+    ``(F + damping*I)^-1 grad`` in ``param.grad``, with F the empirical Fisher of the batch.
+
+    With U the n x p matrix of per-example gradients, ``gram = U U^T`` and g = U^T 1 (divided by n when the
+    loss is a mean), Woodbury gives ``(U^T U / n + damping I)^-1 g = U^T (1 - b) / damping`` where
+    ``(gram / n + damping I) b = gram 1`` (and the 1/n factors of the mean distributed as below)."""
+    n = gram.shape[0]
+    rhs = gram.sum(dim=1)
+    scale = n if data_average else 1
+    b = cholesky_solve(gram / scale, rhs, damping)
+    ones = torch.ones_like(b)
+    if data_average:
+        return (ones / n - b / n ** 2) / damping
+    return (ones - b) / damping
 
 
 @dataclass
@@ -50,27 +68,20 @@ class SmwEmpNaturalGradientMaker(GradientMaker):
         super().__init__(model)
         self.config = config
 
-    def forward_and_backward(self) -> Tuple[Any, Tensor]:
+    def _loss_is_a_mean(self) -> bool:
         if isinstance(self._loss_fn, nn.Module):
-            data_average = self._loss_fn.reduction == 'mean'
-        else:
-            data_average = self._loss_fn_kwargs.get('reduction', 'mean') == 'mean'
-        model, n, damping = self.model, self.config.data_size, self.config.damping
-        with extend(model, OP_GRAM_HADAMARD):
-            zero_kernel(model, n, n)
-            self.forward()
-            batch_loss = self._loss
-            params = [p for p in model.parameters() if p.requires_grad]
-            torch.autograd.grad(batch_loss.sum(), params, retain_graph=True)
-        UtU = model.kernel  # n x n Gram matrix of per-example gradients
-        Utg = UtU.sum(dim=1)
-        if data_average:
-            UtU = UtU / n
-        b = cholesky_solve(UtU, Utg, damping)
-        ones = torch.ones_like(b)
-        if data_average:
-            b = b / n ** 2
-            ones = ones / n
-        batch_loss.backward(gradient=(ones - b) / damping)
-        self._loss = batch_loss.mean() if data_average else batch_loss.sum()
+            return self._loss_fn.reduction == 'mean'
+        return self._loss_fn_kwargs.get('reduction', 'mean') == 'mean'
+
+    def forward_and_backward(self) -> Tuple[Any, Tensor]:
+        n = self.config.data_size
+        with extend(self.model, OP_GRAM_HADAMARD):
+            zero_kernel(self.model, n, n)
+            self.forward()                       # per-example losses (reduction forced to 'none')
+            losses = self._loss
+            trainable = [p for p in self.model.parameters() if p.requires_grad]
+            torch.autograd.grad(losses.sum(), trainable, retain_graph=True)   # fills model.kernel through the hooks
+        mean = self._loss_is_a_mean()
+        losses.backward(gradient=woodbury_example_weights(self.model.kernel, self.config.damping, mean))
+        self._loss = losses.mean() if mean else losses.sum()
         return self._model_output, self._loss
