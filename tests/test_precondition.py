@@ -521,3 +521,36 @@ def test_makers_under_bf16_autocast(name):
     full, mixed = run(False), run(True)
     assert torch.isfinite(mixed).all()
     assert F.cosine_similarity(full, mixed, dim=0) > 0.98
+
+
+@pytest.mark.parametrize('maker', [asdl.KfacGradientMaker, asdl.FusedKfacGradientMaker])
+@pytest.mark.parametrize('stop', [1, 2, 4, 5])
+def test_resume_at_any_point_of_the_update_schedule(maker, stop):
+    """Curvature every 2nd and inverses every 3rd step: a run resumed after ``stop`` steps continues with
+    the gradients of the uninterrupted run."""
+    def make(model):
+        cfg = asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=0.3, curvature_upd_interval=2,
+                                         preconditioner_upd_interval=3)
+        return maker(model, cfg, fisher_type=asdl.FISHER_EMP)
+
+    def one_step(gm, model, opt):
+        opt.zero_grad()
+        step(gm, model, x, t)
+        grads = torch.cat([p.grad.flatten() for p in model.parameters()]).clone()
+        opt.step()
+        return grads
+
+    torch.manual_seed(1)
+    model = make_net('cnn')
+    x, t = make_data('cnn', 8, 'cross_entropy')
+    gm, opt = make(model), torch.optim.SGD(model.parameters(), lr=0.01)
+    for _ in range(stop):
+        one_step(gm, model, opt)
+    state, weights = copy.deepcopy(gm.state_dict()), copy.deepcopy(model.state_dict())
+    want = [one_step(gm, model, opt) for _ in range(3)]
+    resumed = make_net('cnn')
+    resumed.load_state_dict(weights)
+    gm2, opt2 = make(resumed), torch.optim.SGD(resumed.parameters(), lr=0.01)
+    gm2.load_state_dict(state)
+    for w in want:
+        torch.testing.assert_close(one_step(gm2, resumed, opt2), w, rtol=1e-5, atol=1e-7)
