@@ -4,7 +4,9 @@
 namespace b200 {
 void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
                bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta, bool sym,
-               c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo, int64_t nsplit);
+               c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo, int64_t nsplit,
+               c10::optional<at::Tensor> out_mid, int64_t kchunk);
+void set_gemm_wide(int64_t mode);
 int64_t read_status(int64_t dev);
 int64_t launch_count();
 void reserve_scratch(int64_t dev, int64_t nfloats);
@@ -21,7 +23,7 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
                    bool a_kmajor, bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta,
                    bool sym, c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
                    int64_t dst_ptr, int64_t ldc, bool atomic, std::vector<int64_t> extra_ptrs,
-                   int64_t nsplit);
+                   int64_t nsplit, c10::optional<at::Tensor> out_mid, int64_t kchunk);
 void gemm_plan_finalize(int64_t id);
 void gemm_plan_run(int64_t id);
 void cast_pad_bf16_grouped(at::Tensor table, int64_t count);
@@ -50,13 +52,16 @@ void symm_mirror_lower(at::Tensor local, at::Tensor mats, int64_t n_max);
 void symm_reduce_slots(at::Tensor local, at::Tensor table, int64_t world, int64_t slot_stride, int64_t n_max,
                        double beta);
 void chol_inverse(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs, at::Tensor damping);
+void chol_inverse_tc(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs, at::Tensor damping);
+void chol_inverse_tc_clear_cache();
 }  // namespace b200
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("umma_gemm", &b200::umma_gemm, "tcgen05 TN GEMM / SYRK", py::arg("a_segs"),
         py::arg("b_segs"), py::arg("a_kmajor"), py::arg("b_kmajor"), py::arg("C"),
         py::arg("alpha"), py::arg("beta"), py::arg("sym"), py::arg("out_hi"), py::arg("out_lo"),
-        py::arg("nsplit"));
+        py::arg("nsplit"), py::arg("out_mid") = py::none(), py::arg("kchunk") = 0);
+  m.def("set_gemm_wide", &b200::set_gemm_wide);
   m.def("read_status", &b200::read_status);
   m.def("launch_count", &b200::launch_count);
   m.def("reserve_scratch", &b200::reserve_scratch);
@@ -65,7 +70,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("umma_gemm_to_ptr", &b200::umma_gemm_to_ptr);
   m.def("gemm_plan_new", &b200::gemm_plan_new);
   m.def("gemm_plan_free", &b200::gemm_plan_free);
-  m.def("gemm_plan_add", &b200::gemm_plan_add);
+  m.def("gemm_plan_add", &b200::gemm_plan_add, py::arg("plan"), py::arg("a_segs"), py::arg("b_segs"),
+        py::arg("a_kmajor"), py::arg("b_kmajor"), py::arg("C"), py::arg("alpha"), py::arg("beta"), py::arg("sym"),
+        py::arg("out_hi"), py::arg("out_lo"), py::arg("dst_ptr"), py::arg("ldc"), py::arg("atomic"),
+        py::arg("extra_ptrs"), py::arg("nsplit"), py::arg("out_mid") = py::none(), py::arg("kchunk") = 0);
   m.def("gemm_plan_finalize", &b200::gemm_plan_finalize);
   m.def("gemm_plan_run", &b200::gemm_plan_run);
   m.def("cast_pad_bf16_grouped", &b200::cast_pad_bf16_grouped);
@@ -84,5 +92,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_scale_segments", &b200::symm_scale_segments);
   m.def("symm_mirror_lower", &b200::symm_mirror_lower);
   m.def("symm_reduce_slots", &b200::symm_reduce_slots);
-  m.def("chol_inverse", &b200::chol_inverse, "grouped damped SPD inverse (fp32)");
+  m.def("chol_inverse", &b200::chol_inverse, "grouped damped SPD inverse (fp32, CUDA cores)");
+  m.def("chol_inverse_tc", &b200::chol_inverse_tc, "grouped damped SPD inverse (fp32-accurate, tensor cores)");
+  m.def("chol_inverse_tc_clear_cache", &b200::chol_inverse_tc_clear_cache);
 }

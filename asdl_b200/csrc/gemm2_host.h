@@ -1,0 +1,28 @@
+// Host-side interface of the persistent tcgen05 GEMM (umma_gemm2.cuh) for the other translation
+// units of the extension (the tensor-core Cholesky inverse builds its own problem tables and work
+// lists and runs them through these launchers).
+#pragma once
+#include "host_utils.h"
+#include "umma_gemm2.cuh"
+
+namespace b200 {
+
+// Tensor map of one bf16 operand.  `mn` x `k` logical extents; `kmajor`: stored [mn, k] row-major
+// with pitch `ld` elements, otherwise stored [k, mn] row-major.  `box_mn`: tile extent along MN
+// for K-major operands (128 for A, the tile width for B); MN-major operands are always loaded as
+// 64 x 64 boxes.
+void g2_encode_operand(CUtensorMap* tm, const void* base, int64_t mn, int64_t k, int64_t ld,
+                       bool kmajor, int box_mn);
+
+// SM count of a device (cached).
+int g2_sm_count(int dev);
+
+// Runs `n_work` work items of a device-resident problem table on `stream`.
+void g2_launch_list(const GemmProblem2* d_probs, const GemmWork2* d_work, int n_work, bool wide,
+                    int dev, cudaStream_t stream);
+
+// Split-K reduction of the listed tiles (one work item per tile).
+void g2_launch_reduce_list(const GemmProblem2* d_probs, const GemmWork2* d_work, int n_work, bool wide,
+                           cudaStream_t stream);
+
+}  // namespace b200

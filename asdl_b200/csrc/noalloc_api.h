@@ -22,7 +22,10 @@ extern "C" {
 //
 //   x      device pointer, bf16, `rows` x `n` row-major with row pitch `ldx` elements;
 //          16-byte aligned, `ldx` a multiple of 8
-//   c      device pointer, fp32, n x n with row pitch `ldc` (>= n); read only when beta != 0
+//   c      device pointer, fp32, n x n with row pitch `ldc` (>= n); read only when beta != 0;
+//          16-byte aligned whenever `ldc` is a multiple of 4 (the kernel then uses 16-byte
+//          accesses), 4-byte aligned otherwise
+//   rows   at most 2^31 - 65; n at most 65536
 //   nsplit number of row slices reduced through the scratch buffer; 0 picks one automatically
 //   stream a cudaStream_t (0 = the default stream); the call only enqueues work on it
 //   err / err_len  optional buffer that receives a message when the call fails
@@ -44,6 +47,15 @@ extern "C" {
 int asdl_b200_syrk_bf16_noalloc(const void* x, long long rows, int n, long long ldx, float* c,
                                 int ldc, float alpha, float beta, int nsplit, void* stream,
                                 char* err, int err_len);
+
+
+// Every wait inside the kernels is bounded; one that runs out leaves its output tile unwritten
+// and records a code in a status word of the library image.  This function waits for the work
+// enqueued so far on the current device, copies that word to *code (0 = no problem, otherwise
+// 1..3 = a wait for a load stage / a free stage / the accumulator ran out) and clears it.
+// Returns 0 when *code was written.  Allocates nothing.  Call it after the stream that ran
+// asdl_b200_syrk_bf16_noalloc has been synchronised, or simply when the results are needed.
+int asdl_b200_noalloc_status(int* code);
 
 #ifdef __cplusplus
 }

@@ -29,6 +29,8 @@ static __device__ __align__(256) float g_noalloc_scratch[kScratchFloats];
 static __device__ int g_noalloc_status;
 
 constexpr int kMaxDevices = 64;
+constexpr long long kMaxRows = 0x7fffffffll - 64;  // rows + 63 must fit a signed 32-bit integer
+constexpr long long kMaxN = 1 << 16;               // 512 tile rows: the tile count stays far below 2^31
 
 struct DeviceSlot {
   bool ready = false;
@@ -101,6 +103,13 @@ extern "C" int asdl_b200_syrk_bf16_noalloc(const void* x, long long rows, int n,
   if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return fail(err, err_len, 4, "x must be 16-byte aligned");
   if (ldc < n) return fail(err, err_len, 5, "ldc (%lld) must be >= n (%lld)", ldc, n);
   if (nsplit < 0) return fail(err, err_len, 6, "nsplit (%lld) must be >= 0", nsplit);
+  // the epilogue reads and writes C with 16-byte vectors whenever the row pitch allows it
+  if ((ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(c) & 15) != 0)
+    return fail(err, err_len, 17, "c must be 16-byte aligned when ldc (%lld) is a multiple of 4", ldc);
+  if ((reinterpret_cast<uintptr_t>(c) & 3) != 0) return fail(err, err_len, 17, "c must be 4-byte aligned");
+  // the kernel keeps the row count and the tile arithmetic in 32-bit integers
+  if (rows > kMaxRows) return fail(err, err_len, 18, "rows (%lld) exceeds the supported maximum (%lld)", rows, kMaxRows);
+  if (n > kMaxN) return fail(err, err_len, 19, "n (%lld) exceeds the supported maximum (%lld)", n, kMaxN);
 
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -158,5 +167,24 @@ extern "C" int asdl_b200_syrk_bf16_noalloc(const void* x, long long rows, int n,
     splitk_reduce_kernel_noalloc<<<dim3(P.ntiles, 16, 1), 256, 0, s>>>(P, nullptr, nullptr);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(err, err_len, 16, "kernel launch failed with CUDA error %lld", e);
+  return 0;
+}
+
+// Reads the status word that the kernels of this entry point write when one of their bounded
+// waits ran out (the b200::ERR_* codes), stores it in *code and clears it.  Waits for the work
+// already enqueued on the current device; allocates nothing.
+extern "C" int asdl_b200_noalloc_status(int* code) {
+  if (code == nullptr) return 1;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 7;
+  DeviceSlot* slot = nullptr;
+  if (int rc = device_slot(dev, &slot, nullptr, 0)) return rc;
+  int value = 0;
+  if (cudaMemcpyFromSymbol(&value, g_noalloc_status, sizeof(int)) != cudaSuccess) return 20;
+  if (value != 0) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_noalloc_status, &zero, sizeof(int)) != cudaSuccess) return 21;
+  }
+  *code = value;
   return 0;
 }

@@ -1,15 +1,21 @@
-// Host launcher for the tcgen05 TN-GEMM / SYRK kernel (see umma_gemm.cuh).
-#include "host_utils.h"
-#include "umma_gemm.cuh"
+// Host launcher for the persistent tcgen05 TN-GEMM / SYRK kernel (see umma_gemm2.cuh).
+#include "gemm2_host.h"
 
+#include <algorithm>
 #include <unordered_map>
 
 namespace b200 {
 
 namespace {
 
+// Split-K partials of single launches go through one scratch buffer per device, used as a ring.
+// Launches on one stream reuse it in order; a launch on another stream first waits for the
+// stream that used the ring last, so two streams never overlap on it.
 struct Ring {
   size_t off = 0;
+  cudaStream_t last = nullptr;
+  bool used = false;
+  cudaEvent_t ev = nullptr;
 };
 Ring g_scratch_ring[16];
 
@@ -22,20 +28,93 @@ void check_operand(const at::Tensor& t, const char* name) {
               " must be 16-byte aligned");
 }
 
-bool g_attr_set = false;
+bool g_attr_set[2] = {false, false};
+int g_wide_mode = 0;  // 0: 128-wide tiles only, 1: 256-wide tiles for large outputs, 2: wherever legal
+
+template <int BN>
+void ensure_attr() {
+  const int i = BN == 128 ? 0 : 1;
+  if (!g_attr_set[i]) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(umma_gemm2_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         G2Cfg<BN>::SMEM_BYTES));
+    g_attr_set[i] = true;
+  }
+}
+
+bool stream_is_capturing(cudaStream_t s) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &st) != cudaSuccess) {
+    cudaGetLastError();
+    return true;
+  }
+  return st != cudaStreamCaptureStatusNone;
+}
+
+int tile_count(int tiles_m, int tiles_n, bool sym, int bn) {
+  if (!sym) return tiles_m * tiles_n;
+  int n = 0;
+  for (int tm = 0; tm < tiles_m; ++tm) n += (tm * G2_BM) / bn + 1;
+  return n;
+}
 
 }  // namespace
 
+int g2_sm_count(int dev) {
+  static int cached[64] = {0};
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+  const int n = at::cuda::getDeviceProperties(dev)->multiProcessorCount;
+  if (dev >= 0 && dev < 64) cached[dev] = n;
+  return n;
+}
+
+void g2_encode_operand(CUtensorMap* tm, const void* base, int64_t mn, int64_t k, int64_t ld,
+                       bool kmajor, int box_mn) {
+  if (kmajor)
+    encode_tmap_bf16_2d(tm, base, k, mn, ld, 64, box_mn);
+  else
+    encode_tmap_bf16_2d(tm, base, mn, k, ld, 64, G2_BK);
+}
+
+void g2_launch_list(const GemmProblem2* d_probs, const GemmWork2* d_work, int n_work, bool wide,
+                    int dev, cudaStream_t stream) {
+  if (n_work <= 0) return;
+  const int grid = std::min(n_work, g2_sm_count(dev));
+  GemmProblem2 dummy;
+  std::memset(&dummy, 0, sizeof(dummy));
+  if (wide) {
+    ensure_attr<256>();
+    umma_gemm2_kernel<256><<<grid, G2_THREADS, G2Cfg<256>::SMEM_BYTES, stream>>>(dummy, d_probs, d_work, n_work);
+  } else {
+    ensure_attr<128>();
+    umma_gemm2_kernel<128><<<grid, G2_THREADS, G2Cfg<128>::SMEM_BYTES, stream>>>(dummy, d_probs, d_work, n_work);
+  }
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
+void g2_launch_reduce_list(const GemmProblem2* d_probs, const GemmWork2* d_work, int n_work, bool wide,
+                           cudaStream_t stream) {
+  if (n_work <= 0) return;
+  GemmProblem2 dummy;
+  std::memset(&dummy, 0, sizeof(dummy));
+  if (wide)
+    splitk_reduce2_kernel<256><<<dim3(n_work, 32, 1), 256, 0, stream>>>(dummy, d_probs, d_work);
+  else
+    splitk_reduce2_kernel<128><<<dim3(n_work, 16, 1), 256, 0, stream>>>(dummy, d_probs, d_work);
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
 // Fills the scalar fields of a problem and encodes its tensor maps.
-void gemm_fill_problem(GemmProblem& P, const std::vector<at::Tensor>& a_segs,
+void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
                        const std::vector<at::Tensor>& b_segs, bool a_kmajor, bool b_kmajor,
                        const c10::optional<at::Tensor>& C, double alpha, double beta, bool sym,
-                       const c10::optional<at::Tensor>& out_hi,
-                       const c10::optional<at::Tensor>& out_lo, int64_t nsplit_req, int n_sms,
+                       const c10::optional<at::Tensor>& out_hi, const c10::optional<at::Tensor>& out_mid,
+                       const c10::optional<at::Tensor>& out_lo, int64_t nsplit_req, int64_t kchunk, int n_sms,
                        bool allow_no_output = false) {
   const int nseg = static_cast<int>(a_segs.size());
-  TORCH_CHECK(nseg >= 1 && nseg <= 3 && b_segs.size() == a_segs.size(),
-              "between 1 and 3 operand segments are supported");
+  TORCH_CHECK(nseg >= 1 && nseg <= G2_MAX_SEG && b_segs.size() == a_segs.size(),
+              "between 1 and 6 operand segments are supported");
   std::memset(&P, 0, sizeof(P));
   const at::Tensor& a0 = a_segs[0];
   const at::Tensor& b0 = b_segs[0];
@@ -44,34 +123,33 @@ void gemm_fill_problem(GemmProblem& P, const std::vector<at::Tensor>& a_segs,
   const int64_t N = b_kmajor ? b0.size(0) : b0.size(1);
   const int64_t Kb = b_kmajor ? b0.size(1) : b0.size(0);
   TORCH_CHECK(K == Kb, "contraction sizes differ: ", K, " vs ", Kb);
+  TORCH_CHECK(M > 0 && N > 0 && M < (1 << 30) && N < (1 << 30) && K < (1ll << 31) - 64, "matrix sizes out of range");
+  TORCH_CHECK(kchunk >= 0, "kchunk must not be negative");
+  if (sym) TORCH_CHECK(M == N, "symmetric mode needs a square output");
+  const bool wide = kchunk == 0 && (g_wide_mode == 2 || (g_wide_mode == 1 && N >= 1024 && M >= 1024));
+  const int bn = wide ? 256 : 128;
   for (int s = 0; s < nseg; ++s) {
     check_operand(a_segs[s], "A");
     check_operand(b_segs[s], "B");
     TORCH_CHECK(a_segs[s].sizes() == a0.sizes() && b_segs[s].sizes() == b0.sizes(),
                 "all segments must have the same shape");
-    if (a_kmajor)
-      encode_tmap_bf16_2d(&P.tmA[s], a_segs[s].data_ptr(), K, M, a_segs[s].stride(0), 64, G_BM);
-    else
-      encode_tmap_bf16_2d(&P.tmA[s], a_segs[s].data_ptr(), M, K, a_segs[s].stride(0), 64, G_BK);
-    if (b_kmajor)
-      encode_tmap_bf16_2d(&P.tmB[s], b_segs[s].data_ptr(), K, N, b_segs[s].stride(0), 64, G_BN);
-    else
-      encode_tmap_bf16_2d(&P.tmB[s], b_segs[s].data_ptr(), N, K, b_segs[s].stride(0), 64, G_BK);
+    g2_encode_operand(&P.tmA[s], a_segs[s].data_ptr(), M, K, a_segs[s].stride(0), a_kmajor, G2_BM);
+    g2_encode_operand(&P.tmB[s], b_segs[s].data_ptr(), N, K, b_segs[s].stride(0), b_kmajor, bn);
   }
-  bool same_ab = sym && a_kmajor == b_kmajor;
+  bool same_ab = sym && !wide && a_kmajor == b_kmajor;
   for (int s = 0; s < nseg && same_ab; ++s)
     same_ab = a_segs[s].data_ptr() == b_segs[s].data_ptr() &&
               a_segs[s].stride(0) == b_segs[s].stride(0);
-  if (sym) TORCH_CHECK(M == N, "symmetric mode needs a square output");
 
   P.M = static_cast<int>(M);
   P.N = static_cast<int>(N);
   P.K = static_cast<int>(K);
   P.nseg = nseg;
+  P.kchunk = static_cast<int>(kchunk);
   P.alpha = static_cast<float>(alpha);
   P.beta = static_cast<float>(beta);
-  P.flags = (sym ? GF_SYM : 0) | (a_kmajor ? GF_A_KMAJOR : 0) | (b_kmajor ? GF_B_KMAJOR : 0) |
-            (same_ab ? GF_SAME_AB : 0);
+  P.flags = (sym ? G2F_SYM : 0) | (a_kmajor ? G2F_A_KMAJOR : 0) | (b_kmajor ? G2F_B_KMAJOR : 0) |
+            (same_ab ? G2F_SAME_AB : 0) | (wide ? G2F_WIDE : 0);
   if (C.has_value()) {
     const at::Tensor& c = *C;
     TORCH_CHECK(c.is_cuda() && c.scalar_type() == at::kFloat && c.dim() == 2 && c.stride(1) == 1 &&
@@ -90,19 +168,27 @@ void gemm_fill_problem(GemmProblem& P, const std::vector<at::Tensor>& a_segs,
                 "out_hi must be a [M, >=N] bf16 CUDA tensor");
     P.out_hi = reinterpret_cast<__nv_bfloat16*>(h.data_ptr());
     P.ld_out = static_cast<int>(h.stride(0));
+    auto same_layout = [&](const at::Tensor& t) {
+      return t.sizes() == h.sizes() && t.strides() == h.strides() && t.scalar_type() == at::kBFloat16 && t.is_cuda();
+    };
     if (out_lo.has_value()) {
-      TORCH_CHECK(out_lo->sizes() == h.sizes() && out_lo->strides() == h.strides() &&
-                      out_lo->scalar_type() == at::kBFloat16,
-                  "out_lo must match out_hi");
+      TORCH_CHECK(same_layout(*out_lo), "out_lo must match out_hi");
       P.out_lo = reinterpret_cast<__nv_bfloat16*>(out_lo->data_ptr());
     }
+    if (out_mid.has_value()) {
+      TORCH_CHECK(out_lo.has_value() && same_layout(*out_mid), "out_mid needs out_lo and must match out_hi");
+      P.out_mid = reinterpret_cast<__nv_bfloat16*>(out_mid->data_ptr());
+    }
+    if (sym) TORCH_CHECK(h.size(1) >= M, "bf16 outputs of a symmetric product are written on both triangles");
+  } else {
+    TORCH_CHECK(!out_lo.has_value() && !out_mid.has_value(), "out_lo / out_mid need out_hi");
   }
   TORCH_CHECK(allow_no_output || P.C != nullptr || P.out_hi != nullptr, "no output given");
 
-  P.tiles_m = (P.M + G_BM - 1) / G_BM;
-  P.tiles_n = (P.N + G_BN - 1) / G_BN;
-  P.ntiles = sym ? P.tiles_m * (P.tiles_m + 1) / 2 : P.tiles_m * P.tiles_n;
-  const int kb_total = (P.K + G_BK - 1) / G_BK;
+  P.tiles_m = (P.M + G2_BM - 1) / G2_BM;
+  P.tiles_n = (P.N + bn - 1) / bn;
+  P.ntiles = tile_count(P.tiles_m, P.tiles_n, sym, bn);
+  const int kb_total = (P.K + G2_BK - 1) / G2_BK;
   int nsplit = static_cast<int>(nsplit_req);
   if (nsplit <= 0) {
     const int target = 2 * n_sms;
@@ -116,54 +202,72 @@ void gemm_fill_problem(GemmProblem& P, const std::vector<at::Tensor>& a_segs,
   P.nsplit = nsplit;
 }
 
-void gemm_attach_scratch(GemmProblem& P, int dev) {
+static bool needs_ws(const GemmProblem2& P) { return P.nsplit > 1 && !(P.flags & G2F_ATOMIC); }
+static int tile_width(const GemmProblem2& P) { return (P.flags & G2F_WIDE) ? 256 : 128; }
+
+void gemm_attach_scratch(GemmProblem2& P, int dev, cudaStream_t stream) {
   DeviceState& st = device_state(dev);
   P.status = st.status.data_ptr<int>();
   const int slot = dev & 15;
-  if (P.nsplit > 1 && !(P.flags & GF_ATOMIC)) {
-    const size_t need = static_cast<size_t>(P.ntiles) * P.nsplit * G_BM * G_BN;
+  if (needs_ws(P)) {
+    const size_t need = static_cast<size_t>(P.ntiles) * P.nsplit * G2_BM * tile_width(P);
     const size_t cap_min = need * 4;
     float* base = ensure_scratch(dev, cap_min);
     const size_t cap = static_cast<size_t>(device_state(dev).scratch.numel());
     Ring& sr = g_scratch_ring[slot];
+    if (sr.used && sr.last != stream && !stream_is_capturing(stream) && !stream_is_capturing(sr.last)) {
+      // another stream used the ring last: order this launch after that stream's work
+      if (sr.ev == nullptr) B200_CUDA_CHECK(cudaEventCreateWithFlags(&sr.ev, cudaEventDisableTiming));
+      B200_CUDA_CHECK(cudaEventRecord(sr.ev, sr.last));
+      B200_CUDA_CHECK(cudaStreamWaitEvent(stream, sr.ev, 0));
+    }
+    sr.last = stream;
+    sr.used = true;
     if (sr.off + need > cap) sr.off = 0;
     P.ws = base + sr.off;
     sr.off += need;
   }
 }
 
-void gemm_launch_single(const GemmProblem& P, cudaStream_t stream) {
-  if (!g_attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(umma_gemm_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM_BYTES));
-    g_attr_set = true;
+void gemm_launch_single(const GemmProblem2& P, int dev, cudaStream_t stream) {
+  const int n_work = P.ntiles * P.nsplit;
+  const int grid = std::min(n_work, g2_sm_count(dev));
+  const bool wide = (P.flags & G2F_WIDE) != 0;
+  if (wide) {
+    ensure_attr<256>();
+    umma_gemm2_kernel<256><<<grid, G2_THREADS, G2Cfg<256>::SMEM_BYTES, stream>>>(P, nullptr, nullptr, n_work);
+  } else {
+    ensure_attr<128>();
+    umma_gemm2_kernel<128><<<grid, G2_THREADS, G2Cfg<128>::SMEM_BYTES, stream>>>(P, nullptr, nullptr, n_work);
   }
-  dim3 grid(P.ntiles, P.nsplit, 1);
-  umma_gemm_kernel<<<grid, G_THREADS, G_SMEM_BYTES, stream>>>(P, nullptr, nullptr);
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch();
-  if (P.nsplit > 1 && !(P.flags & GF_ATOMIC)) {
-    dim3 rgrid(P.ntiles, 16, 1);
-    splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(P, nullptr, nullptr);
+  if (needs_ws(P)) {
+    if (wide)
+      splitk_reduce2_kernel<256><<<dim3(P.ntiles, 32, 1), 256, 0, stream>>>(P, nullptr, nullptr);
+    else
+      splitk_reduce2_kernel<128><<<dim3(P.ntiles, 16, 1), 256, 0, stream>>>(P, nullptr, nullptr);
     B200_CUDA_CHECK(cudaGetLastError());
     count_launch();
   }
 }
 
-// Python entry: C = alpha * A^T B (+ beta C), optionally symmetric, optionally bf16 hi/lo outputs.
+// Python entry: C = alpha * A^T B (+ beta C), optionally symmetric, optionally bf16 split outputs.
+// `kchunk` > 0 cuts the contraction into chunks of that many 64-wide K blocks that are summed in
+// fp32 registers (fp32-grade products from split operands; see umma_gemm2.cuh).
 void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
                bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta, bool sym,
                c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
-               int64_t nsplit) {
+               int64_t nsplit, c10::optional<at::Tensor> out_mid, int64_t kchunk) {
   TORCH_CHECK(!a_segs.empty(), "no operands");
   const int dev = a_segs[0].get_device();
   c10::cuda::CUDAGuard guard(dev);
-  const int n_sms = at::cuda::getDeviceProperties(dev)->multiProcessorCount;
-  GemmProblem P;
-  gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, C, alpha, beta, sym, out_hi, out_lo,
-                    nsplit, n_sms);
-  gemm_attach_scratch(P, dev);
-  gemm_launch_single(P, at::cuda::getCurrentCUDAStream(dev).stream());
+  GemmProblem2 P;
+  gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, C, alpha, beta, sym, out_hi, out_mid, out_lo,
+                    nsplit, kchunk, g2_sm_count(dev));
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  gemm_attach_scratch(P, dev, stream);
+  gemm_launch_single(P, dev, stream);
 }
 
 // Variant whose fp32 result goes to raw device addresses - typically symmetric-memory buffers of
@@ -174,44 +278,45 @@ void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_
                       std::vector<int64_t> extra_ptrs, int64_t nsplit) {
   TORCH_CHECK(!a_segs.empty(), "no operands");
   TORCH_CHECK(dst_ptr != 0 && (dst_ptr & 15) == 0, "destination must be a 16-byte aligned device address");
-  TORCH_CHECK(static_cast<int>(extra_ptrs.size()) <= G_MAX_EXTRA, "too many extra destinations");
+  TORCH_CHECK(static_cast<int>(extra_ptrs.size()) <= G2_MAX_EXTRA, "too many extra destinations");
   TORCH_CHECK(!((atomic == 1 || atomic == 2) && !extra_ptrs.empty()),
               "extra destinations are not supported in atomic mode");
   const int dev = a_segs[0].get_device();
   c10::cuda::CUDAGuard guard(dev);
-  const int n_sms = at::cuda::getDeviceProperties(dev)->multiProcessorCount;
-  GemmProblem P;
-  // a dummy bf16 output satisfies the "some output" check; it is cleared again below
+  GemmProblem2 P;
   gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, c10::nullopt, alpha, 0.0, sym,
-                    c10::nullopt, c10::nullopt, nsplit, n_sms, /*allow_no_output=*/true);
+                    c10::nullopt, c10::nullopt, c10::nullopt, nsplit, 0, g2_sm_count(dev),
+                    /*allow_no_output=*/true);
   P.C = reinterpret_cast<float*>(dst_ptr);
   P.Cin = P.C;
   P.ldc = static_cast<int>(ldc);
   TORCH_CHECK(P.ldc >= P.N, "ldc is smaller than the number of columns");
-  if (atomic == 1 || atomic == 2) P.flags |= GF_ATOMIC;
+  if (atomic == 1 || atomic == 2) P.flags |= G2F_ATOMIC;
   if (atomic == 2 || atomic == 3) {
     TORCH_CHECK(sym, "lower-triangle output needs the symmetric mode");
-    P.flags |= GF_LOWER;
+    P.flags |= G2F_LOWER;
   }
   P.n_extra = static_cast<int>(extra_ptrs.size());
   for (int e = 0; e < P.n_extra; ++e) {
     TORCH_CHECK((extra_ptrs[e] & 15) == 0, "destinations must be 16-byte aligned");
     P.C_extra[e] = reinterpret_cast<float*>(extra_ptrs[e]);
   }
-  gemm_attach_scratch(P, dev);
-  gemm_launch_single(P, at::cuda::getCurrentCUDAStream(dev).stream());
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  gemm_attach_scratch(P, dev, stream);
+  gemm_launch_single(P, dev, stream);
 }
 
 // ---- grouped execution ---------------------------------------------------------------------------
 // A plan is a fixed list of GEMM problems whose operand addresses do not change (persistent
 // buffers).  Its problem table and tile list live in device memory, so running the plan is two
-// launches at most (all tiles of all problems, then the split-K reductions) with no host-side
-// descriptor work - which also makes it replayable from a CUDA graph.
+// launches at most (all tiles of all problems on persistent CTAs, then the split-K reductions)
+// with no host-side descriptor work - which also makes it replayable from a CUDA graph.
 struct GemmPlan {
-  std::vector<GemmProblem> problems;
+  std::vector<GemmProblem2> problems;
   std::vector<std::vector<at::Tensor>> keep_alive;  // operands / outputs referenced by raw pointer
   at::Tensor d_problems, d_work, d_rwork, scratch;
   int n_work = 0, n_rwork = 0, dev = 0;
+  bool wide = false;
   bool finalized = false;
 };
 
@@ -230,16 +335,24 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
                    bool a_kmajor, bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta,
                    bool sym, c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
                    int64_t dst_ptr, int64_t ldc, bool atomic, std::vector<int64_t> extra_ptrs,
-                   int64_t nsplit) {
+                   int64_t nsplit, c10::optional<at::Tensor> out_mid, int64_t kchunk) {
   auto it = g_plans.find(id);
   TORCH_CHECK(it != g_plans.end() && !it->second.finalized, "unknown or finalized plan");
   GemmPlan& plan = it->second;
   TORCH_CHECK(!a_segs.empty(), "no operands");
   plan.dev = a_segs[0].get_device();
   c10::cuda::CUDAGuard guard(plan.dev);
-  GemmProblem P;
-  gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, C, alpha, beta, sym, out_hi, out_lo,
-                    nsplit <= 0 ? 1 : nsplit, 148, /*allow_no_output=*/dst_ptr != 0);
+  GemmProblem2 P;
+  const int saved_mode = g_wide_mode;
+  g_wide_mode = 0;  // the tiles of a plan share one kernel instantiation: 128-wide
+  try {
+    gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, C, alpha, beta, sym, out_hi, out_mid, out_lo,
+                      nsplit <= 0 ? 1 : nsplit, kchunk, g2_sm_count(plan.dev), /*allow_no_output=*/dst_ptr != 0);
+  } catch (...) {
+    g_wide_mode = saved_mode;
+    throw;
+  }
+  g_wide_mode = saved_mode;
   if (dst_ptr != 0) {
     TORCH_CHECK((dst_ptr & 15) == 0, "destination must be 16-byte aligned");
     P.C = reinterpret_cast<float*>(dst_ptr);
@@ -247,8 +360,8 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
     P.ldc = static_cast<int>(ldc);
     TORCH_CHECK(P.ldc >= P.N, "ldc is smaller than the number of columns");
   }
-  if (atomic) P.flags |= GF_ATOMIC;
-  TORCH_CHECK(static_cast<int>(extra_ptrs.size()) <= G_MAX_EXTRA, "too many extra destinations");
+  if (atomic) P.flags |= G2F_ATOMIC;
+  TORCH_CHECK(static_cast<int>(extra_ptrs.size()) <= G2_MAX_EXTRA, "too many extra destinations");
   TORCH_CHECK(!(atomic && !extra_ptrs.empty()), "extra destinations are not supported in atomic mode");
   P.n_extra = static_cast<int>(extra_ptrs.size());
   for (int e = 0; e < P.n_extra; ++e) P.C_extra[e] = reinterpret_cast<float*>(extra_ptrs[e]);
@@ -257,6 +370,7 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
   keep.insert(keep.end(), b_segs.begin(), b_segs.end());
   if (C.has_value()) keep.push_back(*C);
   if (out_hi.has_value()) keep.push_back(*out_hi);
+  if (out_mid.has_value()) keep.push_back(*out_mid);
   if (out_lo.has_value()) keep.push_back(*out_lo);
   plan.keep_alive.push_back(std::move(keep));
 }
@@ -271,41 +385,52 @@ void gemm_plan_finalize(int64_t id) {
   // scratch for split-K problems (private to the plan)
   size_t scratch_floats = 0;
   for (auto& P : plan.problems)
-    if (P.nsplit > 1 && !(P.flags & GF_ATOMIC))
-      scratch_floats += static_cast<size_t>(P.ntiles) * P.nsplit * G_BM * G_BN;
+    if (needs_ws(P)) scratch_floats += static_cast<size_t>(P.ntiles) * P.nsplit * G2_BM * 128;
   auto f32 = at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, plan.dev);
   if (scratch_floats > 0) plan.scratch = at::empty({static_cast<int64_t>(scratch_floats)}, f32);
   size_t off = 0;
-  struct Item { int problem, tm, tn, split; long long cost; };
+  struct Item {
+    GemmWork2 w;
+    long long cost;
+  };
   std::vector<Item> items, ritems;
   for (size_t pi = 0; pi < plan.problems.size(); ++pi) {
-    GemmProblem& P = plan.problems[pi];
+    GemmProblem2& P = plan.problems[pi];
     P.status = st.status.data_ptr<int>();
-    const bool split = P.nsplit > 1 && !(P.flags & GF_ATOMIC);
+    const bool split = needs_ws(P);
     if (split) {
       P.ws = plan.scratch.data_ptr<float>() + off;
-      off += static_cast<size_t>(P.ntiles) * P.nsplit * G_BM * G_BN;
+      off += static_cast<size_t>(P.ntiles) * P.nsplit * G2_BM * 128;
     }
-    const long long cost = static_cast<long long>(P.nseg) * ((P.K + G_BK - 1) / G_BK) / P.nsplit + 2;
+    const int kb_total = (P.K + G2_BK - 1) / G2_BK;
+    int tile = 0;
     for (int tm = 0; tm < P.tiles_m; ++tm)
-      for (int tn = 0; tn < ((P.flags & GF_SYM) ? tm + 1 : P.tiles_n); ++tn) {
-        for (int s = 0; s < P.nsplit; ++s) items.push_back({static_cast<int>(pi), tm, tn, s, cost});
-        if (split) ritems.push_back({static_cast<int>(pi), tm, tn, 0, 0});
+      for (int tn = 0; tn < ((P.flags & G2F_SYM) ? tm + 1 : P.tiles_n); ++tn, ++tile) {
+        for (int s = 0; s < P.nsplit; ++s) {
+          const int kb0 = static_cast<int>((static_cast<long long>(s) * kb_total) / P.nsplit);
+          const int kb1 = static_cast<int>((static_cast<long long>(s + 1) * kb_total) / P.nsplit);
+          GemmWork2 w;
+          std::memset(&w, 0, sizeof(w));
+          w.problem = static_cast<int>(pi);
+          w.a_mn = w.c_row = tm * G2_BM;
+          w.b_mn = w.c_col = tn * 128;
+          w.a_k0 = w.b_k0 = kb0 * G2_BK;
+          w.nkb = kb1 - kb0;
+          w.tile_id = tile;
+          w.split = s;
+          items.push_back({w, static_cast<long long>(P.nseg) * w.nkb + 2});
+          if (split && s == 0) ritems.push_back({w, 0});
+        }
       }
   }
-  // longest tiles first: the tail of the launch is then made of short tiles
+  // longest tiles first: with CTAs taking items round-robin the tail is made of short tiles
   std::stable_sort(items.begin(), items.end(), [](const Item& a, const Item& b) { return a.cost > b.cost; });
   auto upload_work = [&](const std::vector<Item>& v) {
-    std::vector<int> flat;
-    flat.reserve(v.size() * 4);
-    for (auto& w : v) {
-      flat.push_back(w.problem);
-      flat.push_back(w.tm);
-      flat.push_back(w.tn);
-      flat.push_back(w.split);
-    }
-    at::Tensor host = at::from_blob(flat.data(), {static_cast<int64_t>(flat.size())},
-                                    at::TensorOptions().dtype(at::kInt)).clone();
+    std::vector<GemmWork2> flat;
+    flat.reserve(v.size());
+    for (auto& w : v) flat.push_back(w.w);
+    at::Tensor host = at::from_blob(flat.data(), {static_cast<int64_t>(flat.size() * sizeof(GemmWork2))},
+                                    at::TensorOptions().dtype(at::kByte)).clone();
     return host.to(at::Device(at::kCUDA, plan.dev));
   };
   plan.n_work = static_cast<int>(items.size());
@@ -313,7 +438,7 @@ void gemm_plan_finalize(int64_t id) {
   plan.d_work = upload_work(items);
   if (plan.n_rwork > 0) plan.d_rwork = upload_work(ritems);
   at::Tensor host = at::from_blob(plan.problems.data(),
-                                  {static_cast<int64_t>(plan.problems.size() * sizeof(GemmProblem))},
+                                  {static_cast<int64_t>(plan.problems.size() * sizeof(GemmProblem2))},
                                   at::TensorOptions().dtype(at::kByte)).clone();
   plan.d_problems = host.to(at::Device(at::kCUDA, plan.dev));
   TORCH_CHECK((reinterpret_cast<uintptr_t>(plan.d_problems.data_ptr()) & 63) == 0,
@@ -327,22 +452,18 @@ void gemm_plan_run(int64_t id) {
   GemmPlan& plan = it->second;
   c10::cuda::CUDAGuard guard(plan.dev);
   auto stream = at::cuda::getCurrentCUDAStream(plan.dev).stream();
-  if (!g_attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(umma_gemm_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM_BYTES));
-    g_attr_set = true;
-  }
-  const GemmProblem* probs = reinterpret_cast<const GemmProblem*>(plan.d_problems.data_ptr());
-  umma_gemm_kernel<<<plan.n_work, G_THREADS, G_SMEM_BYTES, stream>>>(
-      plan.problems[0], probs, reinterpret_cast<const GemmWork*>(plan.d_work.data_ptr<int>()));
-  B200_CUDA_CHECK(cudaGetLastError());
-  count_launch();
-  if (plan.n_rwork > 0) {
-    splitk_reduce_kernel<<<dim3(plan.n_rwork, 16, 1), 256, 0, stream>>>(
-        plan.problems[0], probs, reinterpret_cast<const GemmWork*>(plan.d_rwork.data_ptr<int>()));
-    B200_CUDA_CHECK(cudaGetLastError());
-    count_launch();
-  }
+  const GemmProblem2* probs = reinterpret_cast<const GemmProblem2*>(plan.d_problems.data_ptr());
+  g2_launch_list(probs, reinterpret_cast<const GemmWork2*>(plan.d_work.data_ptr()), plan.n_work, false,
+                 plan.dev, stream);
+  if (plan.n_rwork > 0)
+    g2_launch_reduce_list(probs, reinterpret_cast<const GemmWork2*>(plan.d_rwork.data_ptr()), plan.n_rwork,
+                          false, stream);
+}
+
+// 0: 128-wide tiles only; 1: 256-wide tiles for outputs of at least 1024 x 1024; 2: wherever legal.
+void set_gemm_wide(int64_t mode) {
+  TORCH_CHECK(mode >= 0 && mode <= 2, "mode must be 0, 1 or 2");
+  g_wide_mode = static_cast<int>(mode);
 }
 
 // Reads and clears the device status word (synchronises the current stream).

@@ -1,0 +1,671 @@
+// Persistent tcgen05 "TN" GEMM / SYRK for sm_100a (second generation of umma_gemm.cuh).
+//
+//   C[M x N] (fp32)  =  alpha * sum_seg  op(A_seg)^T-contract-K  op(B_seg)   (+ beta * Cin)
+//
+// Operands are bf16 matrices contracted over K, each either MN-major ([K, M] row-major, the layout
+// of activations, so that X^T Y needs no transpose copy) or K-major ([M, K] row-major).  Up to six
+// (A_seg, B_seg) pairs accumulate into one result: with three-way splits v = hi + mid + lo the six
+// significant part products reproduce an fp32 product on the bf16 tensor cores.
+//
+// What is new against the first generation:
+//   * persistent CTAs (one per SM) walk a list of work items - tiles of one problem or of a whole
+//     plan of problems - so a grouped launch pays one prologue per SM, not one per tile;
+//   * two TMEM accumulators: the MMA warp fills one while the eight epilogue warps drain the other,
+//     so stores (including stores into other GPUs' memory) overlap the next tile's main loop;
+//   * "chunked K": a problem may ask for the contraction to be cut into chunks of `kchunk` 64-wide
+//     K blocks.  Each chunk is accumulated in TMEM, read back and added to a running fp32 sum in
+//     registers with round-to-nearest adds.  The tensor core truncates when it adds into its
+//     accumulator, which biases long sums; short chunks bound that bias to a few 2^-24, and the
+//     segments are issued small-magnitude-first inside a chunk for the same reason;
+//   * a work item carries its own operand origins and K range, so triangular operands (Cholesky
+//     panels, triangular inverses) skip their zero blocks and sub-matrices of one tensor map serve
+//     as operands;
+//   * three-way bf16 split outputs (hi / mid / lo) straight from the epilogue.
+//
+// Roles inside a CTA of 320 threads:
+//   warp 0       TMA producer (cp.async.bulk.tensor, 128B swizzle, STAGES-deep ring)
+//   warp 1       TMEM allocator + single-thread tcgen05.mma issuer
+//   warps 2..9   epilogue: tcgen05.ld -> registers -> global; warp w reads TMEM lanes
+//                32*(w%4)..+31 (a hardware rule) and one half of the tile's columns.
+// Every wait is bounded in wall time; on expiry the status word is set and the CTA unwinds.
+// TMA loads only ever read this GPU's memory; peer memory is written with per-thread stores.
+#pragma once
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+constexpr int G2_BM = 128;
+constexpr int G2_BK = 64;
+constexpr int G2_THREADS = 320;
+constexpr int G2_MAX_SEG = 6;
+constexpr int G2_MAX_EXTRA = 7;
+constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;  // 16 KiB
+
+template <int BN>
+struct G2Cfg {
+  static constexpr int STAGES = (BN == 128) ? 6 : 4;
+  static constexpr int B_BYTES = BN * G2_BK * 2;
+  static constexpr int STAGE_BYTES = G2_A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+enum : int {
+  G2F_SYM = 1,        // symmetric output: tiles on or below the diagonal only, mirrored
+  G2F_A_KMAJOR = 2,   // A given as [M, K] row-major
+  G2F_B_KMAJOR = 4,   // B given as [N, K] row-major
+  G2F_SAME_AB = 8,    // A and B are the same matrix (diagonal tiles load once; BN = 128 only)
+  G2F_ATOMIC = 16,    // C += alpha * result with reductions (C may live on another GPU); beta unused
+  G2F_LOWER = 32,     // with G2F_SYM: write / add the lower triangle only
+  G2F_WIDE = 64,      // the problem's tensor maps and tile grid are laid out for BN = 256
+};
+
+enum : int {
+  G2W_NO_SPLIT_OUT = 1,  // work item: do not write the bf16 outputs of the problem for this tile
+};
+
+struct alignas(64) GemmProblem2 {
+  CUtensorMap tmA[G2_MAX_SEG];
+  CUtensorMap tmB[G2_MAX_SEG];
+  float* C;               // may be null when only bf16 outputs are wanted
+  const float* Cin;       // read when beta != 0 (may alias C)
+  __nv_bfloat16* out_hi;  // optional bf16 image of the result
+  __nv_bfloat16* out_mid; // optional second part of a three-way split (needs out_hi and out_lo)
+  __nv_bfloat16* out_lo;  // optional residual
+  float* ws;              // split-K scratch: [tile][split][128][BN] fp32
+  int* status;            // device error word
+  float* C_extra[G2_MAX_EXTRA];  // plain copies of the fp32 result (same ldc), e.g. peer GPUs
+  int n_extra;
+  int M, N, K;
+  int ldc, ld_out;
+  int nseg;
+  int tiles_m, tiles_n, ntiles, nsplit;
+  int flags;
+  int kchunk;             // K blocks per accumulation chunk; 0 = the whole contraction in TMEM
+  float alpha, beta;
+};
+
+struct GemmWork2 {
+  int problem;
+  int a_mn, b_mn;   // first M / N element of the operand tiles
+  int a_k0, b_k0;   // first K element of the operand tiles
+  int nkb;          // number of 64-wide K blocks
+  int c_row, c_col; // output origin
+  int tile_id;      // index of the tile inside the problem's split-K scratch
+  int split;        // split-K slice
+  int wflags;
+  int pad;
+};
+
+// number of column tiles scheduled in tile row tm
+template <int BN>
+__device__ __forceinline__ int g2_tiles_in_row(const GemmProblem2& P, int tm) {
+  return (P.flags & G2F_SYM) ? (tm * G2_BM) / BN + 1 : P.tiles_n;
+}
+
+// Work item `idx` of a single-problem launch: idx = tile * nsplit + split.
+template <int BN>
+__device__ __forceinline__ GemmWork2 g2_decode(const GemmProblem2& P, int idx) {
+  GemmWork2 w;
+  const int t = idx / P.nsplit;
+  w.split = idx - t * P.nsplit;
+  int tm = 0, rem = t;
+  while (true) {
+    const int cnt = g2_tiles_in_row<BN>(P, tm);
+    if (rem < cnt) break;
+    rem -= cnt;
+    ++tm;
+  }
+  const int kb_total = (P.K + G2_BK - 1) / G2_BK;
+  const int kb0 = static_cast<int>((static_cast<long long>(w.split) * kb_total) / P.nsplit);
+  const int kb1 = static_cast<int>((static_cast<long long>(w.split + 1) * kb_total) / P.nsplit);
+  w.problem = 0;
+  w.a_mn = tm * G2_BM;
+  w.b_mn = rem * BN;
+  w.a_k0 = w.b_k0 = kb0 * G2_BK;
+  w.nkb = kb1 - kb0;
+  w.c_row = w.a_mn;
+  w.c_col = w.b_mn;
+  w.tile_id = t;
+  w.wflags = 0;
+  w.pad = 0;
+  return w;
+}
+
+__device__ __forceinline__ void g2_red_add_f32(float* p, float v) {
+  asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void g2_red_add_v4_f32(float* p, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b),
+               "f"(c), "f"(d)
+               : "memory");
+}
+
+// 16-byte accesses need a 16-byte aligned row start: ldc a multiple of 4 and an aligned base
+__device__ __forceinline__ bool g2_vec_ok(const float* base, int ldc) {
+  return ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(base) & 15) == 0);
+}
+
+// Accumulating variant of the final store (G2F_ATOMIC): every element is added to C with a
+// reduction instruction, so that several CTAs / GPUs can contribute to the same matrix.
+__device__ __forceinline__ void g2_reduce_chunk(const GemmProblem2& P, const float* v, int gr, int gc0,
+                                                bool diag_tile) {
+  if (gr >= P.M) return;
+  const bool sym = (P.flags & G2F_SYM) != 0;
+  const float alpha = P.alpha;
+  float* c = P.C + static_cast<size_t>(gr) * P.ldc + gc0;
+  const bool vec_ok = (gc0 + 32 <= P.N) && g2_vec_ok(P.C, P.ldc) && !(sym && diag_tile);
+  if (vec_ok) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      g2_red_add_v4_f32(c + 4 * j, alpha * v[4 * j], alpha * v[4 * j + 1], alpha * v[4 * j + 2],
+                        alpha * v[4 * j + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int gc = gc0 + j;
+      if (gc < P.N && !(sym && diag_tile && gc > gr)) g2_red_add_f32(c + j, alpha * v[j]);
+    }
+  }
+  if (sym && !(P.flags & G2F_LOWER)) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int gc = gc0 + j;
+      if (gc < P.N && (!diag_tile || gc < gr))
+        g2_red_add_f32(P.C + static_cast<size_t>(gc) * P.ldc + gr, alpha * v[j]);
+    }
+  }
+}
+
+// Final store of 32 consecutive columns of one row held by this thread.
+__device__ __forceinline__ void g2_store_chunk(const GemmProblem2& P, const float* v, int gr, int gc0,
+                                               bool diag_tile, bool split_out) {
+  if (gr >= P.M) return;
+  const bool sym = (P.flags & G2F_SYM) != 0;
+  const float alpha = P.alpha, beta = P.beta;
+  float out[32];
+  const bool full = (gc0 + 32 <= P.N);
+  const bool vec_ok = full && g2_vec_ok(P.C != nullptr ? P.C : P.Cin, P.ldc);
+  if (beta != 0.f) {
+    const float* cin = P.Cin + static_cast<size_t>(gr) * P.ldc + gc0;
+    if (vec_ok && g2_vec_ok(P.Cin, P.ldc)) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 c4 = *reinterpret_cast<const float4*>(cin + 4 * j);
+        out[4 * j + 0] = alpha * v[4 * j + 0] + beta * c4.x;
+        out[4 * j + 1] = alpha * v[4 * j + 1] + beta * c4.y;
+        out[4 * j + 2] = alpha * v[4 * j + 2] + beta * c4.z;
+        out[4 * j + 3] = alpha * v[4 * j + 3] + beta * c4.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) out[j] = (gc0 + j < P.N) ? alpha * v[j] + beta * cin[j] : 0.f;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) out[j] = alpha * v[j];
+  }
+  if (P.C != nullptr) {
+    float* c = P.C + static_cast<size_t>(gr) * P.ldc + gc0;
+    if (!sym || !diag_tile) {
+      if (vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<float4*>(c + 4 * j) =
+              make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (gc0 + j < P.N) c[j] = out[j];
+      }
+      if (sym && !(P.flags & G2F_LOWER)) {  // strictly-lower tile: mirrored (transposed) store
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (gc0 + j < P.N) P.C[static_cast<size_t>(gc0 + j) * P.ldc + gr] = out[j];
+      }
+    } else {
+      // diagonal tile: keep the lower triangle, mirror it so the result is exactly symmetric
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int gc = gc0 + j;
+        if (gc <= gr && gc < P.N) {
+          c[j] = out[j];
+          if (gc < gr && !(P.flags & G2F_LOWER)) P.C[static_cast<size_t>(gc) * P.ldc + gr] = out[j];
+        }
+      }
+    }
+  }
+  for (int e = 0; e < P.n_extra; ++e) {  // plain (non-symmetric) result replicated to peers
+    float* c = P.C_extra[e] + static_cast<size_t>(gr) * P.ldc + gc0;
+    if (full && g2_vec_ok(P.C_extra[e], P.ldc)) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float4*>(c + 4 * j) =
+            make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (gc0 + j < P.N) c[j] = out[j];
+    }
+  }
+  if (P.out_hi != nullptr && split_out) {
+    const size_t o = static_cast<size_t>(gr) * P.ld_out + gc0;
+    // a symmetric problem's bf16 images are consumed as full matrices: write the mirror image too
+    const bool mirror = sym && !(P.flags & G2F_LOWER);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int gc = gc0 + j;
+      if (gc >= P.N || (sym && diag_tile && gc > gr)) continue;
+      const float x = out[j];
+      const __nv_bfloat16 h = __float2bfloat16_rn(x);
+      P.out_hi[o + j] = h;
+      const size_t om = static_cast<size_t>(gc) * P.ld_out + gr;
+      if (mirror && gc != gr) P.out_hi[om] = h;
+      if (P.out_lo != nullptr) {
+        const float r1 = x - __bfloat162float(h);
+        if (P.out_mid != nullptr) {
+          const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+          const __nv_bfloat16 l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+          P.out_mid[o + j] = m;
+          P.out_lo[o + j] = l;
+          if (mirror && gc != gr) {
+            P.out_mid[om] = m;
+            P.out_lo[om] = l;
+          }
+        } else {
+          const __nv_bfloat16 l = __float2bfloat16_rn(r1);
+          P.out_lo[o + j] = l;
+          if (mirror && gc != gr) P.out_lo[om] = l;
+        }
+      }
+    }
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(G2_THREADS, 1)
+umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem2* __restrict__ probs,
+                  const GemmWork2* __restrict__ work, int n_work) {
+  using Cfg = G2Cfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment is required by the 128B swizzle atoms.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int wi = blockIdx.x; wi < n_work && ok; wi += gridDim.x) {
+        const GemmWork2 w = (work != nullptr) ? work[wi] : g2_decode<BN>(single, wi);
+        const GemmProblem2& P = (work != nullptr) ? probs[w.problem] : single;
+        const bool a_k = (P.flags & G2F_A_KMAJOR) != 0;
+        const bool b_k = (P.flags & G2F_B_KMAJOR) != 0;
+        const bool shared_ab = BN == 128 && (P.flags & G2F_SAME_AB) && w.a_mn == w.b_mn && w.a_k0 == w.b_k0;
+        const uint32_t bytes = shared_ab ? G2_A_BYTES : Cfg::STAGE_BYTES;
+        const int kchunk = P.kchunk > 0 ? P.kchunk : (w.nkb > 0 ? w.nkb : 1);
+        for (int c0 = 0; c0 < w.nkb && ok; c0 += kchunk) {
+          const int c1 = (c0 + kchunk < w.nkb) ? c0 + kchunk : w.nkb;
+          for (int seg = 0; seg < P.nseg && ok; ++seg) {
+            for (int kb = c0; kb < c1; ++kb, ++it) {
+              const int s = it % STAGES;
+              const uint32_t ph = (it / STAGES) & 1;
+              if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+                set_error(P.status, ERR_WAIT_EMPTY);
+                ok = false;
+                break;
+              }
+              uint8_t* sA = smem + s * Cfg::STAGE_BYTES;
+              uint8_t* sB = sA + G2_A_BYTES;
+              mbar_expect_tx(&full_bar[s], bytes);
+              const int ka = w.a_k0 + kb * G2_BK, kbb = w.b_k0 + kb * G2_BK;
+              if (a_k) {
+                tma_load_2d(sA, &P.tmA[seg], &full_bar[s], ka, w.a_mn);
+              } else {
+                tma_load_2d(sA, &P.tmA[seg], &full_bar[s], w.a_mn, ka);
+                tma_load_2d(sA + G2_BK * 128, &P.tmA[seg], &full_bar[s], w.a_mn + 64, ka);
+              }
+              if (!shared_ab) {
+                if (b_k) {
+                  tma_load_2d(sB, &P.tmB[seg], &full_bar[s], kbb, w.b_mn);
+                } else {
+#pragma unroll
+                  for (int h = 0; h < BN / 64; ++h)
+                    tma_load_2d(sB + h * G2_BK * 128, &P.tmB[seg], &full_bar[s], w.b_mn + 64 * h, kbb);
+                }
+              }
+            }
+          }
+        }
+      }
+      if (!ok) {
+        // give copies that are still in flight a bounded chance to land before teardown
+        const uint32_t pending = it < static_cast<uint32_t>(STAGES) ? it : static_cast<uint32_t>(STAGES);
+        for (uint32_t j = 0; j < pending; ++j) {
+          const uint32_t jt = it - 1 - j;
+          mbar_wait(&full_bar[jt % STAGES], (jt / STAGES) & 1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0, ch = 0;
+      bool ok = true;
+      for (int wi = blockIdx.x; wi < n_work && ok; wi += gridDim.x) {
+        const GemmWork2 w = (work != nullptr) ? work[wi] : g2_decode<BN>(single, wi);
+        const GemmProblem2& P = (work != nullptr) ? probs[w.problem] : single;
+        const bool a_k = (P.flags & G2F_A_KMAJOR) != 0;
+        const bool b_k = (P.flags & G2F_B_KMAJOR) != 0;
+        const bool shared_ab = BN == 128 && (P.flags & G2F_SAME_AB) && w.a_mn == w.b_mn && w.a_k0 == w.b_k0;
+        const uint32_t idesc = make_idesc_bf16(G2_BM, BN, !a_k, !b_k);
+        const int kchunk = P.kchunk > 0 ? P.kchunk : (w.nkb > 0 ? w.nkb : 1);
+        for (int c0 = 0; c0 < w.nkb && ok; c0 += kchunk, ++ch) {
+          const int c1 = (c0 + kchunk < w.nkb) ? c0 + kchunk : w.nkb;
+          const uint32_t ab = ch & 1;
+          if (!mbar_wait(&acc_empty[ab], ((ch >> 1) & 1) ^ 1)) {
+            set_error(P.status, ERR_WAIT_ACC);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t tacc = tmem_base + ab * BN;
+          uint32_t first = 1;
+          for (int seg = 0; seg < P.nseg && ok; ++seg) {
+            for (int kb = c0; kb < c1; ++kb, ++it) {
+              const int s = it % STAGES;
+              const uint32_t ph = (it / STAGES) & 1;
+              if (!mbar_wait(&full_bar[s], ph)) {
+                set_error(P.status, ERR_WAIT_FULL);
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+              const uint32_t aA = smem_u32(smem + s * Cfg::STAGE_BYTES);
+              const uint32_t aB = shared_ab ? aA : aA + G2_A_BYTES;
+#pragma unroll
+              for (int k = 0; k < G2_BK / 16; ++k) {
+                // MN-major: 16 K-rows of 128 B each per MMA; K-major: 16 K-elements = 32 B per MMA.
+                const uint64_t da = a_k ? make_smem_desc_sw128(aA + k * 32, 16, 1024)
+                                        : make_smem_desc_sw128(aA + k * 16 * 128, G2_BK * 128, 1024);
+                const uint64_t db = b_k ? make_smem_desc_sw128(aB + k * 32, 16, 1024)
+                                        : make_smem_desc_sw128(aB + k * 16 * 128, G2_BK * 128, 1024);
+                umma_bf16(tacc, da, db, idesc, first ? 0u : 1u);
+                first = 0;
+              }
+              umma_commit(&empty_bar[s]);
+            }
+          }
+          if (ok) umma_commit(&acc_full[ab]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------------
+    const int q = warp & 3;             // TMEM lane quarter this warp may access
+    const int half = (warp - 2) >> 2;   // which half of the tile's columns
+    constexpr int COLS = BN / 2;        // columns per warp
+    constexpr int PASSES = COLS / 64;
+    const int row = q * 32 + lane;
+    uint32_t ch = 0;
+    bool ok = true;
+    for (int wi = blockIdx.x; wi < n_work && ok; wi += gridDim.x) {
+      const GemmWork2 w = (work != nullptr) ? work[wi] : g2_decode<BN>(single, wi);
+      const GemmProblem2& P = (work != nullptr) ? probs[w.problem] : single;
+      const int kchunk = P.kchunk > 0 ? P.kchunk : (w.nkb > 0 ? w.nkb : 1);
+      const int nchunks = (w.nkb + kchunk - 1) / kchunk;
+      const int gr = w.c_row + row;
+      const bool sym = (P.flags & G2F_SYM) != 0;
+      const bool atomic = (P.flags & G2F_ATOMIC) != 0;
+      const bool to_ws = P.nsplit > 1 && !atomic;
+      const bool split_out = !(w.wflags & G2W_NO_SPLIT_OUT);
+      const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+
+      auto finish = [&](const float* v, int col0) {
+        // v: 64 consecutive columns of this thread's row starting at tile column col0
+        if (to_ws) {
+          float* part = P.ws + (static_cast<size_t>(w.tile_id) * P.nsplit + w.split) * (G2_BM * BN) +
+                        static_cast<size_t>(row) * BN + col0;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            *reinterpret_cast<float4*>(part + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          return;
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int gc0 = w.c_col + col0 + c * 32;
+          // with wide tiles a symmetric problem's tile may reach past the diagonal block: skip that part
+          const bool beyond = sym && (gc0 / G2_BM) > (w.c_row / G2_BM);
+          const bool diag = sym && (gc0 / G2_BM) == (w.c_row / G2_BM);
+          if (gc0 < P.N && !beyond && !(diag && gc0 > gr)) {
+            if (atomic)
+              g2_reduce_chunk(P, v + c * 32, gr, gc0, diag);
+            else
+              g2_store_chunk(P, v + c * 32, gr, gc0, diag, split_out);
+          }
+        }
+      };
+
+      if (nchunks <= 1) {
+        const uint32_t ab = ch & 1;
+        if (nchunks == 1) {
+          ok = mbar_wait(&acc_full[ab], (ch >> 1) & 1);
+          if (!ok) set_error(P.status, ERR_WAIT_ACC);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+        }
+#pragma unroll
+        for (int pass = 0; pass < PASSES; ++pass) {
+          float v[64];
+          const int col0 = half * COLS + pass * 64;
+          if (nchunks == 1) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(tmem_base + lane_addr + ab * BN + col0, r0);
+            tmem_ld_32x32(tmem_base + lane_addr + ab * BN + col0 + 32, r1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              v[j] = __uint_as_float(r0[j]);
+              v[32 + j] = __uint_as_float(r1[j]);
+            }
+            if (pass == PASSES - 1) {  // everything this warp needs is in registers: free the accumulator
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[ab]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = 0.f;
+          }
+          finish(v, col0);
+        }
+        if (nchunks == 1) ++ch;
+      } else if (PASSES != 1) {
+        set_error(P.status, ERR_BAD_ARG);  // chunked contraction needs 128-wide tiles (refused on the host)
+        ok = false;
+        break;
+      } else {
+        // chunked contraction: running fp32 sum in registers
+        float run[64];
+        const int col0 = half * COLS;
+        for (int c = 0; c < nchunks; ++c, ++ch) {
+          const uint32_t ab = ch & 1;
+          ok = mbar_wait(&acc_full[ab], (ch >> 1) & 1);
+          if (!ok) set_error(P.status, ERR_WAIT_ACC);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(tmem_base + lane_addr + ab * BN + col0, r0);
+          tmem_ld_32x32(tmem_base + lane_addr + ab * BN + col0 + 32, r1);
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[ab]);
+          if (c == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              run[j] = __uint_as_float(r0[j]);
+              run[32 + j] = __uint_as_float(r1[j]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              run[j] += __uint_as_float(r0[j]);
+              run[32 + j] += __uint_as_float(r1[j]);
+            }
+          }
+        }
+        if (!ok) break;
+        finish(run, col0);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// Sums split-K partials and applies the epilogue.  One block handles a 32x32 patch of one tile:
+// reads and direct stores are 128-byte coalesced, the mirrored store goes through shared memory.
+// grid: (work items, 4 * BN / 32).
+template <int BN>
+__global__ void __launch_bounds__(256)
+splitk_reduce2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem2* __restrict__ probs,
+                      const GemmWork2* __restrict__ work) {
+  __shared__ float tile[32][33];
+  GemmWork2 w;
+  const GemmProblem2* Pp;
+  if (work != nullptr) {
+    w = work[blockIdx.x];
+    Pp = probs + w.problem;
+  } else {
+    w = g2_decode<BN>(single, blockIdx.x * single.nsplit);
+    Pp = &single;
+  }
+  const GemmProblem2& P = *Pp;
+  const bool sym = (P.flags & G2F_SYM) != 0;
+  constexpr int PC = BN / 32;  // patches per tile row
+  const int sub_r = blockIdx.y / PC, sub_c = blockIdx.y % PC;
+  const int tm = w.c_row / G2_BM;
+  const int cb = (w.c_col + sub_c * 32) / G2_BM;  // 128-wide column block of this patch
+  if (sym && cb > tm) return;
+  const bool diag_tile = sym && cb == tm;
+  if (diag_tile && (w.c_col + sub_c * 32) > (w.c_row + sub_r * 32)) return;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  // patches that lie completely outside the matrix (edge tiles of small problems) have no work
+  if (w.c_row + sub_r * 32 >= P.M || w.c_col + sub_c * 32 >= P.N) return;
+  const float* base = P.ws + static_cast<size_t>(w.tile_id) * P.nsplit * (G2_BM * BN);
+  const int gc = w.c_col + sub_c * 32 + tx;
+  // sum the partials in split order; the loads of the four rows of a thread and of four splits are
+  // issued together (16 independent loads in flight per thread)
+  float accs[4] = {0.f, 0.f, 0.f, 0.f};
+  {
+    const float* p0 = base + static_cast<size_t>(sub_r * 32 + ty) * BN + sub_c * 32 + tx;
+    int s = 0;
+    for (; s + 4 <= P.nsplit; s += 4) {
+      float v[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          v[i][u] = __ldcg(p0 + static_cast<size_t>(8 * i) * BN + static_cast<size_t>(s + u) * (G2_BM * BN));
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) accs[i] += v[i][u];
+    }
+    for (; s < P.nsplit; ++s)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        accs[i] += __ldcg(p0 + static_cast<size_t>(8 * i) * BN + static_cast<size_t>(s) * (G2_BM * BN));
+  }
+  const bool mirror_bf16 = sym && !(P.flags & G2F_LOWER);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int lr = ty + 8 * i;
+    const int gr = w.c_row + sub_r * 32 + lr;
+    float val = P.alpha * accs[i];
+    const bool inb = gr < P.M && gc < P.N;
+    if (inb && P.beta != 0.f) val += P.beta * P.Cin[static_cast<size_t>(gr) * P.ldc + gc];
+    tile[lr][tx] = val;
+    const bool keep = inb && !(diag_tile && gc > gr);
+    if (keep) {
+      if (P.C != nullptr) P.C[static_cast<size_t>(gr) * P.ldc + gc] = val;
+      for (int e = 0; e < P.n_extra; ++e) P.C_extra[e][static_cast<size_t>(gr) * P.ldc + gc] = val;
+      if (P.out_hi != nullptr) {
+        const size_t o = static_cast<size_t>(gr) * P.ld_out + gc;
+        const size_t om = static_cast<size_t>(gc) * P.ld_out + gr;
+        const bool mir = mirror_bf16 && gc != gr;
+        const __nv_bfloat16 h = __float2bfloat16_rn(val);
+        P.out_hi[o] = h;
+        if (mir) P.out_hi[om] = h;
+        if (P.out_lo != nullptr) {
+          const float r1 = val - __bfloat162float(h);
+          if (P.out_mid != nullptr) {
+            const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+            const __nv_bfloat16 l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+            P.out_mid[o] = m;
+            P.out_lo[o] = l;
+            if (mir) {
+              P.out_mid[om] = m;
+              P.out_lo[om] = l;
+            }
+          } else {
+            const __nv_bfloat16 l = __float2bfloat16_rn(r1);
+            P.out_lo[o] = l;
+            if (mir) P.out_lo[om] = l;
+          }
+        }
+      }
+    }
+  }
+  if (!sym || P.C == nullptr || (P.flags & G2F_LOWER)) return;
+  __syncthreads();
+  // mirrored store: element (r, c) of the patch goes to C[c][r]
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int lc = ty + 8 * i;                       // patch column -> destination row
+    const int dst_r = w.c_col + sub_c * 32 + lc;     // global column index of the source
+    const int dst_c = w.c_row + sub_r * 32 + tx;     // global row index of the source
+    if (dst_r < P.N && dst_c < P.M && dst_r < dst_c)
+      P.C[static_cast<size_t>(dst_r) * P.ldc + dst_c] = tile[tx][lc];
+  }
+}
+
+}  // namespace b200

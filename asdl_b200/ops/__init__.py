@@ -30,7 +30,7 @@ import torch
 
 from . import _build
 
-__all__ = ['gram', 'matmul_tn', 'kron_apply', 'conv_patch_gram', 'spd_inverse', 'spd_inverse_grouped', 'damped_cholesky',
+__all__ = ['gram', 'matmul_tn', 'split3', 'matmul_fp32_tc', 'kron_apply', 'conv_patch_gram', 'spd_inverse', 'spd_inverse_grouped', 'damped_cholesky',
            'unitwise_inverse', 'batchnorm_unitwise_stats', 'batchnorm_unitwise_stats_from_input',
            'batch_norm_train', 'layer_norm',
            'set_backend', 'get_backend', 'set_precision', 'get_precision', 'extension',
@@ -39,6 +39,18 @@ __all__ = ['gram', 'matmul_tn', 'kron_apply', 'conv_patch_gram', 'spd_inverse', 
 _backend = 'auto'      # 'auto' | 'torch'
 _precision = 'auto'    # 'auto' | 'bf16' | 'bf16x3'
 _ext = None
+
+#: which of the library's grouped SPD inverses runs on CUDA: ``'tensor_core'`` (128-wide panels, every
+#: O(n^3) product on the tcgen05 GEMM from three-way bf16 splits) or ``'cuda_core'`` (64-wide
+#: panels, fp32 FMA tile products)
+CHOLESKY_BACKEND = 'tensor_core'
+
+#: segment order of an fp32-grade product from three-way splits (hi, mid, lo): the six significant
+#: part products, small magnitudes first (the tensor core truncates when it adds into its accumulator)
+SPLIT3_ORDER_A = (2, 0, 1, 1, 0, 0)
+SPLIT3_ORDER_B = (0, 2, 1, 0, 1, 0)
+#: K blocks (of 64) per accumulation chunk of such a product
+SPLIT3_KCHUNK = 2
 
 
 def set_backend(name: str):
@@ -135,6 +147,32 @@ def _segments(a_hi, a_lo, b_hi, b_lo):
 def _f32(t: torch.Tensor) -> torch.Tensor:
     """Half-precision tensors as fp32 (the PyTorch paths accumulate and return fp32, like the kernels do)."""
     return t.float() if t.dtype in (torch.bfloat16, torch.float16) else t
+
+
+def split3(x: torch.Tensor):
+    """fp32 [rows, n] -> three bf16 parts (hi, mid, lo) with hi + mid + lo == x to 24 bits, as views
+    [rows, n] into storage whose row pitch is a multiple of 64 elements (CUDA only)."""
+    rows, n = x.shape
+    ld = _round_up(max(n, 8), 64)
+    parts = [torch.empty(rows, ld, device=x.device, dtype=torch.bfloat16) for _ in range(3)]
+    src = x if (x.stride(1) == 1 and x.dtype == torch.float32) else x.float().contiguous()
+    extension().cast_split3(src, *parts)
+    return [p[:, :n] for p in parts]
+
+
+def matmul_fp32_tc(a_parts, b_parts, a_kmajor: bool, b_kmajor: bool, out=None, alpha: float = 1.0, beta: float = 0.0,
+                   sym: bool = False, out_parts=None):
+    """fp32-grade product on the bf16 tensor cores from three-way splits of both operands
+    (``a_parts`` / ``b_parts``: the (hi, mid, lo) triples of :func:`split3`): six part products,
+    issued small-magnitude-first, the contraction accumulated in TMEM in chunks of 128 and summed
+    in fp32 registers.  ``out_parts``: optional (hi, mid, lo) bf16 buffers that receive the split
+    of the result from the epilogue."""
+    a_segs = [a_parts[i] for i in SPLIT3_ORDER_A]
+    b_segs = [b_parts[i] for i in SPLIT3_ORDER_B]
+    oh, om, ol = out_parts if out_parts is not None else (None, None, None)
+    extension().umma_gemm(a_segs, b_segs, a_kmajor, b_kmajor, out, float(alpha), float(beta), sym, oh, ol, 1,
+                          om, SPLIT3_KCHUNK)
+    return out
 
 
 def gram(x: torch.Tensor, scale: float = 1.0, out: Optional[torch.Tensor] = None,
@@ -300,7 +338,7 @@ def damped_cholesky(mat: torch.Tensor, damping) -> torch.Tensor:
 def spd_inverse(mat: torch.Tensor, damping=0.0) -> torch.Tensor:
     """``(mat + damping*I)^-1`` for symmetric positive (semi-)definite ``mat``; the input is left
     untouched.  ``damping`` may be a Python number or a 0-d / 1-element tensor (kept on the
-    device).  CUDA fp32: the library's grouped blocked Cholesky-inverse kernels."""
+    device).  CUDA fp32: the library's grouped blocked Cholesky-inverse kernels (``CHOLESKY_BACKEND``)."""
     if cuda_kernels_enabled(mat) and mat.dtype == torch.float32 and mat.ndim == 2:
         out = torch.empty(mat.shape, device=mat.device, dtype=torch.float32)
         spd_inverse_grouped([mat], [out], damping)
@@ -328,7 +366,10 @@ def spd_inverse_grouped(mats, outs, damping):
         damp = torch.full((count,), float(damping), device=dev, dtype=torch.float32)
     if cuda_kernels_enabled(*mats) and all(m.dtype == torch.float32 for m in mats):
         mats = [m if m.stride(-1) == 1 else m.contiguous() for m in mats]
-        extension().chol_inverse(list(mats), list(outs), damp)
+        if CHOLESKY_BACKEND == 'tensor_core':
+            extension().chol_inverse_tc(list(mats), list(outs), damp)
+        else:
+            extension().chol_inverse(list(mats), list(outs), damp)
         return outs
     for m, o, d in zip(mats, outs, damp):
         o.copy_(torch.cholesky_inverse(damped_cholesky(m, d)))

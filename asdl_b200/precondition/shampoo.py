@@ -36,7 +36,7 @@ __all__ = ['ShampooGradientMaker', 'Preconditioner', 'BlockPartitioner', 'Comput
 _invalid = -1
 
 #: Which batches of statistics take the grouped tensor-core chain for their inverse roots:
-#: 'auto' (well-damped ones: ridge >= 1e-4 of the largest eigenvalue), 'always', or 'never'
+#: 'auto' / 'always' (every fp32 CUDA batch of size >= 128 with a power-of-two exponent), or 'never'
 #: (batched fp32 matrix products of PyTorch).
 TENSOR_CORE_ROOTS = 'auto'
 
@@ -536,15 +536,20 @@ def _power_iteration_batched(mats, num_iters=100, error_tolerance=1e-6, check_ev
 class _NewtonChainCuda:
     """Coupled Newton iteration for a batch of equally sized matrices on the tensor cores.
 
-    Every product of an iteration (T^2, T^4, ..., T^p M and R T) runs as two grouped tcgen05
-    launches over the whole batch: the operands are split three ways into bf16 parts
-    (v = hi + mid + lo carries the full fp32 significand) and the six significant part products
-    hi*hi, hi*mid, mid*hi, hi*lo, mid*mid, lo*hi are accumulated in fp32, which reproduces an fp32
-    product to ~2^-24 - enough for ridges of 1e-6 times the largest eigenvalue.  All iterates are
-    polynomials in the (symmetric) input, hence symmetric, so the row-major buffers serve directly
-    as MN-major operands and nothing is transposed; the products run in the GEMM's symmetric mode
-    (lower tiles, mirrored), which keeps the iterates exactly symmetric at half the work.  Buffers and launch plans are cached per
-    (batch, size, p) because Shampoo calls this with the same shapes at every root update."""
+    Every product of an iteration (T^2, T^4, ..., T^p M and R T) runs as one grouped tcgen05 launch
+    over the whole batch: the operands are split three ways into bf16 parts (v = hi + mid + lo
+    carries the full fp32 significand) and the six significant part products are issued
+    small-magnitude-first; the contraction is accumulated in TMEM in chunks of K = 128 that the
+    epilogue warps add into an fp32 running sum in registers.  The tensor core truncates when it
+    adds into its accumulator, which biases a long sum by ~1e-6 of its largest term - more than a
+    ridge of 1e-6; the short chunks keep the bias at a few 2^-24, which reproduces an fp32 product
+    and lets the iteration converge at that ridge.  All iterates are polynomials in the (symmetric)
+    input, hence symmetric, so the row-major buffers serve directly as MN-major operands and nothing
+    is transposed; the products run in the GEMM's symmetric mode (lower tiles, mirrored), which keeps
+    the iterates exactly symmetric at half the work, and the epilogue writes the three-way split of
+    every intermediate power, so no separate splitting pass runs between the products.  Buffers and
+    launch plans are cached per (batch, size, p) because Shampoo calls this with the same shapes at
+    every root update."""
 
     _cache: Dict[Tuple[int, int, int, int], '_NewtonChainCuda'] = {}
 
@@ -558,56 +563,54 @@ class _NewtonChainCuda:
     @classmethod
     def clear_cache(cls):
         """Release the cached buffers and launch plans."""
+        for chain in cls._cache.values():
+            for plan in chain.plans:
+                chain.ext.gemm_plan_free(plan)
         cls._cache.clear()
 
     def __init__(self, b, n, p, device):
         ext = ops.extension()
         self.ext, self.b, self.n, self.p = ext, b, n, p
         self.squarings = p.bit_length() - 1
-        ld = (n + 7) // 8 * 8
+        ld = (n + 63) // 64 * 64
         self.ld = ld
         f32 = dict(device=device, dtype=torch.float32)
         bf16 = dict(device=device, dtype=torch.bfloat16)
         triple = lambda: tuple(torch.zeros(b, n, ld, **bf16) for _ in range(3))  # noqa: E731
         self.M, self.R, self.T = (torch.zeros(b, n, n, **f32) for _ in range(3))
         self.M_new, self.R_new = torch.zeros(b, n, n, **f32), torch.zeros(b, n, n, **f32)
-        self.P = [torch.zeros(b, n, n, **f32) for _ in range(self.squarings)]   # T^2, T^4, ... in fp32
         self.M_s, self.R_s, self.T_s = triple(), triple(), triple()
-        self.P_s = [triple() for _ in range(self.squarings)]
+        self.P_s = [triple() for _ in range(self.squarings)]   # splits of T^2, T^4, ...
         self.plans = []
 
-        def product(a, bb, out):
-            """Two plans: out = a1 b1 + a1 b2 + a2 b1, then out += a1 b3 + a2 b2 + a3 b1."""
-            first, second = ext.gemm_plan_new(), ext.gemm_plan_new()
+        def product(a, bb, out, out_split):
+            """One plan: out (fp32, may be None) and / or its three-way split = a . bb, fp32-grade."""
+            plan = ext.gemm_plan_new()
             for i in range(b):
-                a1, a2, a3 = (t[i][:, :n] for t in a)
-                b1, b2, b3 = (t[i][:, :n] for t in bb)
+                a_parts = [t[i][:, :n] for t in a]
+                b_parts = [t[i][:, :n] for t in bb]
+                a_segs = [a_parts[j] for j in ops.SPLIT3_ORDER_A]
+                b_segs = [b_parts[j] for j in ops.SPLIT3_ORDER_B]
+                oh, om, ol = (t[i] for t in out_split) if out_split is not None else (None, None, None)
                 # symmetric mode: lower-triangular tiles only, mirrored (half the work, and the iterates
                 # stay exactly symmetric, which the transposed operand reads rely on)
-                ext.gemm_plan_add(first, [a1, a1, a2], [b1, b2, b1], False, False, out[i], 1.0, 0.0, True,
-                                  None, None, 0, 0, False, [], 1)
-                ext.gemm_plan_add(second, [a1, a2, a3], [b3, b2, b1], False, False, out[i], 1.0, 1.0, True,
-                                  None, None, 0, 0, False, [], 1)
-            ext.gemm_plan_finalize(first)
-            ext.gemm_plan_finalize(second)
-            self.plans += [first, second]
-            return first, second
+                ext.gemm_plan_add(plan, a_segs, b_segs, False, False, out[i] if out is not None else None,
+                                  1.0, 0.0, True, oh, ol, 0, 0, False, [], 1, om, ops.SPLIT3_KCHUNK)
+            ext.gemm_plan_finalize(plan)
+            self.plans.append(plan)
+            return plan
 
         prev = self.T_s
         self.square_plans = []
         for k in range(self.squarings):
-            self.square_plans.append(product(prev, prev, self.P[k]))
+            self.square_plans.append(product(prev, prev, None, self.P_s[k]))
             prev = self.P_s[k]
-        self.plan_m = product(prev, self.M_s, self.M_new)
-        self.plan_r = product(self.R_s, self.T_s, self.R_new)
+        self.plan_m = product(prev, self.M_s, self.M_new, None)
+        self.plan_r = product(self.R_s, self.T_s, self.R_new, None)
 
     def _split(self, src, parts):
         rows = self.b * self.n
         self.ext.cast_split3(src.view(rows, self.n), *(t.view(rows, self.ld) for t in parts))
-
-    def _run(self, plans):
-        self.ext.gemm_plan_run(plans[0])
-        self.ext.gemm_plan_run(plans[1])
 
     def run(self, g, z, iter_count, error_tolerance, check_every=4):
         """g: [b, n, n] damped matrices, z: [b] scaling; returns (g)^{-1/p} as a new tensor."""
@@ -630,11 +633,10 @@ class _NewtonChainCuda:
             torch.mul(self.M, alpha, out=self.T)
             self.T.diagonal(dim1=1, dim2=2).add_(1 - alpha)
             self._split(self.T, self.T_s)
-            for k, plans in enumerate(self.square_plans):
-                self._run(plans)
-                self._split(self.P[k], self.P_s[k])
-            self._run(self.plan_m)
-            self._run(self.plan_r)
+            for plan in self.square_plans:
+                self.ext.gemm_plan_run(plan)
+            self.ext.gemm_plan_run(self.plan_m)
+            self.ext.gemm_plan_run(self.plan_r)
             new_error = (self.M_new - eye).abs().amax(dim=(1, 2))
             grew = (new_error > error * 1.2) if it > 0 else torch.zeros_like(active)
             # rounding puts a floor of a few 1e-7 * sqrt(n) under the residual: a matrix whose small
@@ -675,7 +677,7 @@ def inverse_pth_root_batched(mats, p, iter_count=100, error_tolerance=1e-6, ridg
     z = (1 + p) / (2 * torch.linalg.matrix_norm(g))
     if (mats.is_cuda and dtype == torch.float32 and n >= 128 and p >= 2 and (p & (p - 1)) == 0
             and ops.get_backend() != 'torch'
-            and (TENSOR_CORE_ROOTS == 'always' or (TENSOR_CORE_ROOTS == 'auto' and ridge_epsilon >= 1e-4))):
+            and TENSOR_CORE_ROOTS in ('always', 'auto')):
         chain = _NewtonChainCuda.get(b, n, p, mats.device)
         return chain.run(g, z, iter_count, error_tolerance, check_every)
     root = eye * z.pow(1.0 / p).view(b, 1, 1)

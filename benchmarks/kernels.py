@@ -116,8 +116,33 @@ def bench_inverse(timer, sizes, hbm, flops_peak, src):
             torch.cholesky_inverse(torch.linalg.cholesky(m + 1e-3 * eye))
     ms_lib = timer(lib)
     fl = sum(float(s) ** 3 for s in sizes)  # potrf n^3/3 + trtri n^3/3 + lauum n^3/3
-    emit(case='chol_inverse_grouped_fp32', sizes=sizes, ms=round(ms, 3), tflops_fp32=round(fl / ms / 1e9, 2),
-         cusolver_loop_ms=round(ms_lib, 3), speedup_vs_cusolver=round(ms_lib / ms, 2))
+    n = sizes[0]
+    eye = torch.eye(n, device='cuda', dtype=torch.float64)
+    resid = ((mats[0].double() + 1e-3 * eye) @ outs[0].double() - eye).abs().max().item()
+    emit(case='chol_inverse_grouped_fp32', backend=ops.CHOLESKY_BACKEND, sizes=sizes if len(sizes) < 8 else
+         f'{len(sizes)} factors {min(sizes)}..{max(sizes)}', ms=round(ms, 3), tflops_fp32=round(fl / ms / 1e9, 2),
+         cusolver_loop_ms=round(ms_lib, 3), speedup_vs_cusolver=round(ms_lib / ms, 2), residual_first=float(f'{resid:.2e}'))
+
+
+def bench_roots(timer, b, n, p, ridge):
+    """Shampoo inverse p-th roots of a batch: the grouped tensor-core chain against the batched fp32
+    matrix products of PyTorch (cuBLAS), same iteration, same stopping rule."""
+    from asdl_b200.precondition import shampoo
+    a = torch.randn(b, n, n // 2, device='cuda')
+    mats = a @ a.transpose(1, 2) / n
+    out = {}
+    for mode in ('auto', 'never'):
+        shampoo.TENSOR_CORE_ROOTS = mode
+        out[mode] = timer(lambda: shampoo.inverse_pth_root_batched(mats, p, ridge_epsilon=ridge))
+        roots = shampoo.inverse_pth_root_batched(mats, p, ridge_epsilon=ridge)
+        ev, evec = torch.linalg.eigh(mats[0].double())
+        ev = ev.clamp_min(0) + ridge * ev.max()
+        exact = (evec * ev.pow(-1.0 / p)) @ evec.T
+        out[mode + '_err'] = ((roots[0].double() - exact).norm() / exact.norm()).item()
+    shampoo.TENSOR_CORE_ROOTS = 'auto'
+    emit(case='inverse_pth_root_batched', batch=b, n=n, p=p, ridge=ridge, ms=round(out['auto'], 3),
+         rel_err_vs_fp64=float(f"{out['auto_err']:.2e}"), torch_bmm_ms=round(out['never'], 3),
+         torch_bmm_rel_err=float(f"{out['never_err']:.2e}"), speedup_vs_torch=round(out['never'] / out['auto'], 2))
 
 
 def bench_im2col(timer, n, c, hw, k, stride, pad, hbm, flops_peak, src):
@@ -159,13 +184,18 @@ def bench_batchnorm(timer, n, c, hw, hbm, flops_peak, src):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--only', default=None, choices=['syrk', 'syrk_x3', 'precond', 'inverse', 'im2col', 'batchnorm'])
+    ap.add_argument('--only', default=None, choices=['syrk', 'syrk_x3', 'precond', 'inverse', 'roots', 'im2col', 'batchnorm'])
+    ap.add_argument('--wide', type=int, default=0, help='tile width policy of the GEMM: 0 = 128, 1 = 256 for large outputs, 2 = 256 wherever legal')
+    ap.add_argument('--chol', default=None, choices=['tensor_core', 'cuda_core'], help='grouped inverse backend')
     ap.add_argument('--rows', type=int, default=None)
     ap.add_argument('--n', type=int, default=None)
     ap.add_argument('--iters', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     args = ap.parse_args()
     hbm, fl, src = peaks()
+    ops.extension().set_gemm_wide(args.wide)
+    if args.chol:
+        ops.CHOLESKY_BACKEND = args.chol
     timer = Timer(args.iters, args.warmup)
     want = lambda name: args.only in (None, name)  # noqa: E731
     if want('syrk'):
@@ -181,9 +211,17 @@ def main():
         for m, n in [(512, 4608), (2048, 512), (1024, 4096), (4096, 1024)]:
             bench_precond(timer, m, n, hbm, fl, src)
     if want('inverse'):
-        for sizes in ([args.n] if args.n else None, [4608], [1024] * 8, [64] * 16 + [256] * 16 + [512] * 8 + [1024] * 8 + [2304] * 6):
-            if sizes:
-                bench_inverse(timer, sizes, hbm, fl, src)
+        resnet = ([147, 64] + [64, 64] + [64, 256] * 4 + [256, 64] * 2 + [576, 64] * 3 + [256, 128] + [1152, 128] * 4
+                  + [128, 512] * 4 + [256, 512] + [512, 128] * 3 + [512, 256] + [2304, 256] * 6 + [256, 1024] * 6
+                  + [512, 1024] + [1024, 256] * 5 + [1024, 512] + [4608, 512] * 3 + [512, 2048] * 3 + [1024, 2048]
+                  + [2048, 512] * 2 + [2048, 1000])
+        cases = [[args.n]] if args.n else [[2048], [4608], [1024] * 8,
+                                           [64] * 16 + [256] * 16 + [512] * 8 + [1024] * 8 + [2304] * 6, resnet]
+        for sizes in cases:
+            bench_inverse(timer, sizes, hbm, fl, src)
+    if want('roots'):
+        for b, n, p, ridge in [(8, 1024, 4, 1e-6), (30, 1024, 4, 1e-6), (30, 768, 4, 1e-6)]:
+            bench_roots(timer, b, n, p, ridge)
     if want('im2col'):
         bench_im2col(timer, 32, 64, 56, 3, 1, 1, hbm, fl, src)
         bench_im2col(timer, 32, 256, 14, 3, 1, 1, hbm, fl, src)

@@ -546,3 +546,107 @@ def test_barrier_completes_alone_and_gives_up_on_a_missing_peer(ext):
 
 def test_fused_kfac_cuda_graph_matches_cpu():
     _fused_kfac_gpu_matches_cpu(True)
+
+
+@pytest.mark.parametrize('m,n,k,sym', [(256, 256, 2048, False), (200, 328, 1000, False), (384, 384, 4096, True),
+                                       (130, 130, 192, True)])
+def test_fp32_grade_product_from_three_way_splits(ext, m, n, k, sym):
+    """Six part products, chunked contraction: the result has to be as good as an fp32 product (a
+    single long bf16x3 accumulation in TMEM is off by ~1e-5 from truncation alone)."""
+    torch.manual_seed(0)
+    a = torch.randn(k, m, device=DEV) * torch.logspace(-2, 2, m, device=DEV)
+    b = a if sym else torch.randn(k, n, device=DEV)
+    ap, bp = ops.split3(a), ops.split3(b)
+    out = torch.full((m, n), float('nan'), device=DEV)
+    parts = [torch.zeros(m, (n + 63) // 64 * 64, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
+    ops.matmul_fp32_tc(ap, bp, False, False, out=out, sym=sym, out_parts=parts)
+    ref = a.double().T @ b.double()
+    fp32 = (a.T @ b).double()
+    err, err32 = (out.double() - ref).abs().max().item(), (fp32 - ref).abs().max().item()
+    assert err <= 4 * err32 + 1e-30, (err, err32)
+    assert rel_err(out, ref.float()) < 3e-7
+    total = sum(p[:, :n].double() for p in parts)
+    assert (total - out.double()).abs().max().item() <= out.abs().max().item() * 2.0 ** -22
+    if sym:
+        assert torch.equal(out, out.T)
+    # K-major operands give the same product
+    out2 = torch.empty(m, n, device=DEV)
+    ak, bk = ops.split3(a.T.contiguous()), ops.split3(b.T.contiguous())
+    ops.matmul_fp32_tc(ak, bk, True, True, out=out2)
+    assert rel_err(out2, ref.float()) < 3e-7
+
+
+@pytest.mark.parametrize('mode', [2])
+def test_wide_tiles_match_narrow_tiles(ext, mode):
+    torch.manual_seed(0)
+    try:
+        for rows, n in [(2048, 1024), (700, 392), (4096, 130)]:
+            x = torch.randn(rows, n, device=DEV).to(torch.bfloat16)
+            y = torch.randn(rows, 520, device=DEV).to(torch.bfloat16)
+            for nsplit in (1, 3):
+                ext.set_gemm_wide(0)
+                c0 = torch.empty(n, n, device=DEV)
+                ext.umma_gemm([x], [x], False, False, c0, 1.0, 0.0, True, None, None, nsplit)
+                g0 = torch.empty(n, 520, device=DEV)
+                ext.umma_gemm([x], [y], False, False, g0, 1.0, 0.0, False, None, None, nsplit)
+                ext.set_gemm_wide(mode)
+                c1 = torch.full((n, n), float('nan'), device=DEV)
+                ext.umma_gemm([x], [x], False, False, c1, 1.0, 0.0, True, None, None, nsplit)
+                g1 = torch.full((n, 520), float('nan'), device=DEV)
+                ext.umma_gemm([x], [y], False, False, g1, 1.0, 0.0, False, None, None, nsplit)
+                g2 = torch.full((n, 520), float('nan'), device=DEV)
+                ext.umma_gemm([x], [y.T.contiguous()], False, True, g2, 1.0, 0.0, False, None, None, nsplit)
+                assert rel_err(c1, c0) < 1e-6 and torch.equal(c1, c1.T)
+                assert rel_err(g1, g0) < 1e-6 and rel_err(g2, g0) < 1e-6
+    finally:
+        ext.set_gemm_wide(0)
+    ops.check_status()
+
+
+@pytest.mark.parametrize('backend', ['tensor_core', 'cuda_core'])
+@pytest.mark.parametrize('sizes', [[1], [128], [129, 300, 40], [1500, 640, 257], [2304, 576, 64, 64]])
+def test_chol_inverse_backends(backend, sizes):
+    """Both grouped inverses against fp64, on well and badly conditioned matrices."""
+    torch.manual_seed(1)
+    saved = ops.CHOLESKY_BACKEND
+    ops.CHOLESKY_BACKEND = backend
+    try:
+        mats, damp = [], []
+        for i, n in enumerate(sizes):
+            a = torch.randn(n, max(n // 2, 1), device=DEV)      # rank-deficient: the damping carries the inverse
+            mats.append(a @ a.T / max(n // 2, 1))
+            damp.append(1e-3 * (i + 1))
+        outs = [torch.empty_like(m) for m in mats]
+        for _ in range(2):                                       # the second call runs from the cached tables
+            ops.spd_inverse_grouped(mats, outs, torch.tensor(damp, device=DEV))
+        ops.check_status()
+        for m, o, d in zip(mats, outs, damp):
+            n = m.shape[0]
+            eye = torch.eye(n, device=DEV, dtype=torch.float64)
+            ref = torch.linalg.inv(m.double() + d * eye)
+            assert rel_err(o, ref.float()) < 2e-4, (n, rel_err(o, ref.float()))
+            assert torch.equal(o, o.T)
+            resid = ((m.double() + d * eye) @ o.double() - eye).abs().max().item()
+            assert resid < 1e-3, (n, resid)
+    finally:
+        ops.CHOLESKY_BACKEND = saved
+
+
+def test_inverse_root_chain_at_small_ridge():
+    """The ViT Shampoo configuration: blocks of 1024, fourth roots, ridge 1e-6, condition number >= 1e6."""
+    from asdl_b200.precondition import shampoo
+    torch.manual_seed(0)
+    n, p = 1024, 4
+    q, _ = torch.linalg.qr(torch.randn(n, n, device=DEV, dtype=torch.float64))
+    evals = torch.logspace(-8, 0, n, device=DEV, dtype=torch.float64)
+    mats = torch.stack([(q * evals) @ q.T, (q * evals.flip(0) * 30) @ q.T]).float()
+    ext = ops.extension()
+    before = ext.launch_count()
+    roots = shampoo.inverse_pth_root_batched(mats, p, ridge_epsilon=1e-6)
+    assert ext.launch_count() - before > 10                # the grouped tensor-core chain ran
+    for m, r in zip(mats.double(), roots.double()):
+        ev, evec = torch.linalg.eigh(m)
+        ev = ev.clamp_min(0) + 1e-6 * ev.max()
+        exact = (evec * ev.pow(-1.0 / p)) @ evec.T
+        assert rel_err(r, exact) < 2e-3, rel_err(r, exact)
+    ops.check_status()

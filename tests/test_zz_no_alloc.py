@@ -30,6 +30,19 @@ def _entry_point():
     return fn
 
 
+def _status(lib_fn=None):
+    """The entry point's own status word (read and cleared through its exported C symbol)."""
+    from asdl_b200.ops import _build
+    lib = ctypes.CDLL(_build._so_path())
+    fn = lib.asdl_b200_noalloc_status
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.POINTER(ctypes.c_int)]
+    code = ctypes.c_int(-1)
+    rc = fn(ctypes.byref(code))
+    assert rc == 0, f'asdl_b200_noalloc_status failed with {rc}'
+    return code.value
+
+
 def _call(fn, x, c, alpha, beta, nsplit):
     err = ctypes.create_string_buffer(256)
     stream = torch.cuda.current_stream().cuda_stream
@@ -57,6 +70,7 @@ def test_noalloc_entry_matches_regular_entry_twice():
         ref = (x.double().T @ x.double() / rows + beta * c0.double()).float()
         torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-4)
         assert torch.equal(got, got.T)
+        assert _status() == 0
     ops.check_status()
 
 
@@ -72,4 +86,17 @@ def test_noalloc_entry_rejects_oversized_request():
     bad = torch.zeros(64, 12, device='cuda', dtype=torch.bfloat16)
     rc, msg = _call(fn, bad, c, 1.0, 0.0, 1)  # row pitch of 12 elements is not TMA-legal
     assert rc != 0 and 'ldx' in msg
+    # a C pointer that is not 16-byte aligned with a row pitch that makes the kernel use 16-byte accesses:
+    # refused on the host, nothing is launched
+    flat = torch.zeros(128 * 128 + 4, device='cuda')
+    x_ok = torch.zeros(256, 128, device='cuda', dtype=torch.bfloat16)
+    err = ctypes.create_string_buffer(256)
+    rc = fn(x_ok.data_ptr(), 256, 128, 128, flat.data_ptr() + 4, 128, 1.0, 0.0, 1,
+            torch.cuda.current_stream().cuda_stream, err, len(err))
+    assert rc != 0 and 'aligned' in err.value.decode()
+    # row counts beyond the 32-bit range are refused before anything touches x
+    rc = fn(x_ok.data_ptr(), 1 << 31, 128, 128, flat.data_ptr(), 128, 1.0, 0.0, 1,
+            torch.cuda.current_stream().cuda_stream, err, len(err))
+    assert rc != 0 and 'rows' in err.value.decode()
     torch.cuda.synchronize()
+    assert _status() == 0
