@@ -4,13 +4,12 @@
 // Blocked right-looking Cholesky with 128-wide panels, triangular inverse by recursive doubling,
 // then X^T X.  Every O(n^3) product runs on the persistent tcgen05 GEMM (umma_gemm2.cuh) from
 // three-way bf16 splits of the fp32 values (v = hi + mid + lo carries the whole significand; the
-// six significant part products are issued small-magnitude-first), and every subtraction /
-// accumulation between products happens in fp32 on the CUDA cores:
-//   * the trailing update of a right-looking factorisation is a K = 128 product subtracted from
-//     the fp32 matrix in the GEMM epilogue, so the tensor core never carries a long sum;
-//   * the long contractions of the triangular inverse and of X^T X use the kernel's chunked-K
-//     mode (K = 128 per TMEM chunk, fp32 running sum in registers).
-// Only the 128 x 128 diagonal blocks are factored and inverted on the CUDA cores (one CTA each).
+// kernel's "split3" flavour issues the six significant part products small-magnitude-first and
+// sums the contraction in fp32 registers, one 64-wide K block per TMEM chunk), and every
+// subtraction between products happens in fp32 on the CUDA cores: the trailing update of a
+// right-looking factorisation is a K = 128 product subtracted from the fp32 matrix in the GEMM
+// epilogue.  Only the 128 x 128 diagonal blocks are factored and inverted on the CUDA cores (one
+// CTA each, the block held in registers as 8 x 8 cyclic tiles of a 16 x 16 thread grid).
 //
 //   potrf, step k:  diag(k):   L_kk = chol(A_kk), T_k = L_kk^-1                  (CUDA cores)
 //                   panel(k):  L_ik = A_ik T_k^T                  for i > k      (GEMM, K = 128)
@@ -71,78 +70,133 @@ __global__ void tc_prepare_kernel(const TcMat* mats, const float* damping) {
   }
 }
 
-// ---- diagonal block k: Cholesky factor and its inverse, 512 threads ---------------------------
-constexpr int DP = TB + 1;  // padded row pitch in shared memory
-
-__global__ void __launch_bounds__(512) tc_diag_kernel(const TcMat* mats, int k, int* status) {
+// ---- diagonal block k: Cholesky factor and its inverse ----------------------------------------
+// 256 threads form a 16 x 16 grid; thread (ty, tx) keeps the entries (ty + 16u, tx + 16v), u, v = 0..7,
+// of the block in registers (a cyclic layout keeps every thread busy while the active part shrinks).
+// Right-looking column steps: the owners of column j publish it through shared memory, everybody
+// scales it and updates its own entries; one barrier per step (the column buffer is double-buffered).
+// The inverse is a forward substitution on the identity in the same layout: row j of the inverse
+// becomes final at step j and is subtracted, times column j of the factor, from the rows below.
+__global__ void __launch_bounds__(256, 1) tc_diag_kernel(const TcMat* mats, int k, int* status) {
   const TcMat M = mats[blockIdx.x];
   if (k >= M.nb) return;
-  extern __shared__ float dsm[];
-  float* S = dsm;             // [TB][DP] factor
-  float* T = dsm + TB * DP;   // [TB][DP] inverse
+  __shared__ float colbuf[2][TB];
+  __shared__ float rowbuf[2][TB];
   const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
   const int r0 = k * TB;
-  for (int e = tid; e < TB * TB; e += 512) {
-    const int r = e >> 7, c = e & 127;
-    const int gr = r0 + r, gc = r0 + c;
-    float v = 0.f;
-    if (gr < M.n && gc < M.n)
-      v = (c <= r) ? M.L[static_cast<size_t>(gr) * M.n + gc] : 0.f;
-    else if (r == c)
-      v = 1.f;  // identity padding keeps the block factorisable
-    S[r * DP + c] = v;
-    T[r * DP + c] = (r == c) ? 1.f : 0.f;
-  }
-  __syncthreads();
-  const int tx = tid & 31, ty = tid >> 5;  // 32 x 16
-  // right-looking factorisation: after step j column j is final and the trailing block is updated
-  for (int j = 0; j < TB; ++j) {
-    if (tid == 0) {
-      float d = S[j * DP + j];
+  float a[8][8], t[8][8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      const int r = ty + 16 * u, c = tx + 16 * v;
+      const int gr = r0 + r, gc = r0 + c;
+      float x = 0.f;
+      if (gr < M.n && gc < M.n)
+        x = (c <= r) ? M.L[static_cast<size_t>(gr) * M.n + gc] : 0.f;
+      else if (r == c)
+        x = 1.f;  // identity padding keeps the block factorisable
+      a[u][v] = x;
+      t[u][v] = (r == c) ? 1.f : 0.f;
+    }
+  // ---- factorisation
+#pragma unroll
+  for (int vo = 0; vo < 8; ++vo) {
+    for (int txo = 0; txo < 16; ++txo) {
+      const int j = vo * 16 + txo;
+      float* col = colbuf[j & 1];
+      if (tx == txo) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) col[ty + 16 * u] = a[u][vo];
+      }
+      __syncthreads();
+      float d = col[j];
       if (!(d > 0.f)) {
-        set_error(status, ERR_NOT_SPD);
+        if (tid == 0) set_error(status, ERR_NOT_SPD);
         d = 1.f;
       }
-      S[j * DP + j] = sqrtf(d);
-    }
-    __syncthreads();
-    const float inv = 1.f / S[j * DP + j];
-    if (tid > j && tid < TB) S[tid * DP + j] *= inv;
-    __syncthreads();
-    for (int i = j + 1 + ty; i < TB; i += 16) {
-      const float lij = S[i * DP + j];
-      for (int c = j + 1 + tx; c <= i; c += 32) S[i * DP + c] = fmaf(-lij, S[c * DP + j], S[i * DP + c]);
-    }
-    // the next step reads column j+1 of the trailing block
-    __syncthreads();
-  }
-  // T = S^-1 by forward substitution on the identity, row by row: row j becomes final, then every
-  // later row gets its contribution.  Lanes run over rows while few columns exist, over columns later.
-  for (int j = 0; j < TB; ++j) {
-    const float inv = 1.f / S[j * DP + j];
-    if (tid <= j) T[j * DP + tid] *= inv;
-    __syncthreads();
-    if (j < 32) {
-      for (int c = ty; c <= j; c += 16) {
-        const float tjc = T[j * DP + c];
-        for (int i = j + 1 + tx; i < TB; i += 32) T[i * DP + c] = fmaf(-S[i * DP + j], tjc, T[i * DP + c]);
+      d = sqrtf(d);
+      const float inv = 1.f / d;
+      if (tx == txo) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = ty + 16 * u;
+          if (i > j)
+            a[u][vo] *= inv;
+          else if (i == j)
+            a[u][vo] = d;
+        }
       }
-    } else {
-      for (int i = j + 1 + ty; i < TB; i += 16) {
-        const float lij = S[i * DP + j];
-        for (int c = tx; c <= j; c += 32) T[i * DP + c] = fmaf(-lij, T[j * DP + c], T[i * DP + c]);
+      float rv[8], cv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = ty + 16 * u;
+        rv[u] = (u >= vo && i > j) ? col[i] * inv : 0.f;
+      }
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        const int c = tx + 16 * v;
+        cv[v] = (v >= vo && c > j) ? col[c] * inv : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          if (u >= vo && v >= vo && v <= u) a[u][v] = fmaf(-rv[u], cv[v], a[u][v]);
+    }
+  }
+  __syncthreads();
+  // ---- inverse
+#pragma unroll
+  for (int vo = 0; vo < 8; ++vo) {
+    for (int txo = 0; txo < 16; ++txo) {
+      const int j = vo * 16 + txo;
+      float* col = colbuf[j & 1];   // column j of the factor
+      float* row = rowbuf[j & 1];   // row j of the right-hand side
+      if (tx == txo) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) col[ty + 16 * u] = a[u][vo];
+      }
+      if (ty == txo) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v) row[tx + 16 * v] = t[vo][v];
+      }
+      __syncthreads();
+      const float inv = 1.f / col[j];
+      if (ty == txo) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v) t[vo][v] *= inv;
+      }
+      float lv[8], tv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = ty + 16 * u;
+        lv[u] = (u >= vo && i > j) ? col[i] : 0.f;
+      }
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        const int c = tx + 16 * v;
+        tv[v] = (v <= vo && c <= j) ? row[c] * inv : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          if (u >= vo && v <= vo) t[u][v] = fmaf(-lv[u], tv[v], t[u][v]);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      const int r = ty + 16 * u, c = tx + 16 * v;
+      const int gr = r0 + r, gc = r0 + c;
+      if (gr < M.n && gc < M.n) {
+        if (c <= r) M.L[static_cast<size_t>(gr) * M.n + gc] = a[u][v];
+        split3_store(M.Xs, static_cast<size_t>(gr) * M.ldp + gc, c <= r ? t[u][v] : 0.f);
       }
     }
-    __syncthreads();
-  }
-  for (int e = tid; e < TB * TB; e += 512) {
-    const int r = e >> 7, c = e & 127;
-    const int gr = r0 + r, gc = r0 + c;
-    if (gr < M.n && gc < M.n) {
-      if (c <= r) M.L[static_cast<size_t>(gr) * M.n + gc] = S[r * DP + c];
-      split3_store(M.Xs, static_cast<size_t>(gr) * M.ldp + gc, c <= r ? T[r * DP + c] : 0.f);
-    }
-  }
 }
 
 struct Launch {
@@ -171,25 +225,21 @@ int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 enum { PB_PANEL = 0, PB_TRAIL = 1, PB_W = 2, PB_X21 = 3, PB_LAUUM = 4, PB_COUNT = 5 };
 
 void fill_problem(GemmProblem2& P, __nv_bfloat16* const* a_parts, bool a_k, __nv_bfloat16* const* b_parts, bool b_k,
-                  int n, int ldp, float* C, int ldc, float alpha, float beta, int flags, int kchunk,
+                  int n, int ldp, float* C, int ldc, float alpha, float beta, int flags,
                   __nv_bfloat16* const* out_parts, int* status) {
   std::memset(&P, 0, sizeof(P));
-  // small-magnitude products first: (lo,hi) (hi,lo) (mid,mid) (mid,hi) (hi,mid) (hi,hi)
-  static const int ia[6] = {2, 0, 1, 1, 0, 0};
-  static const int ib[6] = {0, 2, 1, 0, 1, 0};
-  for (int s = 0; s < 6; ++s) {
-    g2_encode_operand(&P.tmA[s], a_parts[ia[s]], n, n, ldp, a_k, G2_BM);
-    g2_encode_operand(&P.tmB[s], b_parts[ib[s]], n, n, ldp, b_k, 128);
+  for (int s = 0; s < 3; ++s) {  // (hi, mid, lo) parts; the kernel forms the six part products itself
+    g2_encode_operand(&P.tmA[s], a_parts[s], n, n, ldp, a_k, G2_BM);
+    g2_encode_operand(&P.tmB[s], b_parts[s], n, n, ldp, b_k, 128);
   }
-  P.nseg = 6;
+  P.nseg = 3;
   P.M = P.N = P.K = n;
   P.C = C;
   P.Cin = C;
   P.ldc = ldc;
   P.alpha = alpha;
   P.beta = beta;
-  P.flags = flags | (a_k ? G2F_A_KMAJOR : 0) | (b_k ? G2F_B_KMAJOR : 0);
-  P.kchunk = kchunk;
+  P.flags = flags | G2F_SPLIT3 | (a_k ? G2F_A_KMAJOR : 0) | (b_k ? G2F_B_KMAJOR : 0);
   P.nsplit = 1;
   P.tiles_m = P.tiles_n = (n + TB - 1) / TB;
   P.ntiles = 0;
@@ -296,16 +346,16 @@ void chol_inverse_tc(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs,
       nb_max = std::max(nb_max, M.nb);
       GemmProblem2* pb = &probs[static_cast<size_t>(s) * PB_COUNT];
       // L_ik = A_ik T_k^T : both operands K-major, result to L (fp32) and Ls (splits), in place
-      fill_problem(pb[PB_PANEL], M.Ls, true, M.Xs, true, M.n, M.ldp, M.L, M.n, 1.f, 0.f, 0, 0, M.Ls, status);
+      fill_problem(pb[PB_PANEL], M.Ls, true, M.Xs, true, M.n, M.ldp, M.L, M.n, 1.f, 0.f, 0, M.Ls, status);
       // A_ij -= L_ik L_jk^T : lower tiles of the fp32 matrix; splits written for the next panel column only
       fill_problem(pb[PB_TRAIL], M.Ls, true, M.Ls, true, M.n, M.ldp, M.L, M.n, -1.f, 1.f,
-                   G2F_SYM | G2F_LOWER, 0, M.Ls, status);
-      // W = L_21 X_11 and X_21 = -X_22 W : chunked contraction, bf16 splits only
-      fill_problem(pb[PB_W], M.Ls, true, M.Xs, false, M.n, M.ldp, nullptr, M.n, 1.f, 0.f, 0, 2, Ws, status);
-      fill_problem(pb[PB_X21], M.Xs, true, Ws, false, M.n, M.ldp, nullptr, M.n, -1.f, 0.f, 0, 2, M.Xs, status);
+                   G2F_SYM | G2F_LOWER, M.Ls, status);
+      // W = L_21 X_11 and X_21 = -X_22 W : bf16 splits only
+      fill_problem(pb[PB_W], M.Ls, true, M.Xs, false, M.n, M.ldp, nullptr, M.n, 1.f, 0.f, 0, Ws, status);
+      fill_problem(pb[PB_X21], M.Xs, true, Ws, false, M.n, M.ldp, nullptr, M.n, -1.f, 0.f, 0, M.Xs, status);
       // out = X^T X : both operands MN-major, lower tiles mirrored
       fill_problem(pb[PB_LAUUM], M.Xs, false, M.Xs, false, M.n, M.ldp, M.L, M.n, 1.f, 0.f,
-                   G2F_SYM, 2, nullptr, status);
+                   G2F_SYM, nullptr, status);
     }
     std::vector<GemmWork2> work;
     auto push_list = [&](const std::vector<GemmWork2>& items) {
@@ -385,12 +435,6 @@ void chol_inverse_tc(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs,
     prep = &g_cache.back();
   }
 
-  static bool attr_set = false;
-  constexpr int diag_smem = 2 * TB * DP * static_cast<int>(sizeof(float));
-  if (!attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(tc_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, diag_smem));
-    attr_set = true;
-  }
   const TcMat* dm = reinterpret_cast<const TcMat*>(prep->d_mats.data_ptr());
   const GemmProblem2* dp = reinterpret_cast<const GemmProblem2*>(prep->d_probs.data_ptr());
   const GemmWork2* dw = reinterpret_cast<const GemmWork2*>(prep->d_work.data_ptr());
@@ -399,10 +443,10 @@ void chol_inverse_tc(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs,
   count_launch();
   for (const Launch& l : prep->launches) {
     if (l.kind == 0) {
-      tc_diag_kernel<<<l.count, 512, diag_smem, stream>>>(dm, l.arg, status);
+      tc_diag_kernel<<<l.count, 256, 0, stream>>>(dm, l.arg, status);
       count_launch();
     } else {
-      g2_launch_list(dp, dw + l.arg, l.count, false, dev, stream);
+      g2_launch_list(dp, dw + l.arg, l.count, G2_SPLIT3, dev, stream);
     }
   }
   B200_CUDA_CHECK(cudaGetLastError());

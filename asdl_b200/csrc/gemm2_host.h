@@ -7,6 +7,8 @@
 
 namespace b200 {
 
+enum G2Flavour { G2_PLAIN = 0, G2_WIDE = 1, G2_SPLIT3 = 2 };
+
 // Tensor map of one bf16 operand.  `mn` x `k` logical extents; `kmajor`: stored [mn, k] row-major
 // with pitch `ld` elements, otherwise stored [k, mn] row-major.  `box_mn`: tile extent along MN
 // for K-major operands (128 for A, the tile width for B); MN-major operands are always loaded as
@@ -17,8 +19,17 @@ void g2_encode_operand(CUtensorMap* tm, const void* base, int64_t mn, int64_t k,
 // SM count of a device (cached).
 int g2_sm_count(int dev);
 
+// One launch of a kernel flavour: either `single` (work == nullptr; its tiles are decoded from the
+// work index) or a device-resident problem table with a work list.  Defined in gemm2_<flavour>.cu.
+void g2_run_plain(const GemmProblem2& single, const GemmProblem2* probs, const GemmWork2* work, int n_work,
+                  int n_sms, cudaStream_t stream);
+void g2_run_wide(const GemmProblem2& single, const GemmProblem2* probs, const GemmWork2* work, int n_work,
+                 int n_sms, cudaStream_t stream);
+void g2_run_split3(const GemmProblem2& single, const GemmProblem2* probs, const GemmWork2* work, int n_work,
+                   int n_sms, cudaStream_t stream);
+
 // Runs `n_work` work items of a device-resident problem table on `stream`.
-void g2_launch_list(const GemmProblem2* d_probs, const GemmWork2* d_work, int n_work, bool wide,
+void g2_launch_list(const GemmProblem2* d_probs, const GemmWork2* d_work, int n_work, G2Flavour flavour,
                     int dev, cudaStream_t stream);
 
 // Split-K reduction of the listed tiles (one work item per tile).

@@ -28,18 +28,7 @@ void check_operand(const at::Tensor& t, const char* name) {
               " must be 16-byte aligned");
 }
 
-bool g_attr_set[2] = {false, false};
 int g_wide_mode = 0;  // 0: 128-wide tiles only, 1: 256-wide tiles for large outputs, 2: wherever legal
-
-template <int BN>
-void ensure_attr() {
-  const int i = BN == 128 ? 0 : 1;
-  if (!g_attr_set[i]) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(umma_gemm2_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         G2Cfg<BN>::SMEM_BYTES));
-    g_attr_set[i] = true;
-  }
-}
 
 bool stream_is_capturing(cudaStream_t s) {
   cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
@@ -75,21 +64,18 @@ void g2_encode_operand(CUtensorMap* tm, const void* base, int64_t mn, int64_t k,
     encode_tmap_bf16_2d(tm, base, mn, k, ld, 64, G2_BK);
 }
 
-void g2_launch_list(const GemmProblem2* d_probs, const GemmWork2* d_work, int n_work, bool wide,
+void g2_launch_list(const GemmProblem2* d_probs, const GemmWork2* d_work, int n_work, G2Flavour flavour,
                     int dev, cudaStream_t stream) {
   if (n_work <= 0) return;
-  const int grid = std::min(n_work, g2_sm_count(dev));
   GemmProblem2 dummy;
   std::memset(&dummy, 0, sizeof(dummy));
-  if (wide) {
-    ensure_attr<256>();
-    umma_gemm2_kernel<256><<<grid, G2_THREADS, G2Cfg<256>::SMEM_BYTES, stream>>>(dummy, d_probs, d_work, n_work);
-  } else {
-    ensure_attr<128>();
-    umma_gemm2_kernel<128><<<grid, G2_THREADS, G2Cfg<128>::SMEM_BYTES, stream>>>(dummy, d_probs, d_work, n_work);
-  }
-  B200_CUDA_CHECK(cudaGetLastError());
-  count_launch();
+  const int n_sms = g2_sm_count(dev);
+  if (flavour == G2_WIDE)
+    g2_run_wide(dummy, d_probs, d_work, n_work, n_sms, stream);
+  else if (flavour == G2_SPLIT3)
+    g2_run_split3(dummy, d_probs, d_work, n_work, n_sms, stream);
+  else
+    g2_run_plain(dummy, d_probs, d_work, n_work, n_sms, stream);
 }
 
 void g2_launch_reduce_list(const GemmProblem2* d_probs, const GemmWork2* d_work, int n_work, bool wide,
@@ -110,11 +96,12 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
                        const std::vector<at::Tensor>& b_segs, bool a_kmajor, bool b_kmajor,
                        const c10::optional<at::Tensor>& C, double alpha, double beta, bool sym,
                        const c10::optional<at::Tensor>& out_hi, const c10::optional<at::Tensor>& out_mid,
-                       const c10::optional<at::Tensor>& out_lo, int64_t nsplit_req, int64_t kchunk, int n_sms,
+                       const c10::optional<at::Tensor>& out_lo, int64_t nsplit_req, bool split3, int n_sms,
                        bool allow_no_output = false) {
   const int nseg = static_cast<int>(a_segs.size());
   TORCH_CHECK(nseg >= 1 && nseg <= G2_MAX_SEG && b_segs.size() == a_segs.size(),
               "between 1 and 6 operand segments are supported");
+  TORCH_CHECK(!split3 || nseg == 3, "a split3 product takes the (hi, mid, lo) parts of both operands");
   std::memset(&P, 0, sizeof(P));
   const at::Tensor& a0 = a_segs[0];
   const at::Tensor& b0 = b_segs[0];
@@ -124,9 +111,8 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
   const int64_t Kb = b_kmajor ? b0.size(1) : b0.size(0);
   TORCH_CHECK(K == Kb, "contraction sizes differ: ", K, " vs ", Kb);
   TORCH_CHECK(M > 0 && N > 0 && M < (1 << 30) && N < (1 << 30) && K < (1ll << 31) - 64, "matrix sizes out of range");
-  TORCH_CHECK(kchunk >= 0, "kchunk must not be negative");
   if (sym) TORCH_CHECK(M == N, "symmetric mode needs a square output");
-  const bool wide = kchunk == 0 && (g_wide_mode == 2 || (g_wide_mode == 1 && N >= 1024 && M >= 1024));
+  const bool wide = !split3 && (g_wide_mode == 2 || (g_wide_mode == 1 && N >= 1024 && M >= 1024));
   const int bn = wide ? 256 : 128;
   for (int s = 0; s < nseg; ++s) {
     check_operand(a_segs[s], "A");
@@ -136,7 +122,7 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
     g2_encode_operand(&P.tmA[s], a_segs[s].data_ptr(), M, K, a_segs[s].stride(0), a_kmajor, G2_BM);
     g2_encode_operand(&P.tmB[s], b_segs[s].data_ptr(), N, K, b_segs[s].stride(0), b_kmajor, bn);
   }
-  bool same_ab = sym && !wide && a_kmajor == b_kmajor;
+  bool same_ab = sym && !wide && !split3 && a_kmajor == b_kmajor;
   for (int s = 0; s < nseg && same_ab; ++s)
     same_ab = a_segs[s].data_ptr() == b_segs[s].data_ptr() &&
               a_segs[s].stride(0) == b_segs[s].stride(0);
@@ -145,11 +131,10 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
   P.N = static_cast<int>(N);
   P.K = static_cast<int>(K);
   P.nseg = nseg;
-  P.kchunk = static_cast<int>(kchunk);
   P.alpha = static_cast<float>(alpha);
   P.beta = static_cast<float>(beta);
   P.flags = (sym ? G2F_SYM : 0) | (a_kmajor ? G2F_A_KMAJOR : 0) | (b_kmajor ? G2F_B_KMAJOR : 0) |
-            (same_ab ? G2F_SAME_AB : 0) | (wide ? G2F_WIDE : 0);
+            (same_ab ? G2F_SAME_AB : 0) | (wide ? G2F_WIDE : 0) | (split3 ? G2F_SPLIT3 : 0);
   if (C.has_value()) {
     const at::Tensor& c = *C;
     TORCH_CHECK(c.is_cuda() && c.scalar_type() == at::kFloat && c.dim() == 2 && c.stride(1) == 1 &&
@@ -189,7 +174,7 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
   P.tiles_n = (P.N + bn - 1) / bn;
   P.ntiles = tile_count(P.tiles_m, P.tiles_n, sym, bn);
   const int kb_total = (P.K + G2_BK - 1) / G2_BK;
-  int nsplit = static_cast<int>(nsplit_req);
+  int nsplit = split3 ? 1 : static_cast<int>(nsplit_req);  // the chunked sum of a split3 product is not split
   if (nsplit <= 0) {
     const int target = 2 * n_sms;
     nsplit = target / (P.ntiles > 0 ? P.ntiles : 1);
@@ -231,17 +216,14 @@ void gemm_attach_scratch(GemmProblem2& P, int dev, cudaStream_t stream) {
 
 void gemm_launch_single(const GemmProblem2& P, int dev, cudaStream_t stream) {
   const int n_work = P.ntiles * P.nsplit;
-  const int grid = std::min(n_work, g2_sm_count(dev));
+  const int n_sms = g2_sm_count(dev);
   const bool wide = (P.flags & G2F_WIDE) != 0;
-  if (wide) {
-    ensure_attr<256>();
-    umma_gemm2_kernel<256><<<grid, G2_THREADS, G2Cfg<256>::SMEM_BYTES, stream>>>(P, nullptr, nullptr, n_work);
-  } else {
-    ensure_attr<128>();
-    umma_gemm2_kernel<128><<<grid, G2_THREADS, G2Cfg<128>::SMEM_BYTES, stream>>>(P, nullptr, nullptr, n_work);
-  }
-  B200_CUDA_CHECK(cudaGetLastError());
-  count_launch();
+  if (P.flags & G2F_SPLIT3)
+    g2_run_split3(P, nullptr, nullptr, n_work, n_sms, stream);
+  else if (wide)
+    g2_run_wide(P, nullptr, nullptr, n_work, n_sms, stream);
+  else
+    g2_run_plain(P, nullptr, nullptr, n_work, n_sms, stream);
   if (needs_ws(P)) {
     if (wide)
       splitk_reduce2_kernel<256><<<dim3(P.ntiles, 32, 1), 256, 0, stream>>>(P, nullptr, nullptr);
@@ -253,18 +235,18 @@ void gemm_launch_single(const GemmProblem2& P, int dev, cudaStream_t stream) {
 }
 
 // Python entry: C = alpha * A^T B (+ beta C), optionally symmetric, optionally bf16 split outputs.
-// `kchunk` > 0 cuts the contraction into chunks of that many 64-wide K blocks that are summed in
-// fp32 registers (fp32-grade products from split operands; see umma_gemm2.cuh).
+// `split3`: the three segments are the (hi, mid, lo) parts of fp32 operands and the product is
+// formed fp32-grade (six part products, one accumulation chunk per K block; see umma_gemm2.cuh).
 void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
                bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta, bool sym,
                c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
-               int64_t nsplit, c10::optional<at::Tensor> out_mid, int64_t kchunk) {
+               int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3) {
   TORCH_CHECK(!a_segs.empty(), "no operands");
   const int dev = a_segs[0].get_device();
   c10::cuda::CUDAGuard guard(dev);
   GemmProblem2 P;
   gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, C, alpha, beta, sym, out_hi, out_mid, out_lo,
-                    nsplit, kchunk, g2_sm_count(dev));
+                    nsplit, split3, g2_sm_count(dev));
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
   gemm_attach_scratch(P, dev, stream);
   gemm_launch_single(P, dev, stream);
@@ -285,7 +267,7 @@ void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_
   c10::cuda::CUDAGuard guard(dev);
   GemmProblem2 P;
   gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, c10::nullopt, alpha, 0.0, sym,
-                    c10::nullopt, c10::nullopt, c10::nullopt, nsplit, 0, g2_sm_count(dev),
+                    c10::nullopt, c10::nullopt, c10::nullopt, nsplit, false, g2_sm_count(dev),
                     /*allow_no_output=*/true);
   P.C = reinterpret_cast<float*>(dst_ptr);
   P.Cin = P.C;
@@ -316,7 +298,7 @@ struct GemmPlan {
   std::vector<std::vector<at::Tensor>> keep_alive;  // operands / outputs referenced by raw pointer
   at::Tensor d_problems, d_work, d_rwork, scratch;
   int n_work = 0, n_rwork = 0, dev = 0;
-  bool wide = false;
+  int split3 = -1;  // -1: no problem yet, 0: plain products, 1: split3 products (never mixed)
   bool finalized = false;
 };
 
@@ -335,19 +317,22 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
                    bool a_kmajor, bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta,
                    bool sym, c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
                    int64_t dst_ptr, int64_t ldc, bool atomic, std::vector<int64_t> extra_ptrs,
-                   int64_t nsplit, c10::optional<at::Tensor> out_mid, int64_t kchunk) {
+                   int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3) {
   auto it = g_plans.find(id);
   TORCH_CHECK(it != g_plans.end() && !it->second.finalized, "unknown or finalized plan");
   GemmPlan& plan = it->second;
   TORCH_CHECK(!a_segs.empty(), "no operands");
   plan.dev = a_segs[0].get_device();
+  TORCH_CHECK(plan.split3 < 0 || plan.split3 == static_cast<int>(split3),
+              "a plan holds either plain or split3 products, not both");
+  plan.split3 = split3 ? 1 : 0;
   c10::cuda::CUDAGuard guard(plan.dev);
   GemmProblem2 P;
   const int saved_mode = g_wide_mode;
   g_wide_mode = 0;  // the tiles of a plan share one kernel instantiation: 128-wide
   try {
     gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, C, alpha, beta, sym, out_hi, out_mid, out_lo,
-                      nsplit <= 0 ? 1 : nsplit, kchunk, g2_sm_count(plan.dev), /*allow_no_output=*/dst_ptr != 0);
+                      nsplit <= 0 ? 1 : nsplit, split3, g2_sm_count(plan.dev), /*allow_no_output=*/dst_ptr != 0);
   } catch (...) {
     g_wide_mode = saved_mode;
     throw;
@@ -418,7 +403,7 @@ void gemm_plan_finalize(int64_t id) {
           w.nkb = kb1 - kb0;
           w.tile_id = tile;
           w.split = s;
-          items.push_back({w, static_cast<long long>(P.nseg) * w.nkb + 2});
+          items.push_back({w, static_cast<long long>((P.flags & G2F_SPLIT3) ? 6 : P.nseg) * w.nkb + 2});
           if (split && s == 0) ritems.push_back({w, 0});
         }
       }
@@ -453,8 +438,8 @@ void gemm_plan_run(int64_t id) {
   c10::cuda::CUDAGuard guard(plan.dev);
   auto stream = at::cuda::getCurrentCUDAStream(plan.dev).stream();
   const GemmProblem2* probs = reinterpret_cast<const GemmProblem2*>(plan.d_problems.data_ptr());
-  g2_launch_list(probs, reinterpret_cast<const GemmWork2*>(plan.d_work.data_ptr()), plan.n_work, false,
-                 plan.dev, stream);
+  g2_launch_list(probs, reinterpret_cast<const GemmWork2*>(plan.d_work.data_ptr()), plan.n_work,
+                 plan.split3 == 1 ? G2_SPLIT3 : G2_PLAIN, plan.dev, stream);
   if (plan.n_rwork > 0)
     g2_launch_reduce_list(probs, reinterpret_cast<const GemmWork2*>(plan.d_rwork.data_ptr()), plan.n_rwork,
                           false, stream);

@@ -3,32 +3,35 @@
 //   C[M x N] (fp32)  =  alpha * sum_seg  op(A_seg)^T-contract-K  op(B_seg)   (+ beta * Cin)
 //
 // Operands are bf16 matrices contracted over K, each either MN-major ([K, M] row-major, the layout
-// of activations, so that X^T Y needs no transpose copy) or K-major ([M, K] row-major).  Up to six
-// (A_seg, B_seg) pairs accumulate into one result: with three-way splits v = hi + mid + lo the six
-// significant part products reproduce an fp32 product on the bf16 tensor cores.
+// of activations, so that X^T Y needs no transpose copy) or K-major ([M, K] row-major).
 //
-// What is new against the first generation:
-//   * persistent CTAs (one per SM) walk a list of work items - tiles of one problem or of a whole
-//     plan of problems - so a grouped launch pays one prologue per SM, not one per tile;
-//   * two TMEM accumulators: the MMA warp fills one while the eight epilogue warps drain the other,
-//     so stores (including stores into other GPUs' memory) overlap the next tile's main loop;
-//   * "chunked K": a problem may ask for the contraction to be cut into chunks of `kchunk` 64-wide
-//     K blocks.  Each chunk is accumulated in TMEM, read back and added to a running fp32 sum in
-//     registers with round-to-nearest adds.  The tensor core truncates when it adds into its
-//     accumulator, which biases long sums; short chunks bound that bias to a few 2^-24, and the
-//     segments are issued small-magnitude-first inside a chunk for the same reason;
-//   * a work item carries its own operand origins and K range, so triangular operands (Cholesky
-//     panels, triangular inverses) skip their zero blocks and sub-matrices of one tensor map serve
-//     as operands;
-//   * three-way bf16 split outputs (hi / mid / lo) straight from the epilogue.
+// Persistent CTAs walk a list of work items - tiles of one problem or of a whole plan of problems -
+// so a grouped launch pays one prologue per CTA, not one per tile.  Every CTA owns two TMEM
+// accumulators: the MMA warp fills one while the epilogue warps drain the other, so stores
+// (including stores into other GPUs' memory) overlap the next tile's main loop.  A work item
+// carries its own operand origins and K range, so triangular operands (Cholesky panels,
+// triangular inverses) skip their zero blocks and sub-matrices of one tensor map serve as operands.
 //
-// Roles inside a CTA of 320 threads:
-//   warp 0       TMA producer (cp.async.bulk.tensor, 128B swizzle, STAGES-deep ring)
-//   warp 1       TMEM allocator + single-thread tcgen05.mma issuer
-//   warps 2..9   epilogue: tcgen05.ld -> registers -> global; warp w reads TMEM lanes
-//                32*(w%4)..+31 (a hardware rule) and one half of the tile's columns.
-// Every wait is bounded in wall time; on expiry the status word is set and the CTA unwinds.
-// TMA loads only ever read this GPU's memory; peer memory is written with per-thread stores.
+// Three flavours of one kernel template:
+//   plain   128 x 128 tiles, two CTAs per SM with a 3-stage ring each (two independent pipelines
+//           per SM hide each other's load latency), four epilogue warps; up to six (A_seg, B_seg)
+//           pairs accumulate into one TMEM accumulator (bf16, or "bf16x3" from hi/lo splits);
+//   wide    128 x 256 tiles (a third less operand traffic per FLOP), one CTA per SM, 4 stages,
+//           eight epilogue warps;
+//   split3  fp32-grade products from three-way splits v = hi + mid + lo of both operands: a stage
+//           holds the three A parts and the three B parts of one 64-wide K block (96 KiB, loaded
+//           once) and the MMA warp issues the six significant part products from them,
+//           small magnitudes first.  Every K block is its own accumulation chunk: it goes to a
+//           fresh TMEM accumulator that the eight epilogue warps read back and add to a running
+//           fp32 sum in registers with round-to-nearest adds.  The tensor core truncates when it
+//           adds into its accumulator, which biases long sums (about 1e-6 of the largest term at
+//           K = 1024); with one K block per chunk the bias stays at a few 2^-24.
+//
+// Roles inside a CTA: warp 0 TMA producer (cp.async.bulk.tensor, 128B swizzle), warp 1 TMEM
+// allocator + single-thread tcgen05.mma issuer, warps 2.. epilogue (tcgen05.ld -> registers ->
+// global; warp w reads TMEM lanes 32*(w%4)..+31, a hardware rule).  Every wait is bounded in wall
+// time; on expiry the status word is set and the CTA unwinds.  TMA loads only ever read this GPU's
+// memory; peer memory is written with per-thread stores from the epilogue.
 #pragma once
 #include "sm100_ptx.cuh"
 
@@ -36,19 +39,22 @@ namespace b200 {
 
 constexpr int G2_BM = 128;
 constexpr int G2_BK = 64;
-constexpr int G2_THREADS = 320;
 constexpr int G2_MAX_SEG = 6;
 constexpr int G2_MAX_EXTRA = 7;
 constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;  // 16 KiB
 
-template <int BN>
+template <int BN, int EPI_WARPS, int MINB, bool SPLIT3>
 struct G2Cfg {
-  static constexpr int STAGES = (BN == 128) ? 6 : 4;
+  static constexpr int STAGES = SPLIT3 ? 2 : (BN == 256 ? 4 : (MINB == 2 ? 3 : 6));
   static constexpr int B_BYTES = BN * G2_BK * 2;
-  static constexpr int STAGE_BYTES = G2_A_BYTES + B_BYTES;
+  static constexpr int STAGE_BYTES = SPLIT3 ? 3 * (G2_A_BYTES + B_BYTES) : G2_A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
+using G2Plain = G2Cfg<128, 4, 2, false>;
+using G2Wide = G2Cfg<256, 8, 1, false>;
+using G2Split3 = G2Cfg<128, 8, 1, true>;
 
 enum : int {
   G2F_SYM = 1,        // symmetric output: tiles on or below the diagonal only, mirrored
@@ -58,6 +64,7 @@ enum : int {
   G2F_ATOMIC = 16,    // C += alpha * result with reductions (C may live on another GPU); beta unused
   G2F_LOWER = 32,     // with G2F_SYM: write / add the lower triangle only
   G2F_WIDE = 64,      // the problem's tensor maps and tile grid are laid out for BN = 256
+  G2F_SPLIT3 = 128,   // tmA[0..2] / tmB[0..2] are the (hi, mid, lo) parts of the operands
 };
 
 enum : int {
@@ -81,7 +88,7 @@ struct alignas(64) GemmProblem2 {
   int nseg;
   int tiles_m, tiles_n, ntiles, nsplit;
   int flags;
-  int kchunk;             // K blocks per accumulation chunk; 0 = the whole contraction in TMEM
+  int reserved;
   float alpha, beta;
 };
 
@@ -282,12 +289,13 @@ __device__ __forceinline__ void g2_store_chunk(const GemmProblem2& P, const floa
   }
 }
 
-template <int BN>
-__global__ void __launch_bounds__(G2_THREADS, 1)
+template <int BN, int EPI_WARPS, int MINB, bool SPLIT3>
+__global__ void __launch_bounds__(64 + 32 * EPI_WARPS, MINB)
 umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem2* __restrict__ probs,
                   const GemmWork2* __restrict__ work, int n_work) {
-  using Cfg = G2Cfg<BN>;
+  using Cfg = G2Cfg<BN, EPI_WARPS, MINB, SPLIT3>;
   constexpr int STAGES = Cfg::STAGES;
+  static_assert(!SPLIT3 || (BN == 128 && EPI_WARPS == 8), "the split3 flavour runs 128-wide tiles with 8 epilogue warps");
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128B swizzle atoms.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -308,7 +316,7 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], EPI_WARPS);  // one arrival per epilogue warp
     }
     mbar_fence_init();
   }
@@ -331,37 +339,42 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
         const GemmProblem2& P = (work != nullptr) ? probs[w.problem] : single;
         const bool a_k = (P.flags & G2F_A_KMAJOR) != 0;
         const bool b_k = (P.flags & G2F_B_KMAJOR) != 0;
-        const bool shared_ab = BN == 128 && (P.flags & G2F_SAME_AB) && w.a_mn == w.b_mn && w.a_k0 == w.b_k0;
+        const bool shared_ab = !SPLIT3 && BN == 128 && (P.flags & G2F_SAME_AB) && w.a_mn == w.b_mn &&
+                               w.a_k0 == w.b_k0;
         const uint32_t bytes = shared_ab ? G2_A_BYTES : Cfg::STAGE_BYTES;
-        const int kchunk = P.kchunk > 0 ? P.kchunk : (w.nkb > 0 ? w.nkb : 1);
-        for (int c0 = 0; c0 < w.nkb && ok; c0 += kchunk) {
-          const int c1 = (c0 + kchunk < w.nkb) ? c0 + kchunk : w.nkb;
-          for (int seg = 0; seg < P.nseg && ok; ++seg) {
-            for (int kb = c0; kb < c1; ++kb, ++it) {
-              const int s = it % STAGES;
-              const uint32_t ph = (it / STAGES) & 1;
-              if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
-                set_error(P.status, ERR_WAIT_EMPTY);
-                ok = false;
-                break;
-              }
-              uint8_t* sA = smem + s * Cfg::STAGE_BYTES;
-              uint8_t* sB = sA + G2_A_BYTES;
-              mbar_expect_tx(&full_bar[s], bytes);
-              const int ka = w.a_k0 + kb * G2_BK, kbb = w.b_k0 + kb * G2_BK;
+        const int nseg = SPLIT3 ? 1 : P.nseg;
+        for (int seg = 0; seg < nseg && ok; ++seg) {
+          for (int kb = 0; kb < w.nkb; ++kb, ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+              set_error(P.status, ERR_WAIT_EMPTY);
+              ok = false;
+              break;
+            }
+            uint8_t* stage = smem + s * Cfg::STAGE_BYTES;
+            mbar_expect_tx(&full_bar[s], bytes);
+            const int ka = w.a_k0 + kb * G2_BK, kbb = w.b_k0 + kb * G2_BK;
+            constexpr int NPART = SPLIT3 ? 3 : 1;
+#pragma unroll
+            for (int part = 0; part < NPART; ++part) {
+              const CUtensorMap* ta = SPLIT3 ? &P.tmA[part] : &P.tmA[seg];
+              const CUtensorMap* tb = SPLIT3 ? &P.tmB[part] : &P.tmB[seg];
+              uint8_t* sA = stage + part * G2_A_BYTES;
+              uint8_t* sB = stage + NPART * G2_A_BYTES + part * Cfg::B_BYTES;
               if (a_k) {
-                tma_load_2d(sA, &P.tmA[seg], &full_bar[s], ka, w.a_mn);
+                tma_load_2d(sA, ta, &full_bar[s], ka, w.a_mn);
               } else {
-                tma_load_2d(sA, &P.tmA[seg], &full_bar[s], w.a_mn, ka);
-                tma_load_2d(sA + G2_BK * 128, &P.tmA[seg], &full_bar[s], w.a_mn + 64, ka);
+                tma_load_2d(sA, ta, &full_bar[s], w.a_mn, ka);
+                tma_load_2d(sA + G2_BK * 128, ta, &full_bar[s], w.a_mn + 64, ka);
               }
               if (!shared_ab) {
                 if (b_k) {
-                  tma_load_2d(sB, &P.tmB[seg], &full_bar[s], kbb, w.b_mn);
+                  tma_load_2d(sB, tb, &full_bar[s], kbb, w.b_mn);
                 } else {
 #pragma unroll
                   for (int h = 0; h < BN / 64; ++h)
-                    tma_load_2d(sB + h * G2_BK * 128, &P.tmB[seg], &full_bar[s], w.b_mn + 64 * h, kbb);
+                    tma_load_2d(sB + h * G2_BK * 128, tb, &full_bar[s], w.b_mn + 64 * h, kbb);
                 }
               }
             }
@@ -387,11 +400,47 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
         const GemmProblem2& P = (work != nullptr) ? probs[w.problem] : single;
         const bool a_k = (P.flags & G2F_A_KMAJOR) != 0;
         const bool b_k = (P.flags & G2F_B_KMAJOR) != 0;
-        const bool shared_ab = BN == 128 && (P.flags & G2F_SAME_AB) && w.a_mn == w.b_mn && w.a_k0 == w.b_k0;
+        const bool shared_ab = !SPLIT3 && BN == 128 && (P.flags & G2F_SAME_AB) && w.a_mn == w.b_mn &&
+                               w.a_k0 == w.b_k0;
         const uint32_t idesc = make_idesc_bf16(G2_BM, BN, !a_k, !b_k);
-        const int kchunk = P.kchunk > 0 ? P.kchunk : (w.nkb > 0 ? w.nkb : 1);
-        for (int c0 = 0; c0 < w.nkb && ok; c0 += kchunk, ++ch) {
-          const int c1 = (c0 + kchunk < w.nkb) ? c0 + kchunk : w.nkb;
+        if (w.nkb <= 0) continue;
+        if constexpr (SPLIT3) {
+          for (int kb = 0; kb < w.nkb && ok; ++kb, ++it, ++ch) {
+            const uint32_t ab = ch & 1;
+            if (!mbar_wait(&acc_empty[ab], ((ch >> 1) & 1) ^ 1)) {
+              set_error(P.status, ERR_WAIT_ACC);
+              ok = false;
+              break;
+            }
+            const int s = it % STAGES;
+            if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
+              set_error(P.status, ERR_WAIT_FULL);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t tacc = tmem_base + ab * BN;
+            const uint32_t base = smem_u32(smem + s * Cfg::STAGE_BYTES);
+            // part products in issue order: (lo,hi) (hi,lo) (mid,mid) (mid,hi) (hi,mid) (hi,hi)
+            constexpr int PART_A[6] = {2, 0, 1, 1, 0, 0};
+            constexpr int PART_B[6] = {0, 2, 1, 0, 1, 0};
+#pragma unroll
+            for (int pr = 0; pr < 6; ++pr) {
+              const uint32_t aA = base + PART_A[pr] * G2_A_BYTES;
+              const uint32_t aB = base + 3 * G2_A_BYTES + PART_B[pr] * Cfg::B_BYTES;
+#pragma unroll
+              for (int k = 0; k < G2_BK / 16; ++k) {
+                const uint64_t da = a_k ? make_smem_desc_sw128(aA + k * 32, 16, 1024)
+                                        : make_smem_desc_sw128(aA + k * 16 * 128, G2_BK * 128, 1024);
+                const uint64_t db = b_k ? make_smem_desc_sw128(aB + k * 32, 16, 1024)
+                                        : make_smem_desc_sw128(aB + k * 16 * 128, G2_BK * 128, 1024);
+                umma_bf16(tacc, da, db, idesc, (pr | k) ? 1u : 0u);
+              }
+            }
+            umma_commit(&empty_bar[s]);
+            umma_commit(&acc_full[ab]);
+          }
+        } else {
           const uint32_t ab = ch & 1;
           if (!mbar_wait(&acc_empty[ab], ((ch >> 1) & 1) ^ 1)) {
             set_error(P.status, ERR_WAIT_ACC);
@@ -402,7 +451,7 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
           const uint32_t tacc = tmem_base + ab * BN;
           uint32_t first = 1;
           for (int seg = 0; seg < P.nseg && ok; ++seg) {
-            for (int kb = c0; kb < c1; ++kb, ++it) {
+            for (int kb = 0; kb < w.nkb; ++kb, ++it) {
               const int s = it % STAGES;
               const uint32_t ph = (it / STAGES) & 1;
               if (!mbar_wait(&full_bar[s], ph)) {
@@ -427,14 +476,15 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
             }
           }
           if (ok) umma_commit(&acc_full[ab]);
+          ++ch;
         }
       }
     }
   } else {
     // ------------------------------ epilogue ----------------------------------------
-    const int q = warp & 3;             // TMEM lane quarter this warp may access
-    const int half = (warp - 2) >> 2;   // which half of the tile's columns
-    constexpr int COLS = BN / 2;        // columns per warp
+    const int q = warp & 3;                                   // TMEM lane quarter this warp may access
+    constexpr int COLS = BN / (EPI_WARPS / 4);                // columns per warp
+    const int col_base = ((warp - 2) >> 2) * COLS;            // first column of this warp's share
     constexpr int PASSES = COLS / 64;
     const int row = q * 32 + lane;
     uint32_t ch = 0;
@@ -442,8 +492,7 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
     for (int wi = blockIdx.x; wi < n_work && ok; wi += gridDim.x) {
       const GemmWork2 w = (work != nullptr) ? work[wi] : g2_decode<BN>(single, wi);
       const GemmProblem2& P = (work != nullptr) ? probs[w.problem] : single;
-      const int kchunk = P.kchunk > 0 ? P.kchunk : (w.nkb > 0 ? w.nkb : 1);
-      const int nchunks = (w.nkb + kchunk - 1) / kchunk;
+      const int nchunks = SPLIT3 ? w.nkb : (w.nkb > 0 ? 1 : 0);
       const int gr = w.c_row + row;
       const bool sym = (P.flags & G2F_SYM) != 0;
       const bool atomic = (P.flags & G2F_ATOMIC) != 0;
@@ -476,7 +525,7 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
         }
       };
 
-      if (nchunks <= 1) {
+      if constexpr (!SPLIT3) {
         const uint32_t ab = ch & 1;
         if (nchunks == 1) {
           ok = mbar_wait(&acc_full[ab], (ch >> 1) & 1);
@@ -488,7 +537,7 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
 #pragma unroll
         for (int pass = 0; pass < PASSES; ++pass) {
           float v[64];
-          const int col0 = half * COLS + pass * 64;
+          const int col0 = col_base + pass * 64;
           if (nchunks == 1) {
             uint32_t r0[32], r1[32];
             tmem_ld_32x32(tmem_base + lane_addr + ab * BN + col0, r0);
@@ -511,14 +560,11 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
           finish(v, col0);
         }
         if (nchunks == 1) ++ch;
-      } else if (PASSES != 1) {
-        set_error(P.status, ERR_BAD_ARG);  // chunked contraction needs 128-wide tiles (refused on the host)
-        ok = false;
-        break;
       } else {
-        // chunked contraction: running fp32 sum in registers
+        // one chunk per K block: running fp32 sum in registers
         float run[64];
-        const int col0 = half * COLS;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) run[j] = 0.f;
         for (int c = 0; c < nchunks; ++c, ++ch) {
           const uint32_t ab = ch & 1;
           ok = mbar_wait(&acc_full[ab], (ch >> 1) & 1);
@@ -527,28 +573,20 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
           if (!ok) break;
           tc_fence_after_sync();
           uint32_t r0[32], r1[32];
-          tmem_ld_32x32(tmem_base + lane_addr + ab * BN + col0, r0);
-          tmem_ld_32x32(tmem_base + lane_addr + ab * BN + col0 + 32, r1);
+          tmem_ld_32x32(tmem_base + lane_addr + ab * BN + col_base, r0);
+          tmem_ld_32x32(tmem_base + lane_addr + ab * BN + col_base + 32, r1);
           tmem_ld_wait();
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[ab]);
-          if (c == 0) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              run[j] = __uint_as_float(r0[j]);
-              run[32 + j] = __uint_as_float(r1[j]);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              run[j] += __uint_as_float(r0[j]);
-              run[32 + j] += __uint_as_float(r1[j]);
-            }
+          for (int j = 0; j < 32; ++j) {
+            run[j] += __uint_as_float(r0[j]);
+            run[32 + j] += __uint_as_float(r1[j]);
           }
         }
         if (!ok) break;
-        finish(run, col0);
+        finish(run, col_base);
       }
     }
   }

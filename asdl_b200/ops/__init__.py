@@ -45,12 +45,6 @@ _ext = None
 #: panels, fp32 FMA tile products)
 CHOLESKY_BACKEND = 'tensor_core'
 
-#: segment order of an fp32-grade product from three-way splits (hi, mid, lo): the six significant
-#: part products, small magnitudes first (the tensor core truncates when it adds into its accumulator)
-SPLIT3_ORDER_A = (2, 0, 1, 1, 0, 0)
-SPLIT3_ORDER_B = (0, 2, 1, 0, 1, 0)
-#: K blocks (of 64) per accumulation chunk of such a product
-SPLIT3_KCHUNK = 2
 
 
 def set_backend(name: str):
@@ -163,15 +157,14 @@ def split3(x: torch.Tensor):
 def matmul_fp32_tc(a_parts, b_parts, a_kmajor: bool, b_kmajor: bool, out=None, alpha: float = 1.0, beta: float = 0.0,
                    sym: bool = False, out_parts=None):
     """fp32-grade product on the bf16 tensor cores from three-way splits of both operands
-    (``a_parts`` / ``b_parts``: the (hi, mid, lo) triples of :func:`split3`): six part products,
-    issued small-magnitude-first, the contraction accumulated in TMEM in chunks of 128 and summed
-    in fp32 registers.  ``out_parts``: optional (hi, mid, lo) bf16 buffers that receive the split
-    of the result from the epilogue."""
-    a_segs = [a_parts[i] for i in SPLIT3_ORDER_A]
-    b_segs = [b_parts[i] for i in SPLIT3_ORDER_B]
+    (``a_parts`` / ``b_parts``: the (hi, mid, lo) triples of :func:`split3`): the kernel loads the
+    six part tiles of a K block once, issues the six significant part products
+    small-magnitude-first into a fresh TMEM accumulator and adds every K block to a running fp32
+    sum in registers.  ``out_parts``: optional (hi, mid, lo) bf16 buffers that receive the split of
+    the result from the epilogue."""
     oh, om, ol = out_parts if out_parts is not None else (None, None, None)
-    extension().umma_gemm(a_segs, b_segs, a_kmajor, b_kmajor, out, float(alpha), float(beta), sym, oh, ol, 1,
-                          om, SPLIT3_KCHUNK)
+    extension().umma_gemm(list(a_parts), list(b_parts), a_kmajor, b_kmajor, out, float(alpha), float(beta), sym,
+                          oh, ol, 1, om, True)
     return out
 
 

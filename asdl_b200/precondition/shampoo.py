@@ -538,12 +538,12 @@ class _NewtonChainCuda:
 
     Every product of an iteration (T^2, T^4, ..., T^p M and R T) runs as one grouped tcgen05 launch
     over the whole batch: the operands are split three ways into bf16 parts (v = hi + mid + lo
-    carries the full fp32 significand) and the six significant part products are issued
-    small-magnitude-first; the contraction is accumulated in TMEM in chunks of K = 128 that the
-    epilogue warps add into an fp32 running sum in registers.  The tensor core truncates when it
-    adds into its accumulator, which biases a long sum by ~1e-6 of its largest term - more than a
-    ridge of 1e-6; the short chunks keep the bias at a few 2^-24, which reproduces an fp32 product
-    and lets the iteration converge at that ridge.  All iterates are polynomials in the (symmetric)
+    carries the full fp32 significand), the kernel loads the six part tiles of a 64-wide K block
+    once and issues the six significant part products small-magnitude-first into a fresh TMEM
+    accumulator, which the epilogue warps add into an fp32 running sum in registers.  The tensor
+    core truncates when it adds into its accumulator, which biases a long sum by ~1e-6 of its
+    largest term - more than a ridge of 1e-6; one K block per chunk keeps the bias at a few 2^-24,
+    which lets the iteration converge at that ridge.  All iterates are polynomials in the (symmetric)
     input, hence symmetric, so the row-major buffers serve directly as MN-major operands and nothing
     is transposed; the products run in the GEMM's symmetric mode (lower tiles, mirrored), which keeps
     the iterates exactly symmetric at half the work, and the epilogue writes the three-way split of
@@ -587,15 +587,13 @@ class _NewtonChainCuda:
             """One plan: out (fp32, may be None) and / or its three-way split = a . bb, fp32-grade."""
             plan = ext.gemm_plan_new()
             for i in range(b):
-                a_parts = [t[i][:, :n] for t in a]
-                b_parts = [t[i][:, :n] for t in bb]
-                a_segs = [a_parts[j] for j in ops.SPLIT3_ORDER_A]
-                b_segs = [b_parts[j] for j in ops.SPLIT3_ORDER_B]
+                a_segs = [t[i][:, :n] for t in a]
+                b_segs = [t[i][:, :n] for t in bb]
                 oh, om, ol = (t[i] for t in out_split) if out_split is not None else (None, None, None)
                 # symmetric mode: lower-triangular tiles only, mirrored (half the work, and the iterates
                 # stay exactly symmetric, which the transposed operand reads rely on)
                 ext.gemm_plan_add(plan, a_segs, b_segs, False, False, out[i] if out is not None else None,
-                                  1.0, 0.0, True, oh, ol, 0, 0, False, [], 1, om, ops.SPLIT3_KCHUNK)
+                                  1.0, 0.0, True, oh, ol, 0, 0, False, [], 1, om, True)
             ext.gemm_plan_finalize(plan)
             self.plans.append(plan)
             return plan
