@@ -104,6 +104,40 @@ struct GemmWork2 {
   int pad;
 };
 
+// What the epilogue needs of a problem, read once per work item into registers: a problem of a
+// grouped launch lives in global memory, and reading its fields through the pointer between the
+// stores would force the compiler to reload them after every store.
+struct G2Epi {
+  float* C;
+  const float* Cin;
+  __nv_bfloat16 *out_hi, *out_mid, *out_lo;
+  float* ws;
+  const GemmProblem2* full;   // for the rarely used fields (extra destinations)
+  int M, N, ldc, ld_out, flags, n_extra, nsplit;
+  float alpha, beta;
+};
+
+__device__ __forceinline__ G2Epi g2_epi(const GemmProblem2& P) {
+  G2Epi e;
+  e.C = P.C;
+  e.Cin = P.Cin;
+  e.out_hi = P.out_hi;
+  e.out_mid = P.out_mid;
+  e.out_lo = P.out_lo;
+  e.ws = P.ws;
+  e.full = &P;
+  e.M = P.M;
+  e.N = P.N;
+  e.ldc = P.ldc;
+  e.ld_out = P.ld_out;
+  e.flags = P.flags;
+  e.n_extra = P.n_extra;
+  e.nsplit = P.nsplit;
+  e.alpha = P.alpha;
+  e.beta = P.beta;
+  return e;
+}
+
 // number of column tiles scheduled in tile row tm
 template <int BN>
 __device__ __forceinline__ int g2_tiles_in_row(const GemmProblem2& P, int tm) {
@@ -155,7 +189,7 @@ __device__ __forceinline__ bool g2_vec_ok(const float* base, int ldc) {
 
 // Accumulating variant of the final store (G2F_ATOMIC): every element is added to C with a
 // reduction instruction, so that several CTAs / GPUs can contribute to the same matrix.
-__device__ __forceinline__ void g2_reduce_chunk(const GemmProblem2& P, const float* v, int gr, int gc0,
+__device__ __forceinline__ void g2_reduce_chunk(const G2Epi& P, const float* v, int gr, int gc0,
                                                 bool diag_tile) {
   if (gr >= P.M) return;
   const bool sym = (P.flags & G2F_SYM) != 0;
@@ -185,7 +219,7 @@ __device__ __forceinline__ void g2_reduce_chunk(const GemmProblem2& P, const flo
 }
 
 // Final store of 32 consecutive columns of one row held by this thread.
-__device__ __forceinline__ void g2_store_chunk(const GemmProblem2& P, const float* v, int gr, int gc0,
+__device__ __forceinline__ void g2_store_chunk(const G2Epi& P, const float* v, int gr, int gc0,
                                                bool diag_tile, bool split_out) {
   if (gr >= P.M) return;
   const bool sym = (P.flags & G2F_SYM) != 0;
@@ -243,8 +277,9 @@ __device__ __forceinline__ void g2_store_chunk(const GemmProblem2& P, const floa
     }
   }
   for (int e = 0; e < P.n_extra; ++e) {  // plain (non-symmetric) result replicated to peers
-    float* c = P.C_extra[e] + static_cast<size_t>(gr) * P.ldc + gc0;
-    if (full && g2_vec_ok(P.C_extra[e], P.ldc)) {
+    float* const extra = P.full->C_extra[e];
+    float* c = extra + static_cast<size_t>(gr) * P.ldc + gc0;
+    if (full && g2_vec_ok(extra, P.ldc)) {
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         *reinterpret_cast<float4*>(c + 4 * j) =
@@ -491,7 +526,9 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
     bool ok = true;
     for (int wi = blockIdx.x; wi < n_work && ok; wi += gridDim.x) {
       const GemmWork2 w = (work != nullptr) ? work[wi] : g2_decode<BN>(single, wi);
-      const GemmProblem2& P = (work != nullptr) ? probs[w.problem] : single;
+      const GemmProblem2& Pg = (work != nullptr) ? probs[w.problem] : single;
+      const G2Epi P = g2_epi(Pg);
+      int* const status = Pg.status;
       const int nchunks = SPLIT3 ? w.nkb : (w.nkb > 0 ? 1 : 0);
       const int gr = w.c_row + row;
       const bool sym = (P.flags & G2F_SYM) != 0;
@@ -529,7 +566,7 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
         const uint32_t ab = ch & 1;
         if (nchunks == 1) {
           ok = mbar_wait(&acc_full[ab], (ch >> 1) & 1);
-          if (!ok) set_error(P.status, ERR_WAIT_ACC);
+          if (!ok) set_error(status, ERR_WAIT_ACC);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
@@ -568,7 +605,7 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
         for (int c = 0; c < nchunks; ++c, ++ch) {
           const uint32_t ab = ch & 1;
           ok = mbar_wait(&acc_full[ab], (ch >> 1) & 1);
-          if (!ok) set_error(P.status, ERR_WAIT_ACC);
+          if (!ok) set_error(status, ERR_WAIT_ACC);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
@@ -616,7 +653,7 @@ splitk_reduce2_kernel(const __grid_constant__ GemmProblem2 single, const GemmPro
     w = g2_decode<BN>(single, blockIdx.x * single.nsplit);
     Pp = &single;
   }
-  const GemmProblem2& P = *Pp;
+  const G2Epi P = g2_epi(*Pp);
   const bool sym = (P.flags & G2F_SYM) != 0;
   constexpr int PC = BN / 32;  // patches per tile row
   const int sub_r = blockIdx.y / PC, sub_c = blockIdx.y % PC;
@@ -665,7 +702,7 @@ splitk_reduce2_kernel(const __grid_constant__ GemmProblem2 single, const GemmPro
     const bool keep = inb && !(diag_tile && gc > gr);
     if (keep) {
       if (P.C != nullptr) P.C[static_cast<size_t>(gr) * P.ldc + gc] = val;
-      for (int e = 0; e < P.n_extra; ++e) P.C_extra[e][static_cast<size_t>(gr) * P.ldc + gc] = val;
+      for (int e = 0; e < P.n_extra; ++e) P.full->C_extra[e][static_cast<size_t>(gr) * P.ldc + gc] = val;
       if (P.out_hi != nullptr) {
         const size_t o = static_cast<size_t>(gr) * P.ld_out + gc;
         const size_t om = static_cast<size_t>(gc) * P.ld_out + gr;
