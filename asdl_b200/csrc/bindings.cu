@@ -46,7 +46,9 @@ std::vector<at::Tensor> ln_backward(at::Tensor x, at::Tensor dy, at::Tensor weig
                                     at::Tensor rstd);
 void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot, int64_t wait_ms);
 void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale);
-void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs);
+void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, int64_t mc_ptr);
+void symm_bucket_reduce(at::Tensor peers, int64_t rank, int64_t world, int64_t slot, at::Tensor segs, double scale,
+                        int64_t mc_ptr, int64_t wait_ms, int64_t blocks);
 void symm_scale_segments(at::Tensor local, at::Tensor segs, double beta);
 void symm_mirror_lower(at::Tensor local, at::Tensor mats, int64_t n_max);
 void symm_reduce_slots(at::Tensor local, at::Tensor table, int64_t world, int64_t slot_stride, int64_t n_max,
@@ -88,7 +90,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ln_backward", &b200::ln_backward);
   m.def("symm_barrier", &b200::symm_barrier);
   m.def("symm_reduce_segments", &b200::symm_reduce_segments);
-  m.def("symm_bcast_segments", &b200::symm_bcast_segments);
+  m.def("symm_bcast_segments", &b200::symm_bcast_segments, py::arg("peers"), py::arg("rank"), py::arg("world"),
+        py::arg("segs"), py::arg("mc_ptr") = 0);
+  m.def("symm_bucket_reduce", &b200::symm_bucket_reduce);
   m.def("symm_scale_segments", &b200::symm_scale_segments);
   m.def("symm_mirror_lower", &b200::symm_mirror_lower);
   m.def("symm_reduce_slots", &b200::symm_reduce_slots);

@@ -74,159 +74,109 @@ __global__ void __launch_bounds__(256) tc_prepare_kernel(const TcMat* mats, cons
 }
 
 // ---- diagonal block k: Cholesky factor and its inverse ----------------------------------------
-// One CTA of 256 threads holds the 128 x 128 block in shared memory and works on it in 16-wide
-// sub-panels, so that only 8 x 3 block-wide barriers are needed for the factorisation:
-//   (a) warp 0 factors the 16 x 16 diagonal sub-block in registers (one row per lane, columns
-//       exchanged with shuffles) and inverts it by forward substitution;
-//   (b) all threads form the sub-panel  P <- P * inv(L_dd)^T;
-//   (c) all threads subtract P P^T from the trailing part.
-// The inverse of the whole block then follows from the inverted 16 x 16 diagonal sub-blocks by
-// recursive doubling (X_21 = -X_22 L_21 X_11 for sub-blocks of 16, 32, 64).
-constexpr int DP = 132;                 // row pitch of the shared-memory matrices (floats)
-constexpr int WP = 68;                  // row pitch of the temporary of the doubling steps
-constexpr int TC_DIAG_SMEM = (2 * TB * DP + 64 * WP + 16 * 17) * static_cast<int>(sizeof(float));
-
+// 256 threads form a 16 x 16 grid; thread (ty, tx) keeps the entries (ty + 16u, tx + 16v), u, v = 0..7,
+// of the block and of the inverse in registers (a cyclic layout keeps every thread busy while the
+// active part shrinks).  One pass of 128 column steps does both: at step j the owners of column j of
+// the block and of row j of the right-hand side publish them through shared memory; everybody scales
+// them (L[:, j] and T[j, :] are final now) and updates its own entries of the trailing block and of
+// the rows of the right-hand side below j.  One barrier per step: the exchange buffers are
+// double-buffered.  This chain of 128 dependent steps is the critical path of every panel step, so
+// the pivot's reciprocal square root comes from the fast instruction plus one Newton step.
 __global__ void __launch_bounds__(256, 1) tc_diag_kernel(const TcMat* mats, int k, int* status) {
   const TcMat M = mats[blockIdx.x];
   if (k >= M.nb) return;
-  extern __shared__ float dsm[];
-  float* A = dsm;                 // [TB][DP] the block, later its factor (lower triangle)
-  float* X = A + TB * DP;         // [TB][DP] inverse of the factor
-  float* W = X + TB * DP;         // [64][WP] L_21 X_11 of a doubling step
-  float* Ti = W + 64 * WP;        // [16][17] inverse of the current diagonal sub-block
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int r0 = k * TB;
-  for (int e = tid; e < TB * TB; e += 256) {
-    const int r = e >> 7, c = e & 127;
-    const int gr = r0 + r, gc = r0 + c;
-    float v = 0.f;
-    if (gr < M.n && gc < M.n)
-      v = (c <= r) ? M.L[static_cast<size_t>(gr) * M.n + gc] : 0.f;
-    else if (r == c)
-      v = 1.f;  // identity padding keeps the block factorisable
-    A[r * DP + c] = v;
-    X[r * DP + c] = 0.f;
-  }
-  __syncthreads();
+  __shared__ float colbuf[2][TB];
+  __shared__ float rowbuf[2][TB];
+  const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
-  for (int kb = 0; kb < 8; ++kb) {
-    const int j0 = 16 * kb;
-    if (warp == 0) {
-      // (a) 16 x 16 diagonal sub-block: lane r (and its twin r + 16) holds row r
-      const int r = lane & 15;
-      float row[16];
+  const int r0 = k * TB;
+  float a[8][8], t[8][8];
 #pragma unroll
-      for (int m = 0; m < 16; ++m) row[m] = (m <= r) ? A[(j0 + r) * DP + j0 + m] : 0.f;
-      bool bad = false;
+  for (int u = 0; u < 8; ++u)
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        float d = __shfl_sync(0xffffffffu, row[j], j);
-        if (!(d > 0.f)) {
-          bad = true;
-          d = 1.f;
+    for (int v = 0; v < 8; ++v) {
+      const int r = ty + 16 * u, c = tx + 16 * v;
+      const int gr = r0 + r, gc = r0 + c;
+      float x = 0.f;
+      if (gr < M.n && gc < M.n)
+        x = (c <= r) ? M.L[static_cast<size_t>(gr) * M.n + gc] : 0.f;
+      else if (r == c)
+        x = 1.f;  // identity padding keeps the block factorisable
+      a[u][v] = x;
+      t[u][v] = (r == c) ? 1.f : 0.f;
+    }
+  bool bad = false;
+#pragma unroll
+  for (int vo = 0; vo < 8; ++vo) {
+    for (int txo = 0; txo < 16; ++txo) {
+      const int j = vo * 16 + txo;
+      float* col = colbuf[j & 1];   // column j of the block, before scaling
+      float* row = rowbuf[j & 1];   // row j of the right-hand side, before scaling
+      if (tx == txo) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (u >= vo) col[ty + 16 * u] = a[u][vo];
+      }
+      if (ty == txo) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          if (v <= vo) row[tx + 16 * v] = t[vo][v];
+      }
+      __syncthreads();
+      float d = col[j];
+      if (!(d > 0.f)) {
+        bad = true;
+        d = 1.f;
+      }
+      float inv = rsqrtf(d);
+      inv = inv * fmaf(-0.5f * d, inv * inv, 1.5f);   // one Newton step: full fp32 accuracy
+      const float sq = d * inv;
+      float rv[8], cv[8], tv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) rv[u] = (u >= vo && ty + 16 * u > j) ? col[ty + 16 * u] * inv : 0.f;
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        const int c = tx + 16 * v;
+        cv[v] = (v >= vo && c > j) ? col[c] * inv : 0.f;
+        tv[v] = (v <= vo && c <= j) ? row[c] * inv : 0.f;
+      }
+      if (tx == txo) {   // column j of the factor
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (u >= vo) {
+            const int i = ty + 16 * u;
+            if (i > j)
+              a[u][vo] = rv[u];
+            else if (i == j)
+              a[u][vo] = sq;
+          }
+      }
+      if (ty == txo) {   // row j of the inverse
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          if (v <= vo) t[vo][v] = tv[v];
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          if (u >= vo && v >= vo && v <= u) a[u][v] = fmaf(-rv[u], cv[v], a[u][v]);
+          if (u >= vo && v <= vo) t[u][v] = fmaf(-rv[u], tv[v], t[u][v]);
         }
-        const float sq = sqrtf(d);
-        const float inv = 1.f / sq;
-        const float lj = (r == j) ? sq : row[j] * inv;   // rows above the diagonal hold zeros
-        row[j] = lj;
-#pragma unroll
-        for (int c = j + 1; c < 16; ++c) {
-          const float lc = __shfl_sync(0xffffffffu, lj, c);
-          if (r >= c) row[c] = fmaf(-lj, lc, row[c]);
-        }
-      }
-      if (bad && lane == 0) set_error(status, ERR_NOT_SPD);
-      // inverse, column c in lane c: t[i] = (delta_ic - sum_{m<i} l[i][m] t[m]) / l[i][i]
-      float t[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float acc = (i == r) ? 1.f : 0.f;
-#pragma unroll
-        for (int m = 0; m < i; ++m) acc = fmaf(-__shfl_sync(0xffffffffu, row[m], i), t[m], acc);
-        t[i] = acc / __shfl_sync(0xffffffffu, row[i], i);
-      }
-      if (lane < 16) {
-#pragma unroll
-        for (int m = 0; m < 16; ++m) {
-          if (m <= r) A[(j0 + r) * DP + j0 + m] = row[m];
-          Ti[m * 17 + r] = t[m];                    // Ti[i][c] with c = this lane
-          X[(j0 + m) * DP + j0 + r] = t[m];
-        }
-      }
-    }
-    __syncthreads();
-    const int below = TB - j0 - 16;   // rows under the diagonal sub-block
-    // (b) sub-panel: P[i][c] = sum_m A[i][j0 + m] * Ti[c][m]; a row is handled by the 16 threads of
-    //     one half-warp, which all read the row before any of them writes its element
-    for (int ii = ty; ii < below; ii += 16) {
-      const float* arow = A + (j0 + 16 + ii) * DP + j0;
-      float acc = 0.f;
-#pragma unroll
-      for (int m = 0; m < 16; ++m) acc = fmaf(arow[m], Ti[tx * 17 + m], acc);
-      __syncwarp();
-      A[(j0 + 16 + ii) * DP + j0 + tx] = acc;
-    }
-    __syncthreads();
-    // (c) trailing update: A[i][c] -= sum_m P[i][m] P[c][m] for the 16 x 16 sub-blocks (a, b), b <= a
-    const int nblk = below / 16;
-    for (int a = 0; a < nblk; ++a) {
-      const int i = j0 + 16 + 16 * a + ty;
-      float pi[16];
-#pragma unroll
-      for (int m = 0; m < 16; m += 4) {
-        const float4 q4 = *reinterpret_cast<const float4*>(A + i * DP + j0 + m);
-        pi[m] = q4.x; pi[m + 1] = q4.y; pi[m + 2] = q4.z; pi[m + 3] = q4.w;
-      }
-      for (int b = 0; b <= a; ++b) {
-        const int c = j0 + 16 + 16 * b + tx;
-        float acc = 0.f;
-#pragma unroll
-        for (int m = 0; m < 16; m += 4) {
-          const float4 q4 = *reinterpret_cast<const float4*>(A + c * DP + j0 + m);
-          acc = fmaf(pi[m], q4.x, acc);
-          acc = fmaf(pi[m + 1], q4.y, acc);
-          acc = fmaf(pi[m + 2], q4.z, acc);
-          acc = fmaf(pi[m + 3], q4.w, acc);
-        }
-        A[i * DP + c] -= acc;   // (i, c) with c > i lies above the diagonal: written, never read
-      }
-    }
-    __syncthreads();
-  }
-  // ---- X = L^-1 by recursive doubling from the inverted 16 x 16 diagonal sub-blocks
-  for (int s = 16; s < TB; s *= 2) {
-    const int outs = (TB / (2 * s)) * s * s;   // elements of all X_21 blocks of this level
-    // W = L_21 X_11 (X_11 lower triangular: the sum over j starts at the column's sub-block)
-    for (int o = tid; o < outs; o += 256) {
-      const int p = o / (s * s), rem = o - p * s * s;
-      const int r = rem / s, c = rem - r * s;
-      const int f0 = 2 * p * s, e = f0 + s;
-      const float* lrow = A + (e + r) * DP + f0;
-      float acc = 0.f;
-      for (int j = c & ~15; j < s; ++j) acc = fmaf(lrow[j], X[(f0 + j) * DP + f0 + c], acc);
-      W[(p * s + r) * WP + c] = acc;   // p * s + r < 64 at every level
-    }
-    __syncthreads();
-    // X_21 = -X_22 W (X_22 lower triangular: the sum over j stops at the row)
-    for (int o = tid; o < outs; o += 256) {
-      const int p = o / (s * s), rem = o - p * s * s;
-      const int r = rem / s, c = rem - r * s;
-      const int f0 = 2 * p * s, e = f0 + s;
-      const float* xrow = X + (e + r) * DP + e;
-      float acc = 0.f;
-      for (int j = 0; j <= r; ++j) acc = fmaf(xrow[j], W[(p * s + j) * WP + c], acc);
-      X[(e + r) * DP + f0 + c] = -acc;
-    }
-    __syncthreads();
-  }
-  for (int e = tid; e < TB * TB; e += 256) {
-    const int r = e >> 7, c = e & 127;
-    const int gr = r0 + r, gc = r0 + c;
-    if (gr < M.n && gc < M.n) {
-      if (c <= r) M.L[static_cast<size_t>(gr) * M.n + gc] = A[r * DP + c];
-      split3_store(M.Xs, static_cast<size_t>(gr) * M.ldp + gc, c <= r ? X[r * DP + c] : 0.f);
     }
   }
+  if (bad && tid == 0) set_error(status, ERR_NOT_SPD);
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      const int r = ty + 16 * u, c = tx + 16 * v;
+      const int gr = r0 + r, gc = r0 + c;
+      if (gr < M.n && gc < M.n) {
+        if (c <= r) M.L[static_cast<size_t>(gr) * M.n + gc] = a[u][v];
+        split3_store(M.Xs, static_cast<size_t>(gr) * M.ldp + gc, c <= r ? t[u][v] : 0.f);
+      }
+    }
 }
 
 struct Launch {
@@ -467,11 +417,6 @@ void chol_inverse_tc(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs,
     prep = &g_cache.back();
   }
 
-  static bool attr_set_on[64] = {false};
-  if (!attr_set_on[dev & 63]) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(tc_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_DIAG_SMEM));
-    attr_set_on[dev & 63] = true;
-  }
   const TcMat* dm = reinterpret_cast<const TcMat*>(prep->d_mats.data_ptr());
   const GemmProblem2* dp = reinterpret_cast<const GemmProblem2*>(prep->d_probs.data_ptr());
   const GemmWork2* dw = reinterpret_cast<const GemmWork2*>(prep->d_work.data_ptr());
@@ -480,7 +425,7 @@ void chol_inverse_tc(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs,
   count_launch();
   for (const Launch& l : prep->launches) {
     if (l.kind == 0) {
-      tc_diag_kernel<<<l.count, 256, TC_DIAG_SMEM, stream>>>(dm, l.arg, status);
+      tc_diag_kernel<<<l.count, 256, 0, stream>>>(dm, l.arg, status);
       count_launch();
     } else {
       g2_launch_list(dp, dw + l.arg, l.count, G2_SPLIT3, dev, stream);

@@ -15,6 +15,12 @@
 //   symm_reduce_slots     owner-side sum of the per-rank slots that the peers' SYRK epilogues stored
 //                         into (lower triangles), folded into the running factor and mirrored.
 //   symm_mirror_lower     upper triangle <- lower triangle of local matrices.
+//   symm_bucket_reduce    one kernel per gradient bucket on a communication stream: every rank
+//                         announces "my part of this bucket is in place", waits (bounded) for all
+//                         ranks, and the owner of each listed segment pulls the sum - through the
+//                         NVSwitch with one multimem.ld_reduce per 16 bytes where the buffer has a
+//                         multicast mapping, with one plain peer load per rank otherwise.
+//   symm_bcast_segments   with a multicast mapping one multimem.st per 16 bytes reaches every rank.
 //
 // The first SYMM_FLAG_WORDS 32-bit words of the symmetric buffer are reserved for the barrier
 // slots: word [s * 64 + r] of rank q is "rank r has reached epoch of barrier stream s"; word
@@ -51,6 +57,21 @@ __device__ __forceinline__ float4 ld_peer_f4(const float* p) {
 }
 __device__ __forceinline__ void st_peer_f4(float* p, float4 v) {
   asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y),
+               "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
+// ---- NVLS: one instruction per 16 bytes reads the sum over all ranks / writes to all ranks --------
+__device__ __forceinline__ float4 multimem_ld_reduce_f4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_f4(float* mc, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y),
                "f"(v.z), "f"(v.w)
                : "memory");
 }
@@ -106,15 +127,90 @@ __global__ void symm_reduce_segments_kernel(const long long* peers, int rank, in
   }
 }
 
-__global__ void symm_bcast_segments_kernel(const long long* peers, int rank, int world, const Seg* segs) {
+__global__ void symm_bcast_segments_kernel(const long long* peers, int rank, int world, const Seg* segs,
+                                           float* mc_base) {
   const Seg s = segs[blockIdx.y];
   const float* local = reinterpret_cast<const float*>(peers[rank]) + s.off;
   const long long n4 = s.numel >> 2;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const float4 v = *reinterpret_cast<const float4*>(local + 4 * i);
-    for (int r = 0; r < world; ++r)
-      if (r != rank) st_peer_f4(reinterpret_cast<float*>(peers[r]) + s.off + 4 * i, v);
+    if (mc_base != nullptr) {
+      multimem_st_f4(mc_base + s.off + 4 * i, v);   // the switch delivers it to every rank (this one too)
+    } else {
+      for (int r = 0; r < world; ++r)
+        if (r != rank) st_peer_f4(reinterpret_cast<float*>(peers[r]) + s.off + 4 * i, v);
+    }
+  }
+}
+
+// Flag exchange + owner pull of one gradient bucket in one kernel.  Flag words of barrier slot
+// `slot` in this rank's buffer: [slot*64 + r] "rank r has reached epoch", [slot*64 + 63] the epoch
+// of the last completed call, [slot*64 + 62] count of blocks that finished the current call.  The
+// epoch word only changes when the last block of a call retires, so every block of a call reads
+// the same value at its start and no per-call host argument is needed (CUDA-graph replay).
+__global__ void symm_bucket_reduce_kernel(const long long* peers, int rank, int world, int slot,
+                                          const Seg* segs, int nsegs, float scale, const float* mc_base,
+                                          unsigned long long wait_ns, int* status) {
+  uint32_t* flags = reinterpret_cast<uint32_t*>(peers[rank]) + slot * 64;
+  __shared__ int s_ok;
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(flags + 63) + 1;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();   // this rank's bucket (written by earlier kernels of the stream) before the flag
+    st_release_sys(reinterpret_cast<uint32_t*>(peers[threadIdx.x]) + slot * 64 + rank, epoch);
+  }
+  if (threadIdx.x < world) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
+      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > wait_ns) {
+        set_error(status, ERR_WAIT_PEER);
+        s_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (s_ok) {
+    for (int sidx = 0; sidx < nsegs; ++sidx) {
+      const Seg s = segs[sidx];
+      float* local = reinterpret_cast<float*>(peers[rank]) + s.off;
+      const long long n4 = s.numel >> 2;
+      for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+           i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        float4 acc;
+        if (mc_base != nullptr) {
+          acc = multimem_ld_reduce_f4(mc_base + s.off + 4 * i);
+        } else {
+          acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int r = 0; r < world; ++r) {
+            const float4 v = ld_peer_f4(reinterpret_cast<const float*>(peers[r]) + s.off + 4 * i);
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+          }
+        }
+        acc.x *= scale;
+        acc.y *= scale;
+        acc.z *= scale;
+        acc.w *= scale;
+        *reinterpret_cast<float4*>(local + 4 * i) = acc;
+      }
+    }
+  }
+  // retire: the last block publishes the epoch for the next call
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t done = atomicAdd(flags + 62, 1u) + 1;
+    if (done == gridDim.x) {
+      flags[62] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(flags + 63) = epoch;
+    }
   }
 }
 
@@ -203,6 +299,8 @@ __global__ void symm_reduce_slots_kernel(float* base, const SlotRow* table, int 
 }
 
 // ---- host ------------------------------------------------------------------------------------
+static int sm_count(int dev) { return at::cuda::getDeviceProperties(dev)->multiProcessorCount; }
+
 static void check_table(const at::Tensor& peers, int world) {
   TORCH_CHECK(peers.is_cuda() && peers.scalar_type() == at::kLong && peers.is_contiguous() &&
                   peers.numel() == world, "peers must be a CUDA int64 vector with one pointer per rank");
@@ -235,7 +333,7 @@ void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Ten
   const int dev = peers.get_device();
   c10::cuda::CUDAGuard guard(dev);
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
-  dim3 grid(148, static_cast<unsigned>(segs.size(0)));
+  dim3 grid(sm_count(dev), static_cast<unsigned>(segs.size(0)));
   symm_reduce_segments_kernel<<<grid, 256, 0, stream>>>(
       reinterpret_cast<const long long*>(peers.data_ptr<int64_t>()), static_cast<int>(rank),
       static_cast<int>(world), reinterpret_cast<const Seg*>(segs.data_ptr<int64_t>()),
@@ -244,17 +342,42 @@ void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Ten
   count_launch();
 }
 
-void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs) {
+// `mc_ptr`: address of the buffer's multicast mapping (0: none, plain peer stores are used)
+void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, int64_t mc_ptr) {
   check_table(peers, static_cast<int>(world));
   check_segs(segs);
   if (segs.size(0) == 0) return;
   const int dev = peers.get_device();
   c10::cuda::CUDAGuard guard(dev);
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
-  dim3 grid(148, static_cast<unsigned>(segs.size(0)));
+  dim3 grid(sm_count(dev), static_cast<unsigned>(segs.size(0)));
   symm_bcast_segments_kernel<<<grid, 256, 0, stream>>>(
       reinterpret_cast<const long long*>(peers.data_ptr<int64_t>()), static_cast<int>(rank),
-      static_cast<int>(world), reinterpret_cast<const Seg*>(segs.data_ptr<int64_t>()));
+      static_cast<int>(world), reinterpret_cast<const Seg*>(segs.data_ptr<int64_t>()),
+      reinterpret_cast<float*>(mc_ptr));
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
+// One gradient bucket: flag exchange on barrier slot `slot`, then this rank pulls the sum of the
+// listed segments (the ones it owns) scaled by `scale`.  Every rank has to make the call for every
+// bucket, with an empty segment list if it owns nothing in it.  `blocks`: CTAs of the kernel (the
+// pull shares the GPU with the backward pass it overlaps).
+void symm_bucket_reduce(at::Tensor peers, int64_t rank, int64_t world, int64_t slot, at::Tensor segs, double scale,
+                        int64_t mc_ptr, int64_t wait_ms, int64_t blocks) {
+  check_table(peers, static_cast<int>(world));
+  check_segs(segs);
+  TORCH_CHECK(world <= 62 && slot >= 0 && slot * 64 + 64 <= SYMM_FLAG_WORDS, "bad barrier slot");
+  TORCH_CHECK(wait_ms > 0 && wait_ms <= 60000, "the wait limit must be in (0, 60000] ms");
+  TORCH_CHECK(blocks >= 1 && blocks <= 1024, "blocks out of range");
+  const int dev = peers.get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  symm_bucket_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      reinterpret_cast<const long long*>(peers.data_ptr<int64_t>()), static_cast<int>(rank), static_cast<int>(world),
+      static_cast<int>(slot), reinterpret_cast<const Seg*>(segs.data_ptr<int64_t>()), static_cast<int>(segs.size(0)),
+      static_cast<float>(scale), reinterpret_cast<const float*>(mc_ptr),
+      static_cast<unsigned long long>(wait_ms) * 1000000ull, device_state(dev).status.data_ptr<int>());
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch();
 }
@@ -267,7 +390,7 @@ void symm_scale_segments(at::Tensor local, at::Tensor segs, double beta) {
   const int dev = local.get_device();
   c10::cuda::CUDAGuard guard(dev);
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
-  dim3 grid(148, static_cast<unsigned>(segs.size(0)));
+  dim3 grid(sm_count(dev), static_cast<unsigned>(segs.size(0)));
   symm_scale_segments_kernel<<<grid, 256, 0, stream>>>(
       local.data_ptr<float>(), reinterpret_cast<const Seg*>(segs.data_ptr<int64_t>()),
       static_cast<float>(beta));

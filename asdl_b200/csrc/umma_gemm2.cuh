@@ -294,30 +294,78 @@ __device__ __forceinline__ void g2_store_chunk(const G2Epi& P, const float* v, i
     const size_t o = static_cast<size_t>(gr) * P.ld_out + gc0;
     // a symmetric problem's bf16 images are consumed as full matrices: write the mirror image too
     const bool mirror = sym && !(P.flags & G2F_LOWER);
+    const bool masked = sym && diag_tile;   // entries above the diagonal are not this tile's to write
+    const bool vec = full && !masked && ((P.ld_out & 7) == 0) &&
+                     (((reinterpret_cast<uintptr_t>(P.out_hi) | reinterpret_cast<uintptr_t>(P.out_mid) |
+                        reinterpret_cast<uintptr_t>(P.out_lo)) & 15) == 0);
+    if (vec) {
+      // 32 consecutive bf16 per part: four 16-byte stores instead of 32 two-byte ones (a warp's
+      // lanes hold different rows, so every store instruction touches 32 sectors either way)
+      uint32_t ph[16], pm[16], pl[16];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const int gc = gc0 + j;
-      if (gc >= P.N || (sym && diag_tile && gc > gr)) continue;
-      const float x = out[j];
-      const __nv_bfloat16 h = __float2bfloat16_rn(x);
-      P.out_hi[o + j] = h;
-      const size_t om = static_cast<size_t>(gc) * P.ld_out + gr;
-      if (mirror && gc != gr) P.out_hi[om] = h;
-      if (P.out_lo != nullptr) {
-        const float r1 = x - __bfloat162float(h);
+      for (int j = 0; j < 16; ++j) {
+        const float x0 = out[2 * j], x1 = out[2 * j + 1];
+        const __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
+        const float r0 = x0 - __bfloat162float(h0), r1 = x1 - __bfloat162float(h1);
+        const __nv_bfloat16 m0 = __float2bfloat16_rn(r0), m1 = __float2bfloat16_rn(r1);
+        ph[j] = static_cast<uint32_t>(__bfloat16_as_ushort(h0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(h1)) << 16);
         if (P.out_mid != nullptr) {
-          const __nv_bfloat16 m = __float2bfloat16_rn(r1);
-          const __nv_bfloat16 l = __float2bfloat16_rn(r1 - __bfloat162float(m));
-          P.out_mid[o + j] = m;
-          P.out_lo[o + j] = l;
-          if (mirror && gc != gr) {
-            P.out_mid[om] = m;
-            P.out_lo[om] = l;
-          }
+          const __nv_bfloat16 l0 = __float2bfloat16_rn(r0 - __bfloat162float(m0));
+          const __nv_bfloat16 l1 = __float2bfloat16_rn(r1 - __bfloat162float(m1));
+          pm[j] = static_cast<uint32_t>(__bfloat16_as_ushort(m0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(m1)) << 16);
+          pl[j] = static_cast<uint32_t>(__bfloat16_as_ushort(l0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(l1)) << 16);
         } else {
-          const __nv_bfloat16 l = __float2bfloat16_rn(r1);
-          P.out_lo[o + j] = l;
-          if (mirror && gc != gr) P.out_lo[om] = l;
+          pm[j] = 0u;   // two-way split: the residual goes to out_lo
+          pl[j] = static_cast<uint32_t>(__bfloat16_as_ushort(m0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(m1)) << 16);
+        }
+      }
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        *reinterpret_cast<uint4*>(P.out_hi + o + 8 * q4) = make_uint4(ph[4 * q4], ph[4 * q4 + 1], ph[4 * q4 + 2], ph[4 * q4 + 3]);
+        if (P.out_mid != nullptr)
+          *reinterpret_cast<uint4*>(P.out_mid + o + 8 * q4) = make_uint4(pm[4 * q4], pm[4 * q4 + 1], pm[4 * q4 + 2], pm[4 * q4 + 3]);
+        if (P.out_lo != nullptr)
+          *reinterpret_cast<uint4*>(P.out_lo + o + 8 * q4) = make_uint4(pl[4 * q4], pl[4 * q4 + 1], pl[4 * q4 + 2], pl[4 * q4 + 3]);
+      }
+      if (mirror) {   // transposed image: consecutive lanes write consecutive addresses
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const size_t om = static_cast<size_t>(gc0 + j) * P.ld_out + gr;
+          const uint32_t wh = ph[j >> 1], wm = pm[j >> 1], wl = pl[j >> 1];
+          const unsigned short sh = (j & 1) ? static_cast<unsigned short>(wh >> 16) : static_cast<unsigned short>(wh & 0xffffu);
+          const unsigned short sm = (j & 1) ? static_cast<unsigned short>(wm >> 16) : static_cast<unsigned short>(wm & 0xffffu);
+          const unsigned short sl = (j & 1) ? static_cast<unsigned short>(wl >> 16) : static_cast<unsigned short>(wl & 0xffffu);
+          P.out_hi[om] = __ushort_as_bfloat16(sh);
+          if (P.out_mid != nullptr) P.out_mid[om] = __ushort_as_bfloat16(sm);
+          if (P.out_lo != nullptr) P.out_lo[om] = __ushort_as_bfloat16(sl);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int gc = gc0 + j;
+        if (gc >= P.N || (masked && gc > gr)) continue;
+        const float x = out[j];
+        const __nv_bfloat16 h = __float2bfloat16_rn(x);
+        P.out_hi[o + j] = h;
+        const size_t om = static_cast<size_t>(gc) * P.ld_out + gr;
+        if (mirror && gc != gr) P.out_hi[om] = h;
+        if (P.out_lo != nullptr) {
+          const float r1 = x - __bfloat162float(h);
+          if (P.out_mid != nullptr) {
+            const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+            const __nv_bfloat16 l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+            P.out_mid[o + j] = m;
+            P.out_lo[o + j] = l;
+            if (mirror && gc != gr) {
+              P.out_mid[om] = m;
+              P.out_lo[om] = l;
+            }
+          } else {
+            const __nv_bfloat16 l = __float2bfloat16_rn(r1);
+            P.out_lo[o + j] = l;
+            if (mirror && gc != gr) P.out_lo[om] = l;
+          }
         }
       }
     }

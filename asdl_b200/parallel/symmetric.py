@@ -12,6 +12,8 @@ Replaces the packed ``dist.reduce`` / ``dist.broadcast`` calls of the reference
 """
 from typing import List, Sequence, Tuple
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -39,6 +41,9 @@ class SymmetricArena:
     #: their owner-local work (inverses) and by host stalls, which this has to cover
     barrier_wait_ms = 5000
 
+    #: barrier slot of the kernels that run on the communication stream (slot 0 belongs to the main stream)
+    COMM_SLOT = 1
+
     def __init__(self, numel: int, group=None, device=None):
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
@@ -50,6 +55,16 @@ class SymmetricArena:
         self.world = self.handle.world_size
         self.peer_ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
         self.peers_dev = torch.tensor(self.peer_ptrs, dtype=torch.int64, device=self.device)
+        # NVLS: the address under which the NVSwitch sees all ranks' copies at once (multimem.ld_reduce
+        # / multimem.st in the kernels); 0 when the fabric or the allocator offers none.  Switched off
+        # with ASDL_B200_MULTIMEM=0: a process that dies while its memory is bound to a multicast
+        # object can fault its peers' GPUs, so runs that expect ranks to leave use plain peer accesses.
+        self.multicast_ptr = 0
+        if os.environ.get('ASDL_B200_MULTIMEM', '1') != '0':
+            try:
+                self.multicast_ptr = int(getattr(self.handle, 'multicast_ptr', 0) or 0)
+            except Exception:
+                self.multicast_ptr = 0
         self.buffer.zero_()
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
@@ -72,6 +87,7 @@ class SymmetricArena:
             a = cls.__new__(cls)
             a.group, a.device, a.capacity, a.buffer, a.handle = None, device, capacity, buffers[r], None
             a.rank, a.world, a.peer_ptrs = r, world, list(ptrs)
+            a.multicast_ptr = 0
             a.peers_dev = torch.tensor(ptrs, dtype=torch.int64, device=device)
             a._cursor = 0
             a._emulated = True
@@ -113,8 +129,20 @@ class SymmetricArena:
         ops.extension().symm_reduce_segments(self.peers_dev, self.rank, self.world, segs, float(scale))
 
     def bcast_segments(self, segs: torch.Tensor):
-        """every peer's [seg] <- local[seg] (push over NVLink)."""
-        ops.extension().symm_bcast_segments(self.peers_dev, self.rank, self.world, segs)
+        """every peer's [seg] <- local[seg] (push over NVLink; one multimem.st per 16 bytes where the
+        buffer has a multicast mapping, one store per peer otherwise)."""
+        ops.extension().symm_bcast_segments(self.peers_dev, self.rank, self.world, segs, self.multicast_ptr)
+
+    def bucket_reduce(self, segs: torch.Tensor, scale: float, blocks: int = 16):
+        """One gradient bucket, one kernel: announce that this rank's part of the bucket is in place,
+        wait (bounded) for all ranks, then ``local[seg] <- scale * sum over ranks of their [seg]`` for
+        the listed segments (``multimem.ld_reduce`` through the switch where available).  Every rank
+        calls it for every bucket, with an empty list if it owns nothing in it; meant for a
+        communication stream (it uses its own barrier slot)."""
+        if getattr(self, '_emulated', False) and self.world > 1:
+            raise RuntimeError('emulated ranks share one GPU and cannot wait for each other')
+        ops.extension().symm_bucket_reduce(self.peers_dev, self.rank, self.world, self.COMM_SLOT, segs, float(scale),
+                                           self.multicast_ptr, int(self.barrier_wait_ms), int(blocks))
 
     def mirror_lower(self, mats: torch.Tensor, n_max: int):
         """For every row (offset, n) of ``mats``: the n x n matrix at ``offset`` of the local buffer

@@ -113,10 +113,19 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             symmetric memory and uses the library's own kernels: the statistics SYRKs store their
             lower-triangular tiles straight into per-rank slots on the owner (peer stores from the
             MMA epilogue; the owner sums its slots into the running factor), owners pull-reduce
-            the gradients of their layers, and the preconditioning GEMM's epilogue stores its
+            the gradients of their layers bucket by bucket while the backward pass is still
+            running (``overlap_grad_reduce``), and the preconditioning GEMM's epilogue stores its
             result into every rank's gradient buffer.  ``'torch'`` uses
             ``torch.distributed`` collectives (any backend).  ``'auto'`` picks ``'symmetric'``
             for multi-rank CUDA runs.
+        overlap_grad_reduce: with ``comm='symmetric'``, reduce the gradients in buckets on a
+            communication stream as the backward pass produces them (asdl/precondition/
+            natural_gradient.py:753-757,814-829 reduce them after the backward pass): a tensor hook
+            per parameter copies its gradient into the symmetric buffer, and when a bucket is
+            complete one kernel on the communication stream exchanges flags with the peers and lets
+            every owner pull the sum of its layers' gradients (``multimem.ld_reduce`` through the
+            NVSwitch where the buffer has a multicast mapping).  The main stream joins the
+            communication stream before preconditioning.  ``bucket_mb``: bucket size in MiB.
     Embedding layers are not handled here; list them in ``config.ignore_modules``.
     """
 
@@ -128,7 +137,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                  loss_type: str = LOSS_CROSS_ENTROPY, scale: float = 1, grad_scale: float = 1,
                  n_mc_samples: int = 1, var: float = 1., seed: int = None,
                  precond_precision: str = 'bf16x3', clone_norm_outputs: bool = False,
-                 cuda_graph: bool = False, comm: str = 'auto', grouped: bool = True, **kwargs):
+                 cuda_graph: bool = False, comm: str = 'auto', grouped: bool = True,
+                 overlap_grad_reduce: bool = True, bucket_mb: float = 16.0, **kwargs):
         super().__init__(model, config, fisher_type=fisher_type, loss_type=loss_type, scale=scale,
                          grad_scale=grad_scale, n_mc_samples=n_mc_samples, var=var, seed=seed, **kwargs)
         self.precond_precision = precond_precision
@@ -161,6 +171,10 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             comm = 'symmetric' if (self.world_size > 1 and device.type == 'cuda') else 'torch'
         self.comm = comm if self.world_size > 1 else 'torch'
         self._arena = None
+        self.overlap_grad_reduce = bool(overlap_grad_reduce)
+        self.bucket_mb = float(bucket_mb)
+        self.comm_blocks = 32          # CTAs of a bucket's pull kernel (it shares the GPU with the backward pass)
+        self._buckets, self._comm_stream, self._reduced_in_backward = [], None, False
         if self.comm == 'symmetric':
             self._setup_symmetric()
         elif self.world_size > 1:
@@ -270,6 +284,20 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                     rest_segs.append((off, p.numel()))
         self._rest_segs = arena.segments(rest_segs)
         self._sym_params = params
+        # gradient buckets in the order the backward pass produces them (last parameters first); a
+        # bucket's table lists the segments this rank owns in it
+        target = max(int(self.bucket_mb * (1 << 20) / 4), 1)
+        self._buckets, cur, cur_numel = [], [], 0
+        for i in reversed(range(len(params))):
+            cur.append(i)
+            cur_numel += params[i].numel()
+            if cur_numel >= target or i == 0:
+                owned = [(self._grad_slot[params[j]][0], params[j].numel()) for j in cur
+                         if owner_of_param.get(params[j], j % self.world_size) == rank]
+                self._buckets.append(dict(params=cur, segs=arena.segments(owned)))
+                cur, cur_numel = [], 0
+        if self.overlap_grad_reduce and self.device.type == 'cuda':
+            self._comm_stream = torch.cuda.Stream(device=self.device)
         self._mirror_n_max = max([r[1] for r in mirror_rows], default=0)
         self._slot_table = torch.tensor(slot_rows, dtype=torch.int64, device=self.device).reshape(-1, 3)
         self._stage_segs = arena.segments(stage_segs)
@@ -290,6 +318,92 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                 p.grad = view
             if moved_dst:
                 torch._foreach_copy_(moved_dst, moved_src)
+
+    # ------------------------------------------------------------------ gradient buckets overlapped with backward
+    def _overlap_active(self):
+        return self._arena is not None and self._comm_stream is not None and self.overlap_grad_reduce
+
+    def _overlap_begin(self, views=None, scale=1.0):
+        """Arms the bucketed reduction for the next backward pass that produces parameter gradients.
+        ``views``: the leaf tensors the model runs on instead of its parameters (graph capture), in the
+        order of ``self._sym_params``.  ``scale``: factor applied to the reduced gradients."""
+        params = self._sym_params
+        st = dict(pending=[len(b['params']) for b in self._buckets], fired=set(), next=0, handles=[],
+                  scale=float(scale))
+
+        def on_view_grad(i, b, grad):
+            with torch.no_grad():
+                self._grad_slot[params[i]][1].copy_(grad)
+            self._bucket_progress(st, i, b)
+
+        def on_param_grad(i, b, param):
+            view = self._grad_slot[param][1]
+            g = param.grad
+            with torch.no_grad():
+                if g is not None and g.data_ptr() != view.data_ptr():
+                    view.copy_(g)
+                elif g is None:
+                    view.zero_()
+            param.grad = view
+            self._bucket_progress(st, i, b)
+
+        for b, bucket in enumerate(self._buckets):
+            for i in bucket['params']:
+                if views is not None:
+                    h = views[i].register_hook(lambda grad, i=i, b=b: on_view_grad(i, b, grad))
+                else:
+                    h = params[i].register_post_accumulate_grad_hook(lambda prm, i=i, b=b: on_param_grad(i, b, prm))
+                st['handles'].append(h)
+        return st
+
+    def _bucket_progress(self, st, i, b):
+        if i in st['fired']:
+            return   # a parameter used twice in the graph reports once per use: the last copy wins
+        st['fired'].add(i)
+        st['pending'][b] -= 1
+        # buckets go out in their fixed order on every rank, so kernel k of one rank meets kernel k of the others
+        while st['next'] < len(self._buckets) and st['pending'][st['next']] == 0:
+            self._launch_bucket(st, st['next'])
+            st['next'] += 1
+
+    def _launch_bucket(self, st, b):
+        current = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(current)
+        self._comm_stream.wait_event(ready)
+        with torch.cuda.stream(self._comm_stream):
+            self._arena.bucket_reduce(self._buckets[b]['segs'], st['scale'] / self.world_size, blocks=self.comm_blocks)
+
+    def _overlap_end(self, st, ok=True):
+        """Removes the hooks; parameters that received no gradient count as zero, the remaining buckets
+        go out, and every ``param.grad`` is the parameter's slot in the symmetric buffer."""
+        for h in st['handles']:
+            h.remove()
+        if not ok:
+            return
+        params = self._sym_params
+        with torch.no_grad():
+            for b in range(st['next'], len(self._buckets)):
+                for i in self._buckets[b]['params']:
+                    if i not in st['fired']:
+                        self._grad_slot[params[i]][1].zero_()
+                        st['fired'].add(i)
+                self._launch_bucket(st, b)
+            st['next'] = len(self._buckets)
+        for prm in params:
+            prm.grad = self._grad_slot[prm][1]
+        self._reduced_in_backward = True
+
+    def backward(self):
+        if not self._overlap_active():
+            return super().backward()
+        st = self._overlap_begin()
+        ok = False
+        try:
+            super().backward()
+            ok = True
+        finally:
+            self._overlap_end(st, ok)
 
     # ------------------------------------------------------------------ CUDA-graph replay
     def _tensor_slots(self):
@@ -379,9 +493,14 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             views = fresh_views()
             with _reparametrize_module(self.model, dict(zip(names, views))):
                 self.forward()
-            grads = torch.autograd.grad(self._loss, views, allow_unused=True)
-            for p, g in zip(self._graph_params, grads):
-                p.grad = g if g is not None else torch.zeros_like(p)
+            if self._overlap_active():
+                st = self._overlap_begin(views)
+                torch.autograd.grad(self._loss, views, allow_unused=True)
+                self._overlap_end(st)
+            else:
+                grads = torch.autograd.grad(self._loss, views, allow_unused=True)
+                for p, g in zip(self._graph_params, grads):
+                    p.grad = g if g is not None else torch.zeros_like(p)
             detach_results()
             self.precondition()
 
@@ -667,13 +786,25 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         if cfg is not None and self.fisher_maker.config.seed is not None:
             torch.random.manual_seed(self.fisher_maker.config.seed)
 
+        overlapped = self._overlap_active()
+
         def backward(loss_, retain=False):
-            if views is None:
-                loss_.backward(retain_graph=retain)
-                return
-            grads = torch.autograd.grad(loss_, views, allow_unused=True, retain_graph=retain)
-            for p, g in zip(self._graph_params, grads):
-                p.grad = g if g is not None else torch.zeros_like(p)
+            # the pass that leaves the loss gradient in param.grad; with the bucketed reduction the
+            # division by the data size is folded into the reduction's scale
+            st = self._overlap_begin(views, scale=1.0 / cfg.data_size) if overlapped else None
+            ok = False
+            try:
+                if views is None:
+                    loss_.backward(retain_graph=retain)
+                else:
+                    grads = torch.autograd.grad(loss_, views, allow_unused=True, retain_graph=retain)
+                    if not overlapped:
+                        for p, g in zip(self._graph_params, grads):
+                            p.grad = g if g is not None else torch.zeros_like(p)
+                ok = True
+            finally:
+                if st is not None:
+                    self._overlap_end(st, ok)
 
         try:
             with nvtx_range('kfac_curvature'), self._phase('curvature'):
@@ -711,7 +842,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                     st.module.curvature_inputs = None
         with torch.no_grad():
             grads = [p.grad for p in model.parameters() if p.grad is not None]
-            if grads:
+            if grads and not overlapped:
                 torch._foreach_div_(grads, cfg.data_size)
             loss = loss.detach().div_(cfg.data_size) if views is not None else loss.div_(cfg.data_size)
         self._loss = loss
@@ -832,9 +963,14 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         GEMM stores into every rank's gradient buffer) -> push the small rest -> barrier."""
         arena = self._arena
         with self._phase('grad_reduce'):
-            self._bind_grads_to_arena()
-            arena.barrier()
-            arena.reduce_segments(self._grad_segs, 1.0 / self.world_size)
+            if self._reduced_in_backward:
+                # the buckets were reduced on the communication stream while the backward pass ran
+                self._reduced_in_backward = False
+                torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
+            else:
+                self._bind_grads_to_arena()
+                arena.barrier()
+                arena.reduce_segments(self._grad_segs, 1.0 / self.world_size)
         with nvtx_range('kfac_precondition'), self._phase('precondition'):
             owned = [st for st in self._kron if st.owner == self.world_rank]
             todo = [st for st in owned if st.has_inv]

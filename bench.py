@@ -4,6 +4,8 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 8 --steps 40 --warmup 5
     python bench.py --impl reference ...      # the unmodified reference package, same workload
+    python bench.py --precision tf32 ...      # this library at the reference's precision (fp32 + TF32)
+    python bench.py --impl reference-autocast # the reference under bf16 autocast (shimmed, see below)
 
 Workload (both arms): torchvision-topology ResNet-50 with random initialisation, synthetic
 N(0,1) images [32, 3, 224, 224] per GPU and uniform labels over 1000 classes, K-FAC with damping
@@ -16,6 +18,19 @@ Two numbers are reported.  ``value`` is timed on the device with CUDA events aro
 steps whose inputs already sit in device memory; ``e2e`` repeats K steps through the same public
 API but copies every step's batch from pinned host memory and reads the loss back to the host.
 One JSON line is printed by rank 0.
+
+Attribution aids (none of them changes the two timed regions):
+  * ``--precision tf32`` runs this library without autocast (fp32 activations, TF32 convolutions and
+    matrix products, statistics from bf16 hi/lo splits): the same precision as the stock reference.
+  * ``--impl reference-autocast`` is a SECOND reference line, never a replacement of the stock
+    one: the reference package under bf16 autocast.  Its hooks cannot consume bf16 activations
+    (its factor products would run in bf16 and its Cholesky rejects bf16), so the two hook entry
+    points of its ``Operation`` class are wrapped here, at run time, to up-cast what they receive
+    to fp32.  Nothing under ``baseline/_ref`` is modified.
+  * ``phases``: after the timed regions single steps of each kind (plain / with curvature / with
+    curvature and inverses) are timed with CUDA events, the maker's step counter being set to a
+    step of that kind through its public ``state``; ``amortised_ms_per_step_100`` is
+    (89 plain + 10 curvature + 1 inverse step) / 100, the figure a 100-step window would show.
 """
 import argparse
 import json
@@ -45,7 +60,10 @@ def parse_args():
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=40)
     ap.add_argument('--warmup', type=int, default=5)
-    ap.add_argument('--impl', choices=['ours', 'reference'], default='ours')
+    ap.add_argument('--impl', choices=['ours', 'reference', 'reference-autocast'], default='ours')
+    ap.add_argument('--precision', choices=['bf16', 'tf32'], default='bf16',
+                    help="compute precision of this library's arm: bf16 autocast (default) or fp32 with TF32")
+    ap.add_argument('--no-phases', action='store_true', help='skip the per-step-kind timing after the timed regions')
     ap.add_argument('--no-graph', action='store_true', help='disable CUDA-graph replay of plain steps')
     ap.add_argument('--nvtx', action='store_true',
                     help="wrap every device-timed step in an NVTX range ('plain_step' / 'curvature_step')")
@@ -139,8 +157,13 @@ def build_ours(args, device, world):
                                      cuda_graph=not args.no_graph)
     opt = torch.optim.SGD(model.parameters(), lr=1e-4, momentum=0.9)
 
+    bf16 = args.precision == 'bf16'
+    if not bf16:
+        torch.backends.cuda.matmul.allow_tf32 = True
+        torch.backends.cudnn.allow_tf32 = True
+
     def model_fn(x):
-        with torch.autocast('cuda', dtype=torch.bfloat16):
+        with torch.autocast('cuda', dtype=torch.bfloat16, enabled=bf16):
             return model(x)
 
     def step(x, t):
@@ -158,7 +181,7 @@ def build_ours(args, device, world):
         return (x.to(device, non_blocking=True).contiguous(memory_format=torch.channels_last),
                 t.to(device, non_blocking=True))
 
-    return step, launches, to_device, 'bf16'
+    return step, launches, to_device, ('bf16' if bf16 else 'fp32 (tf32 matmul/conv)'), gm
 
 
 def build_reference(args, device, world):
@@ -180,10 +203,39 @@ def build_reference(args, device, world):
                                         curvature_upd_interval=10, preconditioner_upd_interval=100)
     gm = asdl.KfacGradientMaker(model, config)
     opt = torch.optim.SGD(model.parameters(), lr=1e-4, momentum=0.9)
+    autocast = args.impl == 'reference-autocast'
+    if autocast:
+        # second reference line: bf16 autocast, with the tensors that reach the reference's hooks
+        # up-cast to fp32 (wrappers installed here; the package itself stays as it is)
+        from asdl.operations.operation import Operation
+
+        def upcast(v):
+            if isinstance(v, torch.Tensor) and v.dtype in (torch.bfloat16, torch.float16):
+                return v.float()
+            if isinstance(v, (tuple, list)):
+                return type(v)(upcast(e) for e in v)
+            return v
+
+        fwd, bwd = Operation.forward_post_process, Operation.backward_pre_process
+
+        def forward_post_process(self, in_data, out_data):
+            with torch.autocast('cuda', enabled=False):
+                return fwd(self, upcast(in_data), upcast(out_data))
+
+        def backward_pre_process(self, out_grads, vector=None):
+            with torch.autocast('cuda', enabled=False):
+                return bwd(self, upcast(out_grads), vector)
+
+        Operation.forward_post_process = forward_post_process
+        Operation.backward_pre_process = backward_pre_process
+
+    def model_fn(x):
+        with torch.autocast('cuda', dtype=torch.bfloat16, enabled=autocast):
+            return model(x)
 
     def step(x, t):
         opt.zero_grad(set_to_none=True)
-        dummy = gm.setup_model_call(model, x)
+        dummy = gm.setup_model_call(model_fn, x)
         gm.setup_loss_call(F.cross_entropy, dummy, t)
         _, loss = gm.forward_and_backward()
         opt.step()
@@ -192,7 +244,33 @@ def build_reference(args, device, world):
     def to_device(x, t):
         return x.to(device, non_blocking=True), t.to(device, non_blocking=True)
 
-    return step, (lambda: 0), to_device, 'fp32 (tf32 matmul/conv)'
+    dtype = 'bf16 autocast, hook tensors up-cast to fp32 (second reference line)' if autocast \
+        else 'fp32 (tf32 matmul/conv)'
+    return step, (lambda: 0), to_device, dtype, gm
+
+
+def measure_phases(step, gm, dev_batches, flush):
+    """Device time of one step of each kind, measured after the timed regions.  The step kind is
+    chosen by setting the maker's step counter (curvature every 10 steps, inverses every 100)."""
+    def timed(step_index):
+        gm.state['step'] = step_index
+        flush.zero_()
+        x, t = dev_batches[step_index % len(dev_batches)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step(x, t)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    saved = gm.state['step']
+    plain = statistics.median(timed(1001 + i) for i in range(7))
+    curvature = statistics.median(timed(1010 + 10 * i) for i in range(3))
+    update = statistics.median(timed(1100 + 100 * i) for i in range(2))
+    gm.state['step'] = saved
+    return {'plain_ms': round(plain, 3), 'curvature_ms': round(curvature, 3), 'update_ms': round(update, 3),
+            'amortised_ms_per_step_100': round((89 * plain + 10 * curvature + update) / 100, 3),
+            'how': 'CUDA events around single steps after the timed regions; medians of 7 / 3 / 2 steps'}
 
 
 def barrier(world):
@@ -204,16 +282,16 @@ def barrier(world):
 def main():
     args = parse_args()
     args.warmup = max(args.warmup, 3)  # the step graphs are captured at the second step
-    if args.impl == 'reference' and not os.path.isdir(os.path.join(ROOT, 'baseline', '_ref', 'asdl')):
+    if args.impl != 'ours' and not os.path.isdir(os.path.join(ROOT, 'baseline', '_ref', 'asdl')):
         if int(os.environ.get('RANK', '0')) == 0:
-            print(json.dumps({'impl': 'reference',
+            print(json.dumps({'impl': args.impl,
                               'unavailable': 'reference package not installed under baseline/_ref'}))
         return
     rank, local, world = init_distributed(args.gpus)
     device = torch.device('cuda', local)
     torch.backends.cudnn.benchmark = True  # both arms: fixed shapes, let cuDNN pick its kernels once
     build = build_ours if args.impl == 'ours' else build_reference
-    step, launches, to_device, dtype = build(args, device, world)
+    step, launches, to_device, dtype, gm = build(args, device, world)
 
     n_host = 8
     xs, ts = make_batches(n_host, device, seed=1234 + rank, channels_last=args.impl == 'ours')
@@ -288,6 +366,10 @@ def main():
     barrier(world)
     e2e_s = time.perf_counter() - t0
 
+    phases = None
+    if not args.no_phases:
+        phases = measure_phases(step, gm, dev_batches, flush)
+        barrier(world)
     if args.impl == 'ours':  # a kernel that gave up on a wait (peer barrier, pipeline stage) reports it here
         import asdl_b200
         asdl_b200.ops.check_status()
@@ -317,6 +399,7 @@ def main():
                     'last_loss': last},
             'gpu_launches': int(n_launch),
             'clocks': clocks,
+            'phases': phases,
         }
         print(json.dumps(out), flush=True)
     if world > 1:
