@@ -7,6 +7,9 @@ void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, b
                c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo, int64_t nsplit,
                c10::optional<at::Tensor> out_mid, bool split3);
 void set_gemm_wide(int64_t mode);
+void gemm_batch_begin();
+int64_t gemm_batch_end();
+void gemm_batch_abort();
 int64_t read_status(int64_t dev);
 int64_t launch_count();
 void reserve_scratch(int64_t dev, int64_t nfloats);
@@ -64,6 +67,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("alpha"), py::arg("beta"), py::arg("sym"), py::arg("out_hi"), py::arg("out_lo"),
         py::arg("nsplit"), py::arg("out_mid") = py::none(), py::arg("split3") = false);
   m.def("set_gemm_wide", &b200::set_gemm_wide);
+  m.def("gemm_batch_begin", &b200::gemm_batch_begin);
+  m.def("gemm_batch_end", &b200::gemm_batch_end);
+  m.def("gemm_batch_abort", &b200::gemm_batch_abort);
   m.def("read_status", &b200::read_status);
   m.def("launch_count", &b200::launch_count);
   m.def("reserve_scratch", &b200::reserve_scratch);

@@ -20,13 +20,14 @@ void g2_encode_operand(CUtensorMap* tm, const void* base, int64_t mn, int64_t k,
 int g2_sm_count(int dev);
 
 // One launch of a kernel flavour: either `single` (work == nullptr; its tiles are decoded from the
-// work index) or a device-resident problem table with a work list.  Defined in gemm2_<flavour>.cu.
+// work index), a device-resident problem table with a work list, or such a table with an item
+// prefix per problem (`prefix`, `n_probs` <= G2_MAX_BATCH; `work` null).  Defined in gemm2_<flavour>.cu.
 void g2_run_plain(const GemmProblem2& single, const GemmProblem2* probs, const GemmWork2* work, int n_work,
-                  int n_sms, cudaStream_t stream);
+                  int n_sms, cudaStream_t stream, const int* prefix = nullptr, int n_probs = 0);
 void g2_run_wide(const GemmProblem2& single, const GemmProblem2* probs, const GemmWork2* work, int n_work,
-                 int n_sms, cudaStream_t stream);
+                 int n_sms, cudaStream_t stream, const int* prefix = nullptr, int n_probs = 0);
 void g2_run_split3(const GemmProblem2& single, const GemmProblem2* probs, const GemmWork2* work, int n_work,
-                   int n_sms, cudaStream_t stream);
+                   int n_sms, cudaStream_t stream, const int* prefix = nullptr, int n_probs = 0);
 
 // Runs `n_work` work items of a device-resident problem table on `stream`.
 void g2_launch_list(const GemmProblem2* d_probs, const GemmWork2* d_work, int n_work, G2Flavour flavour,

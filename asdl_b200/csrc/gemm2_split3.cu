@@ -7,7 +7,7 @@
 namespace b200 {
 
 void g2_run_split3(const GemmProblem2& single, const GemmProblem2* probs, const GemmWork2* work, int n_work,
-                  int n_sms, cudaStream_t stream) {
+                  int n_sms, cudaStream_t stream, const int* prefix, int n_probs) {
   if (n_work <= 0) return;
   static bool attr_set_on[64] = {false};
   int dev = 0;
@@ -19,7 +19,7 @@ void g2_run_split3(const GemmProblem2& single, const GemmProblem2* probs, const 
     attr_set = true;
   }
   const int grid = std::min(n_work, 1 * n_sms);
-  umma_gemm2_kernel<128, 8, 1, true><<<grid, G2Split3::THREADS, G2Split3::SMEM_BYTES, stream>>>(single, probs, work, n_work);
+  umma_gemm2_kernel<128, 8, 1, true><<<grid, G2Split3::THREADS, G2Split3::SMEM_BYTES, stream>>>(single, probs, work, n_work, prefix, n_probs);
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch();
 }

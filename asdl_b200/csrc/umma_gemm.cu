@@ -84,9 +84,9 @@ void g2_launch_reduce_list(const GemmProblem2* d_probs, const GemmWork2* d_work,
   GemmProblem2 dummy;
   std::memset(&dummy, 0, sizeof(dummy));
   if (wide)
-    splitk_reduce2_kernel<256><<<dim3(n_work, 32, 1), 256, 0, stream>>>(dummy, d_probs, d_work);
+    splitk_reduce2_kernel<256><<<dim3(n_work, 32, 1), 256, 0, stream>>>(dummy, d_probs, d_work, nullptr, 0);
   else
-    splitk_reduce2_kernel<128><<<dim3(n_work, 16, 1), 256, 0, stream>>>(dummy, d_probs, d_work);
+    splitk_reduce2_kernel<128><<<dim3(n_work, 16, 1), 256, 0, stream>>>(dummy, d_probs, d_work, nullptr, 0);
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch();
 }
@@ -226,12 +226,171 @@ void gemm_launch_single(const GemmProblem2& P, int dev, cudaStream_t stream) {
     g2_run_plain(P, nullptr, nullptr, n_work, n_sms, stream);
   if (needs_ws(P)) {
     if (wide)
-      splitk_reduce2_kernel<256><<<dim3(P.ntiles, 32, 1), 256, 0, stream>>>(P, nullptr, nullptr);
+      splitk_reduce2_kernel<256><<<dim3(P.ntiles, 32, 1), 256, 0, stream>>>(P, nullptr, nullptr, nullptr, 0);
     else
-      splitk_reduce2_kernel<128><<<dim3(P.ntiles, 16, 1), 256, 0, stream>>>(P, nullptr, nullptr);
+      splitk_reduce2_kernel<128><<<dim3(P.ntiles, 16, 1), 256, 0, stream>>>(P, nullptr, nullptr, nullptr, 0);
     B200_CUDA_CHECK(cudaGetLastError());
     count_launch();
   }
+}
+
+// ---- deferred batches ------------------------------------------------------------------------------
+// Between gemm_batch_begin() and gemm_batch_end() the plain single-problem entry points do not launch:
+// they record their problem (and keep its operands alive).  gemm_batch_end() runs everything recorded
+// as ONE persistent launch (plus one split-K reduction launch).  The statistics products of a K-FAC
+// curvature pass - about a hundred products whose tile counts range from 1 to 666 - fill the GPU
+// together instead of one after the other.  The problem table reaches the device through kernel
+// parameters (a few launches of a copy kernel with a 28 KiB argument), not through a host-to-device
+// copy: parameters are captured by value, so a CUDA graph that contains a batch replays without
+// referring to host memory.
+struct GemmBatch {
+  bool active = false;
+  int dev = 0;
+  std::vector<GemmProblem2> problems;
+  std::vector<int> nsplit_req;
+  std::vector<at::Tensor> keep_alive;
+};
+static GemmBatch g_batch;
+
+constexpr int kTableChunk = 28 * 1024;
+struct TableChunk {
+  unsigned char bytes[kTableChunk];
+};
+
+__global__ void table_write_kernel(const __grid_constant__ TableChunk chunk, unsigned char* dst, int nbytes) {
+  const int n16 = nbytes >> 4;   // nbytes and dst are multiples of 16
+  const uint4* src = reinterpret_cast<const uint4*>(chunk.bytes);
+  for (int i = threadIdx.x; i < n16; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = src[i];
+}
+
+static void batch_flush(cudaStream_t stream) {
+  GemmBatch& B = g_batch;
+  if (B.problems.empty()) return;
+  c10::cuda::CUDAGuard guard(B.dev);
+  DeviceState& st = device_state(B.dev);
+  const int n_sms = g2_sm_count(B.dev);
+  // split-K per problem: the batch fills the machine, so a split only has to cut very long contractions
+  // into pieces of comparable length
+  size_t ws_floats = 0;
+  for (size_t i = 0; i < B.problems.size(); ++i) {
+    GemmProblem2& P = B.problems[i];
+    const int kb_total = (P.K + G2_BK - 1) / G2_BK;
+    int nsplit = B.nsplit_req[i];
+    if (nsplit <= 0) nsplit = std::min(32, std::max(1, kb_total / 48));
+    nsplit = std::max(1, std::min(nsplit, kb_total));
+    P.nsplit = nsplit;
+    P.status = st.status.data_ptr<int>();
+    if (needs_ws(P)) ws_floats += static_cast<size_t>(P.ntiles) * P.nsplit * G2_BM * 128;
+  }
+  // expensive items first
+  std::vector<int> order(B.problems.size());
+  for (size_t i = 0; i < order.size(); ++i) order[i] = static_cast<int>(i);
+  auto item_cost = [&](int i) {
+    const GemmProblem2& P = B.problems[i];
+    return static_cast<long long>(P.nseg) * ((P.K + G2_BK - 1) / G2_BK) / P.nsplit;
+  };
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return item_cost(a) > item_cost(b); });
+  at::Tensor scratch;
+  if (ws_floats > 0)
+    scratch = at::empty({static_cast<int64_t>(ws_floats)}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, B.dev));
+  size_t ws_off = 0;
+  for (size_t begin = 0; begin < order.size(); begin += G2_MAX_BATCH) {
+    const int n = static_cast<int>(std::min<size_t>(G2_MAX_BATCH, order.size() - begin));
+    // table: [problems][item prefix (n + 1)][reduction tile prefix (n + 1)], 16-byte granular
+    const size_t probs_bytes = static_cast<size_t>(n) * sizeof(GemmProblem2);
+    const size_t prefix_bytes = ((static_cast<size_t>(n) + 1) * sizeof(int) + 15) / 16 * 16;
+    const size_t total = probs_bytes + 2 * prefix_bytes;
+    std::vector<unsigned char> host(total, 0);
+    GemmProblem2* hp = reinterpret_cast<GemmProblem2*>(host.data());
+    int* prefix = reinterpret_cast<int*>(host.data() + probs_bytes);
+    int* rprefix = reinterpret_cast<int*>(host.data() + probs_bytes + prefix_bytes);
+    int items = 0, rtiles = 0;
+    for (int j = 0; j < n; ++j) {
+      GemmProblem2 P = B.problems[order[begin + j]];
+      if (needs_ws(P)) {
+        P.ws = scratch.data_ptr<float>() + ws_off;
+        ws_off += static_cast<size_t>(P.ntiles) * P.nsplit * G2_BM * 128;
+      }
+      hp[j] = P;
+      prefix[j] = items;
+      rprefix[j] = rtiles;
+      items += P.ntiles * P.nsplit;
+      if (needs_ws(P)) rtiles += P.ntiles;
+    }
+    prefix[n] = items;
+    rprefix[n] = rtiles;
+    at::Tensor table = at::empty({static_cast<int64_t>(total)}, at::TensorOptions().dtype(at::kByte).device(at::kCUDA, B.dev));
+    unsigned char* d = table.data_ptr<unsigned char>();
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(d) & 63) == 0, "problem table is not 64-byte aligned");
+    for (size_t off = 0; off < total; off += kTableChunk) {
+      TableChunk chunk;
+      const int nbytes = static_cast<int>(std::min<size_t>(kTableChunk, total - off));
+      std::memcpy(chunk.bytes, host.data() + off, nbytes);
+      table_write_kernel<<<1, 256, 0, stream>>>(chunk, d + off, nbytes);
+      B200_CUDA_CHECK(cudaGetLastError());
+      count_launch();
+    }
+    GemmProblem2 dummy;
+    std::memset(&dummy, 0, sizeof(dummy));
+    const GemmProblem2* dp = reinterpret_cast<const GemmProblem2*>(d);
+    g2_run_plain(dummy, dp, nullptr, items, n_sms, stream, reinterpret_cast<const int*>(d + probs_bytes), n);
+    if (rtiles > 0) {
+      splitk_reduce2_kernel<128><<<dim3(rtiles, 16, 1), 256, 0, stream>>>(
+          dummy, dp, nullptr, reinterpret_cast<const int*>(d + probs_bytes + prefix_bytes), n);
+      B200_CUDA_CHECK(cudaGetLastError());
+      count_launch();
+    }
+  }
+  B.problems.clear();
+  B.nsplit_req.clear();
+  B.keep_alive.clear();
+}
+
+// Records `P` in the open batch.  Returns false when no batch is open (the caller launches itself).
+static bool batch_append(GemmProblem2& P, int dev, int64_t nsplit_req, cudaStream_t stream,
+                         const std::vector<at::Tensor>& a_segs, const std::vector<at::Tensor>& b_segs,
+                         const c10::optional<at::Tensor>& C) {
+  GemmBatch& B = g_batch;
+  if (!B.active || (P.flags & (G2F_WIDE | G2F_SPLIT3))) return false;
+  if (!B.problems.empty() && B.dev != dev) batch_flush(stream);
+  // two products into one output (a further backward pass adding to a factor) must not share a launch
+  for (const GemmProblem2& Q : B.problems)
+    if (Q.C != nullptr && Q.C == P.C) {
+      batch_flush(stream);
+      break;
+    }
+  B.dev = dev;
+  B.problems.push_back(P);
+  B.nsplit_req.push_back(static_cast<int>(nsplit_req));
+  B.keep_alive.insert(B.keep_alive.end(), a_segs.begin(), a_segs.end());
+  B.keep_alive.insert(B.keep_alive.end(), b_segs.begin(), b_segs.end());
+  if (C.has_value()) B.keep_alive.push_back(*C);
+  return true;
+}
+
+void gemm_batch_begin() {
+  TORCH_CHECK(!g_batch.active, "a GEMM batch is already open");
+  g_batch.active = true;
+}
+
+// Launches what was recorded since gemm_batch_begin() on the current stream; returns the number of products.
+int64_t gemm_batch_end() {
+  TORCH_CHECK(g_batch.active, "no GEMM batch is open");
+  g_batch.active = false;
+  const int64_t n = static_cast<int64_t>(g_batch.problems.size());
+  if (n > 0) {
+    c10::cuda::CUDAGuard guard(g_batch.dev);
+    batch_flush(at::cuda::getCurrentCUDAStream(g_batch.dev).stream());
+  }
+  return n;
+}
+
+// Drops an open batch without launching it (error paths).
+void gemm_batch_abort() {
+  g_batch.active = false;
+  g_batch.problems.clear();
+  g_batch.nsplit_req.clear();
+  g_batch.keep_alive.clear();
 }
 
 // Python entry: C = alpha * A^T B (+ beta C), optionally symmetric, optionally bf16 split outputs.
@@ -248,8 +407,10 @@ void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, b
   gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, C, alpha, beta, sym, out_hi, out_mid, out_lo,
                     nsplit, split3, g2_sm_count(dev));
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
-  gemm_attach_scratch(P, dev, stream);
-  gemm_launch_single(P, dev, stream);
+  if (out_hi.has_value() || !batch_append(P, dev, nsplit, stream, a_segs, b_segs, C)) {
+    gemm_attach_scratch(P, dev, stream);
+    gemm_launch_single(P, dev, stream);
+  }
 }
 
 // Variant whose fp32 result goes to raw device addresses - typically symmetric-memory buffers of
@@ -284,8 +445,10 @@ void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_
     P.C_extra[e] = reinterpret_cast<float*>(extra_ptrs[e]);
   }
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
-  gemm_attach_scratch(P, dev, stream);
-  gemm_launch_single(P, dev, stream);
+  if (!batch_append(P, dev, nsplit, stream, a_segs, b_segs, c10::nullopt)) {
+    gemm_attach_scratch(P, dev, stream);
+    gemm_launch_single(P, dev, stream);
+  }
 }
 
 // ---- grouped execution ---------------------------------------------------------------------------

@@ -41,6 +41,7 @@ constexpr int G2_BM = 128;
 constexpr int G2_BK = 64;
 constexpr int G2_MAX_SEG = 6;
 constexpr int G2_MAX_EXTRA = 7;
+constexpr int G2_MAX_BATCH = 256;   // problems of one launch in batch mode
 constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;  // 16 KiB
 
 template <int BN, int EPI_WARPS, int MINB, bool SPLIT3>
@@ -50,7 +51,8 @@ struct G2Cfg {
   static constexpr int STAGE_BYTES = SPLIT3 ? 3 * (G2_A_BYTES + B_BYTES) : G2_A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ +
+                                    4 * (G2_MAX_BATCH + 4) /*item prefix of a batch*/;
 };
 using G2Plain = G2Cfg<128, 4, 2, false>;
 using G2Wide = G2Cfg<256, 8, 1, false>;
@@ -171,6 +173,36 @@ __device__ __forceinline__ GemmWork2 g2_decode(const GemmProblem2& P, int idx) {
   w.wflags = 0;
   w.pad = 0;
   return w;
+}
+
+// Work item `wi` of a launch, in any of the three ways a launch describes its work:
+//   * a work list (plans, the Cholesky steps): item wi is work[wi];
+//   * a batch of problems without a list: prefix[p] is the first item of problem p (prefix has
+//     n_probs + 1 entries and sits in shared memory); the item is decoded like a single problem's;
+//   * one problem passed by value.
+template <int BN>
+__device__ __forceinline__ const GemmProblem2* g2_item(const GemmProblem2& single, const GemmProblem2* probs,
+                                                       const GemmWork2* work, const int* prefix, int n_probs,
+                                                       int wi, GemmWork2& w) {
+  if (work != nullptr) {
+    w = work[wi];
+    return probs + w.problem;
+  }
+  if (probs != nullptr) {
+    int lo = 0, hi = n_probs;   // largest p with prefix[p] <= wi
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (prefix[mid] <= wi)
+        lo = mid;
+      else
+        hi = mid;
+    }
+    w = g2_decode<BN>(probs[lo], wi - prefix[lo]);
+    w.problem = lo;
+    return probs + lo;
+  }
+  w = g2_decode<BN>(single, wi);
+  return &single;
 }
 
 __device__ __forceinline__ void g2_red_add_f32(float* p, float v) {
@@ -375,7 +407,7 @@ __device__ __forceinline__ void g2_store_chunk(const G2Epi& P, const float* v, i
 template <int BN, int EPI_WARPS, int MINB, bool SPLIT3>
 __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, MINB)
 umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem2* __restrict__ probs,
-                  const GemmWork2* __restrict__ work, int n_work) {
+                  const GemmWork2* __restrict__ work, int n_work, const int* __restrict__ prefix_g, int n_probs) {
   using Cfg = G2Cfg<BN, EPI_WARPS, MINB, SPLIT3>;
   constexpr int STAGES = Cfg::STAGES;
   static_assert(!SPLIT3 || (BN == 128 && EPI_WARPS == 8), "the split3 flavour runs 128-wide tiles with 8 epilogue warps");
@@ -388,9 +420,12 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  int* prefix = reinterpret_cast<int*>(smem + STAGES * Cfg::STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (prefix_g != nullptr)
+    for (int i = threadIdx.x; i <= n_probs && i <= G2_MAX_BATCH; i += blockDim.x) prefix[i] = prefix_g[i];
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -418,8 +453,8 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
       uint32_t it = 0;
       bool ok = true;
       for (int wi = blockIdx.x; wi < n_work && ok; wi += gridDim.x) {
-        const GemmWork2 w = (work != nullptr) ? work[wi] : g2_decode<BN>(single, wi);
-        const GemmProblem2& P = (work != nullptr) ? probs[w.problem] : single;
+        GemmWork2 w;
+        const GemmProblem2& P = *g2_item<BN>(single, probs, work, prefix, n_probs, wi, w);
         const bool a_k = (P.flags & G2F_A_KMAJOR) != 0;
         const bool b_k = (P.flags & G2F_B_KMAJOR) != 0;
         const bool shared_ab = !SPLIT3 && BN == 128 && (P.flags & G2F_SAME_AB) && w.a_mn == w.b_mn &&
@@ -479,8 +514,8 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
       uint32_t it = 0, ch = 0;
       bool ok = true;
       for (int wi = blockIdx.x; wi < n_work && ok; wi += gridDim.x) {
-        const GemmWork2 w = (work != nullptr) ? work[wi] : g2_decode<BN>(single, wi);
-        const GemmProblem2& P = (work != nullptr) ? probs[w.problem] : single;
+        GemmWork2 w;
+        const GemmProblem2& P = *g2_item<BN>(single, probs, work, prefix, n_probs, wi, w);
         const bool a_k = (P.flags & G2F_A_KMAJOR) != 0;
         const bool b_k = (P.flags & G2F_B_KMAJOR) != 0;
         const bool shared_ab = !SPLIT3 && BN == 128 && (P.flags & G2F_SAME_AB) && w.a_mn == w.b_mn &&
@@ -573,8 +608,8 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
     uint32_t ch = 0;
     bool ok = true;
     for (int wi = blockIdx.x; wi < n_work && ok; wi += gridDim.x) {
-      const GemmWork2 w = (work != nullptr) ? work[wi] : g2_decode<BN>(single, wi);
-      const GemmProblem2& Pg = (work != nullptr) ? probs[w.problem] : single;
+      GemmWork2 w;
+      const GemmProblem2& Pg = *g2_item<BN>(single, probs, work, prefix, n_probs, wi, w);
       const G2Epi P = g2_epi(Pg);
       int* const status = Pg.status;
       const int nchunks = SPLIT3 ? w.nkb : (w.nkb > 0 ? 1 : 0);
@@ -690,13 +725,25 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
 template <int BN>
 __global__ void __launch_bounds__(256)
 splitk_reduce2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem2* __restrict__ probs,
-                      const GemmWork2* __restrict__ work) {
+                      const GemmWork2* __restrict__ work, const int* __restrict__ tile_prefix, int n_probs) {
   __shared__ float tile[32][33];
   GemmWork2 w;
   const GemmProblem2* Pp;
   if (work != nullptr) {
     w = work[blockIdx.x];
     Pp = probs + w.problem;
+  } else if (probs != nullptr) {
+    // batch mode: tile_prefix[p] is the first tile (over the problems that were split) of problem p
+    int lo = 0, hi = n_probs;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (tile_prefix[mid] <= static_cast<int>(blockIdx.x))
+        lo = mid;
+      else
+        hi = mid;
+    }
+    Pp = probs + lo;
+    w = g2_decode<BN>(*Pp, (static_cast<int>(blockIdx.x) - tile_prefix[lo]) * Pp->nsplit);
   } else {
     w = g2_decode<BN>(single, blockIdx.x * single.nsplit);
     Pp = &single;

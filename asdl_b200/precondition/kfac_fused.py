@@ -118,6 +118,11 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             result into every rank's gradient buffer.  ``'torch'`` uses
             ``torch.distributed`` collectives (any backend).  ``'auto'`` picks ``'symmetric'``
             for multi-rank CUDA runs.
+        batch_statistics: record the statistics products of a curvature pass (one per Kronecker
+            factor, asdl/operations/linear.py:77,89 and conv.py:80-103) and run them as ONE
+            persistent tcgen05 launch after the backward pass instead of one launch per factor; the
+            layer inputs and output gradients are kept alive until then.  Switch it off for models
+            that modify a layer's input in place after the layer has run.
         overlap_grad_reduce: with ``comm='symmetric'``, reduce the gradients in buckets on a
             communication stream as the backward pass produces them (asdl/precondition/
             natural_gradient.py:753-757,814-829 reduce them after the backward pass): a tensor hook
@@ -138,7 +143,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                  n_mc_samples: int = 1, var: float = 1., seed: int = None,
                  precond_precision: str = 'bf16x3', clone_norm_outputs: bool = False,
                  cuda_graph: bool = False, comm: str = 'auto', grouped: bool = True,
-                 overlap_grad_reduce: bool = True, bucket_mb: float = 16.0, **kwargs):
+                 overlap_grad_reduce: bool = True, bucket_mb: float = 16.0, batch_statistics: bool = True,
+                 **kwargs):
         super().__init__(model, config, fisher_type=fisher_type, loss_type=loss_type, scale=scale,
                          grad_scale=grad_scale, n_mc_samples=n_mc_samples, var=var, seed=seed, **kwargs)
         self.precond_precision = precond_precision
@@ -172,6 +178,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         self.comm = comm if self.world_size > 1 else 'torch'
         self._arena = None
         self.overlap_grad_reduce = bool(overlap_grad_reduce)
+        self.batch_statistics = bool(batch_statistics)
         self.bucket_mb = float(bucket_mb)
         self.comm_blocks = 32          # CTAs of a bucket's pull kernel (it shares the GPU with the backward pass)
         self._buckets, self._comm_stream, self._reduced_in_backward = [], None, False
@@ -806,6 +813,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                 if st is not None:
                     self._overlap_end(st, ok)
 
+        batched = (self.batch_statistics and self.device.type == 'cuda' and ops.get_backend() != 'torch')
+        if batched:
+            ops.extension().gemm_batch_begin()
         try:
             with nvtx_range('kfac_curvature'), self._phase('curvature'):
                 if views is None:
@@ -832,7 +842,12 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                                                 retain_graph=True, allow_unused=True)
                     state['on'] = False
                     backward(loss)
+                if batched:   # every statistics product of the pass in one launch
+                    batched = False
+                    ops.extension().gemm_batch_end()
         finally:
+            if batched:
+                ops.extension().gemm_batch_abort()
             state['on'] = False
             for h in handles:
                 h.remove()

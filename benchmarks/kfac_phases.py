@@ -58,6 +58,8 @@ def main():
     ap.add_argument('--warmup', type=int, default=12)
     ap.add_argument('--no-overlap', action='store_true',
                     help='reduce the gradients after the backward pass instead of bucket by bucket during it')
+    ap.add_argument('--bucket-mb', type=float, default=16.0, help='size of a gradient bucket of the overlapped reduction')
+    ap.add_argument('--comm-blocks', type=int, default=None, help='CTAs of a bucket kernel')
     ap.add_argument('--impl', choices=['ours', 'reference'], default='ours')
     args = ap.parse_args()
     if args.impl == 'reference':
@@ -74,7 +76,9 @@ def main():
                                      preconditioner_upd_interval=30)
     gm = asdl.FusedKfacGradientMaker(model, cfg, cuda_graph=not args.no_graph,
                                      precond_precision=args.precond_precision,
-                                     overlap_grad_reduce=not args.no_overlap)
+                                     overlap_grad_reduce=not args.no_overlap, bucket_mb=args.bucket_mb)
+    if args.comm_blocks:
+        gm.comm_blocks = args.comm_blocks
     opt = torch.optim.SGD(model.parameters(), lr=1e-4, momentum=0.9)
     x = torch.randn(32, 3, 224, 224, device=dev).contiguous(memory_format=torch.channels_last)
     t = torch.randint(0, 1000, (32,), device=dev)
@@ -98,7 +102,8 @@ def main():
     phases = gm.phase_times()
     if local == 0:
         print(json.dumps({'case': 'resnet50_kfac_phases', 'n_gpus': world, 'cuda_graph': not args.no_graph,
-                          'precond_precision': args.precond_precision,
+                          'precond_precision': args.precond_precision, 'overlap': not args.no_overlap,
+                          'bucket_mb': args.bucket_mb, 'comm_blocks': gm.comm_blocks,
                           'phases_ms': {k: [n, round(ms, 3)] for k, (n, ms) in phases.items()}}), flush=True)
     asdl.ops.check_status()
     if world > 1:
