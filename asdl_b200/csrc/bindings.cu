@@ -59,6 +59,14 @@ void symm_reduce_slots(at::Tensor local, at::Tensor table, int64_t world, int64_
 void chol_inverse(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs, at::Tensor damping);
 void chol_inverse_tc(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs, at::Tensor damping);
 void chol_inverse_tc_clear_cache();
+std::vector<at::Tensor> jacobi_eigh(at::Tensor mats, bool want_vectors);
+void ln_unitwise_stats(at::Tensor y, at::Tensor g, at::Tensor weight, at::Tensor bias, at::Tensor stats, double alpha,
+                       double beta);
+void unitwise_inverse_mt(std::vector<std::vector<int64_t>> rows, double damping);
+void unitwise_apply_mt(std::vector<std::vector<int64_t>> rows, double grad_scale);
+void bias_precondition_mt(std::vector<std::vector<int64_t>> rows, double grad_scale);
+void diag_linear_stats(at::Tensor a, at::Tensor g, at::Tensor out, c10::optional<at::Tensor> out_bias, double alpha,
+                       double beta);
 }  // namespace b200
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -105,4 +113,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("chol_inverse", &b200::chol_inverse, "grouped damped SPD inverse (fp32, CUDA cores)");
   m.def("chol_inverse_tc", &b200::chol_inverse_tc, "grouped damped SPD inverse (fp32-accurate, tensor cores)");
   m.def("chol_inverse_tc_clear_cache", &b200::chol_inverse_tc_clear_cache);
+  m.def("jacobi_eigh", &b200::jacobi_eigh, "batched symmetric eigendecomposition, n <= 128 (parallel cyclic Jacobi)");
+  m.def("ln_unitwise_stats", &b200::ln_unitwise_stats);
+  m.def("unitwise_inverse_mt", &b200::unitwise_inverse_mt);
+  m.def("unitwise_apply_mt", &b200::unitwise_apply_mt);
+  m.def("bias_precondition_mt", &b200::bias_precondition_mt);
+  m.def("diag_linear_stats", &b200::diag_linear_stats);
 }

@@ -149,7 +149,10 @@ __global__ void symm_bcast_segments_kernel(const long long* peers, int rank, int
 // of the last completed call, [slot*64 + 62] count of blocks that finished the current call.  The
 // epoch word only changes when the last block of a call retires, so every block of a call reads
 // the same value at its start and no per-call host argument is needed (CUDA-graph replay).
-__global__ void symm_bucket_reduce_kernel(const long long* peers, int rank, int world, int slot,
+constexpr int BUCKET_UNROLL = 8;
+constexpr int BUCKET_THREADS = 128;
+
+__global__ void __launch_bounds__(BUCKET_THREADS) symm_bucket_reduce_kernel(const long long* peers, int rank, int world, int slot,
                                           const Seg* segs, int nsegs, float scale, const float* mc_base,
                                           unsigned long long wait_ns, int* status) {
   uint32_t* flags = reinterpret_cast<uint32_t*>(peers[rank]) + slot * 64;
@@ -174,30 +177,56 @@ __global__ void symm_bucket_reduce_kernel(const long long* peers, int rank, int 
   }
   __syncthreads();
   if (s_ok) {
+    const float* peer[8];
+    const int wcap = world < 8 ? world : 8;
+    for (int r = 0; r < wcap; ++r) peer[r] = reinterpret_cast<const float*>(peers[r]);
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (int sidx = 0; sidx < nsegs; ++sidx) {
       const Seg s = segs[sidx];
       float* local = reinterpret_cast<float*>(peers[rank]) + s.off;
       const long long n4 = s.numel >> 2;
-      for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
-           i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        float4 acc;
-        if (mc_base != nullptr) {
-          acc = multimem_ld_reduce_f4(mc_base + s.off + 4 * i);
-        } else {
-          acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int r = 0; r < world; ++r) {
-            const float4 v = ld_peer_f4(reinterpret_cast<const float*>(peers[r]) + s.off + 4 * i);
-            acc.x += v.x;
-            acc.y += v.y;
-            acc.z += v.z;
-            acc.w += v.w;
+      // BUCKET_UNROLL independent 16-byte transactions per thread and trip: the pull is bound by the
+      // latency of the link, so the number of loads in flight sets its speed.  The blocks are small
+      // (128 threads) on purpose: while a block waits for a peer it stays resident next to the
+      // kernels of the backward pass, and a fat block would take registers those kernels need.
+      for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < n4;
+           i0 += BUCKET_UNROLL * stride) {
+        float4 acc[BUCKET_UNROLL];
+#pragma unroll
+        for (int u = 0; u < BUCKET_UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (i < n4) {
+            if (mc_base != nullptr) {
+              acc[u] = multimem_ld_reduce_f4(mc_base + s.off + 4 * i);
+            } else if (world <= 8) {
+#pragma unroll
+              for (int r = 0; r < 8; ++r)
+                if (r < world) {
+                  const float4 v = ld_peer_f4(peer[r] + s.off + 4 * i);
+                  acc[u].x += v.x;
+                  acc[u].y += v.y;
+                  acc[u].z += v.z;
+                  acc[u].w += v.w;
+                }
+            } else {
+              for (int r = 0; r < world; ++r) {
+                const float4 v = ld_peer_f4(reinterpret_cast<const float*>(peers[r]) + s.off + 4 * i);
+                acc[u].x += v.x;
+                acc[u].y += v.y;
+                acc[u].z += v.z;
+                acc[u].w += v.w;
+              }
+            }
           }
         }
-        acc.x *= scale;
-        acc.y *= scale;
-        acc.z *= scale;
-        acc.w *= scale;
-        *reinterpret_cast<float4*>(local + 4 * i) = acc;
+#pragma unroll
+        for (int u = 0; u < BUCKET_UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < n4)
+            *reinterpret_cast<float4*>(local + 4 * i) =
+                make_float4(acc[u].x * scale, acc[u].y * scale, acc[u].z * scale, acc[u].w * scale);
+        }
       }
     }
   }
@@ -373,7 +402,7 @@ void symm_bucket_reduce(at::Tensor peers, int64_t rank, int64_t world, int64_t s
   const int dev = peers.get_device();
   c10::cuda::CUDAGuard guard(dev);
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
-  symm_bucket_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+  symm_bucket_reduce_kernel<<<static_cast<unsigned>(blocks), BUCKET_THREADS, 0, stream>>>(
       reinterpret_cast<const long long*>(peers.data_ptr<int64_t>()), static_cast<int>(rank), static_cast<int>(world),
       static_cast<int>(slot), reinterpret_cast<const Seg*>(segs.data_ptr<int64_t>()), static_cast<int>(segs.size(0)),
       static_cast<float>(scale), reinterpret_cast<const float*>(mc_ptr),

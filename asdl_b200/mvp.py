@@ -13,6 +13,7 @@ import torch
 import torch.nn as nn
 import torch.distributed as dist
 
+from . import ops
 from .vector import ParamVector, normalization, orthnormal
 
 __all__ = ['power_method', 'stochastic_lanczos_quadrature', 'conjugate_gradient_method',
@@ -119,7 +120,7 @@ def stochastic_lanczos_quadrature(mvp_fn: MvpFn, model: nn.Module, n_v=1, num_it
         if betas:
             off = torch.tensor(betas, device=device)
             T = T + torch.diag(off, 1) + torch.diag(off, -1)
-        eigval, eigvec = torch.linalg.eigh(T)
+        eigval, eigvec = ops.eigh(T)
         all_eigvals.append(eigval.tolist())
         all_weights.append((eigvec[0, :] ** 2).tolist())
     return all_eigvals, all_weights

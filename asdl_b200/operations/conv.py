@@ -110,7 +110,7 @@ class Conv2d(Operation):
         n, d, L = t.shape
         if n * L < d:
             return torch.linalg.svd(_rows(t).float(), full_matrices=True)[2].T
-        return torch.linalg.eigh(gram_fn(t))[1]
+        return ops.eigh(gram_fn(t))[1]
 
     @classmethod
     def cov_kfe_A(cls, module, in_data):

@@ -24,7 +24,7 @@ def _eigenbasis(x, gram_fn):
     n, d = x.shape
     if n < d:
         return torch.linalg.svd(x.float(), full_matrices=True)[2].T
-    return torch.linalg.eigh(gram_fn(x))[1]
+    return ops.eigh(gram_fn(x))[1]
 
 
 class Linear(Operation):

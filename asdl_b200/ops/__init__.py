@@ -15,6 +15,11 @@ What each primitive stands in for in the reference (file:line inside its project
   * ``kron_apply``: asdl/symmatrix.py:536-548 (B W A) and asdl/precondition/shampoo.py:351-367;
   * ``spd_inverse`` / ``spd_inverse_grouped``: asdl/utils.py:91-96 (cholesky_inv);
   * ``unitwise_inverse``: asdl/symmatrix.py:687-698;
+  * ``eigh`` / ``eigvalsh``: the ``torch.linalg.eigh`` calls of asdl/operations/linear.py:103-118,
+    asdl/precondition/newton.py:43, asdl/mvp.py:140 (matrices up to 128 x 128: the library's batched
+    Jacobi kernel);
+  * ``layernorm_unitwise_stats``: asdl/operations/layernorm.py:70-78;
+  * ``diag_linear_stats``: asdl/operations/linear.py:57-66;
   * ``batchnorm_unitwise_stats``: asdl/operations/batchnorm.py:11-55;
   * ``batch_norm_train`` / ``layer_norm``: the models' own normalisation layers (no reference
     counterpart; PyTorch's kernels were the hot spot of the benchmark models).
@@ -30,7 +35,8 @@ import torch
 
 from . import _build
 
-__all__ = ['gram', 'matmul_tn', 'split3', 'matmul_fp32_tc', 'kron_apply', 'conv_patch_gram', 'spd_inverse', 'spd_inverse_grouped', 'damped_cholesky',
+__all__ = ['gram', 'matmul_tn', 'split3', 'matmul_fp32_tc', 'eigh', 'eigvalsh', 'layernorm_unitwise_stats',
+           'diag_linear_stats', 'kron_apply', 'conv_patch_gram', 'spd_inverse', 'spd_inverse_grouped', 'damped_cholesky',
            'unitwise_inverse', 'batchnorm_unitwise_stats', 'batchnorm_unitwise_stats_from_input',
            'batch_norm_train', 'layer_norm',
            'set_backend', 'get_backend', 'set_precision', 'get_precision', 'extension',
@@ -519,6 +525,81 @@ def layer_norm(x, weight, bias, eps=1e-5):
         return _LayerNormFn.apply(x, weight, bias, eps)
     return torch.nn.functional.layer_norm(x, (weight.numel(),) if weight is not None else x.shape[-1:],
                                           weight, bias, eps)
+
+
+#: largest matrix the Jacobi eigensolver kernel takes (it keeps the matrix and the vectors in shared memory)
+JACOBI_MAX_N = 128
+
+
+def _jacobi_ok(mat: torch.Tensor) -> bool:
+    return (cuda_kernels_enabled(mat) and mat.dtype == torch.float32 and mat.ndim in (2, 3)
+            and mat.shape[-1] == mat.shape[-2] and 1 <= mat.shape[-1] <= JACOBI_MAX_N)
+
+
+def eigh(mat: torch.Tensor):
+    """``(eigenvalues ascending, eigenvectors as columns)`` of a symmetric matrix or a batch of them.
+    CUDA fp32 up to 128 x 128: the library's batched parallel-Jacobi kernel (one CTA per matrix, the
+    input is symmetrised on load); anything else: ``torch.linalg.eigh``."""
+    if _jacobi_ok(mat):
+        batched = mat.ndim == 3
+        w, v = extension().jacobi_eigh((mat if batched else mat.unsqueeze(0)).contiguous(), True)
+        return (w, v) if batched else (w[0], v[0])
+    return torch.linalg.eigh(mat)
+
+
+def eigvalsh(mat: torch.Tensor) -> torch.Tensor:
+    """Eigenvalues (ascending) of a symmetric matrix or a batch of them; see :func:`eigh`."""
+    if _jacobi_ok(mat):
+        batched = mat.ndim == 3
+        w, _ = extension().jacobi_eigh((mat if batched else mat.unsqueeze(0)).contiguous(), False)
+        return w if batched else w[0]
+    return torch.linalg.eigvalsh(mat)
+
+
+def layernorm_unitwise_stats(y: torch.Tensor, g: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+                             out: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0) -> torch.Tensor:
+    """Unit-wise curvature blocks of a LayerNorm over the last dimension from its output ``y`` and output
+    gradient ``g`` ([..., d]): ``out <- beta * out + alpha * sum_rows [[gw^2, gw gb], [gw gb, gb^2]]`` with
+    ``gw = (y - bias) / weight * g`` and ``gb = g`` per feature (out: [d, 2, 2] fp32).  CUDA bf16 / fp32:
+    one pass over y and g with the library's kernel; anything else: PyTorch."""
+    d = weight.numel()
+    if out is None:
+        out = torch.zeros(d, 2, 2, device=y.device, dtype=torch.float32)
+        beta = 0.0
+    if (cuda_kernels_enabled(y, g) and weight.ndim == 1 and y.shape[-1] == d and y.dtype == g.dtype
+            and y.dtype in (torch.bfloat16, torch.float32) and weight.dtype == torch.float32 and out.is_contiguous()):
+        extension().ln_unitwise_stats(y.reshape(-1, d).contiguous(), g.reshape(-1, d).contiguous(),
+                                      weight.detach().contiguous(), bias.detach().contiguous(), out,
+                                      float(alpha), float(beta))
+        return out
+    k = weight.ndim
+    xh = (y.float() - bias) / weight
+    gw = (xh * g).reshape(-1, *y.shape[-k:]).flatten(start_dim=1)
+    gb = g.float().reshape(-1, *y.shape[-k:]).flatten(start_dim=1)
+    ww, wb, bb = gw.square().sum(dim=0), (gw * gb).sum(dim=0), gb.square().sum(dim=0)
+    new = torch.stack([torch.stack([ww, wb], dim=1), torch.stack([wb, bb], dim=1)], dim=1)
+    return out.mul_(beta).add_(new, alpha=alpha)
+
+
+def diag_linear_stats(a: torch.Tensor, g: torch.Tensor, out: Optional[torch.Tensor] = None,
+                      out_bias: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0):
+    """Diagonal Fisher of a linear layer: ``out[o, i] <- beta*out + alpha * sum_rows g[r, o]^2 a[r, i]^2`` and
+    ``out_bias[o] <- ... sum_rows g[r, o]^2`` for inputs ``a`` [rows, in] and output gradients ``g``
+    [rows, out].  CUDA bf16 / fp32: one kernel that squares in registers; anything else: PyTorch."""
+    d_in, d_out = a.shape[1], g.shape[1]
+    if out is None:
+        out = torch.zeros(d_out, d_in, device=a.device, dtype=torch.float32)
+        beta = 0.0
+    if (cuda_kernels_enabled(a, g) and a.dtype == g.dtype and a.dtype in (torch.bfloat16, torch.float32)
+            and out.is_contiguous() and out.dtype == torch.float32
+            and (out_bias is None or (out_bias.is_contiguous() and out_bias.dtype == torch.float32))):
+        extension().diag_linear_stats(a.contiguous(), g.contiguous(), out, out_bias, float(alpha), float(beta))
+        return out, out_bias
+    g2, a2 = g.float().square(), a.float().square()
+    out.mul_(beta).add_(g2.T @ a2, alpha=alpha)
+    if out_bias is not None:
+        out_bias.mul_(beta).add_(g2.sum(dim=0), alpha=alpha)
+    return out, out_bias
 
 
 def unitwise_inverse(blocks: torch.Tensor, damping: float = 0.0) -> torch.Tensor:

@@ -180,7 +180,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         self.overlap_grad_reduce = bool(overlap_grad_reduce)
         self.batch_statistics = bool(batch_statistics)
         self.bucket_mb = float(bucket_mb)
-        self.comm_blocks = 32          # CTAs of a bucket's pull kernel (it shares the GPU with the backward pass)
+        # CTAs of a bucket's pull kernel: one per SM (256 threads each, it shares the GPU with the backward pass)
+        self.comm_blocks = (torch.cuda.get_device_properties(device).multi_processor_count
+                            if device.type == 'cuda' else 1)
         self._buckets, self._comm_stream, self._reduced_in_backward = [], None, False
         if self.comm == 'symmetric':
             self._setup_symmetric()
@@ -336,21 +338,20 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         order of ``self._sym_params``.  ``scale``: factor applied to the reduced gradients."""
         params = self._sym_params
         st = dict(pending=[len(b['params']) for b in self._buckets], fired=set(), next=0, handles=[],
-                  scale=float(scale))
+                  scale=float(scale), copies=[[] for _ in self._buckets])
 
         def on_view_grad(i, b, grad):
-            with torch.no_grad():
-                self._grad_slot[params[i]][1].copy_(grad)
+            st['copies'][b].append((self._grad_slot[params[i]][1], grad))
             self._bucket_progress(st, i, b)
 
         def on_param_grad(i, b, param):
             view = self._grad_slot[param][1]
             g = param.grad
-            with torch.no_grad():
-                if g is not None and g.data_ptr() != view.data_ptr():
-                    view.copy_(g)
-                elif g is None:
+            if g is None:
+                with torch.no_grad():
                     view.zero_()
+            elif g.data_ptr() != view.data_ptr():
+                st['copies'][b].append((view, g))
             param.grad = view
             self._bucket_progress(st, i, b)
 
@@ -375,6 +376,11 @@ class FusedKfacGradientMaker(KfacGradientMaker):
 
     def _launch_bucket(self, st, b):
         current = torch.cuda.current_stream(self.device)
+        pairs = st['copies'][b]
+        if pairs:   # the bucket's gradients go into the symmetric buffer with one multi-tensor copy
+            with torch.no_grad():
+                torch._foreach_copy_([v for v, _ in pairs], [g for _, g in pairs])
+            st['copies'][b] = []
         ready = torch.cuda.Event()
         ready.record(current)
         self._comm_stream.wait_event(ready)
@@ -413,6 +419,20 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             self._overlap_end(st, ok)
 
     # ------------------------------------------------------------------ CUDA-graph replay
+    def _capture_key(self, slots):
+        """Everything a captured step depends on besides the contents of its tensor arguments: their
+        layouts first, then the values read at capture time."""
+        cfg = self.config
+        layouts = tuple((tuple(v.shape), v.dtype, v.stride()) for _, _, v in slots)
+        others = []
+        for container in (self._model_args, self._model_kwargs, self._loss_fn_args, self._loss_fn_kwargs):
+            items = container.items() if isinstance(container, dict) else enumerate(container)
+            for k, v in items:
+                if not isinstance(v, torch.Tensor) and isinstance(v, (int, float, bool, str, type(None))):
+                    others.append((k, v))
+        return (layouts, float(cfg.damping), float(cfg.ema_decay), cfg.data_size, float(self.grad_scale),
+                float(self.scale), bool(self.model.training), tuple(others))
+
     def _tensor_slots(self):
         """(container, key) of every tensor among the registered model / loss arguments."""
         slots = []
@@ -433,7 +453,18 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         if not (self._graph_enabled and kind is not None and ready):
             return self._eager_step(step, plain)
         slots = self._tensor_slots()
-        key = tuple((tuple(v.shape), v.dtype, v.stride()) for _, _, v in slots)
+        key = self._capture_key(slots)
+        if self._graphs and key != self._graph_key and key[:1] == self._graph_key[:1]:
+            # same tensor shapes, but something that a capture bakes in has changed (damping, moving
+            # average, data size, gradient scale, training mode, a non-tensor argument): the graphs
+            # are dropped and captured again at the next plain step.  Every rank sees the same
+            # configuration, so every rank takes this decision at the same step.
+            import warnings
+            warnings.warn('FusedKfacGradientMaker: a hyper-parameter or argument captured in the CUDA graphs '
+                          'changed; the steps are captured again.')
+            self._graphs = {}
+            self._graph_key = None
+            self._plain_steps_seen = 0
         if not self._graphs:
             if kind != 'plain':
                 return self._eager_step(step, plain)
@@ -737,15 +768,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         if not isinstance(module, nn.LayerNorm):
             ops.batchnorm_unitwise_stats(y, g, module.weight, module.bias, out=target, alpha=alpha, beta=beta)
             return
-        k = module.weight.ndim
-        xh = (y.float() - module.bias) / module.weight
-        gw = (xh * g).reshape(-1, *y.shape[-k:]).flatten(start_dim=1)
-        gb = g.float().reshape(-1, *y.shape[-k:]).flatten(start_dim=1)
-        ww = gw.square().sum(dim=0)
-        wb = (gw * gb).sum(dim=0)
-        bb = gb.square().sum(dim=0)
-        new = torch.stack([torch.stack([ww, wb], dim=1), torch.stack([wb, bb], dim=1)], dim=1)
-        target.mul_(beta).add_(new, alpha=alpha)
+        # LayerNorm: one pass over y and g on CUDA (1-D weights), PyTorch otherwise
+        ops.layernorm_unitwise_stats(y, g, module.weight, module.bias, out=target, alpha=alpha, beta=beta)
 
     def _sampling_losses(self, logits):
         """The scalar losses whose backward passes (activation gradients only) measure the output-side
@@ -927,10 +951,15 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                     st.kron.A_inv, st.kron.B_inv = st.A_inv, st.B_inv
                     st.has_inv = True
                     self._refresh_cache(st)
-            for st in self._norm:
-                if not self.is_module_for_inv_and_precondition(st.module):
-                    continue
-                st.inv.copy_(ops.unitwise_inverse(st.stats, damping))
+            norms = [st for st in self._norm if self.is_module_for_inv_and_precondition(st.module)]
+            if norms and self._use_norm_kernels():
+                # all 2x2 blocks of all normalisation layers: one launch, closed form
+                ops.extension().unitwise_inverse_mt([[st.stats.data_ptr(), st.inv.data_ptr(), st.stats.shape[0]] for st in norms],
+                                                    float(damping))
+            else:
+                for st in norms:
+                    st.inv.copy_(ops.unitwise_inverse(st.stats, damping))
+            for st in norms:
                 st.unit.inv = st.inv
                 st.has_inv = True
 
@@ -1075,12 +1104,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         ext.gemm_plan_run(group['plans'][1])
         if moved:
             torch._foreach_copy_([g for _, g in moved], [v for v, _ in moved])
-        for st in todo:
-            if st.has_bias and st.module.bias.grad is not None:
-                b = st.module.bias.grad
-                if grad_scale != 1:
-                    b.mul_(grad_scale)
-                b.copy_(torch.mv(st.B_inv, b))
+        self._precondition_biases(todo, grad_scale)
 
     def _precondition_kron(self, st: _KronState, grad_scale, replicate=False):
         g2d, staged = st.grad_matrix()
@@ -1143,7 +1167,49 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             g2d.copy_(out)
         return False
 
+    def _use_norm_kernels(self):
+        return self.device.type == 'cuda' and ops.get_backend() != 'torch'
+
+    def _precondition_biases(self, todo, grad_scale):
+        """bias.grad <- B^-1 bias.grad for every layer of ``todo`` that has a bias: one launch on CUDA."""
+        with_bias = [st for st in todo if st.has_bias and st.module.bias.grad is not None]
+        if not with_bias:
+            return
+        if self._use_norm_kernels() and all(st.module.bias.grad.is_contiguous() and st.B_inv.is_contiguous()
+                                            and st.module.bias.grad.dtype == torch.float32 for st in with_bias):
+            scratch = self.__dict__.setdefault('_bias_scratch', {})
+            rows = []
+            for st in with_bias:
+                if st not in scratch:
+                    scratch[st] = torch.empty(st.d_out, device=self.device, dtype=torch.float32)
+                rows.append([st.B_inv.data_ptr(), st.module.bias.grad.data_ptr(), scratch[st].data_ptr(), st.d_out])
+            ops.extension().bias_precondition_mt(rows, float(grad_scale))   # the addresses travel as kernel parameters
+            return
+        for st in with_bias:
+            b = st.module.bias.grad
+            if grad_scale != 1:
+                b.mul_(grad_scale)
+            b.copy_(torch.mv(st.B_inv, b))
+
     def _precondition_norms(self, grad_scale):
+        if self._use_norm_kernels():
+            norms, grads = [], []
+            for st in self._norm:
+                if not st.has_inv or not self.is_module_for_inv_and_precondition(st.module):
+                    continue
+                w, b = st.module.weight.grad, st.module.bias.grad
+                if w is None or b is None:
+                    continue
+                if not (w.is_contiguous() and b.is_contiguous() and w.dtype == torch.float32 and b.dtype == torch.float32):
+                    norms = None
+                    break
+                norms.append(st)
+                grads.append((w, b))
+            if norms is not None:
+                if norms:   # every normalisation layer's 2x2 blocks applied in one launch
+                    ops.extension().unitwise_apply_mt([[st.inv.data_ptr(), w.data_ptr(), b.data_ptr(), st.inv.shape[0]]
+                                                       for st, (w, b) in zip(norms, grads)], float(grad_scale))
+                return
         gw, gb, i00, i01, i10, i11 = [], [], [], [], [], []
         for st in self._norm:
             if not st.has_inv or not self.is_module_for_inv_and_precondition(st.module):

@@ -7,6 +7,7 @@ from typing import Any, Tuple, Union
 import torch
 from torch import Tensor
 
+from .. import ops
 from ..grad_maker import GradientMaker
 from ..hessian import HessianMaker, HessianConfig
 from ..matrices import SHAPE_FULL
@@ -40,7 +41,7 @@ class NewtonGradientMaker(GradientMaker):
         hessian = self.model.hessian.data
         grads = [p.grad for p in self.model.parameters() if p.requires_grad and p.grad is not None]
         if self.config.absolute:
-            evals, evecs = torch.linalg.eigh(hessian)
+            evals, evecs = ops.eigh(hessian)
             hessian = (evecs * evals.abs()) @ evecs.T
         eye = torch.eye(hessian.shape[0], device=hessian.device, dtype=hessian.dtype)
         g = torch.cat([t.reshape(-1) for t in grads])

@@ -164,7 +164,7 @@ def _fused_kfac_gpu_matches_cpu(graph, **extra):
     for (l1, g1), (l2, g2) in zip(ref, got):
         assert abs(l1 - l2) < 2e-3 * max(1, abs(l1))
         for a, b in zip(g1, g2):
-            assert rel_err(b, a) < 3e-2, (rel_err(b, a), a.shape)
+            assert rel_err(b, a) < 5e-3, (rel_err(b, a), a.shape)
     ops.check_status()
 
 
@@ -669,4 +669,167 @@ def test_inverse_root_chain_at_small_ridge():
     print('inverse root errors: tensor-core chain', got, 'fp32 matmul', want)
     for g, w in zip(got, want):
         assert g < 0.1 and g < 1.5 * w + 2e-3, (got, want)
+    ops.check_status()
+
+
+def test_graph_is_captured_again_when_a_captured_hyper_parameter_changes():
+    """Damping is read at capture time; changing it later has to take effect (the graphs are dropped and
+    captured again), which is checked against an eager maker that sees the same change."""
+    torch.backends.cudnn.allow_tf32 = False
+    x = torch.randn(8, 3, 16, 16, device=DEV).contiguous(memory_format=torch.channels_last)
+    t = torch.randint(0, 5, (8,), device=DEV)
+
+    def run(graph):
+        torch.manual_seed(0)
+        model = _small_cnn().to(DEV).to(memory_format=torch.channels_last)
+        cfg = asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=0.3, curvature_upd_interval=4,
+                                         preconditioner_upd_interval=4)
+        gm = asdl.FusedKfacGradientMaker(model, cfg, fisher_type=asdl.FISHER_EMP, cuda_graph=graph)
+        opt = torch.optim.SGD(model.parameters(), lr=0.01)
+        out = []
+        for step in range(14):
+            if step == 7:
+                cfg.damping = 1e-1
+            opt.zero_grad()
+            d = gm.setup_model_call(model, x)
+            gm.setup_loss_call(F.cross_entropy, d, t)
+            gm.forward_and_backward()
+            out.append([p.grad.detach().clone() for p in model.parameters()])
+            opt.step()
+        return out, gm
+
+    import warnings
+    eager, _ = run(False)
+    with warnings.catch_warnings(record=True) as caught:
+        warnings.simplefilter('always')
+        replayed, gm = run(True)
+    assert any('captured again' in str(w.message) for w in caught)
+    assert gm.replayed_launches > 0
+    for step, (a, b) in enumerate(zip(eager, replayed)):
+        for ga, gb in zip(a, b):
+            assert rel_err(gb, ga) < 5e-3, (step, rel_err(gb, ga))
+    ops.check_status()
+
+
+@pytest.mark.parametrize('fisher,loss', [('fisher_mc', 'mse'), ('fisher_exact', 'cross_entropy'),
+                                         ('fisher_exact', 'mse'), ('fisher_mc2', 'cross_entropy')])
+def test_fused_kfac_fisher_variants_and_reused_layer_match_cpu(fisher, loss):
+    """Several backward passes per curvature step (exact Fisher: one per output; Monte-Carlo with two
+    samples) and a layer applied twice: every further contribution adds to the statistics of the step
+    through the GEMM's accumulate epilogue.  Compared with the same maker on the CPU (PyTorch path),
+    with a fixed sampling seed where labels are sampled."""
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(0)
+            self.conv = nn.Conv2d(3, 8, 3, padding=1)
+            self.shared = nn.Linear(8, 8)
+            self.head = nn.Linear(8, 4)
+
+        def forward(self, x):
+            x = F.relu(self.conv(x)).mean(dim=(2, 3))
+            x = F.relu(self.shared(x))
+            x = F.relu(self.shared(x))
+            return self.head(x)
+
+    n_mc = 2 if fisher == 'fisher_mc2' else 1
+    ftype = asdl.FISHER_EXACT if fisher == 'fisher_exact' else asdl.FISHER_MC
+    ltype = asdl.LOSS_MSE if loss == 'mse' else asdl.LOSS_CROSS_ENTROPY
+    x = torch.randn(6, 3, 8, 8)
+    t = torch.randn(6, 4) if loss == 'mse' else torch.randint(0, 4, (6,))
+    loss_fn = F.mse_loss if loss == 'mse' else F.cross_entropy
+
+    def factors(dev):
+        model = Net().to(dev)
+        cfg = asdl.PreconditioningConfig(data_size=6, damping=1e-2, ema_decay=0.5, curvature_upd_interval=1,
+                                         preconditioner_upd_interval=1)
+        gm = asdl.FusedKfacGradientMaker(model, cfg, fisher_type=ftype, loss_type=ltype, n_mc_samples=n_mc, seed=3)
+        for _ in range(2):
+            d = gm.setup_model_call(model, x.to(dev))
+            gm.setup_loss_call(loss_fn, d, t.to(dev))
+            gm.forward_and_backward()
+        return [(st.A.cpu(), st.B.cpu()) for st in gm._kron], [p.grad.cpu() for p in model.parameters()]
+
+    exact = fisher == 'fisher_exact'           # sampled labels come from different generators on CPU and GPU
+    f_cpu, g_cpu = factors(torch.device('cpu'))
+    f_gpu, g_gpu = factors(torch.device(DEV))
+    for (a1, b1), (a2, b2) in zip(f_cpu, f_gpu):
+        assert rel_err(a2, a1) < 1e-4                    # input-side statistics never depend on the sampling
+        if exact:
+            assert rel_err(b2, b1) < 1e-3
+        else:
+            assert torch.isfinite(b2).all() and b2.abs().sum() > 0
+    if exact:
+        for a, b in zip(g_cpu, g_gpu):
+            assert rel_err(b, a) < 5e-3
+    ops.check_status()
+
+
+@pytest.mark.parametrize('n,batch', [(1, 2), (2, 3), (7, 2), (64, 4), (100, 2), (127, 1), (128, 2)])
+def test_jacobi_eigh_kernel(ext, n, batch):
+    """Batched Jacobi eigensolver against float64 torch.linalg.eigh: eigenvalues, residual and
+    orthogonality, on matrices with eigenvalues spread over eight decades."""
+    torch.manual_seed(n)
+    q, _ = torch.linalg.qr(torch.randn(batch, n, n, device=DEV, dtype=torch.float64))
+    lam = torch.logspace(-6, 2, n, device=DEV, dtype=torch.float64).expand(batch, n) * (1 + torch.rand(batch, n, device=DEV))
+    mats = ((q * lam.unsqueeze(1)) @ q.transpose(1, 2)).float()
+    before = ext.launch_count()
+    w, v = ops.eigh(mats)
+    assert ext.launch_count() > before
+    ref = torch.linalg.eigvalsh(mats.double())
+    scale = ref.abs().amax(dim=1, keepdim=True)
+    assert ((w.double() - ref).abs() <= 5e-6 * scale).all()
+    assert (w[:, 1:] >= w[:, :-1]).all()
+    eye = torch.eye(n, device=DEV, dtype=torch.float64)
+    vd = v.double()
+    assert (vd.transpose(1, 2) @ vd - eye).abs().max().item() < 5e-5
+    resid = (mats.double() @ vd - vd * w.double().unsqueeze(1)).abs().amax(dim=(1, 2)) / scale.squeeze(1)
+    assert resid.max().item() < 5e-5
+    assert ((ops.eigvalsh(mats[0]).double() - ref[0]).abs() <= 5e-6 * scale[0]).all()
+    ops.check_status()
+
+
+@pytest.mark.parametrize('rows,d,dtype', [(37, 24, torch.float32), (512, 768, torch.bfloat16), (4099, 1000, torch.bfloat16)])
+def test_layernorm_unitwise_and_diag_stats_kernels(ext, rows, d, dtype):
+    torch.manual_seed(0)
+    y = torch.randn(rows, d, device=DEV).to(dtype)
+    g = torch.randn(rows, d, device=DEV).to(dtype)
+    weight, bias = torch.rand(d, device=DEV) + 0.5, torch.randn(d, device=DEV)
+    old = torch.rand(d, 2, 2, device=DEV)
+    got = ops.layernorm_unitwise_stats(y, g, weight, bias, out=old.clone(), alpha=0.3, beta=0.7)
+    ops.set_backend('torch')
+    want = ops.layernorm_unitwise_stats(y, g, weight, bias, out=old.clone(), alpha=0.3, beta=0.7)
+    ops.set_backend('auto')
+    assert rel_err(got, want) < 2e-5
+    a = torch.randn(rows, 40, device=DEV).to(dtype)
+    o0, b0 = torch.rand(d, 40, device=DEV), torch.rand(d, device=DEV)
+    got_w, got_b = ops.diag_linear_stats(a, g, out=o0.clone(), out_bias=b0.clone(), alpha=0.5, beta=0.25)
+    want_w = 0.25 * o0 + 0.5 * (g.double().square().T @ a.double().square()).float()
+    want_b = 0.25 * b0 + 0.5 * g.double().square().sum(dim=0).float()
+    assert rel_err(got_w, want_w) < 2e-5 and rel_err(got_b, want_b) < 2e-5
+    ops.check_status()
+
+
+def test_multi_tensor_unitwise_and_bias_kernels(ext):
+    torch.manual_seed(0)
+    sizes = [8, 24, 257, 1000]
+    stats = [torch.rand(f, 2, 2, device=DEV) for f in sizes]
+    stats = [s @ s.transpose(1, 2) for s in stats]
+    invs = [torch.empty_like(s) for s in stats]
+    ext.unitwise_inverse_mt([[s.data_ptr(), i.data_ptr(), s.shape[0]] for s, i in zip(stats, invs)], 0.1)
+    for s, i in zip(stats, invs):
+        assert rel_err(i, torch.linalg.inv(s.double() + 0.1 * torch.eye(2, device=DEV, dtype=torch.float64)).float()) < 1e-5
+    gw = [torch.randn(f, device=DEV) for f in sizes]
+    gb = [torch.randn(f, device=DEV) for f in sizes]
+    want = [(i.double() @ torch.stack([w, b], dim=1).double().unsqueeze(2) * 0.5).squeeze(2) for i, w, b in zip(invs, gw, gb)]
+    ext.unitwise_apply_mt([[i.data_ptr(), w.data_ptr(), b.data_ptr(), i.shape[0]] for i, w, b in zip(invs, gw, gb)], 0.5)
+    for (w, b), ref in zip(zip(gw, gb), want):
+        assert rel_err(w, ref[:, 0].float()) < 1e-5 and rel_err(b, ref[:, 1].float()) < 1e-5
+    mats = [torch.randn(n, n, device=DEV) for n in (5, 64, 1000)]
+    vecs = [torch.randn(m.shape[0], device=DEV) for m in mats]
+    want = [(m.double() @ v.double() * 2.0).float() for m, v in zip(mats, vecs)]
+    scratch = [torch.empty_like(v) for v in vecs]
+    ext.bias_precondition_mt([[m.data_ptr(), v.data_ptr(), s.data_ptr(), m.shape[0]] for m, v, s in zip(mats, vecs, scratch)], 2.0)
+    for v, ref in zip(vecs, want):
+        assert rel_err(v, ref) < 1e-5
     ops.check_status()

@@ -109,3 +109,31 @@ def test_fused_follows_the_generic_maker_for_every_fisher_type_and_option(option
 
     for want, got in zip(run(asdl.KfacGradientMaker), run(asdl.FusedKfacGradientMaker)):
         assert ((want - got).norm() / want.norm()).item() < 1e-4
+
+
+def test_capture_key_covers_what_a_graph_bakes_in():
+    """The key that decides whether captured steps may be replayed changes with every value that a
+    capture reads once: damping, the moving-average weight, the data size, the training mode and
+    non-tensor arguments of the registered calls."""
+    import torch.nn as nn
+    import asdl_b200 as asdl
+    model = nn.Sequential(nn.Linear(4, 3))
+    cfg = asdl.PreconditioningConfig(data_size=4, damping=1e-2, ema_decay=0.1)
+    gm = asdl.FusedKfacGradientMaker(model, cfg)
+    x = torch.randn(4, 4)
+    gm.setup_model_call(model, x)
+    gm.setup_loss_call(lambda y, scale=1.0: y.sum() * scale, gm._model_output if False else x, scale=2.0)
+    key0 = gm._capture_key(gm._tensor_slots())
+    assert key0 == gm._capture_key(gm._tensor_slots())
+    cfg.damping = 1e-1
+    key1 = gm._capture_key(gm._tensor_slots())
+    assert key1 != key0 and key1[0] == key0[0]          # same layouts, different captured values
+    cfg.damping = 1e-2
+    cfg.ema_decay = 0.2
+    assert gm._capture_key(gm._tensor_slots()) != key0
+    cfg.ema_decay = 0.1
+    model.eval()
+    assert gm._capture_key(gm._tensor_slots()) != key0
+    model.train()
+    gm.setup_loss_call(lambda y, scale=1.0: y.sum() * scale, x, scale=3.0)
+    assert gm._capture_key(gm._tensor_slots()) != key0
