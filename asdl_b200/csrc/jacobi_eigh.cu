@@ -2,8 +2,8 @@
 // two-sided Jacobi method, one CTA per matrix, everything in shared memory:
 //     A = V diag(w) V^T,   w ascending (the convention of torch.linalg.eigh).
 // A round rotates n/2 disjoint index pairs at once (round-robin tournament ordering, n - 1 rounds
-// per sweep); sweeps repeat until the off-diagonal mass is below 1e-7 of the diagonal's (at most
-// 30 sweeps).  Jacobi rotations are backward stable and the eigenvalues come out with a small
+// per sweep); sweeps repeat until the off-diagonal mass reaches the rounding floor (4 n eps of the
+// diagonal's norm) or stops shrinking (at most 30 sweeps).  Jacobi rotations are backward stable and the eigenvalues come out with a small
 // RELATIVE error, which suits the ill-conditioned curvature factors this is used for: the
 // Kronecker-factored eigenbasis of small layers, the |H| of saddle-free Newton steps on small
 // models, and the tridiagonal matrices of stochastic Lanczos quadrature.
@@ -50,6 +50,8 @@ jacobi_eigh_kernel(const float* __restrict__ mats, float* __restrict__ evals, fl
   const int half = m / 2;
   float* red = cs + 2 * JN;
   bool converged = false;
+  float prev_off = 3.0e38f;
+  const float tol = 16.f * static_cast<float>(n) * static_cast<float>(n) * 3.55e-15f;   // (4 n eps)^2
   for (int sweep = 0; sweep <= 30; ++sweep) {
     // convergence: off-diagonal against diagonal sum of squares
     float off = 0.f, dia = 0.f;
@@ -77,10 +79,13 @@ jacobi_eigh_kernel(const float* __restrict__ mats, float* __restrict__ evals, fl
       dia_t += red[32 + w];
     }
     __syncthreads();
-    if (!(off_t > 1e-14f * dia_t) || n == 1) {
+    // done at the rounding floor, or when a sweep no longer halves what is left (quadratic convergence
+    // has ended, the rest is rounding noise)
+    if (!(off_t > tol * dia_t) || n == 1 || (sweep >= 3 && off_t > 0.5f * prev_off && off_t < 1e-6f * dia_t)) {
       converged = true;
       break;
     }
+    prev_off = off_t;
     if (sweep == 30) break;
     for (int r = 0; r < m - 1; ++r) {
       // rotation of every pair of this round
@@ -97,7 +102,7 @@ jacobi_eigh_kernel(const float* __restrict__ mats, float* __restrict__ evals, fl
           if (fabsf(apq) > 1e-37f) {
             const float tau = (A[q * JP + q] - A[p * JP + p]) / (2.f * apq);
             const float t = (tau >= 0.f ? 1.f : -1.f) / (fabsf(tau) + sqrtf(1.f + tau * tau));
-            c = rsqrtf(1.f + t * t);
+            c = 1.f / sqrtf(1.f + t * t);   // correctly rounded: c^2 + s^2 = 1 to rounding, no drift of the norm
             s = t * c;
           }
         }
