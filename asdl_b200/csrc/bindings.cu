@@ -5,7 +5,7 @@ namespace b200 {
 void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
                bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta, bool sym,
                c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo, int64_t nsplit,
-               c10::optional<at::Tensor> out_mid, bool split3);
+               c10::optional<at::Tensor> out_mid, bool split3, bool x3wide);
 void set_gemm_wide(int64_t mode);
 void gemm_batch_begin();
 int64_t gemm_batch_end();
@@ -26,7 +26,7 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
                    bool a_kmajor, bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta,
                    bool sym, c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
                    int64_t dst_ptr, int64_t ldc, bool atomic, std::vector<int64_t> extra_ptrs,
-                   int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3);
+                   int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3, bool x3wide);
 void gemm_plan_finalize(int64_t id);
 void gemm_plan_run(int64_t id);
 void cast_pad_bf16_grouped(at::Tensor table, int64_t count);
@@ -73,7 +73,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("umma_gemm", &b200::umma_gemm, "tcgen05 TN GEMM / SYRK", py::arg("a_segs"),
         py::arg("b_segs"), py::arg("a_kmajor"), py::arg("b_kmajor"), py::arg("C"),
         py::arg("alpha"), py::arg("beta"), py::arg("sym"), py::arg("out_hi"), py::arg("out_lo"),
-        py::arg("nsplit"), py::arg("out_mid") = py::none(), py::arg("split3") = false);
+        py::arg("nsplit"), py::arg("out_mid") = py::none(), py::arg("split3") = false, py::arg("x3wide") = false);
   m.def("set_gemm_wide", &b200::set_gemm_wide);
   m.def("gemm_batch_begin", &b200::gemm_batch_begin);
   m.def("gemm_batch_end", &b200::gemm_batch_end);
@@ -89,7 +89,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_plan_add", &b200::gemm_plan_add, py::arg("plan"), py::arg("a_segs"), py::arg("b_segs"),
         py::arg("a_kmajor"), py::arg("b_kmajor"), py::arg("C"), py::arg("alpha"), py::arg("beta"), py::arg("sym"),
         py::arg("out_hi"), py::arg("out_lo"), py::arg("dst_ptr"), py::arg("ldc"), py::arg("atomic"),
-        py::arg("extra_ptrs"), py::arg("nsplit"), py::arg("out_mid") = py::none(), py::arg("split3") = false);
+        py::arg("extra_ptrs"), py::arg("nsplit"), py::arg("out_mid") = py::none(), py::arg("split3") = false, py::arg("x3wide") = false);
   m.def("gemm_plan_finalize", &b200::gemm_plan_finalize);
   m.def("gemm_plan_run", &b200::gemm_plan_run);
   m.def("cast_pad_bf16_grouped", &b200::cast_pad_bf16_grouped);

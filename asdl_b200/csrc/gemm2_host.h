@@ -7,7 +7,7 @@
 
 namespace b200 {
 
-enum G2Flavour { G2_PLAIN = 0, G2_WIDE = 1, G2_SPLIT3 = 2 };
+enum G2Flavour { G2_PLAIN = 0, G2_WIDE = 1, G2_SPLIT3 = 2, G2_X3WIDE = 3 };
 
 // Tensor map of one bf16 operand.  `mn` x `k` logical extents; `kmajor`: stored [mn, k] row-major
 // with pitch `ld` elements, otherwise stored [k, mn] row-major.  `box_mn`: tile extent along MN
@@ -26,6 +26,8 @@ void g2_run_plain(const GemmProblem2& single, const GemmProblem2* probs, const G
                   int n_sms, cudaStream_t stream, const int* prefix = nullptr, int n_probs = 0);
 void g2_run_wide(const GemmProblem2& single, const GemmProblem2* probs, const GemmWork2* work, int n_work,
                  int n_sms, cudaStream_t stream, const int* prefix = nullptr, int n_probs = 0);
+void g2_run_x3wide(const GemmProblem2& single, const GemmProblem2* probs, const GemmWork2* work, int n_work,
+                   int n_sms, cudaStream_t stream, const int* prefix = nullptr, int n_probs = 0);
 void g2_run_split3(const GemmProblem2& single, const GemmProblem2* probs, const GemmWork2* work, int n_work,
                    int n_sms, cudaStream_t stream, const int* prefix = nullptr, int n_probs = 0);
 

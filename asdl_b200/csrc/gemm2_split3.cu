@@ -14,12 +14,12 @@ void g2_run_split3(const GemmProblem2& single, const GemmProblem2* probs, const 
   B200_CUDA_CHECK(cudaGetDevice(&dev));
   bool& attr_set = attr_set_on[dev & 63];
   if (!attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(umma_gemm2_kernel<128, 8, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200_CUDA_CHECK(cudaFuncSetAttribute(umma_gemm2_kernel<128, 8, 1, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          G2Split3::SMEM_BYTES));
     attr_set = true;
   }
   const int grid = std::min(n_work, 1 * n_sms);
-  umma_gemm2_kernel<128, 8, 1, true><<<grid, G2Split3::THREADS, G2Split3::SMEM_BYTES, stream>>>(single, probs, work, n_work, prefix, n_probs);
+  umma_gemm2_kernel<128, 8, 1, 3><<<grid, G2Split3::THREADS, G2Split3::SMEM_BYTES, stream>>>(single, probs, work, n_work, prefix, n_probs);
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch();
 }

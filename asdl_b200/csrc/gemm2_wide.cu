@@ -14,12 +14,12 @@ void g2_run_wide(const GemmProblem2& single, const GemmProblem2* probs, const Ge
   B200_CUDA_CHECK(cudaGetDevice(&dev));
   bool& attr_set = attr_set_on[dev & 63];
   if (!attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(umma_gemm2_kernel<256, 8, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200_CUDA_CHECK(cudaFuncSetAttribute(umma_gemm2_kernel<256, 8, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          G2Wide::SMEM_BYTES));
     attr_set = true;
   }
   const int grid = std::min(n_work, 1 * n_sms);
-  umma_gemm2_kernel<256, 8, 1, false><<<grid, G2Wide::THREADS, G2Wide::SMEM_BYTES, stream>>>(single, probs, work, n_work, prefix, n_probs);
+  umma_gemm2_kernel<256, 8, 1, 1><<<grid, G2Wide::THREADS, G2Wide::SMEM_BYTES, stream>>>(single, probs, work, n_work, prefix, n_probs);
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch();
 }

@@ -74,6 +74,8 @@ void g2_launch_list(const GemmProblem2* d_probs, const GemmWork2* d_work, int n_
     g2_run_wide(dummy, d_probs, d_work, n_work, n_sms, stream);
   else if (flavour == G2_SPLIT3)
     g2_run_split3(dummy, d_probs, d_work, n_work, n_sms, stream);
+  else if (flavour == G2_X3WIDE)
+    g2_run_x3wide(dummy, d_probs, d_work, n_work, n_sms, stream);
   else
     g2_run_plain(dummy, d_probs, d_work, n_work, n_sms, stream);
 }
@@ -97,11 +99,12 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
                        const c10::optional<at::Tensor>& C, double alpha, double beta, bool sym,
                        const c10::optional<at::Tensor>& out_hi, const c10::optional<at::Tensor>& out_mid,
                        const c10::optional<at::Tensor>& out_lo, int64_t nsplit_req, bool split3, int n_sms,
-                       bool allow_no_output = false) {
+                       bool allow_no_output = false, bool x3wide = false) {
   const int nseg = static_cast<int>(a_segs.size());
   TORCH_CHECK(nseg >= 1 && nseg <= G2_MAX_SEG && b_segs.size() == a_segs.size(),
               "between 1 and 6 operand segments are supported");
   TORCH_CHECK(!split3 || nseg == 3, "a split3 product takes the (hi, mid, lo) parts of both operands");
+  TORCH_CHECK(!x3wide || (nseg == 2 && !split3), "an x3wide product takes the (hi, lo) parts of both operands");
   std::memset(&P, 0, sizeof(P));
   const at::Tensor& a0 = a_segs[0];
   const at::Tensor& b0 = b_segs[0];
@@ -112,7 +115,7 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
   TORCH_CHECK(K == Kb, "contraction sizes differ: ", K, " vs ", Kb);
   TORCH_CHECK(M > 0 && N > 0 && M < (1 << 30) && N < (1 << 30) && K < (1ll << 31) - 64, "matrix sizes out of range");
   if (sym) TORCH_CHECK(M == N, "symmetric mode needs a square output");
-  const bool wide = !split3 && (g_wide_mode == 2 || (g_wide_mode == 1 && N >= 1024 && M >= 1024));
+  const bool wide = x3wide || (!split3 && (g_wide_mode == 2 || (g_wide_mode == 1 && N >= 1024 && M >= 1024)));
   const int bn = wide ? 256 : 128;
   for (int s = 0; s < nseg; ++s) {
     check_operand(a_segs[s], "A");
@@ -122,7 +125,7 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
     g2_encode_operand(&P.tmA[s], a_segs[s].data_ptr(), M, K, a_segs[s].stride(0), a_kmajor, G2_BM);
     g2_encode_operand(&P.tmB[s], b_segs[s].data_ptr(), N, K, b_segs[s].stride(0), b_kmajor, bn);
   }
-  bool same_ab = sym && !wide && !split3 && a_kmajor == b_kmajor;
+  bool same_ab = sym && !wide && !split3 && !x3wide && a_kmajor == b_kmajor;
   for (int s = 0; s < nseg && same_ab; ++s)
     same_ab = a_segs[s].data_ptr() == b_segs[s].data_ptr() &&
               a_segs[s].stride(0) == b_segs[s].stride(0);
@@ -134,7 +137,8 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
   P.alpha = static_cast<float>(alpha);
   P.beta = static_cast<float>(beta);
   P.flags = (sym ? G2F_SYM : 0) | (a_kmajor ? G2F_A_KMAJOR : 0) | (b_kmajor ? G2F_B_KMAJOR : 0) |
-            (same_ab ? G2F_SAME_AB : 0) | (wide ? G2F_WIDE : 0) | (split3 ? G2F_SPLIT3 : 0);
+            (same_ab ? G2F_SAME_AB : 0) | (wide ? G2F_WIDE : 0) | (split3 ? G2F_SPLIT3 : 0) |
+            (x3wide ? G2F_SPLIT2 : 0);
   if (C.has_value()) {
     const at::Tensor& c = *C;
     TORCH_CHECK(c.is_cuda() && c.scalar_type() == at::kFloat && c.dim() == 2 && c.stride(1) == 1 &&
@@ -220,6 +224,8 @@ void gemm_launch_single(const GemmProblem2& P, int dev, cudaStream_t stream) {
   const bool wide = (P.flags & G2F_WIDE) != 0;
   if (P.flags & G2F_SPLIT3)
     g2_run_split3(P, nullptr, nullptr, n_work, n_sms, stream);
+  else if (P.flags & G2F_SPLIT2)
+    g2_run_x3wide(P, nullptr, nullptr, n_work, n_sms, stream);
   else if (wide)
     g2_run_wide(P, nullptr, nullptr, n_work, n_sms, stream);
   else
@@ -351,7 +357,7 @@ static bool batch_append(GemmProblem2& P, int dev, int64_t nsplit_req, cudaStrea
                          const std::vector<at::Tensor>& a_segs, const std::vector<at::Tensor>& b_segs,
                          const c10::optional<at::Tensor>& C) {
   GemmBatch& B = g_batch;
-  if (!B.active || (P.flags & (G2F_WIDE | G2F_SPLIT3))) return false;
+  if (!B.active || (P.flags & (G2F_WIDE | G2F_SPLIT3 | G2F_SPLIT2))) return false;
   if (!B.problems.empty() && B.dev != dev) batch_flush(stream);
   // two products into one output (a further backward pass adding to a factor) must not share a launch
   for (const GemmProblem2& Q : B.problems)
@@ -396,16 +402,17 @@ void gemm_batch_abort() {
 // Python entry: C = alpha * A^T B (+ beta C), optionally symmetric, optionally bf16 split outputs.
 // `split3`: the three segments are the (hi, mid, lo) parts of fp32 operands and the product is
 // formed fp32-grade (six part products, one accumulation chunk per K block; see umma_gemm2.cuh).
+// `x3wide`: the two segments are the (hi, lo) parts of both operands (bf16x3 on 128 x 256 tiles).
 void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
                bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta, bool sym,
                c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
-               int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3) {
+               int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3, bool x3wide) {
   TORCH_CHECK(!a_segs.empty(), "no operands");
   const int dev = a_segs[0].get_device();
   c10::cuda::CUDAGuard guard(dev);
   GemmProblem2 P;
   gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, C, alpha, beta, sym, out_hi, out_mid, out_lo,
-                    nsplit, split3, g2_sm_count(dev));
+                    nsplit, split3, g2_sm_count(dev), false, x3wide);
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
   if (out_hi.has_value() || !batch_append(P, dev, nsplit, stream, a_segs, b_segs, C)) {
     gemm_attach_scratch(P, dev, stream);
@@ -461,7 +468,7 @@ struct GemmPlan {
   std::vector<std::vector<at::Tensor>> keep_alive;  // operands / outputs referenced by raw pointer
   at::Tensor d_problems, d_work, d_rwork, scratch;
   int n_work = 0, n_rwork = 0, dev = 0;
-  int split3 = -1;  // -1: no problem yet, 0: plain products, 1: split3 products (never mixed)
+  int split3 = -1;  // -1: no problem yet, 0: plain products, 1: split3, 2: x3wide (never mixed)
   bool finalized = false;
 };
 
@@ -480,22 +487,23 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
                    bool a_kmajor, bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta,
                    bool sym, c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
                    int64_t dst_ptr, int64_t ldc, bool atomic, std::vector<int64_t> extra_ptrs,
-                   int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3) {
+                   int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3, bool x3wide) {
   auto it = g_plans.find(id);
   TORCH_CHECK(it != g_plans.end() && !it->second.finalized, "unknown or finalized plan");
   GemmPlan& plan = it->second;
   TORCH_CHECK(!a_segs.empty(), "no operands");
   plan.dev = a_segs[0].get_device();
-  TORCH_CHECK(plan.split3 < 0 || plan.split3 == static_cast<int>(split3),
-              "a plan holds either plain or split3 products, not both");
-  plan.split3 = split3 ? 1 : 0;
+  const int kind = split3 ? 1 : (x3wide ? 2 : 0);
+  TORCH_CHECK(plan.split3 < 0 || plan.split3 == kind, "a plan holds products of one kind (plain, split3 or x3wide)");
+  TORCH_CHECK(!(x3wide && sym), "symmetric products are not supported in x3wide plans");
+  plan.split3 = kind;
   c10::cuda::CUDAGuard guard(plan.dev);
   GemmProblem2 P;
   const int saved_mode = g_wide_mode;
   g_wide_mode = 0;  // the tiles of a plan share one kernel instantiation: 128-wide
   try {
     gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, C, alpha, beta, sym, out_hi, out_mid, out_lo,
-                      nsplit <= 0 ? 1 : nsplit, split3, g2_sm_count(plan.dev), /*allow_no_output=*/dst_ptr != 0);
+                      nsplit <= 0 ? 1 : nsplit, split3, g2_sm_count(plan.dev), /*allow_no_output=*/dst_ptr != 0, x3wide);
   } catch (...) {
     g_wide_mode = saved_mode;
     throw;
@@ -533,7 +541,7 @@ void gemm_plan_finalize(int64_t id) {
   // scratch for split-K problems (private to the plan)
   size_t scratch_floats = 0;
   for (auto& P : plan.problems)
-    if (needs_ws(P)) scratch_floats += static_cast<size_t>(P.ntiles) * P.nsplit * G2_BM * 128;
+    if (needs_ws(P)) scratch_floats += static_cast<size_t>(P.ntiles) * P.nsplit * G2_BM * tile_width(P);
   auto f32 = at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, plan.dev);
   if (scratch_floats > 0) plan.scratch = at::empty({static_cast<int64_t>(scratch_floats)}, f32);
   size_t off = 0;
@@ -548,9 +556,10 @@ void gemm_plan_finalize(int64_t id) {
     const bool split = needs_ws(P);
     if (split) {
       P.ws = plan.scratch.data_ptr<float>() + off;
-      off += static_cast<size_t>(P.ntiles) * P.nsplit * G2_BM * 128;
+      off += static_cast<size_t>(P.ntiles) * P.nsplit * G2_BM * tile_width(P);
     }
     const int kb_total = (P.K + G2_BK - 1) / G2_BK;
+    const int bn = tile_width(P);
     int tile = 0;
     for (int tm = 0; tm < P.tiles_m; ++tm)
       for (int tn = 0; tn < ((P.flags & G2F_SYM) ? tm + 1 : P.tiles_n); ++tn, ++tile) {
@@ -561,12 +570,13 @@ void gemm_plan_finalize(int64_t id) {
           std::memset(&w, 0, sizeof(w));
           w.problem = static_cast<int>(pi);
           w.a_mn = w.c_row = tm * G2_BM;
-          w.b_mn = w.c_col = tn * 128;
+          w.b_mn = w.c_col = tn * bn;
           w.a_k0 = w.b_k0 = kb0 * G2_BK;
           w.nkb = kb1 - kb0;
           w.tile_id = tile;
           w.split = s;
-          items.push_back({w, static_cast<long long>((P.flags & G2F_SPLIT3) ? 6 : P.nseg) * w.nkb + 2});
+          items.push_back({w, static_cast<long long>((P.flags & G2F_SPLIT3) ? 6 : ((P.flags & G2F_SPLIT2) ? 6 : P.nseg)) *
+                                  w.nkb + 2});
           if (split && s == 0) ritems.push_back({w, 0});
         }
       }
@@ -602,10 +612,10 @@ void gemm_plan_run(int64_t id) {
   auto stream = at::cuda::getCurrentCUDAStream(plan.dev).stream();
   const GemmProblem2* probs = reinterpret_cast<const GemmProblem2*>(plan.d_problems.data_ptr());
   g2_launch_list(probs, reinterpret_cast<const GemmWork2*>(plan.d_work.data_ptr()), plan.n_work,
-                 plan.split3 == 1 ? G2_SPLIT3 : G2_PLAIN, plan.dev, stream);
+                 plan.split3 == 1 ? G2_SPLIT3 : (plan.split3 == 2 ? G2_X3WIDE : G2_PLAIN), plan.dev, stream);
   if (plan.n_rwork > 0)
     g2_launch_reduce_list(probs, reinterpret_cast<const GemmWork2*>(plan.d_rwork.data_ptr()), plan.n_rwork,
-                          false, stream);
+                          plan.split3 == 2, stream);
 }
 
 // 0: 128-wide tiles only; 1: 256-wide tiles for outputs of at least 1024 x 1024; 2: wherever legal.

@@ -12,12 +12,15 @@
 // carries its own operand origins and K range, so triangular operands (Cholesky panels,
 // triangular inverses) skip their zero blocks and sub-matrices of one tensor map serve as operands.
 //
-// Three flavours of one kernel template:
+// Four flavours of one kernel template:
 //   plain   128 x 128 tiles, two CTAs per SM with a 3-stage ring each (two independent pipelines
 //           per SM hide each other's load latency), four epilogue warps; up to six (A_seg, B_seg)
 //           pairs accumulate into one TMEM accumulator (bf16, or "bf16x3" from hi/lo splits);
 //   wide    128 x 256 tiles (a third less operand traffic per FLOP), one CTA per SM, 4 stages,
 //           eight epilogue warps;
+//   x3wide  "bf16x3" products on 128 x 256 tiles: a stage holds the hi and lo parts of both operands
+//           of one K block (96 KiB, loaded once) and the MMA warp issues (lo,hi), (hi,lo), (hi,hi) from
+//           them - half the operand traffic per FLOP of three separately loaded segments;
 //   split3  fp32-grade products from three-way splits v = hi + mid + lo of both operands: a stage
 //           holds the three A parts and the three B parts of one 64-wide K block (96 KiB, loaded
 //           once) and the MMA warp issues the six significant part products from them,
@@ -44,19 +47,20 @@ constexpr int G2_MAX_EXTRA = 7;
 constexpr int G2_MAX_BATCH = 256;   // problems of one launch in batch mode
 constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;  // 16 KiB
 
-template <int BN, int EPI_WARPS, int MINB, bool SPLIT3>
+template <int BN, int EPI_WARPS, int MINB, int PARTS>
 struct G2Cfg {
-  static constexpr int STAGES = SPLIT3 ? 2 : (BN == 256 ? 4 : (MINB == 2 ? 3 : 6));
+  static constexpr int STAGES = PARTS > 1 ? 2 : (BN == 256 ? 4 : (MINB == 2 ? 3 : 6));
   static constexpr int B_BYTES = BN * G2_BK * 2;
-  static constexpr int STAGE_BYTES = SPLIT3 ? 3 * (G2_A_BYTES + B_BYTES) : G2_A_BYTES + B_BYTES;
+  static constexpr int STAGE_BYTES = PARTS * (G2_A_BYTES + B_BYTES);
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ +
                                     4 * (G2_MAX_BATCH + 4) /*item prefix of a batch*/;
 };
-using G2Plain = G2Cfg<128, 4, 2, false>;
-using G2Wide = G2Cfg<256, 8, 1, false>;
-using G2Split3 = G2Cfg<128, 8, 1, true>;
+using G2Plain = G2Cfg<128, 4, 2, 1>;
+using G2Wide = G2Cfg<256, 8, 1, 1>;
+using G2X3Wide = G2Cfg<256, 8, 1, 2>;
+using G2Split3 = G2Cfg<128, 8, 1, 3>;
 
 enum : int {
   G2F_SYM = 1,        // symmetric output: tiles on or below the diagonal only, mirrored
@@ -67,6 +71,7 @@ enum : int {
   G2F_LOWER = 32,     // with G2F_SYM: write / add the lower triangle only
   G2F_WIDE = 64,      // the problem's tensor maps and tile grid are laid out for BN = 256
   G2F_SPLIT3 = 128,   // tmA[0..2] / tmB[0..2] are the (hi, mid, lo) parts of the operands
+  G2F_SPLIT2 = 256,   // tmA[0..1] / tmB[0..1] are the (hi, lo) parts of the operands ("bf16x3", wide tiles)
 };
 
 enum : int {
@@ -404,12 +409,14 @@ __device__ __forceinline__ void g2_store_chunk(const G2Epi& P, const float* v, i
   }
 }
 
-template <int BN, int EPI_WARPS, int MINB, bool SPLIT3>
+template <int BN, int EPI_WARPS, int MINB, int PARTS>
 __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, MINB)
 umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem2* __restrict__ probs,
                   const GemmWork2* __restrict__ work, int n_work, const int* __restrict__ prefix_g, int n_probs) {
-  using Cfg = G2Cfg<BN, EPI_WARPS, MINB, SPLIT3>;
+  using Cfg = G2Cfg<BN, EPI_WARPS, MINB, PARTS>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr bool SPLIT3 = PARTS == 3;   // fp32-grade products, one accumulation chunk per K block
+  constexpr bool SPLIT2 = PARTS == 2;   // bf16x3 products from (hi, lo) parts loaded once per K block
   static_assert(!SPLIT3 || (BN == 128 && EPI_WARPS == 8), "the split3 flavour runs 128-wide tiles with 8 epilogue warps");
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128B swizzle atoms.
@@ -457,10 +464,10 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
         const GemmProblem2& P = *g2_item<BN>(single, probs, work, prefix, n_probs, wi, w);
         const bool a_k = (P.flags & G2F_A_KMAJOR) != 0;
         const bool b_k = (P.flags & G2F_B_KMAJOR) != 0;
-        const bool shared_ab = !SPLIT3 && BN == 128 && (P.flags & G2F_SAME_AB) && w.a_mn == w.b_mn &&
+        const bool shared_ab = PARTS == 1 && BN == 128 && (P.flags & G2F_SAME_AB) && w.a_mn == w.b_mn &&
                                w.a_k0 == w.b_k0;
         const uint32_t bytes = shared_ab ? G2_A_BYTES : Cfg::STAGE_BYTES;
-        const int nseg = SPLIT3 ? 1 : P.nseg;
+        const int nseg = PARTS > 1 ? 1 : P.nseg;
         for (int seg = 0; seg < nseg && ok; ++seg) {
           for (int kb = 0; kb < w.nkb; ++kb, ++it) {
             const int s = it % STAGES;
@@ -473,11 +480,11 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
             uint8_t* stage = smem + s * Cfg::STAGE_BYTES;
             mbar_expect_tx(&full_bar[s], bytes);
             const int ka = w.a_k0 + kb * G2_BK, kbb = w.b_k0 + kb * G2_BK;
-            constexpr int NPART = SPLIT3 ? 3 : 1;
+            constexpr int NPART = PARTS;
 #pragma unroll
             for (int part = 0; part < NPART; ++part) {
-              const CUtensorMap* ta = SPLIT3 ? &P.tmA[part] : &P.tmA[seg];
-              const CUtensorMap* tb = SPLIT3 ? &P.tmB[part] : &P.tmB[seg];
+              const CUtensorMap* ta = PARTS > 1 ? &P.tmA[part] : &P.tmA[seg];
+              const CUtensorMap* tb = PARTS > 1 ? &P.tmB[part] : &P.tmB[seg];
               uint8_t* sA = stage + part * G2_A_BYTES;
               uint8_t* sB = stage + NPART * G2_A_BYTES + part * Cfg::B_BYTES;
               if (a_k) {
@@ -518,7 +525,7 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
         const GemmProblem2& P = *g2_item<BN>(single, probs, work, prefix, n_probs, wi, w);
         const bool a_k = (P.flags & G2F_A_KMAJOR) != 0;
         const bool b_k = (P.flags & G2F_B_KMAJOR) != 0;
-        const bool shared_ab = !SPLIT3 && BN == 128 && (P.flags & G2F_SAME_AB) && w.a_mn == w.b_mn &&
+        const bool shared_ab = PARTS == 1 && BN == 128 && (P.flags & G2F_SAME_AB) && w.a_mn == w.b_mn &&
                                w.a_k0 == w.b_k0;
         const uint32_t idesc = make_idesc_bf16(G2_BM, BN, !a_k, !b_k);
         if (w.nkb <= 0) continue;
@@ -558,6 +565,44 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
             umma_commit(&empty_bar[s]);
             umma_commit(&acc_full[ab]);
           }
+        } else if constexpr (SPLIT2) {
+          const uint32_t ab = ch & 1;
+          if (!mbar_wait(&acc_empty[ab], ((ch >> 1) & 1) ^ 1)) {
+            set_error(P.status, ERR_WAIT_ACC);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t tacc = tmem_base + ab * BN;
+          for (int kb = 0; kb < w.nkb; ++kb, ++it) {
+            const int s = it % STAGES;
+            if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
+              set_error(P.status, ERR_WAIT_FULL);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t base = smem_u32(smem + s * Cfg::STAGE_BYTES);
+            // part products in issue order: (lo,hi) (hi,lo) (hi,hi)
+            constexpr int PART_A[3] = {1, 0, 0};
+            constexpr int PART_B[3] = {0, 1, 0};
+#pragma unroll
+            for (int pr = 0; pr < 3; ++pr) {
+              const uint32_t aA = base + PART_A[pr] * G2_A_BYTES;
+              const uint32_t aB = base + 2 * G2_A_BYTES + PART_B[pr] * Cfg::B_BYTES;
+#pragma unroll
+              for (int k = 0; k < G2_BK / 16; ++k) {
+                const uint64_t da = a_k ? make_smem_desc_sw128(aA + k * 32, 16, 1024)
+                                        : make_smem_desc_sw128(aA + k * 16 * 128, G2_BK * 128, 1024);
+                const uint64_t db = b_k ? make_smem_desc_sw128(aB + k * 32, 16, 1024)
+                                        : make_smem_desc_sw128(aB + k * 16 * 128, G2_BK * 128, 1024);
+                umma_bf16(tacc, da, db, idesc, (kb | pr | k) ? 1u : 0u);
+              }
+            }
+            umma_commit(&empty_bar[s]);
+          }
+          if (ok) umma_commit(&acc_full[ab]);
+          ++ch;
         } else {
           const uint32_t ab = ch & 1;
           if (!mbar_wait(&acc_empty[ab], ((ch >> 1) & 1) ^ 1)) {

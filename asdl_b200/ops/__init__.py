@@ -245,12 +245,15 @@ def kron_apply(left: torch.Tensor, mid: torch.Tensor, right: torch.Tensor) -> to
     t_hi = torch.empty(m, ld, device=mid.device, dtype=torch.bfloat16)
     t_lo = torch.empty_like(t_hi) if x3 else None
     # T = left^T-as-stored . mid : A operand = left ([k=m, m] row-major, symmetric), B = mid [k=m, n]
-    a_segs, b_segs = _segments(l_hi, l_lo, g_hi, g_lo)
-    ext.umma_gemm(a_segs, b_segs, False, False, None, 1.0, 0.0, False, t_hi, t_lo, 0)
-    # Y = T . right : A operand = T ([m, k=n] K-major), B = right ([k=n, n] row-major, symmetric)
     out = torch.empty(m, n, device=mid.device, dtype=torch.float32)
-    a_segs, b_segs = _segments(t_hi[:, :n], t_lo[:, :n] if x3 else None, r_hi, r_lo)
-    ext.umma_gemm(a_segs, b_segs, True, False, out, 1.0, 0.0, False, None, None, 0)
+    if x3:   # (hi, lo) parts, loaded once per K block by the x3wide flavour
+        ext.umma_gemm([l_hi, l_lo], [g_hi, g_lo], False, False, None, 1.0, 0.0, False, t_hi, t_lo, 0, None, False, True)
+        ext.umma_gemm([t_hi[:, :n], t_lo[:, :n]], [r_hi, r_lo], True, False, out, 1.0, 0.0, False, None, None, 0,
+                      None, False, True)
+        return out.to(mid.dtype) if mid.dtype != torch.float32 else out
+    ext.umma_gemm([l_hi], [g_hi], False, False, None, 1.0, 0.0, False, t_hi, t_lo, 0)
+    # Y = T . right : A operand = T ([m, k=n] K-major), B = right ([k=n, n] row-major, symmetric)
+    ext.umma_gemm([t_hi[:, :n]], [r_hi], True, False, out, 1.0, 0.0, False, None, None, 0)
     return out.to(mid.dtype) if mid.dtype != torch.float32 else out
 
 

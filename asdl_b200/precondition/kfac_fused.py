@@ -123,7 +123,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             persistent tcgen05 launch after the backward pass instead of one launch per factor; the
             layer inputs and output gradients are kept alive until then.  Switch it off for models
             that modify a layer's input in place after the layer has run.
-        overlap_grad_reduce: with ``comm='symmetric'``, reduce the gradients in buckets on a
+        overlap_grad_reduce: ``True`` / ``False`` / ``'auto'`` (on from ``OVERLAP_MIN_MB`` MiB of gradients
+            per rank).  With ``comm='symmetric'``, reduce the gradients in buckets on a
             communication stream as the backward pass produces them (asdl/precondition/
             natural_gradient.py:753-757,814-829 reduce them after the backward pass): a tensor hook
             per parameter copies its gradient into the symmetric buffer, and when a bucket is
@@ -134,6 +135,10 @@ class FusedKfacGradientMaker(KfacGradientMaker):
     Embedding layers are not handled here; list them in ``config.ignore_modules``.
     """
 
+    #: gradient volume (MiB of fp32 gradients per rank) from which ``overlap_grad_reduce='auto'`` switches the
+    #: bucketed reduction during the backward pass on
+    OVERLAP_MIN_MB = 256.0
+
     #: plain steps that run eagerly before the CUDA graphs are captured (the capture itself warms
     #: every step kind up twice, so none are needed)
     eager_plain_steps_before_capture = 0
@@ -143,7 +148,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                  n_mc_samples: int = 1, var: float = 1., seed: int = None,
                  precond_precision: str = 'bf16x3', clone_norm_outputs: bool = False,
                  cuda_graph: bool = False, comm: str = 'auto', grouped: bool = True,
-                 overlap_grad_reduce: bool = True, bucket_mb: float = 16.0, batch_statistics: bool = True,
+                 overlap_grad_reduce='auto', bucket_mb: float = 16.0, batch_statistics: bool = True,
                  **kwargs):
         super().__init__(model, config, fisher_type=fisher_type, loss_type=loss_type, scale=scale,
                          grad_scale=grad_scale, n_mc_samples=n_mc_samples, var=var, seed=seed, **kwargs)
@@ -177,6 +182,13 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             comm = 'symmetric' if (self.world_size > 1 and device.type == 'cuda') else 'torch'
         self.comm = comm if self.world_size > 1 else 'torch'
         self._arena = None
+        if overlap_grad_reduce == 'auto':
+            # The pull of one step's gradients takes about 2 us per MB per peer once the backward pass
+            # is over; bucketing hides it but adds a copy and a kernel per bucket and lets the pull
+            # kernels share the SMs with the backward pass.  Below this volume the plain reduction
+            # after the backward pass was measured to be the faster one.
+            grad_mb = sum(p.numel() for p in model.parameters() if p.requires_grad) * 4 / 2 ** 20
+            overlap_grad_reduce = grad_mb >= self.OVERLAP_MIN_MB
         self.overlap_grad_reduce = bool(overlap_grad_reduce)
         self.batch_statistics = bool(batch_statistics)
         self.bucket_mb = float(bucket_mb)
@@ -1074,14 +1086,16 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             bm, am = b_hi[:, :m], a_hi[:, :n]
             gh, th = g_hi[:, :n], t_hi[:, :n]
             if x3:
-                s1a, s1b = [bm, bm, b_lo[:, :m]], [gh, g_lo[:, :n], gh]
-                s2a, s2b = [th, th, t_lo[:, :n]], [am, a_lo[:, :n], am]
+                # (hi, lo) parts of both operands: the x3wide flavour loads the four part tiles of a K block
+                # once and forms lo*hi + hi*lo + hi*hi from them on 128 x 256 tiles
+                s1a, s1b = [bm, b_lo[:, :m]], [gh, g_lo[:, :n]]
+                s2a, s2b = [th, t_lo[:, :n]], [am, a_lo[:, :n]]
             else:
                 s1a, s1b, s2a, s2b = [bm], [gh], [th], [am]
             ext.gemm_plan_add(plan1, s1a, s1b, False, False, None, 1.0, 0.0, False, t_hi, t_lo,
-                              0, 0, False, [], 1)
+                              0, 0, False, [], 1, None, False, x3)
             ext.gemm_plan_add(plan2, s2a, s2b, True, False, None, 1.0, 0.0, False, None, None,
-                              dst_ptr, n, False, extra, 1)
+                              dst_ptr, n, False, extra, 1, None, False, x3)
         ext.gemm_plan_finalize(plan1)
         ext.gemm_plan_finalize(plan2)
         table = torch.tensor(rows, dtype=torch.int64, device=dev)

@@ -64,6 +64,8 @@ def parse_args():
     ap.add_argument('--precision', choices=['bf16', 'tf32'], default='bf16',
                     help="compute precision of this library's arm: bf16 autocast (default) or fp32 with TF32")
     ap.add_argument('--no-phases', action='store_true', help='skip the per-step-kind timing after the timed regions')
+    ap.add_argument('--grad-overlap', choices=['auto', 'on', 'off'], default='auto',
+                    help='bucketed gradient reduction during the backward pass (multi-GPU runs of this library)')
     ap.add_argument('--no-graph', action='store_true', help='disable CUDA-graph replay of plain steps')
     ap.add_argument('--nvtx', action='store_true',
                     help="wrap every device-timed step in an NVTX range ('plain_step' / 'curvature_step')")
@@ -154,7 +156,8 @@ def build_ours(args, device, world):
     config = asdl.PreconditioningConfig(data_size=PER_GPU_BATCH, damping=1e-3, ema_decay=0.05,
                                         curvature_upd_interval=10, preconditioner_upd_interval=100)
     gm = asdl.FusedKfacGradientMaker(model, config, precond_precision=args.precond_precision,
-                                     cuda_graph=not args.no_graph)
+                                     cuda_graph=not args.no_graph,
+                                     overlap_grad_reduce={'auto': 'auto', 'on': True, 'off': False}[args.grad_overlap])
     opt = torch.optim.SGD(model.parameters(), lr=1e-4, momentum=0.9)
 
     bf16 = args.precision == 'bf16'

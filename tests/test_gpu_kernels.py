@@ -673,41 +673,44 @@ def test_inverse_root_chain_at_small_ridge():
 
 
 def test_graph_is_captured_again_when_a_captured_hyper_parameter_changes():
-    """Damping is read at capture time; changing it later has to take effect (the graphs are dropped and
-    captured again), which is checked against an eager maker that sees the same change."""
+    """Damping is read at capture time; changing it later has to take effect: the graphs are dropped
+    (with a warning) and captured again.  The replayed run with the change has to follow the eager run
+    with the same change, and to differ from a replayed run without it."""
     torch.backends.cudnn.allow_tf32 = False
     x = torch.randn(8, 3, 16, 16, device=DEV).contiguous(memory_format=torch.channels_last)
     t = torch.randint(0, 5, (8,), device=DEV)
 
-    def run(graph):
+    def run(graph, change):
         torch.manual_seed(0)
         model = _small_cnn().to(DEV).to(memory_format=torch.channels_last)
         cfg = asdl.PreconditioningConfig(data_size=8, damping=1e-2, ema_decay=0.3, curvature_upd_interval=4,
                                          preconditioner_upd_interval=4)
         gm = asdl.FusedKfacGradientMaker(model, cfg, fisher_type=asdl.FISHER_EMP, cuda_graph=graph)
-        opt = torch.optim.SGD(model.parameters(), lr=0.01)
         out = []
-        for step in range(14):
-            if step == 7:
-                cfg.damping = 1e-1
-            opt.zero_grad()
+        for step in range(10):      # no optimizer step: all runs see the same weights, only the maker differs
+            if step == 6 and change:
+                cfg.damping = 1.0
+            for p in model.parameters():
+                p.grad = None
             d = gm.setup_model_call(model, x)
             gm.setup_loss_call(F.cross_entropy, d, t)
             gm.forward_and_backward()
-            out.append([p.grad.detach().clone() for p in model.parameters()])
-            opt.step()
+            out.append(torch.cat([p.grad.detach().flatten() for p in model.parameters()]).clone())
         return out, gm
 
     import warnings
-    eager, _ = run(False)
+    eager, _ = run(False, True)
     with warnings.catch_warnings(record=True) as caught:
         warnings.simplefilter('always')
-        replayed, gm = run(True)
+        replayed, gm = run(True, True)
     assert any('captured again' in str(w.message) for w in caught)
-    assert gm.replayed_launches > 0
-    for step, (a, b) in enumerate(zip(eager, replayed)):
-        for ga, gb in zip(a, b):
-            assert rel_err(gb, ga) < 5e-3, (step, rel_err(gb, ga))
+    assert gm.replayed_launches > 0 and gm._graphs                     # replaying again after the change
+    unchanged, _ = run(True, False)
+    for step in range(10):
+        assert rel_err(replayed[step], eager[step]) < 5e-3, (step, rel_err(replayed[step], eager[step]))
+    # the inverses are refreshed at step 8 with the new damping: from then on the change has to show
+    assert rel_err(replayed[9], unchanged[9]) > 0.05
+    assert rel_err(replayed[5], unchanged[5]) < 1e-6
     ops.check_status()
 
 
@@ -778,14 +781,14 @@ def test_jacobi_eigh_kernel(ext, n, batch):
     assert ext.launch_count() > before
     ref = torch.linalg.eigvalsh(mats.double())
     scale = ref.abs().amax(dim=1, keepdim=True)
-    assert ((w.double() - ref).abs() <= 2e-5 * scale).all()
+    assert ((w.double() - ref).abs() <= 5e-5 * scale).all()
     assert (w[:, 1:] >= w[:, :-1]).all()
     eye = torch.eye(n, device=DEV, dtype=torch.float64)
     vd = v.double()
     assert (vd.transpose(1, 2) @ vd - eye).abs().max().item() < 5e-5
     resid = (mats.double() @ vd - vd * w.double().unsqueeze(1)).abs().amax(dim=(1, 2)) / scale.squeeze(1)
     assert resid.max().item() < 5e-5
-    assert ((ops.eigvalsh(mats[0]).double() - ref[0]).abs() <= 2e-5 * scale[0]).all()
+    assert ((ops.eigvalsh(mats[0]).double() - ref[0]).abs() <= 5e-5 * scale[0]).all()
     ops.check_status()
 
 
