@@ -19,14 +19,14 @@ void im2col_bf16(at::Tensor x, at::Tensor out, c10::optional<at::Tensor> out_lo,
                  std::vector<int64_t> padding, std::vector<int64_t> dilation, bool c_major);
 void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
                       bool b_kmajor, int64_t dst_ptr, int64_t ldc, double alpha, bool sym, int64_t atomic,
-                      std::vector<int64_t> extra_ptrs, int64_t nsplit);
+                      std::vector<int64_t> extra_ptrs, int64_t nsplit, bool mcast);
 int64_t gemm_plan_new();
 void gemm_plan_free(int64_t id);
 void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs,
                    bool a_kmajor, bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta,
                    bool sym, c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
                    int64_t dst_ptr, int64_t ldc, bool atomic, std::vector<int64_t> extra_ptrs,
-                   int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3, bool x3wide);
+                   int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3, bool x3wide, bool mcast);
 void gemm_plan_finalize(int64_t id);
 void gemm_plan_run(int64_t id);
 void cast_pad_bf16_grouped(at::Tensor table, int64_t count);
@@ -48,7 +48,8 @@ std::vector<at::Tensor> ln_forward(at::Tensor x, at::Tensor weight, at::Tensor b
 std::vector<at::Tensor> ln_backward(at::Tensor x, at::Tensor dy, at::Tensor weight, at::Tensor mean,
                                     at::Tensor rstd);
 void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot, int64_t wait_ms);
-void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale);
+void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale,
+                          int64_t mc_ptr);
 void symm_bcast_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, int64_t mc_ptr);
 void symm_bucket_reduce(at::Tensor peers, int64_t rank, int64_t world, int64_t slot, at::Tensor segs, double scale,
                         int64_t mc_ptr, int64_t wait_ms, int64_t blocks);
@@ -83,13 +84,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("reserve_scratch", &b200::reserve_scratch);
   m.def("cast_pad_bf16", &b200::cast_pad_bf16);
   m.def("im2col_bf16", &b200::im2col_bf16);
-  m.def("umma_gemm_to_ptr", &b200::umma_gemm_to_ptr);
+  m.def("umma_gemm_to_ptr", &b200::umma_gemm_to_ptr, py::arg("a_segs"), py::arg("b_segs"), py::arg("a_kmajor"),
+        py::arg("b_kmajor"), py::arg("dst_ptr"), py::arg("ldc"), py::arg("alpha"), py::arg("sym"), py::arg("atomic"),
+        py::arg("extra_ptrs"), py::arg("nsplit"), py::arg("mcast") = false);
   m.def("gemm_plan_new", &b200::gemm_plan_new);
   m.def("gemm_plan_free", &b200::gemm_plan_free);
   m.def("gemm_plan_add", &b200::gemm_plan_add, py::arg("plan"), py::arg("a_segs"), py::arg("b_segs"),
         py::arg("a_kmajor"), py::arg("b_kmajor"), py::arg("C"), py::arg("alpha"), py::arg("beta"), py::arg("sym"),
         py::arg("out_hi"), py::arg("out_lo"), py::arg("dst_ptr"), py::arg("ldc"), py::arg("atomic"),
-        py::arg("extra_ptrs"), py::arg("nsplit"), py::arg("out_mid") = py::none(), py::arg("split3") = false, py::arg("x3wide") = false);
+        py::arg("extra_ptrs"), py::arg("nsplit"), py::arg("out_mid") = py::none(), py::arg("split3") = false, py::arg("x3wide") = false, py::arg("mcast") = false);
   m.def("gemm_plan_finalize", &b200::gemm_plan_finalize);
   m.def("gemm_plan_run", &b200::gemm_plan_run);
   m.def("cast_pad_bf16_grouped", &b200::cast_pad_bf16_grouped);
@@ -103,7 +106,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ln_forward", &b200::ln_forward);
   m.def("ln_backward", &b200::ln_backward);
   m.def("symm_barrier", &b200::symm_barrier);
-  m.def("symm_reduce_segments", &b200::symm_reduce_segments);
+  m.def("symm_reduce_segments", &b200::symm_reduce_segments, py::arg("peers"), py::arg("rank"), py::arg("world"),
+        py::arg("segs"), py::arg("scale"), py::arg("mc_ptr") = 0);
   m.def("symm_bcast_segments", &b200::symm_bcast_segments, py::arg("peers"), py::arg("rank"), py::arg("world"),
         py::arg("segs"), py::arg("mc_ptr") = 0);
   m.def("symm_bucket_reduce", &b200::symm_bucket_reduce);

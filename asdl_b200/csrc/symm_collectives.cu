@@ -105,13 +105,16 @@ __global__ void symm_barrier_kernel(const long long* peers, int rank, int world,
 }
 
 __global__ void symm_reduce_segments_kernel(const long long* peers, int rank, int world,
-                                            const Seg* segs, float scale) {
+                                            const Seg* segs, float scale, const float* mc_base) {
   const Seg s = segs[blockIdx.y];
   float* local = reinterpret_cast<float*>(peers[rank]) + s.off;
   const long long n4 = s.numel >> 2;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (mc_base != nullptr) {   // the switch adds the ranks' copies: one transaction per 16 bytes
+      acc = multimem_ld_reduce_f4(mc_base + s.off + 4 * i);
+    } else
     for (int r = 0; r < world; ++r) {
       const float4 v = ld_peer_f4(reinterpret_cast<const float*>(peers[r]) + s.off + 4 * i);
       acc.x += v.x;
@@ -355,7 +358,8 @@ void symm_barrier(at::Tensor peers, int64_t rank, int64_t world, int64_t slot, i
   count_launch();
 }
 
-void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale) {
+void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Tensor segs, double scale,
+                          int64_t mc_ptr) {
   check_table(peers, static_cast<int>(world));
   check_segs(segs);
   if (segs.size(0) == 0) return;
@@ -366,7 +370,7 @@ void symm_reduce_segments(at::Tensor peers, int64_t rank, int64_t world, at::Ten
   symm_reduce_segments_kernel<<<grid, 256, 0, stream>>>(
       reinterpret_cast<const long long*>(peers.data_ptr<int64_t>()), static_cast<int>(rank),
       static_cast<int>(world), reinterpret_cast<const Seg*>(segs.data_ptr<int64_t>()),
-      static_cast<float>(scale));
+      static_cast<float>(scale), reinterpret_cast<const float*>(mc_ptr));
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch();
 }

@@ -425,7 +425,7 @@ void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, b
 // `extra_ptrs` receive plain copies of it (non-atomic mode only).  All destinations use `ldc`.
 void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, bool a_kmajor,
                       bool b_kmajor, int64_t dst_ptr, int64_t ldc, double alpha, bool sym, int64_t atomic,
-                      std::vector<int64_t> extra_ptrs, int64_t nsplit) {
+                      std::vector<int64_t> extra_ptrs, int64_t nsplit, bool mcast) {
   TORCH_CHECK(!a_segs.empty(), "no operands");
   TORCH_CHECK(dst_ptr != 0 && (dst_ptr & 15) == 0, "destination must be a 16-byte aligned device address");
   TORCH_CHECK(static_cast<int>(extra_ptrs.size()) <= G2_MAX_EXTRA, "too many extra destinations");
@@ -450,6 +450,10 @@ void umma_gemm_to_ptr(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_
   for (int e = 0; e < P.n_extra; ++e) {
     TORCH_CHECK((extra_ptrs[e] & 15) == 0, "destinations must be 16-byte aligned");
     P.C_extra[e] = reinterpret_cast<float*>(extra_ptrs[e]);
+  }
+  if (mcast) {
+    TORCH_CHECK(!sym && atomic == 0, "multicast destinations take the plain result of a non-symmetric product");
+    P.flags |= G2F_MCAST;
   }
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
   if (!batch_append(P, dev, nsplit, stream, a_segs, b_segs, c10::nullopt)) {
@@ -487,7 +491,7 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
                    bool a_kmajor, bool b_kmajor, c10::optional<at::Tensor> C, double alpha, double beta,
                    bool sym, c10::optional<at::Tensor> out_hi, c10::optional<at::Tensor> out_lo,
                    int64_t dst_ptr, int64_t ldc, bool atomic, std::vector<int64_t> extra_ptrs,
-                   int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3, bool x3wide) {
+                   int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3, bool x3wide, bool mcast) {
   auto it = g_plans.find(id);
   TORCH_CHECK(it != g_plans.end() && !it->second.finalized, "unknown or finalized plan");
   GemmPlan& plan = it->second;
@@ -503,7 +507,7 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
   g_wide_mode = 0;  // the tiles of a plan share one kernel instantiation: 128-wide
   try {
     gemm_fill_problem(P, a_segs, b_segs, a_kmajor, b_kmajor, C, alpha, beta, sym, out_hi, out_mid, out_lo,
-                      nsplit <= 0 ? 1 : nsplit, split3, g2_sm_count(plan.dev), /*allow_no_output=*/dst_ptr != 0, x3wide);
+                      nsplit <= 0 ? 1 : nsplit, split3, g2_sm_count(plan.dev), /*allow_no_output=*/dst_ptr != 0 || !extra_ptrs.empty(), x3wide);
   } catch (...) {
     g_wide_mode = saved_mode;
     throw;
@@ -513,6 +517,8 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
     TORCH_CHECK((dst_ptr & 15) == 0, "destination must be 16-byte aligned");
     P.C = reinterpret_cast<float*>(dst_ptr);
     P.Cin = P.C;
+  }
+  if (dst_ptr != 0 || !extra_ptrs.empty()) {
     P.ldc = static_cast<int>(ldc);
     TORCH_CHECK(P.ldc >= P.N, "ldc is smaller than the number of columns");
   }
@@ -521,6 +527,10 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
   TORCH_CHECK(!(atomic && !extra_ptrs.empty()), "extra destinations are not supported in atomic mode");
   P.n_extra = static_cast<int>(extra_ptrs.size());
   for (int e = 0; e < P.n_extra; ++e) P.C_extra[e] = reinterpret_cast<float*>(extra_ptrs[e]);
+  if (mcast) {
+    TORCH_CHECK(!sym && !atomic, "multicast destinations take the plain result of a non-symmetric product");
+    P.flags |= G2F_MCAST;
+  }
   plan.problems.push_back(P);
   std::vector<at::Tensor> keep = a_segs;
   keep.insert(keep.end(), b_segs.begin(), b_segs.end());

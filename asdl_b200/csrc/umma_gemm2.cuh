@@ -72,6 +72,7 @@ enum : int {
   G2F_WIDE = 64,      // the problem's tensor maps and tile grid are laid out for BN = 256
   G2F_SPLIT3 = 128,   // tmA[0..2] / tmB[0..2] are the (hi, mid, lo) parts of the operands
   G2F_SPLIT2 = 256,   // tmA[0..1] / tmB[0..1] are the (hi, lo) parts of the operands ("bf16x3", wide tiles)
+  G2F_MCAST = 512,    // C_extra[] are NVLS multicast addresses: one multimem.st reaches every GPU of the group
 };
 
 enum : int {
@@ -219,6 +220,15 @@ __device__ __forceinline__ void g2_red_add_v4_f32(float* p, float a, float b, fl
                : "memory");
 }
 
+__device__ __forceinline__ void g2_multimem_st_v4(float* mc, float a, float b, float c, float d) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void g2_multimem_st_f32(float* mc, float a) {
+  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc), "f"(a) : "memory");
+}
+
 // 16-byte accesses need a 16-byte aligned row start: ldc a multiple of 4 and an aligned base
 __device__ __forceinline__ bool g2_vec_ok(const float* base, int ldc) {
   return ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(base) & 15) == 0);
@@ -316,7 +326,17 @@ __device__ __forceinline__ void g2_store_chunk(const G2Epi& P, const float* v, i
   for (int e = 0; e < P.n_extra; ++e) {  // plain (non-symmetric) result replicated to peers
     float* const extra = P.full->C_extra[e];
     float* c = extra + static_cast<size_t>(gr) * P.ldc + gc0;
-    if (full && g2_vec_ok(extra, P.ldc)) {
+    if (P.flags & G2F_MCAST) {   // through the switch: the store lands in every GPU's copy
+      if (full && g2_vec_ok(extra, P.ldc)) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          g2_multimem_st_v4(c + 4 * j, out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (gc0 + j < P.N) g2_multimem_st_f32(c + j, out[j]);
+      }
+    } else if (full && g2_vec_ok(extra, P.ldc)) {
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         *reinterpret_cast<float4*>(c + 4 * j) =
@@ -842,7 +862,13 @@ splitk_reduce2_kernel(const __grid_constant__ GemmProblem2 single, const GemmPro
     const bool keep = inb && !(diag_tile && gc > gr);
     if (keep) {
       if (P.C != nullptr) P.C[static_cast<size_t>(gr) * P.ldc + gc] = val;
-      for (int e = 0; e < P.n_extra; ++e) P.full->C_extra[e][static_cast<size_t>(gr) * P.ldc + gc] = val;
+      for (int e = 0; e < P.n_extra; ++e) {
+        float* dst = P.full->C_extra[e] + static_cast<size_t>(gr) * P.ldc + gc;
+        if (P.flags & G2F_MCAST)
+          g2_multimem_st_f32(dst, val);
+        else
+          *dst = val;
+      }
       if (P.out_hi != nullptr) {
         const size_t o = static_cast<size_t>(gr) * P.ld_out + gc;
         const size_t om = static_cast<size_t>(gc) * P.ld_out + gr;

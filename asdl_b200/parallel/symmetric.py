@@ -110,6 +110,10 @@ class SymmetricArena:
     def ptr(self, rank: int, offset: int) -> int:
         return self.peer_ptrs[rank] + 4 * offset
 
+    def mc_ptr(self, offset: int) -> int:
+        """Multicast address of ``offset`` (a store to it reaches every rank's copy); 0 without NVLS."""
+        return self.multicast_ptr + 4 * offset if self.multicast_ptr else 0
+
     def segments(self, pairs: Sequence[Tuple[int, int]]) -> torch.Tensor:
         """Device table of (offset, numel rounded up to 4) rows for the segment kernels."""
         rows = [[int(o), _round_up(int(n), 4)] for o, n in pairs]
@@ -125,8 +129,10 @@ class SymmetricArena:
         ops.extension().symm_barrier(self.peers_dev, self.rank, self.world, slot, int(self.barrier_wait_ms))
 
     def reduce_segments(self, segs: torch.Tensor, scale: float):
-        """local[seg] <- scale * sum over ranks of their [seg] (pull over NVLink)."""
-        ops.extension().symm_reduce_segments(self.peers_dev, self.rank, self.world, segs, float(scale))
+        """local[seg] <- scale * sum over ranks of their [seg] (pull over NVLink; ``multimem.ld_reduce``
+        through the switch where the buffer has a multicast mapping)."""
+        ops.extension().symm_reduce_segments(self.peers_dev, self.rank, self.world, segs, float(scale),
+                                             self.multicast_ptr)
 
     def bcast_segments(self, segs: torch.Tensor):
         """every peer's [seg] <- local[seg] (push over NVLink; one multimem.st per 16 bytes where the

@@ -139,6 +139,13 @@ class FusedKfacGradientMaker(KfacGradientMaker):
     #: bucketed reduction during the backward pass on
     OVERLAP_MIN_MB = 256.0
 
+    #: Replicate the preconditioned gradients from the GEMM epilogue with ``multimem.st`` (one store through
+    #: the NVSwitch instead of one store per peer).  Off: in the epilogue every lane of a warp holds a
+    #: different row, so a store instruction is 32 separate 16-byte multicast writes, and on 2 GPUs the
+    #: step was measured 0.48 ms SLOWER with it than with plain peer stores (7.11 vs 6.63 ms); the coalesced
+    #: segment kernels (gradient pull, broadcast of the rest) do use the multicast mapping.
+    multicast_epilogue = False
+
     #: plain steps that run eagerly before the CUDA graphs are captured (the capture itself warms
     #: every step kind up twice, so none are needed)
     eager_plain_steps_before_capture = 0
@@ -1061,6 +1068,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         for st in todo:
             m, n = st.d_out, st.d_in
             w = st.module.weight
+            mcast = False
             if arena is None:
                 region = flat[off:off + m * n]
                 off += (m * n + 63) // 64 * 64
@@ -1068,8 +1076,12 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             else:
                 a_off, view = self._grad_slot[w]
                 region = arena.buffer[a_off:a_off + m * n]
-                dst_ptr = arena.ptr(arena.rank, a_off)
-                extra = [arena.ptr(r, a_off) for r in range(arena.world) if r != arena.rank]
+                if arena.multicast_ptr and self.multicast_epilogue:
+                    # one multimem.st per 16 bytes reaches every rank, this one included
+                    dst_ptr, extra, mcast = 0, [arena.mc_ptr(a_off)], True
+                else:
+                    dst_ptr = arena.ptr(arena.rank, a_off)
+                    extra = [arena.ptr(r, a_off) for r in range(arena.world) if r != arena.rank]
             # the region holds the gradient as a contiguous [d_out, d_in] matrix in the factor's order
             if w.ndim == 4 and st.khwc:
                 view = region.view(m, w.shape[2], w.shape[3], w.shape[1]).permute(0, 3, 1, 2)
@@ -1095,7 +1107,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             ext.gemm_plan_add(plan1, s1a, s1b, False, False, None, 1.0, 0.0, False, t_hi, t_lo,
                               0, 0, False, [], 1, None, False, x3)
             ext.gemm_plan_add(plan2, s2a, s2b, True, False, None, 1.0, 0.0, False, None, None,
-                              dst_ptr, n, False, extra, 1, None, False, x3)
+                              dst_ptr, n, False, extra, 1, None, False, x3, mcast)
         ext.gemm_plan_finalize(plan1)
         ext.gemm_plan_finalize(plan2)
         table = torch.tensor(rows, dtype=torch.int64, device=dev)
