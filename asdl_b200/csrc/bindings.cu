@@ -66,6 +66,7 @@ void ln_unitwise_stats(at::Tensor y, at::Tensor g, at::Tensor weight, at::Tensor
 void unitwise_inverse_mt(std::vector<std::vector<int64_t>> rows, double damping);
 void unitwise_apply_mt(std::vector<std::vector<int64_t>> rows, double grad_scale);
 void bias_precondition_mt(std::vector<std::vector<int64_t>> rows, double grad_scale);
+at::Tensor batched_mv(at::Tensor a, at::Tensor x);
 void diag_linear_stats(at::Tensor a, at::Tensor g, at::Tensor out, c10::optional<at::Tensor> out_bias, double alpha,
                        double beta);
 }  // namespace b200
@@ -123,4 +124,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("unitwise_apply_mt", &b200::unitwise_apply_mt);
   m.def("bias_precondition_mt", &b200::bias_precondition_mt);
   m.def("diag_linear_stats", &b200::diag_linear_stats);
+  m.def("batched_mv", &b200::batched_mv);
 }

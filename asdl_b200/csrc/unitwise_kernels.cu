@@ -329,3 +329,54 @@ void diag_linear_stats(at::Tensor a, at::Tensor g, at::Tensor out, c10::optional
 }
 
 }  // namespace b200
+
+// ---- batched matrix-vector product: y[b] = A[b] x[b] for b matrices of one size -----------------------
+// The power iteration of Shampoo's inverse roots (asdl/precondition/shampoo.py:532-558) is a chain of such
+// products on a batch of statistics; one warp takes one row, so a step reads every matrix exactly once.
+namespace b200 {
+namespace {
+__global__ void __launch_bounds__(256) batched_mv_kernel(const float* __restrict__ a, const float* __restrict__ x,
+                                                         float* __restrict__ y, int n) {
+  const float* A = a + static_cast<size_t>(blockIdx.y) * n * n;
+  const float* xv = x + static_cast<size_t>(blockIdx.y) * n;
+  float* yv = y + static_cast<size_t>(blockIdx.y) * n;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int r = blockIdx.x * 8 + warp; r < n; r += gridDim.x * 8) {
+    const float* row = A + static_cast<size_t>(r) * n;
+    float acc = 0.f;
+    if ((n & 3) == 0) {
+      for (int c = 4 * lane; c < n; c += 128) {
+        const float4 av = *reinterpret_cast<const float4*>(row + c);
+        const float4 xx = *reinterpret_cast<const float4*>(xv + c);
+        acc = fmaf(av.x, xx.x, fmaf(av.y, xx.y, fmaf(av.z, xx.z, fmaf(av.w, xx.w, acc))));
+      }
+    } else {
+      for (int c = lane; c < n; c += 32) acc = fmaf(row[c], xv[c], acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) yv[r] = acc;
+  }
+}
+}  // namespace
+
+// a: [b, n, n] fp32 contiguous, x: [b, n]; returns [b, n]
+at::Tensor batched_mv(at::Tensor a, at::Tensor x) {
+  TORCH_CHECK(a.is_cuda() && x.is_cuda() && a.scalar_type() == at::kFloat && x.scalar_type() == at::kFloat && a.dim() == 3 &&
+                  a.size(1) == a.size(2) && x.dim() == 2 && x.size(0) == a.size(0) && x.size(1) == a.size(1) &&
+                  a.is_contiguous() && x.is_contiguous(), "a [b, n, n] and x [b, n] must be contiguous fp32 CUDA tensors");
+  const int dev = a.get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  auto y = at::empty_like(x);
+  const int n = static_cast<int>(a.size(1));
+  if (a.size(0) == 0 || n == 0) return y;
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0,
+              "16-byte alignment required");
+  const unsigned gx = static_cast<unsigned>(std::max(1, std::min((n + 7) / 8, 128)));
+  batched_mv_kernel<<<dim3(gx, static_cast<unsigned>(a.size(0))), 256, 0, at::cuda::getCurrentCUDAStream(dev).stream()>>>(
+      a.data_ptr<float>(), x.data_ptr<float>(), y.data_ptr<float>(), n);
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return y;
+}
+}  // namespace b200

@@ -52,10 +52,19 @@ class ShampooGradientMaker(PreconditionedGradientMaker):
         sync_group: process group for data-parallel runs.
         grouped: on CUDA, process all blocks of all 2-D parameters with grouped kernel launches
             (statistics, and the application of the roots) instead of a few launches per block.
+        comm: data-parallel transport.  ``'symmetric'`` keeps every gradient in one NVLink symmetric
+            buffer and moves them with the library's own kernels: after a flag barrier every owner
+            pulls the sum of its parameters' gradients (``multimem.ld_reduce`` through the NVSwitch
+            where available, plain peer loads otherwise), and after preconditioning pushes the result
+            to all ranks (``multimem.st`` / peer stores) - no ``torch.cat`` packing, no NCCL call
+            (asdl/precondition/shampoo.py:225-297 packs flat vectors and calls ``dist.reduce`` /
+            ``dist.broadcast``).  ``'torch'`` uses ``torch.distributed`` (any backend).  ``'auto'``
+            picks ``'symmetric'`` for multi-rank CUDA runs.
     """
 
     def __init__(self, model: torch.nn.Module, config: PreconditioningConfig,
-                 block_size: int = _invalid, sync_group: dist.ProcessGroup = None, grouped: bool = True):
+                 block_size: int = _invalid, sync_group: dist.ProcessGroup = None, grouped: bool = True,
+                 comm: str = 'auto'):
         super().__init__(model, config)
         self.sync_group = sync_group
         self.grouped = grouped
@@ -75,6 +84,52 @@ class ShampooGradientMaker(PreconditionedGradientMaker):
             if self.partitioned_modules[i] == self.world_rank:
                 self.preconditioners.append(Preconditioner(p, config, block_size=block_size))
                 self._owned.append(i)
+        if comm not in ('auto', 'symmetric', 'torch'):
+            raise ValueError("comm has to be 'auto', 'symmetric' or 'torch'")
+        device = next(model.parameters()).device
+        if comm == 'auto':
+            comm = 'symmetric' if (self.world_size > 1 and device.type == 'cuda') else 'torch'
+        self.comm = comm if self.world_size > 1 else 'torch'
+        self._arena = None
+        if self.comm == 'symmetric':
+            self._setup_symmetric(device)
+
+    def _setup_symmetric(self, device):
+        """One symmetric buffer with a slot per trainable parameter.  Preconditioned parameters belong to
+        their Shampoo owner, all others (biases, normalisation parameters) to ranks in turn; an owner
+        pulls the averaged gradient of what it owns and pushes the final gradient to everybody."""
+        from ..parallel.symmetric import SymmetricArena, _round_up
+        params = [p for p in self.model.parameters() if p.requires_grad]
+        total = sum(_round_up(p.numel(), 64) for p in params) + 64
+        arena = self._arena = SymmetricArena(total, group=self.sync_group, device=device)
+        owner_of = {id(p): o for p, o in zip(self._params, self.partitioned_modules)}
+        self._sym_params, self._grad_slot, owned = params, {}, []
+        rest = 0
+        for p in params:
+            off, flat = arena.alloc(p.numel())
+            self._grad_slot[p] = flat.as_strided(p.shape, p.stride()) if p.is_contiguous() else flat.view(p.shape)
+            owner = owner_of.get(id(p))
+            if owner is None:
+                owner = rest % self.world_size
+                rest += 1
+            if owner == self.world_rank:
+                owned.append((off, p.numel()))
+        self._owned_segs = arena.segments(owned)
+
+    def _bind_grads_to_arena(self):
+        """Gradients live in the symmetric buffer; anything autograd allocated elsewhere is moved there."""
+        with torch.no_grad():
+            dst, src = [], []
+            for p in self._sym_params:
+                view = self._grad_slot[p]
+                if p.grad is None:
+                    view.zero_()
+                elif p.grad.data_ptr() != view.data_ptr():
+                    dst.append(view)
+                    src.append(p.grad)
+                p.grad = view
+            if dst:
+                torch._foreach_copy_(dst, src)
 
     def get_distr_prec_partition(self):
         """Owner rank per preconditioned parameter (second return value).  The first value lists,
@@ -173,6 +228,13 @@ class ShampooGradientMaker(PreconditionedGradientMaker):
     def reduce_scatter_grads(self):
         """Average the gradients of every preconditioned parameter onto its owner and all other
         gradients onto everyone."""
+        if self._arena is not None:
+            # barrier (every rank's gradients are in its buffer) -> owners pull the sums of what they own
+            self._bind_grads_to_arena()
+            self._arena.barrier()
+            self._arena.reduce_segments(self._owned_segs, 1.0 / self.world_size)
+            self._grads_synced = True
+            return
         handles = []
         for owner, grads in self._groups().items():
             if not grads:
@@ -198,6 +260,11 @@ class ShampooGradientMaker(PreconditionedGradientMaker):
 
     def all_gather_grads(self):
         """Owners broadcast their preconditioned gradients."""
+        if self._arena is not None:
+            self._bind_grads_to_arena()   # a block-wise path may have replaced param.grad
+            self._arena.bcast_segments(self._owned_segs)
+            self._arena.barrier()
+            return
         handles = []
         for owner, grads in self._groups().items():
             if not grads:
@@ -520,11 +587,14 @@ def _power_iteration_batched(mats, num_iters=100, error_tolerance=1e-6, check_ev
     """Largest eigenvalue of each PSD matrix in a batch; the loop is left only when every matrix
     has converged, checked on the host once per ``check_every`` iterations."""
     b, n, _ = mats.shape
+    # CUDA fp32: the library's batched matrix-vector kernel (a warp per row, every matrix read once per step)
+    ext = (ops.extension() if (mats.is_cuda and mats.dtype == torch.float32 and mats.is_contiguous()
+                               and ops.get_backend() != 'torch') else None)
     v = torch.rand(b, n, device=mats.device, dtype=mats.dtype) * 2 - 1
     value = torch.zeros(b, device=mats.device, dtype=mats.dtype)
     for it in range(num_iters):
         v = v / torch.linalg.vector_norm(v, dim=1, keepdim=True).clamp_min(1e-30)
-        mv = torch.bmm(mats, v.unsqueeze(2)).squeeze(2)
+        mv = ext.batched_mv(mats, v) if ext is not None else torch.bmm(mats, v.unsqueeze(2)).squeeze(2)
         new_value = (v * mv).sum(dim=1)
         err = (new_value - value).abs()
         value, v = new_value, mv

@@ -145,6 +145,70 @@ def bench_roots(timer, b, n, p, ridge):
          torch_bmm_rel_err=float(f"{out['never_err']:.2e}"), speedup_vs_torch=round(out['never'] / out['auto'], 2))
 
 
+def bench_layouts(timer, m, n, k, flops_peak, src):
+    """One bf16 GEMM in the four operand layouts (MN-major = [K, M] row-major, K-major = [M, K])."""
+    ext = ops.extension()
+    a = torch.randn(k, m, device='cuda').to(torch.bfloat16)
+    b = torch.randn(k, n, device='cuda').to(torch.bfloat16)
+    ak, bk = a.T.contiguous(), b.T.contiguous()
+    out = torch.empty(m, n, device='cuda')
+    res = {}
+    for name, (x, y, xk, yk) in {'mn_mn': (a, b, False, False), 'k_k': (ak, bk, True, True),
+                                 'k_mn': (ak, b, True, False), 'mn_k': (a, bk, False, True)}.items():
+        res[name] = round(timer(lambda: ext.umma_gemm([x], [y], xk, yk, out, 1.0, 0.0, False, None, None, 1)), 4)
+    ms_lib = timer(lambda: torch.matmul(ak, b))
+    fl = 2.0 * m * n * k
+    emit(case='gemm_bf16_layouts', m=m, n=n, k=k, ms=res, cublas_ms=round(ms_lib, 4),
+         frac_of_peak_flops={kk: round(fl / (v * 1e-3) / flops_peak, 3) for kk, v in res.items()}, peak_source=src)
+
+
+def bench_eigh(timer, batch, n):
+    """Batched Jacobi eigensolver (n <= 128) against torch.linalg.eigh (cuSOLVER)."""
+    a = torch.randn(batch, n, 2 * n, device='cuda')
+    mats = a @ a.transpose(1, 2) / (2 * n)
+    ms = timer(lambda: ops.eigh(mats))
+    ms_lib = timer(lambda: torch.linalg.eigh(mats))
+    w, v = ops.eigh(mats)
+    ref = torch.linalg.eigvalsh(mats.double())
+    err = ((w.double() - ref).abs().max() / ref.abs().max()).item()
+    emit(case='jacobi_eigh_fp32', batch=batch, n=n, ms=round(ms, 4), cusolver_ms=round(ms_lib, 4),
+         speedup_vs_cusolver=round(ms_lib / ms, 2), max_rel_eigenvalue_error=float(f'{err:.2e}'))
+
+
+def bench_lnstats(timer, rows, d, hbm, src):
+    """Unit-wise LayerNorm statistics: one pass over y and g against the chain of PyTorch elementwise ops."""
+    y = torch.randn(rows, d, device='cuda').to(torch.bfloat16)
+    g = torch.randn(rows, d, device='cuda').to(torch.bfloat16)
+    w, b = torch.rand(d, device='cuda') + 0.5, torch.randn(d, device='cuda')
+    out = torch.zeros(d, 2, 2, device='cuda')
+    ms = timer(lambda: ops.layernorm_unitwise_stats(y, g, w, b, out=out, alpha=0.05, beta=0.95))
+    ops.set_backend('torch')
+    ms_lib = timer(lambda: ops.layernorm_unitwise_stats(y, g, w, b, out=out, alpha=0.05, beta=0.95))
+    ops.set_backend('auto')
+    by = 2.0 * 2 * rows * d
+    emit(case='layernorm_unitwise_stats_bf16', rows=rows, d=d, ms=round(ms, 4), gbs=round(by / ms / 1e6, 1),
+         frac_of_peak_hbm=round(by / (ms * 1e-3) / hbm, 3), peak_source=src, torch_ms=round(ms_lib, 4),
+         speedup_vs_torch=round(ms_lib / ms, 2))
+
+
+def bench_symm(timer, world, mb, hbm, src):
+    """The segment kernels of the NVLink transport on ranks emulated on ONE GPU (every "peer" buffer is
+    local memory, so this measures the kernels against HBM, not the link): owner pull-reduce and push."""
+    from asdl_b200.parallel.symmetric import SymmetricArena
+    numel = int(mb * (1 << 20) / 4)
+    arenas = SymmetricArena.local_group(numel + 1024, world)
+    offs = [a.alloc(numel)[0] for a in arenas]
+    for a in arenas:
+        a.buffer.normal_()
+    segs = arenas[0].segments([(offs[0], numel)])
+    ms_r = timer(lambda: arenas[0].reduce_segments(segs, 1.0 / world))
+    ms_b = timer(lambda: arenas[0].bcast_segments(segs))
+    emit(case='symm_reduce_segments_emulated', world=world, mbytes=mb, ms=round(ms_r, 4),
+         frac_of_peak_hbm=round(4.0 * numel * (world + 1) / (ms_r * 1e-3) / hbm, 3), peak_source=src)
+    emit(case='symm_bcast_segments_emulated', world=world, mbytes=mb, ms=round(ms_b, 4),
+         frac_of_peak_hbm=round(4.0 * numel * world / (ms_b * 1e-3) / hbm, 3), peak_source=src)
+
+
 def bench_im2col(timer, n, c, hw, k, stride, pad, hbm, flops_peak, src):
     ext = ops.extension()
     x = torch.randn(n, c, hw, hw, device='cuda').to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
@@ -184,7 +248,7 @@ def bench_batchnorm(timer, n, c, hw, hbm, flops_peak, src):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--only', default=None, choices=['syrk', 'syrk_x3', 'precond', 'inverse', 'roots', 'im2col', 'batchnorm'])
+    ap.add_argument('--only', default=None, choices=['syrk', 'syrk_x3', 'layouts', 'precond', 'inverse', 'roots', 'eigh', 'lnstats', 'symm', 'im2col', 'batchnorm'])
     ap.add_argument('--wide', type=int, default=0, help='tile width policy of the GEMM: 0 = 128, 1 = 256 for large outputs, 2 = 256 wherever legal')
     ap.add_argument('--chol', default=None, choices=['tensor_core', 'cuda_core'], help='grouped inverse backend')
     ap.add_argument('--rows', type=int, default=None)
@@ -222,6 +286,17 @@ def main():
     if want('roots'):
         for b, n, p, ridge in [(8, 1024, 4, 1e-6), (30, 1024, 4, 1e-6), (30, 768, 4, 1e-6)]:
             bench_roots(timer, b, n, p, ridge)
+    if want('layouts'):
+        for m, n, k in [(4096, 4096, 8192), (2048, 2048, 2048)]:
+            bench_layouts(timer, m, n, k, fl, src)
+    if want('eigh'):
+        for batch, n in [(64, 64), (16, 128), (256, 32)]:
+            bench_eigh(timer, batch, n)
+    if want('lnstats'):
+        for rows, d in [(8192, 1024), (12608, 768)]:
+            bench_lnstats(timer, rows, d, hbm, src)
+    if want('symm'):
+        bench_symm(timer, 4, 64, hbm, src)
     if want('im2col'):
         bench_im2col(timer, 32, 64, 56, 3, 1, 1, hbm, fl, src)
         bench_im2col(timer, 32, 256, 14, 3, 1, 1, hbm, fl, src)

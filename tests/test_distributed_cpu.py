@@ -144,6 +144,55 @@ def test_vanished_rank_ends_the_collective_with_an_error():
     assert outcome.startswith('error:'), outcome
 
 
+def _vanishing_maker_worker(rank, world, port, out_dir):
+    """A data-parallel maker runs one step on two ranks; rank 1 then leaves between steps.  Rank 0's next
+    step has to raise within the process-group timeout, leave no hooks on the model and not advance
+    the maker's step counter."""
+    dist.init_process_group('gloo', init_method=f'tcp://127.0.0.1:{port}', rank=rank, world_size=world,
+                            timeout=timedelta(seconds=5))
+    x, t = _data(4 * world)
+    n = x.shape[0] // world
+    model = _net()
+    gm = _make('fused', model, n)
+    xs, ts = x[rank * n:(rank + 1) * n], t[rank * n:(rank + 1) * n]
+
+    def one_step():
+        for p in model.parameters():
+            p.grad = None
+        d = gm.setup_model_call(model, xs)
+        gm.setup_loss_call(F.cross_entropy, d, ts)
+        gm.forward_and_backward()
+
+    one_step()
+    if rank == 1:
+        os._exit(0)                      # leaves between steps, with nothing in flight
+    before = gm.state['step']
+    try:
+        one_step()
+        outcome = 'completed'
+    except Exception as exc:
+        hooks = sum(len(m._forward_hooks) + len(m._forward_pre_hooks) + len(m._backward_hooks) for m in model.modules())
+        outcome = f'error:{type(exc).__name__}:hooks={hooks}:step_advanced={gm.state["step"] != before}'
+    with open(os.path.join(out_dir, 'rank0.txt'), 'w') as fh:
+        fh.write(outcome)
+    os._exit(0)
+
+
+def test_vanished_rank_makes_the_next_maker_step_raise_and_leaves_the_model_clean():
+    with tempfile.TemporaryDirectory() as out_dir:
+        ctx = mp.get_context('spawn')
+        port = _free_port()
+        procs = [ctx.Process(target=_vanishing_maker_worker, args=(r, 2, port, out_dir)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout=120)
+            assert not p.is_alive()
+        outcome = open(os.path.join(out_dir, 'rank0.txt')).read()
+    assert outcome.startswith('error:'), outcome
+    assert 'hooks=0' in outcome and 'step_advanced=False' in outcome, outcome
+
+
 def test_owner_assignment_is_balanced_and_deterministic():
     costs = [4608 ** 3] * 3 + [2304 ** 3] * 6 + [1024 ** 3] * 12 + [64 ** 3] * 30
     owners = assign_owners(costs, 8)

@@ -836,3 +836,12 @@ def test_multi_tensor_unitwise_and_bias_kernels(ext):
     for v, ref in zip(vecs, want):
         assert rel_err(v, ref) < 1e-5
     ops.check_status()
+
+
+@pytest.mark.parametrize('b,n', [(3, 257), (8, 1024), (1, 5)])
+def test_batched_matrix_vector_kernel(ext, b, n):
+    torch.manual_seed(0)
+    a, x = torch.randn(b, n, n, device=DEV), torch.randn(b, n, device=DEV)
+    got = ext.batched_mv(a, x)
+    want = torch.bmm(a.double(), x.double().unsqueeze(2)).squeeze(2).float()
+    assert rel_err(got, want) < 1e-5

@@ -118,6 +118,22 @@ def _train_resnet(dev, world, rank):
     return out
 
 
+def _train_shampoo(model, x, t, **kw):
+    cfg = asdl.PreconditioningConfig(damping=1e-4, preconditioner_upd_interval=2)
+    gm = asdl.ShampooGradientMaker(model, cfg, block_size=16, **kw)
+    opt = torch.optim.SGD(model.parameters(), lr=0.01)
+    out = []
+    for _ in range(5):
+        opt.zero_grad(set_to_none=True)
+        d = gm.setup_model_call(model, x)
+        gm.setup_loss_call(F.cross_entropy, d, t)
+        gm.forward_and_backward()
+        out.append(torch.cat([p.grad.flatten() for p in model.parameters()]).cpu().clone())
+        opt.step()
+    ops.check_status()
+    return out
+
+
 TRANSPORTS = (('torch', dict(comm='torch')),
               ('symmetric', dict(comm='symmetric', overlap_grad_reduce=False)),
               ('symmetric_overlap', dict(comm='symmetric', bucket_mb=0.01)),      # several buckets on a tiny model
@@ -143,6 +159,11 @@ def _worker(rank, world, port, out_dir):
         for name, kw in TRANSPORTS:
             model = _net().to(dev).to(memory_format=torch.channels_last)
             results[name] = _train(model, xs, ts, n, **kw)
+            torch.cuda.synchronize()
+            dist.barrier()
+        for name, kw in (('shampoo_torch', dict(comm='torch')), ('shampoo_symmetric', dict(comm='symmetric'))):
+            model = _net().to(dev)
+            results[name] = _train_shampoo(model, xs.contiguous(), ts, **kw)
             torch.cuda.synchronize()
             dist.barrier()
         results['resnet'] = _train_resnet(dev, world, rank)
@@ -178,6 +199,14 @@ def test_data_parallel_transports_match_single_process(world):
                 assert rel_err(per_rank[r][name][step], a) < 1e-6, (name, step, r, 'ranks disagree')
             worst[name] = max(worst.get(name, 0.0), rel_err(a, single[step]))
             assert rel_err(a, single[step]) < 5e-3, (name, step, rel_err(a, single[step]))
+    single_shampoo = _train_shampoo(_net().to(dev), x.to(dev), t.to(dev))
+    for name in ('shampoo_torch', 'shampoo_symmetric'):
+        for step, ref in enumerate(single_shampoo):
+            a = per_rank[0][name][step]
+            for r in range(1, world):
+                assert rel_err(per_rank[r][name][step], a) < 1e-6, (name, step, r, 'ranks disagree')
+            worst[name] = max(worst.get(name, 0.0), rel_err(a, ref))
+            assert rel_err(a, ref) < 5e-3, (name, step, rel_err(a, ref))
     for step, a in enumerate(per_rank[0]['resnet']):
         assert torch.isfinite(a).all(), ('resnet', step)
         for r in range(1, world):
