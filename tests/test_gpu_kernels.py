@@ -287,7 +287,7 @@ def test_shampoo_grouped_launches_match_per_block_path():
     assert gm._group is not None and len(gm._group.blocks) == 2 * 3 + 3 * 3 + 3
     # a step without a root update: 1 staging + 1 statistics + 2 application launches for all 18
     # blocks together; the steps that refresh the roots add the power iteration and the root chain
-    assert sorted(launches)[:2] == [4, 4] or max(sorted(launches)[:2]) <= 4, launches
+    assert max(sorted(launches)[:2]) <= 4, launches
     for step, (g_ref, g_got) in enumerate(zip(ref, got)):
         for a, b in zip(g_ref, g_got):
             assert rel_err(b, a) < 5e-3, (step, rel_err(b, a), a.shape)
