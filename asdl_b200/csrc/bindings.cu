@@ -67,6 +67,8 @@ void unitwise_inverse_mt(std::vector<std::vector<int64_t>> rows, double damping)
 void unitwise_apply_mt(std::vector<std::vector<int64_t>> rows, double grad_scale);
 void bias_precondition_mt(std::vector<std::vector<int64_t>> rows, double grad_scale);
 at::Tensor batched_mv(at::Tensor a, at::Tensor x);
+void gram_hadamard(std::vector<at::Tensor> a1, std::vector<at::Tensor> a2, std::vector<at::Tensor> g1,
+                   std::vector<at::Tensor> g2, at::Tensor kernel, double alpha, double one);
 void diag_linear_stats(at::Tensor a, at::Tensor g, at::Tensor out, c10::optional<at::Tensor> out_bias, double alpha,
                        double beta);
 }  // namespace b200
@@ -125,4 +127,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("bias_precondition_mt", &b200::bias_precondition_mt);
   m.def("diag_linear_stats", &b200::diag_linear_stats);
   m.def("batched_mv", &b200::batched_mv);
+  m.def("gram_hadamard", &b200::gram_hadamard,
+        "kernel += alpha * (A1 A2^T + one) o (G1 G2^T), both Gram tiles in TMEM, multiplied in the epilogue");
 }

@@ -7,7 +7,7 @@
 
 namespace b200 {
 
-enum G2Flavour { G2_PLAIN = 0, G2_WIDE = 1, G2_SPLIT3 = 2, G2_X3WIDE = 3 };
+enum G2Flavour { G2_PLAIN = 0, G2_WIDE = 1, G2_SPLIT3 = 2, G2_X3WIDE = 3, G2_PAIR = 4 };
 
 // Tensor map of one bf16 operand.  `mn` x `k` logical extents; `kmajor`: stored [mn, k] row-major
 // with pitch `ld` elements, otherwise stored [k, mn] row-major.  `box_mn`: tile extent along MN
@@ -30,6 +30,12 @@ void g2_run_x3wide(const GemmProblem2& single, const GemmProblem2* probs, const 
                    int n_sms, cudaStream_t stream, const int* prefix = nullptr, int n_probs = 0);
 void g2_run_split3(const GemmProblem2& single, const GemmProblem2* probs, const GemmWork2* work, int n_work,
                    int n_sms, cudaStream_t stream, const int* prefix = nullptr, int n_probs = 0);
+
+// CTA-pair flavour (tcgen05.mma.cta_group::2, umma_gemm2_pair.cuh): one problem by value, `n_work`
+// pair tiles x split-K slices.  Defined in gemm2_pair.cu.
+void g2_run_pair(const GemmProblem2& single, int n_work, int n_sms, cudaStream_t stream);
+// number of 256 x 256 pair tiles of a problem laid out for this flavour
+int g2_pair_tiles(const GemmProblem2& P);
 
 // Runs `n_work` work items of a device-resident problem table on `stream`.
 void g2_launch_list(const GemmProblem2* d_probs, const GemmWork2* d_work, int n_work, G2Flavour flavour,

@@ -28,7 +28,10 @@ void check_operand(const at::Tensor& t, const char* name) {
               " must be 16-byte aligned");
 }
 
-int g_wide_mode = 0;  // 0: 128-wide tiles only, 1: 256-wide tiles for large outputs, 2: wherever legal
+constexpr int kDefaultTileMode = 3;
+// 0: 128-wide tiles only, 1: 256-wide tiles for large outputs, 2: 256-wide wherever legal,
+// 3: CTA-pair tiles (256 x 256, cta_group::2) for large products, 128-wide otherwise, 4: CTA pairs for every product
+int g_wide_mode = kDefaultTileMode;
 
 bool stream_is_capturing(cudaStream_t s) {
   cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
@@ -116,7 +119,13 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
   TORCH_CHECK(M > 0 && N > 0 && M < (1 << 30) && N < (1 << 30) && K < (1ll << 31) - 64, "matrix sizes out of range");
   if (sym) TORCH_CHECK(M == N, "symmetric mode needs a square output");
   const bool wide = x3wide || (!split3 && (g_wide_mode == 2 || (g_wide_mode == 1 && N >= 1024 && M >= 1024)));
-  const int bn = wide ? 256 : 128;
+  // CTA pairs pay from outputs of 2048 x 2048 and about 2e10 multiply-adds on (measured: 20 % faster than
+  // 128-wide tiles at 4096 x 4096 x 8192, slower below 2048 x 2048 where a launch is a wave or less)
+  const bool pair = !wide && !split3 &&
+                    (g_wide_mode == 4 || (g_wide_mode == 3 && N >= 2048 && M >= 2048 &&
+                                          static_cast<double>(M) * static_cast<double>(N) * static_cast<double>(K) >= 2e10));
+  const int bn = wide ? 256 : 128;        // B rows of a tensor-map box
+  const int bn_grid = pair ? 256 : bn;    // tile width of the grid and of the split-K scratch
   for (int s = 0; s < nseg; ++s) {
     check_operand(a_segs[s], "A");
     check_operand(b_segs[s], "B");
@@ -125,7 +134,7 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
     g2_encode_operand(&P.tmA[s], a_segs[s].data_ptr(), M, K, a_segs[s].stride(0), a_kmajor, G2_BM);
     g2_encode_operand(&P.tmB[s], b_segs[s].data_ptr(), N, K, b_segs[s].stride(0), b_kmajor, bn);
   }
-  bool same_ab = sym && !wide && !split3 && !x3wide && a_kmajor == b_kmajor;
+  bool same_ab = sym && !wide && !pair && !split3 && !x3wide && a_kmajor == b_kmajor;
   for (int s = 0; s < nseg && same_ab; ++s)
     same_ab = a_segs[s].data_ptr() == b_segs[s].data_ptr() &&
               a_segs[s].stride(0) == b_segs[s].stride(0);
@@ -138,7 +147,7 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
   P.beta = static_cast<float>(beta);
   P.flags = (sym ? G2F_SYM : 0) | (a_kmajor ? G2F_A_KMAJOR : 0) | (b_kmajor ? G2F_B_KMAJOR : 0) |
             (same_ab ? G2F_SAME_AB : 0) | (wide ? G2F_WIDE : 0) | (split3 ? G2F_SPLIT3 : 0) |
-            (x3wide ? G2F_SPLIT2 : 0);
+            (x3wide ? G2F_SPLIT2 : 0) | (pair ? G2F_PAIR : 0);
   if (C.has_value()) {
     const at::Tensor& c = *C;
     TORCH_CHECK(c.is_cuda() && c.scalar_type() == at::kFloat && c.dim() == 2 && c.stride(1) == 1 &&
@@ -175,8 +184,8 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
   TORCH_CHECK(allow_no_output || P.C != nullptr || P.out_hi != nullptr, "no output given");
 
   P.tiles_m = (P.M + G2_BM - 1) / G2_BM;
-  P.tiles_n = (P.N + bn - 1) / bn;
-  P.ntiles = tile_count(P.tiles_m, P.tiles_n, sym, bn);
+  P.tiles_n = (P.N + bn_grid - 1) / bn_grid;
+  P.ntiles = tile_count(P.tiles_m, P.tiles_n, sym, bn_grid);
   const int kb_total = (P.K + G2_BK - 1) / G2_BK;
   int nsplit = split3 ? 1 : static_cast<int>(nsplit_req);  // the chunked sum of a split3 product is not split
   if (nsplit <= 0) {
@@ -192,7 +201,7 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
 }
 
 static bool needs_ws(const GemmProblem2& P) { return P.nsplit > 1 && !(P.flags & G2F_ATOMIC); }
-static int tile_width(const GemmProblem2& P) { return (P.flags & G2F_WIDE) ? 256 : 128; }
+static int tile_width(const GemmProblem2& P) { return (P.flags & (G2F_WIDE | G2F_PAIR)) ? 256 : 128; }
 
 void gemm_attach_scratch(GemmProblem2& P, int dev, cudaStream_t stream) {
   DeviceState& st = device_state(dev);
@@ -221,8 +230,10 @@ void gemm_attach_scratch(GemmProblem2& P, int dev, cudaStream_t stream) {
 void gemm_launch_single(const GemmProblem2& P, int dev, cudaStream_t stream) {
   const int n_work = P.ntiles * P.nsplit;
   const int n_sms = g2_sm_count(dev);
-  const bool wide = (P.flags & G2F_WIDE) != 0;
-  if (P.flags & G2F_SPLIT3)
+  const bool wide = (P.flags & (G2F_WIDE | G2F_PAIR)) != 0;   // layout of the split-K scratch
+  if (P.flags & G2F_PAIR)
+    g2_run_pair(P, g2_pair_tiles(P) * P.nsplit, n_sms, stream);
+  else if (P.flags & G2F_SPLIT3)
     g2_run_split3(P, nullptr, nullptr, n_work, n_sms, stream);
   else if (P.flags & G2F_SPLIT2)
     g2_run_x3wide(P, nullptr, nullptr, n_work, n_sms, stream);
@@ -357,7 +368,7 @@ static bool batch_append(GemmProblem2& P, int dev, int64_t nsplit_req, cudaStrea
                          const std::vector<at::Tensor>& a_segs, const std::vector<at::Tensor>& b_segs,
                          const c10::optional<at::Tensor>& C) {
   GemmBatch& B = g_batch;
-  if (!B.active || (P.flags & (G2F_WIDE | G2F_SPLIT3 | G2F_SPLIT2))) return false;
+  if (!B.active || (P.flags & (G2F_WIDE | G2F_SPLIT3 | G2F_SPLIT2 | G2F_PAIR))) return false;
   if (!B.problems.empty() && B.dev != dev) batch_flush(stream);
   // two products into one output (a further backward pass adding to a factor) must not share a launch
   for (const GemmProblem2& Q : B.problems)
@@ -628,10 +639,12 @@ void gemm_plan_run(int64_t id) {
                           plan.split3 == 2, stream);
 }
 
-// 0: 128-wide tiles only; 1: 256-wide tiles for outputs of at least 1024 x 1024; 2: wherever legal.
+// Tile policy of the single-problem entry points.  0: 128-wide tiles only; 1: 256-wide tiles for outputs of
+// at least 1024 x 1024; 2: 256-wide wherever legal; 3 (the default): CTA-pair tiles (256 x 256 over two SMs,
+// cta_group::2) for large products and 128-wide tiles otherwise; 4: CTA pairs for every product; -1: the default.
 void set_gemm_wide(int64_t mode) {
-  TORCH_CHECK(mode >= 0 && mode <= 2, "mode must be 0, 1 or 2");
-  g_wide_mode = static_cast<int>(mode);
+  TORCH_CHECK(mode >= -1 && mode <= 4, "mode must be -1 (default), 0, 1, 2, 3 or 4");
+  g_wide_mode = mode < 0 ? kDefaultTileMode : static_cast<int>(mode);
 }
 
 // Reads and clears the device status word (synchronises the current stream).

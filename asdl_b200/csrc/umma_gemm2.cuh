@@ -73,6 +73,7 @@ enum : int {
   G2F_SPLIT3 = 128,   // tmA[0..2] / tmB[0..2] are the (hi, mid, lo) parts of the operands
   G2F_SPLIT2 = 256,   // tmA[0..1] / tmB[0..1] are the (hi, lo) parts of the operands ("bf16x3", wide tiles)
   G2F_MCAST = 512,    // C_extra[] are NVLS multicast addresses: one multimem.st reaches every GPU of the group
+  G2F_PAIR = 1024,    // CTA-pair flavour (umma_gemm2_pair.cuh): 128-row tensor maps, tile grid of BN = 256
 };
 
 enum : int {

@@ -134,6 +134,9 @@ class Conv2d(Operation):
         bg = torch.bmm(out_grads, in_data.transpose(1, 2))  # n x c_out x d
         return torch.einsum('noi,noj->oij', bg, bg)  # c_out x d x d
 
+    def _gram_hadamard_scale(self, a, g):
+        return 1.0 / g.shape[-1] if (a.ndim == 3 and g.ndim == 3) else None
+
     @staticmethod
     def gram_A(module, in_data1, in_data2=None):
         m1 = in_data1.flatten(start_dim=1)

@@ -114,6 +114,9 @@ class Linear(Operation):
         outer = torch.einsum('ni,nj->nij', in_data, in_data).flatten(start_dim=1)
         return (out_grads.square().T @ outer).view(-1, f_in, f_in)  # f_out x f_in x f_in
 
+    def _gram_hadamard_scale(self, a, g):
+        return 1.0 if (a.ndim == 2 and g.ndim == 2) else None
+
     @staticmethod
     def gram_A(module, in_data1, in_data2=None):
         return in_data1 @ (in_data1 if in_data2 is None else in_data2).T

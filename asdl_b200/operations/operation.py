@@ -390,6 +390,16 @@ class Operation:
         concatenated sets (n1 rows then the rest) the rectangular n1 x n2 block is produced."""
         owner, module = self._kernel_owner(name), self._module
         n1 = owner.kernel.shape[0]
+        fused_scale = self._gram_hadamard_scale(a, g)
+        if fused_scale is not None and ops.cuda_kernels_enabled(owner.kernel, a, g) and owner.kernel.dtype == torch.float32:
+            # both Gram tiles in TMEM, multiplied in the epilogue of one launch
+            a2d, g2d = a.flatten(start_dim=1), g.flatten(start_dim=1)
+            one = 1.0 if original_requires_grad(module, 'bias') else 0.0
+            if g.shape[0] == n1:
+                ops.gram_hadamard(owner.kernel, a2d, g2d, one=one, scale=fused_scale)
+            else:
+                ops.gram_hadamard(owner.kernel, a2d[:n1], g2d[:n1], a2d[n1:], g2d[n1:], one=one, scale=fused_scale)
+            return
         if g.shape[0] == n1:
             A = self.gram_A(module, a)
             B = self.gram_B(module, g)
@@ -399,6 +409,11 @@ class Operation:
         if original_requires_grad(module, 'bias'):
             A = A + 1.
         owner.kernel += B.mul(A)
+
+    def _gram_hadamard_scale(self, a, g):
+        """Factor of gram_B when gram_A / gram_B are plain products of the flattened operands (Linear:
+        1, Conv2d: 1 / spatial size), else None (the layer's own gram_A / gram_B are called)."""
+        return None
 
     def _bwd_gram_direct(self, name, a, g, vector):
         owner, module = self._kernel_owner(name), self._module

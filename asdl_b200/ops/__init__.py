@@ -31,6 +31,8 @@ Precision policy of the tensor-core products (``set_precision``):
 """
 from typing import Optional
 
+import os
+
 import torch
 
 from . import _build
@@ -80,7 +82,18 @@ def extension():
     global _ext
     if _ext is None:
         _ext = _build.load()
+        tiles = os.environ.get('ASDL_B200_GEMM_TILES')   # tile policy of the GEMM, see set_gemm_tiles
+        if tiles is not None:
+            _ext.set_gemm_wide(int(tiles))
     return _ext
+
+
+def set_gemm_tiles(mode: int = -1):
+    """Tile policy of the tcgen05 GEMM's single-problem launches: 0 = 128 x 128 tiles, 1 / 2 = 128 x 256
+    tiles for large / all outputs, 3 = 256 x 256 tiles on CTA pairs (``cta_group::2``) for large
+    products and 128 x 128 otherwise (the default, also -1), 4 = CTA pairs for every product.  The
+    environment variable ``ASDL_B200_GEMM_TILES`` sets the initial policy."""
+    extension().set_gemm_wide(int(mode))
 
 
 def cuda_kernels_enabled(*tensors):
@@ -222,6 +235,42 @@ def matmul_tn(a: torch.Tensor, b: torch.Tensor, scale: float = 1.0,
     extension().umma_gemm(a_segs, b_segs, False, False, out, float(scale), float(beta), False,
                           None, None, 0)
     return out
+
+
+def gram_hadamard(kernel: torch.Tensor, a1: torch.Tensor, g1: torch.Tensor, a2: Optional[torch.Tensor] = None,
+                  g2: Optional[torch.Tensor] = None, one: float = 0.0, scale: float = 1.0) -> torch.Tensor:
+    """``kernel += scale * (a1 a2^T + one) o (g1 g2^T)``: one layer's term of the Hadamard-factored
+    Gram / NTK matrix (asdl/operations/operation.py:335-351).  a*: layer inputs [n, d_in], g*: output
+    gradients [n, d_out] of the two example sets (the second defaults to the first); ``one`` = 1 for a
+    layer with a bias.
+
+    CUDA: one launch; every CTA forms both 128 x 128 Gram tiles in its two TMEM accumulators and
+    multiplies them in the epilogue, so neither Gram matrix is written to memory.  fp32 inputs are
+    split into (hi, lo) bf16 parts and every Gram is the sum of three part products."""
+    a2 = a1 if a2 is None else a2
+    g2 = g1 if g2 is None else g2
+    if (not cuda_kernels_enabled(kernel, a1, g1) or kernel.dtype != torch.float32 or kernel.ndim != 2
+            or kernel.stride(1) != 1 or a1.shape[1] == 0 or g1.shape[1] == 0):
+        A = _f32(a1) @ _f32(a2).T
+        B = _f32(g1) @ _f32(g2).T
+        if scale != 1.0:
+            B = B * scale
+        kernel += B.mul(A + one if one != 0.0 else A).to(kernel.dtype)
+        return kernel
+    x3 = _use_x3(a1.dtype) or _use_x3(g1.dtype)
+
+    def parts(t):
+        return [p for p in _stage_bf16(t, x3) if p is not None]
+
+    pa1, pg1 = parts(a1), parts(g1)
+    pa2 = pa1 if a2 is a1 else parts(a2)
+    pg2 = pg1 if g2 is g1 else parts(g2)
+    if len(pa1) != len(pa2):      # one side was already an aligned bf16 matrix: use single parts on both
+        pa1, pa2 = pa1[:1], pa2[:1]
+    if len(pg1) != len(pg2):
+        pg1, pg2 = pg1[:1], pg2[:1]
+    extension().gram_hadamard(pa1, pa2, pg1, pg2, kernel, float(scale), float(one))
+    return kernel
 
 
 def kron_apply(left: torch.Tensor, mid: torch.Tensor, right: torch.Tensor) -> torch.Tensor:

@@ -249,7 +249,7 @@ def bench_batchnorm(timer, n, c, hw, hbm, flops_peak, src):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--only', default=None, choices=['syrk', 'syrk_x3', 'layouts', 'precond', 'inverse', 'roots', 'eigh', 'lnstats', 'symm', 'im2col', 'batchnorm'])
-    ap.add_argument('--wide', type=int, default=0, help='tile width policy of the GEMM: 0 = 128, 1 = 256 for large outputs, 2 = 256 wherever legal')
+    ap.add_argument('--wide', type=int, default=-1, help='tile policy of the GEMM: -1 = default (3), 0 = 128 wide, 1 = 256 wide for large outputs, 2 = 256 wide wherever legal, 3 = CTA pairs (256 x 256, cta_group::2) for large products, 4 = CTA pairs everywhere')
     ap.add_argument('--chol', default=None, choices=['tensor_core', 'cuda_core'], help='grouped inverse backend')
     ap.add_argument('--rows', type=int, default=None)
     ap.add_argument('--n', type=int, default=None)

@@ -601,7 +601,81 @@ def test_wide_tiles_match_narrow_tiles(ext, mode):
                 assert rel_err(c1, c0) < 1e-6 and torch.equal(c1, c1.T)
                 assert rel_err(g1, g0) < 1e-6 and rel_err(g2, g0) < 1e-6
     finally:
-        ext.set_gemm_wide(0)
+        ext.set_gemm_wide(-1)
+    ops.check_status()
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize('n1,n2,d_in,d_out', [(200, 200, 300, 10), (130, 77, 72, 260), (5, 300, 9, 1)])
+def test_gram_hadamard_kernel(n1, n2, d_in, d_out, dtype):
+    """kernel += scale * (a1 a2^T + one) o (g1 g2^T) against fp64 from the same (rounded) inputs."""
+    torch.manual_seed(0)
+    a1, g1 = torch.randn(n1, d_in, device=DEV).to(dtype), torch.randn(n1, d_out, device=DEV).to(dtype)
+    same = n1 == n2
+    a2 = a1 if same else torch.randn(n2, d_in, device=DEV).to(dtype)
+    g2 = g1 if same else torch.randn(n2, d_out, device=DEV).to(dtype)
+    start = torch.randn(n1, n2, device=DEV)
+    kernel = start.clone()
+    before = ops.extension().launch_count()
+    ops.gram_hadamard(kernel, a1, g1, None if same else a2, None if same else g2, one=1.0, scale=0.25)
+    assert ops.extension().launch_count() - before <= 1 + 4          # the product itself + operand staging
+    ref = start.double() + 0.25 * (a1.double() @ a2.double().T + 1.0) * (g1.double() @ g2.double().T)
+    # fp32 inputs: three bf16 part products per Gram (the lo . lo term, 2^-16 relative, is left out)
+    assert rel_err(kernel, ref.float()) < (2e-5 if dtype == torch.float32 else 2e-6), rel_err(kernel, ref.float())
+    ops.check_status()
+
+
+def test_hadamard_ntk_on_cuda_matches_cpu():
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.ReLU(), nn.Flatten(), nn.Linear(8 * 36, 32), nn.ReLU(),
+                          nn.Linear(32, 4, bias=False))
+    x1, x2 = torch.randn(9, 3, 6, 6), torch.randn(5, 3, 6, 6)
+    want = asdl.empirical_class_wise_hadamard_ntk(model, x1, x2)
+    before = ops.extension().launch_count()
+    got = asdl.empirical_class_wise_hadamard_ntk(copy.deepcopy(model).to(DEV), x1.to(DEV), x2.to(DEV))
+    assert ops.extension().launch_count() > before
+    assert rel_err(got.cpu(), want) < 1e-5
+    want1 = asdl.empirical_class_wise_hadamard_ntk(model, x1)
+    got1 = asdl.empirical_class_wise_hadamard_ntk(copy.deepcopy(model).to(DEV), x1.to(DEV))
+    assert rel_err(got1.cpu(), want1) < 1e-5
+    ops.check_status()
+
+
+def test_cta_pair_tiles_match_narrow_tiles(ext):
+    """cta_group::2 flavour (256 x 256 tiles over two SMs) against the 128 x 128 flavour: even and odd
+    counts of 128-row tiles, ragged edges, split-K, K-major operands, several segments, beta and the
+    bf16 images of the result."""
+    torch.manual_seed(0)
+    try:
+        for rows, n, ny in [(2048, 1024, 1032), (704, 1160, 1288), (1000, 1288, 2048)]:
+            x = torch.randn(rows, n, device=DEV).to(torch.bfloat16)
+            y = torch.randn(rows, ny, device=DEV).to(torch.bfloat16)
+            x2 = torch.randn(rows, n, device=DEV).to(torch.bfloat16)
+            for nsplit in (1, 3):
+                res = []
+                for mode in (0, 4):
+                    ext.set_gemm_wide(mode)
+                    c = torch.full((n, n), float('nan'), device=DEV)
+                    ext.umma_gemm([x], [x], False, False, c, 1.0, 0.0, True, None, None, nsplit)
+                    g = torch.full((n, ny), float('nan'), device=DEV)
+                    ext.umma_gemm([x], [y], False, False, g, 1.0, 0.0, False, None, None, nsplit)
+                    gk = torch.full((n, ny), float('nan'), device=DEV)
+                    ext.umma_gemm([x.T.contiguous()], [y.T.contiguous()], True, True, gk, 1.0, 0.0, False, None, None, nsplit)
+                    s2 = torch.ones(n, n, device=DEV)
+                    hi = torch.zeros(n, (n + 63) // 64 * 64, device=DEV, dtype=torch.bfloat16)
+                    lo = torch.zeros_like(hi)
+                    ext.umma_gemm([x, x2], [x, x2], False, False, s2, 0.5, 0.25, True, hi, lo, nsplit)
+                    res.append((c, g, gk, s2, hi, lo))
+                (c0, g0, gk0, s0, hi0, lo0), (c1, g1, gk1, s1, hi1, lo1) = res
+                assert rel_err(c1, c0) < 1e-6 and torch.equal(c1, c1.T)
+                assert rel_err(g1, g0) < 1e-6 and rel_err(gk1, g0) < 1e-6
+                assert rel_err(s1, s0) < 1e-6 and torch.equal(s1, s1.T)
+                assert rel_err(hi1[:, :n].float() + lo1[:, :n].float(), s1) < 1e-4
+                assert rel_err(hi1.float(), hi0.float()) < 1e-2   # a last-bit difference of the sum may flip a bf16 rounding
+            ref = x.float().T @ y.float()
+            assert rel_err(g1, ref) < 1e-5
+    finally:
+        ext.set_gemm_wide(-1)
     ops.check_status()
 
 
