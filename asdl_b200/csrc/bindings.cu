@@ -67,6 +67,10 @@ void unitwise_inverse_mt(std::vector<std::vector<int64_t>> rows, double damping)
 void unitwise_apply_mt(std::vector<std::vector<int64_t>> rows, double grad_scale);
 void bias_precondition_mt(std::vector<std::vector<int64_t>> rows, double grad_scale);
 at::Tensor batched_mv(at::Tensor a, at::Tensor x);
+void embedding_diag_stats(at::Tensor idx, at::Tensor g, at::Tensor out, int64_t padding_idx, double scale);
+void embedding_counts(at::Tensor idx, at::Tensor counts);
+void bfgs_powell_damping(at::Tensor H, at::Tensor s, at::Tensor y, double mu1, double mu2);
+void bfgs_inv_update(at::Tensor H, at::Tensor s, at::Tensor y);
 void gram_hadamard(std::vector<at::Tensor> a1, std::vector<at::Tensor> a2, std::vector<at::Tensor> g1,
                    std::vector<at::Tensor> g2, at::Tensor kernel, double alpha, double one);
 void diag_linear_stats(at::Tensor a, at::Tensor g, at::Tensor out, c10::optional<at::Tensor> out_bias, double alpha,
@@ -127,6 +131,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("bias_precondition_mt", &b200::bias_precondition_mt);
   m.def("diag_linear_stats", &b200::diag_linear_stats);
   m.def("batched_mv", &b200::batched_mv);
+  m.def("embedding_diag_stats", &b200::embedding_diag_stats, "out[idx[t], :] += scale * g[t, :]^2 (reductions, no sort)");
+  m.def("embedding_counts", &b200::embedding_counts, "counts[example, idx] += 1");
+  m.def("bfgs_powell_damping", &b200::bfgs_powell_damping, "Powell damping + LM shift of a BFGS pair, in place");
+  m.def("bfgs_inv_update", &b200::bfgs_inv_update, "symmetrise H and apply the rank-2 BFGS update of the inverse, in place");
   m.def("gram_hadamard", &b200::gram_hadamard,
         "kernel += alpha * (A1 A2^T + one) o (G1 G2^T), both Gram tiles in TMEM, multiplied in the epilogue");
 }

@@ -29,6 +29,7 @@ void check_operand(const at::Tensor& t, const char* name) {
 }
 
 constexpr int kDefaultTileMode = 3;
+bool g_batch_open = false;   // a deferred batch is recording (see gemm_batch_begin)
 // 0: 128-wide tiles only, 1: 256-wide tiles for large outputs, 2: 256-wide wherever legal,
 // 3: CTA-pair tiles (256 x 256, cta_group::2) for large products, 128-wide otherwise, 4: CTA pairs for every product
 int g_wide_mode = kDefaultTileMode;
@@ -120,10 +121,12 @@ void gemm_fill_problem(GemmProblem2& P, const std::vector<at::Tensor>& a_segs,
   if (sym) TORCH_CHECK(M == N, "symmetric mode needs a square output");
   const bool wide = x3wide || (!split3 && (g_wide_mode == 2 || (g_wide_mode == 1 && N >= 1024 && M >= 1024)));
   // CTA pairs pay from outputs of 2048 x 2048 and about 2e10 multiply-adds on (measured: 20 % faster than
-  // 128-wide tiles at 4096 x 4096 x 8192, slower below 2048 x 2048 where a launch is a wave or less)
+  // 128-wide tiles at 4096 x 4096 x 8192, slower below 2048 x 2048 where a launch is a wave or less).  While a
+  // batch is recording, a product leaves the batch for a pair launch of its own only from 1e11 multiply-adds
+  // on: smaller ones fill the GPU better together with the rest of the batch.
+  const double macs = static_cast<double>(M) * static_cast<double>(N) * static_cast<double>(K);
   const bool pair = !wide && !split3 &&
-                    (g_wide_mode == 4 || (g_wide_mode == 3 && N >= 2048 && M >= 2048 &&
-                                          static_cast<double>(M) * static_cast<double>(N) * static_cast<double>(K) >= 2e10));
+                    (g_wide_mode == 4 || (g_wide_mode == 3 && N >= 2048 && M >= 2048 && macs >= (g_batch_open ? 1e11 : 2e10)));
   const int bn = wide ? 256 : 128;        // B rows of a tensor-map box
   const int bn_grid = pair ? 256 : bn;    // tile width of the grid and of the split-K scratch
   for (int s = 0; s < nseg; ++s) {
@@ -388,12 +391,14 @@ static bool batch_append(GemmProblem2& P, int dev, int64_t nsplit_req, cudaStrea
 void gemm_batch_begin() {
   TORCH_CHECK(!g_batch.active, "a GEMM batch is already open");
   g_batch.active = true;
+  g_batch_open = true;
 }
 
 // Launches what was recorded since gemm_batch_begin() on the current stream; returns the number of products.
 int64_t gemm_batch_end() {
   TORCH_CHECK(g_batch.active, "no GEMM batch is open");
   g_batch.active = false;
+  g_batch_open = false;
   const int64_t n = static_cast<int64_t>(g_batch.problems.size());
   if (n > 0) {
     c10::cuda::CUDAGuard guard(g_batch.dev);
@@ -405,6 +410,7 @@ int64_t gemm_batch_end() {
 // Drops an open batch without launching it (error paths).
 void gemm_batch_abort() {
   g_batch.active = false;
+  g_batch_open = false;
   g_batch.problems.clear();
   g_batch.nsplit_req.clear();
   g_batch.keep_alive.clear();

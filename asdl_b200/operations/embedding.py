@@ -48,6 +48,9 @@ class Embedding(Operation):
         n = in_data.shape[0]
         idx = in_data.reshape(n, -1).long()
         counts = torch.zeros(n, module.num_embeddings, device=idx.device, dtype=torch.float32)
+        if idx.is_cuda and ops.cuda_kernels_enabled(counts):
+            ops.extension().embedding_counts(idx.contiguous(), counts)    # reductions, one thread per token
+            return ops.gram(counts.to(module.weight.device))              # V x V on the tensor cores
         counts.scatter_add_(1, idx, torch.ones_like(idx, dtype=torch.float32))
         counts = counts.to(module.weight.device)
         return counts.T @ counts  # V x V
@@ -61,6 +64,14 @@ class Embedding(Operation):
         """Sum over tokens of the squared output-gradient, scattered to the looked-up rows
         (every token counts as its own example, as in the reference)."""
         idx = in_data.reshape(-1).long()
+        if (idx.is_cuda and ops.cuda_kernels_enabled(out_grads) and module.weight.dtype == torch.float32
+                and out_grads.dtype in (torch.float32, torch.bfloat16)):
+            cov = torch.zeros_like(module.weight, memory_format=torch.contiguous_format)
+            g = out_grads.reshape(idx.shape[0], -1)
+            g = g if g.stride(1) == 1 else g.contiguous()
+            ops.extension().embedding_diag_stats(idx.contiguous(), g, cov,
+                                                 -1 if module.padding_idx is None else int(module.padding_idx), 1.0)
+            return cov
         g2 = out_grads.reshape(idx.shape[0], -1).square()
         cov = torch.zeros_like(module.weight)
         cov.index_add_(0, idx, g2.to(cov.dtype))

@@ -114,6 +114,26 @@ class Linear(Operation):
         outer = torch.einsum('ni,nj->nij', in_data, in_data).flatten(start_dim=1)
         return (out_grads.square().T @ outer).view(-1, f_in, f_in)  # f_out x f_in x f_in
 
+    def _cvp_without_batch_grads(self, a, g, vector, has_w, has_b):
+        """With per-example gradients g_n a_n^T (and g_n for the bias) the coefficient of example n is
+        c_n = g_n^T V_w a_n + g_n . v_b, and the product is (g o c)^T a (and its column sums): two
+        GEMMs over the batch instead of an n x d_out x d_in tensor (asdl/operations/operation.py:247-263
+        forms the per-example gradients)."""
+        if a.ndim != 2 or g.ndim != 2:
+            return None
+        module = self._module
+        d_out, d_in = module.weight.shape
+        nw = d_out * d_in if has_w else 0
+        coef = torch.zeros(g.shape[0], device=g.device, dtype=torch.float32)
+        if has_w:
+            coef += (ops.matmul_nn(g, vector[:nw].view(d_out, d_in)) * a).sum(dim=1)
+        if has_b:
+            coef += g.float() @ vector[nw:].float()
+        weighted = g.float() * coef.unsqueeze(1)
+        out_w = ops.matmul_tn(weighted, a).to(module.weight.dtype) if has_w else None
+        out_b = weighted.sum(dim=0).to(module.bias.dtype) if has_b else None
+        return out_w, out_b
+
     def _gram_hadamard_scale(self, a, g):
         return 1.0 if (a.ndim == 2 and g.ndim == 2) else None
 

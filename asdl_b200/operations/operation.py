@@ -284,7 +284,7 @@ class Operation:
 
     def _bwd_cov(self, name, a, g, vector):
         _, _, bg = self.collect_batch_grads(a, g)
-        cov = torch.matmul(bg.T, bg).mul_(self._cov_scale)
+        cov = ops.gram(bg, scale=self._cov_scale)     # bg^T bg: the tensor-core SYRK on CUDA
         if name == OP_COV:
             self.accumulate_result(cov, OP_COV, 'data')
         else:
@@ -295,11 +295,17 @@ class Operation:
             raise ValueError('vector is not set.')
         if vector.ndim != 1:
             raise ValueError(f'vector.ndim has to be 1. Got {vector.ndim}.')
-        _, _, bg = self.collect_batch_grads(a, g)
-        cvp = torch.mv(bg.T, torch.mv(bg, vector)).mul_(self._cov_scale)
         module = self._module
         has_w = original_requires_grad(module, 'weight')
         has_b = original_requires_grad(module, 'bias')
+        direct = self._cvp_without_batch_grads(a, g, vector, has_w, has_b)
+        if direct is not None:
+            for key, value in zip(('weight', 'bias'), direct):
+                if value is not None:
+                    self.accumulate_result(value.mul_(self._cov_scale), OP_CVP, key)
+            return
+        _, _, bg = self.collect_batch_grads(a, g)
+        cvp = torch.mv(bg.T, torch.mv(bg, vector)).mul_(self._cov_scale)
         if has_w and has_b:
             nw = module.weight.numel()
             self.accumulate_result(cvp[:nw].view_as(module.weight), OP_CVP, 'weight')
@@ -409,6 +415,11 @@ class Operation:
         if original_requires_grad(module, 'bias'):
             A = A + 1.
         owner.kernel += B.mul(A)
+
+    def _cvp_without_batch_grads(self, a, g, vector, has_w, has_b):
+        """sum_n g_n (g_n . v) split into (weight, bias) without forming the per-example gradients, or
+        None when the layer has no such form (the per-example gradients are then collected)."""
+        return None
 
     def _gram_hadamard_scale(self, a, g):
         """Factor of gram_B when gram_A / gram_B are plain products of the flattened operands (Linear:

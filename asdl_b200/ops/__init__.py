@@ -237,6 +237,21 @@ def matmul_tn(a: torch.Tensor, b: torch.Tensor, scale: float = 1.0,
     return out
 
 
+def matmul_nn(a: torch.Tensor, b: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """``scale * a b`` with a: [m, k], b: [k, n] in their natural row-major layouts (a is the K-major
+    operand of the tcgen05 GEMM, b the MN-major one: no transpose copy)."""
+    if not cuda_kernels_enabled(a, b) or a.numel() == 0 or b.numel() == 0:
+        prod = _f32(a) @ _f32(b)
+        return prod * scale if scale != 1.0 else prod
+    x3 = _use_x3(a.dtype) or _use_x3(b.dtype)
+    a_hi, a_lo = _stage_bf16(a, x3)
+    b_hi, b_lo = _stage_bf16(b, x3)
+    out = torch.empty(a.shape[0], b.shape[1], device=a.device, dtype=torch.float32)
+    a_segs, b_segs = _segments(a_hi, a_lo, b_hi, b_lo)
+    extension().umma_gemm(a_segs, b_segs, True, False, out, float(scale), 0.0, False, None, None, 0)
+    return out
+
+
 def gram_hadamard(kernel: torch.Tensor, a1: torch.Tensor, g1: torch.Tensor, a2: Optional[torch.Tensor] = None,
                   g2: Optional[torch.Tensor] = None, one: float = 0.0, scale: float = 1.0) -> torch.Tensor:
     """``kernel += scale * (a1 a2^T + one) o (g1 g2^T)``: one layer's term of the Hadamard-factored

@@ -17,6 +17,7 @@ import torch
 import torch.nn as nn
 from torch import Tensor
 
+from .. import ops
 from ..core import extend
 from ..operations import (OP_MEAN_INPUTS, OP_SPATIAL_MEAN_OUTPUTS, OP_SPATIAL_MEAN_OUTGRADS,
                           OP_OUT_SPATIAL_SIZE, OP_COV_KRON, OP_BFGS_KRON_S_AS, OperationContext)
@@ -188,6 +189,12 @@ class KronBfgsGradientMaker(PreconditionedGradientMaker):
                 self._B_inv_exists = self._B_inv_exists or kron.B_inv is not None
 
 
+def _bfgs_kernels_ok(H, s, y):
+    """The CUDA kernels of the BFGS update take fp32 tensors in their natural layout."""
+    return (ops.cuda_kernels_enabled(H, s, y) and H.dtype == s.dtype == y.dtype == torch.float32
+            and H.ndim == 2 and H.stride(1) == 1 and s.is_contiguous() and y.is_contiguous())
+
+
 def powell_lm_damping_(H: Tensor, s: Tensor, y: Tensor, mu1: float, mu2: float):
     """Make the pair (s, y) safe for a BFGS update of H = B^-1: Powell's damping pulls s towards
     H y when s^T y < mu1 * y^T H y, then y <- y + mu2 * s (Levenberg-Marquardt on H^-1).
@@ -196,6 +203,9 @@ def powell_lm_damping_(H: Tensor, s: Tensor, y: Tensor, mu1: float, mu2: float):
         raise ValueError(f'mu1 has to be in (0, 1). Got {mu1}.')
     if mu2 <= 0:
         raise ValueError(f'mu2 has to be > 0. Got {mu2}.')
+    if _bfgs_kernels_ok(H, s, y):
+        ops.extension().bfgs_powell_damping(H, s, y, float(mu1), float(mu2))
+        return
     Hy = torch.mv(H, y)
     ytHy = torch.dot(y, Hy)
     sty = torch.dot(s, y)
@@ -215,6 +225,9 @@ def bfgs_inv_update_(H: Tensor, s: Tensor, y: Tensor):
     for name, v in (('s', s), ('y', y)):
         if v.ndim != 1 or v.shape[0] != n:
             raise ValueError(f'{name} has to be a {Tensor} containing a vector of same dimension as H.')
+    if _bfgs_kernels_ok(H, s, y):
+        ops.extension().bfgs_inv_update(H, s, y)
+        return H
     H.copy_((H + H.T) / 2)
     sty = torch.dot(s, y)
     Hy = torch.mv(H, y)

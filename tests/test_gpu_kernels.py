@@ -641,6 +641,92 @@ def test_hadamard_ntk_on_cuda_matches_cpu():
     ops.check_status()
 
 
+@pytest.mark.parametrize('n', [1, 33, 200, 1000])
+def test_bfgs_kernels_match_the_pytorch_path(n):
+    """Powell damping and the rank-2 update of the inverse on CUDA against the same functions on CPU
+    (PyTorch ops), for a pair with and a pair without usable curvature."""
+    from asdl_b200.precondition.kbfgs import powell_lm_damping_, bfgs_inv_update_
+    torch.manual_seed(n)
+    base = torch.randn(n, n)
+    H0 = base @ base.T / n + torch.eye(n) + 1e-3 * torch.randn(n, n)       # not exactly symmetric
+    for flip in (1.0, -1.0):
+        s0, y0 = torch.randn(n), torch.randn(n)
+        y0 = flip * (y0 + 2 * s0)                                          # flip = -1: s^T y < 0
+        Hc, sc, yc = H0.clone(), s0.clone(), y0.clone()
+        Hg, sg, yg = H0.to(DEV), s0.to(DEV), y0.to(DEV)
+        before = ops.extension().launch_count()
+        powell_lm_damping_(Hc, sc, yc, 0.2, 0.1)
+        powell_lm_damping_(Hg, sg, yg, 0.2, 0.1)
+        assert rel_err(sg.cpu(), sc) < 1e-5 and rel_err(yg.cpu(), yc) < 1e-5
+        bfgs_inv_update_(Hc, sc, yc)
+        bfgs_inv_update_(Hg, sg, yg)
+        assert ops.extension().launch_count() - before == 5
+        assert rel_err(Hg.cpu(), Hc) < 1e-5, rel_err(Hg.cpu(), Hc)
+        assert torch.equal(Hg, Hg.T)
+        # a pair without curvature leaves the (symmetrised) matrix alone
+        Hc2, Hg2 = H0.clone(), H0.to(DEV)
+        bfgs_inv_update_(Hc2, s0.clone(), -s0.clone())
+        bfgs_inv_update_(Hg2, s0.to(DEV), -s0.to(DEV))
+        assert rel_err(Hg2.cpu(), Hc2) < 1e-6
+    ops.check_status()
+
+
+def test_embedding_statistics_kernels():
+    torch.manual_seed(0)
+    emb = nn.Embedding(37, 20, padding_idx=3)
+    idx = torch.randint(0, 37, (6, 11))
+    idx[0, :4] = 3
+    g = torch.randn(6, 11, 20)
+    from asdl_b200.operations.embedding import Embedding as EmbOp
+    want_diag = EmbOp.cov_diag_weight(emb, idx, g)
+    want_A = EmbOp.cov_kron_A(emb, idx)
+    emb_g = copy.deepcopy(emb).to(DEV)
+    before = ops.extension().launch_count()
+    got_diag = EmbOp.cov_diag_weight(emb_g, idx.to(DEV), g.to(DEV))
+    got_diag16 = EmbOp.cov_diag_weight(emb_g, idx.to(DEV), g.to(DEV).to(torch.bfloat16))
+    got_A = EmbOp.cov_kron_A(emb_g, idx.to(DEV))
+    assert ops.extension().launch_count() - before >= 4
+    assert rel_err(got_diag.cpu(), want_diag) < 1e-6
+    assert rel_err(got_diag16.cpu(), want_diag) < 1e-2
+    assert got_diag[3].abs().max().item() == 0.0
+    assert torch.equal(got_A.cpu(), want_A)        # small integer counts: exact
+    ops.check_status()
+
+
+def test_cvp_and_cov_on_cuda_match_cpu():
+    """Layer-wise covariance (SYRK of the per-example gradients) and covariance-vector products (two
+    GEMMs over the batch for Linear layers) against the CPU path."""
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(12, 20), nn.Tanh(), nn.Linear(20, 7, bias=False), nn.Tanh(), nn.Linear(7, 3))
+    x, t = torch.randn(16, 12), torch.randint(0, 3, (16,))
+    vec = [torch.randn_like(p) for p in model.parameters()]
+
+    def run(model, x, t, vec):
+        cfg = asdl.FisherConfig(fisher_type=asdl.FISHER_EMP, fisher_shapes=[asdl.SHAPE_LAYER_WISE], data_size=16)
+        fm = asdl.get_fisher_maker(model, cfg)
+        d = fm.setup_model_call(model, x)
+        fm.setup_loss_call(F.cross_entropy, d, t)
+        fm.forward_and_backward()
+        covs = [m.fisher.data.detach().cpu().clone() for m in model if hasattr(m, 'fisher')]
+        fm = asdl.get_fisher_maker(model, cfg)
+        d = fm.setup_model_call(model, x)
+        fm.setup_loss_call(F.cross_entropy, d, t)
+        fm.forward_and_backward(fvp=True, vec=asdl.ParamVector(list(model.parameters()), vec))
+        fvps = [v.detach().cpu().clone() for m in model if hasattr(m, 'fvp') for v in m.fvp.values()]
+        return covs, fvps
+
+    covs_c, fvps_c = run(model, x, t, vec)
+    before = ops.extension().launch_count()
+    covs_g, fvps_g = run(copy.deepcopy(model).to(DEV), x.to(DEV), t.to(DEV), [v.to(DEV) for v in vec])
+    assert ops.extension().launch_count() > before
+    assert len(covs_c) == 3 and len(fvps_c) == 5
+    for a, b in zip(covs_c, covs_g):
+        assert rel_err(b, a) < 2e-5
+    for a, b in zip(fvps_c, fvps_g):
+        assert rel_err(b, a) < 2e-5
+    ops.check_status()
+
+
 def test_cta_pair_tiles_match_narrow_tiles(ext):
     """cta_group::2 flavour (256 x 256 tiles over two SMs) against the 128 x 128 flavour: even and odd
     counts of 128-row tiles, ragged edges, split-K, K-major operands, several segments, beta and the
