@@ -237,6 +237,32 @@ def matmul_tn(a: torch.Tensor, b: torch.Tensor, scale: float = 1.0,
     return out
 
 
+def matmul(a: torch.Tensor, b: torch.Tensor, trans_a: bool = False, trans_b: bool = False, alpha: float = 1.0,
+           out: Optional[torch.Tensor] = None, beta: float = 0.0, sym: bool = False) -> torch.Tensor:
+    """``alpha * op(a) op(b) (+ beta * out)`` for row-major matrices, op = transpose where asked.  No operand
+    is copied for its layout: the tcgen05 GEMM takes either operand K-major or MN-major.  ``sym``: the
+    result is known to be symmetric (a a^T, a^T a); only its lower tiles are multiplied and mirrored."""
+    if not cuda_kernels_enabled(a, b) or a.numel() == 0 or b.numel() == 0:
+        prod = (_f32(a).T if trans_a else _f32(a)) @ (_f32(b).T if trans_b else _f32(b))
+        if alpha != 1.0:
+            prod = prod * alpha
+        if out is None:
+            return prod
+        return out.mul_(beta).add_(prod.to(out.dtype)) if beta != 0.0 else out.copy_(prod)
+    x3 = _use_x3(a.dtype) or _use_x3(b.dtype)
+    a_hi, a_lo = _stage_bf16(a, x3)
+    b_hi, b_lo = (a_hi, a_lo) if b is a else _stage_bf16(b, x3)
+    m = a.shape[1] if trans_a else a.shape[0]
+    n = b.shape[0] if trans_b else b.shape[1]
+    if out is None:
+        out = torch.empty(m, n, device=a.device, dtype=torch.float32)
+        beta = 0.0
+    a_segs, b_segs = _segments(a_hi, a_lo, b_hi, b_lo)
+    # A operand: stored [m, k] (not transposed) is K-major; B operand: stored [n, k] (transposed) is K-major
+    extension().umma_gemm(a_segs, b_segs, not trans_a, trans_b, out, float(alpha), float(beta), bool(sym), None, None, 0)
+    return out
+
+
 def matmul_nn(a: torch.Tensor, b: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
     """``scale * a b`` with a: [m, k], b: [k, n] in their natural row-major layouts (a is the K-major
     operand of the tcgen05 GEMM, b the MN-major one: no transpose copy)."""

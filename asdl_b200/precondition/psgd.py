@@ -25,6 +25,8 @@ import torch.nn as nn
 from torch import Tensor
 from torch.linalg import solve_triangular
 
+from .. import ops
+
 from .prec_grad_maker import PreconditionedGradientMaker, PreconditioningConfig
 
 __all__ = ['PsgdGradientMaker', 'KronPsgdGradientMaker', 'update_precond_kron', 'precond_grad_kron',
@@ -230,11 +232,17 @@ class _Dense:
     def scaled(self, s):
         return _Dense(self.Q * s)
 
+    def _tc(self, *others):
+        """Dense products of factors from 256 x 256 on run on the tensor-core GEMM (fp32 operands as three
+        bf16 part products, fp32 accumulation); smaller ones are launch-bound either way."""
+        return (self.Q.shape[0] >= 256 and self.Q.dtype == torch.float32
+                and ops.cuda_kernels_enabled(self.Q, *others) and all(o.dtype == torch.float32 and o.ndim == 2 for o in others))
+
     def left_mul(self, X):            # Q X
-        return self.Q @ X
+        return ops.matmul(self.Q, X) if self._tc(X) else self.Q @ X
 
     def right_mul_t(self, X):         # X Q^T
-        return X @ self.Q.T
+        return ops.matmul(X, self.Q, trans_b=True) if self._tc(X) else X @ self.Q.T
 
     def left_solve_t(self, X):        # Q^-T X
         return solve_triangular(self.Q.T, X, upper=False)
@@ -243,14 +251,24 @@ class _Dense:
         return solve_triangular(self.Q, X, upper=True, left=False)
 
     def updated(self, A, B, step, on_rows):
+        if self._tc(A, B):
+            # A A^T - B B^T (rows) or A^T A - B^T B (columns): two symmetric products into one matrix
+            M = ops.matmul(A, A, trans_a=not on_rows, trans_b=on_rows, sym=True)
+            ops.matmul(B, B, trans_a=not on_rows, trans_b=on_rows, alpha=-1.0, out=M, beta=1.0, sym=True)
+            G = torch.triu(M)
+            return self.Q - (step / (G.abs().max() + _TINY)) * ops.matmul(G, self.Q)
         M = (A @ A.T - B @ B.T) if on_rows else (A.T @ A - B.T @ B)
         G = torch.triu(M)
         return self.Q - (step / (G.abs().max() + _TINY)) * (G @ self.Q)
 
     def gram_apply_left(self, X):     # Q^T Q X
+        if self._tc(X):
+            return ops.matmul(self.Q, ops.matmul(self.Q, X), trans_a=True)
         return self.Q.T @ (self.Q @ X)
 
     def gram_apply_right(self, X):    # X Q^T Q
+        if self._tc(X):
+            return ops.matmul(ops.matmul(X, self.Q, trans_b=True), self.Q)
         return (X @ self.Q.T) @ self.Q
 
 

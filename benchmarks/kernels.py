@@ -191,6 +191,57 @@ def bench_lnstats(timer, rows, d, hbm, src):
          speedup_vs_torch=round(ms_lib / ms, 2))
 
 
+def bench_gram_hadamard(timer, n, d_in, d_out, flops_peak, src):
+    """kernel += (a a^T + 1) o (g g^T): both Gram tiles in TMEM, multiplied in the epilogue, against the
+    PyTorch ops of the same update (two matmuls, an add, a multiply, an accumulate)."""
+    a = torch.randn(n, d_in, device='cuda').to(torch.bfloat16)
+    g = torch.randn(n, d_out, device='cuda').to(torch.bfloat16)
+    kernel = torch.zeros(n, n, device='cuda')
+    ms = timer(lambda: ops.gram_hadamard(kernel, a, g, one=1.0))
+    ops.set_backend('torch')
+    ms_lib = timer(lambda: ops.gram_hadamard(kernel, a, g, one=1.0))
+    ops.set_backend('auto')
+    fl = 2.0 * n * n * (d_in + d_out)
+    emit(case='gram_hadamard_bf16', n=n, d_in=d_in, d_out=d_out, ms=round(ms, 4), tflops=round(fl / ms / 1e9, 1),
+         frac_of_peak_flops=round(fl / (ms * 1e-3) / flops_peak, 3), peak_source=src, torch_ms=round(ms_lib, 4),
+         speedup_vs_torch=round(ms_lib / ms, 2))
+
+
+def bench_bfgs(timer, n):
+    """Powell damping + rank-2 update of the inverse (5 launches) against the PyTorch ops of the same update."""
+    from asdl_b200.precondition.kbfgs import powell_lm_damping_, bfgs_inv_update_
+    base = torch.randn(n, n, device='cuda')
+    H = base @ base.T / n + torch.eye(n, device='cuda')
+    s0 = torch.randn(n, device='cuda')
+    y0 = torch.randn(n, device='cuda') + 2 * s0
+
+    def run():
+        s, y = s0.clone(), y0.clone()
+        powell_lm_damping_(H, s, y, 0.2, 1e-3)
+        bfgs_inv_update_(H, s, y)
+
+    ms = timer(run)
+    ops.set_backend('torch')
+    ms_lib = timer(run)
+    ops.set_backend('auto')
+    emit(case='bfgs_damping_and_update_fp32', n=n, ms=round(ms, 4), torch_ms=round(ms_lib, 4),
+         speedup_vs_torch=round(ms_lib / ms, 2), passes_over_H='mat-vec read, symmetrise read + write, update read + write')
+
+
+def bench_embedding(timer, tokens, vocab, dim):
+    """Diagonal statistics of an embedding table (reductions per token row) against index_add_ of the squares."""
+    from asdl_b200.operations.embedding import Embedding as EmbOp
+    emb = torch.nn.Embedding(vocab, dim).cuda()
+    idx = torch.randint(0, vocab, (tokens,), device='cuda')
+    g = torch.randn(tokens, dim, device='cuda').to(torch.bfloat16)
+    ms = timer(lambda: EmbOp.cov_diag_weight(emb, idx, g))
+    ops.set_backend('torch')
+    ms_lib = timer(lambda: EmbOp.cov_diag_weight(emb, idx, g.float()))
+    ops.set_backend('auto')
+    emit(case='embedding_diag_stats_bf16', tokens=tokens, vocab=vocab, dim=dim, ms=round(ms, 4), torch_ms=round(ms_lib, 4),
+         speedup_vs_torch=round(ms_lib / ms, 2), includes='zero-fill of the vocab x dim output')
+
+
 def bench_symm(timer, world, mb, hbm, src):
     """The segment kernels of the NVLink transport on ranks emulated on ONE GPU (every "peer" buffer is
     local memory, so this measures the kernels against HBM, not the link): owner pull-reduce and push."""
@@ -248,7 +299,7 @@ def bench_batchnorm(timer, n, c, hw, hbm, flops_peak, src):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--only', default=None, choices=['syrk', 'syrk_x3', 'layouts', 'precond', 'inverse', 'roots', 'eigh', 'lnstats', 'symm', 'im2col', 'batchnorm'])
+    ap.add_argument('--only', default=None, choices=['syrk', 'syrk_x3', 'layouts', 'precond', 'inverse', 'roots', 'eigh', 'lnstats', 'gram_hadamard', 'bfgs', 'embedding', 'symm', 'im2col', 'batchnorm'])
     ap.add_argument('--wide', type=int, default=-1, help='tile policy of the GEMM: -1 = default (3), 0 = 128 wide, 1 = 256 wide for large outputs, 2 = 256 wide wherever legal, 3 = CTA pairs (256 x 256, cta_group::2) for large products, 4 = CTA pairs everywhere')
     ap.add_argument('--chol', default=None, choices=['tensor_core', 'cuda_core'], help='grouped inverse backend')
     ap.add_argument('--rows', type=int, default=None)
@@ -295,6 +346,14 @@ def main():
     if want('lnstats'):
         for rows, d in [(8192, 1024), (12608, 768)]:
             bench_lnstats(timer, rows, d, hbm, src)
+    if want('gram_hadamard'):
+        for n, d_in, d_out in [(2048, 4608, 512), (1024, 1024, 1024), (4096, 768, 3072)]:
+            bench_gram_hadamard(timer, n, d_in, d_out, fl, src)
+    if want('bfgs'):
+        for n in (1024, 4608):
+            bench_bfgs(timer, n)
+    if want('embedding'):
+        bench_embedding(timer, 8192, 50304, 1024)
     if want('symm'):
         bench_symm(timer, 4, 64, hbm, src)
     if want('im2col'):

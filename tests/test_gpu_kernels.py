@@ -421,7 +421,8 @@ def test_transposing_cast_kernel(ext, rows, cols):
     ops.check_status()
 
 
-@pytest.mark.parametrize('rows,d', [(64, 256), (197 * 3, 768), (1000, 1024), (9, 4096), (33, 1536)])
+@pytest.mark.parametrize('rows,d', [(64, 256), (197 * 3, 768), (1000, 1024), (9, 4096), (33, 1536), (1001, 2048),
+                                    (517, 3072), (600, 4096)])
 def test_layer_norm_kernels(ext, rows, d):
     """Forward and backward (input, weight, bias gradients) against F.layer_norm in fp32."""
     torch.manual_seed(0)
@@ -724,6 +725,39 @@ def test_cvp_and_cov_on_cuda_match_cpu():
         assert rel_err(b, a) < 2e-5
     for a, b in zip(fvps_c, fvps_g):
         assert rel_err(b, a) < 2e-5
+    ops.check_status()
+
+
+def test_general_matmul_and_psgd_dense_products():
+    """ops.matmul in its four operand layouts (no transpose copies) and the dense Kronecker PSGD step and
+    application built on it, against fp64 / the CPU path."""
+    from asdl_b200.precondition.psgd import update_precond_kron, precond_grad_kron
+    torch.manual_seed(0)
+    a, b = torch.randn(300, 520, device=DEV), torch.randn(520, 264, device=DEV)
+    ref = a.double() @ b.double()
+    for ta in (False, True):
+        for tb in (False, True):
+            x = a.T.contiguous() if ta else a
+            y = b.T.contiguous() if tb else b
+            assert rel_err(ops.matmul(x, y, trans_a=ta, trans_b=tb), ref.float()) < 2e-5
+    acc = torch.ones(300, 300, device=DEV)
+    ops.matmul(a, a, trans_b=True, alpha=-0.5, out=acc, beta=2.0, sym=True)
+    assert rel_err(acc, (2.0 - 0.5 * (a.double() @ a.double().T)).float()) < 2e-5
+    # one PSGD fitting step and one application with 320 x 320 and 260 x 260 upper-triangular factors
+    m, n = 320, 260
+    Ql = torch.triu(torch.randn(m, m) * 0.05) + torch.eye(m)
+    Qr = torch.triu(torch.randn(n, n) * 0.05) + torch.eye(n)
+    dX, dG, grad = torch.randn(m, n) * 0.1, torch.randn(m, n), torch.randn(m, n)
+    Ql_g, Qr_g = Ql.to(DEV), Qr.to(DEV)
+    before = ops.extension().launch_count()
+    new_l, new_r = update_precond_kron(Ql.clone(), Qr.clone(), dX, dG, step=0.05)
+    got_l, got_r = update_precond_kron(Ql_g, Qr_g, dX.to(DEV), dG.to(DEV), step=0.05)
+    assert ops.extension().launch_count() > before
+    assert rel_err(got_l.cpu(), new_l) < 1e-4 and rel_err(got_r.cpu(), new_r) < 1e-4
+    assert rel_err(got_l.cpu() - Ql, new_l - Ql) < 2e-3          # the update itself, not only the factor
+    want = precond_grad_kron(new_l, new_r, grad)
+    got = precond_grad_kron(got_l, got_r, grad.to(DEV))
+    assert rel_err(got.cpu(), want) < 1e-4
     ops.check_status()
 
 

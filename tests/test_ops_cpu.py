@@ -136,3 +136,48 @@ def test_layer_norm_and_backends():
     with pytest.raises(ValueError):
         ops.set_backend('no_such_backend')
     ops.check_status()     # nothing to report without a GPU
+
+
+def test_general_matmul_gram_hadamard_and_small_statistics():
+    """PyTorch paths of the products and statistics added with the second kernel set: the general matmul
+    in its four layouts, the Hadamard-factored Gram update, the BFGS pair damping / inverse update, and
+    the embedding statistics, each against an independent formula."""
+    torch.manual_seed(0)
+    a, b = torch.randn(6, 9), torch.randn(9, 4)
+    for ta in (False, True):
+        for tb in (False, True):
+            x, y = (a.T.contiguous() if ta else a), (b.T.contiguous() if tb else b)
+            torch.testing.assert_close(ops.matmul(x, y, trans_a=ta, trans_b=tb, alpha=2.0), 2.0 * a @ b)
+    out = torch.ones(6, 6)
+    ops.matmul(a, a, trans_b=True, alpha=-1.0, out=out, beta=3.0, sym=True)
+    torch.testing.assert_close(out, 3.0 - a @ a.T)
+    torch.testing.assert_close(ops.matmul_nn(a, b, scale=0.5), 0.5 * a @ b)
+    # kernel += scale * (a1 a2^T + one) o (g1 g2^T), entry by entry
+    a1, a2, g1, g2 = torch.randn(5, 7), torch.randn(3, 7), torch.randn(5, 2), torch.randn(3, 2)
+    kernel = torch.full((5, 3), 0.5)
+    ops.gram_hadamard(kernel, a1, g1, a2, g2, one=1.0, scale=0.25)
+    want = torch.tensor([[0.5 + 0.25 * (a1[i] @ a2[j] + 1.0) * (g1[i] @ g2[j]) for j in range(3)] for i in range(5)])
+    torch.testing.assert_close(kernel, want)
+    # BFGS: the updated inverse satisfies the secant equation H y = s for the damped pair and stays symmetric
+    from asdl_b200.precondition.kbfgs import powell_lm_damping_, bfgs_inv_update_
+    base = torch.randn(8, 8, dtype=torch.float64)
+    H = base @ base.T / 8 + torch.eye(8, dtype=torch.float64)
+    s, y = torch.randn(8, dtype=torch.float64), torch.randn(8, dtype=torch.float64)
+    powell_lm_damping_(H, s, y, 0.2, 0.1)
+    assert (s @ y) > 0
+    bfgs_inv_update_(H, s, y)
+    torch.testing.assert_close(H @ y, s)
+    torch.testing.assert_close(H, H.T)
+    # embedding: diagonal statistics and per-example counts against loops over tokens
+    from asdl_b200.operations.embedding import Embedding as EmbOp
+    emb = nn.Embedding(11, 4, padding_idx=2)
+    idx, g = torch.randint(0, 11, (3, 5)), torch.randn(3, 5, 4)
+    diag = torch.zeros(11, 4)
+    counts = torch.zeros(3, 11)
+    for n in range(3):
+        for t in range(5):
+            counts[n, idx[n, t]] += 1
+            if idx[n, t] != 2:
+                diag[idx[n, t]] += g[n, t] ** 2
+    torch.testing.assert_close(EmbOp.cov_diag_weight(emb, idx, g), diag)
+    torch.testing.assert_close(EmbOp.cov_kron_A(emb, idx), counts.T @ counts)
