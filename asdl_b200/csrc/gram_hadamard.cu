@@ -144,12 +144,27 @@ gram_hadamard_kernel(const __grid_constant__ HadamardProblem P) {
         tmem_ld_wait();
         if (gr < P.M) {
           float* dst = P.C + static_cast<size_t>(gr) * P.ldc + col0 + c * 32;
+          float upd[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            if (col0 + c * 32 + j < P.N) {
-              const float a = have_a ? __uint_as_float(ra[j]) : 0.f;
-              dst[j] += P.alpha * (a + P.one) * __uint_as_float(rg[j]);
-            }
+            const float a = have_a ? __uint_as_float(ra[j]) : 0.f;
+            upd[j] = P.alpha * (a + P.one) * __uint_as_float(rg[j]);
+          }
+          const bool vec = (col0 + c * 32 + 32 <= P.N) && ((P.ldc & 3) == 0) &&
+                           ((reinterpret_cast<uintptr_t>(P.C) & 15) == 0);
+          if (vec) {
+            // all eight 16-byte loads of the row segment are in flight before the first store
+            float4 cur[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cur[j] = *reinterpret_cast<const float4*>(dst + 4 * j);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<float4*>(dst + 4 * j) = make_float4(cur[j].x + upd[4 * j], cur[j].y + upd[4 * j + 1],
+                                                                    cur[j].z + upd[4 * j + 2], cur[j].w + upd[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + c * 32 + j < P.N) dst[j] += upd[j];
           }
         }
       }

@@ -19,6 +19,8 @@ for the reference life cycle) nothing is allocated or re-packed per step:
 """
 from typing import Dict, List
 
+import os
+
 import torch
 import torch.nn as nn
 import torch.distributed as dist
@@ -145,6 +147,13 @@ class FusedKfacGradientMaker(KfacGradientMaker):
     #: step was measured 0.48 ms SLOWER with it than with plain peer stores (7.11 vs 6.63 ms); the coalesced
     #: segment kernels (gradient pull, broadcast of the rest) do use the multicast mapping.
     multicast_epilogue = False
+
+    #: Where the owners' preconditioned gradients of the Kronecker layers reach the other ranks: True - the
+    #: final GEMM's epilogue stores every tile into every rank's buffer (no extra pass, but world - 1 peer
+    #: stores of 16 bytes per lane); False - the epilogue stores locally and the coalesced broadcast kernel
+    #: that pushes the remaining gradients (``multimem.st`` where the buffer has a multicast mapping) pushes
+    #: these too.  The environment variable ASDL_B200_REPLICATE_IN_EPILOGUE (0 / 1) overrides it.
+    replicate_in_epilogue = True
 
     #: plain steps that run eagerly before the CUDA graphs are captured (the capture itself warms
     #: every step kind up twice, so none are needed)
@@ -1037,17 +1046,21 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         with nvtx_range('kfac_precondition'), self._phase('precondition'):
             owned = [st for st in self._kron if st.owner == self.world_rank]
             todo = [st for st in owned if st.has_inv]
-            replicated = len(todo) == len(owned)
+            replicated = len(todo) == len(owned) and self._replicate_in_epilogue()
             if todo and self._use_grouped(todo):
                 self._precondition_kron_grouped(todo, grad_scale)
             else:
                 for st in todo:
-                    replicated &= self._precondition_kron(st, grad_scale, replicate=True)
+                    replicated &= self._precondition_kron(st, grad_scale, replicate=self._replicate_in_epilogue())
             self._precondition_norms(grad_scale)
         # the GEMM epilogues have already stored the Kronecker layers' results on every rank
         with self._phase('grad_bcast'):
             arena.bcast_segments(self._rest_segs if replicated else self._grad_segs)
             arena.barrier()
+
+    def _replicate_in_epilogue(self):
+        env = os.environ.get('ASDL_B200_REPLICATE_IN_EPILOGUE')
+        return bool(int(env)) if env is not None else bool(self.replicate_in_epilogue)
 
     # grouped path: all layers' products in a handful of launches ------------------------------------
     def _use_grouped(self, todo):
@@ -1076,7 +1089,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             else:
                 a_off, view = self._grad_slot[w]
                 region = arena.buffer[a_off:a_off + m * n]
-                if arena.multicast_ptr and self.multicast_epilogue:
+                if not self._replicate_in_epilogue():
+                    dst_ptr, extra = arena.ptr(arena.rank, a_off), []
+                elif arena.multicast_ptr and self.multicast_epilogue:
                     # one multimem.st per 16 bytes reaches every rank, this one included
                     dst_ptr, extra, mcast = 0, [arena.mc_ptr(a_off)], True
                 else:
