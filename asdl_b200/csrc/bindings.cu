@@ -55,6 +55,7 @@ void symm_bucket_reduce(at::Tensor peers, int64_t rank, int64_t world, int64_t s
                         int64_t mc_ptr, int64_t wait_ms, int64_t blocks);
 void symm_scale_segments(at::Tensor local, at::Tensor segs, double beta);
 void symm_mirror_lower(at::Tensor local, at::Tensor mats, int64_t n_max);
+void symm_pull_slots(at::Tensor local, at::Tensor peers, at::Tensor table, int64_t world, int64_t n_max, double beta);
 void symm_reduce_slots(at::Tensor local, at::Tensor table, int64_t world, int64_t slot_stride, int64_t n_max,
                        double beta);
 void chol_inverse(std::vector<at::Tensor> mats, std::vector<at::Tensor> outs, at::Tensor damping);
@@ -121,6 +122,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_scale_segments", &b200::symm_scale_segments);
   m.def("symm_mirror_lower", &b200::symm_mirror_lower);
   m.def("symm_reduce_slots", &b200::symm_reduce_slots);
+  m.def("symm_pull_slots", &b200::symm_pull_slots);
   m.def("chol_inverse", &b200::chol_inverse, "grouped damped SPD inverse (fp32, CUDA cores)");
   m.def("chol_inverse_tc", &b200::chol_inverse_tc, "grouped damped SPD inverse (fp32-accurate, tensor cores)");
   m.def("chol_inverse_tc_clear_cache", &b200::chol_inverse_tc_clear_cache);

@@ -14,6 +14,8 @@
 //   symm_scale_segments   local beta-scaling of segments (moving-average decay of owned factors).
 //   symm_reduce_slots     owner-side sum of the per-rank slots that the peers' SYRK epilogues stored
 //                         into (lower triangles), folded into the running factor and mirrored.
+//   symm_pull_slots       the same sum with every rank's contribution read from that rank's own buffer
+//                         (coalesced peer loads): the SYRK epilogues store locally.
 //   symm_mirror_lower     upper triangle <- lower triangle of local matrices.
 //   symm_bucket_reduce    one kernel per gradient bucket on a communication stream: every rank
 //                         announces "my part of this bucket is in place", waits (bounded) for all
@@ -330,6 +332,70 @@ __global__ void symm_reduce_slots_kernel(float* base, const SlotRow* table, int 
   }
 }
 
+// Pull variant: every rank keeps its own contribution to a factor in ITS OWN buffer (the SYRK epilogue
+// stores locally), at the same offset on every rank; the owner reads that offset from every rank with
+// coalesced loads over NVLink (128 bytes per warp and row), sums in rank order and mirrors.  A lane-per-row
+// epilogue store into a peer is sixteen bytes per lane and instruction; a pull moves whole lines.
+__device__ __forceinline__ float ld_peer_f32(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void symm_pull_slots_kernel(float* base, const long long* __restrict__ peers, const SlotRow* table, int world,
+                                       float beta) {
+  __shared__ float tile[32][33];
+  const SlotRow m = table[blockIdx.y];
+  const int n = static_cast<int>(m.n);
+  const int nt = (n + 31) / 32;
+  const int t = blockIdx.x;
+  if (t >= nt * (nt + 1) / 2) return;
+  int r = static_cast<int>((sqrtf(8.f * t + 1.f) - 1.f) * 0.5f);
+  while ((r + 1) * (r + 2) / 2 <= t) ++r;
+  while (r * (r + 1) / 2 > t) --r;
+  const int tr = r, tc = t - r * (r + 1) / 2;  // tile row >= tile column
+  float* f = base + m.f_off;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  // the four rows of a thread and up to four ranks at a time: sixteen loads in flight per thread
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  bool live[4];
+  size_t idx[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int gr = tr * 32 + ty + 8 * k, gc = tc * 32 + tx;
+    live[k] = gr < n && gc < n && gc <= gr;
+    idx[k] = static_cast<size_t>(gr) * n + gc;
+  }
+  for (int q0 = 0; q0 < world; q0 += 4) {
+    float v[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const bool have = q0 + u < world;
+      const float* src = have ? reinterpret_cast<const float*>(peers[q0 + u]) + m.slot_off : nullptr;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[u][k] = (have && live[k]) ? ld_peer_f32(src + idx[k]) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[k] += v[u][k];
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float v = acc[k];
+    if (live[k]) {
+      if (beta != 0.f) v = fmaf(beta, f[idx[k]], v);
+      f[idx[k]] = v;
+    }
+    tile[ty + 8 * k][tx] = live[k] ? v : 0.f;
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int dr = tc * 32 + i, dc = tr * 32 + tx;  // destination (row, col) = source (col, row)
+    if (dr < n && dc < n && dc > dr) f[static_cast<size_t>(dr) * n + dc] = tile[tx][i];
+  }
+}
+
 // ---- host ------------------------------------------------------------------------------------
 static int sm_count(int dev) { return at::cuda::getDeviceProperties(dev)->multiProcessorCount; }
 
@@ -467,6 +533,29 @@ void symm_reduce_slots(at::Tensor local, at::Tensor table, int64_t world, int64_
   symm_reduce_slots_kernel<<<grid, 256, 0, stream>>>(local.data_ptr<float>(),
                                                      reinterpret_cast<const SlotRow*>(table.data_ptr<int64_t>()),
                                                      static_cast<int>(world), slot_stride, static_cast<float>(beta));
+  B200_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+}
+
+// table: [k, 3] rows of (offset of the local factor, offset of the contribution on EVERY rank, n); peers: one
+// base pointer per rank.  factor <- beta * factor + sum over ranks of their contributions (lower triangles), mirrored.
+void symm_pull_slots(at::Tensor local, at::Tensor peers, at::Tensor table, int64_t world, int64_t n_max, double beta) {
+  TORCH_CHECK(local.is_cuda() && local.scalar_type() == at::kFloat && local.is_contiguous(),
+              "local must be a contiguous fp32 CUDA tensor");
+  check_table(peers, static_cast<int>(world));
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.is_contiguous() && table.dim() == 2 &&
+                  table.size(1) == 3, "table must be a CUDA int64 [k, 3] tensor");
+  if (table.size(0) == 0) return;
+  TORCH_CHECK(n_max > 0 && world > 0, "bad arguments");
+  const int nt = static_cast<int>((n_max + 31) / 32);
+  const int dev = local.get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  dim3 grid(nt * (nt + 1) / 2, static_cast<unsigned>(table.size(0)));
+  symm_pull_slots_kernel<<<grid, 256, 0, stream>>>(local.data_ptr<float>(),
+                                                   reinterpret_cast<const long long*>(peers.data_ptr<int64_t>()),
+                                                   reinterpret_cast<const SlotRow*>(table.data_ptr<int64_t>()),
+                                                   static_cast<int>(world), static_cast<float>(beta));
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch();
 }

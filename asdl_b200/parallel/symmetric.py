@@ -162,5 +162,12 @@ class SymmetricArena:
         their SYRK epilogues; this reduction reads local memory only."""
         ops.extension().symm_reduce_slots(self.buffer, table, self.world, int(slot_stride), int(n_max), float(beta))
 
+    def pull_slots(self, table: torch.Tensor, n_max: int, beta: float):
+        """For every row (factor offset, contribution offset, n) of ``table``: the local n x n factor becomes
+        ``beta * factor + sum over ranks of the n x n block at `contribution offset` of THAT rank's buffer``
+        (lower triangles, mirrored).  Every rank's SYRK epilogue stores into its own buffer; the owner reads
+        the peers' copies with coalesced loads over NVLink."""
+        ops.extension().symm_pull_slots(self.buffer, self.peers_dev, table, self.world, int(n_max), float(beta))
+
     def scale_segments(self, segs: torch.Tensor, beta: float):
         ops.extension().symm_scale_segments(self.buffer, segs, float(beta))

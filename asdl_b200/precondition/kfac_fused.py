@@ -152,8 +152,15 @@ class FusedKfacGradientMaker(KfacGradientMaker):
     #: final GEMM's epilogue stores every tile into every rank's buffer (no extra pass, but world - 1 peer
     #: stores of 16 bytes per lane); False - the epilogue stores locally and the coalesced broadcast kernel
     #: that pushes the remaining gradients (``multimem.st`` where the buffer has a multicast mapping) pushes
-    #: these too.  The environment variable ASDL_B200_REPLICATE_IN_EPILOGUE (0 / 1) overrides it.
-    replicate_in_epilogue = True
+    #: these too.  Measured (ResNet-50, 20-step window): 7.15 against 7.68 ms per step at 4 GPUs, 7.27 against
+    #: 7.39 at 2.  The environment variable ASDL_B200_REPLICATE_IN_EPILOGUE (0 / 1) overrides it.
+    replicate_in_epilogue = False
+
+    #: How a rank's share of a factor's statistics reaches the factor's owner: True - every rank's SYRK epilogue
+    #: stores its lower-triangular tiles into its OWN buffer and the owner pulls them from all ranks with
+    #: coalesced loads while it sums; False - the epilogue stores them into a slot in the owner's buffer
+    #: (16 bytes per lane and store over NVLink).  ASDL_B200_PULL_STATISTICS (0 / 1) overrides it.
+    pull_statistics = True
 
     #: plain steps that run eagerly before the CUDA graphs are captured (the capture itself warms
     #: every step kind up twice, so none are needed)
@@ -289,7 +296,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         arena = self._arena = SymmetricArena(total, group=self.sync_group, device=self.device)
         rank = self.world_rank
         self._slots_off, _ = arena.alloc(self.world_size * self._slot_stride)
-        stage_segs, grad_segs, mirror_rows, slot_rows = [], [], [], []
+        stage_segs, grad_segs, mirror_rows, slot_rows, pull_rows = [], [], [], [], []
         for st in self._kron:
             st.A_off, st.A = arena.alloc(st.d_in, st.d_in)
             st.B_off, st.B = arena.alloc(st.d_out, st.d_out)
@@ -299,6 +306,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                 mirror_rows += [[st.A_off, st.d_in], [st.B_off, st.d_out]]
                 slot_rows += [[st.A_off, self._slots_off + st.slot_rel[0], st.d_in],
                               [st.B_off, self._slots_off + st.slot_rel[1], st.d_out]]
+                # pull variant: region `rank` of every rank's slot area holds that rank's share of this owner's factors
+                pull_rows += [[st.A_off, self._slots_off + rank * self._slot_stride + st.slot_rel[0], st.d_in],
+                              [st.B_off, self._slots_off + rank * self._slot_stride + st.slot_rel[1], st.d_out]]
         for st in self._norm:
             st.stage_off, st.stage = arena.alloc(*st.stats.shape)
             st.owner = self._owner.get(st.module, 0)
@@ -337,6 +347,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             self._comm_stream = torch.cuda.Stream(device=self.device)
         self._mirror_n_max = max([r[1] for r in mirror_rows], default=0)
         self._slot_table = torch.tensor(slot_rows, dtype=torch.int64, device=self.device).reshape(-1, 3)
+        self._pull_table = torch.tensor(pull_rows, dtype=torch.int64, device=self.device).reshape(-1, 3)
         self._stage_segs = arena.segments(stage_segs)
         self._grad_segs = arena.segments(grad_segs)
 
@@ -774,10 +785,17 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             segs_a = [hi, hi, lo] if lo is not None else [hi]
         segs_b = [segs_a[0], segs_a[2], segs_a[0]] if len(segs_a) == 3 else segs_a
         n_dim = st.d_in if is_A else st.d_out
-        off = self._slots_off + self.world_rank * self._slot_stride + st.slot_rel[0 if is_A else 1]
-        # plain (coalesced) stores of the lower-triangular tiles into this rank's slot on the owner; a further
-        # backward pass of the same curvature pass adds to the slot (the slot has one writer, this rank)
-        ext.umma_gemm_to_ptr(segs_a, segs_b, False, False, arena.ptr(st.owner, off), n_dim,
+        if self._pull_statistics():
+            # this rank's own buffer, region of the factor's owner: the owner pulls it after the barrier
+            off = self._slots_off + st.owner * self._slot_stride + st.slot_rel[0 if is_A else 1]
+            target = arena.ptr(self.world_rank, off)
+        else:
+            # this rank's slot in the owner's buffer: peer stores from the epilogue
+            off = self._slots_off + self.world_rank * self._slot_stride + st.slot_rel[0 if is_A else 1]
+            target = arena.ptr(st.owner, off)
+        # lower-triangular tiles only; a further backward pass of the same curvature pass adds to the region
+        # (it has one writer, this rank)
+        ext.umma_gemm_to_ptr(segs_a, segs_b, False, False, target, n_dim,
                              float(scale), True, 2 if accumulate else 3, [], 0)
 
     @staticmethod
@@ -917,7 +935,10 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             alpha, beta = self._stat_weights()
             self._arena.barrier()  # every rank's tiles have landed in the owners' slots
             if self._mirror_n_max > 0:  # running factor <- beta * factor + sum of the slots, mirrored
-                self._arena.reduce_slots(self._slot_table, self._slot_stride, self._mirror_n_max, beta)
+                if self._pull_statistics():
+                    self._arena.pull_slots(self._pull_table, self._mirror_n_max, beta)
+                else:
+                    self._arena.reduce_slots(self._slot_table, self._slot_stride, self._mirror_n_max, beta)
             self._arena.reduce_segments(self._stage_segs, 1.0 / self.world_size)
             with torch.no_grad():
                 mine = [st for st in self._norm if st.owner == self.world_rank]
@@ -1057,6 +1078,10 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         with self._phase('grad_bcast'):
             arena.bcast_segments(self._rest_segs if replicated else self._grad_segs)
             arena.barrier()
+
+    def _pull_statistics(self):
+        env = os.environ.get('ASDL_B200_PULL_STATISTICS')
+        return bool(int(env)) if env is not None else bool(self.pull_statistics)
 
     def _replicate_in_epilogue(self):
         env = os.environ.get('ASDL_B200_REPLICATE_IN_EPILOGUE')
