@@ -8,11 +8,14 @@ rank holds activations a [B, n] (bf16, N(0,1)) and contributes a^T a / (B W) to 
 owner adds damping, inverts in fp32 and applies the inverse to an n x n gradient; every rank ends
 up with all W preconditioned gradients.
 
-  fused    SYRK whose epilogue stores its lower-triangular tiles into this rank's slot on the
-           owner over NVLink (compute + send in one kernel), bounded flag barrier, owner-side sum
-           of the slots, grouped Cholesky inverse,
-           tcgen05 GEMM whose epilogue stores the result into every rank's buffer (compute +
-           all-gather in one kernel).
+  fused    --transport pull (default): tcgen05 SYRKs whose epilogues store lower-triangular tiles into this
+           rank's own symmetric buffer, bounded flag barrier, owner-side kernel that reads every rank's
+           share with coalesced loads over NVLink while it sums and mirrors (reduce + transfer in one
+           kernel), grouped Cholesky inverse on the tensor cores, tcgen05 GEMM, coalesced broadcast of the
+           result into every rank's buffer (multimem.st through the switch where mapped), barrier.
+           --transport push: the SYRK epilogue stores its tiles into this rank's slot on the owner and the
+           GEMM epilogue stores the result into every rank's buffer (compute + send in one kernel); a
+           lane of the epilogue holds a row of the accumulator, so these are 16-byte stores over NVLink.
   library  torch.matmul (cuBLAS, fp32 output) + dist.all_reduce (NCCL) + torch.linalg.cholesky /
            cholesky_inverse (cuSOLVER) + torch.matmul + dist.all_gather.
 
@@ -73,6 +76,10 @@ def main():
     ap.add_argument('--iters', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--damping', type=float, default=1e-3)
+    ap.add_argument('--transport', default='pull', choices=['pull', 'push'],
+                    help="pull: SYRK epilogues store locally, the owner reads every rank's share with coalesced peer loads "
+                         "while it sums, and the result is pushed by the coalesced broadcast kernel; "
+                         "push: the SYRK and GEMM epilogues store straight into the other GPUs' buffers")
     args = ap.parse_args()
     rank = int(os.environ.get('RANK', '0'))
     local = int(os.environ.get('LOCAL_RANK', '0'))
@@ -102,20 +109,33 @@ def main():
         damp = torch.full((1,), args.damping, device=dev)
         peers_y = [arena.ptr(r, y_off[rank][0]) for r in range(world) if r != rank]
 
+        pull_table = torch.tensor([[f_off[rank][0], slots_off + rank * nn_, n]], dtype=torch.int64, device=dev)
+        y_segs = arena.segments([(y_off[rank][0], nn_)])
+        pull = args.transport == 'pull'
+
         def fused():
-            for k in range(world):  # staggered: at any time every owner receives from one peer
+            for k in range(world):
                 r = (rank + 1 + k) % world
-                ext.umma_gemm_to_ptr([a], [a], False, False, arena.ptr(r, slots_off + rank * nn_), n,
+                if pull:   # region r of this rank's own buffer holds its share of factor r
+                    target = arena.ptr(rank, slots_off + r * nn_)
+                else:      # staggered: at any time every owner receives from one peer
+                    target = arena.ptr(r, slots_off + rank * nn_)
+                ext.umma_gemm_to_ptr([a], [a], False, False, target, n,
                                      1.0 / (B * world), True, 3, [], 0)   # lower-triangular tiles, plain stores
             arena.barrier()
-            arena.reduce_slots(slot_table, nn_, n, 0.0)
+            if pull:
+                arena.pull_slots(pull_table, n, 0.0)
+            else:
+                arena.reduce_slots(slot_table, nn_, n, 0.0)
             ops.spd_inverse_grouped([f_off[rank][1]], [inv], damp)
             ext.cast_pad_bf16(inv, i_hi, i_lo, 1.0)
             ext.cast_pad_bf16(grad, g_hi, g_lo, 1.0)
             gh, gl, ih, il = g_hi[:, :n], g_lo[:, :n], i_hi[:, :n], i_lo[:, :n]
             # Y = G A^-1: G is [n(M), n(K)] K-major; A^-1 symmetric, read as [K, N] MN-major
             ext.umma_gemm_to_ptr([gh, gh, gl], [ih, il, ih], True, False, arena.ptr(rank, y_off[rank][0]), n,
-                                 1.0, False, False, peers_y, 0)
+                                 1.0, False, False, [] if pull else peers_y, 0)
+            if pull and world > 1:
+                arena.bcast_segments(y_segs)
             arena.barrier()
 
         stack = torch.empty(world, n, n, device=dev)
@@ -154,7 +174,8 @@ def main():
         roof_ms = max(flops / peak, wire / NVLINK_BPS) * 1e3
         if rank == 0:
             print(json.dumps({
-                'case': 'curvature_micro', 'n': n, 'batch': B, 'n_gpus': world, 'fused_ms': round(ms_fused, 4),
+                'case': 'curvature_micro', 'n': n, 'batch': B, 'n_gpus': world, 'transport': args.transport,
+                'fused_ms': round(ms_fused, 4),
                 'library_ms': round(ms_lib, 4), 'speedup': round(ms_lib / ms_fused, 2),
                 'inverse_ms_in_fused': round(ms_inv, 4),
                 'roofline_ms_excl_inverse': round(roof_ms, 4),
