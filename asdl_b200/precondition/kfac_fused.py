@@ -113,11 +113,12 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             two GEMM launches for the whole model) instead of a few launches per layer.
         comm: data-parallel transport.  ``'symmetric'`` keeps factors and gradients in NVLink
             symmetric memory and uses the library's own kernels: the statistics SYRKs store their
-            lower-triangular tiles straight into per-rank slots on the owner (peer stores from the
-            MMA epilogue; the owner sums its slots into the running factor), owners pull-reduce
-            the gradients of their layers bucket by bucket while the backward pass is still
-            running (``overlap_grad_reduce``), and the preconditioning GEMM's epilogue stores its
-            result into every rank's gradient buffer.  ``'torch'`` uses
+            lower-triangular tiles into this rank's buffer and the owner of a factor reads every
+            rank's share over NVLink while it sums them into the running factor
+            (``pull_statistics``), owners pull-reduce the gradients of their layers - bucket by
+            bucket while the backward pass is still running with ``overlap_grad_reduce`` - and push
+            their preconditioned gradients into every rank's gradient buffer with a coalesced
+            broadcast kernel (``replicate_in_epilogue`` selects the GEMM epilogue instead).  ``'torch'`` uses
             ``torch.distributed`` collectives (any backend).  ``'auto'`` picks ``'symmetric'``
             for multi-rank CUDA runs.
         batch_statistics: record the statistics products of a curvature pass (one per Kronecker
@@ -1052,8 +1053,9 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             self.sync_grad_post_precondition()
 
     def _precondition_symmetric(self, grad_scale):
-        """barrier -> owners pull-reduce the gradients of their layers -> precondition (the final
-        GEMM stores into every rank's gradient buffer) -> push the small rest -> barrier."""
+        """barrier -> owners pull-reduce the gradients of their layers -> precondition -> owners push
+        their gradients into every rank's buffer (only the small rest when the final GEMM's epilogue has
+        already stored the Kronecker layers' results everywhere) -> barrier."""
         arena = self._arena
         with self._phase('grad_reduce'):
             if self._reduced_in_backward:
@@ -1074,7 +1076,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
                 for st in todo:
                     replicated &= self._precondition_kron(st, grad_scale, replicate=self._replicate_in_epilogue())
             self._precondition_norms(grad_scale)
-        # the GEMM epilogues have already stored the Kronecker layers' results on every rank
+        # with replicate_in_epilogue the GEMM epilogues have already stored the Kronecker layers' results on every rank
         with self._phase('grad_bcast'):
             arena.bcast_segments(self._rest_segs if replicated else self._grad_segs)
             arena.barrier()
