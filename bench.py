@@ -39,6 +39,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 import torch
@@ -74,16 +75,56 @@ def parse_args():
 
 
 class ClockSampler:
-    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks / throttle reasons of the job's GPUs while the timed region runs: an NVML thread
+    (a reading every 10 ms, no start-up delay, so even a 150 ms region gets a dozen samples per GPU), or an
+    ``nvidia-smi -lms`` child process where the NVML bindings are missing.  Reads only; sets nothing."""
     QUERY = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
              'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
              'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+    REASON_BITS = {'sw_power_cap': 0x4, 'hw_slowdown': 0x8, 'sw_thermal_slowdown': 0x20, 'hw_thermal_slowdown': 0x40}
 
     def __init__(self):
         self.proc = None
         self.path = None
+        self.thread = None
+        self.samples = []
+        self.max_clocks = []
+        self.reason_mask = 0
+        self._stop = False
 
-    def start(self):
+    def _nvml_handles(self, gpu_indices):
+        import pynvml
+        pynvml.nvmlInit()
+        handles = []
+        for i in gpu_indices:
+            try:
+                uuid = str(torch.cuda.get_device_properties(i).uuid)
+                handles.append(pynvml.nvmlDeviceGetHandleByUUID(('GPU-' + uuid) if not uuid.startswith('GPU-') else uuid))
+            except Exception:
+                handles.append(pynvml.nvmlDeviceGetHandleByIndex(i))
+        return pynvml, handles
+
+    def _run(self, pynvml, handles):
+        reasons = getattr(pynvml, 'nvmlDeviceGetCurrentClocksEventReasons', None) or \
+            getattr(pynvml, 'nvmlDeviceGetCurrentClocksThrottleReasons')
+        while not self._stop:
+            for h in handles:
+                try:
+                    self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                    self.reason_mask |= int(reasons(h))
+                except Exception:
+                    pass
+            time.sleep(0.01)
+
+    def start(self, gpu_indices=(0,)):
+        try:
+            pynvml, handles = self._nvml_handles(list(gpu_indices))
+            self.max_clocks = [float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)) for h in handles]
+            self.thread = threading.Thread(target=self._run, args=(pynvml, handles), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix='.csv')
             os.close(fd)
@@ -95,6 +136,16 @@ class ClockSampler:
 
     def stop(self, gpu_indices):
         out = {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': []}
+        if self.thread is not None:
+            self._stop = True
+            self.thread.join(timeout=2)
+            if self.samples:
+                out['sm_mhz'] = statistics.median(self.samples)
+                out['sm_max_mhz'] = max(self.max_clocks) if self.max_clocks else None
+                out['samples'] = len(self.samples)
+                out['source'] = 'nvml, every 10 ms during the timed region'
+            out['reasons'] = sorted(n for n, bit in self.REASON_BITS.items() if self.reason_mask & bit)
+            return out
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -121,6 +172,7 @@ class ClockSampler:
             out['sm_mhz'] = statistics.median(clocks)
             out['sm_max_mhz'] = max(max_clocks)
             out['samples'] = len(clocks)
+            out['source'] = 'nvidia-smi -lms 200'
         out['reasons'] = sorted(reasons)
         return out
 
@@ -312,7 +364,7 @@ def main():
     sampler = ClockSampler()
     barrier(world)
     if rank == 0:
-        sampler.start()
+        sampler.start(list(range(world)))
     l0 = launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier(world)
