@@ -144,9 +144,10 @@ bn_fwd_finalize(const float* __restrict__ part, const float* __restrict__ weight
   const float invstd = static_cast<float>(1.0 / sqrt(var + static_cast<double>(eps)));
   mean_out[c] = static_cast<float>(mean);
   invstd_out[c] = invstd;
-  const float scale = weight[c] * invstd;
+  // explicit roundings: the backward pass recomputes scale and shift bit for bit (ReLU mask from x)
+  const float scale = __fmul_rn(weight[c], invstd);
   coef[c] = scale;
-  coef[channels + c] = bias[c] - static_cast<float>(mean) * scale;
+  coef[channels + c] = __fmaf_rn(-static_cast<float>(mean), scale, bias[c]);
   if (running_mean != nullptr) {
     const double unbiased = rows > 1 ? var * static_cast<double>(rows) / static_cast<double>(rows - 1) : var;
     running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * static_cast<float>(mean);
@@ -190,11 +191,17 @@ bn_apply(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ 
   }
 }
 
-// g = RELU ? dy * (y > 0) : dy;   dx = g * k_dy[c] + x * k_x[c] + k_const[c];   dres = g (optional)
-template <bool RELU, bool DRES>
+// How the backward kernels find the ReLU mask: no activation, from the saved output y, or recomputed from x
+// (y > 0 exactly when x * scale[c] + shift[c] > 0; only without a residual).  Recomputing saves one read of an
+// activation-sized tensor in each of the two backward passes.
+enum : int { MASK_NONE = 0, MASK_FROM_Y = 1, MASK_FROM_X = 2 };
+
+// g = masked dy;   dx = g * k_dy[c] + x * k_x[c] + k_const[c];   dres = g (optional)
+template <int MASK, bool DRES>
 __global__ void __launch_bounds__(256)
 bn_dx(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
-      const __nv_bfloat16* __restrict__ y, const float* __restrict__ k_dy, const float* __restrict__ k_x,
+      const __nv_bfloat16* __restrict__ y, const float* __restrict__ scale, const float* __restrict__ shift,
+      const float* __restrict__ k_dy, const float* __restrict__ k_x,
       const float* __restrict__ k_const, __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dres,
       long long vecs, int vec_per_row) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -204,11 +211,18 @@ bn_dx(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
     float g[8], xv[8], a[8], b[8], out[8];
     unpack8(ld_stream(dy + i * 8), g);
     unpack8(ld_stream(x + i * 8), xv);
-    if (RELU) {
+    if (MASK == MASK_FROM_Y) {
       float yv[8];
       unpack8(ld_stream(y + i * 8), yv);
 #pragma unroll
       for (int k = 0; k < 8; ++k) g[k] = yv[k] > 0.f ? g[k] : 0.f;
+    }
+    if (MASK == MASK_FROM_X) {
+      float sc[8], sh[8];
+      load8(scale + c0, sc);
+      load8(shift + c0, sh);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] = fmaf(xv[k], sc[k], sh[k]) > 0.f ? g[k] : 0.f;
     }
     load8(k_dy + c0, a);
     load8(k_x + c0, b);
@@ -220,12 +234,12 @@ bn_dx(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
   }
 }
 
-template <bool RELU>
+template <int MASK>
 __global__ void __launch_bounds__(THREADS)
 bn_bwd_sums(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
             const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
-            const float* __restrict__ invstd, float* __restrict__ part, long long rows, int channels,
-            long long rows_per_split) {
+            const float* __restrict__ invstd, const float* __restrict__ weight, const float* __restrict__ bias,
+            float* __restrict__ part, long long rows, int channels, long long rows_per_split) {
   const int group = threadIdx.x % GROUPS;
   const int lane = threadIdx.x / GROUPS;
   const int c0 = (blockIdx.x * GROUPS + group) * 8;
@@ -235,13 +249,28 @@ bn_bwd_sums(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
 #pragma unroll
   for (int i = 0; i < 8; ++i) s_dy[i] = s_dyx[i] = 0.f;
   if (c0 < channels) {
-    float mu[8], is[8];
+    float mu[8], is[8], sc[8], sh[8];
     load8(mean + c0, mu);
     load8(invstd + c0, is);
+    if (MASK == MASK_FROM_X) {   // the forward pass's scale and shift, same roundings
+      load8(weight + c0, sc);
+      load8(bias + c0, sh);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        sc[i] = __fmul_rn(sc[i], is[i]);
+        sh[i] = __fmaf_rn(-mu[i], sc[i], sh[i]);
+      }
+    }
     const __nv_bfloat16* bx = x + c0;
     const __nv_bfloat16* bg = dy + c0;
     const __nv_bfloat16* by = y + c0;
-    constexpr int U = RELU ? 2 : 4;  // two or three tensors in flight per row
+    constexpr int U = MASK == MASK_FROM_Y ? 2 : 4;  // two or three tensors in flight per row
+    auto masked = [&](const float (&xv)[8], float (&gv)[8]) {
+      if (MASK == MASK_FROM_X) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) gv[i] = fmaf(xv[i], sc[i], sh[i]) > 0.f ? gv[i] : 0.f;
+      }
+    };
     long long r = r_begin + lane;
     for (; r + (U - 1) * LANES < r_end; r += U * LANES) {
       uint4 rx[U], rg[U], ry[U];
@@ -249,19 +278,20 @@ bn_bwd_sums(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
       for (int u = 0; u < U; ++u) {
         rx[u] = ld_stream(bx + (r + u * LANES) * channels);
         rg[u] = ld_stream(bg + (r + u * LANES) * channels);
-        if (RELU) ry[u] = ld_stream(by + (r + u * LANES) * channels);
+        if (MASK == MASK_FROM_Y) ry[u] = ld_stream(by + (r + u * LANES) * channels);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         float xv[8], gv[8];
         unpack8(rx[u], xv);
         unpack8(rg[u], gv);
-        if (RELU) {
+        if (MASK == MASK_FROM_Y) {
           float yv[8];
           unpack8(ry[u], yv);
 #pragma unroll
           for (int i = 0; i < 8; ++i) gv[i] = yv[i] > 0.f ? gv[i] : 0.f;
         }
+        masked(xv, gv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           s_dy[i] += gv[i];
@@ -273,12 +303,13 @@ bn_bwd_sums(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
       float xv[8], gv[8];
       unpack8(ld_stream(bx + r * channels), xv);
       unpack8(ld_stream(bg + r * channels), gv);
-      if (RELU) {
+      if (MASK == MASK_FROM_Y) {
         float yv[8];
         unpack8(ld_stream(by + r * channels), yv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) gv[i] = yv[i] > 0.f ? gv[i] : 0.f;
       }
+      masked(xv, gv);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         s_dy[i] += gv[i];
@@ -293,7 +324,7 @@ bn_bwd_sums(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
 //    = dy * k_dy + x * k_x + k_const  with
 //   k_dy = w*invstd, k_x = -k_dy * invstd * m2, k_const = -k_dy * (m1 - mean * invstd * m2)
 __global__ void __launch_bounds__(256)
-bn_bwd_finalize(const float* __restrict__ part, const float* __restrict__ weight,
+bn_bwd_finalize(const float* __restrict__ part, const float* __restrict__ weight, const float* __restrict__ bias,
                 const float* __restrict__ mean, const float* __restrict__ invstd,
                 float* __restrict__ dweight, float* __restrict__ dbias,
                 float* __restrict__ coef, int channels, int splits, long long rows) {
@@ -316,6 +347,11 @@ bn_bwd_finalize(const float* __restrict__ part, const float* __restrict__ weight
   coef[2 * channels + c] = static_cast<float>(k_dy);
   coef[3 * channels + c] = static_cast<float>(-k_dy * invstd[c] * m2);
   coef[4 * channels + c] = static_cast<float>(-k_dy * (m1 - static_cast<double>(mean[c]) * invstd[c] * m2));
+  if (bias != nullptr) {   // the forward pass's scale and shift (rows 0 and 1) for a ReLU mask recomputed from x
+    const float scale = __fmul_rn(weight[c], invstd[c]);
+    coef[c] = scale;
+    coef[channels + c] = __fmaf_rn(-mean[c], scale, bias[c]);
+  }
 }
 
 struct Shape {
@@ -423,21 +459,30 @@ std::vector<at::Tensor> bn_forward_train(at::Tensor x, at::Tensor weight, at::Te
   return {y, mean, invstd};
 }
 
-// Backward of y = act(batch_norm(x) (+ residual)).  `y` is needed when the activation is a ReLU.
+// Backward of y = act(batch_norm(x) (+ residual)).  The ReLU mask comes from `y`, or - when `bias_for_mask` is given
+// instead (ReLU without a residual) - is recomputed from x, which saves a read of y in both passes.
 // Returns (dx, dweight, dbias) and, with `want_dres`, the gradient of the residual (dy masked by
 // the activation; without an activation it is dy itself and is not returned).
 std::vector<at::Tensor> bn_backward_train(at::Tensor x, at::Tensor dy, at::Tensor weight, at::Tensor mean,
-                                          at::Tensor invstd, c10::optional<at::Tensor> y, bool want_dres) {
+                                          at::Tensor invstd, c10::optional<at::Tensor> y, bool want_dres,
+                                          c10::optional<at::Tensor> bias_for_mask) {
   const Shape s = plan(x);
   check_like(dy, x, "dy");
   check_vec(weight, s.channels, "weight");
   check_vec(mean, s.channels, "mean");
   check_vec(invstd, s.channels, "invstd");
-  const bool relu = y.has_value();
+  const bool from_x = bias_for_mask.has_value();
+  TORCH_CHECK(!(from_x && (y.has_value() || want_dres)), "the mask is recomputed from x only without y and without a residual");
+  const bool relu = y.has_value() || from_x;
   const __nv_bfloat16* yp = nullptr;
-  if (relu) {
+  if (y.has_value()) {
     check_like(*y, x, "y");
     yp = reinterpret_cast<const __nv_bfloat16*>(y->data_ptr());
+  }
+  const float* bp = nullptr;
+  if (from_x) {
+    check_vec(*bias_for_mask, s.channels, "bias");
+    bp = bias_for_mask->data_ptr<float>();
   }
   const bool dres_out = want_dres && relu;
   const int dev = x.get_device();
@@ -455,25 +500,32 @@ std::vector<at::Tensor> bn_backward_train(at::Tensor x, at::Tensor dy, at::Tenso
   auto* dxp = reinterpret_cast<__nv_bfloat16*>(dx.data_ptr());
   auto* drp = dres_out ? reinterpret_cast<__nv_bfloat16*>(dres.data_ptr()) : nullptr;
   const dim3 sgrid(s.chunks, s.splits);
-  if (relu)
-    bn_bwd_sums<true><<<sgrid, THREADS, 0, stream>>>(xp, gp, yp, mean.data_ptr<float>(), invstd.data_ptr<float>(),
-                                                     part.data_ptr<float>(), s.rows, s.channels, s.rows_per_split);
+  const float *wp = weight.data_ptr<float>(), *mp = mean.data_ptr<float>(), *ip = invstd.data_ptr<float>();
+  if (from_x)
+    bn_bwd_sums<MASK_FROM_X><<<sgrid, THREADS, 0, stream>>>(xp, gp, xp, mp, ip, wp, bp, part.data_ptr<float>(), s.rows,
+                                                            s.channels, s.rows_per_split);
+  else if (relu)
+    bn_bwd_sums<MASK_FROM_Y><<<sgrid, THREADS, 0, stream>>>(xp, gp, yp, mp, ip, wp, nullptr, part.data_ptr<float>(), s.rows,
+                                                            s.channels, s.rows_per_split);
   else
-    bn_bwd_sums<false><<<sgrid, THREADS, 0, stream>>>(xp, gp, xp, mean.data_ptr<float>(), invstd.data_ptr<float>(),
-                                                      part.data_ptr<float>(), s.rows, s.channels, s.rows_per_split);
+    bn_bwd_sums<MASK_NONE><<<sgrid, THREADS, 0, stream>>>(xp, gp, xp, mp, ip, wp, nullptr, part.data_ptr<float>(), s.rows,
+                                                          s.channels, s.rows_per_split);
   bn_bwd_finalize<<<(s.channels + 7) / 8, 256, 0, stream>>>(
-      part.data_ptr<float>(), weight.data_ptr<float>(), mean.data_ptr<float>(), invstd.data_ptr<float>(),
-      dweight.data_ptr<float>(), dbias.data_ptr<float>(), coef.data_ptr<float>(), s.channels, s.splits, s.rows);
+      part.data_ptr<float>(), wp, bp, mp, ip, dweight.data_ptr<float>(), dbias.data_ptr<float>(), coef.data_ptr<float>(),
+      s.channels, s.splits, s.rows);
   const long long vecs = s.rows * (s.channels / 8);
   const int grid = affine_grid(vecs), vpr = s.channels / 8;
   const float* k = coef.data_ptr<float>();
+  const float *sc = k, *sh = k + s.channels;
   const float *k_dy = k + 2 * s.channels, *k_x = k + 3 * s.channels, *k_c = k + 4 * s.channels;
-  if (relu && dres_out)
-    bn_dx<true, true><<<grid, 256, 0, stream>>>(gp, xp, yp, k_dy, k_x, k_c, dxp, drp, vecs, vpr);
+  if (from_x)
+    bn_dx<MASK_FROM_X, false><<<grid, 256, 0, stream>>>(gp, xp, nullptr, sc, sh, k_dy, k_x, k_c, dxp, nullptr, vecs, vpr);
+  else if (relu && dres_out)
+    bn_dx<MASK_FROM_Y, true><<<grid, 256, 0, stream>>>(gp, xp, yp, sc, sh, k_dy, k_x, k_c, dxp, drp, vecs, vpr);
   else if (relu)
-    bn_dx<true, false><<<grid, 256, 0, stream>>>(gp, xp, yp, k_dy, k_x, k_c, dxp, nullptr, vecs, vpr);
+    bn_dx<MASK_FROM_Y, false><<<grid, 256, 0, stream>>>(gp, xp, yp, sc, sh, k_dy, k_x, k_c, dxp, nullptr, vecs, vpr);
   else
-    bn_dx<false, false><<<grid, 256, 0, stream>>>(gp, xp, nullptr, k_dy, k_x, k_c, dxp, nullptr, vecs, vpr);
+    bn_dx<MASK_NONE, false><<<grid, 256, 0, stream>>>(gp, xp, nullptr, sc, sh, k_dy, k_x, k_c, dxp, nullptr, vecs, vpr);
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch(3);
   if (dres_out) return {dx, dweight, dbias, dres};

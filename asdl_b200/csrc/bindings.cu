@@ -40,7 +40,8 @@ std::vector<at::Tensor> bn_forward_train(at::Tensor x, at::Tensor weight, at::Te
                                          c10::optional<at::Tensor> num_batches_tracked, double momentum,
                                          double eps, c10::optional<at::Tensor> residual, bool relu);
 std::vector<at::Tensor> bn_backward_train(at::Tensor x, at::Tensor dy, at::Tensor weight, at::Tensor mean,
-                                          at::Tensor invstd, c10::optional<at::Tensor> y, bool want_dres);
+                                          at::Tensor invstd, c10::optional<at::Tensor> y, bool want_dres,
+                                          c10::optional<at::Tensor> bias_for_mask);
 void bn_unitwise_stats_xhat(at::Tensor x, at::Tensor dy, c10::optional<at::Tensor> y, at::Tensor mean,
                             at::Tensor invstd, at::Tensor stats, double alpha, double beta);
 bool ln_supported_size(int64_t d);

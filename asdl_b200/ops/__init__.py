@@ -499,6 +499,10 @@ def batchnorm_unitwise_stats(y: torch.Tensor, g: torch.Tensor, weight: torch.Ten
     return out.mul_(beta).add_(new, alpha=alpha)
 
 
+#: ReLU mask of the fused BatchNorm backward: recomputed from x (True) or read from the saved output (False)
+BN_RELU_MASK_FROM_X = os.environ.get('ASDL_B200_BN_MASK_FROM_X', '1') != '0'
+
+
 class _BatchNormTrain(torch.autograd.Function):
     """Training-mode batch normalisation (+ residual add, + ReLU) on the library's NHWC bf16 kernels."""
 
@@ -509,7 +513,10 @@ class _BatchNormTrain(torch.autograd.Function):
                                                        running_var, num_batches_tracked, float(momentum),
                                                        float(eps), residual, bool(relu))
         ctx.relu, ctx.has_residual = bool(relu), residual is not None
-        ctx.save_for_backward(x, weight, mean, invstd, *([y] if relu else []))
+        # ReLU without a residual: y > 0 exactly when x * scale + shift > 0, so the backward kernels recompute the
+        # mask from x (which they read anyway) and the bias, instead of reading y once more in each pass
+        ctx.mask_from_x = ctx.relu and not ctx.has_residual and BN_RELU_MASK_FROM_X
+        ctx.save_for_backward(x, weight, mean, invstd, *([bias] if ctx.mask_from_x else ([y] if relu else [])))
         ctx.mark_non_differentiable(mean, invstd)
         return y, mean, invstd
 
@@ -518,8 +525,9 @@ class _BatchNormTrain(torch.autograd.Function):
         x, weight, mean, invstd, *rest = ctx.saved_tensors
         if not dy.is_contiguous(memory_format=torch.channels_last):
             dy = dy.contiguous(memory_format=torch.channels_last)
-        y = rest[0] if ctx.relu else None
-        out = extension().bn_backward_train(x, dy, weight.detach(), mean, invstd, y, ctx.has_residual)
+        y = rest[0] if (ctx.relu and not ctx.mask_from_x) else None
+        bias = rest[0].detach() if ctx.mask_from_x else None
+        out = extension().bn_backward_train(x, dy, weight.detach(), mean, invstd, y, ctx.has_residual, bias)
         dx, dweight, dbias = out[:3]
         dres = None
         if ctx.has_residual:
