@@ -74,7 +74,10 @@ def _train(model, x, t, data_size, multimem=True, **kw):
     os.environ['ASDL_B200_MULTIMEM'] = '1' if multimem else '0'   # read when the symmetric buffer is set up
     cfg = asdl.PreconditioningConfig(data_size=data_size, damping=1e-2, ema_decay=0.4,
                                      curvature_upd_interval=3, preconditioner_upd_interval=3)
+    push = kw.pop('push', False)
     gm = asdl.FusedKfacGradientMaker(model, cfg, fisher_type=asdl.FISHER_EMP, **kw)
+    if push:   # statistics and preconditioned gradients sent from the GEMM epilogues instead of pulled / broadcast
+        gm.pull_statistics, gm.replicate_in_epilogue = False, True
     opt = torch.optim.SGD(model.parameters(), lr=0.01)
     out = []
     for _ in range(STEPS):
@@ -139,7 +142,9 @@ TRANSPORTS = (('torch', dict(comm='torch')),
               ('symmetric_overlap', dict(comm='symmetric', bucket_mb=0.01)),      # several buckets on a tiny model
               ('symmetric_overlap_peer_loads', dict(comm='symmetric', bucket_mb=0.01, multimem=False)),
               ('symmetric_graph', dict(comm='symmetric', cuda_graph=True, overlap_grad_reduce=False)),
-              ('symmetric_graph_overlap', dict(comm='symmetric', cuda_graph=True, bucket_mb=0.01)))
+              ('symmetric_graph_overlap', dict(comm='symmetric', cuda_graph=True, bucket_mb=0.01)),
+              ('symmetric_push', dict(comm='symmetric', overlap_grad_reduce=False, push=True)),
+              ('symmetric_graph_push', dict(comm='symmetric', cuda_graph=True, overlap_grad_reduce=False, push=True)))
 
 
 def _worker(rank, world, port, out_dir):
