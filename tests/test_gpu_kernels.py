@@ -518,6 +518,19 @@ def test_gemm_epilogue_reduces_into_and_replicates_to_other_buffers(ext):
     owner.reduce_slots(torch.tensor([[f_off, s_off, 200]], dtype=torch.int64, device=DEV), 200 * 200, 200, 0.25)
     want = 0.25 * (held + held.T) + 0.5 * (ref + x2.float().T @ x2.float())
     assert rel_err(factor, want) < 1e-4 and torch.equal(factor, factor.T)
+    # pull transport: every rank stores its share into ITS OWN buffer (same offset everywhere) and the owner
+    # reads all ranks' copies while it sums (five emulated ranks: the kernel loads from four ranks at a time, so
+    # both the full group and the remainder are exercised)
+    group = SymmetricArena.local_group(2 * 200 * 200 + 256, 5)
+    offs = [(g.alloc(200, 200), g.alloc(200, 200)) for g in group]
+    (pf_off, pfactor), (share_off, _) = offs[0]
+    pfactor.copy_(held + held.T)
+    datas = [torch.randn(300 + 8 * r, 200, device=DEV).to(torch.bfloat16) for r in range(5)]
+    for r, (g, data) in enumerate(zip(group, datas)):
+        ext.umma_gemm_to_ptr([data], [data], False, False, g.ptr(r, share_off), 200, 0.5, True, 3, [], 0)
+    group[0].pull_slots(torch.tensor([[pf_off, share_off, 200]], dtype=torch.int64, device=DEV), 200, 0.25)
+    want = 0.25 * (held + held.T) + 0.5 * sum(d.float().T @ d.float() for d in datas)
+    assert rel_err(pfactor, want) < 1e-4 and torch.equal(pfactor, pfactor.T)
     a = torch.randn(96, 160, device=DEV).to(torch.bfloat16)   # [K, M]
     b = torch.randn(96, 72, device=DEV).to(torch.bfloat16)    # [K, N]
     outs = [torch.zeros(160, 72, device=DEV) for _ in range(4)]
