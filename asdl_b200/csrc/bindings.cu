@@ -29,7 +29,7 @@ void gemm_plan_add(int64_t id, std::vector<at::Tensor> a_segs, std::vector<at::T
                    int64_t nsplit, c10::optional<at::Tensor> out_mid, bool split3, bool x3wide, bool mcast);
 void gemm_plan_finalize(int64_t id);
 void gemm_plan_run(int64_t id);
-void cast_pad_bf16_grouped(at::Tensor table, int64_t count);
+void cast_pad_bf16_grouped(at::Tensor table, int64_t count, int64_t max_elems);
 void cast_split3(at::Tensor src, at::Tensor hi, at::Tensor mid, at::Tensor lo);
 void transpose_cast(at::Tensor src, at::Tensor dst);
 void bn_unitwise_stats(at::Tensor y, at::Tensor g, at::Tensor weight, at::Tensor bias, at::Tensor stats,
@@ -104,7 +104,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("extra_ptrs"), py::arg("nsplit"), py::arg("out_mid") = py::none(), py::arg("split3") = false, py::arg("x3wide") = false, py::arg("mcast") = false);
   m.def("gemm_plan_finalize", &b200::gemm_plan_finalize);
   m.def("gemm_plan_run", &b200::gemm_plan_run);
-  m.def("cast_pad_bf16_grouped", &b200::cast_pad_bf16_grouped);
+  m.def("cast_pad_bf16_grouped", &b200::cast_pad_bf16_grouped, py::arg("table"), py::arg("count"), py::arg("max_elems") = 0);
   m.def("cast_split3", &b200::cast_split3);
   m.def("transpose_cast", &b200::transpose_cast);
   m.def("bn_unitwise_stats", &b200::bn_unitwise_stats);

@@ -116,16 +116,49 @@ void cast_split3(at::Tensor src, at::Tensor hi, at::Tensor mid, at::Tensor lo) {
 }
 
 // Grouped fp32 -> bf16 hi/lo staging: one launch converts many matrices.  Each table row holds
-// (src fp32 ptr, hi ptr, lo ptr or 0, rows, n, src pitch, dst pitch) as int64.
-__global__ void cast_pad_grouped_kernel(const long long* __restrict__ table) {
+// (src fp32 ptr, hi ptr, lo ptr or 0, rows, n, src pitch, dst pitch) as int64.  blockIdx.y is the matrix;
+// the grid is as wide as the largest matrix needs, so the CTAs of a small matrix past its end leave at once.
+// Matrices whose rows are 16-byte aligned on both sides go eight elements per thread and trip (two 16-byte loads,
+// one 16-byte store per part); the others one element at a time.
+__global__ void __launch_bounds__(256) cast_pad_grouped_kernel(const long long* __restrict__ table) {
   const long long* e = table + static_cast<long long>(blockIdx.y) * 7;
   const float* src = reinterpret_cast<const float*>(e[0]);
   __nv_bfloat16* hi = reinterpret_cast<__nv_bfloat16*>(e[1]);
   __nv_bfloat16* lo = reinterpret_cast<__nv_bfloat16*>(e[2]);
   const long long rows = e[3], n = e[4], lds = e[5], ldo = e[6];
+  const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long first = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const bool vec = ((n & 7) == 0) && ((ldo & 7) == 0) && ((lds & 3) == 0) &&
+                   (((e[0] | e[1] | e[2]) & 15) == 0);
+  if (vec) {
+    const long long vpr = ldo >> 3, total = rows * vpr;
+    for (long long v = first; v < total; v += step) {
+      const long long r = v / vpr, c = (v - r * vpr) << 3;
+      float x[8];
+      if (c < n) {
+        const float4 a = *reinterpret_cast<const float4*>(src + r * lds + c);
+        const float4 b = *reinterpret_cast<const float4*>(src + r * lds + c + 4);
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) x[k] = 0.f;
+      }
+      uint32_t ph[4], pl[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const __nv_bfloat16 h0 = __float2bfloat16_rn(x[2 * k]), h1 = __float2bfloat16_rn(x[2 * k + 1]);
+        const __nv_bfloat16 l0 = __float2bfloat16_rn(x[2 * k] - __bfloat162float(h0));
+        const __nv_bfloat16 l1 = __float2bfloat16_rn(x[2 * k + 1] - __bfloat162float(h1));
+        ph[k] = static_cast<uint32_t>(__bfloat16_as_ushort(h0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(h1)) << 16);
+        pl[k] = static_cast<uint32_t>(__bfloat16_as_ushort(l0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(l1)) << 16);
+      }
+      *reinterpret_cast<uint4*>(hi + (v << 3)) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+      if (lo != nullptr) *reinterpret_cast<uint4*>(lo + (v << 3)) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+    }
+    return;
+  }
   const long long total = rows * ldo;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+  for (long long i = first; i < total; i += step) {
     const long long r = i / ldo;
     const long long c = i - r * ldo;
     const float v = (c < n) ? src[r * lds + c] : 0.f;
@@ -135,13 +168,17 @@ __global__ void cast_pad_grouped_kernel(const long long* __restrict__ table) {
   }
 }
 
-void cast_pad_bf16_grouped(at::Tensor table, int64_t count) {
+// `max_elems`: rows x destination pitch of the largest matrix of the table (0: unknown, a narrow grid is used).
+void cast_pad_bf16_grouped(at::Tensor table, int64_t count, int64_t max_elems) {
   TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.is_contiguous() &&
                   table.numel() == count * 7, "table must be a CUDA int64 [count, 7] tensor");
   if (count == 0) return;
   c10::cuda::CUDAGuard guard(table.get_device());
   auto stream = at::cuda::getCurrentCUDAStream().stream();
-  cast_pad_grouped_kernel<<<dim3(32, static_cast<unsigned>(count)), 256, 0, stream>>>(
+  // eight elements per thread and at least two trips per thread for the largest matrix, at most 512 CTAs per matrix
+  int gx = 32;
+  if (max_elems > 0) gx = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>((max_elems / 8 + 511) / 512, 512)));
+  cast_pad_grouped_kernel<<<dim3(gx, static_cast<unsigned>(count)), 256, 0, stream>>>(
       reinterpret_cast<const long long*>(table.data_ptr<int64_t>()));
   B200_CUDA_CHECK(cudaGetLastError());
   count_launch();

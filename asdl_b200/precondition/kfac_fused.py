@@ -1153,7 +1153,8 @@ class FusedKfacGradientMaker(KfacGradientMaker):
         ext.gemm_plan_finalize(plan1)
         ext.gemm_plan_finalize(plan2)
         table = torch.tensor(rows, dtype=torch.int64, device=dev)
-        return dict(key=tuple(id(st) for st in todo), views=views, table=table, plans=(plan1, plan2),
+        max_elems = max(r[3] * r[6] for r in rows)
+        return dict(key=tuple(id(st) for st in todo), views=views, table=table, plans=(plan1, plan2), max_elems=max_elems,
                     keep=keep, flat=None if arena is not None else flat)
 
     def _precondition_kron_grouped(self, todo, grad_scale):
@@ -1167,7 +1168,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             torch._foreach_copy_([v for v, _ in moved], [g for _, g in moved])
         if grad_scale != 1:
             torch._foreach_mul_(group['views'], grad_scale)
-        ext.cast_pad_bf16_grouped(group['table'], len(todo))
+        ext.cast_pad_bf16_grouped(group['table'], len(todo), group['max_elems'])
         ext.gemm_plan_run(group['plans'][0])
         ext.gemm_plan_run(group['plans'][1])
         if moved:

@@ -381,8 +381,9 @@ class _MatrixBlockGroup:
                 src = ptrs[pi] + 4 * (rs.start * ncols + cs.start)
                 rows.append([src, g_hi.data_ptr(), g_lo.data_ptr(), m, n, ncols, ld_n])
             self._grad_table = torch.tensor(rows, dtype=torch.int64, device=self.device)
+            self._grad_max_elems = max(r[3] * r[6] for r in rows)
             self._grad_ptrs = ptrs
-        self.ext.cast_pad_bf16_grouped(self._grad_table, len(self.blocks))
+        self.ext.cast_pad_bf16_grouped(self._grad_table, len(self.blocks), self._grad_max_elems)
 
     def update_statistics(self):
         ids = tuple(id(t) for prec in self.precs for t in prec.statistics)
@@ -402,7 +403,7 @@ class _MatrixBlockGroup:
         rows = [[prec.preconditioners[i].data_ptr(), hi.data_ptr(), lo.data_ptr(), n, n, n, ld]
                 for prec, i, hi, lo, n, ld in self.root_slots]
         table = torch.tensor(rows, dtype=torch.int64, device=self.device)
-        self.ext.cast_pad_bf16_grouped(table, len(rows))
+        self.ext.cast_pad_bf16_grouped(table, len(rows), max(r[3] * r[6] for r in rows))
         self._roots_ready = True
 
     _roots_ready = False
