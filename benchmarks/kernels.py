@@ -258,6 +258,17 @@ def bench_symm(timer, world, mb, hbm, src):
          frac_of_peak_hbm=round(4.0 * numel * (world + 1) / (ms_r * 1e-3) / hbm, 3), peak_source=src)
     emit(case='symm_bcast_segments_emulated', world=world, mbytes=mb, ms=round(ms_b, 4),
          frac_of_peak_hbm=round(4.0 * numel * world / (ms_b * 1e-3) / hbm, 3), peak_source=src)
+    # owner-side pull of a factor's statistics: every emulated rank holds its share (lower triangle) at the same offset
+    n = 4096
+    group = SymmetricArena.local_group(2 * n * n + 1024, world)
+    offs = [(g.alloc(n, n), g.alloc(n, n)) for g in group]
+    for g in group:
+        g.buffer.normal_()
+    table = torch.tensor([[offs[0][0][0], offs[0][1][0], n]], dtype=torch.int64, device='cuda')
+    ms_p = timer(lambda: group[0].pull_slots(table, n, 0.95))
+    by = 4.0 * n * n * (0.5 * world + 0.5 + 1.0)   # lower triangles of all ranks and of the factor read, full factor written
+    emit(case='symm_pull_slots_emulated', world=world, n=n, ms=round(ms_p, 4),
+         frac_of_peak_hbm=round(by / (ms_p * 1e-3) / hbm, 3), peak_source=src)
 
 
 def bench_im2col(timer, n, c, hw, k, stride, pad, hbm, flops_peak, src):
