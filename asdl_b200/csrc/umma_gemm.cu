@@ -437,6 +437,102 @@ void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, b
   }
 }
 
+// Implicit-im2col SYRK: C = alpha * M^T M (+ beta * C) with M the patch matrix [n * oh * ow, kh * kw * c] of a
+// stride-1, dilation-1 convolution input, columns ordered (kh, kw, c) - the input-side Kronecker factor of a
+// convolution (asdl/operations/conv.py:80-88 builds M with unfold) without materialising M.
+//   x: bf16 [n, c, h, w] in channels_last memory format (NHWC in memory), c a multiple of 64, kh * kw <= 12.
+// The producer warp gathers every operand tile with 4-D TMA boxes of x (see G2F_CONV in umma_gemm2.cuh); the
+// zero padding of the convolution and the output pixels past the image are TMA's out-of-bounds fill.
+void umma_syrk_conv(at::Tensor x, at::Tensor C, int64_t kh, int64_t kw, int64_t ph, int64_t pw, double alpha,
+                    double beta, int64_t nsplit_req) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 4 &&
+                  x.is_contiguous(at::MemoryFormat::ChannelsLast),
+              "x must be a 4-d channels_last bf16 CUDA tensor");
+  const int64_t n = x.size(0), c = x.size(1), h = x.size(2), w = x.size(3);
+  TORCH_CHECK(c % 64 == 0 && kh >= 1 && kw >= 1 && kh * kw <= 2 * G2_MAX_SEG && ph >= 0 && pw >= 0 && ph < kh && pw < kw,
+              "implicit im2col needs a channel count that is a multiple of 64, at most 12 filter taps and padding below the filter size");
+  const int64_t oh = h + 2 * ph - kh + 1, ow = w + 2 * pw - kw + 1;
+  TORCH_CHECK(oh > ph && ow > pw && n >= 1, "the output must be larger than the padding");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "x must be 16-byte aligned");
+  const int64_t ncol = kh * kw * c;
+  TORCH_CHECK(C.is_cuda() && C.scalar_type() == at::kFloat && C.dim() == 2 && C.stride(1) == 1 && C.size(0) == ncol &&
+                  C.size(1) == ncol,
+              "C must be a [kh kw c, kh kw c] fp32 CUDA matrix with unit column stride");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(C.data_ptr()) & 15) == 0 || (C.stride(0) & 3) != 0,
+              "C must be 16-byte aligned when its row pitch is a multiple of four elements");
+  const int dev = x.get_device();
+  c10::cuda::CUDAGuard guard(dev);
+  GemmProblem2 P;
+  std::memset(&P, 0, sizeof(P));
+  // pixel block of a K step: bw x bh output pixels of bi images, bw * bh * bi = 64, least overhang (ties: widest rows)
+  int bw = 8, bh = 8, bi = 1;
+  {
+    long long best = -1;
+    for (int a = 6; a >= 0; --a)
+      for (int b = 6 - a; b >= 0; --b) {
+        const int cw = 1 << a, ch = 1 << b, ci = 1 << (6 - a - b);
+        const long long vol = ((ow + cw - 1) / cw) * cw * ((oh + ch - 1) / ch) * ch * ((n + ci - 1) / ci) * ci;
+        if (best < 0 || vol < best) {
+          best = vol;
+          bw = cw;
+          bh = ch;
+          bi = ci;
+        }
+      }
+  }
+  const int th = static_cast<int>((oh + bh - 1) / bh), tw = static_cast<int>((ow + bw - 1) / bw);
+  const int ti = static_cast<int>((n + bi - 1) / bi);
+  TORCH_CHECK(static_cast<long long>(ti) * th * tw < (1ll << 24), "too many pixel blocks");
+  for (int q = 0; q < kh * kw; ++q) {
+    const int64_t khh = q / kw, kww = q % kw;
+    // extents of tap q: the last valid output pixel (oh - 1, ow - 1) reads input (oh - 1 + khh - ph, ow - 1 + kww - pw)
+    const cuuint64_t wq = static_cast<cuuint64_t>(std::min<int64_t>(w, ow + kww - pw));
+    const cuuint64_t hq = static_cast<cuuint64_t>(std::min<int64_t>(h, oh + khh - ph));
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(c), wq, hq, static_cast<cuuint64_t>(n)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(c) * 2, static_cast<cuuint64_t>(w * c) * 2,
+                             static_cast<cuuint64_t>(h * w * c) * 2};
+    cuuint32_t box[4] = {64, static_cast<cuuint32_t>(bw), static_cast<cuuint32_t>(bh), static_cast<cuuint32_t>(bi)};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUtensorMap* tm = q < G2_MAX_SEG ? &P.tmA[q] : &P.tmB[q - G2_MAX_SEG];
+    CUresult r = get_encode_tiled()(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x.data_ptr(), dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (4-d) failed with code ", static_cast<int>(r));
+  }
+  P.M = P.N = static_cast<int>(ncol);
+  P.K = ti * th * tw * G2_BK;   // 64 output pixels per K block
+  P.nseg = 1;
+  P.alpha = static_cast<float>(alpha);
+  P.beta = static_cast<float>(beta);
+  P.flags = G2F_SYM | G2F_SAME_AB | G2F_CONV;
+  P.C = C.data_ptr<float>();
+  P.Cin = P.C;
+  P.ldc = static_cast<int>(C.stride(0));
+  P.conv_c = static_cast<int>(c);
+  P.conv_kw = static_cast<int>(kw);
+  P.conv_taps = static_cast<int>(kh * kw);
+  P.conv_ph = static_cast<int>(ph);
+  P.conv_pw = static_cast<int>(pw);
+  P.conv_th = th;
+  P.conv_tw = tw;
+  P.conv_box = bw | (bh << 8) | (bi << 16);
+  P.tiles_m = (P.M + G2_BM - 1) / G2_BM;
+  P.tiles_n = (P.N + 127) / 128;
+  P.ntiles = tile_count(P.tiles_m, P.tiles_n, true, 128);
+  const int kb_total = P.K / G2_BK;
+  int nsplit = static_cast<int>(nsplit_req);
+  if (nsplit <= 0) {
+    nsplit = (2 * g2_sm_count(dev)) / std::max(P.ntiles, 1);
+    nsplit = std::min(std::min(nsplit, kb_total / 8), 32);
+  }
+  P.nsplit = std::max(1, std::min(nsplit, kb_total));
+  auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  if (!batch_append(P, dev, nsplit_req, stream, {x}, {}, C)) {
+    gemm_attach_scratch(P, dev, stream);
+    gemm_launch_single(P, dev, stream);
+  }
+}
+
 // Variant whose fp32 result goes to raw device addresses - typically symmetric-memory buffers of
 // this or another GPU.  `dst_ptr` receives the result (accumulated with reductions when `atomic`),
 // `extra_ptrs` receive plain copies of it (non-atomic mode only).  All destinations use `ldc`.

@@ -74,7 +74,19 @@ enum : int {
   G2F_SPLIT2 = 256,   // tmA[0..1] / tmB[0..1] are the (hi, lo) parts of the operands ("bf16x3", wide tiles)
   G2F_MCAST = 512,    // C_extra[] are NVLS multicast addresses: one multimem.st reaches every GPU of the group
   G2F_PAIR = 1024,    // CTA-pair flavour (umma_gemm2_pair.cuh): 128-row tensor maps, tile grid of BN = 256
+  G2F_CONV = 2048,    // implicit im2col SYRK: both operands are patch matrices gathered by 4-D TMA loads (below)
 };
+
+// Implicit im2col (G2F_CONV): the operand is the patch matrix of a stride-1 convolution input x [N, H, W, C] (bf16,
+// channels innermost, C a multiple of 64), columns ordered (kh, kw, c), rows = output pixels.  It never exists in
+// memory: a K block is a bw x bh rectangle of output pixels of bi consecutive images (bw * bh * bi = 64, chosen per
+// layer so that the blocks cover the output with the least overhang: 8 x 8 x 1 for a 56 x 56 output, 2 x 2 x 16 for
+// 14 x 14), a 64-column chunk is 64 channels of one filter tap, and the [64 pixels] x [64 channels] tile of a chunk is
+// one 4-D TMA box {64, bw, bh, bi} of x, shifted by the tap offset minus the padding.  Tap q has its own tensor map (slots tmA[0..5], tmB[0..5]) whose W and H extents end
+// where the tap's last valid output pixel reads: coordinates before the image are the padding and coordinates past
+// the extents belong to output pixels that do not exist - TMA fills both with zeros.  The shared-memory image of a
+// box is exactly the MN-major tile of the explicit patch matrix, so the MMA side does not change.
+
 
 enum : int {
   G2W_NO_SPLIT_OUT = 1,  // work item: do not write the bf16 outputs of the problem for this tile
@@ -99,6 +111,11 @@ struct alignas(64) GemmProblem2 {
   int flags;
   int reserved;
   float alpha, beta;
+  // G2F_CONV geometry
+  int conv_c, conv_kw, conv_taps;   // channels, filter width, kh * kw
+  int conv_ph, conv_pw;             // padding
+  int conv_th, conv_tw;             // pixel blocks per image column / row
+  int conv_box;                     // bw | bh << 8 | bi << 16
 };
 
 struct GemmWork2 {
@@ -501,6 +518,32 @@ umma_gemm2_kernel(const __grid_constant__ GemmProblem2 single, const GemmProblem
             uint8_t* stage = smem + s * Cfg::STAGE_BYTES;
             mbar_expect_tx(&full_bar[s], bytes);
             const int ka = w.a_k0 + kb * G2_BK, kbb = w.b_k0 + kb * G2_BK;
+            if constexpr (PARTS == 1 && BN == 128) {
+              if (P.flags & G2F_CONV) {
+                // K block -> (group of images, block of output pixels); 64-column chunk -> (filter tap, channel offset)
+                const int pb = ka >> 6, per_img = P.conv_th * P.conv_tw;
+                const int bw = P.conv_box & 0xff, bh = (P.conv_box >> 8) & 0xff, bi = P.conv_box >> 16;
+                const int ib = pb / per_img, rem = pb - ib * per_img;
+                const int img = ib * bi, oy0 = (rem / P.conv_tw) * bh, ox0 = (rem % P.conv_tw) * bw;
+                auto gather = [&](uint8_t* dst, int col) {
+                  const int q = col / P.conv_c, c0 = col - q * P.conv_c;
+                  if (q < P.conv_taps) {
+                    const CUtensorMap* tm = q < G2_MAX_SEG ? &P.tmA[q] : &P.tmB[q - G2_MAX_SEG];
+                    const int khh = q / P.conv_kw, kww = q - khh * P.conv_kw;
+                    tma_load_4d(dst, tm, &full_bar[s], c0, ox0 + kww - P.conv_pw, oy0 + khh - P.conv_ph, img);
+                  } else {   // columns past the matrix: a box that lies outside the tensor reads zeros
+                    tma_load_4d(dst, &P.tmA[0], &full_bar[s], 0, 0, 1 << 20, img);
+                  }
+                };
+                gather(stage, w.a_mn);
+                gather(stage + G2_BK * 128, w.a_mn + 64);
+                if (!shared_ab) {
+                  gather(stage + G2_A_BYTES, w.b_mn);
+                  gather(stage + G2_A_BYTES + G2_BK * 128, w.b_mn + 64);
+                }
+                continue;
+              }
+            }
             constexpr int NPART = PARTS;
 #pragma unroll
             for (int part = 0; part < NPART; ++part) {

@@ -347,6 +347,11 @@ def kron_apply(left: torch.Tensor, mid: torch.Tensor, right: torch.Tensor) -> to
     return out.to(mid.dtype) if mid.dtype != torch.float32 else out
 
 
+#: stride-1 convolutions on channels_last bf16 inputs with a multiple of 64 channels: gather the patch tiles
+#: inside the SYRK (4-D TMA boxes) instead of writing the patch matrix to memory first
+IMPLICIT_IM2COL = os.environ.get('ASDL_B200_IMPLICIT_IM2COL', '1') != '0'
+
+
 def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
                     out: Optional[torch.Tensor] = None, beta: float = 0.0,
                     channels_last_order: bool = False) -> torch.Tensor:
@@ -355,8 +360,10 @@ def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
 
     ``channels_last_order=False`` orders rows/columns as (c, kh, kw) (matching
     ``weight.view(c_out, -1)``); ``True`` uses (kh, kw, c), the order of a channels_last weight.
-    CUDA: a bf16 im2col kernel (vectorised for channels_last inputs) feeds the tcgen05 SYRK; 1x1
-    stride-1 convolutions on channels_last activations need no staging at all.  fp32 inputs are
+    CUDA: stride-1 convolutions on channels_last bf16 inputs with a multiple of 64 channels never form the
+    patch matrix - the SYRK's producer gathers 8 x 8 pixel blocks of one filter tap with 4-D TMA boxes, padding
+    and image edges being TMA's zero fill (``IMPLICIT_IM2COL``); 1x1 stride-1 convolutions read the activations
+    in place; everything else goes through a bf16 im2col kernel (vectorised for channels_last inputs).  fp32 inputs are
     staged as bf16 hi/lo patch pairs and multiplied in three passes (precision policy 'auto')."""
     from ..utils import im2col_2d, _conv_geometry, _explicit_padding
     (kh, kw), (sh, sw), _, (dh, dw) = _conv_geometry(conv)
@@ -377,6 +384,16 @@ def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
             and c % 8 == 0 and not _use_x3(x.dtype)):
         rows = x.permute(0, 2, 3, 1).reshape(n * h * w, c)  # a view: NHWC memory is already [rows, c]
         return gram(rows, scale=scale, out=out, beta=beta)
+    if (IMPLICIT_IM2COL and channels_last_order and x.dtype == torch.bfloat16 and not _use_x3(x.dtype)
+            and sh == sw == dh == dw == 1 and c % 64 == 0 and kh * kw <= 12 and ph < kh and pw < kw
+            and ho > ph and wo > pw and x.is_contiguous(memory_format=torch.channels_last)
+            and (out is None or (out.dtype == torch.float32 and out.stride(1) == 1))):
+        # no patch matrix: the SYRK's producer gathers its operand tiles from x with 4-D TMA boxes
+        if out is None:
+            out = torch.empty(ncol, ncol, device=x.device, dtype=torch.float32)
+            beta = 0.0
+        extension().umma_syrk_conv(x, out, kh, kw, ph, pw, float(scale), float(beta), 0)
+        return out
     ld = _round_up(max(ncol, 8), 8)
     x3 = _use_x3(x.dtype)
     patches = torch.empty(n * ho * wo, ld, device=x.device, dtype=torch.bfloat16)

@@ -774,6 +774,48 @@ def test_general_matmul_and_psgd_dense_products():
     ops.check_status()
 
 
+@pytest.mark.parametrize('n,c,h,w,kh,kw,ph,pw', [(4, 64, 20, 20, 3, 3, 1, 1), (3, 128, 14, 14, 3, 3, 1, 1),
+                                                 (2, 64, 7, 7, 3, 3, 1, 1), (2, 64, 10, 13, 3, 2, 1, 0),
+                                                 (2, 192, 9, 9, 3, 3, 0, 0), (1, 64, 33, 17, 2, 3, 1, 2)])
+def test_implicit_im2col_syrk_matches_the_explicit_patch_matrix(ext, n, c, h, w, kh, kw, ph, pw):
+    """A factor of a stride-1 convolution gathered inside the SYRK by 4-D TMA boxes (padding, ragged image
+    edges, pixel blocks past the image) against the same product from the explicit bf16 patch matrix and
+    against fp64; alone, with a moving average, and inside a deferred batch."""
+    torch.manual_seed(0)
+    conv = nn.Conv2d(c, 8, (kh, kw), padding=(ph, pw)).to(DEV)
+    x = torch.randn(n, c, h, w, device=DEV).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    saved = ops.IMPLICIT_IM2COL
+    try:
+        ops.IMPLICIT_IM2COL = False
+        want = ops.conv_patch_gram(x, conv, scale=0.5, channels_last_order=True)
+        ops.IMPLICIT_IM2COL = True
+        before = ext.launch_count()
+        got = ops.conv_patch_gram(x, conv, scale=0.5, channels_last_order=True)
+        assert ext.launch_count() - before <= 2            # the SYRK (+ its split-K reduction), no im2col kernel
+        assert rel_err(got, want) < 1e-5 and torch.equal(got, got.T)
+        patches = F.unfold(x.float(), (kh, kw), padding=(ph, pw))                      # n x (c kh kw) x L, (c, kh, kw) order
+        patches = patches.view(n, c, kh * kw, -1).permute(0, 2, 1, 3).reshape(n, c * kh * kw, -1)
+        rows = patches.permute(0, 2, 1).reshape(-1, c * kh * kw).double()
+        assert rel_err(got, (0.5 * rows.T @ rows).float()) < 1e-5
+        # moving average into an existing factor, and the same product recorded in a deferred batch
+        acc = want.clone()
+        ops.conv_patch_gram(x, conv, scale=0.5, out=acc, beta=0.25, channels_last_order=True)
+        assert rel_err(acc, 1.25 * want) < 1e-5
+        out_b = torch.full_like(want, float('nan'))
+        other = torch.randn(300, 72, device=DEV).to(torch.bfloat16)
+        ext.gemm_batch_begin()
+        try:
+            ops.conv_patch_gram(x, conv, scale=0.5, out=out_b, channels_last_order=True)
+            g_other = ops.gram(other)
+        finally:
+            ext.gemm_batch_end()
+        assert rel_err(out_b, want) < 1e-5     # another split of the pixel range: another summation order
+        assert rel_err(g_other, other.float().T @ other.float()) < 1e-5
+    finally:
+        ops.IMPLICIT_IM2COL = saved
+    ops.check_status()
+
+
 def test_cta_pair_tiles_match_narrow_tiles(ext):
     """cta_group::2 flavour (256 x 256 tiles over two SMs) against the 128 x 128 flavour: even and odd
     counts of 128-row tiles, ragged edges, split-K, K-major operands, several segments, beta and the
