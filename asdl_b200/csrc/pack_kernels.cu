@@ -337,7 +337,8 @@ void im2col_bf16(at::Tensor x, at::Tensor out, c10::optional<at::Tensor> out_lo,
     lo_p = reinterpret_cast<__nv_bfloat16*>(out_lo->data_ptr());
   }
   const int threads = 256;
-  const bool vec = lo_p == nullptr && !c_major && x.scalar_type() == at::kBFloat16 && p.sC == 1 && (p.C % 8) == 0 &&
+  // with a single filter tap the (c, kh, kw) and (kh, kw, c) column orders are the same
+  const bool vec = lo_p == nullptr && (!c_major || p.KH * p.KW == 1) && x.scalar_type() == at::kBFloat16 && p.sC == 1 && (p.C % 8) == 0 &&
                    p.ldo == static_cast<long long>(p.C) * p.KH * p.KW && (p.sW % 8) == 0 &&
                    (p.sH % 8) == 0 && (p.sN % 8) == 0 &&
                    (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0;
