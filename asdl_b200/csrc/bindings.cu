@@ -73,8 +73,8 @@ void embedding_diag_stats(at::Tensor idx, at::Tensor g, at::Tensor out, int64_t 
 void embedding_counts(at::Tensor idx, at::Tensor counts);
 void bfgs_powell_damping(at::Tensor H, at::Tensor s, at::Tensor y, double mu1, double mu2);
 void bfgs_inv_update(at::Tensor H, at::Tensor s, at::Tensor y);
-void umma_syrk_conv(at::Tensor x, at::Tensor C, int64_t kh, int64_t kw, int64_t ph, int64_t pw, double alpha,
-                    double beta, int64_t nsplit_req);
+void umma_syrk_conv(at::Tensor x, c10::optional<at::Tensor> C, int64_t kh, int64_t kw, int64_t ph, int64_t pw,
+                    double alpha, double beta, int64_t nsplit_req, int64_t dst_ptr, int64_t ldc, int64_t mode);
 void gram_hadamard(std::vector<at::Tensor> a1, std::vector<at::Tensor> a2, std::vector<at::Tensor> g1,
                    std::vector<at::Tensor> g2, at::Tensor kernel, double alpha, double one);
 void diag_linear_stats(at::Tensor a, at::Tensor g, at::Tensor out, c10::optional<at::Tensor> out_bias, double alpha,
@@ -141,7 +141,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("bfgs_powell_damping", &b200::bfgs_powell_damping, "Powell damping + LM shift of a BFGS pair, in place");
   m.def("bfgs_inv_update", &b200::bfgs_inv_update, "symmetrise H and apply the rank-2 BFGS update of the inverse, in place");
   m.def("umma_syrk_conv", &b200::umma_syrk_conv,
-        "alpha * M^T M (+ beta * C) for the patch matrix M of a stride-1 convolution input, gathered by 4-d TMA boxes");
+        "alpha * M^T M (+ beta * C) for the patch matrix M of a stride-1 convolution input, gathered by 4-d TMA boxes",
+        py::arg("x"), py::arg("C"), py::arg("kh"), py::arg("kw"), py::arg("ph"), py::arg("pw"), py::arg("alpha"),
+        py::arg("beta"), py::arg("nsplit"), py::arg("dst_ptr") = 0, py::arg("ldc") = 0, py::arg("mode") = 0);
   m.def("gram_hadamard", &b200::gram_hadamard,
         "kernel += alpha * (A1 A2^T + one) o (G1 G2^T), both Gram tiles in TMEM, multiplied in the epilogue");
 }

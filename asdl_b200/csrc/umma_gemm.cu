@@ -443,8 +443,10 @@ void umma_gemm(std::vector<at::Tensor> a_segs, std::vector<at::Tensor> b_segs, b
 //   x: bf16 [n, c, h, w] in channels_last memory format (NHWC in memory), c a multiple of 64, kh * kw <= 12.
 // The producer warp gathers every operand tile with 4-D TMA boxes of x (see G2F_CONV in umma_gemm2.cuh); the
 // zero padding of the convolution and the output pixels past the image are TMA's out-of-bounds fill.
-void umma_syrk_conv(at::Tensor x, at::Tensor C, int64_t kh, int64_t kw, int64_t ph, int64_t pw, double alpha,
-                    double beta, int64_t nsplit_req) {
+// With `dst_ptr` != 0 the result goes to that raw device address with pitch `ldc` instead of `C` (a symmetric-memory
+// region); `mode` 3 stores the lower-triangular tiles only, 2 adds them with reductions (as in umma_gemm_to_ptr).
+void umma_syrk_conv(at::Tensor x, c10::optional<at::Tensor> C_opt, int64_t kh, int64_t kw, int64_t ph, int64_t pw,
+                    double alpha, double beta, int64_t nsplit_req, int64_t dst_ptr, int64_t ldc, int64_t mode) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 4 &&
                   x.is_contiguous(at::MemoryFormat::ChannelsLast),
               "x must be a 4-d channels_last bf16 CUDA tensor");
@@ -455,11 +457,24 @@ void umma_syrk_conv(at::Tensor x, at::Tensor C, int64_t kh, int64_t kw, int64_t 
   TORCH_CHECK(oh > ph && ow > pw && n >= 1, "the output must be larger than the padding");
   TORCH_CHECK((reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "x must be 16-byte aligned");
   const int64_t ncol = kh * kw * c;
-  TORCH_CHECK(C.is_cuda() && C.scalar_type() == at::kFloat && C.dim() == 2 && C.stride(1) == 1 && C.size(0) == ncol &&
-                  C.size(1) == ncol,
-              "C must be a [kh kw c, kh kw c] fp32 CUDA matrix with unit column stride");
-  TORCH_CHECK((reinterpret_cast<uintptr_t>(C.data_ptr()) & 15) == 0 || (C.stride(0) & 3) != 0,
-              "C must be 16-byte aligned when its row pitch is a multiple of four elements");
+  TORCH_CHECK((dst_ptr != 0) != C_opt.has_value(), "give either C or a destination address");
+  float* c_ptr = nullptr;
+  int64_t c_ld = 0;
+  if (C_opt.has_value()) {
+    const at::Tensor& C = *C_opt;
+    TORCH_CHECK(C.is_cuda() && C.scalar_type() == at::kFloat && C.dim() == 2 && C.stride(1) == 1 && C.size(0) == ncol &&
+                    C.size(1) == ncol,
+                "C must be a [kh kw c, kh kw c] fp32 CUDA matrix with unit column stride");
+    TORCH_CHECK(mode == 0, "lower-triangle modes write to a destination address");
+    c_ptr = C.data_ptr<float>();
+    c_ld = C.stride(0);
+  } else {
+    TORCH_CHECK(beta == 0.0 && (mode == 2 || mode == 3) && ldc >= ncol, "a destination address takes mode 2 or 3, beta 0 and ldc >= columns");
+    c_ptr = reinterpret_cast<float*>(dst_ptr);
+    c_ld = ldc;
+  }
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(c_ptr) & 15) == 0 || (c_ld & 3) != 0,
+              "the output must be 16-byte aligned when its row pitch is a multiple of four elements");
   const int dev = x.get_device();
   c10::cuda::CUDAGuard guard(dev);
   GemmProblem2 P;
@@ -504,10 +519,10 @@ void umma_syrk_conv(at::Tensor x, at::Tensor C, int64_t kh, int64_t kw, int64_t 
   P.nseg = 1;
   P.alpha = static_cast<float>(alpha);
   P.beta = static_cast<float>(beta);
-  P.flags = G2F_SYM | G2F_SAME_AB | G2F_CONV;
-  P.C = C.data_ptr<float>();
+  P.flags = G2F_SYM | G2F_SAME_AB | G2F_CONV | (mode == 2 ? G2F_ATOMIC : 0) | (mode >= 2 ? G2F_LOWER : 0);
+  P.C = c_ptr;
   P.Cin = P.C;
-  P.ldc = static_cast<int>(C.stride(0));
+  P.ldc = static_cast<int>(c_ld);
   P.conv_c = static_cast<int>(c);
   P.conv_kw = static_cast<int>(kw);
   P.conv_taps = static_cast<int>(kh * kw);
@@ -527,7 +542,7 @@ void umma_syrk_conv(at::Tensor x, at::Tensor C, int64_t kh, int64_t kw, int64_t 
   }
   P.nsplit = std::max(1, std::min(nsplit, kb_total));
   auto stream = at::cuda::getCurrentCUDAStream(dev).stream();
-  if (!batch_append(P, dev, nsplit_req, stream, {x}, {}, C)) {
+  if (!batch_append(P, dev, nsplit_req, stream, {x}, {}, C_opt)) {
     gemm_attach_scratch(P, dev, stream);
     gemm_launch_single(P, dev, stream);
   }

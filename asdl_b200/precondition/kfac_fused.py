@@ -770,6 +770,19 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             if (pointwise and t.dtype == torch.bfloat16 and c % 8 == 0
                     and t.is_contiguous(memory_format=torch.channels_last)):
                 segs_a = [t.permute(0, 2, 3, 1).reshape(-1, c)]
+            elif (ops.IMPLICIT_IM2COL and st.khwc and t.dtype == torch.bfloat16 and sh == sw == dh == dw == 1
+                  and c % 64 == 0 and kh * kw <= 12 and ph < kh and pw < kw and output.shape[-2] > ph
+                  and output.shape[-1] > pw and t.is_contiguous(memory_format=torch.channels_last)):
+                # no patch matrix: the SYRK's producer gathers its tiles from the input with 4-D TMA boxes
+                if self._pull_statistics():
+                    off = self._slots_off + st.owner * self._slot_stride + st.slot_rel[0]
+                    target = arena.ptr(self.world_rank, off)
+                else:
+                    off = self._slots_off + self.world_rank * self._slot_stride + st.slot_rel[0]
+                    target = arena.ptr(st.owner, off)
+                ext.umma_syrk_conv(t, None, kh, kw, ph, pw, float(scale), 0.0, 0, target, st.d_in,
+                                   2 if accumulate else 3)
+                return
             else:
                 rows = n * output.shape[-2] * output.shape[-1]
                 ncol = c * kh * kw

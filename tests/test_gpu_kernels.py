@@ -810,6 +810,13 @@ def test_implicit_im2col_syrk_matches_the_explicit_patch_matrix(ext, n, c, h, w,
         finally:
             ext.gemm_batch_end()
         assert rel_err(out_b, want) < 1e-5     # another split of the pixel range: another summation order
+        # the data-parallel statistics path: lower-triangular tiles stored to / added at a raw address
+        ncol = c * kh * kw
+        slot = torch.zeros(ncol, ncol, device=DEV)
+        ext.umma_syrk_conv(x, None, kh, kw, ph, pw, 0.5, 0.0, 0, slot.data_ptr(), ncol, 3)
+        assert rel_err(torch.tril(slot), torch.tril(want)) < 1e-5 and torch.triu(slot, 1).abs().max() == 0
+        ext.umma_syrk_conv(x, None, kh, kw, ph, pw, 0.5, 0.0, 0, slot.data_ptr(), ncol, 2)
+        assert rel_err(torch.tril(slot), 2 * torch.tril(want)) < 1e-5 and torch.triu(slot, 1).abs().max() == 0
         assert rel_err(g_other, other.float().T @ other.float()) < 1e-5
     finally:
         ops.IMPLICIT_IM2COL = saved
