@@ -350,6 +350,23 @@ def kron_apply(left: torch.Tensor, mid: torch.Tensor, right: torch.Tensor) -> to
 #: stride-1 convolutions on channels_last bf16 inputs with a multiple of 64 channels: gather the patch tiles
 #: inside the SYRK (4-D TMA boxes) instead of writing the patch matrix to memory first
 IMPLICIT_IM2COL = os.environ.get('ASDL_B200_IMPLICIT_IM2COL', '1') != '0'
+#: ... when the patch matrix would take at least this many MiB.  Measured on single layers (32 images): at 56 x 56 x 64
+#: channels (110 MiB of patches) the implicit SYRK takes the time of im2col + SYRK (0.128 vs 0.124 ms); on the small
+#: maps of deep layers (14 x 14 x 256: 28 MiB) the 4-D boxes of 2 x 2 pixels x 16 images load at half the rate of the
+#: 2-D boxes of an explicit matrix (0.144 vs 0.077 ms), so those keep the explicit path.
+IMPLICIT_IM2COL_MIN_MB = float(os.environ.get('ASDL_B200_IMPLICIT_IM2COL_MIN_MB', '64'))
+
+
+def implicit_im2col_eligible(x: torch.Tensor, kernel, stride, dilation, padding, out_hw, khwc_order: bool) -> bool:
+    """True when the input-side factor of this convolution is formed without a patch matrix (4-D TMA gather
+    inside the SYRK): stride 1, no dilation, channels_last bf16 input with a multiple of 64 channels, at most 12
+    filter taps, (kh, kw, c) column order, and a patch matrix large enough for the saved memory traffic to pay."""
+    (kh, kw), (sh, sw), (dh, dw), (ph, pw), (ho, wo) = kernel, stride, dilation, padding, out_hw
+    n, c = x.shape[0], x.shape[1]
+    return bool(IMPLICIT_IM2COL and khwc_order and x.is_cuda and x.dtype == torch.bfloat16 and not _use_x3(x.dtype)
+                and sh == sw == dh == dw == 1 and c % 64 == 0 and kh * kw <= 12 and ph < kh and pw < kw
+                and ho > ph and wo > pw and x.is_contiguous(memory_format=torch.channels_last)
+                and n * ho * wo * c * kh * kw * 2 >= IMPLICIT_IM2COL_MIN_MB * 2 ** 20)
 
 
 def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
@@ -360,8 +377,8 @@ def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
 
     ``channels_last_order=False`` orders rows/columns as (c, kh, kw) (matching
     ``weight.view(c_out, -1)``); ``True`` uses (kh, kw, c), the order of a channels_last weight.
-    CUDA: stride-1 convolutions on channels_last bf16 inputs with a multiple of 64 channels never form the
-    patch matrix - the SYRK's producer gathers 8 x 8 pixel blocks of one filter tap with 4-D TMA boxes, padding
+    CUDA: stride-1 convolutions on channels_last bf16 inputs with a multiple of 64 channels whose patch matrix
+    would take ``IMPLICIT_IM2COL_MIN_MB`` or more never form it - the SYRK's producer gathers 8 x 8 pixel blocks of one filter tap with 4-D TMA boxes, padding
     and image edges being TMA's zero fill (``IMPLICIT_IM2COL``); 1x1 stride-1 convolutions read the activations
     in place; everything else goes through a bf16 im2col kernel (vectorised for channels_last inputs).  fp32 inputs are
     staged as bf16 hi/lo patch pairs and multiplied in three passes (precision policy 'auto')."""
@@ -384,9 +401,7 @@ def conv_patch_gram(x: torch.Tensor, conv: torch.nn.Conv2d, scale: float = 1.0,
             and c % 8 == 0 and not _use_x3(x.dtype)):
         rows = x.permute(0, 2, 3, 1).reshape(n * h * w, c)  # a view: NHWC memory is already [rows, c]
         return gram(rows, scale=scale, out=out, beta=beta)
-    if (IMPLICIT_IM2COL and channels_last_order and x.dtype == torch.bfloat16 and not _use_x3(x.dtype)
-            and sh == sw == dh == dw == 1 and c % 64 == 0 and kh * kw <= 12 and ph < kh and pw < kw
-            and ho > ph and wo > pw and x.is_contiguous(memory_format=torch.channels_last)
+    if (implicit_im2col_eligible(x, (kh, kw), (sh, sw), (dh, dw), (ph, pw), (ho, wo), channels_last_order)
             and (out is None or (out.dtype == torch.float32 and out.stride(1) == 1))):
         # no patch matrix: the SYRK's producer gathers its operand tiles from x with 4-D TMA boxes
         if out is None:

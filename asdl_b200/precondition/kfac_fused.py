@@ -770,9 +770,7 @@ class FusedKfacGradientMaker(KfacGradientMaker):
             if (pointwise and t.dtype == torch.bfloat16 and c % 8 == 0
                     and t.is_contiguous(memory_format=torch.channels_last)):
                 segs_a = [t.permute(0, 2, 3, 1).reshape(-1, c)]
-            elif (ops.IMPLICIT_IM2COL and st.khwc and t.dtype == torch.bfloat16 and sh == sw == dh == dw == 1
-                  and c % 64 == 0 and kh * kw <= 12 and ph < kh and pw < kw and output.shape[-2] > ph
-                  and output.shape[-1] > pw and t.is_contiguous(memory_format=torch.channels_last)):
+            elif ops.implicit_im2col_eligible(t, (kh, kw), (sh, sw), (dh, dw), (ph, pw), output.shape[-2:], st.khwc):
                 # no patch matrix: the SYRK's producer gathers its tiles from the input with 4-D TMA boxes
                 if self._pull_statistics():
                     off = self._slots_off + st.owner * self._slot_stride + st.slot_rel[0]

@@ -191,6 +191,26 @@ def bench_lnstats(timer, rows, d, hbm, src):
          speedup_vs_torch=round(ms_lib / ms, 2))
 
 
+def bench_conv_syrk(timer, n, c, hw, k, flops_peak, src):
+    """Input-side factor of a stride-1 k x k convolution (padding k // 2) on a channels_last bf16 input: patches
+    gathered inside the SYRK by 4-D TMA boxes against the bf16 im2col kernel followed by the SYRK."""
+    conv = torch.nn.Conv2d(c, 8, k, padding=k // 2).cuda()
+    x = torch.randn(n, c, hw, hw, device='cuda').to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    ncol = c * k * k
+    out = torch.empty(ncol, ncol, device='cuda')
+    saved, saved_mb = ops.IMPLICIT_IM2COL, ops.IMPLICIT_IM2COL_MIN_MB
+    ops.IMPLICIT_IM2COL, ops.IMPLICIT_IM2COL_MIN_MB = True, 0.0
+    ms = timer(lambda: ops.conv_patch_gram(x, conv, out=out, channels_last_order=True))
+    ops.IMPLICIT_IM2COL = False
+    ms_explicit = timer(lambda: ops.conv_patch_gram(x, conv, out=out, channels_last_order=True))
+    ops.IMPLICIT_IM2COL, ops.IMPLICIT_IM2COL_MIN_MB = saved, saved_mb
+    fl = 2.0 * n * hw * hw * ncol * ncol
+    emit(case='conv_patch_syrk_bf16', n=n, c=c, hw=hw, k=k, ncol=ncol, implicit_ms=round(ms, 4),
+         explicit_im2col_ms=round(ms_explicit, 4), speedup=round(ms_explicit / ms, 2),
+         tflops_full_product=round(fl / ms / 1e9, 1), frac_of_peak_flops=round(fl / (ms * 1e-3) / flops_peak, 3),
+         patch_matrix_mb=round(n * hw * hw * ncol * 2 / 2 ** 20, 1), peak_source=src)
+
+
 def bench_gram_hadamard(timer, n, d_in, d_out, flops_peak, src):
     """kernel += (a a^T + 1) o (g g^T): both Gram tiles in TMEM, multiplied in the epilogue, against the
     PyTorch ops of the same update (two matmuls, an add, a multiply, an accumulate)."""
@@ -310,7 +330,7 @@ def bench_batchnorm(timer, n, c, hw, hbm, flops_peak, src):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--only', default=None, choices=['syrk', 'syrk_x3', 'layouts', 'precond', 'inverse', 'roots', 'eigh', 'lnstats', 'gram_hadamard', 'bfgs', 'embedding', 'symm', 'im2col', 'batchnorm'])
+    ap.add_argument('--only', default=None, choices=['syrk', 'syrk_x3', 'layouts', 'precond', 'inverse', 'roots', 'eigh', 'lnstats', 'conv_syrk', 'gram_hadamard', 'bfgs', 'embedding', 'symm', 'im2col', 'batchnorm'])
     ap.add_argument('--wide', type=int, default=-1, help='tile policy of the GEMM: -1 = default (3), 0 = 128 wide, 1 = 256 wide for large outputs, 2 = 256 wide wherever legal, 3 = CTA pairs (256 x 256, cta_group::2) for large products, 4 = CTA pairs everywhere')
     ap.add_argument('--chol', default=None, choices=['tensor_core', 'cuda_core'], help='grouped inverse backend')
     ap.add_argument('--rows', type=int, default=None)
@@ -357,6 +377,9 @@ def main():
     if want('lnstats'):
         for rows, d in [(8192, 1024), (12608, 768)]:
             bench_lnstats(timer, rows, d, hbm, src)
+    if want('conv_syrk'):
+        for n, c, hw in [(32, 64, 56), (32, 128, 28), (32, 256, 14), (32, 512, 7)]:
+            bench_conv_syrk(timer, n, c, hw, 3, fl, src)
     if want('gram_hadamard'):
         for n, d_in, d_out in [(2048, 4608, 512), (1024, 1024, 1024), (4096, 768, 3072)]:
             bench_gram_hadamard(timer, n, d_in, d_out, fl, src)

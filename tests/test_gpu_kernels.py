@@ -784,8 +784,9 @@ def test_implicit_im2col_syrk_matches_the_explicit_patch_matrix(ext, n, c, h, w,
     torch.manual_seed(0)
     conv = nn.Conv2d(c, 8, (kh, kw), padding=(ph, pw)).to(DEV)
     x = torch.randn(n, c, h, w, device=DEV).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
-    saved = ops.IMPLICIT_IM2COL
+    saved, saved_mb = ops.IMPLICIT_IM2COL, ops.IMPLICIT_IM2COL_MIN_MB
     try:
+        ops.IMPLICIT_IM2COL_MIN_MB = 0.0          # the size threshold is a speed policy: every eligible layer here
         ops.IMPLICIT_IM2COL = False
         want = ops.conv_patch_gram(x, conv, scale=0.5, channels_last_order=True)
         ops.IMPLICIT_IM2COL = True
@@ -819,7 +820,7 @@ def test_implicit_im2col_syrk_matches_the_explicit_patch_matrix(ext, n, c, h, w,
         assert rel_err(torch.tril(slot), 2 * torch.tril(want)) < 1e-5 and torch.triu(slot, 1).abs().max() == 0
         assert rel_err(g_other, other.float().T @ other.float()) < 1e-5
     finally:
-        ops.IMPLICIT_IM2COL = saved
+        ops.IMPLICIT_IM2COL, ops.IMPLICIT_IM2COL_MIN_MB = saved, saved_mb
     ops.check_status()
 
 

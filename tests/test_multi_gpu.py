@@ -96,7 +96,8 @@ def _train_resnet(dev, world, rank):
     sampled labels are per rank, so the check is that all ranks end up with the same gradients."""
     from asdl_b200.models import resnet_tiny
     torch.manual_seed(0)
-    # width 64: the 3 x 3 convolutions take the implicit-im2col statistics path (a multiple of 64 channels)
+    # width 64 and no size threshold: the 3 x 3 convolutions take the implicit-im2col statistics path
+    ops.IMPLICIT_IM2COL_MIN_MB = 0.0
     model = resnet_tiny(num_classes=10, width=64, fused=True).to(dev).to(memory_format=torch.channels_last)
     cfg = asdl.PreconditioningConfig(data_size=8, damping=1e-3, ema_decay=0.05,
                                      curvature_upd_interval=2, preconditioner_upd_interval=4)
