@@ -181,3 +181,17 @@ def test_general_matmul_gram_hadamard_and_small_statistics():
                 diag[idx[n, t]] += g[n, t] ** 2
     torch.testing.assert_close(EmbOp.cov_diag_weight(emb, idx, g), diag)
     torch.testing.assert_close(EmbOp.cov_kron_A(emb, idx), counts.T @ counts)
+
+
+def test_gpu_only_policies_fall_back_on_cpu():
+    """The tile policy, the implicit-im2col policy and the fused BatchNorm are CUDA paths: CPU tensors never
+    qualify, and the convolution factor of a CPU input equals the product of its explicit patch matrix."""
+    torch.manual_seed(0)
+    conv = nn.Conv2d(64, 4, 3, padding=1)
+    x = torch.randn(2, 64, 6, 6).to(memory_format=torch.channels_last)
+    assert not ops.implicit_im2col_eligible(x.bfloat16(), (3, 3), (1, 1), (1, 1), (1, 1), (6, 6), True)
+    assert not ops.batch_norm_train_supported(x.bfloat16(), torch.ones(64), torch.zeros(64))
+    got = ops.conv_patch_gram(x, conv, scale=0.5, channels_last_order=True)
+    patches = F.unfold(x, 3, padding=1).view(2, 64, 9, -1).permute(0, 2, 1, 3).reshape(2, 64 * 9, -1)
+    rows = patches.permute(0, 2, 1).reshape(-1, 64 * 9)
+    torch.testing.assert_close(got, 0.5 * rows.T @ rows, rtol=1e-4, atol=1e-4)
