@@ -1,4 +1,4 @@
-// Batched symmetric eigendecomposition of small fp32 matrices (n <= 128) by the parallel cyclic
+// Batched symmetric eigendecomposition of small fp32 matrices (n <= 160) by the parallel cyclic
 // two-sided Jacobi method, one CTA per matrix, everything in shared memory:
 //     A = V diag(w) V^T,   w ascending (the convention of torch.linalg.eigh).
 // A round rotates n/2 disjoint index pairs at once (round-robin tournament ordering, n - 1 rounds
@@ -17,7 +17,7 @@ namespace b200 {
 
 namespace {
 
-constexpr int JN = 128;         // largest matrix
+constexpr int JN = 160;         // largest matrix: A and V (two (JN x (JN + 1)) fp32 arrays) fill 205 of the 227 KB of shared memory
 constexpr int JP = JN + 1;      // shared-memory row pitch
 constexpr int J_THREADS = 512;
 constexpr int J_SMEM = (2 * JN * JP + 4 * JN) * static_cast<int>(sizeof(float)) + 2 * JN * static_cast<int>(sizeof(int));
@@ -166,7 +166,7 @@ jacobi_eigh_kernel(const float* __restrict__ mats, float* __restrict__ evals, fl
 
 }  // namespace
 
-// mats: [batch, n, n] fp32 contiguous (n <= 128); returns (eigenvalues [batch, n] ascending, eigenvectors
+// mats: [batch, n, n] fp32 contiguous (n <= 160); returns (eigenvalues [batch, n] ascending, eigenvectors
 // [batch, n, n] as columns, or an empty tensor when `want_vectors` is false).
 std::vector<at::Tensor> jacobi_eigh(at::Tensor mats, bool want_vectors) {
   TORCH_CHECK(mats.is_cuda() && mats.scalar_type() == at::kFloat && mats.dim() == 3 && mats.size(1) == mats.size(2) &&

@@ -661,7 +661,7 @@ def layer_norm(x, weight, bias, eps=1e-5):
 
 
 #: largest matrix the Jacobi eigensolver kernel takes (it keeps the matrix and the vectors in shared memory)
-JACOBI_MAX_N = 128
+JACOBI_MAX_N = 160
 
 
 def _jacobi_ok(mat: torch.Tensor) -> bool:
@@ -671,7 +671,7 @@ def _jacobi_ok(mat: torch.Tensor) -> bool:
 
 def eigh(mat: torch.Tensor):
     """``(eigenvalues ascending, eigenvectors as columns)`` of a symmetric matrix or a batch of them.
-    CUDA fp32 up to 128 x 128: the library's batched parallel-Jacobi kernel (one CTA per matrix, the
+    CUDA fp32 up to 160 x 160: the library's batched parallel-Jacobi kernel (one CTA per matrix, the
     input is symmetrised on load); anything else: ``torch.linalg.eigh``."""
     if _jacobi_ok(mat):
         batched = mat.ndim == 3

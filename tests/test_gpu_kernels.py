@@ -1027,7 +1027,7 @@ def test_fused_kfac_fisher_variants_and_reused_layer_match_cpu(fisher, loss):
     ops.check_status()
 
 
-@pytest.mark.parametrize('n,batch', [(1, 2), (2, 3), (7, 2), (64, 4), (100, 2), (127, 1), (128, 2)])
+@pytest.mark.parametrize('n,batch', [(1, 2), (2, 3), (7, 2), (64, 4), (100, 2), (127, 1), (128, 2), (160, 2)])
 def test_jacobi_eigh_kernel(ext, n, batch):
     """Batched Jacobi eigensolver against float64 torch.linalg.eigh: eigenvalues, residual and
     orthogonality, on matrices with eigenvalues spread over eight decades."""
