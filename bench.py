@@ -462,7 +462,12 @@ def main():
                        'curvature_upd_interval': 10, 'preconditioner_upd_interval': 100,
                        'ema_decay': 0.05, 'fisher': 'mc', 'optimizer': 'sgd(momentum=0.9) step included',
                        'l2': 'flushed every step by a 256 MiB memset; per-step activations exceed L2',
-                       'cuda_graph': (not args.no_graph) if args.impl == 'ours' else False},
+                       'cuda_graph': (not args.no_graph) if args.impl == 'ours' else False,
+                       'e2e_loop': 'every batch copied from pinned memory into one of two static device buffers on a '
+                                   'copy stream; every loss copied to pinned memory and read one step later',
+                       **({'transport': ('nvlink symmetric memory: statistics pulled by the owners, gradients pull-reduced, '
+                                         'preconditioned gradients broadcast; no NCCL call inside a step')}
+                          if args.impl == 'ours' and world > 1 else {})},
             'e2e': {'value': round(e2e_value, 2), 'unit': 'images/s',
                     'ms_per_step': round(e2e_ms / args.steps, 3),
                     'h2d_bytes_per_step': h2d // args.steps, 'd2h_bytes_per_step': d2h // args.steps,
